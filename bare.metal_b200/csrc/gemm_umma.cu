@@ -1,0 +1,400 @@
+// Persistent, warp-specialised tcgen05 GEMM. See gemm_umma.cuh for the operand convention.
+//
+// CTA = 192 threads: warp 0 = TMA producer, warp 1 = TMEM owner + UMMA issuer,
+// warps 2..5 = epilogue (warp w reads TMEM lanes 32*(w&3) .. +31).
+// Tile = 128 (M) x tile_n (N, <= 256) x 64 (K per stage), 4-stage shared-memory ring,
+// two TMEM accumulator buffers of 256 fp32 columns so the epilogue of tile i overlaps the
+// main loop of tile i+1. One CTA per SM; work units (tile, k-split) are dealt round-robin.
+#include "gemm_umma.cuh"
+
+#include <cuda.h>
+#include <stdio.h>
+
+#include <atomic>
+
+#include "ptx_sm100.cuh"
+
+namespace bmb {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int STAGES = 4;
+constexpr int MAX_BN = 256;
+constexpr int A_STAGE_BYTES = BM * BK * 2;      // 16 KB
+constexpr int B_STAGE_BYTES = MAX_BN * BK * 2;  // 32 KB
+constexpr int MN_BOX_BYTES = 64 * BK * 2;       // one 64(mn) x 64(k) box of an MN-major operand
+constexpr int NUM_THREADS = 192;
+constexpr int SMEM_DYN_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 1024;
+constexpr uint32_t TMEM_COLS = 512;
+
+struct KArgs {
+    int M, N, K;
+    int BN;
+    int a_mn, b_mn;
+    int tiles_m, tiles_n, splits, kb_total, kb_per_split;
+    void* C;
+    int ldc;
+    int out_mode;
+    const __nv_bfloat16* R;
+    int ldr;
+    int* err;
+};
+
+struct __align__(8) Barriers {
+    uint64_t full[STAGES];
+    uint64_t empty[STAGES];
+    uint64_t acc_full[2];
+    uint64_t acc_empty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+__device__ __forceinline__ void decode_unit(const KArgs& p, int u, int& m0, int& n0, int& kb0, int& kb1) {
+    const int ntiles = p.tiles_m * p.tiles_n;
+    const int split = u / ntiles;
+    const int tile = u - split * ntiles;
+    const int tm = tile / p.tiles_n;
+    const int tn = tile - tm * p.tiles_n;
+    m0 = tm * BM;
+    n0 = tn * p.BN;
+    kb0 = split * p.kb_per_split;
+    kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                      const KArgs p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ Barriers bars;
+
+    // 1024-byte alignment: the 128B swizzle pattern is a function of address bits [7,10).
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* sA = smem;
+    uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int units = p.tiles_m * p.tiles_n * p.splits;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&bars.full[s], 1);
+            mbar_init(&bars.empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&bars.acc_full[b], 1);
+            mbar_init(&bars.acc_empty[b], 4);
+        }
+        bars.abort_flag = 0;
+        mbar_fence_init();
+        fence_proxy_async_smem();
+    }
+    if (warp == 1) {
+        tmem_alloc(&bars.tmem_base, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = bars.tmem_base;
+    volatile int* abort_flag = &bars.abort_flag;
+
+    const uint32_t stage_tx_bytes = (uint32_t)(BM * BK * 2 + p.BN * BK * 2);
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            tma_prefetch_desc(&tmA);
+            tma_prefetch_desc(&tmB);
+            uint32_t c = 0;  // k-block counter across all of this CTA's units
+            bool ok = true;
+            for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+                int m0, n0, kb0, kb1;
+                decode_unit(p, u, m0, n0, kb0, kb1);
+                for (int kb = kb0; kb < kb1; ++kb, ++c) {
+                    const int s = c % STAGES;
+                    const uint32_t ph = (c / STAGES) & 1;
+                    if (!mbar_wait(&bars.empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
+                    mbar_expect_tx(&bars.full[s], stage_tx_bytes);
+                    uint8_t* a_dst = sA + s * A_STAGE_BYTES;
+                    uint8_t* b_dst = sB + s * B_STAGE_BYTES;
+                    const int k0 = kb * BK;
+                    if (!p.a_mn) {
+                        tma_load_2d(a_dst, &tmA, &bars.full[s], k0, m0);
+                    } else {
+                        tma_load_2d(a_dst, &tmA, &bars.full[s], m0, k0);
+                        tma_load_2d(a_dst + MN_BOX_BYTES, &tmA, &bars.full[s], m0 + 64, k0);
+                    }
+                    if (!p.b_mn) {
+                        tma_load_2d(b_dst, &tmB, &bars.full[s], k0, n0);
+                    } else {
+                        for (int j = 0; j < p.BN / 64; ++j)
+                            tma_load_2d(b_dst + j * MN_BOX_BYTES, &tmB, &bars.full[s], n0 + 64 * j, k0);
+                    }
+                }
+            }
+            // Tail: do not let the CTA retire while UMMA commits may still arrive on `empty`.
+            for (int i = 0; i < STAGES && ok; ++i, ++c) {
+                const int s = c % STAGES;
+                const uint32_t ph = (c / STAGES) & 1;
+                if (!mbar_wait(&bars.empty[s], ph ^ 1, abort_flag)) ok = false;
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ UMMA issuer --------------------------------
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc_bf16_f32(BM, p.BN, p.a_mn, p.b_mn);
+            // K-major operand: rows of 128 B, 8-row swizzle atoms 1024 B apart; one UMMA (K=16) = 32 B along the row.
+            // MN-major operand: 64(mn) x 64(k) boxes of 8 KB; 8-deep k groups 1024 B apart inside a box,
+            // 64-wide mn groups one box apart; one UMMA (K=16) = two k groups = 2048 B.
+            const uint32_t a_lbo = p.a_mn ? MN_BOX_BYTES : 16, a_sbo = 1024, a_kstep = p.a_mn ? 2048 : 32;
+            const uint32_t b_lbo = p.b_mn ? MN_BOX_BYTES : 16, b_sbo = 1024, b_kstep = p.b_mn ? 2048 : 32;
+            uint32_t c = 0;
+            int it = 0;
+            bool ok = true;
+            for (int u = blockIdx.x; u < units && ok; u += gridDim.x, ++it) {
+                int m0, n0, kb0, kb1;
+                decode_unit(p, u, m0, n0, kb0, kb1);
+                const int buf = it & 1;
+                const uint32_t acc_ph = (it >> 1) & 1;
+                if (!mbar_wait(&bars.acc_empty[buf], acc_ph ^ 1, abort_flag)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t tmem_acc = tmem_base + (uint32_t)buf * MAX_BN;
+                for (int kb = kb0; kb < kb1; ++kb, ++c) {
+                    const int s = c % STAGES;
+                    const uint32_t ph = (c / STAGES) & 1;
+                    if (!mbar_wait(&bars.full[s], ph, abort_flag)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t a_addr = smem_u32(sA + s * A_STAGE_BYTES);
+                    const uint32_t b_addr = smem_u32(sB + s * B_STAGE_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) {
+                        const uint64_t ad = umma_smem_desc_sw128(a_addr + k * a_kstep, a_lbo, a_sbo);
+                        const uint64_t bd = umma_smem_desc_sw128(b_addr + k * b_kstep, b_lbo, b_sbo);
+                        umma_bf16_ss(tmem_acc, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&bars.empty[s]);  // releases the stage once these UMMAs have read it
+                }
+                if (ok) umma_commit(&bars.acc_full[buf]);
+            }
+        }
+    } else {
+        // ------------------------------ epilogue -----------------------------------
+        const int q = warp & 3;
+        int it = 0;
+        bool ok = true;
+        for (int u = blockIdx.x; u < units && ok; u += gridDim.x, ++it) {
+            int m0, n0, kb0, kb1;
+            decode_unit(p, u, m0, n0, kb0, kb1);
+            const int buf = it & 1;
+            const uint32_t acc_ph = (it >> 1) & 1;
+            ok = mbar_wait(&bars.acc_full[buf], acc_ph, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld is warp-collective: leave together or not at all
+            if (!ok) break;
+            tc_fence_after_sync();
+            const int row = m0 + q * 32 + lane;
+            const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)buf * MAX_BN;
+            for (int ch = 0; ch < p.BN / 32; ++ch) {
+                uint32_t r[32];
+                tmem_ld_32x32(taddr0 + ch * 32, r);
+                tmem_ld_wait();
+                const int col0 = n0 + ch * 32;
+                if (row < p.M && col0 < p.N) {
+                    const int ncols = min(32, p.N - col0);
+                    if (p.out_mode == GEMM_OUT_BF16) {
+                        __nv_bfloat16* crow = (__nv_bfloat16*)p.C + (size_t)row * p.ldc + col0;
+                        const __nv_bfloat16* rrow = p.R ? p.R + (size_t)row * p.ldr + col0 : nullptr;
+                        const bool vec = (ncols == 32) && ((((uintptr_t)crow) & 15) == 0) &&
+                                         (!rrow || (((uintptr_t)rrow) & 15) == 0);
+                        if (vec) {
+#pragma unroll
+                            for (int v = 0; v < 4; ++v) {
+                                float f[8];
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(r[v * 8 + i]);
+                                if (rrow) {
+                                    const uint4 rv = *(const uint4*)(rrow + v * 8);
+                                    const __nv_bfloat162* rb = (const __nv_bfloat162*)&rv;
+#pragma unroll
+                                    for (int i = 0; i < 4; ++i) {
+                                        const float2 t = __bfloat1622float2(rb[i]);
+                                        f[2 * i] += t.x;
+                                        f[2 * i + 1] += t.y;
+                                    }
+                                }
+                                uint4 o;
+                                __nv_bfloat162* ob = (__nv_bfloat162*)&o;
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) ob[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+                                *(uint4*)(crow + v * 8) = o;
+                            }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) {
+                                if (i < ncols) {
+                                    float f = __uint_as_float(r[i]);
+                                    if (rrow) f += __bfloat162float(rrow[i]);
+                                    crow[i] = __float2bfloat16_rn(f);
+                                }
+                            }
+                        }
+                    } else if (p.out_mode == GEMM_OUT_F32) {
+                        float* crow = (float*)p.C + (size_t)row * p.ldc + col0;
+                        const bool vec = (ncols == 32) && ((((uintptr_t)crow) & 15) == 0);
+                        if (vec) {
+#pragma unroll
+                            for (int v = 0; v < 8; ++v)
+                                *(uint4*)(crow + v * 4) = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (i < ncols) crow[i] = __uint_as_float(r[i]);
+                        }
+                    } else {
+                        float* crow = (float*)p.C + (size_t)row * p.ldc + col0;
+                        const bool vec = (ncols == 32) && ((((uintptr_t)crow) & 15) == 0);
+                        if (vec) {
+#pragma unroll
+                            for (int v = 0; v < 8; ++v)
+                                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(crow + v * 4),
+                                             "f"(__uint_as_float(r[v * 4])), "f"(__uint_as_float(r[v * 4 + 1])),
+                                             "f"(__uint_as_float(r[v * 4 + 2])), "f"(__uint_as_float(r[v * 4 + 3]))
+                                             : "memory");
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (i < ncols) atomicAdd(crow + i, __uint_as_float(r[i]));
+                        }
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars.acc_empty[buf]);
+        }
+    }
+
+    // ------------------------------ teardown ---------------------------------------
+    __syncwarp();
+    if (*abort_flag) {
+        // A wait ran out: give copies and UMMAs still in flight time to land before the
+        // shared memory and TMEM they target are released.
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 2000000ull) __nanosleep(1000);
+        if (threadIdx.x == 0 && p.err) atomicExch(p.err, 1000 + (int)blockIdx.x);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// 2-D bf16 tensor map with 128B swizzle. inner/outer extents in elements, row pitch `ld` in elements.
+int make_map(CUtensorMap* tm, const void* base, uint64_t inner, uint64_t outer, uint64_t ld, uint32_t box_inner,
+             uint32_t box_outer) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return -10;
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {ld * 2};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)base, dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : -11;
+}
+
+int choose_tile_n(int N, int b_mn) {
+    const int step = b_mn ? 64 : 32;
+    int best = 64;
+    double best_cost = 1e30;
+    for (int bn = 64; bn <= MAX_BN; bn += step) {
+        const double padded = (double)((N + bn - 1) / bn) * bn;
+        const double cost = padded * (1.0 + 24.0 / bn);
+        if (cost < best_cost - 1e-9 || (cost < best_cost + 1e-9 && bn > best)) {
+            best_cost = cost;
+            best = bn;
+        }
+    }
+    return best;
+}
+
+std::atomic<long> g_launches{0};
+int g_num_sms = 0;
+
+}  // namespace
+
+long gemm_bf16_umma_launch_count() { return g_launches.load(); }
+
+int gemm_bf16_umma(const GemmProblem& g, int* err_flag, cudaStream_t stream) {
+    if (g.M <= 0 || g.N <= 0 || g.K <= 0) return -1;
+    if ((g.lda % 8) || (g.ldb % 8)) return -2;  // TMA: row pitch must be a multiple of 16 bytes
+    if ((((uintptr_t)g.A) & 15) || (((uintptr_t)g.B) & 15)) return -3;
+    if (g.splits > 1 && g.out_mode != GEMM_OUT_F32_ATOMIC) return -4;
+
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             SMEM_DYN_BYTES);
+        if (e != cudaSuccess) return -5;
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+        attr_done = true;
+    }
+
+    KArgs p;
+    p.M = g.M; p.N = g.N; p.K = g.K;
+    p.BN = g.tile_n > 0 ? g.tile_n : choose_tile_n(g.N, g.b_mn_major);
+    if (p.BN < 32 || p.BN > MAX_BN || (p.BN % 32) || (g.b_mn_major && (p.BN % 64))) return -6;
+    p.a_mn = g.a_mn_major ? 1 : 0;
+    p.b_mn = g.b_mn_major ? 1 : 0;
+    p.tiles_m = (g.M + BM - 1) / BM;
+    p.tiles_n = (g.N + p.BN - 1) / p.BN;
+    p.kb_total = (g.K + BK - 1) / BK;
+    int splits = g.splits > 0 ? g.splits : 1;
+    if (splits > p.kb_total) splits = p.kb_total;
+    p.kb_per_split = (p.kb_total + splits - 1) / splits;
+    p.splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;
+    p.C = g.C; p.ldc = g.ldc; p.out_mode = g.out_mode;
+    p.R = g.R; p.ldr = g.ldr;
+    p.err = err_flag;
+
+    CUtensorMap tmA, tmB;
+    int rc;
+    if (!p.a_mn) rc = make_map(&tmA, g.A, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda, BK, BM);
+    else         rc = make_map(&tmA, g.A, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)g.lda, 64, BK);
+    if (rc) return rc;
+    if (!p.b_mn) rc = make_map(&tmB, g.B, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb, BK, (uint32_t)p.BN);
+    else         rc = make_map(&tmB, g.B, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb, 64, BK);
+    if (rc) return rc;
+
+    const long units = (long)p.tiles_m * p.tiles_n * p.splits;
+    const int grid = (int)(units < g_num_sms ? units : g_num_sms);
+    gemm_bf16_umma_kernel<<<grid, NUM_THREADS, SMEM_DYN_BYTES, stream>>>(tmA, tmB, p);
+    g_launches.fetch_add(1);
+    return cudaGetLastError() == cudaSuccess ? 0 : -7;
+}
+
+}  // namespace bmb
