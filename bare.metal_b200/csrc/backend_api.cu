@@ -1,0 +1,405 @@
+// extern "C" surface of the CUDA backend (include/bm_cuda_backend.h): context, memory, and one
+// typed entry point per operation of the training step. Each entry point validates its
+// arguments, picks the kernel for the activation dtype and enqueues it on the context's stream.
+#include "../../include/bm_cuda_backend.h"
+
+#include <stdio.h>
+#include <stdlib.h>
+
+#include <map>
+#include <mutex>
+
+#include "attention_mma.cuh"
+#include "gemm_umma.cuh"
+#include "kernels.cuh"
+
+using namespace bmb;
+
+struct bmc_ctx_s {
+    int device;
+    cudaStream_t stream;
+    int* d_err;  // set by kernels whose bounded waits ran out
+    int sticky_status;
+    size_t allocated, peak;
+    std::map<void*, size_t> allocs;
+    std::mutex mu;
+    long launches;
+    int num_sms;
+    // scratch owned by the context
+    float* rms_scratch;
+    size_t rms_scratch_floats;
+    void* attn_scratch;
+    size_t attn_scratch_bytes;
+    cudaEvent_t ev0[8], ev1[8];
+};
+
+namespace {
+
+#define BMC_CHECK_CTX(ctx) \
+    if (!(ctx)) return -100;
+
+int note(bmc_ctx_t* ctx, int rc, int nlaunch = 1) {
+    if (rc == 0) {
+        ctx->launches += nlaunch;
+        cudaError_t e = cudaPeekAtLastError();
+        if (e != cudaSuccess) {
+            ctx->sticky_status = -200 - (int)e;
+            return ctx->sticky_status;
+        }
+    }
+    return rc;
+}
+
+void* scratch_get(bmc_ctx_t* ctx, void** slot, size_t* cap, size_t bytes) {
+    if (*cap >= bytes) return *slot;
+    if (*slot) {
+        cudaStreamSynchronize(ctx->stream);
+        cudaFree(*slot);
+        *slot = nullptr;
+        *cap = 0;
+    }
+    if (cudaMalloc(slot, bytes) != cudaSuccess) return nullptr;
+    *cap = bytes;
+    return *slot;
+}
+
+}  // namespace
+
+extern "C" {
+
+bmc_ctx_t* bmc_create(int device_ordinal) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n <= 0 || device_ordinal < 0 || device_ordinal >= n) {
+        fprintf(stderr, "bmc_create: no usable CUDA device (count=%d, requested=%d); this backend has no CPU fallback\n", n,
+                device_ordinal);
+        return nullptr;
+    }
+    if (cudaSetDevice(device_ordinal) != cudaSuccess) return nullptr;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device_ordinal) != cudaSuccess) return nullptr;
+    if (prop.major != 10) {
+        fprintf(stderr, "bmc_create: device %d is sm_%d%d; this backend is built for sm_100a only\n", device_ordinal, prop.major,
+                prop.minor);
+        return nullptr;
+    }
+    bmc_ctx_t* ctx = new bmc_ctx_s();
+    ctx->device = device_ordinal;
+    ctx->num_sms = prop.multiProcessorCount;
+    ctx->sticky_status = 0;
+    ctx->allocated = ctx->peak = 0;
+    ctx->launches = 0;
+    ctx->rms_scratch = nullptr;
+    ctx->rms_scratch_floats = 0;
+    ctx->attn_scratch = nullptr;
+    ctx->attn_scratch_bytes = 0;
+    if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) { delete ctx; return nullptr; }
+    if (cudaMalloc(&ctx->d_err, sizeof(int)) != cudaSuccess) { delete ctx; return nullptr; }
+    cudaMemset(ctx->d_err, 0, sizeof(int));
+    for (int i = 0; i < 8; ++i) {
+        cudaEventCreate(&ctx->ev0[i]);
+        cudaEventCreate(&ctx->ev1[i]);
+    }
+    return ctx;
+}
+
+void bmc_destroy(bmc_ctx_t* ctx) {
+    if (!ctx) return;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    for (auto& kv : ctx->allocs) cudaFree(kv.first);
+    if (ctx->rms_scratch) cudaFree(ctx->rms_scratch);
+    if (ctx->attn_scratch) cudaFree(ctx->attn_scratch);
+    cudaFree(ctx->d_err);
+    for (int i = 0; i < 8; ++i) {
+        cudaEventDestroy(ctx->ev0[i]);
+        cudaEventDestroy(ctx->ev1[i]);
+    }
+    cudaStreamDestroy(ctx->stream);
+    delete ctx;
+}
+
+void* bmc_alloc(bmc_ctx_t* ctx, size_t bytes) {
+    if (!ctx || bytes == 0) return nullptr;
+    void* p = nullptr;
+    if (cudaMalloc(&p, bytes) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    ctx->allocs[p] = bytes;
+    ctx->allocated += bytes;
+    if (ctx->allocated > ctx->peak) ctx->peak = ctx->allocated;
+    return p;
+}
+void bmc_free(bmc_ctx_t* ctx, void* p) {
+    if (!ctx || !p) return;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    auto it = ctx->allocs.find(p);
+    if (it == ctx->allocs.end()) return;
+    ctx->allocated -= it->second;
+    ctx->allocs.erase(it);
+    cudaStreamSynchronize(ctx->stream);
+    cudaFree(p);
+}
+size_t bmc_allocated_bytes(bmc_ctx_t* ctx) { return ctx ? ctx->allocated : 0; }
+size_t bmc_peak_allocated_bytes(bmc_ctx_t* ctx) { return ctx ? ctx->peak : 0; }
+
+int bmc_upload(bmc_ctx_t* ctx, void* d_dst, const void* h_src, size_t bytes) {
+    BMC_CHECK_CTX(ctx);
+    return cudaMemcpyAsync(d_dst, h_src, bytes, cudaMemcpyHostToDevice, ctx->stream) == cudaSuccess ? 0 : -1;
+}
+int bmc_download(bmc_ctx_t* ctx, void* h_dst, const void* d_src, size_t bytes) {
+    BMC_CHECK_CTX(ctx);
+    if (cudaMemcpyAsync(h_dst, d_src, bytes, cudaMemcpyDeviceToHost, ctx->stream) != cudaSuccess) return -1;
+    return cudaStreamSynchronize(ctx->stream) == cudaSuccess ? 0 : -2;
+}
+int bmc_memset(bmc_ctx_t* ctx, void* d_ptr, int byte_value, size_t bytes) {
+    BMC_CHECK_CTX(ctx);
+    return cudaMemsetAsync(d_ptr, byte_value, bytes, ctx->stream) == cudaSuccess ? 0 : -1;
+}
+int bmc_copy(bmc_ctx_t* ctx, void* d_dst, const void* d_src, size_t bytes) {
+    BMC_CHECK_CTX(ctx);
+    return cudaMemcpyAsync(d_dst, d_src, bytes, cudaMemcpyDeviceToDevice, ctx->stream) == cudaSuccess ? 0 : -1;
+}
+int bmc_status(bmc_ctx_t* ctx) {
+    BMC_CHECK_CTX(ctx);
+    if (ctx->sticky_status) return ctx->sticky_status;
+    int h = 0;
+    if (cudaMemcpyAsync(&h, ctx->d_err, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream) != cudaSuccess) return -3;
+    cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) {
+        ctx->sticky_status = -200 - (int)e;
+        return ctx->sticky_status;
+    }
+    if (h) {
+        cudaMemsetAsync(ctx->d_err, 0, sizeof(int), ctx->stream);
+        return h;
+    }
+    return 0;
+}
+int bmc_sync(bmc_ctx_t* ctx) {
+    BMC_CHECK_CTX(ctx);
+    cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) {
+        ctx->sticky_status = -200 - (int)e;
+        return ctx->sticky_status;
+    }
+    return bmc_status(ctx);
+}
+void* bmc_stream(bmc_ctx_t* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
+long bmc_launch_count(bmc_ctx_t* ctx) { return ctx ? ctx->launches : 0; }
+void* bmc_host_alloc(size_t bytes) {
+    void* p = nullptr;
+    if (cudaMallocHost(&p, bytes) != cudaSuccess) return nullptr;
+    return p;
+}
+void bmc_host_free(void* p) {
+    if (p) cudaFreeHost(p);
+}
+int bmc_timer_begin(bmc_ctx_t* ctx, int slot) {
+    BMC_CHECK_CTX(ctx);
+    if (slot < 0 || slot >= 8) return -1;
+    return cudaEventRecord(ctx->ev0[slot], ctx->stream) == cudaSuccess ? 0 : -2;
+}
+float bmc_timer_end(bmc_ctx_t* ctx, int slot) {
+    if (!ctx || slot < 0 || slot >= 8) return -1.f;
+    cudaEventRecord(ctx->ev1[slot], ctx->stream);
+    cudaEventSynchronize(ctx->ev1[slot]);
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, ctx->ev0[slot], ctx->ev1[slot]);
+    return ms;
+}
+
+// ---- embedding ---------------------------------------------------------------------------------------
+int bmc_embedding_forward(bmc_ctx_t* ctx, int dtype, void* d_out, const float* d_table, const int* d_tokens, int n_tok, int D) {
+    BMC_CHECK_CTX(ctx);
+    if (dtype == BMC_F32) return note(ctx, embedding_forward<float>((float*)d_out, d_table, d_tokens, n_tok, D, ctx->stream));
+    return note(ctx, embedding_forward<bf16>((bf16*)d_out, d_table, d_tokens, n_tok, D, ctx->stream));
+}
+int bmc_embedding_backward(bmc_ctx_t* ctx, int dtype, float* d_gwte, const void* d_gout, const int* d_tokens, int n_tok, int D) {
+    BMC_CHECK_CTX(ctx);
+    if (dtype == BMC_F32) return note(ctx, embedding_backward_f32(d_gwte, (const float*)d_gout, d_tokens, n_tok, D, ctx->stream));
+    return note(ctx, embedding_backward_bf16(d_gwte, (const bf16*)d_gout, d_tokens, n_tok, D, ctx->stream));
+}
+
+// ---- RMSNorm -----------------------------------------------------------------------------------------
+int bmc_rmsnorm_forward(bmc_ctx_t* ctx, int dtype, void* d_out, float* d_rstd, const void* d_x, const float* d_w, int N, int C, float eps) {
+    BMC_CHECK_CTX(ctx);
+    if (dtype == BMC_F32) return note(ctx, rmsnorm_forward<float>((float*)d_out, d_rstd, (const float*)d_x, d_w, N, C, eps, ctx->stream));
+    return note(ctx, rmsnorm_forward<bf16>((bf16*)d_out, d_rstd, (const bf16*)d_x, d_w, N, C, eps, ctx->stream));
+}
+int bmc_rmsnorm_backward(bmc_ctx_t* ctx, int dtype, void* d_gx, float* d_gw, int gw_accumulate, const void* d_gout, const void* d_x,
+                         const float* d_w, const float* d_rstd, int N, int C, int w_row0, int w_row1) {
+    BMC_CHECK_CTX(ctx);
+    const size_t need = rmsnorm_backward_scratch_floats(C);
+    size_t cap_bytes = ctx->rms_scratch_floats * sizeof(float);
+    float* scratch = (float*)scratch_get(ctx, (void**)&ctx->rms_scratch, &cap_bytes, need * sizeof(float));
+    ctx->rms_scratch_floats = cap_bytes / sizeof(float);
+    if (!scratch) return -50;
+    if (dtype == BMC_F32)
+        return note(ctx, rmsnorm_backward<float>((float*)d_gx, d_gw, gw_accumulate, (const float*)d_gout, (const float*)d_x, d_w, d_rstd, N,
+                                                 C, w_row0, w_row1, scratch, ctx->stream), 2);
+    return note(ctx, rmsnorm_backward<bf16>((bf16*)d_gx, d_gw, gw_accumulate, (const bf16*)d_gout, (const bf16*)d_x, d_w, d_rstd, N, C,
+                                            w_row0, w_row1, scratch, ctx->stream), 2);
+}
+
+// ---- linear layers -----------------------------------------------------------------------------------
+int bmc_matmul_forward(bmc_ctx_t* ctx, int dtype, void* d_out, int ldo, const void* d_inp, int ldi, const void* d_weight,
+                       const void* d_residual, int ldr, int BT, int C, int OC) {
+    BMC_CHECK_CTX(ctx);
+    if (dtype == BMC_F32)
+        return note(ctx, gemm_f32_simt((float*)d_out, ldo, 0, (const float*)d_inp, ldi, 1, (const float*)d_weight, C, 1,
+                                       (const float*)d_residual, ldr, BT, OC, C, ctx->stream));
+    GemmProblem g{BT, OC, C, (const bf16*)d_inp, ldi, 0, (const bf16*)d_weight, C, 0, d_out, ldo, GEMM_OUT_BF16,
+                  (const bf16*)d_residual, ldr, 1, 0};
+    return note(ctx, gemm_bf16_umma(g, ctx->d_err, ctx->stream));
+}
+int bmc_matmul_backward_inp(bmc_ctx_t* ctx, int dtype, void* d_ginp, int ldgi, int accumulate, const void* d_gout, int ldgo,
+                            const void* d_weight, int BT, int C, int OC) {
+    BMC_CHECK_CTX(ctx);
+    if (dtype == BMC_F32)
+        return note(ctx, gemm_f32_simt((float*)d_ginp, ldgi, accumulate, (const float*)d_gout, ldgo, 1, (const float*)d_weight, 1, C,
+                                       nullptr, 0, BT, C, OC, ctx->stream));
+    // ginp[BT, C] = gout[BT, OC] (K-major, reduction over OC) x W[OC, C] (MN-major: reduction index is W's row)
+    GemmProblem g{BT, C, OC, (const bf16*)d_gout, ldgo, 0, (const bf16*)d_weight, C, 1, d_ginp, ldgi, GEMM_OUT_BF16,
+                  accumulate ? (const bf16*)d_ginp : nullptr, ldgi, 1, 0};
+    return note(ctx, gemm_bf16_umma(g, ctx->d_err, ctx->stream));
+}
+int bmc_matmul_backward_w(bmc_ctx_t* ctx, int dtype, float* d_gw, const void* d_gout, int ldgo, const void* d_inp, int ldi, int BT,
+                          int C, int OC) {
+    BMC_CHECK_CTX(ctx);
+    if (dtype == BMC_F32)
+        return note(ctx, gemm_f32_simt(d_gw, C, 1, (const float*)d_gout, 1, ldgo, (const float*)d_inp, 1, ldi, nullptr, 0, OC, C, BT,
+                                       ctx->stream));
+    // gw[OC, C] += gout^T[OC, BT] x inp[BT, C]: both operands MN-major, reduction over the tokens, split so
+    // that about two waves of CTAs exist even when OC x C is only a few dozen tiles.
+    const int tiles = ((OC + 127) / 128) * ((C + 191) / 192);
+    int splits = tiles >= 2 * ctx->num_sms ? 1 : (2 * ctx->num_sms + tiles - 1) / tiles;
+    const int kb_total = (BT + 63) / 64;
+    if (splits > kb_total / 4) splits = kb_total / 4 > 0 ? kb_total / 4 : 1;
+    GemmProblem g{OC, C, BT, (const bf16*)d_gout, ldgo, 1, (const bf16*)d_inp, ldi, 1, d_gw, C, GEMM_OUT_F32_ATOMIC, nullptr, 0, splits, 0};
+    return note(ctx, gemm_bf16_umma(g, ctx->d_err, ctx->stream));
+}
+
+// ---- RoPE --------------------------------------------------------------------------------------------
+int bmc_rope(bmc_ctx_t* ctx, int dtype, void* d_q, int ldq, void* d_k, int ldk, const float* d_cs_table, int rows, int S, int NH, int NKV,
+             int HD, int dir) {
+    BMC_CHECK_CTX(ctx);
+    if (dtype == BMC_F32) return note(ctx, rope_apply<float>((float*)d_q, ldq, (float*)d_k, ldk, d_cs_table, rows, S, NH, NKV, HD, dir, ctx->stream));
+    return note(ctx, rope_apply<bf16>((bf16*)d_q, ldq, (bf16*)d_k, ldk, d_cs_table, rows, S, NH, NKV, HD, dir, ctx->stream));
+}
+
+// ---- attention ---------------------------------------------------------------------------------------
+int bmc_attention_forward(bmc_ctx_t* ctx, int dtype, void* d_out, int ldo, float* d_lse, const void* d_q, int ldq, const void* d_k,
+                          const void* d_v, int ldkv, const uint8_t* d_mask, int B, int S, int NH, int NKV, int HD, float scale) {
+    BMC_CHECK_CTX(ctx);
+    if (dtype == BMC_F32)
+        return note(ctx, attention_forward_simt<float>((float*)d_out, ldo, d_lse, (const float*)d_q, ldq, (const float*)d_k,
+                                                       (const float*)d_v, ldkv, d_mask, B, S, NH, NKV, HD, scale, ctx->stream));
+    if (flash_attention_supported(HD, NH, NKV, d_mask != nullptr))
+        return note(ctx, flash_attention_forward((bf16*)d_out, ldo, d_lse, (const bf16*)d_q, ldq, (const bf16*)d_k, (const bf16*)d_v,
+                                                 ldkv, B, S, NH, NKV, HD, scale, ctx->stream));
+    return note(ctx, attention_forward_simt<bf16>((bf16*)d_out, ldo, d_lse, (const bf16*)d_q, ldq, (const bf16*)d_k, (const bf16*)d_v,
+                                                  ldkv, d_mask, B, S, NH, NKV, HD, scale, ctx->stream));
+}
+int bmc_attention_backward(bmc_ctx_t* ctx, int dtype, void* d_gq, int ldgq, void* d_gk, void* d_gv, int ldgkv, const void* d_gout,
+                           int ldo, const void* d_out, const float* d_lse, const void* d_q, int ldq, const void* d_k, const void* d_v,
+                           int ldkv, const uint8_t* d_mask, int B, int S, int NH, int NKV, int HD, float scale) {
+    BMC_CHECK_CTX(ctx);
+    const size_t rows = (size_t)B * S;
+    if (dtype == BMC_F32) {
+        // gK/gV accumulate through atomics and must start from zero (reference: zero_buffer before attention_backward,
+        // src/baremetal/scheduler.c:1372-1383). K and V rows may be interleaved with other columns, so clear row by row.
+        cudaMemset2DAsync(d_gk, (size_t)ldgkv * 4, 0, (size_t)NKV * HD * 4, rows, ctx->stream);
+        cudaMemset2DAsync(d_gv, (size_t)ldgkv * 4, 0, (size_t)NKV * HD * 4, rows, ctx->stream);
+        return note(ctx, attention_backward_simt<float>((float*)d_gq, ldgq, (float*)d_gk, (float*)d_gv, ldgkv, (const float*)d_gout, ldo,
+                                                        (const float*)d_out, d_lse, (const float*)d_q, ldq, (const float*)d_k,
+                                                        (const float*)d_v, ldkv, d_mask, B, S, NH, NKV, HD, scale, ctx->stream));
+    }
+    if (flash_attention_supported(HD, NH, NKV, d_mask != nullptr)) {
+        const size_t need = flash_attention_backward_scratch_bytes(B, S, NH, HD);
+        void* scratch = scratch_get(ctx, &ctx->attn_scratch, &ctx->attn_scratch_bytes, need);
+        if (!scratch) return -50;
+        return note(ctx, flash_attention_backward((bf16*)d_gq, ldgq, (bf16*)d_gk, (bf16*)d_gv, ldgkv, (const bf16*)d_gout, ldo,
+                                                  (const bf16*)d_out, d_lse, (const bf16*)d_q, ldq, (const bf16*)d_k, (const bf16*)d_v,
+                                                  ldkv, B, S, NH, NKV, HD, scale, scratch, ctx->stream), 3);
+    }
+    // General shapes (head_dim != 64, masks): exact fp32 kernel into fp32 scratch, then one cast per output.
+    const int QD = NH * HD, KVD = NKV * HD;
+    const size_t need = rows * (size_t)(QD + 2 * KVD) * sizeof(float);
+    float* scratch = (float*)scratch_get(ctx, &ctx->attn_scratch, &ctx->attn_scratch_bytes, need);
+    if (!scratch) return -50;
+    float* sgq = scratch;
+    float* sgk = sgq + rows * QD;
+    float* sgv = sgk + rows * KVD;
+    cudaMemsetAsync(sgk, 0, rows * 2 * KVD * sizeof(float), ctx->stream);
+    int rc = attention_backward_simt<bf16>(sgq, QD, sgk, sgv, KVD, (const bf16*)d_gout, ldo, (const bf16*)d_out, d_lse, (const bf16*)d_q,
+                                           ldq, (const bf16*)d_k, (const bf16*)d_v, ldkv, d_mask, B, S, NH, NKV, HD, scale, ctx->stream);
+    if (rc) return rc;
+    rc = cast_rows_f32_to_bf16((bf16*)d_gq, ldgq, sgq, QD, (int)rows, QD, ctx->stream);
+    if (!rc) rc = cast_rows_f32_to_bf16((bf16*)d_gk, ldgkv, sgk, KVD, (int)rows, KVD, ctx->stream);
+    if (!rc) rc = cast_rows_f32_to_bf16((bf16*)d_gv, ldgkv, sgv, KVD, (int)rows, KVD, ctx->stream);
+    return note(ctx, rc, 4);
+}
+
+// ---- SwiGLU / add ------------------------------------------------------------------------------------
+int bmc_swiglu_forward(bmc_ctx_t* ctx, int dtype, void* d_out, int ldo, const void* d_gate, const void* d_up, int ldgu, int rows, int H) {
+    BMC_CHECK_CTX(ctx);
+    if (dtype == BMC_F32) return note(ctx, swiglu_forward<float>((float*)d_out, ldo, (const float*)d_gate, (const float*)d_up, ldgu, rows, H, ctx->stream));
+    return note(ctx, swiglu_forward<bf16>((bf16*)d_out, ldo, (const bf16*)d_gate, (const bf16*)d_up, ldgu, rows, H, ctx->stream));
+}
+int bmc_swiglu_backward(bmc_ctx_t* ctx, int dtype, void* d_ggate, void* d_gup, int ldg, const void* d_gate, const void* d_up, int ldgu,
+                        const void* d_gout, int ldo, int rows, int H) {
+    BMC_CHECK_CTX(ctx);
+    if (dtype == BMC_F32)
+        return note(ctx, swiglu_backward<float>((float*)d_ggate, (float*)d_gup, ldg, (const float*)d_gate, (const float*)d_up, ldgu,
+                                                (const float*)d_gout, ldo, rows, H, ctx->stream));
+    return note(ctx, swiglu_backward<bf16>((bf16*)d_ggate, (bf16*)d_gup, ldg, (const bf16*)d_gate, (const bf16*)d_up, ldgu,
+                                           (const bf16*)d_gout, ldo, rows, H, ctx->stream));
+}
+int bmc_add_forward(bmc_ctx_t* ctx, int dtype, void* d_out, const void* d_a, const void* d_b, size_t n) {
+    BMC_CHECK_CTX(ctx);
+    if (dtype == BMC_F32) return note(ctx, add_forward<float>((float*)d_out, (const float*)d_a, (const float*)d_b, n, ctx->stream));
+    return note(ctx, add_forward<bf16>((bf16*)d_out, (const bf16*)d_a, (const bf16*)d_b, n, ctx->stream));
+}
+
+// ---- loss --------------------------------------------------------------------------------------------
+int bmc_xent(bmc_ctx_t* ctx, int dtype, void* d_logits, int ldv, float* d_row_loss, float* d_loss, const int* d_targets,
+             const uint8_t* d_loss_mask, int B, int S, int V, float grad_scale) {
+    BMC_CHECK_CTX(ctx);
+    int rc;
+    if (dtype == BMC_F32)
+        rc = xent_forward_backward<float>((float*)d_logits, d_row_loss, d_targets, d_loss_mask, B * S, V, ldv, grad_scale, ctx->stream);
+    else
+        rc = xent_forward_backward<bf16>((bf16*)d_logits, d_row_loss, d_targets, d_loss_mask, B * S, V, ldv, grad_scale, ctx->stream);
+    if (rc) return rc;
+    if (d_loss) rc = loss_reduce(d_loss, d_row_loss, B, S, ctx->stream);
+    return note(ctx, rc, d_loss ? 2 : 1);
+}
+
+// ---- optimizer / casts / sampler ---------------------------------------------------------------------
+int bmc_adamw(bmc_ctx_t* ctx, float* d_w, void* d_w_bf16, const void* d_g, int grad_dtype, float* d_m, float* d_v, size_t n,
+              const float* h_hp) {
+    BMC_CHECK_CTX(ctx);
+    if (grad_dtype == BMC_F32) return note(ctx, adamw_f32grad(d_w, (bf16*)d_w_bf16, (const float*)d_g, d_m, d_v, n, h_hp, ctx->stream));
+    return note(ctx, adamw_bf16grad(d_w, (bf16*)d_w_bf16, (const bf16*)d_g, d_m, d_v, n, h_hp, ctx->stream));
+}
+int bmc_cast_f32_to_bf16(bmc_ctx_t* ctx, void* d_out, const float* d_in, size_t n) {
+    BMC_CHECK_CTX(ctx);
+    return note(ctx, cast_f32_to_bf16((bf16*)d_out, d_in, n, ctx->stream));
+}
+int bmc_cast_bf16_to_f32(bmc_ctx_t* ctx, float* d_out, const void* d_in, size_t n) {
+    BMC_CHECK_CTX(ctx);
+    return note(ctx, cast_bf16_to_f32(d_out, (const bf16*)d_in, n, ctx->stream));
+}
+int bmc_seq_prefix_accumulate(bmc_ctx_t* ctx, int dtype, void* d_x, float* d_carry_f32, int B, size_t per_seq) {
+    BMC_CHECK_CTX(ctx);
+    if (dtype == BMC_F32) return note(ctx, seq_prefix_accumulate<float>((float*)d_x, d_carry_f32, B, per_seq, ctx->stream));
+    return note(ctx, seq_prefix_accumulate<bf16>((bf16*)d_x, d_carry_f32, B, per_seq, ctx->stream));
+}
+int bmc_argmax(bmc_ctx_t* ctx, int* d_index, const float* d_logits, int V) {
+    BMC_CHECK_CTX(ctx);
+    return note(ctx, argmax_first(d_index, d_logits, V, ctx->stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,200 @@
+// Data-parallel gradient all-reduce over NCCL (NVLink 5 / NVSwitch), overlapped with backward.
+//
+// Gradients are produced in fp32 in one flat array (trainer-state order: layer 0 .. layer L-1, final norm,
+// tied embedding). Layers are grouped into buckets; as soon as backward has finished the lowest layer of a
+// bucket, the compute stream records an event, and the communication stream (a) casts that fp32 range to
+// bf16 into a flat bf16 gradient array, (b) all-reduces it in place (sum). Backward runs from the last layer
+// to the first, so buckets complete from the end of the array towards the start and their reductions overlap
+// the remaining backward work; the final-norm + embedding bucket completes last. AdamW then reads the reduced
+// bf16 gradients with grad_scale = 1 / (sequences per rank * world).
+//
+// NCCL is bound at run time with dlopen("libnccl.so.2"), so a single-GPU process never needs the library and
+// a process that already loaded NCCL (e.g. through torch) shares that copy.
+#include <dlfcn.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <vector>
+
+#include "../host/dp.h"
+#include "kernels.cuh"
+
+namespace {
+
+typedef struct ncclComm* ncclComm_t;
+typedef struct { char internal[128]; } ncclUniqueId;
+enum { ncclSuccess = 0 };
+enum { ncclFloat32 = 7, ncclBfloat16 = 9 };
+enum { ncclSum = 0 };
+
+struct NcclApi {
+    void* lib;
+    int (*GetUniqueId)(ncclUniqueId*);
+    int (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int);
+    int (*CommDestroy)(ncclComm_t);
+    int (*AllReduce)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t);
+    const char* (*GetErrorString)(int);
+};
+
+NcclApi* nccl() {
+    static NcclApi api;
+    static int state = 0;  // 0 = untried, 1 = ok, -1 = failed
+    if (state == 0) {
+        state = -1;
+        api.lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (!api.lib) api.lib = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+        if (api.lib) {
+            api.GetUniqueId = (int (*)(ncclUniqueId*))dlsym(api.lib, "ncclGetUniqueId");
+            api.CommInitRank = (int (*)(ncclComm_t*, int, ncclUniqueId, int))dlsym(api.lib, "ncclCommInitRank");
+            api.CommDestroy = (int (*)(ncclComm_t))dlsym(api.lib, "ncclCommDestroy");
+            api.AllReduce = (int (*)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t))dlsym(api.lib, "ncclAllReduce");
+            api.GetErrorString = (const char* (*)(int))dlsym(api.lib, "ncclGetErrorString");
+            if (api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllReduce) state = 1;
+        }
+        if (state != 1) fprintf(stderr, "[ERROR] data parallel: cannot load NCCL (libnccl.so.2): %s\n", dlerror());
+    }
+    return state == 1 ? &api : nullptr;
+}
+
+struct Bucket {
+    size_t begin, end;  // element range in the flat parameter order
+    int ready_at;       // bm_dp_bucket_ready(layer) value that completes the bucket
+};
+
+}  // namespace
+
+struct bm_dp_s {
+    bmc_ctx_t* be;
+    int rank, world;
+    ncclComm_t comm;
+    cudaStream_t comm_stream;
+    std::vector<Bucket> buckets;
+    std::vector<cudaEvent_t> ready_ev;
+    cudaEvent_t done_ev;
+    float* d_grad_f32;
+    bmb::bf16* d_grad_bf16;
+    float* d_loss_buf;
+    size_t P;
+    int last_microstep;
+};
+
+extern "C" {
+
+int bmx_dp_unique_id(void* out_id) {
+    NcclApi* api = nccl();
+    if (!api || !out_id) return -1;
+    ncclUniqueId id;
+    if (api->GetUniqueId(&id) != ncclSuccess) return -2;
+    memcpy(out_id, &id, sizeof id);
+    return 0;
+}
+
+struct bm_dp_s* bm_dp_create(bmc_ctx_t* be, int rank, int world, const void* nccl_id, size_t P, int n_layers, const size_t* layer_begin,
+                             float* d_grad_f32) {
+    NcclApi* api = nccl();
+    if (!api || !be || !nccl_id || world < 1 || rank < 0 || rank >= world) return nullptr;
+    bm_dp_s* dp = new bm_dp_s();
+    dp->be = be;
+    dp->rank = rank;
+    dp->world = world;
+    dp->P = P;
+    dp->d_grad_f32 = d_grad_f32;
+    dp->last_microstep = 1;
+    ncclUniqueId id;
+    memcpy(&id, nccl_id, sizeof id);
+    int rc = api->CommInitRank(&dp->comm, world, id, rank);
+    if (rc != ncclSuccess) {
+        fprintf(stderr, "[ERROR] ncclCommInitRank failed: %s\n", api->GetErrorString ? api->GetErrorString(rc) : "?");
+        delete dp;
+        return nullptr;
+    }
+    cudaStreamCreateWithFlags(&dp->comm_stream, cudaStreamNonBlocking);
+    cudaEventCreateWithFlags(&dp->done_ev, cudaEventDisableTiming);
+    if (cudaMalloc(&dp->d_grad_bf16, P * sizeof(bmb::bf16)) != cudaSuccess || cudaMalloc(&dp->d_loss_buf, 16) != cudaSuccess) {
+        fprintf(stderr, "[ERROR] data parallel: out of device memory\n");
+        delete dp;
+        return nullptr;
+    }
+    // Buckets of ~4 layers, highest layers first in completion order. The tail (final norm + embedding)
+    // is one bucket completed by the embedding scatter.
+    int per = 4;
+    const char* e = getenv("BM_DP_LAYERS_PER_BUCKET");
+    if (e && atoi(e) > 0) per = atoi(e);
+    for (int hi = n_layers; hi > 0; hi -= per) {
+        const int lo = hi - per > 0 ? hi - per : 0;
+        dp->buckets.push_back(Bucket{layer_begin[lo], layer_begin[hi], lo});
+    }
+    dp->buckets.push_back(Bucket{layer_begin[n_layers], P, -1});
+    dp->ready_ev.resize(dp->buckets.size());
+    for (auto& ev : dp->ready_ev) cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+    return dp;
+}
+
+void bm_dp_destroy(struct bm_dp_s* dp) {
+    if (!dp) return;
+    cudaStreamSynchronize(dp->comm_stream);
+    NcclApi* api = nccl();
+    if (api && dp->comm) api->CommDestroy(dp->comm);
+    for (auto& ev : dp->ready_ev) cudaEventDestroy(ev);
+    cudaEventDestroy(dp->done_ev);
+    cudaFree(dp->d_grad_bf16);
+    cudaFree(dp->d_loss_buf);
+    cudaStreamDestroy(dp->comm_stream);
+    delete dp;
+}
+
+int bm_dp_world(struct bm_dp_s* dp) { return dp ? dp->world : 1; }
+void bm_dp_begin_window(struct bm_dp_s*) {}
+void bm_dp_set_last_microstep(struct bm_dp_s* dp, int is_last) { if (dp) dp->last_microstep = is_last; }
+
+int bm_dp_bucket_ready(struct bm_dp_s* dp, int layer) {
+    if (!dp || !dp->last_microstep) return 0;
+    NcclApi* api = nccl();
+    cudaStream_t compute = (cudaStream_t)bmc_stream(dp->be);
+    for (size_t i = 0; i < dp->buckets.size(); ++i) {
+        const Bucket& b = dp->buckets[i];
+        if (b.ready_at != layer) continue;
+        cudaEventRecord(dp->ready_ev[i], compute);
+        cudaStreamWaitEvent(dp->comm_stream, dp->ready_ev[i], 0);
+        const size_t n = b.end - b.begin;
+        if (bmb::cast_f32_to_bf16(dp->d_grad_bf16 + b.begin, dp->d_grad_f32 + b.begin, n, dp->comm_stream)) return -1;
+        const int rc = api->AllReduce(dp->d_grad_bf16 + b.begin, dp->d_grad_bf16 + b.begin, n, ncclBfloat16, ncclSum, dp->comm, dp->comm_stream);
+        if (rc != ncclSuccess) {
+            fprintf(stderr, "[ERROR] ncclAllReduce failed: %s\n", api->GetErrorString ? api->GetErrorString(rc) : "?");
+            return -2;
+        }
+    }
+    return 0;
+}
+
+int bm_dp_adamw(struct bm_dp_s* dp, bm_trainer_t* t, const float* hp) {
+    cudaStream_t compute = (cudaStream_t)bmc_stream(dp->be);
+    cudaEventRecord(dp->done_ev, dp->comm_stream);
+    cudaStreamWaitEvent(compute, dp->done_ev, 0);
+    return bmc_adamw(dp->be, t->d_master, t->d_wlow, dp->d_grad_bf16, BMC_BF16, t->d_m, t->d_v, t->P, hp);
+}
+
+float bm_dp_mean_loss(struct bm_dp_s* dp, float local_loss) {
+    NcclApi* api = nccl();
+    if (!dp || !api) return local_loss;
+    cudaMemcpyAsync(dp->d_loss_buf, &local_loss, sizeof(float), cudaMemcpyHostToDevice, dp->comm_stream);
+    if (api->AllReduce(dp->d_loss_buf, dp->d_loss_buf, 1, ncclFloat32, ncclSum, dp->comm, dp->comm_stream) != ncclSuccess) return -1.0f;
+    float sum = 0.f;
+    cudaMemcpyAsync(&sum, dp->d_loss_buf, sizeof(float), cudaMemcpyDeviceToHost, dp->comm_stream);
+    cudaStreamSynchronize(dp->comm_stream);
+    return sum / (float)dp->world;
+}
+
+int bmx_trainer_dp_init(bm_trainer_t* t, int rank, int world, const void* nccl_id) {
+    if (!t || t->dp) return -1;
+    if (world <= 1) return 0;
+    const int L = t->model->arch.n_layers;
+    std::vector<size_t> layer_begin(L + 1);
+    for (int l = 0; l < L; ++l) layer_begin[l] = t->params[9 * l].off;
+    layer_begin[L] = t->params[9 * L].off;
+    t->dp = bm_dp_create(t->ctx->be, rank, world, nccl_id, t->P, L, layer_begin.data(), t->d_grad);
+    return t->dp ? 0 : -2;
+}
+
+}  // extern "C"

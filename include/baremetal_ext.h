@@ -1,0 +1,70 @@
+/* Additions beside the reference's public API. Nothing here changes a signature of include/baremetal.h.
+ *
+ *  - introspection of the trainer's per-tensor state, which the reference exposes only through its
+ *    internal structs (bm_trainer_s::opt_states src/baremetal/trainer.h:13-22,33 and
+ *    bmt_scheduler_get_grad_buffer src/baremetal/scheduler.h:50) and which its tests reach by
+ *    including those headers;
+ *  - a step variant whose inputs already live in device memory (the reference always stages tokens
+ *    from the host, src/baremetal/trainer.c:473-516);
+ *  - data-parallel set-up: the reference is single-device (one MTLDevice, src/backend/metal/device.m:20),
+ *    so rank/world size and the NCCL id arrive through an added call and bm_train_step keeps its signature.
+ */
+#ifndef BAREMETAL_EXT_H
+#define BAREMETAL_EXT_H
+
+#include <stddef.h>
+#include <stdint.h>
+#include "baremetal.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { BMX_WEIGHT = 0, BMX_GRAD = 1, BMX_ADAM_M = 2, BMX_ADAM_V = 3 };
+
+/* tensors in trainer-state order: per layer ln1w, qw, kw, vw, ow, ln2w, gate, up, down; lnfw; tied embedding */
+int    bmx_trainer_num_tensors(bm_trainer_t* t);
+size_t bmx_trainer_tensor_size(bm_trainer_t* t, int i);
+/* copies tensor i of the chosen kind (fp32) to host_out; returns 0 or -1 */
+int    bmx_trainer_read(bm_trainer_t* t, int what, int i, float* host_out);
+/* Reference-compatibility options (value 1 = behave like the reference, 0 = default, the mathematically
+ * intended result). They exist so that parity with the reference can be shown on batches of more than one
+ * sequence and over several fp32 steps, where the reference deviates from the exact gradient:
+ *   "ref_norm_grad"        RMSNorm weight gradients keep only the last sequence of the batch
+ *                          (rmsnorm_backward_w overwrites, src/kernels/backward.metal:400);
+ *   "ref_input_grad_carry" the embedding scatter of sequence b adds the input gradients of all earlier
+ *                          sequences of the optimizer window as well (the layer-0 input gradient buffer is
+ *                          never cleared in between, src/baremetal/scheduler.c:263-266, trainer.c:459-470);
+ *   "ref_stale_embedding"  in fp32 mode the embedding gather keeps reading the initial table after updates
+ *                          (embed_lookup falls back to the host copy, src/baremetal/trainer.c:287-293);
+ *   "ref_quirks"           all of the above.
+ * Set before the first step. Also enabled for every trainer by the environment variable BM_REF_QUIRKS=1. */
+int    bmx_trainer_set_option(bm_trainer_t* t, const char* key, int value);
+long   bmx_trainer_launch_count(bm_trainer_t* t);
+size_t bmx_trainer_device_bytes(bm_trainer_t* t);
+
+/* One optimizer micro-step with inputs/targets already in device memory (int32[B*T] each). Enqueues the
+ * whole step and returns without waiting; 0 on success. bmx_train_last_loss() waits and returns the loss. */
+int    bmx_train_step_resident(bm_trainer_t* t, const int* d_inputs, const int* d_targets, int B, int T);
+float  bmx_train_last_loss(bm_trainer_t* t);
+/* device allocation helpers for callers that keep inputs resident */
+void*  bmx_device_alloc(bm_context_t* ctx, size_t bytes);
+void   bmx_device_free(bm_context_t* ctx, void* d_ptr);
+int    bmx_device_upload(bm_context_t* ctx, void* d_dst, const void* h_src, size_t bytes);
+int    bmx_device_sync(bm_context_t* ctx);
+/* GPU time of work enqueued between begin and end on the context's stream, in ms (end blocks). */
+int    bmx_timer_begin(bm_context_t* ctx, int slot);
+float  bmx_timer_end(bm_context_t* ctx, int slot);
+
+/* Data parallel: every rank holds a full replica and calls bm_train_step with its own B sequences;
+ * gradients are summed across ranks (bf16 buckets over NCCL, overlapped with backward) before AdamW and the
+ * returned loss is the mean over all ranks. `nccl_id` is the 128-byte ncclUniqueId created on rank 0 with
+ * bmx_dp_unique_id() and handed to the other ranks by the launcher. */
+#define BMX_DP_ID_BYTES 128
+int    bmx_dp_unique_id(void* out_id);
+int    bmx_trainer_dp_init(bm_trainer_t* t, int rank, int world, const void* nccl_id);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,132 @@
+/* C ABI of the sm_100a CUDA backend (libbaremetal_b200.so).
+ *
+ * This is the layer that sits where the reference has src/backend/backend.h + its Metal shaders:
+ * the C11 host code (trainer, model, optimizer state) calls these entry points and nothing else
+ * to reach the GPU. Where the reference dispatches a kernel *by name* with a buffer list and
+ * Metal grid sizes (backend_encode_dispatch, src/backend/backend.h:55-62), this ABI has one typed
+ * entry point per operation: plain device pointers, explicit shapes and leading dimensions,
+ * an int status. Launch geometry is chosen inside the backend.
+ *
+ * Conventions
+ *  - every pointer argument named d_* is DEVICE memory obtained from bmc_alloc();
+ *  - `dtype` is the activation storage type (BMC_F32 or BMC_BF16); arithmetic is fp32 either way.
+ *    With BMC_BF16 the matmul entry points run on the tcgen05 tensor cores and expect bf16
+ *    weights; with BMC_F32 they run fp32 FFMA and expect fp32 weights;
+ *  - all work is enqueued on the context's compute stream; nothing blocks except bmc_sync(),
+ *    bmc_download() and bmc_status();
+ *  - return value 0 = enqueued, <0 = rejected (bad shape/alignment, missing device). There is no
+ *    CPU fallback: without a usable CUDA device bmc_create() returns NULL.
+ */
+#ifndef BM_CUDA_BACKEND_H
+#define BM_CUDA_BACKEND_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct bmc_ctx_s bmc_ctx_t;
+
+enum { BMC_F32 = 0, BMC_BF16 = 1 };
+
+/* ---- context, memory, transfers (replace backend_create/destroy, backend_buffer_alloc/free/map/unmap,
+ *      backend_encode_wait: src/backend/backend.h:17-18,40-44,65-66) ---- */
+bmc_ctx_t* bmc_create(int device_ordinal);
+void       bmc_destroy(bmc_ctx_t* ctx);
+void*      bmc_alloc(bmc_ctx_t* ctx, size_t bytes);            /* NULL when bytes == 0 or out of memory */
+void       bmc_free(bmc_ctx_t* ctx, void* d_ptr);
+size_t     bmc_allocated_bytes(bmc_ctx_t* ctx);               /* backend_get_allocated_memory, backend.h:19 */
+size_t     bmc_peak_allocated_bytes(bmc_ctx_t* ctx);          /* backend_get_peak_allocated_memory, backend.h:20 */
+int        bmc_upload(bmc_ctx_t* ctx, void* d_dst, const void* h_src, size_t bytes);    /* async H2D on the compute stream */
+int        bmc_download(bmc_ctx_t* ctx, void* h_dst, const void* d_src, size_t bytes);  /* D2H, returns after the copy */
+int        bmc_memset(bmc_ctx_t* ctx, void* d_ptr, int byte_value, size_t bytes);
+int        bmc_copy(bmc_ctx_t* ctx, void* d_dst, const void* d_src, size_t bytes);
+int        bmc_sync(bmc_ctx_t* ctx);                          /* waits for the compute stream; returns bmc_status() */
+/* Non-zero when a kernel reported a failed bounded wait or a CUDA call failed since the last call. */
+int        bmc_status(bmc_ctx_t* ctx);
+void*      bmc_stream(bmc_ctx_t* ctx);                        /* the cudaStream_t work is enqueued on */
+/* Kernel launches issued through this context since creation (all entry points). */
+long       bmc_launch_count(bmc_ctx_t* ctx);
+/* Pinned host memory for staging step inputs. */
+void*      bmc_host_alloc(size_t bytes);
+void       bmc_host_free(void* p);
+/* GPU-side phase timing (replaces backend_encode_wait_timed / backend_get_gpu_busy_ms, backend.h:32-37):
+ * bmc_timer_begin/end bracket work on the compute stream with events; end returns elapsed ms (blocking). */
+int        bmc_timer_begin(bmc_ctx_t* ctx, int slot);
+float      bmc_timer_end(bmc_ctx_t* ctx, int slot);
+
+/* ---- embedding (embed_lookup src/baremetal/trainer.c:275-298; embedding_backward src/kernels/backward.metal:636) ---- */
+int bmc_embedding_forward(bmc_ctx_t* ctx, int dtype, void* d_out, const float* d_table_f32, const int* d_tokens, int n_tok, int D);
+int bmc_embedding_backward(bmc_ctx_t* ctx, int dtype, float* d_gwte_f32, const void* d_gout, const int* d_tokens, int n_tok, int D);
+
+/* ---- RMSNorm (rmsnorm_forward forward.metal:993; rmsnorm_backward_x / _w backward.metal:340,379) ----
+ * forward also stores 1/rms per row in d_rstd (may be NULL).
+ * backward: d_gx += dL/dx (accumulates, like the reference kernel); d_gw_f32[j] (+)= sum over rows
+ * [w_row0, w_row1) of gout*x*rstd — the row window lets a caller reproduce the reference's
+ * "last sequence only" weight gradient (backward.metal:400 overwrites per sequence) or the full sum. */
+int bmc_rmsnorm_forward(bmc_ctx_t* ctx, int dtype, void* d_out, float* d_rstd, const void* d_x, const float* d_w, int N, int C, float eps);
+int bmc_rmsnorm_backward(bmc_ctx_t* ctx, int dtype, void* d_gx, float* d_gw_f32, int gw_accumulate, const void* d_gout, const void* d_x,
+                         const float* d_w, const float* d_rstd, int N, int C, int w_row0, int w_row1);
+
+/* ---- linear layers (matmul_forward_* forward.metal:176,449; matmul_backward_inp_* backward.metal:122,174;
+ *      matmul_backward_w_tiled backward.metal:277). Weight is row-major [OC, C] in the activation dtype.
+ *   forward : out[BT,OC] = inp[BT,C] * W^T (+ residual[BT,OC] when d_residual != NULL)
+ *   backward_inp : ginp[BT,C] = gout[BT,OC] * W         (overwrites; pass accumulate=1 for the reference's +=)
+ *   backward_w   : gw_f32[OC,C] += gout^T * inp          (always accumulates, fp32, like the reference) ---- */
+int bmc_matmul_forward(bmc_ctx_t* ctx, int dtype, void* d_out, int ldo, const void* d_inp, int ldi, const void* d_weight,
+                       const void* d_residual, int ldr, int BT, int C, int OC);
+int bmc_matmul_backward_inp(bmc_ctx_t* ctx, int dtype, void* d_ginp, int ldgi, int accumulate, const void* d_gout, int ldgo,
+                            const void* d_weight, int BT, int C, int OC);
+int bmc_matmul_backward_w(bmc_ctx_t* ctx, int dtype, float* d_gw_f32, const void* d_gout, int ldgo, const void* d_inp, int ldi,
+                          int BT, int C, int OC);
+
+/* ---- RoPE (rope_forward_seq forward.metal:2225; rope_backward_seq backward.metal:980), in place.
+ * d_cs_table: float[S][HD/2][2] = (cos, sin)(pos * inv_freq), built by the host with the reference's formula
+ * (rope_inv_freq forward.metal:1260-1279). rows = B*S, position = row % S. dir: +1 forward, -1 backward. ---- */
+int bmc_rope(bmc_ctx_t* ctx, int dtype, void* d_q, int ldq, void* d_k, int ldk, const float* d_cs_table, int rows, int S, int NH,
+             int NKV, int HD, int dir);
+
+/* ---- causal GQA attention (attention_forward_seq / _train_tiled forward.metal:1811,2122;
+ *      attention_backward / _tiled backward.metal:665,820). Q[row,h,:] at d_q + row*ldq + h*HD, K and V
+ *      likewise with NKV heads and pitch ldkv; row = b*S + s. d_lse: float[B][NH][S] log-sum-exp saved
+ *      by forward for backward. d_mask (uint8[B*S], may be NULL): 0 excludes that position as key and query.
+ *      backward overwrites d_gq and d_gk/d_gv (all in the activation dtype, same pitches as q / kv). ---- */
+int bmc_attention_forward(bmc_ctx_t* ctx, int dtype, void* d_out, int ldo, float* d_lse, const void* d_q, int ldq, const void* d_k,
+                          const void* d_v, int ldkv, const uint8_t* d_mask, int B, int S, int NH, int NKV, int HD, float scale);
+int bmc_attention_backward(bmc_ctx_t* ctx, int dtype, void* d_gq, int ldgq, void* d_gk, void* d_gv, int ldgkv, const void* d_gout,
+                           int ldo, const void* d_out, const float* d_lse, const void* d_q, int ldq, const void* d_k, const void* d_v,
+                           int ldkv, const uint8_t* d_mask, int B, int S, int NH, int NKV, int HD, float scale);
+
+/* ---- SwiGLU (swiglu_forward forward.metal:1179; swiglu_backward backward.metal:505) ---- */
+int bmc_swiglu_forward(bmc_ctx_t* ctx, int dtype, void* d_out, int ldo, const void* d_gate, const void* d_up, int ldgu, int rows, int H);
+int bmc_swiglu_backward(bmc_ctx_t* ctx, int dtype, void* d_ggate, void* d_gup, int ldg, const void* d_gate, const void* d_up, int ldgu,
+                        const void* d_gout, int ldo, int rows, int H);
+/* residual add (add_forward forward.metal:1332) */
+int bmc_add_forward(bmc_ctx_t* ctx, int dtype, void* d_out, const void* d_a, const void* d_b, size_t n);
+
+/* ---- loss (host loss loop src/baremetal/scheduler.c:1622-1634 + xent_backward backward.metal:567, masked :597).
+ * Overwrites logits with (softmax - onehot) * grad_scale, writes per-row losses, then reduces them to
+ * *d_loss = mean over B sequences of the per-sequence mean (src/baremetal/trainer.c:528). ---- */
+int bmc_xent(bmc_ctx_t* ctx, int dtype, void* d_logits, int ldv, float* d_row_loss, float* d_loss, const int* d_targets,
+             const uint8_t* d_loss_mask, int B, int S, int V, float grad_scale);
+
+/* ---- AdamW over a flat parameter range (adamw_step src/anneal/adamw.metal:26 + the host recast loop
+ *      src/baremetal/trainer.c:373-396). hp (HOST pointer, 8 floats) = {lr, b1, b2, eps, wd, 1-b1^t, 1-b2^t, grad_scale}.
+ *      grad_dtype: BMC_F32 or BMC_BF16. d_w_bf16 (may be NULL) receives the bf16 working copy. ---- */
+int bmc_adamw(bmc_ctx_t* ctx, float* d_w, void* d_w_bf16, const void* d_g, int grad_dtype, float* d_m, float* d_v, size_t n,
+              const float* h_hp);
+int bmc_cast_f32_to_bf16(bmc_ctx_t* ctx, void* d_out_bf16, const float* d_in, size_t n);
+int bmc_cast_bf16_to_f32(bmc_ctx_t* ctx, float* d_out, const void* d_in_bf16, size_t n);
+/* x[b] <- carry + x[0] + .. + x[b] over the B sequences of a batch (per_seq elements each), carry <- last sum.
+ * Reference-compatibility helper: the reference's layer-0 input gradient is never cleared between the sequences
+ * of an optimizer window (src/baremetal/scheduler.c:263-266, src/baremetal/trainer.c:459-470). */
+int bmc_seq_prefix_accumulate(bmc_ctx_t* ctx, int dtype, void* d_x, float* d_carry_f32, int B, size_t per_seq);
+/* greedy sampler: lowest index among the maxima (bm_sample argmax branch src/baremetal/sampler.c:36-40) */
+int bmc_argmax(bmc_ctx_t* ctx, int* d_index, const float* d_logits, int V);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BM_CUDA_BACKEND_H */
