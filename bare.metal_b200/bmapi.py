@@ -14,7 +14,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(PKG_DIR)
 
 BM_PRECISION_FP32, BM_PRECISION_FP16, BM_PRECISION_BF16 = 0, 1, 2
-BM_DEVICE_CPU, BM_DEVICE_METAL = 0, 1
+BM_DEVICE_CPU, BM_DEVICE_METAL, BM_DEVICE_CUDA = 0, 1, 2
 BM_NORM_RMSNORM, BM_ACT_SWIGLU, BM_POS_ROPE, BM_ATTN_GQA = 1, 1, 1, 1
 CHECKPOINT_MAGIC = 20250718  # src/baremetal/checkpoint.h:11
 
@@ -119,12 +119,15 @@ def state_tensor_order(a):
 def lcg_tokens(n, vocab, seed=42):
     """The reference's synthetic token stream: s = s*1664525 + 1013904223 (mod 2^32), tok = s % V
     (bench/train_bench.c:286-290)."""
-    out = np.empty(n, np.int32)
-    s = seed & 0xFFFFFFFF
-    for i in range(n):
-        s = (s * 1664525 + 1013904223) & 0xFFFFFFFF
-        out[i] = s % vocab
-    return out
+    # closed form of the recurrence, evaluated with wrapping uint32 arithmetic:
+    # s_i = a^i * s_0 + c * (1 + a + ... + a^(i-1))  (mod 2^32)
+    if n <= 0:
+        return np.empty(0, np.int32)
+    with np.errstate(over="ignore"):
+        a_pow = np.cumprod(np.full(n, 1664525, dtype=np.uint32), dtype=np.uint32)           # a^1 .. a^n
+        geo = np.cumsum(np.concatenate((np.ones(1, np.uint32), a_pow[:-1])), dtype=np.uint32)  # sum_{j<i} a^j
+        s = a_pow * np.uint32(seed & 0xFFFFFFFF) + np.uint32(1013904223) * geo
+    return (s % np.uint32(vocab)).astype(np.int32)
 
 
 def lcg_batch(B, S, vocab, seed=42):
@@ -189,6 +192,8 @@ def load_product():
         "bmx_device_alloc": (vp, [vp, C.c_size_t]), "bmx_device_free": (None, [vp, vp]),
         "bmx_device_upload": (C.c_int, [vp, vp, vp, C.c_size_t]), "bmx_device_sync": (C.c_int, [vp]),
         "bmx_timer_begin": (C.c_int, [vp, C.c_int]), "bmx_timer_end": (C.c_float, [vp, C.c_int]),
+        "bmx_model_weight_buffer": (fp, [vp, C.POINTER(C.c_size_t)]),
+        "bmx_gemm_timing": (C.c_int, [vp, C.c_int]), "bmx_gemm_timing_collect": (C.c_int, [vp, C.POINTER(C.c_double)]),
         "bmx_dp_unique_id": (C.c_int, [vp]), "bmx_trainer_dp_init": (C.c_int, [vp, C.c_int, C.c_int, vp]),
     }
     for name, (res, args) in ext.items():

@@ -8,6 +8,7 @@
 
 #include <map>
 #include <mutex>
+#include <vector>
 
 #include "attention_mma.cuh"
 #include "gemm_umma.cuh"
@@ -31,6 +32,11 @@ struct bmc_ctx_s {
     void* attn_scratch;
     size_t attn_scratch_bytes;
     cudaEvent_t ev0[8], ev1[8];
+    // optional per-launch timing of the tensor-core GEMM (bmc_gemm_timing)
+    bool gemm_timing;
+    std::vector<cudaEvent_t> gt_events;  // pairs (begin, end)
+    std::vector<double> gt_flops;
+    size_t gt_used;
 };
 
 namespace {
@@ -63,9 +69,52 @@ void* scratch_get(bmc_ctx_t* ctx, void** slot, size_t* cap, size_t bytes) {
     return *slot;
 }
 
+// tensor-core GEMM launch, bracketed by events when per-launch timing is on
+int run_umma(bmc_ctx_t* ctx, const GemmProblem& g) {
+    if (!ctx->gemm_timing) return gemm_bf16_umma(g, ctx->d_err, ctx->stream);
+    if (ctx->gt_used * 2 + 2 > ctx->gt_events.size()) {
+        for (int i = 0; i < 2; ++i) {
+            cudaEvent_t e;
+            cudaEventCreate(&e);
+            ctx->gt_events.push_back(e);
+        }
+    }
+    cudaEventRecord(ctx->gt_events[ctx->gt_used * 2], ctx->stream);
+    const int rc = gemm_bf16_umma(g, ctx->d_err, ctx->stream);
+    cudaEventRecord(ctx->gt_events[ctx->gt_used * 2 + 1], ctx->stream);
+    if (ctx->gt_flops.size() <= ctx->gt_used) ctx->gt_flops.resize(ctx->gt_used + 1);
+    ctx->gt_flops[ctx->gt_used] = 2.0 * g.M * g.N * g.K;
+    ctx->gt_used++;
+    return rc;
+}
+
 }  // namespace
 
 extern "C" {
+
+int bmc_gemm_timing(bmc_ctx_t* ctx, int enable) {
+    BMC_CHECK_CTX(ctx);
+    ctx->gemm_timing = enable != 0;
+    ctx->gt_used = 0;
+    return 0;
+}
+// out[0] = launches, out[1] = summed duration in ms, out[2] = summed algorithmic FLOPs. Blocks until the stream is idle.
+int bmc_gemm_timing_collect(bmc_ctx_t* ctx, double* out) {
+    BMC_CHECK_CTX(ctx);
+    cudaStreamSynchronize(ctx->stream);
+    double ms = 0, fl = 0;
+    for (size_t i = 0; i < ctx->gt_used; ++i) {
+        float t = 0.f;
+        cudaEventElapsedTime(&t, ctx->gt_events[2 * i], ctx->gt_events[2 * i + 1]);
+        ms += t;
+        fl += ctx->gt_flops[i];
+    }
+    out[0] = (double)ctx->gt_used;
+    out[1] = ms;
+    out[2] = fl;
+    ctx->gt_used = 0;
+    return 0;
+}
 
 bmc_ctx_t* bmc_create(int device_ordinal) {
     int n = 0;
@@ -92,6 +141,8 @@ bmc_ctx_t* bmc_create(int device_ordinal) {
     ctx->rms_scratch_floats = 0;
     ctx->attn_scratch = nullptr;
     ctx->attn_scratch_bytes = 0;
+    ctx->gemm_timing = false;
+    ctx->gt_used = 0;
     if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) { delete ctx; return nullptr; }
     if (cudaMalloc(&ctx->d_err, sizeof(int)) != cudaSuccess) { delete ctx; return nullptr; }
     cudaMemset(ctx->d_err, 0, sizeof(int));
@@ -114,6 +165,7 @@ void bmc_destroy(bmc_ctx_t* ctx) {
         cudaEventDestroy(ctx->ev0[i]);
         cudaEventDestroy(ctx->ev1[i]);
     }
+    for (auto e : ctx->gt_events) cudaEventDestroy(e);
     cudaStreamDestroy(ctx->stream);
     delete ctx;
 }
@@ -252,7 +304,7 @@ int bmc_matmul_forward(bmc_ctx_t* ctx, int dtype, void* d_out, int ldo, const vo
                                        (const float*)d_residual, ldr, BT, OC, C, ctx->stream));
     GemmProblem g{BT, OC, C, (const bf16*)d_inp, ldi, 0, (const bf16*)d_weight, C, 0, d_out, ldo, GEMM_OUT_BF16,
                   (const bf16*)d_residual, ldr, 1, 0};
-    return note(ctx, gemm_bf16_umma(g, ctx->d_err, ctx->stream));
+    return note(ctx, run_umma(ctx, g));
 }
 int bmc_matmul_backward_inp(bmc_ctx_t* ctx, int dtype, void* d_ginp, int ldgi, int accumulate, const void* d_gout, int ldgo,
                             const void* d_weight, int BT, int C, int OC) {
@@ -263,7 +315,7 @@ int bmc_matmul_backward_inp(bmc_ctx_t* ctx, int dtype, void* d_ginp, int ldgi, i
     // ginp[BT, C] = gout[BT, OC] (K-major, reduction over OC) x W[OC, C] (MN-major: reduction index is W's row)
     GemmProblem g{BT, C, OC, (const bf16*)d_gout, ldgo, 0, (const bf16*)d_weight, C, 1, d_ginp, ldgi, GEMM_OUT_BF16,
                   accumulate ? (const bf16*)d_ginp : nullptr, ldgi, 1, 0};
-    return note(ctx, gemm_bf16_umma(g, ctx->d_err, ctx->stream));
+    return note(ctx, run_umma(ctx, g));
 }
 int bmc_matmul_backward_w(bmc_ctx_t* ctx, int dtype, float* d_gw, const void* d_gout, int ldgo, const void* d_inp, int ldi, int BT,
                           int C, int OC) {
@@ -278,7 +330,7 @@ int bmc_matmul_backward_w(bmc_ctx_t* ctx, int dtype, float* d_gw, const void* d_
     const int kb_total = (BT + 63) / 64;
     if (splits > kb_total / 4) splits = kb_total / 4 > 0 ? kb_total / 4 : 1;
     GemmProblem g{OC, C, BT, (const bf16*)d_gout, ldgo, 1, (const bf16*)d_inp, ldi, 1, d_gw, C, GEMM_OUT_F32_ATOMIC, nullptr, 0, splits, 0};
-    return note(ctx, gemm_bf16_umma(g, ctx->d_err, ctx->stream));
+    return note(ctx, run_umma(ctx, g));
 }
 
 // ---- RoPE --------------------------------------------------------------------------------------------

@@ -194,3 +194,10 @@ int bmx_device_upload(bm_context_t* ctx, void* d, const void* h, size_t bytes) {
 int bmx_device_sync(bm_context_t* ctx) { return ctx ? bmc_sync(ctx->be) : -1; }
 int bmx_timer_begin(bm_context_t* ctx, int slot) { return ctx ? bmc_timer_begin(ctx->be, slot) : -1; }
 float bmx_timer_end(bm_context_t* ctx, int slot) { return ctx ? bmc_timer_end(ctx->be, slot) : -1.0f; }
+float* bmx_model_weight_buffer(bm_model_t* model, size_t* n_out) {
+    if (!model) return NULL;
+    if (n_out) *n_out = model->n_parameters;
+    return model->weight_buffer;
+}
+int bmx_gemm_timing(bm_context_t* ctx, int enable) { return ctx ? bmc_gemm_timing(ctx->be, enable) : -1; }
+int bmx_gemm_timing_collect(bm_context_t* ctx, double* out3) { return ctx ? bmc_gemm_timing_collect(ctx->be, out3) : -1; }

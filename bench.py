@@ -1,0 +1,369 @@
+#!/usr/bin/env python3
+"""Benchmark of the SmolLM2 training step (forward + backward + mixed-precision AdamW).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Own arm (default): SmolLM2-360M, bf16 mixed precision, 16 sequences x 2048 tokens per GPU, random-init
+weights N(0, 0.02^2) (RMSNorm gains 1) from seed 42 and the reference's LCG token stream; one process per GPU
+(torchrun for N > 1), data-parallel with a bucketed bf16 NCCL all-reduce overlapped with backward. Prints ONE
+JSON line on rank 0:
+  value  : training tokens/s over all N GPUs with the step's token batch already resident in HBM
+           (CUDA events on the backend's stream, barrier + synchronize on both sides, max over ranks);
+  e2e    : the same through the public API bm_train_step() with HOST int32 buffers — host->device copy of
+           inputs/targets and device->host read of the loss inside the timed region, every step;
+  roofline: the tcgen05 GEMM kernel, achieved TFLOP/s = algorithmic 2*M*N*K FLOPs / per-launch CUDA-event time
+           collected live during the timed steps, against the measured bf16 peak (MEASURED_PEAKS.json);
+  cpu_baseline: the reference's own host code + kernels running on this box's CPU cores (oracle/_ref), on a
+           bounded sample of the same model (rank 0, N = 1 only).
+
+Reference arm (--impl reference): times oracle/_ref (the reference's C11 host code and its Metal kernel sources
+compiled for the CPU) on the host cores, same model, each step a bounded sample (1 sequence x 32 tokens).
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "bare.metal_b200"))
+import bmapi  # noqa: E402
+
+MODEL = "smollm2-360m"
+PER_GPU_BATCH, SEQ_LEN = 16, 2048
+METRIC = "train_tokens_per_sec"
+UNIT = "tokens/s"
+DATASHEET_BF16_TFLOPS = 2250.0
+
+
+def flops_per_token(a, S):
+    """Algorithmic training FLOPs per token: 6 x matmul parameters (tied head counted once) + causal attention
+    6*S*NH*HD*L (half of the full S^2 work), no recompute credited."""
+    HD = a.head_dim
+    per_layer = a.n_heads * HD * a.dim * 2 + 2 * a.n_kv_heads * HD * a.dim + 3 * a.hidden_dim * a.dim
+    p_mm = per_layer * a.n_layers + a.vocab_size * a.dim
+    return 6.0 * p_mm + 6.0 * S * a.n_heads * HD * a.n_layers
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return json.load(f), "measured"
+    except Exception:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.lines = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu_index)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self, t0, t1):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ts, line in self.lines:
+            if ts < t0 or ts > t1 + 0.3:
+                continue
+            p = [x.strip() for x in line.split(",")]
+            if len(p) < 9:
+                continue
+            try:
+                sm.append(float(p[1]))
+                smax = float(p[2])
+            except ValueError:
+                continue
+            for name, val in zip(names, p[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def fill_weights(lib, model, a, seed=42, std=0.02):
+    n = C.c_size_t()
+    ptr = lib.bmx_model_weight_buffer(model, C.byref(n))
+    buf = np.ctypeslib.as_array(ptr, (n.value,))
+    rng = np.random.default_rng(seed)
+    off = 0
+    for name, shape in bmapi.weight_shapes(a):
+        cnt = int(np.prod(shape))
+        if name.startswith("ln"):
+            buf[off:off + cnt] = 1.0
+        else:
+            # generate in slices to bound peak host memory
+            step = 1 << 24
+            for s in range(0, cnt, step):
+                e = min(cnt, s + step)
+                buf[off + s:off + e] = rng.standard_normal(e - s, dtype=np.float32) * np.float32(std)
+        off += cnt
+
+
+def reference_tokens_per_sec(steps, warmup, S_ref=32, B_ref=1):
+    """The reference's own training step on the host cores (oracle/_ref). Returns (tokens/s, cores, sample text)."""
+    ref = bmapi.load_reference()
+    if ref is None:
+        return None, 0, "oracle/_ref/libbm_ref.so not built", None
+    a = bmapi.make_arch(MODEL)
+    a.precision = bmapi.BM_PRECISION_BF16
+    ctx = ref.bm_create(bmapi.BM_DEVICE_METAL)
+    model = ref.bm_create_model(ctx, C.byref(a))
+    # the reference has no setter for weights either; write through its model struct's weight buffer via the .bin path
+    w_path = "/tmp/bm_bench_ref_360m.bin"
+    if not os.path.exists(w_path) or os.path.getsize(w_path) < 1000:
+        w = bmapi.make_weights(a)
+        bmapi.write_bin_checkpoint(w_path, a, w)
+        del w
+    ref.bm_load_weights(model, w_path.encode())
+    ref.bmref_set_precision(model, bmapi.BM_PRECISION_BF16)
+    cfg = bmapi.train_config(lr=3e-4, b1=0.9, b2=0.95, eps=1e-8, wd=0.1, seq_len=S_ref)
+    tr = ref.bm_create_trainer(ctx, model, C.byref(cfg))
+    x, y = bmapi.lcg_batch(B_ref * (steps + warmup), S_ref, a.vocab_size)
+    times = []
+    for i in range(steps + warmup):
+        xs = np.ascontiguousarray(x[i * B_ref:(i + 1) * B_ref])
+        ys = np.ascontiguousarray(y[i * B_ref:(i + 1) * B_ref])
+        t0 = time.perf_counter()
+        loss = ref.bm_train_step(tr, bmapi.as_int_ptr(xs), bmapi.as_int_ptr(ys), B_ref, S_ref)
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(dt)
+        if not np.isfinite(loss):
+            raise RuntimeError("reference step returned a non-finite loss")
+    ref.bm_destroy_trainer(tr)
+    ref.bm_destroy_model(model)
+    ref.bm_destroy(ctx)
+    cores = int(os.environ.get("OMP_NUM_THREADS", os.cpu_count() or 1))
+    tps = B_ref * S_ref * len(times) / sum(times)
+    sample = (f"{MODEL} bf16-weights, {B_ref} sequence x {S_ref} tokens per step, {warmup} warm-up + {len(times)} timed "
+              f"steps, reference C11 host code + its kernel sources on {cores} host threads")
+    return tps, cores, sample, sum(times) / len(times) * 1e3
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    out = reference_tokens_per_sec(args.steps, args.warmup)
+    if out[0] is None:
+        print(json.dumps({"impl": "reference", "unavailable": out[2]}))
+        return 0
+    tps, cores, sample, ms = out
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{MODEL} train step, bf16 weights / fp32 math (the reference's bf16 mode), CPU", "sample": sample},
+        "cpu_baseline": {"value": tps, "unit": UNIT, "cores": cores, "kind": "reference", "sample": sample},
+        "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="own", choices=["own", "reference"])
+    ap.add_argument("--model", default=MODEL)
+    ap.add_argument("--batch", type=int, default=PER_GPU_BATCH)
+    ap.add_argument("--seq-len", type=int, default=SEQ_LEN)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference_arm(args)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        print(f"bench.py: WORLD_SIZE={world} but --gpus {args.gpus}", file=sys.stderr)
+    B, S = args.batch, args.seq_len
+    W = max(args.warmup, 3) if args.warmup >= 0 else 3
+    K = max(args.steps, 1)
+
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local_rank))
+
+    lib = bmapi.load_product()
+    a = bmapi.make_arch(args.model)
+    a.precision = bmapi.BM_PRECISION_BF16
+    ctx = lib.bm_create(bmapi.BM_DEVICE_CUDA)
+    if not ctx:
+        raise SystemExit("bench.py: no CUDA context (the product has no CPU fallback)")
+    model = lib.bm_create_model(ctx, C.byref(a))
+    fill_weights(lib, model, a)
+    cfg = bmapi.train_config(lr=3e-4, b1=0.9, b2=0.95, eps=1e-8, wd=0.1, seq_len=S)
+    tr = lib.bm_create_trainer(ctx, model, C.byref(cfg))
+    if not tr:
+        raise SystemExit("bench.py: bm_create_trainer failed")
+
+    if world > 1:
+        import torch
+        idbuf = (C.c_ubyte * 128)()
+        if rank == 0 and lib.bmx_dp_unique_id(idbuf) != 0:
+            raise SystemExit("bench.py: bmx_dp_unique_id failed")
+        t_id = torch.tensor(list(bytes(idbuf)), dtype=torch.uint8, device="cuda")
+        dist.broadcast(t_id, src=0)
+        idbuf = (C.c_ubyte * 128)(*t_id.cpu().tolist())
+        if lib.bmx_trainer_dp_init(tr, rank, world, idbuf) != 0:
+            raise SystemExit("bench.py: bmx_trainer_dp_init failed")
+
+    # rank r takes sequences r*B .. r*B+B-1 of every global batch
+    n_steps_total = 2 * (W + K)
+    x, y = bmapi.lcg_batch(B * world * n_steps_total, S, a.vocab_size)
+    x = x.reshape(n_steps_total, world, B, S)[:, rank].copy()
+    y = y.reshape(n_steps_total, world, B, S)[:, rank].copy()
+    nbytes = B * S * 4
+    d_x = [lib.bmx_device_alloc(ctx, nbytes) for _ in range(W + K)]
+    d_y = [lib.bmx_device_alloc(ctx, nbytes) for _ in range(W + K)]
+    for i in range(W + K):
+        lib.bmx_device_upload(ctx, d_x[i], x[i].ctypes.data, nbytes)
+        lib.bmx_device_upload(ctx, d_y[i], y[i].ctypes.data, nbytes)
+    lib.bmx_device_sync(ctx)
+
+    def barrier():
+        lib.bmx_device_sync(ctx)
+        if dist is not None:
+            dist.barrier()
+        lib.bmx_device_sync(ctx)
+
+    def max_over_ranks(v):
+        if dist is None:
+            return v
+        import torch
+        t = torch.tensor([v], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---------------- leg 1: inputs resident in HBM -----------------------------------------------------------
+    for i in range(W):
+        if lib.bmx_train_step_resident(tr, d_x[i], d_y[i], B, S) != 0:
+            raise SystemExit("bench.py: warm-up step failed")
+    loss_w = lib.bmx_train_last_loss(tr)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    time.sleep(0.3)
+    barrier()
+    lib.bmx_gemm_timing(ctx, 1)
+    launches0 = lib.bmx_trainer_launch_count(tr)
+    t_wall0 = time.time()
+    lib.bmx_timer_begin(ctx, 7)
+    for i in range(K):
+        if lib.bmx_train_step_resident(tr, d_x[W + i], d_y[W + i], B, S) != 0:
+            raise SystemExit("bench.py: timed step failed")
+    ms_total = lib.bmx_timer_end(ctx, 7)
+    barrier()
+    t_wall1 = time.time()
+    launches1 = lib.bmx_trainer_launch_count(tr)
+    gt = (C.c_double * 3)()
+    lib.bmx_gemm_timing_collect(ctx, gt)
+    lib.bmx_gemm_timing(ctx, 0)
+    loss_t = lib.bmx_train_last_loss(tr)
+    clocks = sampler.stop(t_wall0, t_wall1)
+    ms_total = max_over_ranks(ms_total)
+    ms_per_step = ms_total / K
+    tokens_per_step = B * S * world
+    value = tokens_per_step / (ms_per_step * 1e-3)
+
+    # ---------------- leg 2: end to end through bm_train_step with host buffers ----------------------------------
+    for i in range(2):
+        lib.bm_train_step(tr, bmapi.as_int_ptr(x[W + K + i]), bmapi.as_int_ptr(y[W + K + i]), B, S)
+    barrier()
+    lib.bmx_timer_begin(ctx, 6)
+    t0 = time.perf_counter()
+    loss_e = 0.0
+    for i in range(K):
+        j = W + K + 2 + i
+        loss_e = lib.bm_train_step(tr, bmapi.as_int_ptr(x[j]), bmapi.as_int_ptr(y[j]), B, S)
+    ms_e2e_dev = lib.bmx_timer_end(ctx, 6)
+    barrier()
+    ms_e2e_wall = (time.perf_counter() - t0) * 1e3
+    ms_e2e = max_over_ranks(max(ms_e2e_dev, ms_e2e_wall)) / K
+    e2e_value = tokens_per_step / (ms_e2e * 1e-3)
+
+    if rank == 0:
+        peaks, peak_src = measured_peaks()
+        fpt = flops_per_token(a, S)
+        tflops = value * fpt / 1e12
+        n_l, g_ms, g_fl = gt[0], gt[1], gt[2]
+        ach = (g_fl / (g_ms * 1e-3) / 1e12) if g_ms > 0 else None
+        peak_tf = peaks.get("bf16_tflops_sustained", peaks.get("bf16_tflops"))
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{args.model} training step (fwd+bwd+AdamW), bf16 mixed precision, {B} seq x {S} tokens per GPU",
+                       "global_batch": B * world, "seq_len": S, "parallelism": f"dp{world}",
+                       "optimizer": "AdamW lr 3e-4 beta (0.9, 0.95) eps 1e-8 wd 0.1, fp32 master + moments",
+                       "l2": "no explicit flush: each step streams tens of GB of activations and weights, far beyond the 126 MB L2"},
+            "tflops_per_gpu": tflops / world, "flops_per_token": fpt,
+            "mfu_vs_datasheet_2250": tflops / world / DATASHEET_BF16_TFLOPS,
+            "mfu_vs_measured_sustained": tflops / world / peak_tf,
+            "loss": {"after_warmup": loss_w, "after_timed": loss_t, "after_e2e": loss_e},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": 2 * nbytes * world,
+                    "d2h_bytes_per_step": 4 * world},
+            "gpu_launches": int(launches1 - launches0),
+            "roofline": {"kernel": "gemm_bf16_umma_kernel (tcgen05)", "bound": "tensor", "achieved": ach, "peak": peak_tf,
+                         "unit": "TFLOP/s", "frac": (ach / peak_tf) if ach else None, "traffic": None,
+                         "peak_source": f"bf16_tflops_sustained of {peak_src}", "launches": int(n_l),
+                         "avg_launch_ms": (g_ms / n_l) if n_l else None, "avg_launch_flops": (g_fl / n_l) if n_l else None,
+                         "share_of_step": (g_ms / ms_total) if ms_total else None},
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            try:
+                tps, cores, sample, _ = reference_tokens_per_sec(1, 1)
+                line["cpu_baseline"] = {"value": tps, "unit": UNIT, "cores": cores, "kind": "reference", "sample": sample}
+            except Exception as e:  # the checker is absent: report it, never substitute
+                line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": 0, "kind": "reference", "sample": f"unavailable: {e}"}
+        print(json.dumps(line), flush=True)
+
+    lib.bm_destroy_trainer(tr)
+    lib.bm_destroy_model(model)
+    lib.bm_destroy(ctx)
+    if dist is not None:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -56,6 +56,13 @@ int    bmx_device_sync(bm_context_t* ctx);
 int    bmx_timer_begin(bm_context_t* ctx, int slot);
 float  bmx_timer_end(bm_context_t* ctx, int slot);
 
+/* Host weight buffer of a model (fp32, the flat order of the legacy .bin payload): lets a caller fill in
+ * weights without going through a file. *n_out receives the element count. */
+float* bmx_model_weight_buffer(bm_model_t* model, size_t* n_out);
+/* per-launch timing of the tensor-core GEMM (see bmc_gemm_timing in bm_cuda_backend.h) */
+int    bmx_gemm_timing(bm_context_t* ctx, int enable);
+int    bmx_gemm_timing_collect(bm_context_t* ctx, double* out3);
+
 /* Data parallel: every rank holds a full replica and calls bm_train_step with its own B sequences;
  * gradients are summed across ranks (bf16 buckets over NCCL, overlapped with backward) before AdamW and the
  * returned loss is the mean over all ranks. `nccl_id` is the 128-byte ncclUniqueId created on rank 0 with

@@ -57,6 +57,13 @@ void       bmc_host_free(void* p);
 int        bmc_timer_begin(bmc_ctx_t* ctx, int slot);
 float      bmc_timer_end(bmc_ctx_t* ctx, int slot);
 
+/* Per-launch timing of the tensor-core GEMM kernel: while enabled every launch is bracketed by CUDA events on the
+ * compute stream. collect() waits for the stream and returns out[0] = launches, out[1] = summed kernel time in ms,
+ * out[2] = summed algorithmic FLOPs (2*M*N*K) since enable/collect. (The reference accumulates whole-command-buffer
+ * GPU time instead: backend_get_gpu_busy_ms, src/backend/backend.h:32-34.) */
+int        bmc_gemm_timing(bmc_ctx_t* ctx, int enable);
+int        bmc_gemm_timing_collect(bmc_ctx_t* ctx, double* out3);
+
 /* ---- embedding (embed_lookup src/baremetal/trainer.c:275-298; embedding_backward src/kernels/backward.metal:636) ---- */
 int bmc_embedding_forward(bmc_ctx_t* ctx, int dtype, void* d_out, const float* d_table_f32, const int* d_tokens, int n_tok, int D);
 int bmc_embedding_backward(bmc_ctx_t* ctx, int dtype, float* d_gwte_f32, const void* d_gout, const int* d_tokens, int n_tok, int D);
