@@ -81,6 +81,25 @@ struct bm_dp_s {
 
 extern "C" {
 
+// Bucket plan (pure host logic): groups of `layers_per_bucket` layers, highest layers first — the order in which
+// backward completes them — then one tail bucket holding the final norm and the tied embedding, which the
+// embedding scatter completes last. Bucket i covers elements [begin[i], end[i]) of the flat parameter order and is
+// complete when backward reports ready_at[i] (a layer index, or -1 for the tail). Returns the bucket count;
+// fills the arrays when cap is large enough.
+int bmx_dp_plan_buckets(int n_layers, const size_t* layer_begin, size_t n_params_total, int layers_per_bucket, size_t* begin,
+                        size_t* end, int* ready_at, int cap) {
+    if (layers_per_bucket < 1) layers_per_bucket = 1;
+    int n = 0;
+    for (int hi = n_layers; hi > 0; hi -= layers_per_bucket) {
+        const int lo = hi - layers_per_bucket > 0 ? hi - layers_per_bucket : 0;
+        if (n < cap && begin) { begin[n] = layer_begin[lo]; end[n] = layer_begin[hi]; ready_at[n] = lo; }
+        ++n;
+    }
+    if (n < cap && begin) { begin[n] = layer_begin[n_layers]; end[n] = n_params_total; ready_at[n] = -1; }
+    ++n;
+    return n;
+}
+
 int bmx_dp_unique_id(void* out_id) {
     NcclApi* api = nccl();
     if (!api || !out_id) return -1;
@@ -116,16 +135,14 @@ struct bm_dp_s* bm_dp_create(bmc_ctx_t* be, int rank, int world, const void* ncc
         delete dp;
         return nullptr;
     }
-    // Buckets of ~4 layers, highest layers first in completion order. The tail (final norm + embedding)
-    // is one bucket completed by the embedding scatter.
     int per = 4;
     const char* e = getenv("BM_DP_LAYERS_PER_BUCKET");
     if (e && atoi(e) > 0) per = atoi(e);
-    for (int hi = n_layers; hi > 0; hi -= per) {
-        const int lo = hi - per > 0 ? hi - per : 0;
-        dp->buckets.push_back(Bucket{layer_begin[lo], layer_begin[hi], lo});
-    }
-    dp->buckets.push_back(Bucket{layer_begin[n_layers], P, -1});
+    const int nb = bmx_dp_plan_buckets(n_layers, layer_begin, P, per, nullptr, nullptr, nullptr, 0);
+    std::vector<size_t> bb(nb), be_(nb);
+    std::vector<int> br(nb);
+    bmx_dp_plan_buckets(n_layers, layer_begin, P, per, bb.data(), be_.data(), br.data(), nb);
+    for (int i = 0; i < nb; ++i) dp->buckets.push_back(Bucket{bb[i], be_[i], br[i]});
     dp->ready_ev.resize(dp->buckets.size());
     for (auto& ev : dp->ready_ev) cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
     return dp;

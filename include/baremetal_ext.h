@@ -68,6 +68,9 @@ int    bmx_gemm_timing_collect(bm_context_t* ctx, double* out3);
  * returned loss is the mean over all ranks. `nccl_id` is the 128-byte ncclUniqueId created on rank 0 with
  * bmx_dp_unique_id() and handed to the other ranks by the launcher. */
 #define BMX_DP_ID_BYTES 128
+/* The gradient bucket plan as pure host logic (no GPU needed): see the definition for the meaning of the arrays. */
+int    bmx_dp_plan_buckets(int n_layers, const size_t* layer_begin, size_t n_params_total, int layers_per_bucket, size_t* begin,
+                           size_t* end, int* ready_at, int cap);
 int    bmx_dp_unique_id(void* out_id);
 int    bmx_trainer_dp_init(bm_trainer_t* t, int rank, int world, const void* nccl_id);
 

@@ -1,0 +1,79 @@
+"""Data-parallel arithmetic, checked with two CPU ranks over gloo.
+
+The product's exchange step is: every rank computes the gradient sum of its own sequences, the buckets are all-reduced
+(sum), and AdamW scales by 1 / (sequences per rank * world). Here each rank runs the plain-C oracle (exact-gradient mode)
+on its half of a batch, the flat gradients are all-reduced bucket by bucket following the product's bucket plan, and the
+result must equal a single process running the whole batch — the same identity the GPU path relies on.
+"""
+import ctypes as C
+import os
+import socket
+
+import numpy as np
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import bmapi
+import oracle_check as oc
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, B_per, S, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    a = bmapi.make_arch("tiny")
+    w = bmapi.make_weights(a)
+    cfg = bmapi.train_config(seq_len=S)
+    x, y = bmapi.lcg_batch(B_per * world, S, a.vocab_size)
+    xs = np.ascontiguousarray(x[rank * B_per:(rank + 1) * B_per])  # rank r takes sequences r*B .. r*B+B-1
+    ys = np.ascontiguousarray(y[rank * B_per:(rank + 1) * B_per])
+    tr = oc.PortTrainer(a, w, S, 0, cfg, quirks=0)
+    loss = tr.step(xs, ys)
+    n = tr.n_tensors()
+    sizes = [tr.read(bmapi.BMX_GRAD, i).size for i in range(n)]
+    flat = torch.from_numpy(np.concatenate([tr.read(bmapi.BMX_GRAD, i) for i in range(n)]))
+    # the product's bucket plan over the flat parameter order
+    lib = bmapi.load_product()
+    lib.bmx_dp_plan_buckets.restype = C.c_int
+    L = a.n_layers
+    offs = np.concatenate(([0], np.cumsum(sizes)))
+    layer_begin = (C.c_size_t * (L + 1))(*[int(offs[9 * l]) for l in range(L + 1)])
+    nb = lib.bmx_dp_plan_buckets(L, layer_begin, C.c_size_t(int(offs[-1])), 1, None, None, None, 0)
+    b, e, r = (C.c_size_t * nb)(), (C.c_size_t * nb)(), (C.c_int * nb)()
+    lib.bmx_dp_plan_buckets(L, layer_begin, C.c_size_t(int(offs[-1])), 1, b, e, r, nb)
+    touched = torch.zeros(flat.numel(), dtype=torch.int32)
+    for i in range(nb):  # buckets in the order backward completes them
+        seg = flat[b[i]:e[i]].clone()
+        dist.all_reduce(seg)
+        flat[b[i]:e[i]] = seg
+        touched[b[i]:e[i]] += 1
+    assert int(touched.min()) == 1 and int(touched.max()) == 1  # every element reduced exactly once
+    lt = torch.tensor([loss], dtype=torch.float64)
+    dist.all_reduce(lt)
+    if rank == 0:
+        np.save(os.path.join(out_dir, "grad_sum.npy"), flat.numpy())
+        np.save(os.path.join(out_dir, "loss.npy"), np.array([lt.item() / world]))
+    tr.close()
+    dist.destroy_process_group()
+
+
+def test_two_rank_gradient_exchange_equals_the_full_batch(tmp_path):
+    world, B_per, S = 2, 2, 16
+    mp.spawn(_worker, args=(world, _free_port(), B_per, S, str(tmp_path)), nprocs=world, join=True)
+    a = bmapi.make_arch("tiny")
+    w = bmapi.make_weights(a)
+    cfg = bmapi.train_config(seq_len=S)
+    x, y = bmapi.lcg_batch(B_per * world, S, a.vocab_size)
+    tr = oc.PortTrainer(a, w, S, 0, cfg, quirks=0)
+    loss = tr.step(x, y)
+    full = np.concatenate([tr.read(bmapi.BMX_GRAD, i) for i in range(tr.n_tensors())])
+    tr.close()
+    got = np.load(tmp_path / "grad_sum.npy")
+    assert oc.rel_err(got, full) < 1e-5
+    assert abs(float(np.load(tmp_path / "loss.npy")[0]) - loss) < 1e-5

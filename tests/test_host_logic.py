@@ -1,0 +1,132 @@
+"""Host-side behaviour that needs no GPU: synthetic inputs, file formats, model layout, loud failure without a device,
+the greedy sampler, and the data-parallel bucket plan."""
+import ctypes as C
+import os
+import struct
+
+import numpy as np
+import pytest
+
+import bmapi
+import portk
+
+
+def test_lcg_stream_matches_the_scalar_recurrence():
+    s, out = 42, []
+    for _ in range(200):
+        s = (s * 1664525 + 1013904223) & 0xFFFFFFFF  # bench/train_bench.c:286-290
+        out.append(s % 49152)
+    assert bmapi.lcg_tokens(200, 49152).tolist() == out
+    x, y = bmapi.lcg_batch(3, 8, 1000)
+    flat = bmapi.lcg_tokens(25, 1000)
+    assert x.ravel().tolist() == flat[:24].tolist() and y.ravel().tolist() == flat[1:25].tolist()
+
+
+def test_parameter_counts_of_the_named_models():
+    for name, n in (("smollm2-135m", 134515008), ("smollm2-360m", 361821120)):
+        a = bmapi.make_arch(name)
+        total = sum(int(np.prod(shape)) for _, shape in bmapi.weight_shapes(a))
+        assert total == n
+
+
+def test_bin_checkpoint_round_trip_through_the_host_layer(product, tmp_path):
+    lib = product
+    a = bmapi.make_arch("tiny")
+    w = bmapi.make_weights(a, seed=3)
+    path = str(tmp_path / "tiny.bin")
+    bmapi.write_bin_checkpoint(path, a, w)
+    with open(path, "rb") as f:
+        hdr = struct.unpack("<256i", f.read(1024))
+    assert hdr[0] == 20250718 and hdr[3] == a.dim and hdr[8] == a.vocab_size and hdr[23] == 100000
+    # bm_create_model / bm_load_weights are host-only and work without a GPU
+    model = lib.bm_create_model(None, C.byref(a))
+    assert model
+    lib.bm_load_weights(model, path.encode())
+    n = C.c_size_t()
+    ptr = lib.bmx_model_weight_buffer(model, C.byref(n))
+    flat = np.ctypeslib.as_array(ptr, (n.value,))
+    expect = np.concatenate([w[k].ravel() for k, _ in bmapi.weight_shapes(a)])
+    assert n.value == expect.size == lib.bm_get_num_parameters(model)
+    assert np.array_equal(flat, expect)
+    lib.bm_destroy_model(model)
+
+
+def test_unsupported_architectures_are_rejected(product):
+    lib = product
+    for field in ("bias", "has_qk_norm", "has_ffn_post_norm", "gemma_norm", "embed_scale"):
+        a = bmapi.make_arch("tiny")
+        setattr(a, field, 1)
+        assert not lib.bm_create_model(None, C.byref(a)), field  # bmt_arch_validate, src/baremetal/model.c:14-40
+    a = bmapi.make_arch("tiny")
+    a.weight_tie = 0
+    assert not lib.bm_create_model(None, C.byref(a))
+
+
+def test_no_gpu_means_no_context_not_a_fallback(product):
+    """On a machine without an sm_100 GPU bm_create returns NULL; BM_DEVICE_CPU never yields a context."""
+    lib = product
+    assert not lib.bm_create(bmapi.BM_DEVICE_CPU)
+    ctx = lib.bm_create(bmapi.BM_DEVICE_CUDA)
+    try:
+        import torch
+        has_gpu = torch.cuda.is_available()
+    except Exception:
+        has_gpu = os.path.exists("/dev/nvidia0")
+    if not has_gpu:
+        assert not ctx
+    elif ctx:
+        lib.bm_destroy(ctx)
+
+
+def test_out_of_scope_entry_points_return_their_failure_values(product):
+    lib = product
+    lib.bm_create_session.restype = C.c_void_p
+    lib.bm_create_tokenizer.restype = C.c_void_p
+    assert not lib.bm_create_session(None, None)
+    assert not lib.bm_create_tokenizer(b"/nonexistent")
+    assert lib.bm_load_adapter(None, b"x") == -1
+    assert lib.bm_save_adapter(None, b"x") == -1
+
+
+def test_greedy_sampler_takes_the_first_maximum(product):
+    lib = product
+    rng = np.random.default_rng(0)
+    for trial in range(20):
+        V = int(rng.integers(5, 3000))
+        logits = rng.standard_normal(V).astype(np.float32)
+        if trial % 2:  # plant ties
+            logits[rng.integers(0, V, 4)] = logits.max() + 1.0
+        s = lib.bm_create_sampler(V, 0.0, 0.9, 1)
+        got = lib.bm_sample(s, logits.ctypes.data_as(C.POINTER(C.c_float)))
+        lib.bm_destroy_sampler(s)
+        assert got == int(np.argmax(logits)) == portk.argmax(logits)
+
+
+def test_state_file_reader_matches_the_documented_layout(tmp_path):
+    path = tmp_path / "state.bin"
+    with open(path, "wb") as f:
+        f.write(struct.pack("<ii", 7, 2))
+        for n in (3, 5):
+            f.write(struct.pack("<Q", n))
+            for k in range(3):
+                f.write((np.arange(n, dtype=np.float32) + k).tobytes())
+    step, tensors = bmapi.read_state_file(str(path))
+    assert step == 7 and len(tensors) == 2
+    assert tensors[1][2].tolist() == [2, 3, 4, 5, 6]
+
+
+def test_dp_bucket_plan_partitions_the_parameters(product):
+    lib = product
+    lib.bmx_dp_plan_buckets.restype = C.c_int
+    for L, per in ((32, 4), (30, 4), (2, 4), (7, 3), (5, 1)):
+        layer_begin = (C.c_size_t * (L + 1))(*[100 * l for l in range(L + 1)])
+        P = 100 * L + 50 + 7777
+        n = lib.bmx_dp_plan_buckets(L, layer_begin, C.c_size_t(P), per, None, None, None, 0)
+        b, e, r = (C.c_size_t * n)(), (C.c_size_t * n)(), (C.c_int * n)()
+        assert lib.bmx_dp_plan_buckets(L, layer_begin, C.c_size_t(P), per, b, e, r, n) == n
+        spans = sorted(zip(list(b), list(e)))
+        assert spans[0][0] == 0 and spans[-1][1] == P
+        assert all(spans[i][1] == spans[i + 1][0] for i in range(n - 1))  # exact partition, no overlap
+        assert list(r)[-1] == -1 and list(r)[:-1] == sorted(list(r)[:-1], reverse=True)  # completion order of backward
+        for bi, ri in zip(list(b)[:-1], list(r)[:-1]):
+            assert bi == 100 * ri  # a bucket is complete when its lowest layer is

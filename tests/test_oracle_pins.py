@@ -1,0 +1,255 @@
+"""Pins the CPU oracle (oracle/bm_oracle.c) before anything trusts it:
+ 1. against the golden vectors of the reference's own PyTorch generators (tests/golden/torch_kernel_goldens.npz, made by
+    tests/golden/make_golden.py running test/grad/gen_*.py unmodified) — the same vectors and the same cosine > 0.9999
+    criterion the reference's kernel tests use (e.g. test/matmul_bwd_test.c, test/attn_real_test.c), plus a tight max-abs bound;
+ 2. against golden outputs of the reference's training step executed on CPU (tests/golden/ref_train_step_*.npz);
+ 3. against that reference build itself when oracle/_ref/libbm_ref.so is present.
+"""
+import glob
+import os
+
+import numpy as np
+import pytest
+
+import bmapi
+import oracle_check as oc
+import portk
+
+GOLD_DIR = os.path.join(bmapi.ROOT, "tests", "golden")
+
+
+def close(a, b, tol=2e-5):
+    a, b = np.asarray(a, np.float64).ravel(), np.asarray(b, np.float64).ravel()
+    cos = a @ b / (np.linalg.norm(a) * np.linalg.norm(b) + 1e-30)
+    assert cos > 0.9999, cos
+    scale = max(1.0, np.abs(b).max())
+    assert np.abs(a - b).max() <= tol * scale, np.abs(a - b).max()
+
+
+def test_matmul_backward(goldens):
+    g = goldens
+    inp, w, gout = g["inp"].reshape(3, 16), g["w"].reshape(8, 16), g["gout"].reshape(3, 8)
+    close(portk.matmul_backward_inp(gout, w), g["ginp"])
+    close(portk.matmul_backward_w(gout, inp), g["gw"])
+
+
+def test_rmsnorm_backward(goldens):
+    g = goldens
+    x, w, go = g["rms_x"].reshape(4, 24), g["rms_w"], g["rms_gout"].reshape(4, 24)
+    close(portk.rmsnorm_backward_x(go, w, x), g["rms_gx"])
+    close(portk.rmsnorm_backward_w(go, x), g["rms_gw"])
+
+
+def test_rope_backward_single_position(goldens):
+    g = goldens  # NH=6 NKV=2 HD=8 pos=3 theta=1e4: place the vectors at row 3 of a 4-row sequence
+    gq, gk = np.zeros((4, 6, 8), np.float32), np.zeros((4, 2, 8), np.float32)
+    gq[3], gk[3] = g["rope_gout_q"].reshape(6, 8), g["rope_gout_k"].reshape(2, 8)
+    rq, rk = portk.rope_seq(gq, gk, 10000.0, -1)
+    close(rq[3], g["rope_gq"])
+    close(rk[3], g["rope_gk"])
+
+
+@pytest.mark.parametrize("prefix,NH,NKV,HD,S,theta", [("roseq", 4, 2, 8, 5, 10000.0), ("roreal", 9, 3, 64, 4, 100000.0)])
+def test_rope_seq_backward(goldens, prefix, NH, NKV, HD, S, theta):
+    g = goldens
+    rq, rk = portk.rope_seq(g[prefix + "_gout_q"].reshape(S, NH, HD), g[prefix + "_gout_k"].reshape(S, NKV, HD), theta, -1)
+    close(rq, g[prefix + "_gQ"])
+    close(rk, g[prefix + "_gK"])
+
+
+def test_rope_forward_is_inverse_of_backward(goldens):
+    g = goldens
+    q, k = g["roreal_Q"].reshape(4, 9, 64), g["roreal_K"].reshape(4, 3, 64)
+    fq, fk = portk.rope_seq(q, k, 100000.0, +1)
+    bq, bk = portk.rope_seq(fq, fk, 100000.0, -1)
+    close(bq, q)
+    close(bk, k)
+
+
+def test_swiglu_backward(goldens):
+    g = goldens
+    gg, gu = portk.swiglu_backward(g["swiglu_gate"], g["swiglu_up"], g["swiglu_gout"])
+    close(gg, g["swiglu_ggate"])
+    close(gu, g["swiglu_gup"])
+
+
+def test_xent_backward(goldens):
+    g = goldens
+    loss, grad = portk.xent(g["xent_logits"].reshape(3, 10), g["xent_targets"])
+    close(grad, g["xent_glogits"])
+    lg = g["xent_logits"].reshape(3, 10).astype(np.float64)
+    ref_loss = np.mean([-(lg[n, t] - np.log(np.exp(lg[n]).sum())) for n, t in enumerate(g["xent_targets"])])
+    assert abs(loss - ref_loss) < 1e-5
+
+
+def test_embedding_backward_with_repeated_tokens(goldens):
+    g = goldens
+    out = portk.embedding_backward(np.zeros((8, 5), np.float32), g["embed_gout"].reshape(6, 5), g["embed_tokens"])
+    close(out, g["embed_gwte"])
+    assert len(set(g["embed_tokens"].tolist())) < 6  # the fixture does repeat tokens
+
+
+@pytest.mark.parametrize("prefix,lr,wd", [("", 1e-2, 0.1), ("wd0_", 1e-3, 0.0)])
+def test_adamw_step(goldens, prefix, lr, wd):
+    g = goldens  # betas (0.9, 0.999), eps 1e-8, t = 1; (lr 1e-2, wd 0.1) from gen_adamw.py, (lr 1e-3, wd 0) from gen_adamw_wd0.py / test/adamw_test.c:49
+    b1, b2 = 0.9, 0.999
+    hp = [lr, b1, b2, 1e-8, wd, 1 - b1, 1 - b2, 1.0]
+    w, m, v = portk.adamw(g[prefix + "adamw_w0"], g[prefix + "adamw_g"], np.zeros(64, np.float32), np.zeros(64, np.float32), hp)
+    close(w, g[prefix + "adamw_w"], 1e-6)
+    close(m, g[prefix + "adamw_m"], 1e-6)
+    close(v, g[prefix + "adamw_v"], 1e-6)
+
+
+@pytest.mark.parametrize("prefix,NH,NKV,HD,S", [("attn", 4, 2, 4, 3), ("attn_real", 9, 3, 64, 4)])
+def test_attention_forward_backward(goldens, prefix, NH, NKV, HD, S):
+    g = goldens
+    Q, K, V = (g[f"{prefix}_{n}"].reshape(S, h, HD) for n, h in (("Q", NH), ("K", NKV), ("V", NKV)))
+    scale = 1.0 / np.sqrt(HD)
+    close(portk.attention_forward(Q, K, V, scale), g[prefix + "_out"])
+    gq, gk, gv = portk.attention_backward(g[prefix + "_gout"].reshape(S, NH, HD), Q, K, V, scale)
+    close(gq, g[prefix + "_gQ"])
+    close(gk, g[prefix + "_gK"])
+    close(gv, g[prefix + "_gV"])
+
+
+def test_matmul_rmsnorm_matmul_chain(goldens):
+    g = goldens  # test/sched_bwd_test.c: matmul -> rmsnorm -> matmul, BT4 C16 OC8 OC5
+    inp, w1, rw, w2, gout = g["sb_inp"].reshape(4, 16), g["sb_w1"].reshape(8, 16), g["sb_rmsw"], g["sb_w2"].reshape(5, 8), g["sb_gout"].reshape(4, 5)
+    h = portk.matmul_forward(inp, w1)
+    hn = portk.rmsnorm_forward(h, rw)
+    out = portk.matmul_forward(hn, w2)
+    close(h, g["sb_h"]); close(hn, g["sb_hn"]); close(out, g["sb_out"])
+    ghn = portk.matmul_backward_inp(gout, w2)
+    close(portk.matmul_backward_w(gout, hn), g["sb_gw2"])
+    close(portk.rmsnorm_backward_w(ghn, h), g["sb_grmsw"])
+    gh = portk.rmsnorm_backward_x(ghn, rw, h)
+    close(portk.matmul_backward_w(gh, inp), g["sb_gw1"])
+    close(portk.matmul_backward_inp(gh, w1), g["sb_ginp"])
+
+
+def test_full_decoder_layer(goldens):
+    """One decoder layer, forward intermediates and all ten gradients (test/layer_bwd_test.c; S8 D64 NH4 NKV1 HD16 HID128)."""
+    g = goldens
+    S, D, NH, NKV, HD, HID, theta = 8, 64, 4, 1, 16, 128, 10000.0
+    KV = NKV * HD
+    inp, rw1, rw2 = g["layer_inp"].reshape(S, D), g["layer_rmsw1"], g["layer_rmsw2"]
+    wq, wk, wv = g["layer_wq"].reshape(D, D), g["layer_wk"].reshape(KV, D), g["layer_wv"].reshape(KV, D)
+    wo, wg, wu, wd = g["layer_wproj"].reshape(D, D), g["layer_wgate"].reshape(HID, D), g["layer_wup"].reshape(HID, D), g["layer_wdown"].reshape(D, HID)
+    scale = 1.0 / np.sqrt(HD)
+    n1 = portk.rmsnorm_forward(inp, rw1)
+    q, k, v = portk.matmul_forward(n1, wq), portk.matmul_forward(n1, wk), portk.matmul_forward(n1, wv)
+    qr, kr = portk.rope_seq(q.reshape(S, NH, HD), k.reshape(S, NKV, HD), theta, +1)
+    att = portk.attention_forward(qr, kr, v.reshape(S, NKV, HD), scale).reshape(S, D)
+    res1 = inp + portk.matmul_forward(att, wo)
+    n2 = portk.rmsnorm_forward(res1, rw2)
+    gate, up = portk.matmul_forward(n2, wg), portk.matmul_forward(n2, wu)
+    act = portk.swiglu_forward(gate, up)
+    res2 = res1 + portk.matmul_forward(act, wd)
+    for name, val in (("n1", n1), ("q", qr), ("k", kr), ("attn_out", att), ("res1", res1), ("n2", n2), ("res2", res2)):
+        close(val, g["layer_" + name], 1e-4)
+    gres = g["layer_gout"].reshape(S, D).copy()
+    close(portk.matmul_backward_w(gres, act), g["layer_gwdown"], 1e-4)
+    gact = portk.matmul_backward_inp(gres, wd)
+    gg, gu = portk.swiglu_backward(gate, up, gact)
+    close(portk.matmul_backward_w(gg, n2), g["layer_gwgate"], 1e-4)
+    close(portk.matmul_backward_w(gu, n2), g["layer_gwup"], 1e-4)
+    gn2 = portk.matmul_backward_inp(gu, wu, portk.matmul_backward_inp(gg, wg))
+    close(portk.rmsnorm_backward_w(gn2, res1), g["layer_grmsw2"], 1e-4)
+    gres = portk.rmsnorm_backward_x(gn2, rw2, res1, gres)
+    close(portk.matmul_backward_w(gres, att), g["layer_gwproj"], 1e-4)
+    gatt = portk.matmul_backward_inp(gres, wo)
+    gq, gk, gv = portk.attention_backward(gatt.reshape(S, NH, HD), qr, kr, v.reshape(S, NKV, HD), scale)
+    gq, gk = portk.rope_seq(gq, gk, theta, -1)
+    gq, gk, gv = gq.reshape(S, D), gk.reshape(S, KV), gv.reshape(S, KV)
+    close(portk.matmul_backward_w(gq, n1), g["layer_gwq"], 1e-4)
+    close(portk.matmul_backward_w(gk, n1), g["layer_gwk"], 1e-4)
+    close(portk.matmul_backward_w(gv, n1), g["layer_gwv"], 1e-4)
+    gn1 = portk.matmul_backward_inp(gv, wv, portk.matmul_backward_inp(gk, wk, portk.matmul_backward_inp(gq, wq)))
+    close(portk.rmsnorm_backward_w(gn1, inp), g["layer_grmsw1"], 1e-4)
+    close(portk.rmsnorm_backward_x(gn1, rw1, inp, gres), g["layer_ginp"], 1e-4)
+
+
+def test_argmax_takes_the_lowest_index_among_maxima():
+    x = np.array([0.5, 2.0, -1.0, 2.0, 2.0, 1.0], np.float32)
+    assert portk.argmax(x) == 1  # strict '>' scan, src/baremetal/sampler.c:36-40
+    assert portk.argmax(np.zeros(7, np.float32)) == 0
+
+
+# ---- the training step as a whole ------------------------------------------------------------------------------
+def _run_port(meta, quirks=oc.Q_ALL):
+    arch = str(meta["arch"])
+    B, S, prec, steps, accum = (int(meta[k]) for k in ("B", "S", "precision", "steps", "accum"))
+    a = bmapi.make_arch(arch)
+    w = bmapi.make_weights(a)
+    cfg = bmapi.train_config(seq_len=S, accum=accum)
+    x, y = bmapi.lcg_batch(B * steps * accum, S, a.vocab_size)
+    tr = oc.PortTrainer(a, w, S, prec, cfg, quirks=quirks)
+    losses, grads = [], None
+    for st in range(steps * accum):
+        losses.append(tr.step(np.ascontiguousarray(x[st * B:(st + 1) * B]), np.ascontiguousarray(y[st * B:(st + 1) * B])))
+        if st == accum - 1:
+            grads = [tr.read(bmapi.BMX_GRAD, i) for i in range(tr.n_tensors())]
+    weights = [tr.read(bmapi.BMX_WEIGHT, i) for i in range(tr.n_tensors())]
+    tr.close()
+    return losses, grads, weights
+
+
+def check_against_train_golden(meta, losses, grads, weights, rel_tol, loss_tol):
+    assert np.abs(np.array(losses) - meta["losses"]).max() < loss_tol, (losses, meta["losses"])
+    for i in range(int(meta["n_tensors"])):
+        idx = meta["grad_idx"][i]
+        idx = idx[idx >= 0]
+        gn = float(meta["grad_norm"][i])
+        assert abs(np.linalg.norm(grads[i].astype(np.float64)) - gn) <= rel_tol * gn + 1e-12, i
+        assert np.abs(grads[i][idx] - meta["grad_val"][i][:idx.size]).max() <= rel_tol * max(np.abs(meta["grad_val"][i]).max(), gn / np.sqrt(grads[i].size)) * 10 + 1e-12, i
+        wn = float(meta["weight_norm"][i])
+        assert abs(np.linalg.norm(weights[i].astype(np.float64)) - wn) <= rel_tol * wn, i
+        assert np.abs(weights[i][idx] - meta["weight_val"][i][:idx.size]).max() <= 10 * rel_tol * max(1e-3, np.abs(meta["weight_val"][i]).max()), i
+
+
+SMALL_CASES = sorted(os.path.basename(p)[len("ref_train_step_"):-4] for p in glob.glob(os.path.join(GOLD_DIR, "ref_train_step_*.npz"))
+                     if "135m" not in p)
+
+
+@pytest.mark.parametrize("case", SMALL_CASES)
+def test_port_matches_reference_train_step_golden(case):
+    meta = np.load(os.path.join(GOLD_DIR, f"ref_train_step_{case}.npz"))
+    losses, grads, weights = _run_port(meta)
+    check_against_train_golden(meta, losses, grads, weights, rel_tol=2e-5, loss_tol=2e-5)
+
+
+def test_goldens_exist():
+    assert len(SMALL_CASES) >= 5
+    assert os.path.exists(os.path.join(GOLD_DIR, "ref_train_step_135m_f32_c1.npz"))
+
+
+@pytest.mark.skipif(bmapi.load_reference() is None, reason="reference build oracle/_ref/libbm_ref.so not present")
+@pytest.mark.parametrize("arch,B,S,prec", [("tiny", 2, 16, 0), ("tiny", 1, 24, 2), ("small", 3, 24, 0)])
+def test_port_matches_live_reference_build(arch, B, S, prec):
+    a = bmapi.make_arch(arch)
+    w = bmapi.make_weights(a, seed=7)
+    cfg = bmapi.train_config(seq_len=S)
+    x, y = bmapi.lcg_batch(B * 2, S, a.vocab_size, seed=9)
+    r = oc.LibTrainer(bmapi.load_reference(), "reference", a, w, S, prec, cfg)
+    p = oc.PortTrainer(a, w, S, prec, cfg)
+    for st in range(2):
+        xs, ys = np.ascontiguousarray(x[st * B:(st + 1) * B]), np.ascontiguousarray(y[st * B:(st + 1) * B])
+        assert abs(r.step(xs, ys) - p.step(xs, ys)) < 2e-6
+        for i in range(p.n_tensors()):
+            assert oc.rel_err(p.read(bmapi.BMX_GRAD, i), r.read(bmapi.BMX_GRAD, i)) < 1e-5, (st, i)
+    for i in range(p.n_tensors()):
+        assert oc.rel_err(p.read(bmapi.BMX_WEIGHT, i), r.read(bmapi.BMX_WEIGHT, i)) < 1e-5
+    r.close(); p.close()
+
+
+def test_quirk_flags_change_only_what_they_name():
+    """With a single sequence per window the three reference deviations vanish: flags on == flags off."""
+    a = bmapi.make_arch("tiny")
+    w = bmapi.make_weights(a)
+    cfg = bmapi.train_config(seq_len=16)
+    x, y = bmapi.lcg_batch(1, 16, a.vocab_size)
+    t1, t0 = oc.PortTrainer(a, w, 16, 0, cfg, quirks=oc.Q_ALL), oc.PortTrainer(a, w, 16, 0, cfg, quirks=0)
+    assert t1.step(x, y) == t0.step(x, y)
+    for i in range(t1.n_tensors()):
+        assert np.array_equal(t1.read(bmapi.BMX_GRAD, i), t0.read(bmapi.BMX_GRAD, i))
+    t1.close(); t0.close()
