@@ -77,6 +77,18 @@ int bmc_rmsnorm_forward(bmc_ctx_t* ctx, int dtype, void* d_out, float* d_rstd, c
 int bmc_rmsnorm_backward(bmc_ctx_t* ctx, int dtype, void* d_gx, float* d_gw_f32, int gw_accumulate, const void* d_gout, const void* d_x,
                          const float* d_w, const float* d_rstd, int N, int C, int w_row0, int w_row1);
 
+/* RMSNorm backward without any allocation — no counterpart in the reference (its backend allocates buffers freely and
+ * has no such variant). Same arithmetic and arguments as bmc_rmsnorm_backward, but it takes the raw cudaStream_t to
+ * enqueue on instead of a context, and its partial-sum scratch is a fixed array inside the library (about 2.3 MiB per
+ * GPU, held until exit). For hosts that own all device memory themselves or must never hit the implicit device
+ * synchronisation of cudaMalloc/cudaFree in steady state. C must be <= BMC_STATIC_RMS_MAX_C, otherwise
+ * BMC_ERR_STATIC_TOO_LARGE is returned and nothing is enqueued. All calls on a GPU share the scratch: do not let two of
+ * them overlap on the device. The first call on a device resolves the scratch address; make it before any stream capture. */
+#define BMC_STATIC_RMS_MAX_C 1024
+#define BMC_ERR_STATIC_TOO_LARGE (-60)
+int bmc_rmsnorm_backward_static(void* cuda_stream, int dtype, void* d_gx, float* d_gw_f32, int gw_accumulate, const void* d_gout,
+                                const void* d_x, const float* d_w, const float* d_rstd, int N, int C, int w_row0, int w_row1);
+
 /* ---- linear layers (matmul_forward_* forward.metal:176,449; matmul_backward_inp_* backward.metal:122,174;
  *      matmul_backward_w_tiled backward.metal:277). Weight is row-major [OC, C] in the activation dtype.
  *   forward : out[BT,OC] = inp[BT,C] * W^T (+ residual[BT,OC] when d_residual != NULL)
