@@ -1,0 +1,789 @@
+// bf16 causal GQA flash attention on the sm_100a tensor cores (tcgen05.mma with TMEM accumulators, TMA-fed
+// operand tiles), head_dim 64. Forward pass.
+//
+// One CTA = 256 consecutive queries of one head, handled as two tiles X = A, B of 128 queries that share every K/V
+// tile. For each tile of 128 keys up to the diagonal and each X:
+//   S_X = Q_X K^T        UMMA 128x128x64, A = Q_X (K-major smem), B = K tile (K-major smem), accumulator in TMEM
+//   softmax              one warpgroup per X, one thread per query row: the S row is pulled into registers,
+//                        running max / sum in the log2 domain, P written as bf16 into a 128B-swizzled smem tile;
+//                        O_X in TMEM is rescaled only when the row maximum grew by more than 2^8 since the value the
+//                        accumulator is referenced to (the stale reference cancels in the final division)
+//   O_X += P_X V         UMMA 128x64x128, A = P_X (K-major smem), B = V tile (MN-major smem: the reduction index,
+//                        the key, is the row of V), accumulator in TMEM
+// The single UMMA-issuing thread interleaves the two tiles (PV_A(j), QK_A(j+1), PV_B(j), QK_B(j+1), ...) so that
+// the tensor core works on one tile while the other tile's warpgroup does its softmax. K/V tiles are
+// double-buffered by a TMA producer warp. 10 warps: TMA, UMMA, 4 + 4 softmax.
+// Same semantics as flash_fwd_kernel in attention_mma.cu (reference: attention_forward_train_tiled,
+// src/kernels/forward.metal:2122): out = softmax(scale * Q K^T, causal) V and lse = log-sum-exp of the scaled scores.
+#include <cuda.h>
+#include <stdio.h>
+#include <stdlib.h>
+
+#include "attention_mma.cuh"
+#include "ptx_sm100.cuh"
+
+namespace bmb {
+
+namespace {
+
+constexpr int FQ = 128;   // queries per tile (two tiles per CTA)
+constexpr int FK = 128;   // keys per tile
+constexpr int FHD = 64;
+constexpr int Q_BYTES = FQ * FHD * 2;        // 16 KB per Q tile
+constexpr int KV_TILE_BYTES = FK * FHD * 2;  // 16 KB each for K and V
+constexpr int P_BYTES = FQ * FK * 2;         // 32 KB per P tile
+constexpr int FWD_DYN_SMEM = 2 * Q_BYTES + 2 * 2 * KV_TILE_BYTES + 2 * P_BYTES + 1024;
+constexpr int FWD_THREADS = 320;
+constexpr uint32_t FWD_TMEM_COLS = 512;  // S_A [0,128) S_B [128,256) O_A [256,320) O_B [320,384)
+constexpr float LOG2E_F = 1.4426950408889634f;
+constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
+
+struct __align__(8) FwdBars {
+    uint64_t q_full, kv_full[2], kv_empty[2], s_full[2], p_ready[2], pv_done[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+        "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
+        "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),
+        "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+struct FwdArgs {
+    bf16* out;
+    int ldo;
+    float* lse;
+    int S, NH, NKV;
+    float scale;
+    int* err;
+};
+
+__global__ void __launch_bounds__(FWD_THREADS, 1)
+flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                      const __grid_constant__ CUtensorMap tmV, const FwdArgs p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ FwdBars bars;
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* sQ = smem;                          // 2 tiles
+    uint8_t* sK = sQ + 2 * Q_BYTES;              // 2 stages
+    uint8_t* sV = sK + 2 * KV_TILE_BYTES;        // 2 stages
+    uint8_t* sP = sV + 2 * KV_TILE_BYTES;        // 2 tiles x [2 key halves][128 rows][128 B]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qb = (int)gridDim.x - 1 - (int)blockIdx.x;  // latest (longest) query blocks first
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int kh = h / (p.NH / p.NKV);
+    const int q0 = qb * 2 * FQ;        // first query of tile A; tile B starts FQ later
+    const int row0 = b * p.S;          // first row of this sequence in the [B*S, .] matrices
+    // causal, FQ == FK: tile X attends key tiles 0 .. 2*qb + X; a tile that starts past the sequence is inactive
+    const int n_a = 2 * qb + 1, n_b = (q0 + FQ < p.S) ? 2 * qb + 2 : 0;
+    const int n_tiles = max(n_a, n_b);
+
+    if (threadIdx.x == 0) {
+        mbar_init(&bars.q_full, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&bars.kv_full[i], 1);
+            mbar_init(&bars.kv_empty[i], 1);
+            mbar_init(&bars.s_full[i], 1);
+            mbar_init(&bars.p_ready[i], 4);
+            mbar_init(&bars.pv_done[i], 1);
+        }
+        bars.abort_flag = 0;
+        mbar_fence_init();
+        fence_proxy_async_smem();
+    }
+    if (warp == 1) {
+        tmem_alloc(&bars.tmem_base, FWD_TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = bars.tmem_base;
+    volatile int* abort_flag = &bars.abort_flag;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+            mbar_expect_tx(&bars.q_full, 2 * Q_BYTES);
+            tma_load_2d(sQ, &tmQ, &bars.q_full, h * FHD, row0 + q0);
+            tma_load_2d(sQ + Q_BYTES, &tmQ, &bars.q_full, h * FHD, row0 + q0 + FQ);
+            for (int j = 0; j < n_tiles; ++j) {
+                const int st = j & 1;
+                if (!mbar_wait(&bars.kv_empty[st], ((j >> 1) & 1) ^ 1, abort_flag)) break;
+                mbar_expect_tx(&bars.kv_full[st], 2 * KV_TILE_BYTES);
+                tma_load_2d(sK + st * KV_TILE_BYTES, &tmK, &bars.kv_full[st], kh * FHD, row0 + j * FK);
+                tma_load_2d(sV + st * KV_TILE_BYTES, &tmV, &bars.kv_full[st], kh * FHD, row0 + j * FK);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ UMMA issuer --------------------------------
+        if (lane == 0) {
+            const uint32_t idesc_s = umma_idesc_bf16_f32(FQ, FK, 0, 0);    // S = Q K^T : both operands K-major
+            const uint32_t idesc_o = umma_idesc_bf16_f32(FQ, FHD, 0, 1);   // O += P V  : P K-major, V MN-major
+            // Descriptors differ only in their 14-bit start-address field (address >> 4), so each is built once and
+            // stepped by plain integer adds: +2 per 32 B (one K-step inside a 128-byte row), +128 per 2048 B
+            // (16 rows of an MN-major tile), +1024 per 16 KB (tile stage / key half).
+            const uint64_t qd0 = umma_smem_desc_sw128(smem_u32(sQ), 16, 1024);
+            const uint64_t kd0 = umma_smem_desc_sw128(smem_u32(sK), 16, 1024);
+            const uint64_t vd0 = umma_smem_desc_sw128(smem_u32(sV), FK * 128, 1024);
+            const uint64_t pd0 = umma_smem_desc_sw128(smem_u32(sP), 16, 1024);
+            auto issue_qk = [&](int x, int j) {
+                const uint64_t kd = kd0 + (uint64_t)((j & 1) * (KV_TILE_BYTES >> 4));
+                const uint64_t qd = qd0 + (uint64_t)(x * (Q_BYTES >> 4));
+#pragma unroll
+                for (int k = 0; k < FHD / 16; ++k) umma_bf16_ss(tmem + x * FK, qd + 2 * k, kd + 2 * k, idesc_s, k > 0 ? 1u : 0u);
+                umma_commit(&bars.s_full[x]);
+            };
+            auto issue_pv = [&](int x, int j) {
+                const uint64_t vd = vd0 + (uint64_t)((j & 1) * (KV_TILE_BYTES >> 4));
+                const uint64_t pd = pd0 + (uint64_t)(x * (P_BYTES >> 4));
+#pragma unroll
+                for (int k = 0; k < FK / 16; ++k)
+                    // P: two 64-key halves of [128 rows x 128 B], 16 keys = 32 B inside a half; V: 16 keys = 2048 B
+                    umma_bf16_ss(tmem + 2 * FK + x * FHD, pd + (uint64_t)((k >> 2) * ((FQ * 128) >> 4) + (k & 3) * 2), vd + 128 * k, idesc_o,
+                                 (j > 0 || k > 0) ? 1u : 0u);
+                umma_commit(&bars.pv_done[x]);
+            };
+            bool ok = mbar_wait(&bars.q_full, 0, abort_flag) && mbar_wait(&bars.kv_full[0], 0, abort_flag);
+            if (ok) {
+                tc_fence_after_sync();
+                issue_qk(0, 0);
+                if (n_b > 0) issue_qk(1, 0);
+            }
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                bool next_loaded = false;
+                for (int x = 0; x < 2 && ok; ++x) {
+                    const int n_this = x ? n_b : n_a;
+                    if (j >= n_this) continue;
+                    if (!mbar_wait(&bars.p_ready[x], j & 1, abort_flag)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    issue_pv(x, j);
+                    if (j + 1 < n_this) {
+                        if (!next_loaded) {
+                            if (!mbar_wait(&bars.kv_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+                            tc_fence_after_sync();
+                            next_loaded = true;
+                        }
+                        issue_qk(x, j + 1);
+                    }
+                }
+                if (ok) umma_commit(&bars.kv_empty[j & 1]);  // every UMMA that reads stage j has been issued
+            }
+        }
+    } else {
+        // ------------------------------ softmax / epilogue: warps 2-5 = tile A, 6-9 = tile B ------------
+        const int x = (warp - 2) >> 2;
+        const int quarter = warp & 3;              // TMEM lane quarter this warp may access
+        const int r = quarter * 32 + lane;         // query row inside the tile
+        const int qi = q0 + x * FQ + r;            // query position in the sequence
+        const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
+        const uint32_t s_addr = lane_addr + x * FK, o_addr = lane_addr + 2 * FK + x * FHD;
+        uint8_t* sPx = sP + x * P_BYTES;
+        const float sl2 = p.scale * LOG2E_F;
+        const int n_mine = x ? n_b : n_a;
+        float m_ref = -INFINITY;   // the maximum O and l are currently referenced to (log2 domain)
+        float l_run = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_mine; ++j) {
+            ok = mbar_wait(&bars.s_full[x], j & 1, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after_sync();
+            uint32_t v[4][32];
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch) tmem_ld_32x32(s_addr + ch * 32, v[ch]);
+            tmem_ld_wait();
+            const int k0 = j * FK;
+            if (j == n_mine - 1 || k0 + FK > p.S) {  // diagonal tile or ragged end: mask keys after the query / past the end
+#pragma unroll
+                for (int ch = 0; ch < 4; ++ch)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int kj = k0 + ch * 32 + i;
+                        if (kj > qi || kj >= p.S) v[ch][i] = __float_as_uint(-INFINITY);
+                    }
+            }
+            // eight independent max chains (a single chain of 128 dependent FMNMX would be latency-bound)
+            float mxp[8];
+#pragma unroll
+            for (int t = 0; t < 8; ++t) mxp[t] = -INFINITY;
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch)
+#pragma unroll
+                for (int i = 0; i < 32; ++i) mxp[i & 7] = fmaxf(mxp[i & 7], __uint_as_float(v[ch][i]));
+            float mx = fmaxf(fmaxf(fmaxf(mxp[0], mxp[1]), fmaxf(mxp[2], mxp[3])), fmaxf(fmaxf(mxp[4], mxp[5]), fmaxf(mxp[6], mxp[7])));
+            mx *= sl2;
+            // lazy rescale: keep the old reference unless the maximum grew by more than the threshold
+            float corr = 1.0f;
+            bool need = false;
+            if (m_ref == -INFINITY) {
+                if (mx != -INFINITY) m_ref = mx;  // first finite maximum: O and l are still zero, nothing to rescale
+            } else if (mx > m_ref + RESCALE_THRESHOLD) {
+                corr = ex2_approx(m_ref - mx);
+                m_ref = mx;
+                need = true;
+            }
+            const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+            // probabilities, packed to bf16 in place (pair i, i+1 of chunk ch -> v[ch][i / 2]); four independent sum chains
+            float ls[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch)
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float p0 = fmaf(__uint_as_float(v[ch][i]), sl2, -m_use);
+                    float p1 = fmaf(__uint_as_float(v[ch][i + 1]), sl2, -m_use);
+                    p0 = ex2_approx(p0);
+                    p1 = ex2_approx(p1);
+                    ls[(i >> 1) & 3] += p0 + p1;
+                    __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
+                    v[ch][i >> 1] = *reinterpret_cast<uint32_t*>(&hh);
+                }
+            const float lsum = (ls[0] + ls[1]) + (ls[2] + ls[3]);
+            l_run = l_run * corr + lsum;
+            if (j > 0) {
+                // P_X(j-1) must have been consumed (and O_X updated) before P is overwritten / O rescaled
+                ok = mbar_wait(&bars.pv_done[x], (j - 1) & 1, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after_sync();
+                if (__any_sync(0xffffffffu, need)) {
+#pragma unroll
+                    for (int ch = 0; ch < FHD / 32; ++ch) {
+                        uint32_t o[32];
+                        tmem_ld_32x32(o_addr + ch * 32, o);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+                        tmem_st_32x32(o_addr + ch * 32, o);
+                    }
+                    tmem_st_wait();
+                }
+            }
+            // P row -> swizzled smem (A operand of P V): key half = c / 8, 16-byte chunk inside the 128-byte row = c % 8
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+                uint8_t* prow = sPx + (c >> 3) * (FQ * 128) + r * 128;
+                const int cc = (c & 7) ^ (r & 7);
+                *reinterpret_cast<uint4*>(prow + cc * 16) =
+                    make_uint4(v[c >> 2][(c & 3) * 4], v[c >> 2][(c & 3) * 4 + 1], v[c >> 2][(c & 3) * 4 + 2], v[c >> 2][(c & 3) * 4 + 3]);
+            }
+            tc_fence_before_sync();
+            fence_proxy_async_smem();  // generic-proxy smem writes -> visible to the UMMA (async proxy) reads
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars.p_ready[x]);
+        }
+        if (ok && n_mine > 0) {
+            ok = mbar_wait(&bars.pv_done[x], (n_mine - 1) & 1, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok && n_mine > 0) {
+            tc_fence_after_sync();
+            const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+            bf16* orow = p.out + (size_t)(row0 + qi) * p.ldo + (size_t)h * FHD;
+#pragma unroll
+            for (int ch = 0; ch < FHD / 32; ++ch) {
+                uint32_t o[32];
+                tmem_ld_32x32(o_addr + ch * 32, o);
+                tmem_ld_wait();
+                if (qi < p.S) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint4 w;
+                        __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&w);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            ob[i] = __floats2bfloat162_rn(__uint_as_float(o[c * 8 + 2 * i]) * inv, __uint_as_float(o[c * 8 + 2 * i + 1]) * inv);
+                        *reinterpret_cast<uint4*>(orow + ch * 32 + c * 8) = w;
+                    }
+                }
+            }
+            if (qi < p.S)
+                p.lse[((size_t)b * p.NH + h) * p.S + qi] = l_run > 0.f ? (m_ref + log2f(l_run)) * (1.0f / LOG2E_F) : -INFINITY;
+            tc_fence_before_sync();
+        }
+    }
+
+    // ------------------------------ teardown ---------------------------------------
+    __syncwarp();
+    if (*abort_flag) {
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 2000000ull) __nanosleep(1000);
+        if (threadIdx.x == 0 && p.err) atomicExch(p.err, 2000 + (int)blockIdx.x);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    if (warp == 1) tmem_dealloc(tmem, FWD_TMEM_COLS);
+}
+
+// ================================ backward =====================================================================
+// One CTA owns 128 keys of one KV head (K and V tiles stay in shared memory, dK and dV stay in TMEM) and sweeps every
+// 128-query tile at or after it of every query head that shares the KV head. Per query tile:
+//   S  = Q K^T, dP = dO V^T          two UMMA 128x128x64 into TMEM                       (both operands K-major)
+//   P  = exp2(S*scale*log2e - lse*log2e),  dS = P * (dP - delta) * scale
+//                                     16 warps: warp w handles TMEM lane quarter w%4 and 32 of the 128 key columns;
+//                                     no row maximum is needed because lse is known, so columns split freely.
+//                                     P and dS go to shared memory as bf16 rows [query][key] (128B-swizzled halves).
+//   dV += P^T dO, dK += dS^T Q        UMMA 128x64x128: A = the P / dS tile read MN-major (the reduction index, the query,
+//                                     is the row), B = dO / Q tile read MN-major
+//   dQ  = dS K                        UMMA 128x64x128: A = dS tile read K-major, B = K tile read MN-major
+// dQ tiles are added into an fp32 scratch with red.global.add.v4.f32 (another key block adds to the same rows);
+// dK and dV are written once at the end, so they need no atomics and are deterministic.
+// Reference: attention_backward_tiled, src/kernels/backward.metal:820 (same two-level loop, float atomics for dK/dV there).
+constexpr int BWD_THREADS = 576;  // TMA warp, UMMA warp, 16 compute warps
+constexpr int BWD_DYN_SMEM = 2 * KV_TILE_BYTES + 2 * 2 * Q_BYTES + 2 * P_BYTES + 1024;  // K,V + 2 stages of (Q,dO) + P + dS = 160 KB
+constexpr uint32_t BT_S = 0, BT_DP = 128, BT_DV = 256, BT_DK = 320, BT_DQ = 384;
+
+struct __align__(8) BwdBars {
+    uint64_t kv_full, q_full[2], q_empty[2], sdp_full, pds_ready, dq_full;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+struct BwdArgs {
+#ifdef BMB_TRACE
+    long long* trace;
+#endif
+    float* dq_acc;   // [B*S, NH*64] fp32, zero on entry
+    bf16 *gk, *gv;
+    int ldgkv;
+    const float *lse, *delta;
+    int S, NH, NKV;
+    float scale;
+    int* err;
+};
+
+#ifdef BMB_TRACE
+#define BTRACE(slot, idx) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (idx) < 32) p.trace[(slot) * 32 + (idx)] = clock64(); } while (0)
+#else
+#define BTRACE(slot, idx) do { } while (0)
+#endif
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmG, const BwdArgs p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ BwdBars bars;
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* sK = smem;
+    uint8_t* sV = sK + KV_TILE_BYTES;
+    uint8_t* sQ = sV + KV_TILE_BYTES;       // 2 stages
+    uint8_t* sG = sQ + 2 * Q_BYTES;         // 2 stages (dO tiles)
+    uint8_t* sP = sG + 2 * Q_BYTES;         // [2 key halves][128 query rows][128 B]
+    uint8_t* sD = sP + P_BYTES;             // dS, same layout
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nblk = blockIdx.x, kh = blockIdx.y, b = blockIdx.z;   // key block 0 has the most work and starts first
+    const int mul = p.NH / p.NKV;
+    const int QD = p.NH * FHD;
+    const int n0 = nblk * FK;
+    const int nqb = (p.S + FQ - 1) / FQ;
+    const int row0 = b * p.S;
+    const int per_head = nqb - nblk;        // query tiles nblk .. nqb-1
+    const int total = mul * per_head;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&bars.kv_full, 1);
+        for (int i = 0; i < 2; ++i) { mbar_init(&bars.q_full[i], 1); mbar_init(&bars.q_empty[i], 1); }
+        mbar_init(&bars.sdp_full, 1);
+        mbar_init(&bars.pds_ready, 16);
+        mbar_init(&bars.dq_full, 1);
+        bars.abort_flag = 0;
+        mbar_fence_init();
+        fence_proxy_async_smem();
+    }
+    if (warp == 1) {
+        tmem_alloc(&bars.tmem_base, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = bars.tmem_base;
+    volatile int* abort_flag = &bars.abort_flag;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmG);
+            mbar_expect_tx(&bars.kv_full, 2 * KV_TILE_BYTES);
+            tma_load_2d(sK, &tmK, &bars.kv_full, kh * FHD, row0 + n0);
+            tma_load_2d(sV, &tmV, &bars.kv_full, kh * FHD, row0 + n0);
+            for (int it = 0; it < total; ++it) {
+                const int st = it & 1;
+                const int hl = it / per_head, mb = nblk + (it - hl * per_head);
+                const int h = kh * mul + hl;
+                if (!mbar_wait(&bars.q_empty[st], ((it >> 1) & 1) ^ 1, abort_flag)) break;
+                mbar_expect_tx(&bars.q_full[st], 2 * Q_BYTES);
+                tma_load_2d(sQ + st * Q_BYTES, &tmQ, &bars.q_full[st], h * FHD, row0 + mb * FQ);
+                tma_load_2d(sG + st * Q_BYTES, &tmG, &bars.q_full[st], h * FHD, row0 + mb * FQ);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ UMMA issuer --------------------------------
+        if (lane == 0) {
+            const uint32_t id_s = umma_idesc_bf16_f32(FQ, FK, 0, 0);     // S, dP: A K-major, B K-major, N = 128
+            const uint32_t id_kv = umma_idesc_bf16_f32(FK, FHD, 1, 1);   // dV, dK: A MN-major, B MN-major, N = 64
+            const uint32_t id_q = umma_idesc_bf16_f32(FQ, FHD, 0, 1);    // dQ: A K-major, B MN-major, N = 64
+            // descriptor bases; K-major tiles step +2 (32 B) per UMMA, MN-major tiles +128 (2048 B = 16 rows)
+            const uint64_t k_km = umma_smem_desc_sw128(smem_u32(sK), 16, 1024);
+            const uint64_t v_km = umma_smem_desc_sw128(smem_u32(sV), 16, 1024);
+            const uint64_t k_mn = umma_smem_desc_sw128(smem_u32(sK), FK * 128, 1024);        // N = 64: a single MN group
+            const uint64_t q_km0 = umma_smem_desc_sw128(smem_u32(sQ), 16, 1024);
+            const uint64_t g_km0 = umma_smem_desc_sw128(smem_u32(sG), 16, 1024);
+            const uint64_t q_mn0 = umma_smem_desc_sw128(smem_u32(sQ), FQ * 128, 1024);
+            const uint64_t g_mn0 = umma_smem_desc_sw128(smem_u32(sG), FQ * 128, 1024);
+            const uint64_t p_mn = umma_smem_desc_sw128(smem_u32(sP), FQ * 128, 1024);        // M = 128 keys: LBO = next key half (16 KB)
+            const uint64_t d_mn = umma_smem_desc_sw128(smem_u32(sD), FQ * 128, 1024);
+            const uint64_t d_km = umma_smem_desc_sw128(smem_u32(sD), 16, 1024);
+            bool ok = mbar_wait(&bars.kv_full, 0, abort_flag);
+            for (int it = 0; it < total && ok; ++it) {
+                const int st = it & 1;
+                const uint64_t so = (uint64_t)(st * (Q_BYTES >> 4));
+                if (!mbar_wait(&bars.q_full[st], (it >> 1) & 1, abort_flag)) { ok = false; break; }
+                tc_fence_after_sync();
+                BTRACE(0, it);
+                // S and dP of this tile (their TMEM columns were released by pds_ready of the previous tile)
+#pragma unroll
+                for (int k = 0; k < FHD / 16; ++k) umma_bf16_ss(tmem + BT_S, q_km0 + so + 2 * k, k_km + 2 * k, id_s, k > 0 ? 1u : 0u);
+#pragma unroll
+                for (int k = 0; k < FHD / 16; ++k) umma_bf16_ss(tmem + BT_DP, g_km0 + so + 2 * k, v_km + 2 * k, id_s, k > 0 ? 1u : 0u);
+                umma_commit(&bars.sdp_full);
+                BTRACE(1, it);
+                // P and dS in shared memory, and dQ of the previous tile read out of TMEM
+                if (!mbar_wait(&bars.pds_ready, it & 1, abort_flag)) { ok = false; break; }
+                tc_fence_after_sync();
+                BTRACE(2, it);
+#pragma unroll
+                for (int k = 0; k < FQ / 16; ++k) umma_bf16_ss(tmem + BT_DV, p_mn + 128 * k, g_mn0 + so + 128 * k, id_kv, (it > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+                for (int k = 0; k < FQ / 16; ++k) umma_bf16_ss(tmem + BT_DK, d_mn + 128 * k, q_mn0 + so + 128 * k, id_kv, (it > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+                for (int k = 0; k < FK / 16; ++k)
+                    umma_bf16_ss(tmem + BT_DQ, d_km + (uint64_t)((k >> 2) * ((FQ * 128) >> 4) + (k & 3) * 2), k_mn + 128 * k, id_q, k > 0 ? 1u : 0u);
+                umma_commit(&bars.q_empty[st]);
+                umma_commit(&bars.dq_full);
+                BTRACE(3, it);
+            }
+        }
+    } else {
+        // ------------------------------ 16 compute warps ----------------------------
+        const int cw = warp - 2;
+        const int quarter = warp & 3;           // TMEM lanes this warp may touch: 32*quarter .. +31
+        const int cg = cw >> 2;                 // column group: S/dP columns [32*cg, +32), dQ/dK/dV columns [16*cg, +16)
+        const int r = quarter * 32 + lane;      // row inside the tile (query for S/dP/dQ, key for dK/dV)
+        const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
+        const float sl2 = p.scale * LOG2E_F;
+        bool ok = true;
+        uint32_t dq_regs[16];
+        int prev_h = 0, prev_q0 = 0;
+        for (int it = 0; it < total; ++it) {
+            const int hl = it / per_head, mb = nblk + (it - hl * per_head);
+            const int h = kh * mul + hl, q0 = mb * FQ;
+            const int qi = q0 + r;
+            // per-row statistics (rows past the end: lse = +inf makes every probability zero)
+            float lse2 = INFINITY, dlt = 0.f;
+            if (qi < p.S) {
+                const size_t idx = ((size_t)b * p.NH + h) * p.S + qi;
+                lse2 = p.lse[idx] * LOG2E_F;
+                dlt = p.delta[idx];
+            }
+            ok = mbar_wait(&bars.sdp_full, it & 1, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after_sync();
+            if (cw == 0 && lane == 0) BTRACE(4, it);
+            uint32_t sv[32], dv[32];
+            tmem_ld_32x32(lane_addr + BT_S + cg * 32, sv);
+            tmem_ld_32x32(lane_addr + BT_DP + cg * 32, dv);
+            tmem_ld_wait();
+            if (cw == 0 && lane == 0) BTRACE(5, it);
+            const bool diag = (mb == nblk) || (n0 + FK > p.S);
+            uint32_t pp[16], dd[16];
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+                float p0 = ex2_approx(fmaf(__uint_as_float(sv[i]), sl2, -lse2));
+                float p1 = ex2_approx(fmaf(__uint_as_float(sv[i + 1]), sl2, -lse2));
+                if (diag) {
+                    const int kl = cg * 32 + i;   // key inside the tile; on the diagonal tile n0 == q0
+                    if ((mb == nblk && kl > r) || n0 + kl >= p.S) p0 = 0.f;
+                    if ((mb == nblk && kl + 1 > r) || n0 + kl + 1 >= p.S) p1 = 0.f;
+                }
+                const float d0 = p0 * (__uint_as_float(dv[i]) - dlt) * p.scale;
+                const float d1 = p1 * (__uint_as_float(dv[i + 1]) - dlt) * p.scale;
+                __nv_bfloat162 hp = __floats2bfloat162_rn(p0, p1), hd = __floats2bfloat162_rn(d0, d1);
+                pp[i >> 1] = *reinterpret_cast<uint32_t*>(&hp);
+                dd[i >> 1] = *reinterpret_cast<uint32_t*>(&hd);
+            }
+            if (cw == 0 && lane == 0) BTRACE(6, it);
+            if (it > 0) {
+                // the UMMAs of the previous tile are done: P/dS may be overwritten and its dQ tile is complete
+                ok = mbar_wait(&bars.dq_full, (it - 1) & 1, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after_sync();
+                tmem_ld_32x16(lane_addr + BT_DQ + cg * 16, dq_regs);
+                tmem_ld_wait();
+            }
+            if (cw == 0 && lane == 0) BTRACE(7, it);
+            // rows of P and dS: key half = cg / 2, 16-byte chunks (cg & 1) * 4 .. +3 of the 128-byte row
+            {
+                uint8_t* prow = sP + (cg >> 1) * (FQ * 128) + r * 128;
+                uint8_t* drow = sD + (cg >> 1) * (FQ * 128) + r * 128;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int cc = ((cg & 1) * 4 + c) ^ (r & 7);
+                    *reinterpret_cast<uint4*>(prow + cc * 16) = make_uint4(pp[4 * c], pp[4 * c + 1], pp[4 * c + 2], pp[4 * c + 3]);
+                    *reinterpret_cast<uint4*>(drow + cc * 16) = make_uint4(dd[4 * c], dd[4 * c + 1], dd[4 * c + 2], dd[4 * c + 3]);
+                }
+            }
+            tc_fence_before_sync();
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars.pds_ready);
+            if (cw == 0 && lane == 0) BTRACE(8, it);
+            if (it > 0) {
+                // add the previous tile's dQ into the fp32 scratch while the tensor core works on this tile
+                const int pq = prev_q0 + r;
+                if (pq < p.S) {
+                    float* dst = p.dq_acc + (size_t)(row0 + pq) * QD + (size_t)prev_h * FHD + cg * 16;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 4 * c), "f"(__uint_as_float(dq_regs[4 * c])),
+                                     "f"(__uint_as_float(dq_regs[4 * c + 1])), "f"(__uint_as_float(dq_regs[4 * c + 2])),
+                                     "f"(__uint_as_float(dq_regs[4 * c + 3]))
+                                     : "memory");
+                }
+            }
+            prev_h = h;
+            prev_q0 = q0;
+            if (cw == 0 && lane == 0) BTRACE(9, it);
+        }
+        if (ok && total > 0) {
+            ok = mbar_wait(&bars.dq_full, (total - 1) & 1, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok) {
+            tc_fence_after_sync();
+            if (total > 0) {
+                tmem_ld_32x16(lane_addr + BT_DQ + cg * 16, dq_regs);
+                tmem_ld_wait();
+                const int pq = prev_q0 + r;
+                if (pq < p.S) {
+                    float* dst = p.dq_acc + (size_t)(row0 + pq) * QD + (size_t)prev_h * FHD + cg * 16;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 4 * c), "f"(__uint_as_float(dq_regs[4 * c])),
+                                     "f"(__uint_as_float(dq_regs[4 * c + 1])), "f"(__uint_as_float(dq_regs[4 * c + 2])),
+                                     "f"(__uint_as_float(dq_regs[4 * c + 3]))
+                                     : "memory");
+                }
+            }
+            // dK, dV: row = key, this warp's 16 columns
+            const int kj = n0 + r;
+            uint32_t a[16], c2[16];
+            if (total > 0) {
+                tmem_ld_32x16(lane_addr + BT_DK + cg * 16, a);
+                tmem_ld_32x16(lane_addr + BT_DV + cg * 16, c2);
+                tmem_ld_wait();
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) { a[i] = 0u; c2[i] = 0u; }
+            }
+            if (kj < p.S) {
+                bf16* gkr = p.gk + (size_t)(row0 + kj) * p.ldgkv + (size_t)kh * FHD + cg * 16;
+                bf16* gvr = p.gv + (size_t)(row0 + kj) * p.ldgkv + (size_t)kh * FHD + cg * 16;
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    uint4 wk, wv;
+                    __nv_bfloat162* bk = reinterpret_cast<__nv_bfloat162*>(&wk);
+                    __nv_bfloat162* bv = reinterpret_cast<__nv_bfloat162*>(&wv);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        bk[i] = __floats2bfloat162_rn(__uint_as_float(a[c * 8 + 2 * i]), __uint_as_float(a[c * 8 + 2 * i + 1]));
+                        bv[i] = __floats2bfloat162_rn(__uint_as_float(c2[c * 8 + 2 * i]), __uint_as_float(c2[c * 8 + 2 * i + 1]));
+                    }
+                    *reinterpret_cast<uint4*>(gkr + c * 8) = wk;
+                    *reinterpret_cast<uint4*>(gvr + c * 8) = wv;
+                }
+            }
+            tc_fence_before_sync();
+        }
+    }
+
+    // ------------------------------ teardown ---------------------------------------
+    __syncwarp();
+    if (*abort_flag) {
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 2000000ull) __nanosleep(1000);
+        if (threadIdx.x == 0 && p.err) atomicExch(p.err, 3000 + (int)blockIdx.x);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    if (warp == 1) tmem_dealloc(tmem, 512);
+}
+
+// delta[b, h, s] = sum_d gout * out. One warp per (row, head).
+__global__ void flash_delta_umma_kernel(float* __restrict__ delta, const bf16* __restrict__ gout, const bf16* __restrict__ out, int ldo,
+                                        int B, int S, int NH) {
+    const long wid = (blockIdx.x * (long)blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (wid >= (long)B * S * NH) return;
+    const int h = (int)(wid % NH);
+    const long row = wid / NH;
+    const __nv_bfloat162 a = reinterpret_cast<const __nv_bfloat162*>(gout + row * ldo + (size_t)h * FHD)[lane];
+    const __nv_bfloat162 c = reinterpret_cast<const __nv_bfloat162*>(out + row * ldo + (size_t)h * FHD)[lane];
+    const float2 fa = __bfloat1622float2(a), fc = __bfloat1622float2(c);
+    float d = fa.x * fc.x + fa.y * fc.y;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+    if (lane == 0) delta[((size_t)(row / S) * NH + h) * S + (row % S)] = d;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)ptr;
+    }
+    return fn;
+}
+// [rows, width] bf16 matrix with row pitch ld (elements); box = 64 columns x box_rows rows, 128B swizzle.
+int make_rows_map(CUtensorMap* tm, const void* base, uint64_t width, uint64_t rows, uint64_t ld, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return -10;
+    cuuint64_t dims[2] = {width, rows};
+    cuuint64_t strides[1] = {ld * 2};
+    cuuint32_t box[2] = {64, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS
+               ? 0
+               : -11;
+}
+
+}  // namespace
+
+int flash_attention_forward_umma(bf16* out, int ldo, float* lse, const bf16* q, int ldq, const bf16* k, const bf16* v, int ldkv, int B,
+                                 int S, int NH, int NKV, int HD, float scale, int* err_flag, cudaStream_t st) {
+    if (HD != FHD || NKV <= 0 || NH % NKV) return -1;
+    if ((ldq % 8) || (ldkv % 8) || (ldo % 8) || (((uintptr_t)q) & 15) || (((uintptr_t)k) & 15) || (((uintptr_t)v) & 15) ||
+        (((uintptr_t)out) & 15))
+        return -2;
+    static bool attr_done = false;
+    if (!attr_done) {
+        if (cudaFuncSetAttribute(flash_fwd_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_DYN_SMEM) != cudaSuccess) return -5;
+        attr_done = true;
+    }
+    CUtensorMap tq, tk, tv;
+    const uint64_t rows = (uint64_t)B * S;
+    int rc = make_rows_map(&tq, q, (uint64_t)NH * HD, rows, ldq, FQ);
+    if (!rc) rc = make_rows_map(&tk, k, (uint64_t)NKV * HD, rows, ldkv, FK);
+    if (!rc) rc = make_rows_map(&tv, v, (uint64_t)NKV * HD, rows, ldkv, FK);
+    if (rc) return rc;
+    FwdArgs a{out, ldo, lse, S, NH, NKV, scale, err_flag};
+    dim3 grid((S + 2 * FQ - 1) / (2 * FQ), NH, B);
+    flash_fwd_umma_kernel<<<grid, FWD_THREADS, FWD_DYN_SMEM, st>>>(tq, tk, tv, a);
+    const cudaError_t le = cudaGetLastError();
+    if (le != cudaSuccess) {
+        fprintf(stderr, "flash_attention_forward_umma: launch failed: %s\n", cudaGetErrorString(le));
+        return -7;
+    }
+    return 0;
+}
+
+int flash_attention_backward_umma(bf16* gq, int ldgq, bf16* gk, bf16* gv, int ldgkv, const bf16* gout, int ldo, const bf16* out,
+                                  const float* lse, const bf16* q, int ldq, const bf16* k, const bf16* v, int ldkv, int B, int S, int NH,
+                                  int NKV, int HD, float scale, void* scratch, int* err_flag, cudaStream_t st) {
+    if (HD != FHD || NKV <= 0 || NH % NKV) return -1;
+    if ((ldq % 8) || (ldkv % 8) || (ldo % 8) || (ldgkv % 8) || (ldgq % 4) || (((uintptr_t)q) & 15) || (((uintptr_t)k) & 15) ||
+        (((uintptr_t)v) & 15) || (((uintptr_t)gout) & 15) || (((uintptr_t)gk) & 15) || (((uintptr_t)gv) & 15) || (((uintptr_t)gq) & 7) ||
+        (((uintptr_t)out) & 3))
+        return -2;
+    static bool attr_done = false;
+    if (!attr_done) {
+        if (cudaFuncSetAttribute(flash_bwd_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_DYN_SMEM) != cudaSuccess) return -5;
+        attr_done = true;
+    }
+    const uint64_t rows = (uint64_t)B * S;
+    const int QD = NH * HD;
+    float* dq_acc = (float*)scratch;
+    float* delta = dq_acc + rows * QD;
+    CUtensorMap tq, tk, tv, tg;
+    int rc = make_rows_map(&tq, q, (uint64_t)NH * HD, rows, ldq, FQ);
+    if (!rc) rc = make_rows_map(&tk, k, (uint64_t)NKV * HD, rows, ldkv, FK);
+    if (!rc) rc = make_rows_map(&tv, v, (uint64_t)NKV * HD, rows, ldkv, FK);
+    if (!rc) rc = make_rows_map(&tg, gout, (uint64_t)NH * HD, rows, ldo, FQ);
+    if (rc) return rc;
+    cudaMemsetAsync(dq_acc, 0, rows * QD * sizeof(float), st);
+    const long warps = (long)rows * NH;
+    flash_delta_umma_kernel<<<(int)((warps * 32 + 255) / 256), 256, 0, st>>>(delta, gout, out, ldo, B, S, NH);
+#ifdef BMB_TRACE
+    long long* trace = nullptr;
+    cudaMalloc(&trace, 10 * 32 * sizeof(long long));
+    cudaMemset(trace, 0, 10 * 32 * sizeof(long long));
+    BwdArgs a{trace, dq_acc, gk, gv, ldgkv, lse, delta, S, NH, NKV, scale, err_flag};
+#else
+    BwdArgs a{dq_acc, gk, gv, ldgkv, lse, delta, S, NH, NKV, scale, err_flag};
+#endif
+    dim3 grid((S + FK - 1) / FK, NKV, B);
+    flash_bwd_umma_kernel<<<grid, BWD_THREADS, BWD_DYN_SMEM, st>>>(tq, tk, tv, tg, a);
+#ifdef BMB_TRACE
+    {
+        static int printed = 0;
+        cudaStreamSynchronize(st);
+        long long h[10 * 32];
+        cudaMemcpy(h, trace, sizeof h, cudaMemcpyDeviceToHost);
+        cudaFree(trace);
+        if (printed++ < 1) {
+            const char* names[10] = {"mma:q_full", "mma:sdp_issued", "mma:pds_ready", "mma:st2_issued", "cw:sdp_full", "cw:ld_done", "cw:math_done",
+                                     "cw:dq_ld_done", "cw:arrived", "cw:red_done"};
+            const long long t0 = h[0];
+            for (int j = 0; j < 10; ++j) {
+                fprintf(stderr, "it=%2d", j);
+                for (int sl = 0; sl < 10; ++sl) fprintf(stderr, " %s=%lld", names[sl], h[sl * 32 + j] ? h[sl * 32 + j] - t0 : -1);
+                fprintf(stderr, "\n");
+            }
+        }
+    }
+#endif
+    const cudaError_t le = cudaGetLastError();
+    if (le != cudaSuccess) {
+        fprintf(stderr, "flash_attention_backward_umma: launch failed: %s\n", cudaGetErrorString(le));
+        return -7;
+    }
+    return cast_rows_f32_to_bf16(gq, ldgq, dq_acc, QD, (int)rows, QD, st);
+}
+
+}  // namespace bmb

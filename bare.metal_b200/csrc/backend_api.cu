@@ -348,9 +348,14 @@ int bmc_attention_forward(bmc_ctx_t* ctx, int dtype, void* d_out, int ldo, float
     if (dtype == BMC_F32)
         return note(ctx, attention_forward_simt<float>((float*)d_out, ldo, d_lse, (const float*)d_q, ldq, (const float*)d_k,
                                                        (const float*)d_v, ldkv, d_mask, B, S, NH, NKV, HD, scale, ctx->stream));
-    if (flash_attention_supported(HD, NH, NKV, d_mask != nullptr))
+    if (flash_attention_supported(HD, NH, NKV, d_mask != nullptr)) {
+        static const bool use_mma = [] { const char* e = getenv("BM_ATTN_FWD"); return e && e[0] == 'm'; }();
+        if (!use_mma && (ldo % 8) == 0)
+            return note(ctx, flash_attention_forward_umma((bf16*)d_out, ldo, d_lse, (const bf16*)d_q, ldq, (const bf16*)d_k, (const bf16*)d_v,
+                                                          ldkv, B, S, NH, NKV, HD, scale, ctx->d_err, ctx->stream));
         return note(ctx, flash_attention_forward((bf16*)d_out, ldo, d_lse, (const bf16*)d_q, ldq, (const bf16*)d_k, (const bf16*)d_v,
                                                  ldkv, B, S, NH, NKV, HD, scale, ctx->stream));
+    }
     return note(ctx, attention_forward_simt<bf16>((bf16*)d_out, ldo, d_lse, (const bf16*)d_q, ldq, (const bf16*)d_k, (const bf16*)d_v,
                                                   ldkv, d_mask, B, S, NH, NKV, HD, scale, ctx->stream));
 }
@@ -372,6 +377,11 @@ int bmc_attention_backward(bmc_ctx_t* ctx, int dtype, void* d_gq, int ldgq, void
         const size_t need = flash_attention_backward_scratch_bytes(B, S, NH, HD);
         void* scratch = scratch_get(ctx, &ctx->attn_scratch, &ctx->attn_scratch_bytes, need);
         if (!scratch) return -50;
+        static const bool bwd_mma = [] { const char* e = getenv("BM_ATTN_BWD"); return e && e[0] == 'm'; }();
+        if (!bwd_mma && (ldgkv % 8) == 0 && (ldo % 8) == 0)
+            return note(ctx, flash_attention_backward_umma((bf16*)d_gq, ldgq, (bf16*)d_gk, (bf16*)d_gv, ldgkv, (const bf16*)d_gout, ldo,
+                                                           (const bf16*)d_out, d_lse, (const bf16*)d_q, ldq, (const bf16*)d_k, (const bf16*)d_v,
+                                                           ldkv, B, S, NH, NKV, HD, scale, scratch, ctx->d_err, ctx->stream), 3);
         return note(ctx, flash_attention_backward((bf16*)d_gq, ldgq, (bf16*)d_gk, (bf16*)d_gv, ldgkv, (const bf16*)d_gout, ldo,
                                                   (const bf16*)d_out, d_lse, (const bf16*)d_q, ldq, (const bf16*)d_k, (const bf16*)d_v,
                                                   ldkv, B, S, NH, NKV, HD, scale, scratch, ctx->stream), 3);

@@ -174,13 +174,23 @@ __global__ void rmsnorm_backward_kernel(T* __restrict__ gx, float* __restrict__ 
         scratch[(size_t)blockIdx.x * C + j] = s;
     }
 }
+// 32 columns x 32 row-groups per block: each thread folds every 32nd partial row in a fixed order, then the 32
+// row-groups are combined through shared memory in a fixed order.
 __global__ void rmsnorm_backward_reduce_kernel(float* __restrict__ gw, const float* __restrict__ scratch, int nblocks, int C,
                                                int accumulate) {
-    const int j = blockIdx.x * blockDim.x + threadIdx.x;
-    if (j >= C) return;
+    __shared__ float part[32][33];
+    const int j = blockIdx.x * 32 + threadIdx.x;
     float s = 0.f;
-    for (int b = 0; b < nblocks; ++b) s += scratch[(size_t)b * C + j];
-    gw[j] = accumulate ? gw[j] + s : s;
+    if (j < C)
+        for (int b = threadIdx.y; b < nblocks; b += 32) s += scratch[(size_t)b * C + j];
+    part[threadIdx.y][threadIdx.x] = s;
+    __syncthreads();
+    if (threadIdx.y == 0 && j < C) {
+        float t = 0.f;
+#pragma unroll
+        for (int r = 0; r < 32; ++r) t += part[r][threadIdx.x];
+        gw[j] = accumulate ? gw[j] + t : t;
+    }
 }
 size_t rmsnorm_backward_scratch_floats(int C) { return (size_t)RMS_BWD_MAX_BLOCKS * C; }
 
@@ -197,7 +207,7 @@ static int rmsnorm_backward_launch(T* gx, float* gw, int gw_accumulate, const T*
     }
     if (smem > 64 * 1024) return -2;
     rmsnorm_backward_kernel<T, NV><<<nblocks, BLOCK, smem, st>>>(gx, scratch, gout, x, w, rstd, N, C, w_row0, w_row1);
-    rmsnorm_backward_reduce_kernel<<<ceil_div(C, 128), 128, 0, st>>>(gw, scratch, nblocks, C, gw_accumulate);
+    rmsnorm_backward_reduce_kernel<<<ceil_div(C, 32), dim3(32, 32), 0, st>>>(gw, scratch, nblocks, C, gw_accumulate);
     return 0;
 }
 template <typename T>
@@ -243,11 +253,49 @@ __global__ void rope_kernel(T* __restrict__ q, int ldq, T* __restrict__ k, int l
     base[p] = from_f32<T>(x0 * c - x1 * s);
     base[p + hd2] = from_f32<T>(x0 * s + x1 * c);
 }
+// Vector form: one thread rotates Vec<T>::N adjacent pairs (two 16-byte loads, two 16-byte stores).
+template <typename T>
+__global__ void rope_vec_kernel(T* __restrict__ q, int ldq, T* __restrict__ k, int ldk, const float* __restrict__ cs, int rows, int S,
+                                int NH, int NKV, int HD, float dir) {
+    constexpr int V = Vec<T>::N;
+    const int hd2 = HD >> 1, vph = hd2 / V;  // vectors per half head
+    const long i = blockIdx.x * (long)blockDim.x + threadIdx.x;
+    const long total = (long)rows * (NH + NKV) * vph;
+    if (i >= total) return;
+    const int pv = (int)(i % vph);
+    const long rh = i / vph;
+    const int h = (int)(rh % (NH + NKV));
+    const int row = (int)(rh / (NH + NKV));
+    const int pos = row % S;
+    T* base = (h < NH ? q + (size_t)row * ldq + (size_t)h * HD : k + (size_t)row * ldk + (size_t)(h - NH) * HD) + pv * V;
+    const float* t = cs + ((size_t)pos * hd2 + pv * V) * 2;
+    float x0[V], x1[V], o0[V], o1[V];
+    Vec<T>::load(base, x0);
+    Vec<T>::load(base + hd2, x1);
+#pragma unroll
+    for (int j = 0; j < V; j += 2) {
+        const float4 c4 = *reinterpret_cast<const float4*>(t + 2 * j);  // cos_j, sin_j, cos_j+1, sin_j+1
+        const float s0 = c4.y * dir, s1 = c4.w * dir;
+        o0[j] = x0[j] * c4.x - x1[j] * s0;
+        o1[j] = x0[j] * s0 + x1[j] * c4.x;
+        o0[j + 1] = x0[j + 1] * c4.z - x1[j + 1] * s1;
+        o1[j + 1] = x0[j + 1] * s1 + x1[j + 1] * c4.z;
+    }
+    Vec<T>::store(base, o0);
+    Vec<T>::store(base + hd2, o1);
+}
 template <typename T>
 int rope_apply(T* q, int ldq, T* k, int ldk, const float* cs_table, int rows, int S, int NH, int NKV, int HD, int dir, cudaStream_t st) {
     if (HD % 2) return -1;
+    constexpr int V = Vec<T>::N;
+    const float d = dir >= 0 ? 1.f : -1.f;
+    if ((HD / 2) % V == 0 && ldq % V == 0 && ldk % V == 0 && aligned16(q) && aligned16(k) && aligned16(cs_table)) {
+        const long total = (long)rows * (NH + NKV) * (HD / 2 / V);
+        rope_vec_kernel<T><<<ceil_div(total, 256), 256, 0, st>>>(q, ldq, k, ldk, cs_table, rows, S, NH, NKV, HD, d);
+        return 0;
+    }
     const long total = (long)rows * (NH + NKV) * (HD / 2);
-    rope_kernel<T><<<ceil_div(total, 256), 256, 0, st>>>(q, ldq, k, ldk, cs_table, rows, S, NH, NKV, HD, dir >= 0 ? 1.f : -1.f);
+    rope_kernel<T><<<ceil_div(total, 256), 256, 0, st>>>(q, ldq, k, ldk, cs_table, rows, S, NH, NKV, HD, d);
     return 0;
 }
 template int rope_apply<float>(float*, int, float*, int, const float*, int, int, int, int, int, int, cudaStream_t);
