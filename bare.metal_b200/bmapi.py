@@ -156,6 +156,8 @@ def bind_public_api(lib):
         "bm_destroy_model": (None, [vp]), "bm_get_num_parameters": (C.c_int, [vp]),
         "bm_create_trainer": (vp, [vp, vp, C.POINTER(BmTrainConfig)]),
         "bm_train_step": (C.c_float, [vp, ip, ip, C.c_int, C.c_int]),
+        "bm_train_step_masked": (C.c_float, [vp, ip, ip, C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
+        "bm_train_eval_masked": (C.c_float, [vp, ip, ip, C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
         "bm_train_flush": (None, [vp]),
         "bm_save_state": (None, [vp, C.c_char_p]), "bm_load_state": (None, [vp, C.c_char_p]),
         "bm_destroy_trainer": (None, [vp]),

@@ -427,15 +427,15 @@ int bmc_add_forward(bmc_ctx_t* ctx, int dtype, void* d_out, const void* d_a, con
 
 // ---- loss --------------------------------------------------------------------------------------------
 int bmc_xent(bmc_ctx_t* ctx, int dtype, void* d_logits, int ldv, float* d_row_loss, float* d_loss, const int* d_targets,
-             const uint8_t* d_loss_mask, int B, int S, int V, float grad_scale) {
+             const float* d_row_weight, int B, int S, int V, float grad_scale) {
     BMC_CHECK_CTX(ctx);
     int rc;
     if (dtype == BMC_F32)
-        rc = xent_forward_backward<float>((float*)d_logits, d_row_loss, d_targets, d_loss_mask, B * S, V, ldv, grad_scale, ctx->stream);
+        rc = xent_forward_backward<float>((float*)d_logits, d_row_loss, d_targets, d_row_weight, B * S, V, ldv, grad_scale, ctx->stream);
     else
-        rc = xent_forward_backward<bf16>((bf16*)d_logits, d_row_loss, d_targets, d_loss_mask, B * S, V, ldv, grad_scale, ctx->stream);
+        rc = xent_forward_backward<bf16>((bf16*)d_logits, d_row_loss, d_targets, d_row_weight, B * S, V, ldv, grad_scale, ctx->stream);
     if (rc) return rc;
-    if (d_loss) rc = loss_reduce(d_loss, d_row_loss, B, S, ctx->stream);
+    if (d_loss) rc = loss_reduce(d_loss, d_row_loss, B, S, d_row_weight != nullptr, ctx->stream);
     return note(ctx, rc, d_loss ? 2 : 1);
 }
 

@@ -29,11 +29,12 @@ template <typename T> int swiglu_backward(T* ggate, T* gup, int ldg, const T* ga
 template <typename T> int add_forward(T* out, const T* a, const T* b, size_t n, cudaStream_t st);
 
 // logits -> (softmax - onehot) * grad_scale in place; row_loss[n] = -log softmax[target].
-// mask (may be null): rows with mask==0 get zero gradient and zero loss.
-template <typename T> int xent_forward_backward(T* logits, float* row_loss, const int* targets, const uint8_t* mask, int N, int V,
+// row_weight (may be null): per-row gradient scale replacing grad_scale; 0 = masked row (zero gradient, zero loss). With
+// row weights the stored row loss is already weighted.
+template <typename T> int xent_forward_backward(T* logits, float* row_loss, const int* targets, const float* row_weight, int N, int V,
                                                 int ldv, float grad_scale, cudaStream_t st);
-// loss = mean over B of (sum over S of row_loss / denom_b); denom = S, or the mask count when counts != null.
-int loss_reduce(float* out, const float* row_loss, int B, int S, cudaStream_t st);
+// loss = (1/B) sum_b (1/S) sum_s row_loss   (weighted != 0: the rows are already weighted, so no 1/S)
+int loss_reduce(float* out, const float* row_loss, int B, int S, int weighted, cudaStream_t st);
 
 // hp (HOST pointer) = {lr, b1, b2, eps, wd, 1-b1^t, 1-b2^t, grad_scale}
 int adamw_f32grad(float* w, bf16* w_bf16, const float* g, float* m, float* v, size_t n, const float* hp, cudaStream_t st);

@@ -382,7 +382,7 @@ template int add_forward<bf16>(bf16*, const bf16*, const bf16*, size_t, cudaStre
 constexpr int XENT_THREADS = 512;
 template <typename T>
 __global__ void __launch_bounds__(XENT_THREADS)
-xent_kernel(T* __restrict__ logits, float* __restrict__ row_loss, const int* __restrict__ targets, const uint8_t* __restrict__ mask,
+xent_kernel(T* __restrict__ logits, float* __restrict__ row_loss, const int* __restrict__ targets, const float* __restrict__ row_weight,
             int V, int ldv, float grad_scale) {
     constexpr int VN = Vec<T>::N;
     __shared__ float red[XENT_THREADS / 32];
@@ -391,7 +391,10 @@ xent_kernel(T* __restrict__ logits, float* __restrict__ row_loss, const int* __r
     T* lr = logits + (size_t)row * ldv;
     const int nvec = V / VN;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if (mask && !mask[row]) {
+    // completion-only loss (xent_backward_masked, src/kernels/backward.metal:597): a row's weight is 1 / (number of unmasked
+    // rows of its sequence), or 0 for a masked row (no loss, zero gradient); it replaces the uniform grad_scale.
+    if (row_weight) grad_scale = row_weight[row];
+    if (row_weight && grad_scale == 0.f) {
         float z[VN];
 #pragma unroll
         for (int i = 0; i < VN; ++i) z[i] = 0.f;
@@ -436,7 +439,10 @@ xent_kernel(T* __restrict__ logits, float* __restrict__ row_loss, const int* __r
     sum = bcast;
     const float inv = 1.0f / sum;
     const int tgt = targets[row];
-    if (threadIdx.x == 0) row_loss[row] = -(to_f32(lr[tgt]) - mx - logf(sum));
+    if (threadIdx.x == 0) {
+        const float nll = -(to_f32(lr[tgt]) - mx - logf(sum));
+        row_loss[row] = row_weight ? nll * grad_scale : nll;
+    }
     __syncthreads();  // the target logit is read before any thread overwrites it
     for (int v = threadIdx.x; v < nvec; v += XENT_THREADS) {
         float f[VN], o[VN];
@@ -450,18 +456,18 @@ xent_kernel(T* __restrict__ logits, float* __restrict__ row_loss, const int* __r
     }
 }
 template <typename T>
-int xent_forward_backward(T* logits, float* row_loss, const int* targets, const uint8_t* mask, int N, int V, int ldv, float grad_scale,
+int xent_forward_backward(T* logits, float* row_loss, const int* targets, const float* row_weight, int N, int V, int ldv, float grad_scale,
                           cudaStream_t st) {
     if (V % Vec<T>::N || ldv % Vec<T>::N || !aligned16(logits)) return -1;
-    xent_kernel<T><<<N, XENT_THREADS, 0, st>>>(logits, row_loss, targets, mask, V, ldv, grad_scale);
+    xent_kernel<T><<<N, XENT_THREADS, 0, st>>>(logits, row_loss, targets, row_weight, V, ldv, grad_scale);
     return 0;
 }
-template int xent_forward_backward<float>(float*, float*, const int*, const uint8_t*, int, int, int, float, cudaStream_t);
-template int xent_forward_backward<bf16>(bf16*, float*, const int*, const uint8_t*, int, int, int, float, cudaStream_t);
+template int xent_forward_backward<float>(float*, float*, const int*, const float*, int, int, int, float, cudaStream_t);
+template int xent_forward_backward<bf16>(bf16*, float*, const int*, const float*, int, int, int, float, cudaStream_t);
 
 // loss = (1/B) sum_b (1/S) sum_s row_loss[b,s], summed in a fixed order
 // (reference: per-sequence mean scheduler.c:1634, batch mean trainer.c:528).
-__global__ void loss_reduce_kernel(float* __restrict__ out, const float* __restrict__ row_loss, int B, int S) {
+__global__ void loss_reduce_kernel(float* __restrict__ out, const float* __restrict__ row_loss, int B, int S, int weighted) {
     __shared__ float red[32];
     float total = 0.f;
     for (int b = 0; b < B; ++b) {
@@ -474,13 +480,13 @@ __global__ void loss_reduce_kernel(float* __restrict__ out, const float* __restr
         if (threadIdx.x < 32) {
             float t = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
             t = warp_sum(t);
-            if (threadIdx.x == 0) total += t / (float)S;
+            if (threadIdx.x == 0) total += weighted ? t : t / (float)S;
         }
     }
     if (threadIdx.x == 0) out[0] = total / (float)B;
 }
-int loss_reduce(float* out, const float* row_loss, int B, int S, cudaStream_t st) {
-    loss_reduce_kernel<<<1, 1024, 0, st>>>(out, row_loss, B, S);
+int loss_reduce(float* out, const float* row_loss, int B, int S, int weighted, cudaStream_t st) {
+    loss_reduce_kernel<<<1, 1024, 0, st>>>(out, row_loss, B, S, weighted);
     return 0;
 }
 

@@ -201,3 +201,4 @@ float* bmx_model_weight_buffer(bm_model_t* model, size_t* n_out) {
 }
 int bmx_gemm_timing(bm_context_t* ctx, int enable) { return ctx ? bmc_gemm_timing(ctx->be, enable) : -1; }
 int bmx_gemm_timing_collect(bm_context_t* ctx, double* out3) { return ctx ? bmc_gemm_timing_collect(ctx->be, out3) : -1; }
+int bmx_model_vocab_size(const bm_model_t* model) { return model ? model->arch.vocab_size : 0; }

@@ -79,8 +79,9 @@ struct bm_trainer_s {
     /* backward temporaries */
     void *dres, *dn, *dact, *dgu, *dattn, *dqkv;
     int *d_tokens, *d_targets;
-    uint8_t *d_attn_mask, *d_loss_mask;
-    int *h_stage; /* pinned: tokens then targets */
+    uint8_t* d_attn_mask;
+    float* d_row_weight; /* per-row loss weights of a masked step */
+    int* h_stage;        /* pinned: tokens, targets, row weights, attention mask */
 
     int step, accum_count, window_microsteps;
     int profile;

@@ -1,2 +1,189 @@
+/* baremetal-train: the `train` sub-command of the reference CLI (tools/cli.c:634-805) on the CUDA backend.
+ * Same positional arguments, flags, per-step line and final average line.
+ *
+ * The tokenizer lies outside this build, so <data_file> is one of
+ *   - a file of raw little-endian int32 token ids (any name ending in .bin, .tok or .tokens), or
+ *   - the literal lcg:<seed> for the reference's synthetic token stream (bench/train_bench.c:286-290),
+ * instead of a text file. Windows are contiguous: sequence b of step k continues where the previous one ended and the
+ * target of a position is the next token of the stream (tools/cli.c:762-768). */
+#ifndef BAREMETAL_TRAIN
+#define BAREMETAL_TRAIN
+#endif
 #include <stdio.h>
-int main(void) { fprintf(stderr, "baremetal-train: not built yet\n"); return 2; }
+#include <stdlib.h>
+#include <string.h>
+#include <time.h>
+
+#include "../../include/baremetal.h"
+#include "../../include/baremetal_ext.h"
+
+static double now_ms(void) {
+    struct timespec ts;
+    clock_gettime(CLOCK_MONOTONIC, &ts);
+    return ts.tv_sec * 1e3 + ts.tv_nsec / 1e6;
+}
+static size_t rss_mb(void) { /* tools/cli.c:47-54 uses Mach task_info; Linux: resident pages from /proc/self/statm */
+    FILE* f = fopen("/proc/self/statm", "r");
+    if (!f) return 0;
+    long total = 0, res = 0;
+    if (fscanf(f, "%ld %ld", &total, &res) != 2) res = 0;
+    fclose(f);
+    return (size_t)res * 4096 / (1024 * 1024);
+}
+static int ends_with(const char* s, const char* suf) {
+    const size_t a = strlen(s), b = strlen(suf);
+    return a >= b && strcmp(s + a - b, suf) == 0;
+}
+
+static int usage(const char* argv0) {
+    fprintf(stderr, "Usage: %s train <model_dir|model.bin> <data_file> <output_dir> [options]\n", argv0);
+    fprintf(stderr, "  <data_file>         int32 token ids (*.bin, *.tok, *.tokens) or lcg:<seed> for the synthetic stream\n");
+    fprintf(stderr, "  --steps <int>       Max training steps (default: 100)\n");
+    fprintf(stderr, "  --seq-len <int>     Sequence length S (default: 64)\n");
+    fprintf(stderr, "  --batch-size <int>  Batch size B (default: 1)\n");
+    fprintf(stderr, "  --grad-accum <int>  Micro-steps per optimizer step (default: 1)\n");
+    fprintf(stderr, "  --lr <float>        Learning rate (default: 3e-4)\n");
+    fprintf(stderr, "  --weight-decay <f>  AdamW weight decay (default: 0)\n");
+    fprintf(stderr, "  --save-every <int>  Save checkpoint every N steps (default: 0 = no save)\n");
+    fprintf(stderr, "  --resume <path>     Resume from checkpoint\n");
+    fprintf(stderr, "  --precision <bf16|fp32>  Weight precision (default: bf16)\n");
+    fprintf(stderr, "  --lora-rank <int>   must be 0: adapters are outside this build\n");
+    return 1;
+}
+
+int main(int argc, char** argv) {
+    if (argc < 2 || strcmp(argv[1], "train") != 0 || argc < 5) return usage(argv[0]);
+    const char *model_path = argv[2], *data_file = argv[3], *output_dir = argv[4];
+    int max_steps = 100, seq_len = 64, batch_size = 1, grad_accum = 1, save_every = 0, lora_rank = 0;
+    float lr = 3e-4f, wd = 0.0f;
+    const char *resume_path = NULL, *prec_str = NULL;
+    for (int i = 5; i < argc; i++) {
+        if (strcmp(argv[i], "--steps") == 0 && i + 1 < argc) max_steps = atoi(argv[++i]);
+        else if (strcmp(argv[i], "--seq-len") == 0 && i + 1 < argc) seq_len = atoi(argv[++i]);
+        else if (strcmp(argv[i], "--batch-size") == 0 && i + 1 < argc) batch_size = atoi(argv[++i]);
+        else if (strcmp(argv[i], "--grad-accum") == 0 && i + 1 < argc) grad_accum = atoi(argv[++i]);
+        else if (strcmp(argv[i], "--lr") == 0 && i + 1 < argc) lr = (float)atof(argv[++i]);
+        else if (strcmp(argv[i], "--weight-decay") == 0 && i + 1 < argc) wd = (float)atof(argv[++i]);
+        else if (strcmp(argv[i], "--save-every") == 0 && i + 1 < argc) save_every = atoi(argv[++i]);
+        else if (strcmp(argv[i], "--resume") == 0 && i + 1 < argc) resume_path = argv[++i];
+        else if (strcmp(argv[i], "--precision") == 0 && i + 1 < argc) prec_str = argv[++i];
+        else if (strcmp(argv[i], "--lora-rank") == 0 && i + 1 < argc) lora_rank = atoi(argv[++i]);
+    }
+    if (batch_size < 1) {
+        fprintf(stderr, "Error: batch-size must be >= 1\n");
+        return 1;
+    }
+    if (lora_rank != 0) {
+        fprintf(stderr, "Error: LoRA adapters are outside this build (--lora-rank must be 0)\n");
+        return 1;
+    }
+    bm_context_t* ctx = bm_create(BM_DEVICE_CUDA);
+    if (!ctx) {
+        fprintf(stderr, "No CUDA (sm_100) device available; this engine has no CPU fallback\n");
+        return 1;
+    }
+    bm_arch_t seed_arch;
+    memset(&seed_arch, 0, sizeof seed_arch);
+    /* a placeholder architecture: bm_load_weights re-creates the buffers from the checkpoint's own description */
+    seed_arch.dim = 64; seed_arch.hidden_dim = 64; seed_arch.n_layers = 1; seed_arch.n_heads = 1; seed_arch.n_kv_heads = 1;
+    seed_arch.vocab_size = 8; seed_arch.padded_vocab_size = 8; seed_arch.max_seq_len = 64; seed_arch.head_dim = 64;
+    seed_arch.norm = BM_NORM_RMSNORM; seed_arch.activation = BM_ACT_SWIGLU; seed_arch.pos_enc = BM_POS_ROPE;
+    seed_arch.attention = BM_ATTN_GQA; seed_arch.weight_tie = 1; seed_arch.gated_mlp = 1; seed_arch.rope_theta = 10000.0f;
+    seed_arch.precision = (prec_str && strcmp(prec_str, "fp32") == 0) ? BM_PRECISION_FP32 : BM_PRECISION_BF16;
+    if (prec_str && strcmp(prec_str, "fp16") == 0) {
+        fprintf(stderr, "Error: fp16 weights are not supported by this backend (use bf16 or fp32)\n");
+        return 1;
+    }
+    bm_model_t* model = bm_create_model(ctx, &seed_arch);
+    if (!model) return 1;
+    bm_load_weights(model, model_path);
+    if (bm_get_num_parameters(model) <= 64 * 64 * 8) {
+        fprintf(stderr, "Failed to load model from %s\n", model_path);
+        return 1;
+    }
+    bm_print_model_info(model);
+
+    /* token stream */
+    int* tokens = NULL;
+    long n_tokens = 0;
+    if (strncmp(data_file, "lcg:", 4) == 0) {
+        size_t np = 0;
+        (void)bmx_model_weight_buffer(model, &np);
+        n_tokens = (long)max_steps * batch_size * seq_len + 1;
+        tokens = (int*)malloc((size_t)n_tokens * sizeof(int));
+        /* vocabulary size: the embedding is the first tensor of the buffer; ask the model info instead of guessing */
+        unsigned s = (unsigned)atoi(data_file + 4);
+        const int V = bmx_model_vocab_size(model);
+        for (long i = 0; i < n_tokens; i++) {
+            s = s * 1664525u + 1013904223u;
+            tokens[i] = (int)(s % (unsigned)V);
+        }
+    } else if (ends_with(data_file, ".bin") || ends_with(data_file, ".tok") || ends_with(data_file, ".tokens")) {
+        FILE* f = fopen(data_file, "rb");
+        if (!f) {
+            fprintf(stderr, "Cannot open data file: %s\n", data_file);
+            return 1;
+        }
+        fseek(f, 0, SEEK_END);
+        n_tokens = ftell(f) / (long)sizeof(int);
+        fseek(f, 0, SEEK_SET);
+        tokens = (int*)malloc((size_t)n_tokens * sizeof(int));
+        if (fread(tokens, sizeof(int), (size_t)n_tokens, f) != (size_t)n_tokens) n_tokens = 0;
+        fclose(f);
+    } else {
+        fprintf(stderr, "Text data needs the tokenizer, which is outside this build: pass int32 token ids (*.bin) or lcg:<seed>\n");
+        return 1;
+    }
+    if (n_tokens < 2) {
+        fprintf(stderr, "No tokens in %s\n", data_file);
+        return 1;
+    }
+    fprintf(stderr, "[train] loaded %ld tokens from %s\n", n_tokens, data_file);
+
+    bm_train_config_t cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.learning_rate = lr; cfg.beta1 = 0.9f; cfg.beta2 = 0.95f; cfg.epsilon = 1e-8f; cfg.weight_decay = wd;
+    cfg.grad_clip = 1.0f; cfg.grad_accum_steps = grad_accum > 0 ? grad_accum : 1; cfg.warmup_steps = 10;
+    cfg.max_steps = max_steps; cfg.seq_len = seq_len;
+    bm_trainer_t* trainer = bm_create_trainer(ctx, model, &cfg);
+    if (!trainer) {
+        fprintf(stderr, "Failed to create trainer\n");
+        return 1;
+    }
+    if (resume_path) {
+        bm_load_state(trainer, resume_path);
+        fprintf(stderr, "[train] resumed from %s\n", resume_path);
+    }
+    const int batch_tokens = batch_size * seq_len;
+    int* inputs = (int*)malloc((size_t)batch_tokens * sizeof(int));
+    int* targets = (int*)malloc((size_t)batch_tokens * sizeof(int));
+    long pos = 0;
+    double total_step_time = 0.0;
+    for (int step = 0; step < max_steps; step++) {
+        for (int b = 0; b < batch_size; b++)
+            for (int i = 0; i < seq_len; i++) {
+                inputs[b * seq_len + i] = tokens[pos % n_tokens];
+                targets[b * seq_len + i] = tokens[(pos + 1) % n_tokens];
+                pos++;
+            }
+        const double t0 = now_ms();
+        const float loss = bm_train_step(trainer, inputs, targets, batch_size, seq_len);
+        const double step_ms = now_ms() - t0;
+        total_step_time += step_ms;
+        printf("step %d/%d: loss=%.4f  step_ms=%.0f  gpu_mem=%.1fMB  rss=%zuMB\n", step + 1, max_steps, loss, step_ms,
+               (double)(bmx_trainer_device_bytes(trainer) / (1024 * 1024)), rss_mb());
+        if (save_every > 0 && (step + 1) % save_every == 0) {
+            char path[512];
+            snprintf(path, sizeof path, "%s/checkpoint_%d.bin", output_dir, step + 1);
+            bm_save_state(trainer, path);
+            fprintf(stderr, "[train] saved checkpoint to %s\n", path);
+        }
+    }
+    bm_train_flush(trainer);
+    printf("Avg step time: %.1fms\n", total_step_time / max_steps);
+    free(inputs); free(targets); free(tokens);
+    bm_destroy_trainer(trainer);
+    bm_destroy_model(model);
+    bm_destroy(ctx);
+    return 0;
+}

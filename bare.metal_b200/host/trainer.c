@@ -70,12 +70,13 @@ static void free_activations(bm_trainer_t* t) {
     }
     bmc_free(be, t->x_last); bmc_free(be, t->nf); bmc_free(be, t->logits); bmc_free(be, t->rstdf); bmc_free(be, t->row_loss);
     bmc_free(be, t->dres); bmc_free(be, t->dn); bmc_free(be, t->dact); bmc_free(be, t->dgu); bmc_free(be, t->dattn); bmc_free(be, t->dqkv);
-    bmc_free(be, t->d_tokens); bmc_free(be, t->d_targets); bmc_free(be, t->d_attn_mask); bmc_free(be, t->d_loss_mask);
+    bmc_free(be, t->d_tokens); bmc_free(be, t->d_targets); bmc_free(be, t->d_attn_mask); bmc_free(be, t->d_row_weight);
     t->x_last = t->nf = t->logits = NULL;
     t->rstdf = t->row_loss = NULL;
     t->dres = t->dn = t->dact = t->dgu = t->dattn = t->dqkv = NULL;
     t->d_tokens = t->d_targets = NULL;
-    t->d_attn_mask = t->d_loss_mask = NULL;
+    t->d_attn_mask = NULL;
+    t->d_row_weight = NULL;
     if (t->h_stage) { bmc_host_free(t->h_stage); t->h_stage = NULL; }
     t->B_cap = 0;
 }
@@ -105,9 +106,9 @@ static int ensure_batch(bm_trainer_t* t, int B) {
     ALLOC(t->dres, M * D * e); ALLOC(t->dn, M * D * e); ALLOC(t->dact, M * H * e); ALLOC(t->dgu, M * 2 * H * e);
     ALLOC(t->dattn, M * QD * e); ALLOC(t->dqkv, M * QKVD * e);
     ALLOC(t->d_tokens, M * sizeof(int)); ALLOC(t->d_targets, M * sizeof(int));
-    ALLOC(t->d_attn_mask, M); ALLOC(t->d_loss_mask, M);
+    ALLOC(t->d_attn_mask, M); ALLOC(t->d_row_weight, M * sizeof(float));
 #undef ALLOC
-    t->h_stage = (int*)bmc_host_alloc(2 * M * sizeof(int) + 2 * M);
+    t->h_stage = (int*)bmc_host_alloc(3 * M * sizeof(int) + M);
     if (!ok || !t->h_stage) {
         BM_LOG_ERROR("bm_train_step: out of device memory for B=%d, S=%d", B, t->S);
         free_activations(t);
@@ -229,7 +230,7 @@ enum { P_LN1 = 0, P_Q, P_K, P_V, P_O, P_LN2, P_GATE, P_UP, P_DOWN };
 #define TRY(call) do { int rc__ = (call); if (rc__) { BM_LOG_ERROR("train step: %s failed (%d)", #call, rc__); return rc__; } } while (0)
 
 /* forward + loss. Tokens, targets (and masks) are already in t->d_tokens / t->d_targets. */
-static int forward_and_loss(bm_trainer_t* t, int B, const uint8_t* d_attn_mask, const uint8_t* d_loss_mask, int with_grad) {
+static int forward_and_loss(bm_trainer_t* t, int B, const uint8_t* d_attn_mask, const float* d_row_weight, int with_grad) {
     bmc_ctx_t* be = t->ctx->be;
     const bm_arch_t* a = &t->model->arch;
     const int L = a->n_layers, D = a->dim, H = a->hidden_dim, V = a->vocab_size, S = t->S;
@@ -262,7 +263,7 @@ static int forward_and_loss(bm_trainer_t* t, int B, const uint8_t* d_attn_mask, 
     /* gradient of the per-sequence mean loss: (softmax - onehot) / S (xent_backward, src/kernels/backward.metal:585);
      * the 1 / (number of sequences) factor is applied by AdamW (src/anneal/adamw.metal:38). */
     (void)with_grad;
-    TRY(bmc_xent(be, dt, t->logits, V, t->row_loss, t->d_loss, t->d_targets, d_loss_mask, B, S, V, 1.0f / (float)S));
+    TRY(bmc_xent(be, dt, t->logits, V, t->row_loss, t->d_loss, t->d_targets, d_row_weight, B, S, V, 1.0f / (float)S));
     return 0;
 }
 
@@ -332,7 +333,7 @@ static int adamw_apply(bm_trainer_t* t) {
 }
 
 /* Everything after the inputs are on the device; asynchronous. */
-static int step_enqueue(bm_trainer_t* t, int B, const uint8_t* d_attn_mask, const uint8_t* d_loss_mask, int train) {
+static int step_enqueue(bm_trainer_t* t, int B, const uint8_t* d_attn_mask, const float* d_row_weight, int train) {
     bmc_ctx_t* be = t->ctx->be;
     const int accum = t->cfg.grad_accum_steps > 0 ? t->cfg.grad_accum_steps : 1;
     if (train && t->accum_count == 0) {
@@ -343,7 +344,7 @@ static int step_enqueue(bm_trainer_t* t, int B, const uint8_t* d_attn_mask, cons
         if (t->dp) bm_dp_begin_window(t->dp);
     }
     if (t->profile) bmc_timer_begin(be, 0);
-    TRY(forward_and_loss(t, B, d_attn_mask, d_loss_mask, train));
+    TRY(forward_and_loss(t, B, d_attn_mask, d_row_weight, train));
     if (t->profile) {
         /* the loss kernels are the tail of forward_and_loss; attribute them separately by bracketing again */
         t->prof_forward_ms += bmc_timer_end(be, 0);
@@ -389,37 +390,39 @@ static float step_host(bm_trainer_t* t, const int* inputs, const int* targets, c
     /* stage through pinned memory so the copies are truly asynchronous */
     memcpy(t->h_stage, inputs, M * sizeof(int));
     memcpy(t->h_stage + M, targets, M * sizeof(int));
-    uint8_t* hm = (uint8_t*)(t->h_stage + 2 * M);
+    float* hw = (float*)(t->h_stage + 2 * M);
+    uint8_t* hm = (uint8_t*)(t->h_stage + 3 * M);
     if (attn_mask) memcpy(hm, attn_mask, M);
-    if (loss_mask) memcpy(hm + M, loss_mask, M);
+    if (loss_mask) {
+        /* completion-only loss: every unmasked row of sequence b weighs 1 / count_b (the reference divides by the number of
+         * unmasked rows, src/baremetal/scheduler.c:1661-1676, src/kernels/backward.metal:620); a sequence without any unmasked
+         * row contributes zero loss and zero gradient (scheduler.c:1679-1684) */
+        for (int b = 0; b < B; ++b) {
+            int count = 0;
+            for (int s = 0; s < T; ++s) count += loss_mask[(size_t)b * T + s] ? 1 : 0;
+            const float w = count > 0 ? 1.0f / (float)count : 0.0f;
+            for (int s = 0; s < T; ++s) hw[(size_t)b * T + s] = loss_mask[(size_t)b * T + s] ? w : 0.0f;
+        }
+    }
     bmc_upload(be, t->d_tokens, t->h_stage, M * sizeof(int));
     bmc_upload(be, t->d_targets, t->h_stage + M, M * sizeof(int));
     if (attn_mask) bmc_upload(be, t->d_attn_mask, hm, M);
-    if (loss_mask) bmc_upload(be, t->d_loss_mask, hm + M, M);
-    if (step_enqueue(t, B, attn_mask ? t->d_attn_mask : NULL, loss_mask ? t->d_loss_mask : NULL, train) != 0) return -1.0f;
+    if (loss_mask) bmc_upload(be, t->d_row_weight, hw, M * sizeof(float));
+    if (step_enqueue(t, B, attn_mask ? t->d_attn_mask : NULL, loss_mask ? t->d_row_weight : NULL, train) != 0) return -1.0f;
     return read_loss(t);
 }
 
 float bm_train_step_masked(bm_trainer_t* t, const int* inputs, const int* targets, const uint8_t* attn_mask, const uint8_t* loss_mask,
                            int B, int T) {
-    if (loss_mask) {
-        /* Completion-only loss needs the per-sequence unmasked-row count as its normaliser
-         * (xent_backward_masked, src/kernels/backward.metal:597-627); not built yet. */
-        BM_LOG_ERROR("bm_train_step_masked: loss masks are not supported by this build");
-        return -1.0f;
-    }
-    return step_host(t, inputs, targets, attn_mask, NULL, B, T, 1);
+    return step_host(t, inputs, targets, attn_mask, loss_mask, B, T, 1);
 }
 float bm_train_step(bm_trainer_t* t, const int* inputs, const int* targets, int B, int T) {
     return step_host(t, inputs, targets, NULL, NULL, B, T, 1);
 }
+/* forward + loss only (bm_train_eval_masked, src/baremetal/trainer.c:425-445) */
 float bm_train_eval_masked(bm_trainer_t* t, const int* inputs, const int* targets, const uint8_t* attn_mask, const uint8_t* loss_mask,
                            int B, int T) {
-    if (loss_mask) {
-        BM_LOG_ERROR("bm_train_eval_masked: loss masks are not supported by this build");
-        return -1.0f;
-    }
-    return step_host(t, inputs, targets, attn_mask, NULL, B, T, 0);
+    return step_host(t, inputs, targets, attn_mask, loss_mask, B, T, 0);
 }
 
 void bm_train_flush(bm_trainer_t* t) {

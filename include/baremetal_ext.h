@@ -59,6 +59,7 @@ float  bmx_timer_end(bm_context_t* ctx, int slot);
 /* Host weight buffer of a model (fp32, the flat order of the legacy .bin payload): lets a caller fill in
  * weights without going through a file. *n_out receives the element count. */
 float* bmx_model_weight_buffer(bm_model_t* model, size_t* n_out);
+int    bmx_model_vocab_size(const bm_model_t* model);
 /* per-launch timing of the tensor-core GEMM (see bmc_gemm_timing in bm_cuda_backend.h) */
 int    bmx_gemm_timing(bm_context_t* ctx, int enable);
 int    bmx_gemm_timing_collect(bm_context_t* ctx, double* out3);

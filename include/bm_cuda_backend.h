@@ -128,8 +128,10 @@ int bmc_add_forward(bmc_ctx_t* ctx, int dtype, void* d_out, const void* d_a, con
 /* ---- loss (host loss loop src/baremetal/scheduler.c:1622-1634 + xent_backward backward.metal:567, masked :597).
  * Overwrites logits with (softmax - onehot) * grad_scale, writes per-row losses, then reduces them to
  * *d_loss = mean over B sequences of the per-sequence mean (src/baremetal/trainer.c:528). ---- */
+/* d_row_weight (float[B*S], may be NULL) selects the completion-only form: the weight of a row is 1 / (unmasked rows of its
+ * sequence) or 0 for a masked row, and replaces grad_scale; the loss is then the batch mean of the per-sequence weighted sums. */
 int bmc_xent(bmc_ctx_t* ctx, int dtype, void* d_logits, int ldv, float* d_row_loss, float* d_loss, const int* d_targets,
-             const uint8_t* d_loss_mask, int B, int S, int V, float grad_scale);
+             const float* d_row_weight, int B, int S, int V, float grad_scale);
 
 /* ---- AdamW over a flat parameter range (adamw_step src/anneal/adamw.metal:26 + the host recast loop
  *      src/baremetal/trainer.c:373-396). hp (HOST pointer, 8 floats) = {lr, b1, b2, eps, wd, 1-b1^t, 1-b2^t, grad_scale}.

@@ -103,6 +103,13 @@ class LibTrainer:
         B = x.shape[0]
         return float(self.lib.bm_train_step(self.tr, bmapi.as_int_ptr(x), bmapi.as_int_ptr(y), B, self.S))
 
+    def step_masked(self, x, y, attn_mask, loss_mask, evaluate=False):
+        B = x.shape[0]
+        am = None if attn_mask is None else np.ascontiguousarray(attn_mask, np.uint8).ctypes.data
+        lm = None if loss_mask is None else np.ascontiguousarray(loss_mask, np.uint8).ctypes.data
+        fn = self.lib.bm_train_eval_masked if evaluate else self.lib.bm_train_step_masked
+        return float(fn(self.tr, bmapi.as_int_ptr(x), bmapi.as_int_ptr(y), am, lm, B, self.S))
+
     def n_tensors(self):
         return self.lib.bmref_n_states(self.tr) if self.kind == "reference" else self.lib.bmx_trainer_num_tensors(self.tr)
 

@@ -86,6 +86,42 @@ def test_step_matches_committed_reference_outputs(product, case):
         assert np.linalg.norm(got_w - ref_w) <= 3 * rel * np.linalg.norm(ref_w) + 1e-9, (case, i)
 
 
+@pytest.mark.parametrize("precision,use_attn_mask", [(F32, True), (F32, False), (BF16, True), (BF16, False)])
+def test_masked_step_matches_reference(product, precision, use_attn_mask):
+    """Completion-only loss with a padding mask (bm_train_step_masked; the reference's masked_sft_test.c): attn == 0 removes a
+    position as key and as query, loss == 1 marks the rows that count, each sequence normalised by its own count; one
+    sequence has no counted row at all."""
+    ref = bmapi.load_reference()
+    if ref is None:
+        pytest.skip("reference build not present")
+    a = bmapi.make_arch("gqa")
+    w = bmapi.make_weights(a)
+    B, S = 3, 48
+    cfg = bmapi.train_config(seq_len=S)
+    x, y = bmapi.lcg_batch(B, S, a.vocab_size)
+    attn = np.ones((B, S), np.uint8)
+    attn[0, 40:] = 0
+    attn[1, 30:] = 0
+    loss = np.zeros((B, S), np.uint8)
+    loss[0, 10:40] = 1
+    loss[1, 5:30] = 1  # sequence 2 keeps an all-zero loss mask
+    am = attn if use_attn_mask else None
+    g = oc.LibTrainer(product, "gpu", a, w, S, precision, cfg, quirks=True)
+    r = oc.LibTrainer(ref, "reference", a, w, S, precision, cfg)
+    le_g, le_r = g.step_masked(x, y, am, loss, evaluate=True), r.step_masked(x, y, am, loss, evaluate=True)
+    lg, lr = g.step_masked(x, y, am, loss), r.step_masked(x, y, am, loss)
+    assert abs(lg - lr) < 1e-3 and abs(le_g - le_r) < 1e-3 and abs(le_g - lg) < 1e-6
+    rel, cos = limits(precision)
+    for i in range(g.n_tensors()):
+        gg, rg = g.read(bmapi.BMX_GRAD, i), r.read(bmapi.BMX_GRAD, i)
+        if not rg.any():  # RMSNorm gains keep only the last sequence's gradient in the reference, and that sequence is fully masked
+            assert not gg.any(), i
+            continue
+        assert oc.rel_err(gg, rg) < rel and oc.cosine(gg, rg) > cos, i
+        assert oc.rel_err(g.read(bmapi.BMX_WEIGHT, i), r.read(bmapi.BMX_WEIGHT, i)) < rel, i
+    g.close(); r.close()
+
+
 def test_sequence_length_mismatch_is_an_error(product):
     a = bmapi.make_arch("tiny")
     tr = oc.LibTrainer(product, "gpu", a, bmapi.make_weights(a), 16, F32, bmapi.train_config(seq_len=16))

@@ -130,3 +130,67 @@ def test_dp_bucket_plan_partitions_the_parameters(product):
         assert list(r)[-1] == -1 and list(r)[:-1] == sorted(list(r)[:-1], reverse=True)  # completion order of backward
         for bi, ri in zip(list(b)[:-1], list(r)[:-1]):
             assert bi == 100 * ri  # a bucket is complete when its lowest layer is
+
+
+def _write_safetensors(path, tensors, dtype="F32"):
+    import json
+    header, blobs, off = {}, [], 0
+    for name, arr in tensors.items():
+        if dtype == "BF16":
+            from devutil import f32_to_bf16_bits
+            raw = f32_to_bf16_bits(arr).tobytes()
+        else:
+            raw = np.ascontiguousarray(arr, np.float32).tobytes()
+        header[name] = {"dtype": dtype, "shape": list(arr.shape), "data_offsets": [off, off + len(raw)]}
+        blobs.append(raw)
+        off += len(raw)
+    hj = json.dumps(header).encode()
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(hj)))
+        f.write(hj)
+        for b in blobs:
+            f.write(b)
+
+
+@pytest.mark.parametrize("dtype,sharded", [("F32", False), ("BF16", False), ("F32", True)])
+def test_safetensors_directory_loader(product, tmp_path, dtype, sharded):
+    """HF-style directory (config.json + *.safetensors with Llama tensor names) into the flat model buffer
+    (the reference's loader: src/baremetal/checkpoint_st.c:430-671; its synthetic-shard test: test/sharded_load_test.c)."""
+    import json
+    lib = product
+    a = bmapi.make_arch("tiny")
+    w = bmapi.make_weights(a, seed=11)
+    w["ln1w"] = np.random.default_rng(1).standard_normal(w["ln1w"].shape).astype(np.float32)
+    cfg = {"model_type": "llama", "hidden_size": a.dim, "intermediate_size": a.hidden_dim, "num_hidden_layers": a.n_layers,
+           "num_attention_heads": a.n_heads, "num_key_value_heads": a.n_kv_heads, "vocab_size": a.vocab_size, "head_dim": a.head_dim,
+           "max_position_embeddings": 2048, "rms_norm_eps": 1e-5, "rope_theta": 100000.0, "tie_word_embeddings": True, "hidden_act": "silu"}
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    names = {"ln1w": "input_layernorm.weight", "qw": "self_attn.q_proj.weight", "kw": "self_attn.k_proj.weight",
+             "vw": "self_attn.v_proj.weight", "ow": "self_attn.o_proj.weight", "ln2w": "post_attention_layernorm.weight",
+             "gate": "mlp.gate_proj.weight", "up": "mlp.up_proj.weight", "down": "mlp.down_proj.weight"}
+    tensors = {"model.embed_tokens.weight": w["embed"], "model.norm.weight": w["lnfw"]}
+    for l in range(a.n_layers):
+        for k, suffix in names.items():
+            tensors[f"model.layers.{l}.{suffix}"] = w[k][l]
+    if sharded:
+        items = list(tensors.items())
+        _write_safetensors(tmp_path / "model-00001-of-00002.safetensors", dict(items[:7]), dtype)
+        _write_safetensors(tmp_path / "model-00002-of-00002.safetensors", dict(items[7:]), dtype)
+        wm = {k: ("model-00001-of-00002.safetensors" if i < 7 else "model-00002-of-00002.safetensors") for i, (k, _) in enumerate(items)}
+        (tmp_path / "model.safetensors.index.json").write_text(json.dumps({"metadata": {}, "weight_map": wm}))
+    else:
+        _write_safetensors(tmp_path / "model.safetensors", tensors, dtype)
+    seed = bmapi.make_arch("tiny")
+    seed.dim, seed.n_layers = 64, 1  # deliberately different: the directory's config.json decides
+    model = lib.bm_create_model(None, C.byref(seed))
+    lib.bm_load_weights(model, str(tmp_path).encode())
+    n = C.c_size_t()
+    flat = np.ctypeslib.as_array(lib.bmx_model_weight_buffer(model, C.byref(n)), (n.value,))
+    expect = np.concatenate([w[k].ravel() for k, _ in bmapi.weight_shapes(a)])
+    assert n.value == expect.size
+    if dtype == "BF16":
+        from devutil import bf16_round
+        expect = bf16_round(expect)
+    assert np.array_equal(flat, expect)
+    assert lib.bmx_model_vocab_size(model) == a.vocab_size
+    lib.bm_destroy_model(model)
