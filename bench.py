@@ -193,6 +193,56 @@ def run_reference_arm(args):
     return 0
 
 
+def run_attention(args):
+    """Isolated causal GQA flash attention forward + backward, bf16, 15 query / 5 KV heads, head_dim 64, batch 16
+    (batch 4 at 8192 keeps the capture small); one JSON line per sequence length."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from devutil import BMC_BF16, Backend, Ptr
+    lib = bmapi.load_product()
+    be = Backend(lib)
+    lib.bmc_timer_begin.argtypes = [C.c_void_p, C.c_int]
+    lib.bmc_timer_end.argtypes = [C.c_void_p, C.c_int]
+    lib.bmc_timer_end.restype = C.c_float
+    NH, NKV, HD = 15, 5, 64
+    QD, KV = NH * HD, NKV * HD
+    ld = QD + 2 * KV
+    peaks, src = measured_peaks()
+    for S in ([args.seq_len] if args.seq_len != SEQ_LEN or "--seq-len" in sys.argv else [512, 2048, 8192]):
+        B = 16 if S <= 2048 else 4
+        M = B * S
+        rng = np.random.default_rng(S)
+        d = be.put(rng.standard_normal((M, ld)).astype(np.float32), BMC_BF16)
+        dgo = be.put(rng.standard_normal((M, QD)).astype(np.float32), BMC_BF16)
+        out, lse, dg = be.zeros(M * QD, BMC_BF16), be.zeros(B * NH * S), be.zeros(M * ld, BMC_BF16)
+
+        def fwd():
+            be.call("attention_forward", BMC_BF16, Ptr(out), QD, Ptr(lse), Ptr(d), ld, Ptr(d, QD * 2), Ptr(d, (QD + KV) * 2), ld, None, B, S, NH, NKV, HD, 0.125)
+
+        def bwd():
+            be.call("attention_backward", BMC_BF16, Ptr(dg), ld, Ptr(dg, QD * 2), Ptr(dg, (QD + KV) * 2), ld, Ptr(dgo), QD, Ptr(out), Ptr(lse), Ptr(d), ld,
+                    Ptr(d, QD * 2), Ptr(d, (QD + KV) * 2), ld, None, B, S, NH, NKV, HD, 0.125)
+        res = {}
+        for name, fn in (("fwd", fwd), ("bwd", bwd)):
+            for _ in range(max(args.warmup, 3)):
+                fn()
+            assert lib.bmc_sync(be.ctx) == 0
+            lib.bmc_timer_begin(be.ctx, 0)
+            for _ in range(args.steps):
+                fn()
+            res[name] = lib.bmc_timer_end(be.ctx, 0) / args.steps
+        flops_fwd = 2.0 * B * NH * S * S * HD  # causal-counted: half of the full 4*S^2*HD; backward is twice the forward
+        tf = (3 * flops_fwd) / ((res["fwd"] + res["bwd"]) * 1e-3) / 1e12
+        print(json.dumps({"metric": "attention_fwd_bwd_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+                          "warmup": max(args.warmup, 3), "ms_per_step": res["fwd"] + res["bwd"], "higher_is_better": True, "dtype": "bf16",
+                          "data": "synthetic", "config": {"workload": f"causal GQA flash attention fwd+bwd, NH {NH} NKV {NKV} HD {HD}, batch {B}, seq {S}"},
+                          "fwd_ms": res["fwd"], "bwd_ms": res["bwd"], "fwd_tflops": flops_fwd / (res["fwd"] * 1e-3) / 1e12,
+                          "bwd_tflops": 2 * flops_fwd / (res["bwd"] * 1e-3) / 1e12,
+                          "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                                       "frac": tf / peaks["bf16_tflops"], "traffic": None, "peak_source": f"bf16_tflops (burst) of {src}"}}), flush=True)
+    be.close()
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -203,9 +253,13 @@ def main():
     ap.add_argument("--batch", type=int, default=PER_GPU_BATCH)
     ap.add_argument("--seq-len", type=int, default=SEQ_LEN)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="train", choices=["train", "attention"],
+                    help="train (default, the contract line) or attention: isolated GQA flash attention fwd+bwd")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
+    if args.workload == "attention":
+        return run_attention(args)
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -1,0 +1,93 @@
+"""Isolated causal GQA flash attention, forward + backward, bf16, 15 query heads / 5 KV heads, head_dim 64, at
+seq in {512, 2048, 8192}: O, dQ, dK, dV against the reference's attention arithmetic
+(attention_forward_seq / attention_backward, src/kernels/forward.metal:1811, src/kernels/backward.metal:665, restated in
+oracle/bm_oracle.c with the per-thread array bound lifted). Q, K, V, dO ~ N(0, 1) by seed, rounded to bf16 for both sides.
+S = 512 and 2048: the CPU oracle on whole sequences. S = 8192: the CPU oracle is O(S^2) scalar work, so it checks a prefix of
+the forward exactly (causal outputs of the first queries do not depend on later keys) and the backward is checked against
+the exact-softmax fp32 GPU kernel, which the smaller cases tie to the oracle. Tolerance: 2e-2 relative, cosine > 0.999."""
+import numpy as np
+import pytest
+
+import oracle_check as oc
+import portk
+from devutil import BMC_BF16, BMC_F32, Backend, Ptr, bf16_round
+
+pytestmark = pytest.mark.gpu
+NH, NKV, HD = 15, 5, 64
+QD, KV = NH * HD, NKV * HD
+LD = QD + 2 * KV
+SCALE = 1.0 / np.sqrt(HD)
+
+
+@pytest.fixture(scope="module")
+def be(product):
+    b = Backend(product)
+    yield b
+    b.close()
+
+
+def run_gpu(be, dtype, qkv, go, B, S):
+    es = 2 if dtype == BMC_BF16 else 4
+    d, dgo = be.put(qkv, dtype), be.put(go, dtype)
+    out, lse, dg = be.zeros(B * S * QD, dtype), be.zeros(B * NH * S), be.zeros(B * S * LD, dtype)
+    be.ok("attention_forward", dtype, Ptr(out), QD, Ptr(lse), Ptr(d), LD, Ptr(d, QD * es), Ptr(d, (QD + KV) * es), LD, None, B, S, NH, NKV, HD, float(SCALE))
+    be.ok("attention_backward", dtype, Ptr(dg), LD, Ptr(dg, QD * es), Ptr(dg, (QD + KV) * es), LD, Ptr(dgo), QD, Ptr(out), Ptr(lse), Ptr(d), LD,
+          Ptr(d, QD * es), Ptr(d, (QD + KV) * es), LD, None, B, S, NH, NKV, HD, float(SCALE))
+    return be.get(out, (B, S, QD), dtype), be.get(dg, (B, S, LD), dtype)
+
+
+def close(got, ref, what):
+    assert oc.rel_err(got, ref) < 2e-2, (what, oc.rel_err(got, ref))
+    assert oc.cosine(got.ravel(), ref.ravel()) > 0.999, what
+
+
+@pytest.mark.parametrize("S,B", [(512, 2), (2048, 1)])
+def test_flash_attention_against_the_oracle(be, S, B):
+    rng = np.random.default_rng(S)
+    qkv = bf16_round(rng.standard_normal((B * S, LD)).astype(np.float32))
+    go = bf16_round(rng.standard_normal((B * S, QD)).astype(np.float32))
+    out, dg = run_gpu(be, BMC_BF16, qkv, go, B, S)
+    x = qkv.reshape(B, S, LD)
+    for b in range(B):
+        Q, K, V = x[b, :, :QD].reshape(S, NH, HD), x[b, :, QD:QD + KV].reshape(S, NKV, HD), x[b, :, QD + KV:].reshape(S, NKV, HD)
+        close(out[b].reshape(S, NH, HD), portk.attention_forward(Q, K, V, SCALE), "O")
+        gq, gk, gv = portk.attention_backward(go.reshape(B, S, NH, HD)[b], Q, K, V, SCALE)
+        close(dg[b, :, :QD].reshape(S, NH, HD), gq, "dQ")
+        close(dg[b, :, QD:QD + KV].reshape(S, NKV, HD), gk, "dK")
+        close(dg[b, :, QD + KV:].reshape(S, NKV, HD), gv, "dV")
+
+
+def test_flash_attention_8192(be):
+    S, B = 8192, 1
+    rng = np.random.default_rng(8192)
+    qkv = bf16_round(rng.standard_normal((B * S, LD)).astype(np.float32))
+    go = bf16_round(rng.standard_normal((B * S, QD)).astype(np.float32))
+    out, dg = run_gpu(be, BMC_BF16, qkv, go, B, S)
+    # forward prefix against the CPU oracle
+    n = 768
+    x = qkv.reshape(S, LD)
+    Q, K, V = x[:n, :QD].reshape(n, NH, HD), x[:n, QD:QD + KV].reshape(n, NKV, HD), x[:n, QD + KV:].reshape(n, NKV, HD)
+    close(out[0, :n].reshape(n, NH, HD), portk.attention_forward(Q, K, V, SCALE), "O prefix")
+    # whole problem against the exact fp32 kernel on the same (bf16-rounded) inputs
+    out32, dg32 = run_gpu(be, BMC_F32, qkv, go, B, S)
+    close(out, out32, "O")
+    close(dg[..., :QD], dg32[..., :QD], "dQ")
+    close(dg[..., QD:QD + KV], dg32[..., QD:QD + KV], "dK")
+    close(dg[..., QD + KV:], dg32[..., QD + KV:], "dV")
+    assert np.isfinite(dg).all()
+
+
+def test_exact_kernel_matches_oracle_at_2048(be):
+    """Ties the fp32 GPU kernel used as the 8192 cross-check to the CPU oracle (one KV group, S = 2048)."""
+    S = 2048
+    rng = np.random.default_rng(5)
+    qkv = rng.standard_normal((S, LD)).astype(np.float32)
+    go = rng.standard_normal((S, QD)).astype(np.float32)
+    out, dg = run_gpu(be, BMC_F32, qkv, go, 1, S)
+    Q, K, V = qkv[:, :QD].reshape(S, NH, HD), qkv[:, QD:QD + KV].reshape(S, NKV, HD), qkv[:, QD + KV:].reshape(S, NKV, HD)
+    ref_o = portk.attention_forward(Q, K, V, SCALE)
+    assert oc.rel_err(out[0].reshape(S, NH, HD), ref_o) < 1e-5
+    gq, gk, gv = portk.attention_backward(go.reshape(S, NH, HD), Q, K, V, SCALE)
+    assert oc.rel_err(dg[0, :, :QD].reshape(S, NH, HD), gq) < 2e-5
+    assert oc.rel_err(dg[0, :, QD:QD + KV].reshape(S, NKV, HD), gk) < 2e-5
+    assert oc.rel_err(dg[0, :, QD + KV:].reshape(S, NKV, HD), gv) < 2e-5
