@@ -75,8 +75,10 @@ def weight_shapes(a):
             ("up", (L, H, D)), ("down", (L, D, H)), ("lnfw", (D,))]
 
 
-def make_weights(a, seed=42, std=0.02):
-    """Random-init weights: every matrix N(0, std^2) from `seed`; RMSNorm gains are 1."""
+def make_weights(a, seed=42, std=0.02, layer_scale=1.0):
+    """Random-init weights: every matrix N(0, std^2) from `seed`; RMSNorm gains are 1. layer_scale multiplies the
+    per-layer matrices (not the embedding): with tied embeddings a larger value lets the layers, rather than the input
+    token's own embedding row, decide the next token, which makes greedy continuations non-trivial."""
     rng = np.random.default_rng(seed)
     w = {}
     for name, shape in weight_shapes(a):
@@ -84,6 +86,8 @@ def make_weights(a, seed=42, std=0.02):
             w[name] = np.ones(shape, np.float32)
         else:
             w[name] = (rng.standard_normal(shape, dtype=np.float32) * np.float32(std)).astype(np.float32)
+            if name != "embed" and layer_scale != 1.0:
+                w[name] *= np.float32(layer_scale)
     return w
 
 
@@ -161,6 +165,8 @@ def bind_public_api(lib):
         "bm_train_flush": (None, [vp]),
         "bm_save_state": (None, [vp, C.c_char_p]), "bm_load_state": (None, [vp, C.c_char_p]),
         "bm_destroy_trainer": (None, [vp]),
+        "bm_create_session": (vp, [vp, vp]), "bm_forward": (fp, [vp, ip, C.c_int]), "bm_step": (fp, [vp, C.c_int]),
+        "bm_reset_session": (None, [vp]), "bm_destroy_session": (None, [vp]),
         "bm_create_sampler": (vp, [C.c_int, C.c_float, C.c_float, C.c_uint64]),
         "bm_sample": (C.c_int, [vp, fp]), "bm_destroy_sampler": (None, [vp]),
     }
@@ -196,6 +202,11 @@ def load_product():
         "bmx_timer_begin": (C.c_int, [vp, C.c_int]), "bmx_timer_end": (C.c_float, [vp, C.c_int]),
         "bmx_model_weight_buffer": (fp, [vp, C.POINTER(C.c_size_t)]),
         "bmx_gemm_timing": (C.c_int, [vp, C.c_int]), "bmx_gemm_timing_collect": (C.c_int, [vp, C.POINTER(C.c_double)]),
+        "bmx_model_set_quant": (C.c_int, [vp, C.c_int]), "bmx_model_vocab_size": (C.c_int, [vp]),
+        "bmx_quantize_q8": (C.c_size_t, [fp, vp, fp, C.c_size_t]),
+        "bmx_create_session_batched": (vp, [vp, vp, C.c_int, C.c_int]),
+        "bmx_session_generate_greedy": (C.c_int, [vp, ip, C.c_int, C.c_int, ip]),
+        "bmx_session_logits": (fp, [vp]), "bmx_session_position": (C.c_int, [vp]), "bmx_session_weight_bytes": (C.c_size_t, [vp]),
         "bmx_dp_unique_id": (C.c_int, [vp]), "bmx_trainer_dp_init": (C.c_int, [vp, C.c_int, C.c_int, vp]),
     }
     for name, (res, args) in ext.items():
@@ -226,6 +237,8 @@ def load_reference():
     lib = bind_public_api(C.CDLL(REF_LIB_PATH))
     vp, fp = C.c_void_p, C.POINTER(C.c_float)
     lib.bmref_set_precision.argtypes = [vp, C.c_int]
+    lib.bmref_set_quant.argtypes = [vp, C.c_int]
+    lib.bmt_quantize_q8.restype, lib.bmt_quantize_q8.argtypes = C.c_size_t, [fp, vp, C.c_size_t]
     lib.bmref_n_states.restype, lib.bmref_n_states.argtypes = C.c_int, [vp]
     lib.bmref_state_size.restype, lib.bmref_state_size.argtypes = C.c_size_t, [vp, C.c_int]
     for n in ("bmref_grad", "bmref_weight", "bmref_m", "bmref_v"):

@@ -11,6 +11,7 @@
 #include <vector>
 
 #include "attention_mma.cuh"
+#include "decode_kernels.cuh"
 #include "gemm_umma.cuh"
 #include "kernels.cuh"
 
@@ -37,6 +38,8 @@ struct bmc_ctx_s {
     std::vector<cudaEvent_t> gt_events;  // pairs (begin, end)
     std::vector<double> gt_flops;
     size_t gt_used;
+    cudaGraph_t graph;
+    cudaGraphExec_t graph_exec;
 };
 
 namespace {
@@ -143,6 +146,8 @@ bmc_ctx_t* bmc_create(int device_ordinal) {
     ctx->attn_scratch_bytes = 0;
     ctx->gemm_timing = false;
     ctx->gt_used = 0;
+    ctx->graph = nullptr;
+    ctx->graph_exec = nullptr;
     if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) { delete ctx; return nullptr; }
     if (cudaMalloc(&ctx->d_err, sizeof(int)) != cudaSuccess) { delete ctx; return nullptr; }
     cudaMemset(ctx->d_err, 0, sizeof(int));
@@ -166,6 +171,8 @@ void bmc_destroy(bmc_ctx_t* ctx) {
         cudaEventDestroy(ctx->ev1[i]);
     }
     for (auto e : ctx->gt_events) cudaEventDestroy(e);
+    if (ctx->graph_exec) cudaGraphExecDestroy(ctx->graph_exec);
+    if (ctx->graph) cudaGraphDestroy(ctx->graph);
     cudaStreamDestroy(ctx->stream);
     delete ctx;
 }
@@ -462,6 +469,59 @@ int bmc_seq_prefix_accumulate(bmc_ctx_t* ctx, int dtype, void* d_x, float* d_car
 int bmc_argmax(bmc_ctx_t* ctx, int* d_index, const float* d_logits, int V) {
     BMC_CHECK_CTX(ctx);
     return note(ctx, argmax_first(d_index, d_logits, V, ctx->stream));
+}
+
+// ---- inference (decode) ------------------------------------------------------------------------------
+int bmc_decode_gemv(bmc_ctx_t* ctx, float* d_out, int ldo, const float* d_x, int ldx, int wtype, const void* d_w, const float* d_scales,
+                    const float* d_residual, int ldr, int NB, int C, int OC) {
+    BMC_CHECK_CTX(ctx);
+    return note(ctx, decode_gemv(d_out, ldo, d_x, ldx, wtype, d_w, d_scales, d_residual, ldr, NB, C, OC, ctx->stream));
+}
+int bmc_decode_rmsnorm(bmc_ctx_t* ctx, float* d_out, const float* d_x, const float* d_w, int NB, int C, float eps) {
+    BMC_CHECK_CTX(ctx);
+    return note(ctx, decode_rmsnorm(d_out, d_x, d_w, NB, C, eps, ctx->stream));
+}
+int bmc_decode_rope_kv(bmc_ctx_t* ctx, float* d_qkv, float* d_cache, const float* d_cs_table, const int* d_pos, int layer, int NB, int MS,
+                       int NH, int NKV, int HD) {
+    BMC_CHECK_CTX(ctx);
+    return note(ctx, decode_rope_kv(d_qkv, d_cache, d_cs_table, d_pos, layer, NB, MS, NH, NKV, HD, ctx->stream));
+}
+int bmc_decode_attention(bmc_ctx_t* ctx, float* d_out, const float* d_qkv, const float* d_cache, const int* d_pos, int layer, int NB,
+                         int MS, int NH, int NKV, int HD, float scale) {
+    BMC_CHECK_CTX(ctx);
+    return note(ctx, decode_attention(d_out, d_qkv, d_cache, d_pos, layer, NB, MS, NH, NKV, HD, scale, ctx->stream));
+}
+int bmc_decode_swiglu(bmc_ctx_t* ctx, float* d_out, const float* d_gate_up, int NB, int H) {
+    BMC_CHECK_CTX(ctx);
+    return note(ctx, decode_swiglu(d_out, d_gate_up, NB, H, ctx->stream));
+}
+int bmc_decode_embed(bmc_ctx_t* ctx, float* d_out, int table_type, const void* d_table, const int* d_tokens, int NB, int D) {
+    BMC_CHECK_CTX(ctx);
+    return note(ctx, decode_embed(d_out, table_type, d_table, d_tokens, NB, D, ctx->stream));
+}
+int bmc_decode_argmax(bmc_ctx_t* ctx, int* d_out, const float* d_logits, int NB, int V) {
+    BMC_CHECK_CTX(ctx);
+    return note(ctx, decode_argmax(d_out, d_logits, NB, V, ctx->stream));
+}
+int bmc_decode_advance(bmc_ctx_t* ctx, int* d_pos) {
+    BMC_CHECK_CTX(ctx);
+    return note(ctx, decode_advance(d_pos, ctx->stream));
+}
+int bmc_graph_begin(bmc_ctx_t* ctx) {
+    BMC_CHECK_CTX(ctx);
+    if (ctx->graph_exec) { cudaGraphExecDestroy(ctx->graph_exec); ctx->graph_exec = nullptr; }
+    if (ctx->graph) { cudaGraphDestroy(ctx->graph); ctx->graph = nullptr; }
+    return cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess ? 0 : -1;
+}
+int bmc_graph_end(bmc_ctx_t* ctx) {
+    BMC_CHECK_CTX(ctx);
+    if (cudaStreamEndCapture(ctx->stream, &ctx->graph) != cudaSuccess || !ctx->graph) return -1;
+    return cudaGraphInstantiate(&ctx->graph_exec, ctx->graph, 0) == cudaSuccess ? 0 : -2;
+}
+int bmc_graph_launch(bmc_ctx_t* ctx) {
+    BMC_CHECK_CTX(ctx);
+    if (!ctx->graph_exec) return -1;
+    return cudaGraphLaunch(ctx->graph_exec, ctx->stream) == cudaSuccess ? 0 : -2;
 }
 
 }  // extern "C"

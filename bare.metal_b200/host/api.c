@@ -83,24 +83,8 @@ void bm_destroy_model(bm_model_t* model) {
 void bm_compile(bm_model_t* model) { (void)model; }
 void bm_autotune(bm_model_t* model, int warmup, int iterations) { (void)model; (void)warmup; (void)iterations; }
 
-/* ---- outside this build: same signatures, failure values ---------------------------------------------- */
+/* ---- outside this build (tokenizer, adapters, sampled generation driver): same signatures, failure values ---------------------------------------------- */
 int bm_load_adapter(bm_model_t* model, const char* path) { (void)model; (void)path; return -1; }
-bm_session_t* bm_create_session(bm_context_t* ctx, bm_model_t* model) {
-    (void)ctx; (void)model;
-    BM_LOG_ERROR("bm_create_session: the inference session is outside this build");
-    return NULL;
-}
-float* bm_forward(bm_session_t* s, const int* tokens, int n) { (void)s; (void)tokens; (void)n; return NULL; }
-float* bm_step(bm_session_t* s, int token) { (void)s; (void)token; return NULL; }
-void bm_reset_session(bm_session_t* s) { (void)s; }
-void bm_destroy_session(bm_session_t* s) { (void)s; }
-void bm_profile_begin(bm_session_t* s) { (void)s; }
-void bm_profile_end(bm_session_t* s, double* a, double* m, double* o) {
-    (void)s;
-    if (a) *a = 0.0;
-    if (m) *m = 0.0;
-    if (o) *o = 0.0;
-}
 int bm_run_tokens(bm_context_t* ctx, bm_model_t* model, const int* prompt_ids, int n_prompt, int steps, float temperature, int top_k,
                   float top_p, uint64_t seed, bm_token_cb_t callback, void* user_data) {
     (void)ctx; (void)model; (void)prompt_ids; (void)n_prompt; (void)steps; (void)temperature; (void)top_k; (void)top_p; (void)seed;
@@ -202,3 +186,8 @@ float* bmx_model_weight_buffer(bm_model_t* model, size_t* n_out) {
 int bmx_gemm_timing(bm_context_t* ctx, int enable) { return ctx ? bmc_gemm_timing(ctx->be, enable) : -1; }
 int bmx_gemm_timing_collect(bm_context_t* ctx, double* out3) { return ctx ? bmc_gemm_timing_collect(ctx->be, out3) : -1; }
 int bmx_model_vocab_size(const bm_model_t* model) { return model ? model->arch.vocab_size : 0; }
+int bmx_model_set_quant(bm_model_t* model, int bits) {
+    if (!model || (bits != 0 && bits != 8)) return -1; /* Q4 is outside this build */
+    model->quant_bits = bits;
+    return 0;
+}

@@ -31,6 +31,7 @@ struct bm_model_s {
     bm_precision_t precision;
     size_t n_parameters;
     int head_size, kv_dim, kv_mul;
+    int quant_bits; /* 0 = weights as stored, 8 = Q8 layer matrices for inference sessions */
     float* weight_buffer;
     float *embed, *ln1w, *qw, *kw, *vw, *ow, *ln2w, *gate, *up, *down, *lnfw;
 };

@@ -1,0 +1,386 @@
+/* Inference session: prefill and token-by-token decode with a KV cache, Q8 / bf16 / fp32 weights and fp32 activations.
+ * Counterpart of the reference's session + decode scheduler walk (src/baremetal/session.c:34-185,
+ * src/baremetal/scheduler.c:712-996, decode graph src/baremetal/graph.c:109-240):
+ *   per layer  RMSNorm -> Q,K,V GEMV -> RoPE at the current position -> K,V into the cache -> attention over the cache ->
+ *              O GEMV + residual -> RMSNorm -> gate,up GEMV -> SwiGLU -> down GEMV + residual;
+ *   then       final RMSNorm -> LM-head GEMV (never quantised, src/baremetal/graph.c:228-239) -> logits.
+ * Q8 quantisation is the reference's (bmt_quantize_q8, src/baremetal/quant.c:10-29,54-60): per 32 weights of a row,
+ * scale = amax / 127, q = lroundf(w / scale) clamped to [-128, 127]; applied to every 2-D layer matrix.
+ * The whole step is enqueued without host synchronisation and, after the first token, replayed as a CUDA graph; the
+ * position lives in device memory. bm_forward with several tokens runs the same step per token, which the reference
+ * establishes as equivalent to its sequence prefill (test/prefill_test.c).
+ * The public API drives one sequence; bmx_create_session_batched runs NB independent sequences in lock step. */
+#include <math.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "bm_internal.h"
+
+typedef struct {
+    void* w;       /* int8 q[OC][C], or bf16 / fp32 [OC][C] */
+    float* scales; /* Q8 only: [OC][C/32] */
+    int OC, C;
+} bm_mat_t;
+
+typedef struct {
+    float *ln1, *ln2;
+    bm_mat_t qkv, o, gu, down;
+} bm_dec_layer_t;
+
+struct bm_session_s {
+    bm_context_t* ctx;
+    bm_model_t* model;
+    int NB, MS, pos, wtype, head_type;
+    bm_dec_layer_t* layers;
+    float* lnf;
+    void* head;   /* [V, D] bf16 or fp32: LM head */
+    float* embed; /* [V, D] fp32 embedding table as loaded (src/baremetal/session.c:114-123); aliases head in fp32 mode */
+    float *cache, *cs, *x, *xn, *qkv, *att, *x1, *gu, *act, *logits;
+    int *d_pos, *d_tokens, *d_next, *d_gen;
+    int gen_cap;
+    float* h_logits;
+    int graph_ready;
+};
+
+/* reference quantiser, one 32-wide block (src/baremetal/quant.c:10-29) */
+static void quantize_q8_block(const float* p, float* scale_out, int8_t* q) {
+    float amax = 0.0f;
+    for (int i = 0; i < 32; i++) {
+        const float a = fabsf(p[i]);
+        if (a > amax) amax = a;
+    }
+    const float scale = amax / 127.0f;
+    *scale_out = scale;
+    if (scale == 0.0f) {
+        memset(q, 0, 32);
+        return;
+    }
+    const float inv = 1.0f / scale;
+    for (int i = 0; i < 32; i++) {
+        long v = lroundf(p[i] * inv);
+        if (v > 127) v = 127;
+        if (v < -128) v = -128;
+        q[i] = (int8_t)v;
+    }
+}
+/* exported for tests: quantise n floats (n % 32 == 0) into q[n] and scales[n/32] */
+size_t bmx_quantize_q8(const float* src, int8_t* q, float* scales, size_t n) {
+    if (n == 0 || (n % 32) != 0) return 0;
+    for (size_t b = 0; b < n / 32; b++) quantize_q8_block(src + b * 32, &scales[b], q + b * 32);
+    return n / 32;
+}
+
+/* upload `rows` (OC x C fp32, given as up to three row blocks that are concatenated) in the session's weight type */
+static int upload_matrix(bm_session_t* s, bm_mat_t* m, int wtype, const float* const* parts, const int* part_rows, int n_parts, int C) {
+    bmc_ctx_t* be = s->ctx->be;
+    int OC = 0;
+    for (int i = 0; i < n_parts; i++) OC += part_rows[i];
+    m->OC = OC;
+    m->C = C;
+    const size_t n = (size_t)OC * C;
+    float* host = (float*)malloc(n * sizeof(float));
+    if (!host) return -1;
+    size_t off = 0;
+    for (int i = 0; i < n_parts; i++) {
+        memcpy(host + off, parts[i], (size_t)part_rows[i] * C * sizeof(float));
+        off += (size_t)part_rows[i] * C;
+    }
+    int rc = 0;
+    if (wtype == BMC_W_Q8) {
+        /* quantised from the loaded values; a bf16 checkpoint was widened exactly, so this equals the reference's
+         * bmt_quantize_q8_bf16 for bf16 sources and bmt_quantize_q8 for fp32 ones (src/baremetal/scheduler.c:378-384) */
+        int8_t* q = (int8_t*)malloc(n);
+        float* sc = (float*)malloc(n / 32 * sizeof(float));
+        bmx_quantize_q8(host, q, sc, n);
+        m->w = bmc_alloc(be, n);
+        m->scales = (float*)bmc_alloc(be, n / 32 * sizeof(float));
+        if (!m->w || !m->scales) rc = -1;
+        else { bmc_upload(be, m->w, q, n); bmc_upload(be, m->scales, sc, n / 32 * sizeof(float)); bmc_sync(be); }
+        free(q);
+        free(sc);
+    } else if (wtype == BMC_W_BF16) {
+        uint16_t* h = (uint16_t*)malloc(n * 2);
+        bm_f32_to_bf16_array(host, h, n);
+        m->w = bmc_alloc(be, n * 2);
+        if (!m->w) rc = -1;
+        else { bmc_upload(be, m->w, h, n * 2); bmc_sync(be); }
+        free(h);
+    } else {
+        m->w = bmc_alloc(be, n * sizeof(float));
+        if (!m->w) rc = -1;
+        else { bmc_upload(be, m->w, host, n * sizeof(float)); bmc_sync(be); }
+    }
+    free(host);
+    return rc;
+}
+
+static float* upload_f32(bm_session_t* s, const float* src, size_t n) {
+    float* d = (float*)bmc_alloc(s->ctx->be, n * sizeof(float));
+    if (d) bmc_upload(s->ctx->be, d, src, n * sizeof(float));
+    return d;
+}
+
+bm_session_t* bmx_create_session_batched(bm_context_t* ctx, bm_model_t* model, int n_sequences, int max_positions) {
+    if (!ctx || !ctx->be || !model || !model->weight_buffer || n_sequences < 1) return NULL;
+    const bm_arch_t* a = &model->arch;
+    if (model->precision == BM_PRECISION_FP16) {
+        BM_LOG_ERROR("bm_create_session: fp16 weights are not supported by this backend");
+        return NULL;
+    }
+    if ((a->dim % 32) || (a->hidden_dim % 32) || ((a->n_heads * model->head_size) % 32)) {
+        BM_LOG_ERROR("bm_create_session: layer widths must be multiples of 32");
+        return NULL;
+    }
+    bm_session_t* s = (bm_session_t*)calloc(1, sizeof *s);
+    if (!s) return NULL;
+    s->ctx = ctx;
+    s->model = model;
+    s->NB = n_sequences;
+    s->MS = max_positions > 0 ? max_positions : (a->max_seq_len > 0 ? a->max_seq_len : 2048);
+    const int lowp = model->precision == BM_PRECISION_BF16;
+    s->wtype = model->quant_bits == 8 ? BMC_W_Q8 : (lowp ? BMC_W_BF16 : BMC_W_F32);
+    s->head_type = lowp ? BMC_W_BF16 : BMC_W_F32;
+    bmc_ctx_t* be = ctx->be;
+    const int L = a->n_layers, D = a->dim, H = a->hidden_dim, V = a->vocab_size, HD = model->head_size;
+    const int QD = a->n_heads * HD, KV = model->kv_dim, NB = s->NB, MS = s->MS;
+    s->layers = (bm_dec_layer_t*)calloc(L, sizeof(bm_dec_layer_t));
+    int ok = s->layers != NULL;
+    for (int l = 0; l < L && ok; l++) {
+        bm_dec_layer_t* y = &s->layers[l];
+        y->ln1 = upload_f32(s, model->ln1w + (size_t)l * D, D);
+        y->ln2 = upload_f32(s, model->ln2w + (size_t)l * D, D);
+        const float* p3[3] = {model->qw + (size_t)l * QD * D, model->kw + (size_t)l * KV * D, model->vw + (size_t)l * KV * D};
+        const int r3[3] = {QD, KV, KV};
+        const float* po[1] = {model->ow + (size_t)l * D * QD};
+        const int ro[1] = {D};
+        const float* pg[2] = {model->gate + (size_t)l * H * D, model->up + (size_t)l * H * D};
+        const int rg[2] = {H, H};
+        const float* pd[1] = {model->down + (size_t)l * D * H};
+        const int rd[1] = {D};
+        ok = y->ln1 && y->ln2 && upload_matrix(s, &y->qkv, s->wtype, p3, r3, 3, D) == 0 && upload_matrix(s, &y->o, s->wtype, po, ro, 1, QD) == 0 &&
+             upload_matrix(s, &y->gu, s->wtype, pg, rg, 2, D) == 0 && upload_matrix(s, &y->down, s->wtype, pd, rd, 1, H) == 0;
+    }
+    if (ok) {
+        s->lnf = upload_f32(s, model->lnfw, D);
+        bm_mat_t head = {0};
+        const float* ph[1] = {model->embed};
+        const int rh[1] = {V};
+        ok = s->lnf && upload_matrix(s, &head, s->head_type, ph, rh, 1, D) == 0;
+        s->head = head.w;
+        if (ok && s->head_type == BMC_W_F32) s->embed = (float*)s->head;
+        else if (ok) { s->embed = upload_f32(s, model->embed, (size_t)V * D); ok = s->embed != NULL; }
+    }
+    /* RoPE table with the reference's fp32 formula (rope_inv_freq, src/kernels/forward.metal:1260-1279) */
+    if (ok) {
+        const int hd2 = HD / 2;
+        float* cs = (float*)malloc((size_t)MS * hd2 * 2 * sizeof(float));
+        for (int i = 0; i < hd2; i++) {
+            const float inv = 1.0f / powf(a->rope_theta, (float)(2 * i) / (float)HD);
+            for (int p = 0; p < MS; p++) {
+                cs[((size_t)p * hd2 + i) * 2] = cosf((float)p * inv);
+                cs[((size_t)p * hd2 + i) * 2 + 1] = sinf((float)p * inv);
+            }
+        }
+        s->cs = upload_f32(s, cs, (size_t)MS * hd2 * 2);
+        bmc_sync(be);
+        free(cs);
+    }
+#define DALLOC(p, n) do { (p) = bmc_alloc(be, (size_t)(n)); if (!(p)) ok = 0; } while (0)
+    if (ok) {
+        DALLOC(s->cache, (size_t)L * 2 * NB * MS * KV * sizeof(float));
+        DALLOC(s->x, (size_t)NB * D * 4); DALLOC(s->xn, (size_t)NB * D * 4); DALLOC(s->qkv, (size_t)NB * (QD + 2 * KV) * 4);
+        DALLOC(s->att, (size_t)NB * QD * 4); DALLOC(s->x1, (size_t)NB * D * 4); DALLOC(s->gu, (size_t)NB * 2 * H * 4);
+        DALLOC(s->act, (size_t)NB * H * 4); DALLOC(s->logits, (size_t)NB * V * 4);
+        DALLOC(s->d_pos, 16); DALLOC(s->d_tokens, (size_t)NB * 4); DALLOC(s->d_next, (size_t)NB * 4);
+    }
+#undef DALLOC
+    s->h_logits = (float*)malloc((size_t)NB * V * sizeof(float));
+    if (!ok || !s->cs || !s->h_logits) {
+        BM_LOG_ERROR("bm_create_session: out of memory");
+        bm_destroy_session(s);
+        return NULL;
+    }
+    bmc_memset(be, s->d_pos, 0, 16);
+    bmc_sync(be);
+    return s;
+}
+
+bm_session_t* bm_create_session(bm_context_t* ctx, bm_model_t* model) { return bmx_create_session_batched(ctx, model, 1, 0); }
+
+void bm_destroy_session(bm_session_t* s) {
+    if (!s) return;
+    bmc_ctx_t* be = s->ctx->be;
+    bmc_sync(be);
+    if (s->layers) {
+        for (int l = 0; l < s->model->arch.n_layers; l++) {
+            bm_dec_layer_t* y = &s->layers[l];
+            bmc_free(be, y->ln1); bmc_free(be, y->ln2);
+            bm_mat_t* ms[4] = {&y->qkv, &y->o, &y->gu, &y->down};
+            for (int i = 0; i < 4; i++) { bmc_free(be, ms[i]->w); bmc_free(be, ms[i]->scales); }
+        }
+        free(s->layers);
+    }
+    bmc_free(be, s->lnf); if ((void*)s->embed != s->head) bmc_free(be, s->embed); bmc_free(be, s->head); bmc_free(be, s->cache); bmc_free(be, s->cs); bmc_free(be, s->x); bmc_free(be, s->xn);
+    bmc_free(be, s->qkv); bmc_free(be, s->att); bmc_free(be, s->x1); bmc_free(be, s->gu); bmc_free(be, s->act); bmc_free(be, s->logits);
+    bmc_free(be, s->d_pos); bmc_free(be, s->d_tokens); bmc_free(be, s->d_next); bmc_free(be, s->d_gen);
+    free(s->h_logits);
+    free(s);
+}
+
+void bm_reset_session(bm_session_t* s) {
+    if (!s) return;
+    s->pos = 0;
+    bmc_memset(s->ctx->be, s->d_pos, 0, 4);
+}
+
+#define TRYS(call) do { int rc__ = (call); if (rc__) { BM_LOG_ERROR("decode step: %s failed (%d)", #call, rc__); return rc__; } } while (0)
+
+/* one token for every sequence: tokens are in d_tokens, the position in d_pos; leaves logits, the greedy choice in d_next,
+ * and advances the device position */
+static int enqueue_step(bm_session_t* s) {
+    bmc_ctx_t* be = s->ctx->be;
+    const bm_arch_t* a = &s->model->arch;
+    const int L = a->n_layers, D = a->dim, H = a->hidden_dim, V = a->vocab_size, HD = s->model->head_size, NH = a->n_heads, NKV = a->n_kv_heads;
+    const int QD = NH * HD, KV = NKV * HD, NB = s->NB, MS = s->MS;
+    const float scale = 1.0f / sqrtf((float)HD), eps = 1e-5f;
+    TRYS(bmc_decode_embed(be, s->x, BMC_W_F32, s->embed, s->d_tokens, NB, D));
+    for (int l = 0; l < L; l++) {
+        const bm_dec_layer_t* y = &s->layers[l];
+        TRYS(bmc_decode_rmsnorm(be, s->xn, s->x, y->ln1, NB, D, eps));
+        TRYS(bmc_decode_gemv(be, s->qkv, QD + 2 * KV, s->xn, D, s->wtype, y->qkv.w, y->qkv.scales, NULL, 0, NB, D, QD + 2 * KV));
+        TRYS(bmc_decode_rope_kv(be, s->qkv, s->cache, s->cs, s->d_pos, l, NB, MS, NH, NKV, HD));
+        TRYS(bmc_decode_attention(be, s->att, s->qkv, s->cache, s->d_pos, l, NB, MS, NH, NKV, HD, scale));
+        TRYS(bmc_decode_gemv(be, s->x1, D, s->att, QD, s->wtype, y->o.w, y->o.scales, s->x, D, NB, QD, D));
+        TRYS(bmc_decode_rmsnorm(be, s->xn, s->x1, y->ln2, NB, D, eps));
+        TRYS(bmc_decode_gemv(be, s->gu, 2 * H, s->xn, D, s->wtype, y->gu.w, y->gu.scales, NULL, 0, NB, D, 2 * H));
+        TRYS(bmc_decode_swiglu(be, s->act, s->gu, NB, H));
+        TRYS(bmc_decode_gemv(be, s->x, D, s->act, H, s->wtype, y->down.w, y->down.scales, s->x1, D, NB, H, D));
+    }
+    TRYS(bmc_decode_rmsnorm(be, s->xn, s->x, s->lnf, NB, D, eps));
+    TRYS(bmc_decode_gemv(be, s->logits, V, s->xn, D, s->head_type, s->head, NULL, NULL, 0, NB, D, V));
+    TRYS(bmc_decode_argmax(be, s->d_next, s->logits, NB, V));
+    TRYS(bmc_decode_advance(be, s->d_pos));
+    return 0;
+}
+
+/* the first step runs eagerly (it also sizes every kernel attribute); it is then captured once and replayed */
+static int run_step(bm_session_t* s) {
+    bmc_ctx_t* be = s->ctx->be;
+    if (s->pos >= s->MS) {
+        BM_LOG_ERROR("decode step: position %d exceeds the KV cache (%d)", s->pos, s->MS);
+        return -1;
+    }
+    int rc;
+    if (s->graph_ready == 2) {
+        rc = bmc_graph_launch(be);
+    } else if (s->graph_ready == 1) {
+        rc = bmc_graph_begin(be);
+        if (!rc) rc = enqueue_step(s);
+        if (!rc) rc = bmc_graph_end(be);
+        if (!rc) { s->graph_ready = 2; rc = bmc_graph_launch(be); }
+        else { BM_LOG_ERROR("decode step: graph capture failed (%d), continuing without a graph", rc); s->graph_ready = -1; rc = enqueue_step(s); }
+    } else {
+        rc = enqueue_step(s);
+        if (s->graph_ready == 0) s->graph_ready = getenv("BM_NO_GRAPH") ? -1 : 1;
+    }
+    if (!rc) s->pos++;
+    return rc;
+}
+
+float* bm_step(bm_session_t* s, int token) {
+    if (!s || s->NB != 1) return NULL;
+    bmc_ctx_t* be = s->ctx->be;
+    if (token < 0 || token >= s->model->arch.vocab_size) return NULL;
+    if (bmc_upload(be, s->d_tokens, &token, sizeof(int)) != 0 || bmc_sync(be) != 0) return NULL; /* `token` is a stack variable */
+    if (run_step(s) != 0) return NULL;
+    if (bmc_download(be, s->h_logits, s->logits, (size_t)s->model->arch.vocab_size * sizeof(float)) != 0) return NULL;
+    return s->h_logits;
+}
+
+/* n tokens from the current position; returns the logits after the last one (bm_forward, src/baremetal/session.c:86-149) */
+float* bm_forward(bm_session_t* s, const int* tokens, int n_tokens) {
+    if (!s || s->NB != 1 || !tokens || n_tokens < 1) return NULL;
+    bmc_ctx_t* be = s->ctx->be;
+    for (int i = 0; i < n_tokens; i++) {
+        if (tokens[i] < 0 || tokens[i] >= s->model->arch.vocab_size) return NULL;
+        if (bmc_upload(be, s->d_tokens, &tokens[i], sizeof(int)) != 0) return NULL;
+        if (run_step(s) != 0) return NULL;
+    }
+    if (bmc_download(be, s->h_logits, s->logits, (size_t)s->model->arch.vocab_size * sizeof(float)) != 0) return NULL;
+    return s->h_logits;
+}
+
+void bm_profile_begin(bm_session_t* s) { (void)s; }
+void bm_profile_end(bm_session_t* s, double* attention_ms, double* mlp_ms, double* other_ms) {
+    (void)s;
+    if (attention_ms) *attention_ms = 0.0;
+    if (mlp_ms) *mlp_ms = 0.0;
+    if (other_ms) *other_ms = 0.0;
+}
+
+/* ---- batched greedy generation (include/baremetal_ext.h) ---------------------------------------------------------------- */
+/* Feeds prompt[b][0..n_prompt) to every sequence b, then generates n_new tokens greedily. out[b][0..n_new) receives the ids.
+ * The loop never returns to the host between tokens: the chosen ids are copied device-to-device into the next step's input. */
+int bmx_session_generate_greedy(bm_session_t* s, const int* prompt, int n_prompt, int n_new, int* out) {
+    if (!s || !prompt || n_prompt < 1 || n_new < 1 || !out) return -1;
+    bmc_ctx_t* be = s->ctx->be;
+    const int NB = s->NB;
+    if (s->pos + n_prompt + n_new - 1 > s->MS) return -2; /* n_prompt + n_new - 1 steps are taken */
+    if (s->gen_cap < n_new) {
+        bmc_free(be, s->d_gen);
+        s->d_gen = (int*)bmc_alloc(be, (size_t)n_new * NB * sizeof(int));
+        if (!s->d_gen) return -3;
+        s->gen_cap = n_new;
+    }
+    int* col = (int*)malloc((size_t)NB * n_prompt * sizeof(int));
+    for (int i = 0; i < n_prompt; i++)
+        for (int b = 0; b < NB; b++) col[(size_t)i * NB + b] = prompt[(size_t)b * n_prompt + i];
+    int* d_prompt = (int*)bmc_alloc(be, (size_t)NB * n_prompt * sizeof(int));
+    if (!d_prompt) { free(col); return -3; }
+    bmc_upload(be, d_prompt, col, (size_t)NB * n_prompt * sizeof(int));
+    bmc_sync(be);
+    free(col);
+    int rc = 0;
+    for (int i = 0; i < n_prompt && !rc; i++) {
+        bmc_copy(be, s->d_tokens, d_prompt + (size_t)i * NB, (size_t)NB * sizeof(int));
+        rc = run_step(s);
+    }
+    for (int i = 0; i < n_new && !rc; i++) {
+        bmc_copy(be, s->d_gen + (size_t)i * NB, s->d_next, (size_t)NB * sizeof(int));
+        if (i + 1 < n_new) {
+            bmc_copy(be, s->d_tokens, s->d_next, (size_t)NB * sizeof(int));
+            rc = run_step(s);
+        }
+    }
+    if (!rc) {
+        int* h = (int*)malloc((size_t)n_new * NB * sizeof(int));
+        rc = bmc_download(be, h, s->d_gen, (size_t)n_new * NB * sizeof(int));
+        for (int i = 0; i < n_new; i++)
+            for (int b = 0; b < NB; b++) out[(size_t)b * n_new + i] = h[(size_t)i * NB + b];
+        free(h);
+        if (!rc) rc = bmc_status(be);
+    }
+    bmc_free(be, d_prompt);
+    return rc;
+}
+/* logits of every sequence after the most recent step (NB x V floats, host pointer valid until the next call) */
+const float* bmx_session_logits(bm_session_t* s) {
+    if (!s) return NULL;
+    if (bmc_download(s->ctx->be, s->h_logits, s->logits, (size_t)s->NB * s->model->arch.vocab_size * sizeof(float)) != 0) return NULL;
+    return s->h_logits;
+}
+int bmx_session_position(bm_session_t* s) { return s ? s->pos : -1; }
+size_t bmx_session_weight_bytes(bm_session_t* s) {
+    if (!s) return 0;
+    size_t n = 0;
+    for (int l = 0; l < s->model->arch.n_layers; l++) {
+        const bm_mat_t* ms[4] = {&s->layers[l].qkv, &s->layers[l].o, &s->layers[l].gu, &s->layers[l].down};
+        for (int i = 0; i < 4; i++) {
+            const size_t e = (size_t)ms[i]->OC * ms[i]->C;
+            n += s->wtype == BMC_W_Q8 ? e + e / 32 * 4 : s->wtype == BMC_W_BF16 ? e * 2 : e * 4;
+        }
+    }
+    n += (size_t)s->model->arch.vocab_size * s->model->arch.dim * (s->head_type == BMC_W_BF16 ? 2 : 4);
+    return n;
+}

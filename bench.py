@@ -243,6 +243,66 @@ def run_attention(args):
     return 0
 
 
+def run_decode(args):
+    """Q8 inference: prefill 512 uniform-random tokens, then greedy-decode 256, at batch 1 and 64; one JSON line per batch.
+    Layer matrices are int8 blocks of 32 with one fp32 scale, the LM head is bf16, activations and the KV cache fp32.
+    The timed regions are whole calls of the session API (host prompt in, host token ids out)."""
+    import time
+    lib = bmapi.load_product()
+    a = bmapi.make_arch(args.model)
+    a.precision = bmapi.BM_PRECISION_BF16
+    w = bmapi.make_weights(a)
+    path = f"/tmp/bm_bench_decode_{os.getpid()}.bin"
+    bmapi.write_bin_checkpoint(path, a, w)
+    del w
+    peaks, src = measured_peaks()
+    n_prompt, n_new = 512, 256
+    MS = n_prompt + n_new
+    ctx = lib.bm_create(bmapi.BM_DEVICE_METAL)
+    model = lib.bm_create_model(ctx, C.byref(a))
+    lib.bm_load_weights(model, path.encode())
+    os.unlink(path)
+    assert lib.bmx_model_set_quant(model, 8) == 0
+    L, KV, V = a.n_layers, a.n_kv_heads * a.head_dim, a.vocab_size
+    for NB in (1, 64):
+        sess = lib.bmx_create_session_batched(ctx, model, NB, MS)
+        assert sess, "bmx_create_session_batched failed"
+        wbytes = lib.bmx_session_weight_bytes(sess)
+        prompts = np.random.default_rng(7).integers(0, V, size=(NB, n_prompt), dtype=np.int32)
+        first = np.zeros((NB, 1), np.int32)
+        out = np.zeros((NB, n_new), np.int32)
+        best = None
+        for it in range(max(args.warmup, 1) + max(args.steps, 1)):
+            lib.bm_reset_session(sess)
+            t0 = time.perf_counter()
+            assert lib.bmx_session_generate_greedy(sess, bmapi.as_int_ptr(prompts), n_prompt, 1, bmapi.as_int_ptr(first)) == 0
+            t1 = time.perf_counter()
+            # continues from position 512: feeds the first generated token, returns tokens 2..257; 256 decode steps
+            assert lib.bmx_session_generate_greedy(sess, bmapi.as_int_ptr(first), 1, n_new, bmapi.as_int_ptr(out)) == 0
+            t2 = time.perf_counter()
+            if it >= max(args.warmup, 1) and (best is None or t2 - t1 < best[1]):
+                best = (t1 - t0, t2 - t1)
+        lib.bm_destroy_session(sess)
+        t_pre, t_dec = best
+        # bytes one decode step must read: every weight once per pass over the batch + the KV cache up to the current position
+        kv_avg = L * 2 * (n_prompt + n_new / 2.0) * KV * 4 * NB
+        step_bytes = wbytes + kv_avg
+        gbs = step_bytes * n_new / t_dec / 1e9
+        print(json.dumps({"metric": "decode_tokens_per_sec", "value": NB * n_new / t_dec, "unit": "tokens/s", "n_gpus": 1,
+                          "steps": max(args.steps, 1), "warmup": max(args.warmup, 1), "ms_per_step": t_dec / n_new * 1e3,
+                          "higher_is_better": True, "dtype": "q8 weights / f32 activations", "data": "synthetic",
+                          "config": {"workload": f"{args.model} Q8 inference: prefill {n_prompt} + greedy decode {n_new}, batch {NB}",
+                                     "l2": "weights (>400 MB) exceed L2"},
+                          "prefill_tokens_per_sec": NB * n_prompt / t_pre, "prefill_ms": t_pre * 1e3, "decode_ms": t_dec * 1e3,
+                          "weight_bytes": wbytes,
+                          "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
+                                       "traffic": None, "peak_source": f"hbm_gbs of {src}",
+                                       "bytes_per_step": step_bytes}}), flush=True)
+    lib.bm_destroy_model(model)
+    lib.bm_destroy(ctx)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -253,13 +313,15 @@ def main():
     ap.add_argument("--batch", type=int, default=PER_GPU_BATCH)
     ap.add_argument("--seq-len", type=int, default=SEQ_LEN)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="train", choices=["train", "attention"],
-                    help="train (default, the contract line) or attention: isolated GQA flash attention fwd+bwd")
+    ap.add_argument("--workload", default="train", choices=["train", "attention", "decode"],
+                    help="train (default, the contract line); attention: isolated GQA flash attention fwd+bwd; decode: Q8 prefill + greedy decode")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
     if args.workload == "attention":
         return run_attention(args)
+    if args.workload == "decode":
+        return run_decode(args)
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -7,9 +7,10 @@
  * thread. Failures are reported as NULL / -1 / -1.0f plus a line on stderr.
  *
  * Scope of this build: the training path (bm_create .. bm_create_trainer, bm_train_step*, state
- * save/load, profiling) and the greedy sampler run on the GPU backend. Entry points of the
- * reference outside that path (tokenizer, inference session, adapters, weight export) are exported
- * so that the header is complete, and return the failure value of their signature.
+ * save/load, profiling), the inference session (bm_create_session, bm_forward, bm_step; fp32 / bf16 /
+ * Q8 weights) and the greedy sampler run on the GPU backend. Entry points of the reference outside
+ * those paths (tokenizer, adapters, weight export, the sampled-generation driver) are exported so
+ * that the header is complete, and return the failure value of their signature.
  */
 #ifndef BAREMETAL_H
 #define BAREMETAL_H
@@ -79,7 +80,7 @@ void bm_destroy_model(bm_model_t* model);
 void bm_compile(bm_model_t* model);
 void bm_autotune(bm_model_t* model, int warmup, int iterations);
 
-/* ------------------------------------------------------------------ inference (outside this build) */
+/* ------------------------------------------------------------------ inference */
 int bm_load_adapter(bm_model_t* model, const char* path);
 bm_session_t* bm_create_session(bm_context_t* ctx, bm_model_t* model);
 float* bm_forward(bm_session_t* sess, const int* tokens, int n_tokens);

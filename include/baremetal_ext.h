@@ -64,6 +64,21 @@ int    bmx_model_vocab_size(const bm_model_t* model);
 int    bmx_gemm_timing(bm_context_t* ctx, int enable);
 int    bmx_gemm_timing_collect(bm_context_t* ctx, double* out3);
 
+/* ---- inference ----
+ * Q8 selection: the reference sets bm_model_s::quant_bits from its CLI (tools/cli.c:886); here through a call. bits = 0 or 8. */
+int    bmx_model_set_quant(bm_model_t* model, int bits);
+/* The reference's Q8 block quantiser (bmt_quantize_q8, src/baremetal/quant.c:10-29,54-60) with the int8 values and the scales
+ * in two arrays: q[n], scales[n/32]. Returns the number of blocks, 0 when n is not a positive multiple of 32. */
+size_t bmx_quantize_q8(const float* src, int8_t* q, float* scales, size_t n);
+/* A session that advances n_sequences independent sequences in lock step (the reference API is single-sequence:
+ * bm_create_session == n_sequences 1). max_positions = KV cache length per sequence (0: the model's max_seq_len). */
+bm_session_t* bmx_create_session_batched(bm_context_t* ctx, bm_model_t* model, int n_sequences, int max_positions);
+/* prompt: int[n_sequences][n_prompt]; out: int[n_sequences][n_new] greedy continuations (lowest index among maxima). */
+int    bmx_session_generate_greedy(bm_session_t* s, const int* prompt, int n_prompt, int n_new, int* out);
+const float* bmx_session_logits(bm_session_t* s);
+int    bmx_session_position(bm_session_t* s);
+size_t bmx_session_weight_bytes(bm_session_t* s);
+
 /* Data parallel: every rank holds a full replica and calls bm_train_step with its own B sequences;
  * gradients are summed across ranks (bf16 buckets over NCCL, overlapped with backward) before AdamW and the
  * returned loss is the mean over all ranks. `nccl_id` is the 128-byte ncclUniqueId created on rank 0 with

@@ -147,6 +147,30 @@ int bmc_seq_prefix_accumulate(bmc_ctx_t* ctx, int dtype, void* d_x, float* d_car
 /* greedy sampler: lowest index among the maxima (bm_sample argmax branch src/baremetal/sampler.c:36-40) */
 int bmc_argmax(bmc_ctx_t* ctx, int* d_index, const float* d_logits, int V);
 
+/* ---- token-by-token inference (decode walk src/baremetal/scheduler.c:712-996; kernels matmul_forward_q8_vec forward.metal:575,
+ *      rmsnorm_forward_v2 :1019, rope_forward :1284, kv_store :1317, attention_forward :1362, swiglu_forward :1179), batched over
+ *      NB independent sequences that share one position counter. Activations and the KV cache are fp32.
+ *      Weight types: BMC_W_Q8 = int8 q[OC][C] + float scale[OC][C/32] (the values of the reference's 36-byte blocks,
+ *      src/baremetal/quant.h:19-22, stored as two arrays), BMC_W_BF16, BMC_W_F32.
+ *      d_pos is a DEVICE int holding the position of the token being processed (so a captured step can be replayed).
+ *      KV cache layout: float[L][2][NB][MS][KV]; rope table float[MS][HD/2][2]. ---- */
+enum { BMC_W_Q8 = 0, BMC_W_BF16 = 1, BMC_W_F32 = 2 };
+int bmc_decode_gemv(bmc_ctx_t* ctx, float* d_out, int ldo, const float* d_x, int ldx, int wtype, const void* d_w, const float* d_scales,
+                    const float* d_residual, int ldr, int NB, int C, int OC);
+int bmc_decode_rmsnorm(bmc_ctx_t* ctx, float* d_out, const float* d_x, const float* d_w, int NB, int C, float eps);
+int bmc_decode_rope_kv(bmc_ctx_t* ctx, float* d_qkv, float* d_cache, const float* d_cs_table, const int* d_pos, int layer, int NB, int MS,
+                       int NH, int NKV, int HD);
+int bmc_decode_attention(bmc_ctx_t* ctx, float* d_out, const float* d_qkv, const float* d_cache, const int* d_pos, int layer, int NB,
+                         int MS, int NH, int NKV, int HD, float scale);
+int bmc_decode_swiglu(bmc_ctx_t* ctx, float* d_out, const float* d_gate_up, int NB, int H);
+int bmc_decode_embed(bmc_ctx_t* ctx, float* d_out, int table_type, const void* d_table, const int* d_tokens, int NB, int D);
+int bmc_decode_argmax(bmc_ctx_t* ctx, int* d_out, const float* d_logits, int NB, int V);
+int bmc_decode_advance(bmc_ctx_t* ctx, int* d_pos);
+/* Record everything enqueued between begin and end into a CUDA graph and replay it with launch (one graph per context). */
+int bmc_graph_begin(bmc_ctx_t* ctx);
+int bmc_graph_end(bmc_ctx_t* ctx);
+int bmc_graph_launch(bmc_ctx_t* ctx);
+
 #ifdef __cplusplus
 }
 #endif

@@ -522,3 +522,182 @@ float orc_step(orc_t* o, const int* inputs, const int* targets, int B) {
     }
     return total / (float)B;
 }
+
+/* ======================= inference: prefill / decode with a KV cache, Q8 or plain weights =========================
+ * Restates the reference's decode walk (src/baremetal/scheduler.c:712-996 over the graph of src/baremetal/graph.c:109-240):
+ * fp32 activations, fp32 KV cache, layer matrices optionally Q8 (src/baremetal/quant.c:10-29), LM head never quantised
+ * (graph.c:228-239). Matmul with Q8 weights: val += x[i] * ((float)q[i] * scale) (matmul_forward_q8,
+ * src/kernels/forward.metal:625-648). */
+size_t orc_quantize_q8(const float* src, int8_t* q, float* scales, size_t n) {
+    if (n == 0 || (n % 32) != 0) return 0;
+    for (size_t b = 0; b < n / 32; b++) {
+        const float* p = src + b * 32;
+        float amax = 0.0f;
+        for (int i = 0; i < 32; i++) { const float a = fabsf(p[i]); if (a > amax) amax = a; }
+        const float scale = amax / 127.0f;
+        scales[b] = scale;
+        if (scale == 0.0f) { memset(q + b * 32, 0, 32); continue; }
+        const float inv = 1.0f / scale;
+        for (int i = 0; i < 32; i++) {
+            long v = lroundf(p[i] * inv);
+            if (v > 127) v = 127;
+            if (v < -128) v = -128;
+            q[b * 32 + i] = (int8_t)v;
+        }
+    }
+    return n / 32;
+}
+
+typedef struct { float* w; int8_t* q; float* sc; int OC, C; } orc_mat_t;
+typedef struct {
+    int D, H, L, NH, NKV, V, HD, MS, pos, quant;
+    float theta;
+    float *ln1, *ln2, *lnf, *head, *embed;   /* ln1/ln2: [L][D]; head: [V][D] (bf16-rounded in bf16 mode); embed: [V][D] as loaded */
+    orc_mat_t *q, *k, *v, *o, *gate, *up, *down;   /* [L] */
+    float* cache;                    /* [L][2][MS][KV] */
+    float* logits;
+} orc_dec_t;
+
+static void mat_init(orc_mat_t* m, const float* src, int OC, int C, int quant, int round_bf16) {
+    m->OC = OC; m->C = C; m->w = NULL; m->q = NULL; m->sc = NULL;
+    const size_t n = (size_t)OC * C;
+    if (quant == 8) {
+        /* from the loaded fp32 values (src/baremetal/scheduler.c:378-384; a bf16 source widens exactly) */
+        m->q = (int8_t*)malloc(n);
+        m->sc = (float*)malloc(n / 32 * sizeof(float));
+        orc_quantize_q8(src, m->q, m->sc, n);
+    } else {
+        m->w = (float*)malloc(n * sizeof(float));
+        for (size_t i = 0; i < n; i++) m->w[i] = round_bf16 ? bf16_round(src[i]) : src[i];
+    }
+}
+static void mat_free(orc_mat_t* m) { free(m->w); free(m->q); free(m->sc); }
+static void mat_vec(float* out, const orc_mat_t* m, const float* x) {
+#pragma omp parallel for schedule(static)
+    for (int oc = 0; oc < m->OC; oc++) {
+        float val = 0.0f;
+        if (m->q) {
+            const int nb = m->C / 32;
+            for (int b = 0; b < nb; b++) {
+                const float s = m->sc[(size_t)oc * nb + b];
+                const int8_t* qb = m->q + (size_t)oc * m->C + b * 32;
+                const float* xb = x + b * 32;
+                for (int i = 0; i < 32; i++) val += xb[i] * ((float)qb[i] * s);
+            }
+        } else {
+            const float* wr = m->w + (size_t)oc * m->C;
+            for (int i = 0; i < m->C; i++) val += x[i] * wr[i];
+        }
+        out[oc] = val;
+    }
+}
+
+orc_dec_t* orc_dec_create(int D, int H, int L, int NH, int NKV, int V, int HD, int MS, int quant, int lowp_bf16, float theta,
+                          const float* model_weights) {
+    orc_dec_t* o = (orc_dec_t*)calloc(1, sizeof *o);
+    o->D = D; o->H = H; o->L = L; o->NH = NH; o->NKV = NKV; o->V = V; o->HD = HD; o->MS = MS; o->quant = quant; o->theta = theta;
+    const size_t QD = (size_t)NH * HD, KV = (size_t)NKV * HD;
+    const float* src = model_weights;   /* model order: embed, ln1w[L], qw[L], kw[L], vw[L], ow[L], ln2w[L], gate[L], up[L], down[L], lnfw */
+    const float* embed = src; src += (size_t)V * D;
+    const float* ln1 = src; src += (size_t)L * D;
+    const float* qw = src; src += L * QD * D;
+    const float* kw = src; src += L * KV * D;
+    const float* vw = src; src += L * KV * D;
+    const float* ow = src; src += L * D * QD;
+    const float* ln2 = src; src += (size_t)L * D;
+    const float* gw = src; src += (size_t)L * H * D;
+    const float* uw = src; src += (size_t)L * H * D;
+    const float* dw = src; src += (size_t)L * D * H;
+    const float* lnf = src;
+    o->ln1 = (float*)malloc((size_t)L * D * 4); memcpy(o->ln1, ln1, (size_t)L * D * 4);
+    o->ln2 = (float*)malloc((size_t)L * D * 4); memcpy(o->ln2, ln2, (size_t)L * D * 4);
+    o->lnf = (float*)malloc((size_t)D * 4); memcpy(o->lnf, lnf, (size_t)D * 4);
+    o->head = (float*)malloc((size_t)V * D * 4);
+    o->embed = (float*)malloc((size_t)V * D * 4);
+    memcpy(o->embed, embed, (size_t)V * D * 4);   /* the host gathers rows of the loaded table (src/baremetal/session.c:114-123) */
+    for (size_t i = 0; i < (size_t)V * D; i++) o->head[i] = lowp_bf16 ? bf16_round(embed[i]) : embed[i];
+    orc_mat_t** arrs[7] = {&o->q, &o->k, &o->v, &o->o, &o->gate, &o->up, &o->down};
+    for (int i = 0; i < 7; i++) *arrs[i] = (orc_mat_t*)calloc(L, sizeof(orc_mat_t));
+    const int plain_bf16 = lowp_bf16;
+    for (int l = 0; l < L; l++) {
+        mat_init(&o->q[l], qw + l * QD * D, (int)QD, D, quant, plain_bf16);
+        mat_init(&o->k[l], kw + l * KV * D, (int)KV, D, quant, plain_bf16);
+        mat_init(&o->v[l], vw + l * KV * D, (int)KV, D, quant, plain_bf16);
+        mat_init(&o->o[l], ow + l * D * QD, D, (int)QD, quant, plain_bf16);
+        mat_init(&o->gate[l], gw + (size_t)l * H * D, H, D, quant, plain_bf16);
+        mat_init(&o->up[l], uw + (size_t)l * H * D, H, D, quant, plain_bf16);
+        mat_init(&o->down[l], dw + (size_t)l * D * H, D, H, quant, plain_bf16);
+    }
+    o->cache = (float*)calloc((size_t)L * 2 * MS * KV, sizeof(float));
+    o->logits = (float*)malloc((size_t)V * sizeof(float));
+    return o;
+}
+void orc_dec_destroy(orc_dec_t* o) {
+    if (!o) return;
+    orc_mat_t* arrs[7] = {o->q, o->k, o->v, o->o, o->gate, o->up, o->down};
+    for (int i = 0; i < 7; i++) { for (int l = 0; l < o->L; l++) mat_free(&arrs[i][l]); free(arrs[i]); }
+    free(o->ln1); free(o->ln2); free(o->lnf); free(o->head); free(o->embed); free(o->cache); free(o->logits);
+    free(o);
+}
+void orc_dec_reset(orc_dec_t* o) { o->pos = 0; }
+
+/* bm_step, src/baremetal/session.c:151-185 */
+float* orc_dec_step(orc_dec_t* o, int token) {
+    const int D = o->D, H = o->H, NH = o->NH, NKV = o->NKV, HD = o->HD, MS = o->MS, pos = o->pos;
+    const int QD = NH * HD, KV = NKV * HD, mul = NH / NKV, hd2 = HD / 2;
+    const float eps = 1e-5f, scale = 1.0f / sqrtf((float)HD);
+    float *x = (float*)malloc(D * 4), *xn = (float*)malloc(D * 4), *q = (float*)malloc(QD * 4), *k = (float*)malloc(KV * 4),
+          *v = (float*)malloc(KV * 4), *att = (float*)malloc(QD * 4), *t = (float*)malloc(D * 4), *g = (float*)malloc(H * 4),
+          *u = (float*)malloc(H * 4), *sc = (float*)malloc((size_t)(pos + 1) * 4);
+    memcpy(x, o->embed + (size_t)token * D, D * 4);
+    for (int l = 0; l < o->L; l++) {
+        rmsnorm_forward(xn, x, o->ln1 + (size_t)l * D, 1, D, eps);
+        mat_vec(q, &o->q[l], xn); mat_vec(k, &o->k[l], xn); mat_vec(v, &o->v[l], xn);
+        /* rope_forward at this position, src/kernels/forward.metal:1284-1314 */
+        for (int h = 0; h < NH + NKV; h++) {
+            float* p = h < NH ? q + h * HD : k + (h - NH) * HD;
+            for (int i = 0; i < hd2; i++) {
+                const float freq = 1.0f / powf(o->theta, (float)(2 * i) / (float)HD);
+                const float c = cosf((float)pos * freq), s = sinf((float)pos * freq);
+                const float x0 = p[i], x1 = p[i + hd2];
+                p[i] = x0 * c - x1 * s;
+                p[i + hd2] = x0 * s + x1 * c;
+            }
+        }
+        float* kc = o->cache + ((size_t)l * 2 + 0) * MS * KV;
+        float* vc = o->cache + ((size_t)l * 2 + 1) * MS * KV;
+        memcpy(kc + (size_t)pos * KV, k, KV * 4);   /* kv_store, forward.metal:1317 */
+        memcpy(vc + (size_t)pos * KV, v, KV * 4);
+        /* attention_forward, forward.metal:1362-1460: softmax over positions 0..pos */
+        for (int h = 0; h < NH; h++) {
+            const int kh = h / mul;
+            float mx = -INFINITY;
+            for (int tt = 0; tt <= pos; tt++) {
+                float s = 0.0f;
+                for (int i = 0; i < HD; i++) s += q[h * HD + i] * kc[(size_t)tt * KV + kh * HD + i];
+                sc[tt] = s * scale;
+                if (sc[tt] > mx) mx = sc[tt];
+            }
+            float sum = 0.0f;
+            for (int tt = 0; tt <= pos; tt++) { sc[tt] = expf(sc[tt] - mx); sum += sc[tt]; }
+            for (int d = 0; d < HD; d++) {
+                float acc = 0.0f;
+                for (int tt = 0; tt <= pos; tt++) acc += sc[tt] * vc[(size_t)tt * KV + kh * HD + d];
+                att[h * HD + d] = acc / sum;
+            }
+        }
+        mat_vec(t, &o->o[l], att);
+        for (int i = 0; i < D; i++) x[i] += t[i];
+        rmsnorm_forward(xn, x, o->ln2 + (size_t)l * D, 1, D, eps);
+        mat_vec(g, &o->gate[l], xn); mat_vec(u, &o->up[l], xn);
+        for (int i = 0; i < H; i++) g[i] = g[i] / (1.0f + expf(-g[i])) * u[i];
+        mat_vec(t, &o->down[l], g);
+        for (int i = 0; i < D; i++) x[i] += t[i];
+    }
+    rmsnorm_forward(xn, x, o->lnf, 1, D, eps);
+    orc_mat_t head = {o->head, NULL, NULL, o->V, D};
+    mat_vec(o->logits, &head, xn);
+    o->pos++;
+    free(x); free(xn); free(q); free(k); free(v); free(att); free(t); free(g); free(u); free(sc);
+    return o->logits;
+}

@@ -36,6 +36,12 @@ def load_port():
     lib.orc_read.argtypes = [vp, C.c_int, C.c_int, fp]
     lib.orc_xent.restype = C.c_float
     lib.orc_argmax.restype = C.c_int
+    lib.orc_quantize_q8.restype, lib.orc_quantize_q8.argtypes = C.c_size_t, [fp, vp, fp, C.c_size_t]
+    lib.orc_dec_create.restype = vp
+    lib.orc_dec_create.argtypes = [C.c_int] * 10 + [C.c_float, fp]
+    lib.orc_dec_destroy.argtypes = [vp]
+    lib.orc_dec_reset.argtypes = [vp]
+    lib.orc_dec_step.restype, lib.orc_dec_step.argtypes = fp, [vp, C.c_int]
     return lib
 
 
@@ -120,6 +126,83 @@ class LibTrainer:
 
     def close(self):
         self.lib.bm_destroy_trainer(self.tr)
+        self.lib.bm_destroy_model(self.model)
+        self.lib.bm_destroy(self.ctx)
+
+
+class PortDecoder:
+    """Decode with a KV cache in the plain-C oracle: one sequence, one token per step."""
+    kind = "port"
+
+    def __init__(self, a, w, precision, quant, max_positions):
+        self.lib = load_port()
+        flat = flat_model_weights(a, w)
+        self.V = a.vocab_size
+        self.h = self.lib.orc_dec_create(a.dim, a.hidden_dim, a.n_layers, a.n_heads, a.n_kv_heads, a.vocab_size, a.head_dim,
+                                         max_positions, quant, 1 if precision == bmapi.BM_PRECISION_BF16 else 0, a.rope_theta,
+                                         fptr(flat))
+
+    def step(self, token):
+        p = self.lib.orc_dec_step(self.h, int(token))
+        return np.ctypeslib.as_array(p, shape=(self.V,)).copy()
+
+    def forward(self, tokens):
+        for t in tokens:
+            out = self.step(t)
+        return out
+
+    def reset(self):
+        self.lib.orc_dec_reset(self.h)
+
+    def close(self):
+        self.lib.orc_dec_destroy(self.h)
+
+
+class LibSession:
+    """An inference session behind the public C API: the product (kind 'gpu') or the reference build (kind 'reference')."""
+
+    def __init__(self, lib, kind, a, w, precision, quant, tag="s"):
+        self.lib, self.kind = lib, kind
+        a = bmapi.make_arch({k: getattr(a, k) for k in ("dim", "hidden_dim", "n_layers", "n_heads", "n_kv_heads", "vocab_size")} |
+                            {"head_dim": a.head_dim})
+        a.precision = precision
+        self.V = a.vocab_size
+        path = f"/tmp/bm_{tag}_{os.getpid()}_{kind}.bin"
+        bmapi.write_bin_checkpoint(path, a, w)
+        self.ctx = lib.bm_create(bmapi.BM_DEVICE_METAL)
+        if not self.ctx:
+            raise RuntimeError("bm_create failed (no GPU for the product / no backend)")
+        self.model = lib.bm_create_model(self.ctx, C.byref(a))
+        lib.bm_load_weights(self.model, path.encode())
+        os.unlink(path)
+        if kind == "reference":
+            lib.bmref_set_precision(self.model, precision)
+            lib.bmref_set_quant(self.model, quant)
+        else:
+            assert lib.bmx_model_set_quant(self.model, quant) == 0
+        lib.bm_compile(self.model)
+        self.sess = lib.bm_create_session(self.ctx, self.model)
+        if not self.sess:
+            raise RuntimeError("bm_create_session failed")
+
+    def step(self, token):
+        p = self.lib.bm_step(self.sess, int(token))
+        if not p:
+            raise RuntimeError("bm_step failed")
+        return np.ctypeslib.as_array(p, shape=(self.V,)).copy()
+
+    def forward(self, tokens):
+        t = np.ascontiguousarray(tokens, np.int32)
+        p = self.lib.bm_forward(self.sess, bmapi.as_int_ptr(t), len(t))
+        if not p:
+            raise RuntimeError("bm_forward failed")
+        return np.ctypeslib.as_array(p, shape=(self.V,)).copy()
+
+    def reset(self):
+        self.lib.bm_reset_session(self.sess)
+
+    def close(self):
+        self.lib.bm_destroy_session(self.sess)
         self.lib.bm_destroy_model(self.model)
         self.lib.bm_destroy(self.ctx)
 

@@ -11,6 +11,7 @@
 #include "backend/backend.h"
 
 void bmref_set_precision(bm_model_t* m, int precision) { m->precision = (bm_precision_t)precision; }
+void bmref_set_quant(bm_model_t* m, int bits) { m->quant_bits = bits; }
 int bmref_n_states(bm_trainer_t* t) { return t->n_opt_states; }
 size_t bmref_state_size(bm_trainer_t* t, int i) { return t->opt_states[i].n_params; }
 float* bmref_grad(bm_trainer_t* t, int i) {

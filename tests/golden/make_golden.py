@@ -14,6 +14,10 @@ Part 2 — ref_train_step_*.npz: the reference's training step (its C11 host cod
 seeded random-init models and LCG tokens; losses, per-tensor gradient norms, sampled gradient / post-step weight
 values are stored. Cases: scaled-down family members in fp32 and bf16-weight mode, batches of more than one sequence,
 and the 135M-parameter single-step fp32 configuration (B=1, S=64, AdamW lr 3e-4, beta (0.9, 0.95), wd 0.1).
+
+Part 3 (`--only-decode` regenerates just this part) — ref_quantize_q8.npz: the reference's Q8 block quantiser on seeded
+inputs with its edge cases; ref_decode_*.npz: logits of the reference inference session after every prefix of a seeded
+prompt and a greedy continuation, fp32 / bf16 weights, plain and Q8.
 """
 import ctypes as C
 import os
@@ -34,6 +38,7 @@ GEN_SCRIPTS = ["gen_matmul_bwd", "gen_rmsnorm_bwd", "gen_rope_bwd", "gen_rope_se
                "gen_embed_bwd", "gen_adamw", "gen_attn_bwd", "gen_attn_real", "gen_sched_bwd", "gen_layer_bwd"]
 INT_FILES = {"xent_targets", "embed_tokens"}
 SAMPLE = 64  # sampled values per tensor
+DECODE_LAYER_SCALE = 8.0
 
 
 def torch_goldens(ref_dir):
@@ -101,19 +106,79 @@ def ref_train_case(ref, tag, arch_name, B, S, precision, steps, accum=1):
     print(f"ref_train_step_{tag}.npz: losses {losses}")
 
 
+def q8_inputs():
+    """Seeded quantiser inputs with the edge cases of the scheme: an all-zero block, a block whose extreme is negative,
+    exact .5 ties after scaling, a huge dynamic range, denormal-sized values."""
+    rng = np.random.default_rng(77)
+    x = rng.standard_normal(64 * 32).astype(np.float32) * 0.02
+    x[0:32] = 0.0
+    x[32:64] = np.linspace(-1.0, 0.5, 32, dtype=np.float32)
+    x[64:96] = (np.arange(32, dtype=np.float32) - 16.0) * 0.5 / 127.0 * 127.0   # scale 8/127 -> many x.5 quotients
+    x[96:128] = np.float32(1e-30) * rng.standard_normal(32).astype(np.float32)
+    x[128:160] = np.concatenate([[np.float32(1e4)], rng.standard_normal(31).astype(np.float32)])
+    return x
+
+
+def ref_q8_case(ref):
+    x = q8_inputs()
+    nb = x.size // 32
+    blocks = np.zeros(nb, dtype=np.dtype([("scale", "<f4"), ("q", "i1", (32,))]))   # q8_block_t, src/baremetal/quant.h:19-22
+    assert ref.bmt_quantize_q8(oc.fptr(x), blocks.ctypes.data, x.size) == nb
+    np.savez_compressed(os.path.join(OUT, "ref_quantize_q8.npz"), x=x, scale=blocks["scale"].copy(), q=blocks["q"].copy())
+    print(f"ref_quantize_q8.npz: {nb} blocks")
+
+
+def ref_decode_case(ref, tag, arch_name, precision, quant, n_prompt, n_new):
+    """Logits of the reference session after every prefix (2..n_prompt tokens) of a seeded prompt, then a greedy
+    continuation, each token from a fresh prefill of the whole prefix (the barrier-free path of the CPU build)."""
+    a = bmapi.make_arch(arch_name)
+    w = bmapi.make_weights(a, layer_scale=DECODE_LAYER_SCALE)
+    prompt = bmapi.lcg_tokens(n_prompt, a.vocab_size, seed=1234)
+    s = oc.LibSession(ref, "reference", a, w, precision, quant, tag=tag)
+    logits = []
+    for n in range(2, n_prompt + 1):
+        s.reset()
+        logits.append(s.forward(prompt[:n]))
+    seq = list(int(t) for t in prompt)
+    greedy, margin = [], []
+    for _ in range(n_new):
+        s.reset()
+        lg = s.forward(np.array(seq, np.int32))
+        top = np.argsort(lg)[-2:]
+        greedy.append(int(top[1]))
+        margin.append(float(lg[top[1]] - lg[top[0]]))
+        seq.append(int(top[1]))
+    s.close()
+    np.savez_compressed(os.path.join(OUT, f"ref_decode_{tag}.npz"), arch=np.array(arch_name), precision=precision, quant=quant, layer_scale=DECODE_LAYER_SCALE,
+                        prompt=np.asarray(prompt, np.int32), logits=np.array(logits, np.float32), greedy=np.array(greedy, np.int32),
+                        margin=np.array(margin, np.float32))
+    print(f"ref_decode_{tag}.npz: greedy {greedy[:8]} min margin {min(margin):.3g}")
+
+
 def main():
-    ref_dir = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("BM_REFERENCE", "/root/reference")
-    torch_goldens(ref_dir)
+    args = [a for a in sys.argv[1:] if not a.startswith("--")]
+    ref_dir = args[0] if args else os.environ.get("BM_REFERENCE", "/root/reference")
     ref = bmapi.load_reference()
     if ref is None:
         raise SystemExit("oracle/_ref/libbm_ref.so missing: run oracle/build_ref.sh first")
     F32, BF16 = bmapi.BM_PRECISION_FP32, bmapi.BM_PRECISION_BF16
+    decode_cases = (("gqa_f32", "gqa", F32, 0), ("gqa_f32_q8", "gqa", F32, 8), ("gqa_bf16", "gqa", BF16, 0),
+                    ("gqa_bf16_q8", "gqa", BF16, 8), ("tiny_f32_q8", "tiny", F32, 8))
+    if "--only-decode" in sys.argv:
+        ref_q8_case(ref)
+        for tag, arch, prec, quant in decode_cases:
+            ref_decode_case(ref, tag, arch, prec, quant, 12, 12)
+        return
+    torch_goldens(ref_dir)
     ref_train_case(ref, "tiny_f32_b1", "tiny", 1, 16, F32, 3)
     ref_train_case(ref, "tiny_f32_b3", "tiny", 3, 32, F32, 2)
     ref_train_case(ref, "tiny_bf16_b2", "tiny", 2, 32, BF16, 3)
     ref_train_case(ref, "gqa_f32_b2", "gqa", 2, 128, F32, 2)
     ref_train_case(ref, "gqa_bf16_b2", "gqa", 2, 128, BF16, 2)
     ref_train_case(ref, "small_f32_accum2", "small", 2, 64, F32, 2, accum=2)
+    ref_q8_case(ref)
+    for tag, arch, prec, quant in decode_cases:
+        ref_decode_case(ref, tag, arch, prec, quant, 12, 12)
     if "--skip-135m" not in sys.argv:
         ref_train_case(ref, "135m_f32_c1", "smollm2-135m", 1, 64, F32, 1)
 

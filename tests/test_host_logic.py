@@ -80,9 +80,8 @@ def test_no_gpu_means_no_context_not_a_fallback(product):
 
 def test_out_of_scope_entry_points_return_their_failure_values(product):
     lib = product
-    lib.bm_create_session.restype = C.c_void_p
     lib.bm_create_tokenizer.restype = C.c_void_p
-    assert not lib.bm_create_session(None, None)
+    assert not lib.bm_create_session(None, None)  # no context: no session
     assert not lib.bm_create_tokenizer(b"/nonexistent")
     assert lib.bm_load_adapter(None, b"x") == -1
     assert lib.bm_save_adapter(None, b"x") == -1

@@ -253,3 +253,76 @@ def test_quirk_flags_change_only_what_they_name():
     for i in range(t1.n_tensors()):
         assert np.array_equal(t1.read(bmapi.BMX_GRAD, i), t0.read(bmapi.BMX_GRAD, i))
     t1.close(); t0.close()
+
+
+# ---- inference: Q8 quantiser and decode with a KV cache ---------------------------------------------------------------
+DECODE_GOLDENS = sorted(glob.glob(os.path.join(GOLD_DIR, "ref_decode_*.npz")))
+
+
+def _quantize(fn, x):
+    q = np.zeros(x.size, np.int8)
+    sc = np.zeros(x.size // 32, np.float32)
+    assert fn(oc.fptr(x), q.ctypes.data, oc.fptr(sc), x.size) == x.size // 32
+    return q.reshape(-1, 32), sc
+
+
+def test_quantize_q8_port_is_bit_exact_with_the_reference(port):
+    """Reference quantiser output on seeded inputs with the scheme's edge cases (all-zero block, negative extreme,
+    .5 ties, tiny values, one huge outlier): int8 values and fp32 scales must be identical."""
+    g = np.load(os.path.join(GOLD_DIR, "ref_quantize_q8.npz"))
+    q, sc = _quantize(port.orc_quantize_q8, np.ascontiguousarray(g["x"]))
+    assert np.array_equal(q, g["q"]) and np.array_equal(sc.view(np.uint32), g["scale"].view(np.uint32))
+
+
+def test_quantize_q8_rejects_ragged_input(port):
+    x = np.ones(33, np.float32)
+    q = np.zeros(64, np.int8)
+    sc = np.zeros(2, np.float32)
+    assert port.orc_quantize_q8(oc.fptr(x), q.ctypes.data, oc.fptr(sc), 33) == 0   # src/baremetal/quant.c:55
+    assert port.orc_quantize_q8(oc.fptr(x), q.ctypes.data, oc.fptr(sc), 0) == 0
+
+
+def test_product_host_quantiser_is_bit_exact_with_the_reference():
+    """The product quantises on the host at session creation; same fixture, same bits."""
+    lib = bmapi.load_product()
+    g = np.load(os.path.join(GOLD_DIR, "ref_quantize_q8.npz"))
+    q, sc = _quantize(lib.bmx_quantize_q8, np.ascontiguousarray(g["x"]))
+    assert np.array_equal(q, g["q"]) and np.array_equal(sc.view(np.uint32), g["scale"].view(np.uint32))
+
+
+def test_live_reference_quantiser_matches_port_on_random_blocks(port):
+    ref = bmapi.load_reference()
+    if ref is None:
+        pytest.skip("reference build absent")
+    x = (np.random.default_rng(5).standard_normal(32 * 257) * 0.3).astype(np.float32)
+    blocks = np.zeros(x.size // 32, dtype=np.dtype([("scale", "<f4"), ("q", "i1", (32,))]))
+    assert ref.bmt_quantize_q8(oc.fptr(x), blocks.ctypes.data, x.size) == x.size // 32
+    q, sc = _quantize(port.orc_quantize_q8, x)
+    assert np.array_equal(q, blocks["q"]) and np.array_equal(sc, blocks["scale"])
+
+
+def decode_case(path):
+    g = np.load(path)
+    a = bmapi.make_arch(str(g["arch"]))
+    w = bmapi.make_weights(a, layer_scale=float(g["layer_scale"]))
+    return g, a, w
+
+
+@pytest.mark.parametrize("path", DECODE_GOLDENS, ids=[os.path.basename(p)[11:-4] for p in DECODE_GOLDENS])
+def test_decode_port_matches_reference_session(path):
+    """Token-by-token decode of the plain-C oracle against logits of the reference session after every prompt prefix, and
+    the reference's greedy continuation; fp32 and bf16 weights, plain and Q8."""
+    g, a, w = decode_case(path)
+    dec = oc.PortDecoder(a, w, int(g["precision"]), int(g["quant"]), 64)
+    prompt = g["prompt"]
+    for i, t in enumerate(prompt):
+        lg = dec.step(t)
+        if i >= 1:
+            ref = g["logits"][i - 1]
+            assert np.abs(lg - ref).max() <= 1e-5 * np.abs(ref).max(), (i, np.abs(lg - ref).max())
+    out = []
+    for _ in range(len(g["greedy"])):
+        out.append(int(np.argmax(lg)))
+        lg = dec.step(out[-1])
+    dec.close()
+    assert out == list(g["greedy"])
