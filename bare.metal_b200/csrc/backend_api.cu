@@ -475,7 +475,12 @@ int bmc_argmax(bmc_ctx_t* ctx, int* d_index, const float* d_logits, int V) {
 int bmc_decode_gemv(bmc_ctx_t* ctx, float* d_out, int ldo, const float* d_x, int ldx, int wtype, const void* d_w, const float* d_scales,
                     const float* d_residual, int ldr, int NB, int C, int OC) {
     BMC_CHECK_CTX(ctx);
-    return note(ctx, decode_gemv(d_out, ldo, d_x, ldx, wtype, d_w, d_scales, d_residual, ldr, NB, C, OC, ctx->stream));
+    return note(ctx, decode_gemv(d_out, ldo, d_x, ldx, wtype, d_w, d_scales, d_residual, ldr, 0, nullptr, 0.f, NB, C, OC, ctx->stream));
+}
+int bmc_decode_gemv_fused(bmc_ctx_t* ctx, float* d_out, int ldo, const float* d_x, int ldx, int wtype, const void* d_w, const float* d_scales,
+                          const float* d_residual, int ldr, int prologue, const float* d_norm_weight, float eps, int NB, int C, int OC) {
+    BMC_CHECK_CTX(ctx);
+    return note(ctx, decode_gemv(d_out, ldo, d_x, ldx, wtype, d_w, d_scales, d_residual, ldr, prologue, d_norm_weight, eps, NB, C, OC, ctx->stream));
 }
 int bmc_decode_rmsnorm(bmc_ctx_t* ctx, float* d_out, const float* d_x, const float* d_w, int NB, int C, float eps) {
     BMC_CHECK_CTX(ctx);
@@ -486,10 +491,41 @@ int bmc_decode_rope_kv(bmc_ctx_t* ctx, float* d_qkv, float* d_cache, const float
     BMC_CHECK_CTX(ctx);
     return note(ctx, decode_rope_kv(d_qkv, d_cache, d_cs_table, d_pos, layer, NB, MS, NH, NKV, HD, ctx->stream));
 }
-int bmc_decode_attention(bmc_ctx_t* ctx, float* d_out, const float* d_qkv, const float* d_cache, const int* d_pos, int layer, int NB,
-                         int MS, int NH, int NKV, int HD, float scale) {
+size_t bmc_decode_attention_scratch_bytes(int NB, int MS, int NH, int NKV, int HD) {
+    return decode_attention_scratch_bytes(NB, MS, NH, NKV, HD) + 16;
+}
+int bmc_decode_attention(bmc_ctx_t* ctx, float* d_out, const float* d_qkv, const float* d_cache, const int* d_pos, void* d_scratch, int layer,
+                         int NB, int MS, int NH, int NKV, int HD, float scale) {
     BMC_CHECK_CTX(ctx);
-    return note(ctx, decode_attention(d_out, d_qkv, d_cache, d_pos, layer, NB, MS, NH, NKV, HD, scale, ctx->stream));
+    return note(ctx, decode_attention(d_out, d_qkv, const_cast<float*>(d_cache), nullptr, d_pos, d_scratch, layer, NB, MS, NH, NKV, HD, scale,
+                                      ctx->stream));
+}
+int bmc_decode_attention_fused(bmc_ctx_t* ctx, float* d_out, const float* d_qkv, float* d_cache, const float* d_cs_table, const int* d_pos,
+                               void* d_scratch, int layer, int NB, int MS, int NH, int NKV, int HD, float scale) {
+    BMC_CHECK_CTX(ctx);
+    if (!d_cs_table) return note(ctx, -1);
+    return note(ctx, decode_attention(d_out, d_qkv, d_cache, d_cs_table, d_pos, d_scratch, layer, NB, MS, NH, NKV, HD, scale, ctx->stream));
+}
+int bmc_decode_prep(bmc_ctx_t* ctx, void* d_a, int parts, const float* d_x, int ldx, int mode, const float* d_norm_weight, float eps,
+                    float* d_init_out, int ldo, const float* d_init_src, int ldr, int n_out, int rows, int C) {
+    BMC_CHECK_CTX(ctx);
+    return note(ctx, decode_prep((bf16*)d_a, parts, d_x, ldx, mode, d_norm_weight, eps, d_init_out, ldo, d_init_src, ldr, n_out, rows, C, ctx->stream));
+}
+// out[rows, OC] (fp32, holds the running sum) += a[rows, parts*C] x w[OC, parts*C]^T on the tensor cores
+int bmc_decode_gemm(bmc_ctx_t* ctx, float* d_out, int ldo, const void* d_a, const void* d_w, int parts, int rows, int C, int OC) {
+    BMC_CHECK_CTX(ctx);
+    const int K = parts * C;
+    const int tiles_m = (rows + 127) / 128;
+    int tile_n = 0, splits = 1;
+    if (tiles_m * ((OC + 255) / 256) < ctx->num_sms) {  // few row tiles: narrow column tiles and a split reduction axis fill the GPU
+        tile_n = 64;
+        const int units = tiles_m * ((OC + 63) / 64);
+        splits = (2 * ctx->num_sms + units - 1) / units;
+        const int kb = (K + 63) / 64;
+        if (splits > kb / 2) splits = kb / 2 > 0 ? kb / 2 : 1;
+    }
+    GemmProblem g{rows, OC, K, (const bf16*)d_a, K, 0, (const bf16*)d_w, K, 0, d_out, ldo, GEMM_OUT_F32_ATOMIC, nullptr, 0, splits, tile_n};
+    return note(ctx, run_umma(ctx, g));
 }
 int bmc_decode_swiglu(bmc_ctx_t* ctx, float* d_out, const float* d_gate_up, int NB, int H) {
     BMC_CHECK_CTX(ctx);
@@ -501,7 +537,11 @@ int bmc_decode_embed(bmc_ctx_t* ctx, float* d_out, int table_type, const void* d
 }
 int bmc_decode_argmax(bmc_ctx_t* ctx, int* d_out, const float* d_logits, int NB, int V) {
     BMC_CHECK_CTX(ctx);
-    return note(ctx, decode_argmax(d_out, d_logits, NB, V, ctx->stream));
+    return note(ctx, decode_argmax(d_out, d_logits, NB, V, nullptr, ctx->stream));
+}
+int bmc_decode_argmax_advance(bmc_ctx_t* ctx, int* d_out, const float* d_logits, int NB, int V, int* d_pos) {
+    BMC_CHECK_CTX(ctx);
+    return note(ctx, decode_argmax(d_out, d_logits, NB, V, d_pos, ctx->stream));
 }
 int bmc_decode_advance(bmc_ctx_t* ctx, int* d_pos) {
     BMC_CHECK_CTX(ctx);

@@ -11,6 +11,8 @@
 // arrays — q[OC][C] and scale[OC][C/32] — so rows can be read with aligned 16-byte loads.
 #include "decode_kernels.cuh"
 
+#include <cstdlib>
+
 namespace bmb {
 
 namespace {
@@ -25,6 +27,12 @@ __device__ __forceinline__ float warp_sum_f(float v) {
     return v;
 }
 
+// Programmatic dependent launch: a kernel launched with the stream-serialisation attribute may start while its
+// predecessor is still running; pdl_wait() blocks until the predecessor has completed and its writes are visible.
+// Everything before pdl_wait() may only touch memory no kernel of the step writes (weights, earlier cache rows).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // four int8 -> (float)q * scale, exactly as the reference's dequantisation (forward.metal:610), without the
 // conversion unit: the byte, biased by 128, is placed in the mantissa of 2^23 and the bias subtracted again.
 __device__ __forceinline__ void dequant4(uint32_t pk, float s, float* w) {
@@ -38,46 +46,101 @@ __device__ __forceinline__ void dequant4(uint32_t pk, float s, float* w) {
 // WT: 0 = Q8 (q + scales), 1 = bf16, 2 = fp32. Elements one lane reads with one 16-byte load:
 template <int WT> struct Epl { static constexpr int v = WT == 0 ? 16 : (WT == 1 ? 8 : 4); };
 
+// raw 16-byte weight chunk of one lane (+ its block scale for Q8), loaded before the data it multiplies is known
+struct RawW { uint4 v; float s; };
 template <int WT>
-__device__ __forceinline__ void load_weights16(const void* w, const float* scales, size_t row, int C, int c, float* wv) {
+__device__ __forceinline__ RawW load_raw(const void* w, const float* scales, size_t row, int C, int c) {
+    RawW r;
+    r.s = 0.f;
     if (WT == 0) {
-        const uint4 pk = *reinterpret_cast<const uint4*>((const int8_t*)w + row * C + c);
-        const float s = scales[row * (C / 32) + (c >> 5)];
-        dequant4(pk.x, s, wv); dequant4(pk.y, s, wv + 4); dequant4(pk.z, s, wv + 8); dequant4(pk.w, s, wv + 12);
+        r.v = *reinterpret_cast<const uint4*>((const int8_t*)w + row * C + c);
+        r.s = scales[row * (C / 32) + (c >> 5)];
     } else if (WT == 1) {
-        const uint4 pk = *reinterpret_cast<const uint4*>((const bf16*)w + row * C + c);
-        wv[0] = __uint_as_float(pk.x << 16); wv[1] = __uint_as_float(pk.x & 0xffff0000u);
-        wv[2] = __uint_as_float(pk.y << 16); wv[3] = __uint_as_float(pk.y & 0xffff0000u);
-        wv[4] = __uint_as_float(pk.z << 16); wv[5] = __uint_as_float(pk.z & 0xffff0000u);
-        wv[6] = __uint_as_float(pk.w << 16); wv[7] = __uint_as_float(pk.w & 0xffff0000u);
+        r.v = *reinterpret_cast<const uint4*>((const bf16*)w + row * C + c);
     } else {
-        const float4 v = *reinterpret_cast<const float4*>((const float*)w + row * C + c);
-        wv[0] = v.x; wv[1] = v.y; wv[2] = v.z; wv[3] = v.w;
+        r.v = *reinterpret_cast<const uint4*>((const float*)w + row * C + c);
+    }
+    return r;
+}
+template <int WT>
+__device__ __forceinline__ void expand_raw(const RawW& r, float* wv) {
+    if (WT == 0) {
+        dequant4(r.v.x, r.s, wv); dequant4(r.v.y, r.s, wv + 4); dequant4(r.v.z, r.s, wv + 8); dequant4(r.v.w, r.s, wv + 12);
+    } else if (WT == 1) {
+        wv[0] = __uint_as_float(r.v.x << 16); wv[1] = __uint_as_float(r.v.x & 0xffff0000u);
+        wv[2] = __uint_as_float(r.v.y << 16); wv[3] = __uint_as_float(r.v.y & 0xffff0000u);
+        wv[4] = __uint_as_float(r.v.z << 16); wv[5] = __uint_as_float(r.v.z & 0xffff0000u);
+        wv[6] = __uint_as_float(r.v.w << 16); wv[7] = __uint_as_float(r.v.w & 0xffff0000u);
+    } else {
+        wv[0] = __uint_as_float(r.v.x); wv[1] = __uint_as_float(r.v.y); wv[2] = __uint_as_float(r.v.z); wv[3] = __uint_as_float(r.v.w);
     }
 }
 
-// Single sequence (or a few, one after the other): one warp per output row; the activation row lives in registers
-// (CH chunks of 32 lanes x EPL columns), so the loop touches only the weight stream. Two rows are in flight per warp.
-template <int WT, int CH>
+// Single sequence (or a few, blockIdx.y): one warp per output row; the activation row lives in registers (CH chunks of
+// 32 lanes x EPL columns), so the loop touches only the weight stream. Two rows are in flight per warp, and the first
+// two rows' weights are requested before the kernel waits for its predecessor.
+// PRO: 0 = x as given; 1 = RMSNorm(x) * lnw (rmsnorm_forward, src/kernels/forward.metal:988-1017) folded in;
+//      2 = x is [gate | up] of width 2C and the operand is silu(gate) * up (swiglu_forward, forward.metal:1179).
+template <int WT, int CH, int PRO>
 __global__ void __launch_bounds__(GEMV_WARPS * 32)
 decode_gemv1_kernel(float* __restrict__ out, int ldo, const float* __restrict__ x, int ldx, const void* __restrict__ w,
-                    const float* __restrict__ scales, const float* __restrict__ res, int ldr, int C, int OC) {
+                    const float* __restrict__ scales, const float* __restrict__ res, int ldr, const float* __restrict__ lnw, float eps,
+                    int C, int OC) {
     constexpr int EPL = Epl<WT>::v;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int b = blockIdx.y;
+    const int stride = gridDim.x * GEMV_WARPS;
+    int oc = blockIdx.x * GEMV_WARPS + warp;
+    RawW r0[CH], r1[CH];
+    if (oc < OC) {
+        const int o1 = oc + stride < OC ? oc + stride : oc;
+#pragma unroll
+        for (int j = 0; j < CH; ++j) {
+            const int c = (j * 32 + lane) * EPL;
+            if (c < C) { r0[j] = load_raw<WT>(w, scales, (size_t)oc, C, c); r1[j] = load_raw<WT>(w, scales, (size_t)o1, C, c); }
+        }
+    }
+    pdl_launch_dependents();
+    pdl_wait();
     float xr[CH * EPL];
+    float ss = 0.f;
 #pragma unroll
     for (int j = 0; j < CH; ++j) {
         const int c = (j * 32 + lane) * EPL;
 #pragma unroll
         for (int i = 0; i < EPL; i += 4) {
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (c < C) v = *reinterpret_cast<const float4*>(x + (size_t)b * ldx + c + i);
+            if (c < C) {
+                v = *reinterpret_cast<const float4*>(x + (size_t)b * ldx + c + i);
+                if (PRO == 1) {
+                    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+                } else if (PRO == 2) {
+                    const float4 u = *reinterpret_cast<const float4*>(x + (size_t)b * ldx + C + c + i);
+                    v.x = v.x / (1.0f + expf(-v.x)) * u.x; v.y = v.y / (1.0f + expf(-v.y)) * u.y;
+                    v.z = v.z / (1.0f + expf(-v.z)) * u.z; v.w = v.w / (1.0f + expf(-v.w)) * u.w;
+                }
+            }
             xr[j * EPL + i] = v.x; xr[j * EPL + i + 1] = v.y; xr[j * EPL + i + 2] = v.z; xr[j * EPL + i + 3] = v.w;
         }
     }
-    const int stride = gridDim.x * GEMV_WARPS;
-    for (int oc = blockIdx.x * GEMV_WARPS + warp; oc < OC; oc += 2 * stride) {
+    if (PRO == 1) {
+        ss = warp_sum_f(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)C + eps);
+#pragma unroll
+        for (int j = 0; j < CH; ++j) {
+            const int c = (j * 32 + lane) * EPL;
+            if (c < C) {
+#pragma unroll
+                for (int i = 0; i < EPL; i += 4) {
+                    const float4 g = *reinterpret_cast<const float4*>(lnw + c + i);
+                    xr[j * EPL + i] = xr[j * EPL + i] * inv * g.x; xr[j * EPL + i + 1] = xr[j * EPL + i + 1] * inv * g.y;
+                    xr[j * EPL + i + 2] = xr[j * EPL + i + 2] * inv * g.z; xr[j * EPL + i + 3] = xr[j * EPL + i + 3] * inv * g.w;
+                }
+            }
+        }
+    }
+    bool first = true;
+    for (; oc < OC; oc += 2 * stride) {
         const int oc1 = oc + stride;
         const bool two = oc1 < OC;
         float a0 = 0.f, a1 = 0.f;
@@ -85,9 +148,10 @@ decode_gemv1_kernel(float* __restrict__ out, int ldo, const float* __restrict__ 
         for (int j = 0; j < CH; ++j) {
             const int c = (j * 32 + lane) * EPL;
             if (c < C) {
+                if (!first) { r0[j] = load_raw<WT>(w, scales, (size_t)oc, C, c); r1[j] = load_raw<WT>(w, scales, (size_t)(two ? oc1 : oc), C, c); }
                 float w0[EPL], w1[EPL];
-                load_weights16<WT>(w, scales, (size_t)oc, C, c, w0);
-                load_weights16<WT>(w, scales, (size_t)(two ? oc1 : oc), C, c, w1);
+                expand_raw<WT>(r0[j], w0);
+                expand_raw<WT>(r1[j], w1);
 #pragma unroll
                 for (int i = 0; i < EPL; ++i) {
                     a0 = fmaf(xr[j * EPL + i], w0[i], a0);
@@ -95,6 +159,7 @@ decode_gemv1_kernel(float* __restrict__ out, int ldo, const float* __restrict__ 
                 }
             }
         }
+        first = false;
         a0 = warp_sum_f(a0);
         a1 = warp_sum_f(a1);
         if (lane == 0) {
@@ -115,6 +180,8 @@ decode_gemvb_kernel(float* __restrict__ out, int ldo, const float* __restrict__ 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int b0 = blockIdx.y * GEMV_TB;
     const int nb = min(GEMV_TB, NB - b0);
+    pdl_launch_dependents();
+    pdl_wait();
     for (int i = threadIdx.x * 4; i < GEMV_TB * C; i += blockDim.x * 4) {
         const int b = i / C, c = i - b * C;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -172,6 +239,7 @@ decode_gemvb_kernel(float* __restrict__ out, int ldo, const float* __restrict__ 
 
 __global__ void decode_rmsnorm_kernel(float* __restrict__ out, const float* __restrict__ x, const float* __restrict__ w, int C, float eps) {
     __shared__ float red[32];
+    pdl_wait();
     const float* xr = x + (size_t)blockIdx.x * C;
     float ss = 0.f;
     for (int i = threadIdx.x; i < C; i += blockDim.x) ss += xr[i] * xr[i];
@@ -193,6 +261,7 @@ __global__ void decode_rmsnorm_kernel(float* __restrict__ out, const float* __re
 __global__ void decode_rope_kv_kernel(float* __restrict__ qkv, float* __restrict__ cache, const float* __restrict__ cs,
                                       const int* __restrict__ pos_ptr, int layer, int NB, int MS, int NH, int NKV, int HD) {
     const int b = blockIdx.x;
+    pdl_wait();
     const int pos = *pos_ptr;
     const int QD = NH * HD, KV = NKV * HD, hd2 = HD / 2;
     float* row = qkv + (size_t)b * (QD + 2 * KV);
@@ -213,24 +282,50 @@ __global__ void decode_rope_kv_kernel(float* __restrict__ qkv, float* __restrict
     }
 }
 
-// One block (256 threads) per (KV head, sequence); it serves the MUL query heads that share the KV head, so every cache
-// row is read once. Phase 1: 8 lanes per position read one K row (coalesced) and form the MUL scaled scores.
-// Phase 2: softmax statistics per head over positions 0..pos. Phase 3: 16 (HD 64) position groups accumulate p * V with
-// float4 reads of the V rows; the groups are then summed through shared memory.
+// One block (256 threads) per (KV head, sequence, slice of positions); it serves the MUL query heads that share the KV
+// head, so every cache row is read once. Phase 1: 8 lanes per position read one K row (coalesced) and form the MUL scaled
+// scores. Phase 2: softmax statistics per head over the slice. Phase 3: position groups accumulate p * V with float4
+// reads of the V rows and are summed through shared memory. With more than one slice the (max, sum, accumulator)
+// triples go to scratch and the block that finishes last (an atomic ticket, no waiting) merges them.
+// ROPE: the kernel first rotates this token's q (in registers) and k by the position's angles (rope_forward,
+// forward.metal:1284) and stores k, v into the cache row of the position (kv_store, forward.metal:1317); qkv then holds the
+// un-rotated projections and stays untouched.
 constexpr int ATT_THREADS = 256;
-template <int HD, int MUL>
+template <int HD, int MUL, bool ROPE>
 __global__ void __launch_bounds__(ATT_THREADS)
-decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, const float* __restrict__ cache,
-                        const int* __restrict__ pos_ptr, int layer, int NB, int MS, int NH, int NKV, float scale) {
+decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, float* cache, const float* __restrict__ cs,
+                        const int* __restrict__ pos_ptr, float* part, unsigned* tickets, int layer, int NB, int MS, int NH, int NKV,
+                        int chunk, float scale) {
     extern __shared__ float sm[];
     constexpr int EPL = HD / 8;             // K floats per lane in phase 1
     constexpr int D4 = HD / 4;              // float4 per V row
     constexpr int GROUPS = ATT_THREADS / D4;
-    const int kh = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
+    constexpr int PW = HD + 2;              // partial record: acc[HD], max, sum
+    const int kh = blockIdx.x, b = blockIdx.y, z = blockIdx.z, nz = gridDim.z, tid = threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     const int n = *pos_ptr + 1;
+    const int t_begin = z * chunk, t_end = min(n, t_begin + chunk), len = max(t_end - t_begin, 0);
     const int QD = NH * HD, KV = NKV * HD;
-    float* sc = sm;                                    // [MUL][MS]
-    float* red = sm + (size_t)MUL * MS;                // [MUL][GROUPS][HD] (phase 3) / [MUL][8] (phase 2)
+    float* sc = sm;                                    // [MUL][chunk]
+    float* red = sm + (size_t)MUL * chunk;             // [MUL][GROUPS][HD] (phase 3) / [MUL][8] (phase 2)
+    __shared__ float s_stat[2 * MUL];
+    __shared__ unsigned s_ticket;
+    if (ROPE && n - 1 >= t_begin && n - 1 < t_begin + chunk) {  // block-uniform: the slice that owns the new position
+        constexpr int hd2 = HD / 2;
+        const float* krow = qkv + (size_t)b * (QD + 2 * KV) + QD + (size_t)kh * HD;
+        float* kdst = cache + (((size_t)layer * 2 + 0) * NB + b) * (size_t)MS * KV + (size_t)(n - 1) * KV + (size_t)kh * HD;
+        float* vdst = cache + (((size_t)layer * 2 + 1) * NB + b) * (size_t)MS * KV + (size_t)(n - 1) * KV + (size_t)kh * HD;
+        if (tid < hd2) {
+            const float c = cs[((size_t)(n - 1) * hd2 + tid) * 2], s = cs[((size_t)(n - 1) * hd2 + tid) * 2 + 1];
+            const float x0 = krow[tid], x1 = krow[tid + hd2];
+            kdst[tid] = x0 * c - x1 * s;
+            kdst[tid + hd2] = x0 * s + x1 * c;
+        } else if (tid >= 128 && tid < 128 + HD) {
+            vdst[tid - 128] = krow[KV + tid - 128];
+        }
+        __syncthreads();  // the rows just written are read back below by other threads of this block
+    }
     const float* kc = cache + (((size_t)layer * 2 + 0) * NB + b) * (size_t)MS * KV + (size_t)kh * HD;
     const float* vc = cache + (((size_t)layer * 2 + 1) * NB + b) * (size_t)MS * KV + (size_t)kh * HD;
     const float* qrow = qkv + (size_t)b * (QD + 2 * KV) + (size_t)kh * MUL * HD;
@@ -245,23 +340,39 @@ decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, 
             const float4 v = *reinterpret_cast<const float4*>(qrow + h * HD + sub * EPL + i);
             qr[h][i] = v.x; qr[h][i + 1] = v.y; qr[h][i + 2] = v.z; qr[h][i + 3] = v.w;
         }
+    if (ROPE) {
+        // lanes sub 0..3 hold the first half of the head, sub 4..7 the second: the rotation partner sits 4 lanes away
+        constexpr int hd2 = HD / 2;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+            const int p = (sub & 3) * EPL + i;
+            const float c = cs[((size_t)(n - 1) * hd2 + p) * 2], s = cs[((size_t)(n - 1) * hd2 + p) * 2 + 1];
+#pragma unroll
+            for (int h = 0; h < MUL; ++h) {
+                const float mine = qr[h][i];
+                const float other = __shfl_xor_sync(0xffffffffu, mine, 4);
+                qr[h][i] = sub < 4 ? mine * c - other * s : other * s + mine * c;
+            }
+        }
+    }
     float mx[MUL];
 #pragma unroll
     for (int h = 0; h < MUL; ++h) mx[h] = -INFINITY;
-    for (int t0 = 0; t0 < n; t0 += ATT_THREADS / 8) {
+    for (int t0 = 0; t0 < len; t0 += ATT_THREADS / 8) {
         const int t = t0 + slot;
         float s[MUL];
 #pragma unroll
         for (int h = 0; h < MUL; ++h) s[h] = 0.f;
-        if (t < n) {
-            const float* kt = kc + (size_t)t * KV + sub * EPL;
+        if (t < len) {
+            const float* kt = kc + (size_t)(t_begin + t) * KV + sub * EPL;
+            float4 kv[EPL / 4];
 #pragma unroll
-            for (int i = 0; i < EPL; i += 4) {
-                const float4 kv = *reinterpret_cast<const float4*>(kt + i);
+            for (int i = 0; i < EPL / 4; ++i) kv[i] = *reinterpret_cast<const float4*>(kt + i * 4);
+#pragma unroll
+            for (int i = 0; i < EPL / 4; ++i)
 #pragma unroll
                 for (int h = 0; h < MUL; ++h)
-                    s[h] = fmaf(qr[h][i], kv.x, fmaf(qr[h][i + 1], kv.y, fmaf(qr[h][i + 2], kv.z, fmaf(qr[h][i + 3], kv.w, s[h]))));
-            }
+                    s[h] = fmaf(qr[h][i * 4], kv[i].x, fmaf(qr[h][i * 4 + 1], kv[i].y, fmaf(qr[h][i * 4 + 2], kv[i].z, fmaf(qr[h][i * 4 + 3], kv[i].w, s[h]))));
         }
 #pragma unroll
         for (int h = 0; h < MUL; ++h) {
@@ -270,8 +381,8 @@ decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, 
             v += __shfl_xor_sync(0xffffffffu, v, 2);
             v += __shfl_xor_sync(0xffffffffu, v, 4);
             v *= scale;
-            if (t < n) {
-                if (sub == 0) sc[(size_t)h * MS + t] = v;
+            if (t < len) {
+                if (sub == 0) sc[(size_t)h * chunk + t] = v;
                 mx[h] = fmaxf(mx[h], v);
             }
         }
@@ -284,7 +395,6 @@ decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, 
         if ((tid & 31) == 0) red[h * 8 + (tid >> 5)] = mx[h];
     }
     __syncthreads();
-    float inv[MUL];
 #pragma unroll
     for (int h = 0; h < MUL; ++h) {
         float m = red[h * 8];
@@ -296,21 +406,20 @@ decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, 
 #pragma unroll
     for (int h = 0; h < MUL; ++h) {
         float sum = 0.f;
-        for (int t = tid; t < n; t += ATT_THREADS) {
-            const float e = expf(sc[(size_t)h * MS + t] - mx[h]);
-            sc[(size_t)h * MS + t] = e;
+        for (int t = tid; t < len; t += ATT_THREADS) {
+            const float e = expf(sc[(size_t)h * chunk + t] - mx[h]);
+            sc[(size_t)h * chunk + t] = e;
             sum += e;
         }
         sum = warp_sum_f(sum);
         if ((tid & 31) == 0) red[h * 8 + (tid >> 5)] = sum;
     }
     __syncthreads();
-#pragma unroll
-    for (int h = 0; h < MUL; ++h) {
+    if (tid < MUL) {
         float t = 0.f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) t += red[h * 8 + i];
-        inv[h] = 1.0f / t;
+        for (int i = 0; i < 8; ++i) t += red[tid * 8 + i];
+        s_stat[tid] = t;  // sum of exp over the slice
     }
     __syncthreads();
     // phase 3
@@ -318,13 +427,24 @@ decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, 
     float4 acc[MUL];
 #pragma unroll
     for (int h = 0; h < MUL; ++h) acc[h] = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int t = grp; t < n; t += GROUPS) {
-        const float4 v = *reinterpret_cast<const float4*>(vc + (size_t)t * KV + d4 * 4);
+    for (int t0 = grp; t0 < len; t0 += 4 * GROUPS) {
+        float4 v[4];
 #pragma unroll
-        for (int h = 0; h < MUL; ++h) {
-            const float p = sc[(size_t)h * MS + t];
-            acc[h].x = fmaf(p, v.x, acc[h].x); acc[h].y = fmaf(p, v.y, acc[h].y);
-            acc[h].z = fmaf(p, v.z, acc[h].z); acc[h].w = fmaf(p, v.w, acc[h].w);
+        for (int u = 0; u < 4; ++u) {
+            const int t = t0 + u * GROUPS;
+            v[u] = t < len ? *reinterpret_cast<const float4*>(vc + (size_t)(t_begin + t) * KV + d4 * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int t = t0 + u * GROUPS;
+            if (t < len) {
+#pragma unroll
+                for (int h = 0; h < MUL; ++h) {
+                    const float p = sc[(size_t)h * chunk + t];
+                    acc[h].x = fmaf(p, v[u].x, acc[h].x); acc[h].y = fmaf(p, v[u].y, acc[h].y);
+                    acc[h].z = fmaf(p, v[u].z, acc[h].z); acc[h].w = fmaf(p, v[u].w, acc[h].w);
+                }
+            }
         }
     }
 #pragma unroll
@@ -335,14 +455,88 @@ decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, 
         float t = 0.f;
 #pragma unroll
         for (int g = 0; g < GROUPS; ++g) t += red[((size_t)h * GROUPS + g) * HD + d];
-        float iv = inv[0];
+        if (nz == 1) {
+            out[(size_t)b * QD + (size_t)(kh * MUL + h) * HD + d] = t / s_stat[h];
+        } else {
+            float mh = mx[0];
 #pragma unroll
-        for (int hh = 1; hh < MUL; ++hh) iv = (h == hh) ? inv[hh] : iv;
-        out[(size_t)b * QD + (size_t)(kh * MUL + h) * HD + d] = t * iv;
+            for (int hh = 1; hh < MUL; ++hh) mh = (h == hh) ? mx[hh] : mh;
+            float* rec = part + ((((size_t)b * NKV + kh) * MUL + h) * nz + z) * PW;
+            rec[d] = t;
+            if (d == 0) { rec[HD] = mh; rec[HD + 1] = s_stat[h]; }
+        }
+    }
+    if (nz == 1) return;
+    // merge: the block that draws the last ticket of this (sequence, KV head) combines all slices
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned tk = atomicAdd(&tickets[(size_t)b * NKV + kh], 1u);
+        s_ticket = tk;
+        if (tk == (unsigned)nz - 1) tickets[(size_t)b * NKV + kh] = 0;  // ready for the next launch
+    }
+    __syncthreads();
+    if (s_ticket != (unsigned)nz - 1) return;
+    __threadfence();
+    for (int i = tid; i < MUL * HD; i += ATT_THREADS) {
+        const int h = i / HD, d = i - h * HD;
+        const float* rec = part + ((((size_t)b * NKV + kh) * MUL + h) * nz) * PW;
+        float M = -INFINITY;
+        for (int zz = 0; zz < nz; ++zz) M = fmaxf(M, __ldcg(rec + (size_t)zz * PW + HD));
+        float Lsum = 0.f, a = 0.f;
+        for (int zz = 0; zz < nz; ++zz) {
+            const float mz = __ldcg(rec + (size_t)zz * PW + HD);
+            const float wgt = mz == -INFINITY ? 0.f : expf(mz - M);
+            Lsum = fmaf(__ldcg(rec + (size_t)zz * PW + HD + 1), wgt, Lsum);
+            a = fmaf(__ldcg(rec + (size_t)zz * PW + d), wgt, a);
+        }
+        out[(size_t)b * QD + (size_t)(kh * MUL + h) * HD + d] = a / Lsum;
     }
 }
 
+// Operand preparation for the tensor-core path: one block per row. The fp32 operand row (optionally RMSNorm(x) * lnw, or
+// silu(gate) * up of a [gate | up] row) is split into bf16 hi = rn(v) and lo = rn(v - hi) and written as [hi | lo] (parts 2)
+// or [hi | lo | hi] (parts 3), to be multiplied with weights laid out as [w | w] or [w_hi | w_hi | w_lo]: one bf16 GEMM over the
+// concatenated reduction axis then equals the fp32 product to about 2^-17 relative. The same launch initialises the fp32
+// output row the GEMM accumulates into (with the residual, or zero).
+template <int MODE>
+__global__ void __launch_bounds__(256)
+decode_prep_kernel(bf16* __restrict__ a, int parts, const float* __restrict__ x, int ldx, const float* __restrict__ lnw, float eps,
+                   float* __restrict__ init_out, int ldo, const float* __restrict__ init_src, int ldr, int n_out, int C) {
+    __shared__ float red[8];
+    const size_t row = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
+    const float* xr = x + row * ldx;
+    float inv = 1.f;
+    if (MODE == 1) {
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < C; i += 256) ss += xr[i] * xr[i];
+        ss = warp_sum_f(ss);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+        __syncthreads();
+        float t = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) t += red[i];
+        inv = 1.0f / sqrtf(t / (float)C + eps);
+    }
+    bf16* ar = a + row * (size_t)parts * C;
+    for (int c = threadIdx.x; c < C; c += 256) {
+        float v = xr[c];
+        if (MODE == 1) v = v * inv * lnw[c];
+        if (MODE == 2) v = v / (1.0f + expf(-v)) * xr[C + c];
+        const bf16 hi = __float2bfloat16_rn(v);
+        const bf16 lo = __float2bfloat16_rn(v - __bfloat162float(hi));
+        ar[c] = hi;
+        ar[C + c] = lo;
+        if (parts == 3) ar[2 * C + c] = hi;
+    }
+    if (init_out)
+        for (int j = threadIdx.x; j < n_out; j += 256) init_out[row * ldo + j] = init_src ? init_src[row * ldr + j] : 0.f;
+}
+
 __global__ void decode_swiglu_kernel(float* __restrict__ out, const float* __restrict__ gu, int H, int NB) {
+    pdl_wait();
     const long i = blockIdx.x * (long)blockDim.x + threadIdx.x;
     if (i >= (long)NB * H) return;
     const int b = (int)(i / H), c = (int)(i - (long)b * H);
@@ -352,15 +546,18 @@ __global__ void decode_swiglu_kernel(float* __restrict__ out, const float* __res
 
 template <typename TT>
 __global__ void decode_embed_kernel(float* __restrict__ out, const TT* __restrict__ table, const int* __restrict__ tokens, int D, int NB) {
+    pdl_wait();
     const long i = blockIdx.x * (long)blockDim.x + threadIdx.x;
     if (i >= (long)NB * D) return;
     const int b = (int)(i / D), c = (int)(i - (long)b * D);
     out[i] = to_f32(table[(size_t)tokens[b] * D + c]);
 }
 
-__global__ void decode_argmax_kernel(int* __restrict__ out, const float* __restrict__ logits, int V) {
+// pos (may be null): the step's position counter, advanced by one once every row is done with it
+__global__ void decode_argmax_kernel(int* __restrict__ out, const float* __restrict__ logits, int V, int* pos) {
     __shared__ float sv[32];
     __shared__ int si[32];
+    pdl_wait();
     const float* lr = logits + (size_t)blockIdx.x * V;
     float best = -INFINITY;
     int bi = 0x7fffffff;
@@ -385,33 +582,72 @@ __global__ void decode_argmax_kernel(int* __restrict__ out, const float* __restr
             const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
             if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
         }
-        if (threadIdx.x == 0) out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
+        if (threadIdx.x == 0) {
+            out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
+            if (pos && blockIdx.x == 0) *pos += 1;  // no block of this kernel reads the counter
+        }
     }
 }
 
-__global__ void decode_advance_kernel(int* pos) { *pos += 1; }
+__global__ void decode_advance_kernel(int* pos) {
+    pdl_wait();
+    *pos += 1;
+}
 
 }  // namespace
 
-template <int WT, int CH>
-static void launch_gemv1(float* out, int ldo, const float* x, int ldx, const void* w, const float* scales, const float* res, int ldr,
-                         int NB, int C, int OC, cudaStream_t st) {
+// Launch with the programmatic-stream-serialisation attribute (every kernel of this file waits with pdl_wait()).
+static bool pdl_enabled() {
+    static int v = -1;
+    if (v < 0) v = getenv("BM_NO_PDL") ? 0 : 1;
+    return v == 1;
+}
+template <typename... KArgs, typename... Args>
+static int launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...) == cudaSuccess ? 0 : -9;
+}
+
+template <int WT, int CH, int PRO>
+static int launch_gemv1(float* out, int ldo, const float* x, int ldx, const void* w, const float* scales, const float* res, int ldr,
+                        const float* lnw, float eps, int NB, int C, int OC, cudaStream_t st) {
     int gx = (OC + GEMV_WARPS - 1) / GEMV_WARPS;
     if (gx > 148 * 4) gx = 148 * 4;
-    decode_gemv1_kernel<WT, CH><<<dim3(gx, NB), GEMV_WARPS * 32, 0, st>>>(out, ldo, x, ldx, w, scales, res, ldr, C, OC);
+    return launch_k(decode_gemv1_kernel<WT, CH, PRO>, dim3(gx, NB), dim3(GEMV_WARPS * 32), 0, st, out, ldo, x, ldx, w, scales, res, ldr, lnw,
+                    eps, C, OC);
+}
+template <int WT, int PRO>
+static int gemv1_dispatch(float* out, int ldo, const float* x, int ldx, const void* w, const float* scales, const float* res, int ldr,
+                          const float* lnw, float eps, int NB, int C, int OC, cudaStream_t st) {
+    constexpr int EPL = Epl<WT>::v;
+    const int regs = (C + 32 * EPL - 1) / (32 * EPL) * EPL;  // activation registers per lane
+#define BM_GEMV1(r) return launch_gemv1<WT, r / EPL, PRO>(out, ldo, x, ldx, w, scales, res, ldr, lnw, eps, NB, C, OC, st)
+    if (regs <= 32) BM_GEMV1(32);
+    if (regs <= 48) BM_GEMV1(48);
+    if (regs <= 80) BM_GEMV1(80);
+    if (regs <= 96) BM_GEMV1(96);
+#undef BM_GEMV1
+    return -4;
 }
 template <int WT>
 static int gemv_dispatch(float* out, int ldo, const float* x, int ldx, const void* w, const float* scales, const float* res, int ldr,
-                         int NB, int C, int OC, cudaStream_t st) {
+                         int prologue, const float* lnw, float eps, int NB, int C, int OC, cudaStream_t st) {
     constexpr int EPL = Epl<WT>::v;
-    const int chunks = (C + 32 * EPL - 1) / (32 * EPL);
-    const int max_regs_chunks = 96 / EPL;  // at most 96 activation registers per lane
-    if (NB < 4 && chunks <= max_regs_chunks) {
-        if (chunks * EPL <= 32) launch_gemv1<WT, 32 / EPL>(out, ldo, x, ldx, w, scales, res, ldr, NB, C, OC, st);
-        else if (chunks * EPL <= 48) launch_gemv1<WT, 48 / EPL>(out, ldo, x, ldx, w, scales, res, ldr, NB, C, OC, st);
-        else if (chunks * EPL <= 80) launch_gemv1<WT, 80 / EPL>(out, ldo, x, ldx, w, scales, res, ldr, NB, C, OC, st);
-        else launch_gemv1<WT, 96 / EPL>(out, ldo, x, ldx, w, scales, res, ldr, NB, C, OC, st);
-        return 0;
+    const bool fits = (C + 32 * EPL - 1) / (32 * EPL) * EPL <= 96;
+    if (prologue != 0 || (NB < 4 && fits)) {
+        if (!fits) return -4;
+        if (prologue == 1) return gemv1_dispatch<WT, 1>(out, ldo, x, ldx, w, scales, res, ldr, lnw, eps, NB, C, OC, st);
+        if (prologue == 2) return gemv1_dispatch<WT, 2>(out, ldo, x, ldx, w, scales, res, ldr, lnw, eps, NB, C, OC, st);
+        return gemv1_dispatch<WT, 0>(out, ldo, x, ldx, w, scales, res, ldr, lnw, eps, NB, C, OC, st);
     }
     const size_t smem = (size_t)GEMV_TB * C * sizeof(float);
     if (smem > 200 * 1024) return -2;
@@ -423,69 +659,98 @@ static int gemv_dispatch(float* out, int ldo, const float* x, int ldx, const voi
     const int rows_per_block = GEMV_WARPS * GEMV_ROWS;
     int gx = (OC + rows_per_block - 1) / rows_per_block;
     if (gx > 148 * 4) gx = 148 * 4;
-    decode_gemvb_kernel<WT><<<dim3(gx, (NB + GEMV_TB - 1) / GEMV_TB), GEMV_WARPS * 32, smem, st>>>(out, ldo, x, ldx, w, scales, res, ldr, NB, C, OC);
-    return 0;
+    return launch_k(decode_gemvb_kernel<WT>, dim3(gx, (NB + GEMV_TB - 1) / GEMV_TB), dim3(GEMV_WARPS * 32), smem, st, out, ldo, x, ldx, w, scales,
+                    res, ldr, NB, C, OC);
 }
 
-// x rows must be 16-byte aligned (ldx % 4 == 0); C % 32 == 0.
+// x rows must be 16-byte aligned (ldx % 4 == 0); C % 32 == 0. prologue: 0 = none, 1 = RMSNorm(x) * lnw, 2 = x is [gate | up] and
+// the operand is silu(gate) * up (both only with the register-resident kernel: C <= 96 * 32 columns).
 int decode_gemv(float* out, int ldo, const float* x, int ldx, int wtype, const void* w, const float* scales, const float* res, int ldr,
-                int NB, int C, int OC, cudaStream_t st) {
-    if (C % 32 || NB <= 0 || (ldx & 3)) return -1;
-    if (wtype == 0) return gemv_dispatch<0>(out, ldo, x, ldx, w, scales, res, ldr, NB, C, OC, st);
-    if (wtype == 1) return gemv_dispatch<1>(out, ldo, x, ldx, w, scales, res, ldr, NB, C, OC, st);
-    return gemv_dispatch<2>(out, ldo, x, ldx, w, scales, res, ldr, NB, C, OC, st);
+                int prologue, const float* lnw, float eps, int NB, int C, int OC, cudaStream_t st) {
+    if (C % 32 || NB <= 0 || (ldx & 3) || prologue < 0 || prologue > 2 || (prologue == 1 && !lnw)) return -1;
+    if (wtype == 0) return gemv_dispatch<0>(out, ldo, x, ldx, w, scales, res, ldr, prologue, lnw, eps, NB, C, OC, st);
+    if (wtype == 1) return gemv_dispatch<1>(out, ldo, x, ldx, w, scales, res, ldr, prologue, lnw, eps, NB, C, OC, st);
+    return gemv_dispatch<2>(out, ldo, x, ldx, w, scales, res, ldr, prologue, lnw, eps, NB, C, OC, st);
 }
 int decode_rmsnorm(float* out, const float* x, const float* w, int NB, int C, float eps, cudaStream_t st) {
-    decode_rmsnorm_kernel<<<NB, 256, 0, st>>>(out, x, w, C, eps);
-    return 0;
+    return launch_k(decode_rmsnorm_kernel, dim3(NB), dim3(256), 0, st, out, x, w, C, eps);
 }
 int decode_rope_kv(float* qkv, float* cache, const float* cs, const int* pos, int layer, int NB, int MS, int NH, int NKV, int HD,
                    cudaStream_t st) {
-    decode_rope_kv_kernel<<<NB, 256, 0, st>>>(qkv, cache, cs, pos, layer, NB, MS, NH, NKV, HD);
-    return 0;
+    return launch_k(decode_rope_kv_kernel, dim3(NB), dim3(256), 0, st, qkv, cache, cs, pos, layer, NB, MS, NH, NKV, HD);
 }
-template <int HD, int MUL>
-static int launch_attention(float* out, const float* qkv, const float* cache, const int* pos, int layer, int NB, int MS, int NH, int NKV,
-                            float scale, cudaStream_t st) {
-    const size_t smem = ((size_t)MUL * MS + (size_t)MUL * (ATT_THREADS / (HD / 4)) * HD) * sizeof(float);
+// Number of position slices for a cache of MS rows: enough blocks to fill the GPU about four times over.
+static void attention_split(int NB, int NKV, int MS, int* chunk, int* splits) {
+    int want = (592 + NKV * NB - 1) / (NKV * NB);
+    if (want < 1) want = 1;
+    if (want > 16) want = 16;
+    int c = ((MS + want - 1) / want + 31) / 32 * 32;
+    if (c < 32) c = 32;
+    *chunk = c;
+    *splits = (MS + c - 1) / c;
+}
+size_t decode_attention_scratch_bytes(int NB, int MS, int NH, int NKV, int HD) {
+    int chunk, splits;
+    attention_split(NB, NKV, MS, &chunk, &splits);
+    return (size_t)NB * NH * splits * (HD + 2) * sizeof(float) + (size_t)NB * NKV * sizeof(unsigned);
+}
+template <int HD, int MUL, bool ROPE>
+static int launch_attention(float* out, const float* qkv, float* cache, const float* cs, const int* pos, void* scratch, int layer, int NB,
+                            int MS, int NH, int NKV, float scale, cudaStream_t st) {
+    int chunk, splits;
+    attention_split(NB, NKV, MS, &chunk, &splits);
+    if (splits > 1 && !scratch) { chunk = (MS + 31) / 32 * 32; splits = 1; }
+    const size_t smem = ((size_t)MUL * chunk + (size_t)MUL * (ATT_THREADS / (HD / 4)) * HD) * sizeof(float);
     static size_t attr_smem = 48 * 1024;
     if (smem > attr_smem) {
         if (smem > 220 * 1024) return -2;
-        cudaFuncSetAttribute(decode_attention_kernel<HD, MUL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(decode_attention_kernel<HD, MUL, ROPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         attr_smem = smem;
     }
-    decode_attention_kernel<HD, MUL><<<dim3(NKV, NB), ATT_THREADS, smem, st>>>(out, qkv, cache, pos, layer, NB, MS, NH, NKV, scale);
-    return 0;
+    // scratch: tickets first (zeroed once by the owner; every launch leaves them zero), then the partial records
+    unsigned* tickets = (unsigned*)scratch;
+    float* part = scratch ? (float*)((char*)scratch + (((size_t)NB * NKV * sizeof(unsigned) + 15) / 16) * 16) : nullptr;
+    return launch_k(decode_attention_kernel<HD, MUL, ROPE>, dim3(NKV, NB, splits), dim3(ATT_THREADS), smem, st, out, qkv, cache, cs, pos, part,
+                    tickets, layer, NB, MS, NH, NKV, chunk, scale);
 }
-// head_dim 64 or 128; 1, 2, 3, 4 or 8 query heads per KV head
-int decode_attention(float* out, const float* qkv, const float* cache, const int* pos, int layer, int NB, int MS, int NH, int NKV, int HD,
-                     float scale, cudaStream_t st) {
+// head_dim 64 or 128; 1, 2, 3, 4 or 8 query heads per KV head. cs != null: RoPE and the cache store happen inside.
+// scratch (may be null: one slice per block): decode_attention_scratch_bytes() + 16 bytes, zero-initialised once.
+int decode_attention(float* out, const float* qkv, float* cache, const float* cs, const int* pos, void* scratch, int layer, int NB, int MS,
+                     int NH, int NKV, int HD, float scale, cudaStream_t st) {
     if (NKV <= 0 || NH % NKV) return -1;
     const int mul = NH / NKV;
-#define BM_ATT_CASE(hd, m) if (HD == hd && mul == m) return launch_attention<hd, m>(out, qkv, cache, pos, layer, NB, MS, NH, NKV, scale, st);
+#define BM_ATT_CASE(hd, m)                                                                                                            \
+    if (HD == hd && mul == m)                                                                                                         \
+        return cs ? launch_attention<hd, m, true>(out, qkv, cache, cs, pos, scratch, layer, NB, MS, NH, NKV, scale, st)               \
+                  : launch_attention<hd, m, false>(out, qkv, cache, cs, pos, scratch, layer, NB, MS, NH, NKV, scale, st);
     BM_ATT_CASE(64, 1) BM_ATT_CASE(64, 2) BM_ATT_CASE(64, 3) BM_ATT_CASE(64, 4) BM_ATT_CASE(64, 8)
     BM_ATT_CASE(128, 1) BM_ATT_CASE(128, 2) BM_ATT_CASE(128, 4) BM_ATT_CASE(128, 8)
 #undef BM_ATT_CASE
     return -3;
 }
+int decode_prep(bf16* a, int parts, const float* x, int ldx, int mode, const float* lnw, float eps, float* init_out, int ldo,
+                const float* init_src, int ldr, int n_out, int rows, int C, cudaStream_t st) {
+    if (rows <= 0 || C <= 0 || (parts != 2 && parts != 3) || mode < 0 || mode > 2 || (mode == 1 && !lnw)) return -1;
+    if (mode == 1) return launch_k(decode_prep_kernel<1>, dim3(rows), dim3(256), 0, st, a, parts, x, ldx, lnw, eps, init_out, ldo, init_src, ldr, n_out, C);
+    if (mode == 2) return launch_k(decode_prep_kernel<2>, dim3(rows), dim3(256), 0, st, a, parts, x, ldx, lnw, eps, init_out, ldo, init_src, ldr, n_out, C);
+    return launch_k(decode_prep_kernel<0>, dim3(rows), dim3(256), 0, st, a, parts, x, ldx, lnw, eps, init_out, ldo, init_src, ldr, n_out, C);
+}
 int decode_swiglu(float* out, const float* gu, int NB, int H, cudaStream_t st) {
     const long n = (long)NB * H;
-    decode_swiglu_kernel<<<(int)((n + 255) / 256), 256, 0, st>>>(out, gu, H, NB);
-    return 0;
+    return launch_k(decode_swiglu_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, out, gu, H, NB);
 }
 int decode_embed(float* out, int ttype, const void* table, const int* tokens, int NB, int D, cudaStream_t st) {
     const long n = (long)NB * D;
+    // first kernel of a step: launched without the attribute, so it fully serialises behind whatever precedes the step
     if (ttype == 1) decode_embed_kernel<bf16><<<(int)((n + 255) / 256), 256, 0, st>>>(out, (const bf16*)table, tokens, D, NB);
     else decode_embed_kernel<float><<<(int)((n + 255) / 256), 256, 0, st>>>(out, (const float*)table, tokens, D, NB);
     return 0;
 }
-int decode_argmax(int* out, const float* logits, int NB, int V, cudaStream_t st) {
-    decode_argmax_kernel<<<NB, 1024, 0, st>>>(out, logits, V);
-    return 0;
+int decode_argmax(int* out, const float* logits, int NB, int V, int* pos_to_advance, cudaStream_t st) {
+    return launch_k(decode_argmax_kernel, dim3(NB), dim3(1024), 0, st, out, logits, V, pos_to_advance);
 }
 int decode_advance(int* pos, cudaStream_t st) {
-    decode_advance_kernel<<<1, 1, 0, st>>>(pos);
-    return 0;
+    return launch_k(decode_advance_kernel, dim3(1), dim3(1), 0, st, pos);
 }
 
 }  // namespace bmb

@@ -20,8 +20,12 @@
 typedef struct {
     void* w;       /* int8 q[OC][C], or bf16 / fp32 [OC][C] */
     float* scales; /* Q8 only: [OC][C/32] */
+    void* wx;      /* tensor-core path only: bf16 [OC][parts * C], [w | w] or [w_hi | w_hi | w_lo] of the SAME weight values */
+    int parts;
     int OC, C;
 } bm_mat_t;
+
+#define BM_TC_MIN_SEQUENCES 8 /* from this many sequences on, the products run as tensor-core GEMMs */
 
 typedef struct {
     float *ln1, *ln2;
@@ -38,6 +42,10 @@ struct bm_session_s {
     float* embed; /* [V, D] fp32 embedding table as loaded (src/baremetal/session.c:114-123); aliases head in fp32 mode */
     float *cache, *cs, *x, *xn, *qkv, *att, *x1, *gu, *act, *logits;
     int *d_pos, *d_tokens, *d_next, *d_gen;
+    void* att_scratch;
+    void* a_op; /* tensor-core path: bf16 split operand rows */
+    void* head_wx;
+    int head_parts, tc;
     int gen_cap;
     float* h_logits;
     int graph_ready;
@@ -111,6 +119,39 @@ static int upload_matrix(bm_session_t* s, bm_mat_t* m, int wtype, const float* c
         if (!m->w) rc = -1;
         else { bmc_upload(be, m->w, host, n * sizeof(float)); bmc_sync(be); }
     }
+    if (rc == 0 && s->tc) {
+        /* the values the GEMV path would multiply with, split into bf16 hi + lo (lo is zero for bf16 weights) */
+        const int parts = wtype == BMC_W_BF16 ? 2 : 3;
+        float* eff = (float*)malloc(n * sizeof(float));
+        uint16_t* hi = (uint16_t*)malloc(n * 2);
+        uint16_t* lo = (uint16_t*)malloc(n * 2);
+        uint16_t* wx = (uint16_t*)malloc(n * 2 * parts);
+        if (wtype == BMC_W_Q8) {
+            int8_t* q = (int8_t*)malloc(n);
+            float* sc = (float*)malloc(n / 32 * sizeof(float));
+            bmx_quantize_q8(host, q, sc, n);
+            for (size_t i = 0; i < n; i++) eff[i] = (float)q[i] * sc[i / 32];
+            free(q);
+            free(sc);
+        } else {
+            memcpy(eff, host, n * sizeof(float));
+        }
+        bm_f32_to_bf16_array(eff, hi, n);
+        bm_bf16_to_f32_array(hi, host, n);
+        for (size_t i = 0; i < n; i++) eff[i] -= host[i];
+        bm_f32_to_bf16_array(eff, lo, n);
+        for (int r = 0; r < OC; r++) {
+            uint16_t* d = wx + (size_t)r * parts * C;
+            memcpy(d, hi + (size_t)r * C, (size_t)C * 2);
+            memcpy(d + C, hi + (size_t)r * C, (size_t)C * 2);
+            if (parts == 3) memcpy(d + 2 * (size_t)C, lo + (size_t)r * C, (size_t)C * 2);
+        }
+        m->parts = parts;
+        m->wx = bmc_alloc(be, n * 2 * parts);
+        if (!m->wx) rc = -1;
+        else { bmc_upload(be, m->wx, wx, n * 2 * parts); bmc_sync(be); }
+        free(eff); free(hi); free(lo); free(wx);
+    }
     free(host);
     return rc;
 }
@@ -137,6 +178,7 @@ bm_session_t* bmx_create_session_batched(bm_context_t* ctx, bm_model_t* model, i
     s->ctx = ctx;
     s->model = model;
     s->NB = n_sequences;
+    s->tc = n_sequences >= BM_TC_MIN_SEQUENCES && !getenv("BM_NO_TC_DECODE");
     s->MS = max_positions > 0 ? max_positions : (a->max_seq_len > 0 ? a->max_seq_len : 2048);
     const int lowp = model->precision == BM_PRECISION_BF16;
     s->wtype = model->quant_bits == 8 ? BMC_W_Q8 : (lowp ? BMC_W_BF16 : BMC_W_F32);
@@ -168,6 +210,8 @@ bm_session_t* bmx_create_session_batched(bm_context_t* ctx, bm_model_t* model, i
         const int rh[1] = {V};
         ok = s->lnf && upload_matrix(s, &head, s->head_type, ph, rh, 1, D) == 0;
         s->head = head.w;
+        s->head_wx = head.wx;
+        s->head_parts = head.parts;
         if (ok && s->head_type == BMC_W_F32) s->embed = (float*)s->head;
         else if (ok) { s->embed = upload_f32(s, model->embed, (size_t)V * D); ok = s->embed != NULL; }
     }
@@ -192,6 +236,14 @@ bm_session_t* bmx_create_session_batched(bm_context_t* ctx, bm_model_t* model, i
         DALLOC(s->x, (size_t)NB * D * 4); DALLOC(s->xn, (size_t)NB * D * 4); DALLOC(s->qkv, (size_t)NB * (QD + 2 * KV) * 4);
         DALLOC(s->att, (size_t)NB * QD * 4); DALLOC(s->x1, (size_t)NB * D * 4); DALLOC(s->gu, (size_t)NB * 2 * H * 4);
         DALLOC(s->act, (size_t)NB * H * 4); DALLOC(s->logits, (size_t)NB * V * 4);
+        const size_t asb = bmc_decode_attention_scratch_bytes(NB, MS, a->n_heads, a->n_kv_heads, HD);
+        DALLOC(s->att_scratch, asb);
+        if (s->att_scratch) bmc_memset(be, s->att_scratch, 0, asb);
+        if (s->tc) {
+            int cmax = D > H ? D : H;
+            if (QD > cmax) cmax = QD;
+            DALLOC(s->a_op, (size_t)NB * 3 * cmax * 2);
+        }
         DALLOC(s->d_pos, 16); DALLOC(s->d_tokens, (size_t)NB * 4); DALLOC(s->d_next, (size_t)NB * 4);
     }
 #undef DALLOC
@@ -217,13 +269,13 @@ void bm_destroy_session(bm_session_t* s) {
             bm_dec_layer_t* y = &s->layers[l];
             bmc_free(be, y->ln1); bmc_free(be, y->ln2);
             bm_mat_t* ms[4] = {&y->qkv, &y->o, &y->gu, &y->down};
-            for (int i = 0; i < 4; i++) { bmc_free(be, ms[i]->w); bmc_free(be, ms[i]->scales); }
+            for (int i = 0; i < 4; i++) { bmc_free(be, ms[i]->w); bmc_free(be, ms[i]->scales); bmc_free(be, ms[i]->wx); }
         }
         free(s->layers);
     }
     bmc_free(be, s->lnf); if ((void*)s->embed != s->head) bmc_free(be, s->embed); bmc_free(be, s->head); bmc_free(be, s->cache); bmc_free(be, s->cs); bmc_free(be, s->x); bmc_free(be, s->xn);
     bmc_free(be, s->qkv); bmc_free(be, s->att); bmc_free(be, s->x1); bmc_free(be, s->gu); bmc_free(be, s->act); bmc_free(be, s->logits);
-    bmc_free(be, s->d_pos); bmc_free(be, s->d_tokens); bmc_free(be, s->d_next); bmc_free(be, s->d_gen);
+    bmc_free(be, s->att_scratch); bmc_free(be, s->a_op); bmc_free(be, s->head_wx); bmc_free(be, s->d_pos); bmc_free(be, s->d_tokens); bmc_free(be, s->d_next); bmc_free(be, s->d_gen);
     free(s->h_logits);
     free(s);
 }
@@ -245,22 +297,50 @@ static int enqueue_step(bm_session_t* s) {
     const int QD = NH * HD, KV = NKV * HD, NB = s->NB, MS = s->MS;
     const float scale = 1.0f / sqrtf((float)HD), eps = 1e-5f;
     TRYS(bmc_decode_embed(be, s->x, BMC_W_F32, s->embed, s->d_tokens, NB, D));
+    /* few sequences: five kernels per layer, norms / RoPE / cache store / SwiGLU folded into their consumers */
+    const int fused = NB < 4 && D <= 3072 && H <= 3072 && QD <= 3072;
     for (int l = 0; l < L; l++) {
         const bm_dec_layer_t* y = &s->layers[l];
+        if (s->tc) {
+            TRYS(bmc_decode_prep(be, s->a_op, y->qkv.parts, s->x, D, 1, y->ln1, eps, s->qkv, QD + 2 * KV, NULL, 0, QD + 2 * KV, NB, D));
+            TRYS(bmc_decode_gemm(be, s->qkv, QD + 2 * KV, s->a_op, y->qkv.wx, y->qkv.parts, NB, D, QD + 2 * KV));
+            TRYS(bmc_decode_attention_fused(be, s->att, s->qkv, s->cache, s->cs, s->d_pos, s->att_scratch, l, NB, MS, NH, NKV, HD, scale));
+            TRYS(bmc_decode_prep(be, s->a_op, y->o.parts, s->att, QD, 0, NULL, 0.0f, s->x1, D, s->x, D, D, NB, QD));
+            TRYS(bmc_decode_gemm(be, s->x1, D, s->a_op, y->o.wx, y->o.parts, NB, QD, D));
+            TRYS(bmc_decode_prep(be, s->a_op, y->gu.parts, s->x1, D, 1, y->ln2, eps, s->gu, 2 * H, NULL, 0, 2 * H, NB, D));
+            TRYS(bmc_decode_gemm(be, s->gu, 2 * H, s->a_op, y->gu.wx, y->gu.parts, NB, D, 2 * H));
+            TRYS(bmc_decode_prep(be, s->a_op, y->down.parts, s->gu, 2 * H, 2, NULL, 0.0f, s->x, D, s->x1, D, D, NB, H));
+            TRYS(bmc_decode_gemm(be, s->x, D, s->a_op, y->down.wx, y->down.parts, NB, H, D));
+            continue;
+        }
+        if (fused) {
+            TRYS(bmc_decode_gemv_fused(be, s->qkv, QD + 2 * KV, s->x, D, s->wtype, y->qkv.w, y->qkv.scales, NULL, 0, 1, y->ln1, eps, NB, D, QD + 2 * KV));
+            TRYS(bmc_decode_attention_fused(be, s->att, s->qkv, s->cache, s->cs, s->d_pos, s->att_scratch, l, NB, MS, NH, NKV, HD, scale));
+            TRYS(bmc_decode_gemv(be, s->x1, D, s->att, QD, s->wtype, y->o.w, y->o.scales, s->x, D, NB, QD, D));
+            TRYS(bmc_decode_gemv_fused(be, s->gu, 2 * H, s->x1, D, s->wtype, y->gu.w, y->gu.scales, NULL, 0, 1, y->ln2, eps, NB, D, 2 * H));
+            TRYS(bmc_decode_gemv_fused(be, s->x, D, s->gu, 2 * H, s->wtype, y->down.w, y->down.scales, s->x1, D, 2, NULL, 0.0f, NB, H, D));
+            continue;
+        }
         TRYS(bmc_decode_rmsnorm(be, s->xn, s->x, y->ln1, NB, D, eps));
         TRYS(bmc_decode_gemv(be, s->qkv, QD + 2 * KV, s->xn, D, s->wtype, y->qkv.w, y->qkv.scales, NULL, 0, NB, D, QD + 2 * KV));
         TRYS(bmc_decode_rope_kv(be, s->qkv, s->cache, s->cs, s->d_pos, l, NB, MS, NH, NKV, HD));
-        TRYS(bmc_decode_attention(be, s->att, s->qkv, s->cache, s->d_pos, l, NB, MS, NH, NKV, HD, scale));
+        TRYS(bmc_decode_attention(be, s->att, s->qkv, s->cache, s->d_pos, s->att_scratch, l, NB, MS, NH, NKV, HD, scale));
         TRYS(bmc_decode_gemv(be, s->x1, D, s->att, QD, s->wtype, y->o.w, y->o.scales, s->x, D, NB, QD, D));
         TRYS(bmc_decode_rmsnorm(be, s->xn, s->x1, y->ln2, NB, D, eps));
         TRYS(bmc_decode_gemv(be, s->gu, 2 * H, s->xn, D, s->wtype, y->gu.w, y->gu.scales, NULL, 0, NB, D, 2 * H));
         TRYS(bmc_decode_swiglu(be, s->act, s->gu, NB, H));
         TRYS(bmc_decode_gemv(be, s->x, D, s->act, H, s->wtype, y->down.w, y->down.scales, s->x1, D, NB, H, D));
     }
-    TRYS(bmc_decode_rmsnorm(be, s->xn, s->x, s->lnf, NB, D, eps));
-    TRYS(bmc_decode_gemv(be, s->logits, V, s->xn, D, s->head_type, s->head, NULL, NULL, 0, NB, D, V));
-    TRYS(bmc_decode_argmax(be, s->d_next, s->logits, NB, V));
-    TRYS(bmc_decode_advance(be, s->d_pos));
+    if (s->tc) {
+        TRYS(bmc_decode_prep(be, s->a_op, s->head_parts, s->x, D, 1, s->lnf, eps, s->logits, V, NULL, 0, V, NB, D));
+        TRYS(bmc_decode_gemm(be, s->logits, V, s->a_op, s->head_wx, s->head_parts, NB, D, V));
+    } else if (fused) {
+        TRYS(bmc_decode_gemv_fused(be, s->logits, V, s->x, D, s->head_type, s->head, NULL, NULL, 0, 1, s->lnf, eps, NB, D, V));
+    } else {
+        TRYS(bmc_decode_rmsnorm(be, s->xn, s->x, s->lnf, NB, D, eps));
+        TRYS(bmc_decode_gemv(be, s->logits, V, s->xn, D, s->head_type, s->head, NULL, NULL, 0, NB, D, V));
+    }
+    TRYS(bmc_decode_argmax_advance(be, s->d_next, s->logits, NB, V, s->d_pos));
     return 0;
 }
 
@@ -378,9 +458,9 @@ size_t bmx_session_weight_bytes(bm_session_t* s) {
         const bm_mat_t* ms[4] = {&s->layers[l].qkv, &s->layers[l].o, &s->layers[l].gu, &s->layers[l].down};
         for (int i = 0; i < 4; i++) {
             const size_t e = (size_t)ms[i]->OC * ms[i]->C;
-            n += s->wtype == BMC_W_Q8 ? e + e / 32 * 4 : s->wtype == BMC_W_BF16 ? e * 2 : e * 4;
+            n += s->tc ? e * 2 * ms[i]->parts : s->wtype == BMC_W_Q8 ? e + e / 32 * 4 : s->wtype == BMC_W_BF16 ? e * 2 : e * 4;
         }
     }
-    n += (size_t)s->model->arch.vocab_size * s->model->arch.dim * (s->head_type == BMC_W_BF16 ? 2 : 4);
+    n += (size_t)s->model->arch.vocab_size * s->model->arch.dim * (s->tc ? 2 * s->head_parts : s->head_type == BMC_W_BF16 ? 2 : 4);
     return n;
 }

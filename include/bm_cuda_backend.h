@@ -157,14 +157,36 @@ int bmc_argmax(bmc_ctx_t* ctx, int* d_index, const float* d_logits, int V);
 enum { BMC_W_Q8 = 0, BMC_W_BF16 = 1, BMC_W_F32 = 2 };
 int bmc_decode_gemv(bmc_ctx_t* ctx, float* d_out, int ldo, const float* d_x, int ldx, int wtype, const void* d_w, const float* d_scales,
                     const float* d_residual, int ldr, int NB, int C, int OC);
+/* The same product with a prologue folded into the operand load (single-sequence kernel, C <= 3072):
+ *   prologue 1: RMSNorm(x) * d_norm_weight (rmsnorm_forward_v2 followed by the matmul, as the reference's fused
+ *               rmsnorm_matmul_forward does for the classifier, src/kernels/forward.metal);
+ *   prologue 2: d_x rows are [gate | up] (2C wide) and the operand is silu(gate) * up (swiglu_forward, forward.metal:1179). */
+int bmc_decode_gemv_fused(bmc_ctx_t* ctx, float* d_out, int ldo, const float* d_x, int ldx, int wtype, const void* d_w, const float* d_scales,
+                          const float* d_residual, int ldr, int prologue, const float* d_norm_weight, float eps, int NB, int C, int OC);
 int bmc_decode_rmsnorm(bmc_ctx_t* ctx, float* d_out, const float* d_x, const float* d_w, int NB, int C, float eps);
 int bmc_decode_rope_kv(bmc_ctx_t* ctx, float* d_qkv, float* d_cache, const float* d_cs_table, const int* d_pos, int layer, int NB, int MS,
                        int NH, int NKV, int HD);
-int bmc_decode_attention(bmc_ctx_t* ctx, float* d_out, const float* d_qkv, const float* d_cache, const int* d_pos, int layer, int NB,
-                         int MS, int NH, int NKV, int HD, float scale);
+/* d_scratch: NULL (one block per sequence and KV head walks every position) or a buffer of bmc_decode_attention_scratch_bytes(),
+ * zeroed once by the caller, which lets the positions be split over several blocks that merge their softmax partials. */
+size_t bmc_decode_attention_scratch_bytes(int NB, int MS, int NH, int NKV, int HD);
+int bmc_decode_attention(bmc_ctx_t* ctx, float* d_out, const float* d_qkv, const float* d_cache, const int* d_pos, void* d_scratch, int layer,
+                         int NB, int MS, int NH, int NKV, int HD, float scale);
+/* rope_forward + kv_store + attention_forward in one kernel: d_qkv holds the raw projections and is left untouched */
+int bmc_decode_attention_fused(bmc_ctx_t* ctx, float* d_out, const float* d_qkv, float* d_cache, const float* d_cs_table, const int* d_pos,
+                               void* d_scratch, int layer, int NB, int MS, int NH, int NKV, int HD, float scale);
+/* Tensor-core products with fp32-accurate results, for many rows (batched decode, prefill). bmc_decode_prep splits the fp32 operand
+ * rows (mode 0 = x, 1 = RMSNorm(x) * weight, 2 = silu(gate) * up of [gate | up] rows) into bf16 [hi | lo] (parts 2) or [hi | lo | hi]
+ * (parts 3) and sets the fp32 output rows to d_init_src rows or zero; bmc_decode_gemm accumulates a x w^T into them, where w holds
+ * [w | w] (parts 2: weights exactly representable in bf16) or [w_hi | w_hi | w_lo] (parts 3) per output row. Same arithmetic
+ * as matmul_forward_q8 / _bf16 / _naive (src/kernels/forward.metal:625,52,23) to ~2^-17 relative. */
+int bmc_decode_prep(bmc_ctx_t* ctx, void* d_a, int parts, const float* d_x, int ldx, int mode, const float* d_norm_weight, float eps,
+                    float* d_init_out, int ldo, const float* d_init_src, int ldr, int n_out, int rows, int C);
+int bmc_decode_gemm(bmc_ctx_t* ctx, float* d_out, int ldo, const void* d_a, const void* d_w, int parts, int rows, int C, int OC);
 int bmc_decode_swiglu(bmc_ctx_t* ctx, float* d_out, const float* d_gate_up, int NB, int H);
 int bmc_decode_embed(bmc_ctx_t* ctx, float* d_out, int table_type, const void* d_table, const int* d_tokens, int NB, int D);
 int bmc_decode_argmax(bmc_ctx_t* ctx, int* d_out, const float* d_logits, int NB, int V);
+/* argmax per sequence, then the position counter + 1 (last kernel of a step) */
+int bmc_decode_argmax_advance(bmc_ctx_t* ctx, int* d_out, const float* d_logits, int NB, int V, int* d_pos);
 int bmc_decode_advance(bmc_ctx_t* ctx, int* d_pos);
 /* Record everything enqueued between begin and end into a CUDA graph and replay it with launch (one graph per context). */
 int bmc_graph_begin(bmc_ctx_t* ctx);
