@@ -524,8 +524,18 @@ int bmc_decode_gemm(bmc_ctx_t* ctx, float* d_out, int ldo, const void* d_a, cons
         const int kb = (K + 63) / 64;
         if (splits > kb / 2) splits = kb / 2 > 0 ? kb / 2 : 1;
     }
-    GemmProblem g{rows, OC, K, (const bf16*)d_a, K, 0, (const bf16*)d_w, K, 0, d_out, ldo, GEMM_OUT_F32_ATOMIC, nullptr, 0, splits, tile_n};
+    GemmProblem g{rows, OC, K, (const bf16*)d_a, K, 0, (const bf16*)d_w, K, 0, d_out, ldo, GEMM_OUT_F32_ATOMIC, nullptr, 0, splits, tile_n,
+                  getenv("BM_NO_PDL") ? 0 : 1};
     return note(ctx, run_umma(ctx, g));
+}
+int bmc_decode_kv_scatter(bmc_ctx_t* ctx, float* d_cache, const float* d_qkv, int ldqkv, int layer, int NB, int T, int MS, int QD, int KV) {
+    BMC_CHECK_CTX(ctx);
+    return note(ctx, decode_kv_scatter(d_cache, d_qkv, ldqkv, layer, NB, T, MS, QD, KV, ctx->stream));
+}
+int bmc_prefill_attention(bmc_ctx_t* ctx, float* d_out, int ldo, const float* d_q, int ldq, const float* d_k, const float* d_v, int ldkv, int NB,
+                          int T, int NH, int NKV, int HD, float scale) {
+    BMC_CHECK_CTX(ctx);
+    return note(ctx, prefill_attention_f32(d_out, ldo, d_q, ldq, d_k, d_v, ldkv, NB, T, NH, NKV, HD, scale, ctx->stream));
 }
 int bmc_decode_swiglu(bmc_ctx_t* ctx, float* d_out, const float* d_gate_up, int NB, int H) {
     BMC_CHECK_CTX(ctx);

@@ -98,6 +98,10 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
+    // Launched with programmatic stream serialisation, the set-up above overlaps the tail of the preceding kernel; nothing
+    // before this point touches global memory. Without the launch attribute both instructions are no-ops.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t tmem_base = bars.tmem_base;
     volatile int* abort_flag = &bars.abort_flag;
 
@@ -392,8 +396,21 @@ int gemm_bf16_umma(const GemmProblem& g, int* err_flag, cudaStream_t stream) {
 
     const long units = (long)p.tiles_m * p.tiles_n * p.splits;
     const int grid = (int)(units < g_num_sms ? units : g_num_sms);
-    gemm_bf16_umma_kernel<<<grid, NUM_THREADS, SMEM_DYN_BYTES, stream>>>(tmA, tmB, p);
     g_launches.fetch_add(1);
+    if (g.pdl) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(NUM_THREADS);
+        cfg.dynamicSmemBytes = SMEM_DYN_BYTES;
+        cfg.stream = stream;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = at;
+        cfg.numAttrs = 1;
+        return cudaLaunchKernelEx(&cfg, gemm_bf16_umma_kernel, tmA, tmB, p) == cudaSuccess ? 0 : -7;
+    }
+    gemm_bf16_umma_kernel<<<grid, NUM_THREADS, SMEM_DYN_BYTES, stream>>>(tmA, tmB, p);
     return cudaGetLastError() == cudaSuccess ? 0 : -7;
 }
 

@@ -39,6 +39,7 @@ struct GemmProblem {
     int ldr;
     int splits;  // >1 only with GEMM_OUT_F32_ATOMIC
     int tile_n;  // 0 = choose
+    int pdl;     // 1 = launch with programmatic stream serialisation (the predecessor must be a kernel of the same stream)
 };
 
 // Launches on `stream`. Returns 0, or a negative code for an invalid problem / failed launch.

@@ -44,8 +44,10 @@ struct bm_session_s {
     int *d_pos, *d_tokens, *d_next, *d_gen;
     void* att_scratch;
     void* a_op; /* tensor-core path: bf16 split operand rows */
+    void* pf_buf; /* prefill scratch, grows to the largest prompt seen */
+    size_t pf_bytes;
     void* head_wx;
-    int head_parts, tc;
+    int head_parts, tc, tc_weights;
     int gen_cap;
     float* h_logits;
     int graph_ready;
@@ -119,7 +121,7 @@ static int upload_matrix(bm_session_t* s, bm_mat_t* m, int wtype, const float* c
         if (!m->w) rc = -1;
         else { bmc_upload(be, m->w, host, n * sizeof(float)); bmc_sync(be); }
     }
-    if (rc == 0 && s->tc) {
+    if (rc == 0 && s->tc_weights) {
         /* the values the GEMV path would multiply with, split into bf16 hi + lo (lo is zero for bf16 weights) */
         const int parts = wtype == BMC_W_BF16 ? 2 : 3;
         float* eff = (float*)malloc(n * sizeof(float));
@@ -178,7 +180,8 @@ bm_session_t* bmx_create_session_batched(bm_context_t* ctx, bm_model_t* model, i
     s->ctx = ctx;
     s->model = model;
     s->NB = n_sequences;
-    s->tc = n_sequences >= BM_TC_MIN_SEQUENCES && !getenv("BM_NO_TC_DECODE");
+    s->tc_weights = !getenv("BM_NO_TC_DECODE"); /* split-bf16 copies: prefill of any session, decode of batched ones */
+    s->tc = s->tc_weights && n_sequences >= BM_TC_MIN_SEQUENCES;
     s->MS = max_positions > 0 ? max_positions : (a->max_seq_len > 0 ? a->max_seq_len : 2048);
     const int lowp = model->precision == BM_PRECISION_BF16;
     s->wtype = model->quant_bits == 8 ? BMC_W_Q8 : (lowp ? BMC_W_BF16 : BMC_W_F32);
@@ -275,7 +278,7 @@ void bm_destroy_session(bm_session_t* s) {
     }
     bmc_free(be, s->lnf); if ((void*)s->embed != s->head) bmc_free(be, s->embed); bmc_free(be, s->head); bmc_free(be, s->cache); bmc_free(be, s->cs); bmc_free(be, s->x); bmc_free(be, s->xn);
     bmc_free(be, s->qkv); bmc_free(be, s->att); bmc_free(be, s->x1); bmc_free(be, s->gu); bmc_free(be, s->act); bmc_free(be, s->logits);
-    bmc_free(be, s->att_scratch); bmc_free(be, s->a_op); bmc_free(be, s->head_wx); bmc_free(be, s->d_pos); bmc_free(be, s->d_tokens); bmc_free(be, s->d_next); bmc_free(be, s->d_gen);
+    bmc_free(be, s->att_scratch); bmc_free(be, s->pf_buf); bmc_free(be, s->a_op); bmc_free(be, s->head_wx); bmc_free(be, s->d_pos); bmc_free(be, s->d_tokens); bmc_free(be, s->d_next); bmc_free(be, s->d_gen);
     free(s->h_logits);
     free(s);
 }
@@ -368,6 +371,70 @@ static int run_step(bm_session_t* s) {
     return rc;
 }
 
+#define BM_PREFILL_MIN_TOKENS 8
+
+/* Prompt pass from position 0 for every sequence at once (bm_prefill, src/baremetal/session.c:86-139): all T prompt rows go
+ * through each layer together, products on the tensor cores, causal attention over the prompt, K and V copied into the cache.
+ * tokens: NB x T (host). Leaves the last row's logits, the greedy choice in d_next and the position at T. */
+static int prefill(bm_session_t* s, const int* tokens, int T) {
+    bmc_ctx_t* be = s->ctx->be;
+    const bm_arch_t* a = &s->model->arch;
+    const int L = a->n_layers, D = a->dim, H = a->hidden_dim, V = a->vocab_size, HD = s->model->head_size, NH = a->n_heads, NKV = a->n_kv_heads;
+    const int QD = NH * HD, KV = NKV * HD, NB = s->NB, MS = s->MS, W = QD + 2 * KV;
+    const size_t R = (size_t)NB * T;
+    const float scale = 1.0f / sqrtf((float)HD), eps = 1e-5f;
+    int cmax = D > H ? D : H;
+    if (QD > cmax) cmax = QD;
+    /* one grow-only scratch allocation, carved into 256-byte aligned pieces */
+    size_t sizes[8] = {R * D * 4, R * D * 4, R * W * 4, R * QD * 4, R * 2 * H * 4, (size_t)NB * NH * T * 4, R * 3 * cmax * 2, R * sizeof(int)};
+    size_t offs[8], total = 0;
+    for (int i = 0; i < 8; i++) { offs[i] = total; total += (sizes[i] + 255) / 256 * 256; }
+    int rc = -1;
+    if (total > s->pf_bytes) {
+        bmc_sync(be);
+        bmc_free(be, s->pf_buf);
+        s->pf_buf = bmc_alloc(be, total);
+        s->pf_bytes = s->pf_buf ? total : 0;
+        if (!s->pf_buf) { BM_LOG_ERROR("prefill: out of memory (%zu bytes)", total); return -1; }
+    }
+    char* base = (char*)s->pf_buf;
+    float *x = (float*)(base + offs[0]), *x1 = (float*)(base + offs[1]), *qkv = (float*)(base + offs[2]), *att = (float*)(base + offs[3]);
+    float *gu = (float*)(base + offs[4]), *lse = (float*)(base + offs[5]);
+    void* aop = base + offs[6];
+    int* dtok = (int*)(base + offs[7]);
+#define TRYP(call) do { rc = (call); if (rc) { BM_LOG_ERROR("prefill: %s failed (%d)", #call, rc); goto done; } } while (0)
+    TRYP(bmc_upload(be, dtok, tokens, R * sizeof(int)));
+    TRYP(bmc_decode_embed(be, x, BMC_W_F32, s->embed, dtok, (int)R, D));
+    for (int l = 0; l < L; l++) {
+        const bm_dec_layer_t* y = &s->layers[l];
+        TRYP(bmc_decode_prep(be, aop, y->qkv.parts, x, D, 1, y->ln1, eps, qkv, W, NULL, 0, W, (int)R, D));
+        TRYP(bmc_decode_gemm(be, qkv, W, aop, y->qkv.wx, y->qkv.parts, (int)R, D, W));
+        TRYP(bmc_rope(be, BMC_F32, qkv, W, qkv + QD, W, s->cs, (int)R, T, NH, NKV, HD, 1));
+        TRYP(bmc_decode_kv_scatter(be, s->cache, qkv, W, l, NB, T, MS, QD, KV));
+        if (HD == 64) TRYP(bmc_prefill_attention(be, att, QD, qkv, W, qkv + QD, qkv + QD + KV, W, NB, T, NH, NKV, HD, scale));
+        else TRYP(bmc_attention_forward(be, BMC_F32, att, QD, lse, qkv, W, qkv + QD, qkv + QD + KV, W, NULL, NB, T, NH, NKV, HD, scale));
+        TRYP(bmc_decode_prep(be, aop, y->o.parts, att, QD, 0, NULL, 0.0f, x1, D, x, D, D, (int)R, QD));
+        TRYP(bmc_decode_gemm(be, x1, D, aop, y->o.wx, y->o.parts, (int)R, QD, D));
+        TRYP(bmc_decode_prep(be, aop, y->gu.parts, x1, D, 1, y->ln2, eps, gu, 2 * H, NULL, 0, 2 * H, (int)R, D));
+        TRYP(bmc_decode_gemm(be, gu, 2 * H, aop, y->gu.wx, y->gu.parts, (int)R, D, 2 * H));
+        TRYP(bmc_decode_prep(be, aop, y->down.parts, gu, 2 * H, 2, NULL, 0.0f, x, D, x1, D, D, (int)R, H));
+        TRYP(bmc_decode_gemm(be, x, D, aop, y->down.wx, y->down.parts, (int)R, H, D));
+    }
+    /* only the last row of each sequence feeds the classifier */
+    TRYP(bmc_decode_prep(be, aop, s->head_parts, x + (size_t)(T - 1) * D, T * D, 1, s->lnf, eps, s->logits, V, NULL, 0, V, NB, D));
+    TRYP(bmc_decode_gemm(be, s->logits, V, aop, s->head_wx, s->head_parts, NB, D, V));
+    TRYP(bmc_decode_argmax(be, s->d_next, s->logits, NB, V));
+    TRYP(bmc_upload(be, s->d_pos, &T, sizeof(int)));
+    TRYP(bmc_sync(be));
+    s->pos = T;
+#undef TRYP
+done:
+    return rc;
+}
+static int can_prefill(const bm_session_t* s, int T) {
+    return s->tc_weights && s->pos == 0 && T >= BM_PREFILL_MIN_TOKENS && T <= s->MS && !getenv("BM_NO_PREFILL");
+}
+
 float* bm_step(bm_session_t* s, int token) {
     if (!s || s->NB != 1) return NULL;
     bmc_ctx_t* be = s->ctx->be;
@@ -382,10 +449,15 @@ float* bm_step(bm_session_t* s, int token) {
 float* bm_forward(bm_session_t* s, const int* tokens, int n_tokens) {
     if (!s || s->NB != 1 || !tokens || n_tokens < 1) return NULL;
     bmc_ctx_t* be = s->ctx->be;
-    for (int i = 0; i < n_tokens; i++) {
+    for (int i = 0; i < n_tokens; i++)
         if (tokens[i] < 0 || tokens[i] >= s->model->arch.vocab_size) return NULL;
-        if (bmc_upload(be, s->d_tokens, &tokens[i], sizeof(int)) != 0) return NULL;
-        if (run_step(s) != 0) return NULL;
+    if (can_prefill(s, n_tokens)) {
+        if (prefill(s, tokens, n_tokens) != 0) return NULL;
+    } else {
+        for (int i = 0; i < n_tokens; i++) {
+            if (bmc_upload(be, s->d_tokens, &tokens[i], sizeof(int)) != 0) return NULL;
+            if (run_step(s) != 0) return NULL;
+        }
     }
     if (bmc_download(be, s->h_logits, s->logits, (size_t)s->model->arch.vocab_size * sizeof(float)) != 0) return NULL;
     return s->h_logits;
@@ -413,12 +485,19 @@ int bmx_session_generate_greedy(bm_session_t* s, const int* prompt, int n_prompt
         if (!s->d_gen) return -3;
         s->gen_cap = n_new;
     }
-    int* col = (int*)malloc((size_t)NB * n_prompt * sizeof(int));
+    for (size_t i = 0; i < (size_t)NB * n_prompt; i++)
+        if (prompt[i] < 0 || prompt[i] >= s->model->arch.vocab_size) return -4;
+    if (can_prefill(s, n_prompt)) {
+        int rc0 = prefill(s, prompt, n_prompt);
+        if (rc0) return rc0;
+        n_prompt = 0; /* the loop below then starts from the prompt's greedy choice */
+    }
+    int* col = (int*)malloc(((size_t)NB * n_prompt + 1) * sizeof(int));
     for (int i = 0; i < n_prompt; i++)
         for (int b = 0; b < NB; b++) col[(size_t)i * NB + b] = prompt[(size_t)b * n_prompt + i];
-    int* d_prompt = (int*)bmc_alloc(be, (size_t)NB * n_prompt * sizeof(int));
+    int* d_prompt = (int*)bmc_alloc(be, ((size_t)NB * n_prompt + 1) * sizeof(int));
     if (!d_prompt) { free(col); return -3; }
-    bmc_upload(be, d_prompt, col, (size_t)NB * n_prompt * sizeof(int));
+    if (n_prompt > 0) bmc_upload(be, d_prompt, col, (size_t)NB * n_prompt * sizeof(int));
     bmc_sync(be);
     free(col);
     int rc = 0;

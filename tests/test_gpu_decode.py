@@ -30,9 +30,17 @@ def test_step_logits_match_reference_session(product, path):
         lg = s.step(t)
         if i >= 1:
             assert close(lg, g["logits"][i - 1]), (i, np.abs(lg - g["logits"][i - 1]).max())
-    # the step after the first is replayed from a captured graph; prefill must give the same bits as stepping
+    # the prompt in one pass (tensor-core prefill, test/prefill_test.c): same logits within the bound
     s.reset()
     lf = s.forward(g["prompt"])
+    assert close(lf, g["logits"][-1]) and close(lf, lg), np.abs(lf - lg).max()
+    # and token by token through bm_forward (steps after the first replay a captured graph): the same bits as bm_step
+    os.environ["BM_NO_PREFILL"] = "1"
+    try:
+        s.reset()
+        lf = s.forward(g["prompt"])
+    finally:
+        del os.environ["BM_NO_PREFILL"]
     assert np.array_equal(lf, lg)
     # greedy continuation through the public API
     out = []
@@ -88,17 +96,20 @@ def test_batched_sequences_equal_single_sequences(product, precision, quant, NB)
     product.bm_destroy_session(sess)
     product.bm_destroy_model(model)
     product.bm_destroy(ctx)
+    bound = 10 * TOL
     for b in range(NB):
         dec = oc.PortDecoder(a, w, precision, quant, 32)
         l1 = dec.forward(prompts[b])
-        ids = []
         for i in range(n_new):
-            ids.append(int(np.argmax(l1)))
+            top = np.argsort(l1)[-2:]
+            if l1[top[1]] - l1[top[0]] <= bound * np.abs(l1).max():
+                break                                   # a near-tie: either choice is right, and the sequences part ways
+            assert int(top[1]) == int(out[b, i]), (b, i)
             if i + 1 < n_new:
-                l1 = dec.step(ids[-1])
+                l1 = dec.step(int(out[b, i]))
+        else:
+            assert close(lg[b], l1), b
         dec.close()
-        assert ids == list(out[b]), b
-        assert close(lg[b], l1), b
 
 
 def test_reset_replays_and_cache_overflow_is_refused(product):
@@ -131,3 +142,159 @@ def test_135m_q8_decode_against_oracle(product):
     assert int(np.argmax(lg)) == int(np.argmax(lo))
     s.close()
     dec.close()
+
+
+# ---- kernels of the inference path through the extern "C" backend ABI ----------------------------------------------------
+import portk  # noqa: E402
+from devutil import BMC_F32, Backend, Ptr, bf16_round, f32_to_bf16_bits  # noqa: E402
+
+RNG = np.random.default_rng(77)
+
+
+@pytest.fixture(scope="module")
+def be(product):
+    b = Backend(product)
+    yield b
+    b.close()
+
+
+def rndf(*shape, scale=1.0):
+    return (RNG.standard_normal(shape) * scale).astype(np.float32)
+
+
+@pytest.mark.parametrize("NB,T,NH,NKV", [(2, 200, 6, 2), (1, 64, 3, 1), (3, 65, 2, 2), (1, 513, 15, 5)])
+def test_prefill_attention_fp32(be, NB, T, NH, NKV):
+    HD = 64
+    QD, KV = NH * HD, NKV * HD
+    ld = QD + 2 * KV
+    qkv = rndf(NB * T, ld)
+    d = be.put(qkv)
+    out = be.zeros(NB * T * QD)
+    be.ok("prefill_attention", Ptr(out), QD, Ptr(d), ld, Ptr(d, QD * 4), Ptr(d, (QD + KV) * 4), ld, NB, T, NH, NKV, HD, 0.125)
+    got = be.get(out, (NB, T, NH, HD))
+    x = qkv.reshape(NB, T, ld)
+    for b in range(NB):
+        ref = portk.attention_forward(x[b, :, :QD].reshape(T, NH, HD), x[b, :, QD:QD + KV].reshape(T, NKV, HD),
+                                      x[b, :, QD + KV:].reshape(T, NKV, HD), 0.125)
+        assert oc.rel_err(got[b], ref) < 1e-5
+
+
+def _q8(w):
+    q = np.zeros(w.size, np.int8)
+    sc = np.zeros(w.size // 32, np.float32)
+    lib = oc.load_port()
+    assert lib.orc_quantize_q8(oc.fptr(np.ascontiguousarray(w)), q.ctypes.data, oc.fptr(sc), w.size) == w.size // 32
+    return q.reshape(w.shape), sc.reshape(w.shape[0], -1)
+
+
+@pytest.mark.parametrize("wtype", [0, 1, 2])
+@pytest.mark.parametrize("NB,C,OC,prologue", [(1, 960, 1600, 0), (1, 960, 5120, 1), (2, 2560, 960, 2), (3, 576, 77, 1), (5, 384, 200, 0), (17, 1024, 130, 0)])
+def test_decode_gemv_all_weight_types(be, wtype, NB, C, OC, prologue):
+    """out = operand(x) W^T + residual, Q8 / bf16 / fp32 weights, plain / RMSNorm / SwiGLU operand, single-sequence and batched kernels."""
+    if prologue and NB >= 4:
+        pytest.skip("prologues exist in the single-sequence kernel only")
+    w = rndf(OC, C, scale=0.05)
+    x = rndf(NB, 2 * C if prologue == 2 else C)
+    res = rndf(NB, OC)
+    lnw = (1.0 + 0.1 * rndf(C)).astype(np.float32)
+    if wtype == 0:
+        q, sc = _q8(w)
+        weff = q.astype(np.float32) * np.repeat(sc, 32, axis=1)
+        dw, dsc = be.put(q.view(np.uint8)), be.put(sc)
+    elif wtype == 1:
+        weff = bf16_round(w)
+        hb = f32_to_bf16_bits(w)
+        dw = be.alloc(hb.nbytes)
+        assert be.lib.bmc_upload(be.ctx, dw, hb.ctypes.data, hb.nbytes) == 0
+        dsc = None
+    else:
+        weff, dw, dsc = w, be.put(w), None
+    if prologue == 1:
+        op = x / np.sqrt((x.astype(np.float64) ** 2).mean(axis=1, keepdims=True) + 1e-5).astype(np.float32) * lnw
+    elif prologue == 2:
+        g, u = x[:, :C], x[:, C:]
+        op = g / (1.0 + np.exp(-g)) * u
+    else:
+        op = x
+    ref = (op.astype(np.float64) @ weff.astype(np.float64).T + res).astype(np.float32)
+    out = be.zeros(NB * OC)
+    be.ok("decode_gemv_fused", Ptr(out), OC, Ptr(be.put(x)), x.shape[1], wtype, Ptr(dw), Ptr(dsc) if dsc else None, Ptr(be.put(res)), OC,
+          prologue, Ptr(be.put(lnw)), 1e-5, NB, C, OC)
+    assert oc.rel_err(be.get(out, (NB, OC)), ref) < 1e-5
+
+
+@pytest.mark.parametrize("rows,C,OC,parts,mode", [(64, 960, 1600, 3, 1), (8, 960, 960, 2, 0), (300, 2560, 960, 3, 2), (33, 384, 2048, 2, 1)])
+def test_split_bf16_gemm_matches_fp32_product(be, rows, C, OC, parts, mode):
+    """bmc_decode_prep + bmc_decode_gemm: the tensor-core product of the bf16 hi/lo split operands reproduces the fp32 product."""
+    w = rndf(OC, C, scale=0.05)
+    if parts == 2:
+        w = bf16_round(w)
+    hi = bf16_round(w)
+    lo = bf16_round(w - hi)
+    wx = np.concatenate([hi, hi, lo] if parts == 3 else [hi, hi], axis=1)
+    hb = f32_to_bf16_bits(wx)
+    dwx = be.alloc(hb.nbytes)
+    assert be.lib.bmc_upload(be.ctx, dwx, hb.ctypes.data, hb.nbytes) == 0
+    x = rndf(rows, 2 * C if mode == 2 else C)
+    res = rndf(rows, OC)
+    lnw = (1.0 + 0.1 * rndf(C)).astype(np.float32)
+    if mode == 1:
+        op = x / np.sqrt((x.astype(np.float64) ** 2).mean(axis=1, keepdims=True) + 1e-5).astype(np.float32) * lnw
+    elif mode == 2:
+        op = x[:, :C] / (1.0 + np.exp(-x[:, :C])) * x[:, C:]
+    else:
+        op = x
+    ref = (op.astype(np.float64) @ w.astype(np.float64).T + res).astype(np.float32)
+    a = be.alloc(rows * parts * C * 2)
+    out = be.zeros(rows * OC)
+    be.ok("decode_prep", Ptr(a), parts, Ptr(be.put(x)), x.shape[1], mode, Ptr(be.put(lnw)), 1e-5, Ptr(out), OC, Ptr(be.put(res)), OC, OC, rows, C)
+    be.ok("decode_gemm", Ptr(out), OC, Ptr(a), Ptr(dwx), parts, rows, C, OC)
+    assert oc.rel_err(be.get(out, (rows, OC)), ref) < 2e-5
+
+
+@pytest.mark.parametrize("NB,NH,NKV,MS,pos", [(1, 15, 5, 768, 700), (2, 6, 2, 96, 95), (70, 3, 1, 64, 10), (1, 4, 4, 2048, 1500)])
+def test_decode_attention_split_positions(be, NB, NH, NKV, MS, pos):
+    """One query against a cache of pos + 1 rows, with RoPE and the cache store inside the kernel, positions split over blocks."""
+    HD, L = 64, 2
+    QD, KV = NH * HD, NKV * HD
+    W = QD + 2 * KV
+    layer = 1
+    cache = np.zeros((L, 2, NB, MS, KV), np.float32)
+    cache[layer, :, :, :pos] = rndf(2, NB, pos, KV)
+    qkv = rndf(NB, W)
+    hd2 = HD // 2
+    inv = (1.0 / np.power(np.float32(100000.0), (2 * np.arange(hd2, dtype=np.float32)) / np.float32(HD))).astype(np.float32)
+    ang = np.arange(MS, dtype=np.float32)[:, None] * inv[None, :]
+    cs = np.stack([np.cos(ang), np.sin(ang)], axis=-1).astype(np.float32)
+
+    def rot(xh):  # [..., HD] at position pos
+        c, s = cs[pos, :, 0], cs[pos, :, 1]
+        x0, x1 = xh[..., :hd2], xh[..., hd2:]
+        return np.concatenate([x0 * c - x1 * s, x0 * s + x1 * c], axis=-1)
+    qr = rot(qkv[:, :QD].reshape(NB, NH, HD))
+    kr = rot(qkv[:, QD:QD + KV].reshape(NB, NKV, HD)).reshape(NB, KV)
+    full = cache.copy()
+    full[layer, 0, :, pos] = kr
+    full[layer, 1, :, pos] = qkv[:, QD + KV:]
+    mul = NH // NKV
+    ref = np.zeros((NB, NH, HD), np.float32)
+    for b in range(NB):
+        for h in range(NH):
+            kh = h // mul
+            K = full[layer, 0, b, :pos + 1, kh * HD:(kh + 1) * HD].astype(np.float64)
+            V = full[layer, 1, b, :pos + 1, kh * HD:(kh + 1) * HD].astype(np.float64)
+            sc = K @ qr[b, h].astype(np.float64) * 0.125
+            p = np.exp(sc - sc.max())
+            ref[b, h] = (p / p.sum()) @ V
+    dcache = be.put(cache)
+    dpos = be.put(np.array([pos], np.int32))
+    be.lib.bmc_decode_attention_scratch_bytes.restype = C.c_size_t
+    nbytes = be.lib.bmc_decode_attention_scratch_bytes(NB, MS, NH, NKV, HD)
+    scratch = be.zeros((nbytes + 3) // 4)
+    out = be.zeros(NB * QD)
+    for _ in range(2):  # twice: the tickets must return to zero
+        be.ok("decode_attention_fused", Ptr(out), Ptr(be.put(qkv)), Ptr(dcache), Ptr(be.put(cs)), Ptr(dpos), Ptr(scratch), layer, NB, MS, NH, NKV, HD, 0.125)
+        assert oc.rel_err(be.get(out, (NB, NH, HD)), ref) < 1e-5
+    got_cache = be.get(dcache, cache.shape)
+    assert oc.rel_err(got_cache[layer, :, :, pos], full[layer, :, :, pos]) < 1e-6
+    assert np.array_equal(got_cache[layer, :, :, :pos], cache[layer, :, :, :pos]) and not got_cache[0].any()
