@@ -26,7 +26,11 @@ constexpr int A_STAGE_BYTES = BM * BK * 2;      // 16 KB
 constexpr int B_STAGE_BYTES = MAX_BN * BK * 2;  // 32 KB
 constexpr int MN_BOX_BYTES = 64 * BK * 2;       // one 64(mn) x 64(k) box of an MN-major operand
 constexpr int NUM_THREADS = 192;
-constexpr int SMEM_DYN_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 1024;
+// Epilogue staging: each of the 4 epilogue warps owns 32 rows x 128 payload bytes (64 bf16 or 32 fp32 columns) at a
+// 144-byte pitch, which makes both the row-per-thread accesses and the 8-lanes-per-row accesses bank-conflict free.
+constexpr int STG_PITCH = 144;
+constexpr int STG_WARP_BYTES = 32 * STG_PITCH;
+constexpr int SMEM_DYN_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 4 * STG_WARP_BYTES + 1024;
 constexpr uint32_t TMEM_COLS = 512;
 
 struct KArgs {
@@ -200,77 +204,121 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             tc_fence_after_sync();
             const int row = m0 + q * 32 + lane;
             const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)buf * MAX_BN;
-            for (int ch = 0; ch < p.BN / 32; ++ch) {
+            // Accumulator rows live one per thread (TMEM lane = output row), but a warp-wide store of one 16-byte piece per
+            // row would touch 32 different 128-byte lines. So full chunks go through the warp's staging rows and leave (and
+            // the residual arrives) as whole 128-byte row segments, 4 rows per instruction.
+            uint8_t* stg = smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + q * STG_WARP_BYTES;
+            uint8_t* my_row = stg + lane * STG_PITCH;
+            const int sub = lane & 7, rgrp = lane >> 3;
+            const int row_base = m0 + q * 32;
+            const bool c_al = (((uintptr_t)p.C) & 15) == 0;
+            const bool bf16_fast = p.out_mode == GEMM_OUT_BF16 && c_al && (p.ldc % 8) == 0 && (n0 % 8) == 0 &&
+                                   (!p.R || ((((uintptr_t)p.R) & 15) == 0 && (p.ldr % 8) == 0));
+            const bool f32_fast = p.out_mode != GEMM_OUT_BF16 && c_al && (p.ldc % 4) == 0 && (n0 % 4) == 0;
+            for (int c0 = 0; c0 < p.BN;) {
+                const int col0 = n0 + c0;
+                if (col0 >= p.N) break;
+                if (bf16_fast && c0 + 64 <= p.BN && col0 + 64 <= p.N) {
+                    uint32_t ra[32], rb2[32];
+                    tmem_ld_32x32(taddr0 + c0, ra);
+                    tmem_ld_32x32(taddr0 + c0 + 32, rb2);
+                    if (p.R) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int rr = rgrp + 4 * i, grow = row_base + rr;
+                            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                            if (grow < p.M) v = *(const uint4*)(p.R + (size_t)grow * p.ldr + col0 + sub * 8);
+                            *(uint4*)(stg + rr * STG_PITCH + sub * 16) = v;
+                        }
+                        __syncwarp();
+                    }
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int v = 0; v < 8; ++v) {
+                        float f[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v < 4 ? ra[(v & 3) * 8 + i] : rb2[(v & 3) * 8 + i]);
+                        if (p.R) {
+                            const uint4 rv = *(const uint4*)(my_row + v * 16);
+                            const __nv_bfloat162* rb = (const __nv_bfloat162*)&rv;
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const float2 t = __bfloat1622float2(rb[i]);
+                                f[2 * i] += t.x;
+                                f[2 * i + 1] += t.y;
+                            }
+                        }
+                        uint4 o;
+                        __nv_bfloat162* ob = (__nv_bfloat162*)&o;
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) ob[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+                        *(uint4*)(my_row + v * 16) = o;  // a thread reads and rewrites only its own staging row
+                    }
+                    __syncwarp();
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int rr = rgrp + 4 * i, grow = row_base + rr;
+                        if (grow < p.M)
+                            *(uint4*)((__nv_bfloat16*)p.C + (size_t)grow * p.ldc + col0 + sub * 8) = *(const uint4*)(stg + rr * STG_PITCH + sub * 16);
+                    }
+                    __syncwarp();
+                    c0 += 64;
+                    continue;
+                }
+                if (f32_fast && col0 + 32 <= p.N) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(taddr0 + c0, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int v = 0; v < 8; ++v) *(uint4*)(my_row + v * 16) = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
+                    __syncwarp();
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int rr = rgrp + 4 * i, grow = row_base + rr;
+                        if (grow < p.M) {
+                            const uint4 v = *(const uint4*)(stg + rr * STG_PITCH + sub * 16);
+                            float* dst = (float*)p.C + (size_t)grow * p.ldc + col0 + sub * 4;
+                            if (p.out_mode == GEMM_OUT_F32) {
+                                *(uint4*)dst = v;
+                            } else {
+                                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(__uint_as_float(v.x)),
+                                             "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+                                             : "memory");
+                            }
+                        }
+                    }
+                    __syncwarp();
+                    c0 += 32;
+                    continue;
+                }
+                // ragged or unaligned chunk: one row per thread, element by element where needed
                 uint32_t r[32];
-                tmem_ld_32x32(taddr0 + ch * 32, r);
+                tmem_ld_32x32(taddr0 + c0, r);
                 tmem_ld_wait();
-                const int col0 = n0 + ch * 32;
-                if (row < p.M && col0 < p.N) {
+                c0 += 32;
+                if (row < p.M) {
                     const int ncols = min(32, p.N - col0);
                     if (p.out_mode == GEMM_OUT_BF16) {
                         __nv_bfloat16* crow = (__nv_bfloat16*)p.C + (size_t)row * p.ldc + col0;
                         const __nv_bfloat16* rrow = p.R ? p.R + (size_t)row * p.ldr + col0 : nullptr;
-                        const bool vec = (ncols == 32) && ((((uintptr_t)crow) & 15) == 0) &&
-                                         (!rrow || (((uintptr_t)rrow) & 15) == 0);
-                        if (vec) {
 #pragma unroll
-                            for (int v = 0; v < 4; ++v) {
-                                float f[8];
-#pragma unroll
-                                for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(r[v * 8 + i]);
-                                if (rrow) {
-                                    const uint4 rv = *(const uint4*)(rrow + v * 8);
-                                    const __nv_bfloat162* rb = (const __nv_bfloat162*)&rv;
-#pragma unroll
-                                    for (int i = 0; i < 4; ++i) {
-                                        const float2 t = __bfloat1622float2(rb[i]);
-                                        f[2 * i] += t.x;
-                                        f[2 * i + 1] += t.y;
-                                    }
-                                }
-                                uint4 o;
-                                __nv_bfloat162* ob = (__nv_bfloat162*)&o;
-#pragma unroll
-                                for (int i = 0; i < 4; ++i) ob[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
-                                *(uint4*)(crow + v * 8) = o;
-                            }
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) {
-                                if (i < ncols) {
-                                    float f = __uint_as_float(r[i]);
-                                    if (rrow) f += __bfloat162float(rrow[i]);
-                                    crow[i] = __float2bfloat16_rn(f);
-                                }
+                        for (int i = 0; i < 32; ++i) {
+                            if (i < ncols) {
+                                float f = __uint_as_float(r[i]);
+                                if (rrow) f += __bfloat162float(rrow[i]);
+                                crow[i] = __float2bfloat16_rn(f);
                             }
                         }
                     } else if (p.out_mode == GEMM_OUT_F32) {
                         float* crow = (float*)p.C + (size_t)row * p.ldc + col0;
-                        const bool vec = (ncols == 32) && ((((uintptr_t)crow) & 15) == 0);
-                        if (vec) {
 #pragma unroll
-                            for (int v = 0; v < 8; ++v)
-                                *(uint4*)(crow + v * 4) = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 32; ++i)
-                                if (i < ncols) crow[i] = __uint_as_float(r[i]);
-                        }
+                        for (int i = 0; i < 32; ++i)
+                            if (i < ncols) crow[i] = __uint_as_float(r[i]);
                     } else {
                         float* crow = (float*)p.C + (size_t)row * p.ldc + col0;
-                        const bool vec = (ncols == 32) && ((((uintptr_t)crow) & 15) == 0);
-                        if (vec) {
 #pragma unroll
-                            for (int v = 0; v < 8; ++v)
-                                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(crow + v * 4),
-                                             "f"(__uint_as_float(r[v * 4])), "f"(__uint_as_float(r[v * 4 + 1])),
-                                             "f"(__uint_as_float(r[v * 4 + 2])), "f"(__uint_as_float(r[v * 4 + 3]))
-                                             : "memory");
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 32; ++i)
-                                if (i < ncols) atomicAdd(crow + i, __uint_as_float(r[i]));
-                        }
+                        for (int i = 0; i < 32; ++i)
+                            if (i < ncols) atomicAdd(crow + i, __uint_as_float(r[i]));
                     }
                 }
             }

@@ -243,6 +243,59 @@ def run_attention(args):
     return 0
 
 
+def run_gemm(args):
+    """The linear-layer GEMMs of the 360M step (forward, input gradient, weight gradient) in isolation, bf16 operands drawn
+    from N(0,1), 16 x 2048 token rows; one JSON line per shape and kind. --shape picks one (e.g. gate_up)."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from devutil import BMC_BF16, Backend, Ptr
+    lib = bmapi.load_product()
+    be = Backend(lib)
+    lib.bmc_timer_begin.argtypes = [C.c_void_p, C.c_int]
+    lib.bmc_timer_end.argtypes = [C.c_void_p, C.c_int]
+    lib.bmc_timer_end.restype = C.c_float
+    a = bmapi.make_arch(args.model)
+    BT = args.batch * args.seq_len
+    D, H, QD, KV, V = a.dim, a.hidden_dim, a.n_heads * a.head_dim, a.n_kv_heads * a.head_dim, a.vocab_size
+    shapes = [("qkv", D, QD + 2 * KV), ("o", QD, D), ("gate_up", D, 2 * H), ("down", H, D), ("head", D, V)]
+    peaks, src = measured_peaks()
+    rng = np.random.default_rng(3)
+
+    def rand_bf16(n):
+        # a 16 Mi-element random block tiled over the buffer keeps host time small and the values non-trivial
+        blk = rng.standard_normal(min(n, 1 << 24)).astype(np.float32)
+        return be.put(np.resize(blk, n), BMC_BF16)
+    for name, Cc, OC in shapes:
+        if args.shape and args.shape != name:
+            continue
+        inp, w, gout = rand_bf16(BT * Cc), rand_bf16(OC * Cc), rand_bf16(BT * OC)
+        out, ginp, gw = be.zeros(BT * OC, BMC_BF16), be.zeros(BT * Cc, BMC_BF16), be.zeros(OC * Cc)
+        kinds = {
+            "forward": lambda: be.call("matmul_forward", BMC_BF16, Ptr(out), OC, Ptr(inp), Cc, Ptr(w), None, 0, BT, Cc, OC),
+            "input_grad": lambda: be.call("matmul_backward_inp", BMC_BF16, Ptr(ginp), Cc, 0, Ptr(gout), OC, Ptr(w), BT, Cc, OC),
+            "weight_grad": lambda: be.call("matmul_backward_w", BMC_BF16, Ptr(gw), Ptr(gout), OC, Ptr(inp), Cc, BT, Cc, OC),
+        }
+        for kind, fn in kinds.items():
+            for _ in range(max(args.warmup, 1)):
+                assert fn() == 0
+            assert lib.bmc_sync(be.ctx) == 0
+            lib.bmc_timer_begin(be.ctx, 0)
+            for _ in range(max(args.steps, 1)):
+                fn()
+            ms = lib.bmc_timer_end(be.ctx, 0) / max(args.steps, 1)
+            tf = 2.0 * BT * Cc * OC / (ms * 1e-3) / 1e12
+            print(json.dumps({"metric": "gemm_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": 1, "steps": max(args.steps, 1),
+                              "warmup": max(args.warmup, 1), "ms_per_step": ms, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+                              "config": {"workload": f"{name} {kind}: rows {BT}, in {Cc}, out {OC}"},
+                              "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                                           "frac": tf / peaks["bf16_tflops"], "traffic": None, "peak_source": f"bf16_tflops (burst) of {src}"}}),
+                  flush=True)
+        for pbuf in (inp, w, gout, out, ginp, gw):
+            lib.bmc_free(be.ctx, pbuf)
+            be.bufs.remove(pbuf)
+    be.close()
+    return 0
+
+
 def run_decode(args):
     """Q8 inference: prefill 512 uniform-random tokens, then greedy-decode 256, at batch 1 and 64; one JSON line per batch.
     Layer matrices are int8 blocks of 32 with one fp32 scale, the LM head is bf16, activations and the KV cache fp32.
@@ -316,8 +369,9 @@ def main():
     ap.add_argument("--batch", type=int, default=PER_GPU_BATCH)
     ap.add_argument("--seq-len", type=int, default=SEQ_LEN)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="train", choices=["train", "attention", "decode"],
-                    help="train (default, the contract line); attention: isolated GQA flash attention fwd+bwd; decode: Q8 prefill + greedy decode")
+    ap.add_argument("--workload", default="train", choices=["train", "attention", "decode", "gemm"],
+                    help="train (default, the contract line); attention: isolated GQA flash attention fwd+bwd; decode: Q8 prefill + greedy decode; gemm: the linear-layer GEMMs in isolation")
+    ap.add_argument("--shape", default="", help="--workload gemm: qkv, o, gate_up, down or head (default all)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
@@ -325,6 +379,8 @@ def main():
         return run_attention(args)
     if args.workload == "decode":
         return run_decode(args)
+    if args.workload == "gemm":
+        return run_gemm(args)
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
