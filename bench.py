@@ -309,7 +309,7 @@ def run_decode(args):
     bmapi.write_bin_checkpoint(path, a, w)
     del w
     peaks, src = measured_peaks()
-    n_prompt, n_new = 512, 256
+    n_prompt, n_new = args.prompt_tokens, args.decode_tokens
     MS = n_prompt + n_new
     ctx = lib.bm_create(bmapi.BM_DEVICE_METAL)
     model = lib.bm_create_model(ctx, C.byref(a))
@@ -317,7 +317,7 @@ def run_decode(args):
     os.unlink(path)
     assert lib.bmx_model_set_quant(model, 8) == 0
     L, KV, V = a.n_layers, a.n_kv_heads * a.head_dim, a.vocab_size
-    for NB in (1, 64):
+    for NB in [int(v) for v in args.decode_batches.split(",")]:
         sess = lib.bmx_create_session_batched(ctx, model, NB, MS)
         assert sess, "bmx_create_session_batched failed"
         wbytes = lib.bmx_session_weight_bytes(sess)
@@ -371,6 +371,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="train", choices=["train", "attention", "decode", "gemm"],
                     help="train (default, the contract line); attention: isolated GQA flash attention fwd+bwd; decode: Q8 prefill + greedy decode; gemm: the linear-layer GEMMs in isolation")
+    ap.add_argument("--prompt-tokens", type=int, default=512, help="--workload decode: prompt length")
+    ap.add_argument("--decode-tokens", type=int, default=256, help="--workload decode: generated tokens")
+    ap.add_argument("--decode-batches", default="1,64", help="--workload decode: comma-separated sequence counts")
     ap.add_argument("--shape", default="", help="--workload gemm: qkv, o, gate_up, down or head (default all)")
     args = ap.parse_args()
     if args.impl == "reference":
