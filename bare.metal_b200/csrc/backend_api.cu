@@ -7,6 +7,7 @@
 #include <stdlib.h>
 
 #include <map>
+#include <utility>
 #include <mutex>
 #include <vector>
 
@@ -40,6 +41,10 @@ struct bmc_ctx_s {
     size_t gt_used;
     cudaGraph_t graph;
     cudaGraphExec_t graph_exec;
+    // side stream (bmc_side_begin / _end / _wait): work that may overlap the main stream
+    cudaStream_t side_stream;
+    cudaEvent_t side_fork, side_done[16];
+    int side_next, in_side;
 };
 
 namespace {
@@ -155,13 +160,23 @@ bmc_ctx_t* bmc_create(int device_ordinal) {
         cudaEventCreate(&ctx->ev0[i]);
         cudaEventCreate(&ctx->ev1[i]);
     }
+    if (cudaStreamCreateWithFlags(&ctx->side_stream, cudaStreamNonBlocking) != cudaSuccess) { delete ctx; return nullptr; }
+    cudaEventCreateWithFlags(&ctx->side_fork, cudaEventDisableTiming);
+    for (int i = 0; i < 16; ++i) cudaEventCreateWithFlags(&ctx->side_done[i], cudaEventDisableTiming);
+    ctx->side_next = 0;
+    ctx->in_side = 0;
     return ctx;
 }
 
 void bmc_destroy(bmc_ctx_t* ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
+    if (ctx->in_side) std::swap(ctx->stream, ctx->side_stream);
+    cudaStreamSynchronize(ctx->side_stream);
     cudaStreamSynchronize(ctx->stream);
+    cudaStreamDestroy(ctx->side_stream);
+    cudaEventDestroy(ctx->side_fork);
+    for (int i = 0; i < 16; ++i) cudaEventDestroy(ctx->side_done[i]);
     for (auto& kv : ctx->allocs) cudaFree(kv.first);
     if (ctx->rms_scratch) cudaFree(ctx->rms_scratch);
     if (ctx->attn_scratch) cudaFree(ctx->attn_scratch);
@@ -238,7 +253,8 @@ int bmc_status(bmc_ctx_t* ctx) {
 }
 int bmc_sync(bmc_ctx_t* ctx) {
     BMC_CHECK_CTX(ctx);
-    cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    cudaError_t e = cudaStreamSynchronize(ctx->side_stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
     if (e != cudaSuccess) {
         ctx->sticky_status = -200 - (int)e;
         return ctx->sticky_status;
@@ -246,6 +262,33 @@ int bmc_sync(bmc_ctx_t* ctx) {
     return bmc_status(ctx);
 }
 void* bmc_stream(bmc_ctx_t* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
+// Side stream: everything enqueued between bmc_side_begin and bmc_side_end runs on a second stream, ordered after all work
+// enqueued on the main stream so far, and may overlap what the main stream does next. bmc_side_end returns a ticket;
+// bmc_side_wait(ticket) orders later main-stream work after the side work up to that ticket. Host calls are single-threaded.
+int bmc_side_begin(bmc_ctx_t* ctx) {
+    BMC_CHECK_CTX(ctx);
+    if (ctx->in_side) return -1;
+    if (cudaEventRecord(ctx->side_fork, ctx->stream) != cudaSuccess) return -2;
+    if (cudaStreamWaitEvent(ctx->side_stream, ctx->side_fork, 0) != cudaSuccess) return -2;
+    std::swap(ctx->stream, ctx->side_stream);
+    ctx->in_side = 1;
+    return 0;
+}
+int bmc_side_end(bmc_ctx_t* ctx) {
+    BMC_CHECK_CTX(ctx);
+    if (!ctx->in_side) return -1;
+    const int ticket = ctx->side_next;
+    ctx->side_next = (ctx->side_next + 1) % 16;
+    const cudaError_t e = cudaEventRecord(ctx->side_done[ticket], ctx->stream);
+    std::swap(ctx->stream, ctx->side_stream);
+    ctx->in_side = 0;
+    return e == cudaSuccess ? ticket : -2;
+}
+int bmc_side_wait(bmc_ctx_t* ctx, int ticket) {
+    BMC_CHECK_CTX(ctx);
+    if (ticket < 0 || ticket >= 16 || ctx->in_side) return -1;
+    return cudaStreamWaitEvent(ctx->stream, ctx->side_done[ticket], 0) == cudaSuccess ? 0 : -2;
+}
 long bmc_launch_count(bmc_ctx_t* ctx) { return ctx ? ctx->launches : 0; }
 void* bmc_host_alloc(size_t bytes) {
     void* p = nullptr;

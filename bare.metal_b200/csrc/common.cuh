@@ -19,6 +19,12 @@ template <> struct Vec<float> {
     __device__ __forceinline__ static void store(float* p, const float (&f)[4]) {
         *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
     }
+    // the 16 bytes as loaded, for kernels that keep several vectors in flight and widen them only when used
+    using Raw = uint4;
+    __device__ __forceinline__ static Raw load_raw(const float* p) { return *reinterpret_cast<const uint4*>(p); }
+    __device__ __forceinline__ static void unpack(const Raw& v, float (&f)[4]) {
+        f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y); f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
+    }
 };
 template <> struct Vec<bf16> {
     static constexpr int N = 8;
@@ -38,6 +44,14 @@ template <> struct Vec<bf16> {
 #pragma unroll
         for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
         *reinterpret_cast<uint4*>(p) = v;
+    }
+    using Raw = uint4;
+    __device__ __forceinline__ static Raw load_raw(const bf16* p) { return *reinterpret_cast<const uint4*>(p); }
+    __device__ __forceinline__ static void unpack(const Raw& v, float (&f)[8]) {
+        f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xffff0000u);
+        f[2] = __uint_as_float(v.y << 16); f[3] = __uint_as_float(v.y & 0xffff0000u);
+        f[4] = __uint_as_float(v.z << 16); f[5] = __uint_as_float(v.z & 0xffff0000u);
+        f[6] = __uint_as_float(v.w << 16); f[7] = __uint_as_float(v.w & 0xffff0000u);
     }
 };
 

@@ -64,10 +64,49 @@ int embedding_backward_bf16(float* gwte, const bf16* gout, const int* tokens, in
 
 // ------------------------------------------------------------------------------------------------
 // RMSNorm forward: out = x * rsqrt(mean(x^2) + eps) * w (reference: rmsnorm_forward, src/kernels/forward.metal:993).
-// One warp per row; the second sweep over the row is served by L1.
-template <typename T>
+// One warp per row; the row stays in registers between the sum of squares and the scaling (NV 16-byte vectors per lane),
+// so it is read from memory once. Rows wider than 8 vectors per lane take the two-sweep form.
+template <typename T, int NV>
 __global__ void rmsnorm_forward_kernel(T* __restrict__ out, float* __restrict__ rstd, const T* __restrict__ x,
                                        const float* __restrict__ w, int N, int C, float eps) {
+    constexpr int V = Vec<T>::N;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * WARPS_PER_BLOCK + warp;
+    if (row >= N) return;
+    const T* xr = x + (size_t)row * C;
+    T* orow = out + (size_t)row * C;
+    const int nvec = C / V;
+    float f[NV][V];
+    float ss = 0.f;
+#pragma unroll
+    for (int a = 0; a < NV; ++a) {
+        const int v = lane + a * 32;
+        if (v < nvec) Vec<T>::load(xr + v * V, f[a]);
+    }
+#pragma unroll
+    for (int a = 0; a < NV; ++a) {
+        const int v = lane + a * 32;
+        if (v < nvec)
+#pragma unroll
+            for (int i = 0; i < V; ++i) ss += f[a][i] * f[a][i];
+    }
+    ss = warp_sum(ss) / (float)C;
+    const float r = 1.0f / sqrtf(ss + eps);
+    if (lane == 0 && rstd) rstd[row] = r;
+#pragma unroll
+    for (int a = 0; a < NV; ++a) {
+        const int v = lane + a * 32;
+        if (v < nvec) {
+            float o[V];
+#pragma unroll
+            for (int i = 0; i < V; ++i) o[i] = f[a][i] * r * w[v * V + i];
+            Vec<T>::store(orow + v * V, o);
+        }
+    }
+}
+template <typename T>
+__global__ void rmsnorm_forward_wide_kernel(T* __restrict__ out, float* __restrict__ rstd, const T* __restrict__ x,
+                                            const float* __restrict__ w, int N, int C, float eps) {
     constexpr int V = Vec<T>::N;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = blockIdx.x * WARPS_PER_BLOCK + warp;
@@ -95,7 +134,13 @@ __global__ void rmsnorm_forward_kernel(T* __restrict__ out, float* __restrict__ 
 }
 template <typename T> int rmsnorm_forward(T* out, float* rstd, const T* x, const float* w, int N, int C, float eps, cudaStream_t st) {
     if (C % Vec<T>::N) return -1;
-    rmsnorm_forward_kernel<T><<<ceil_div(N, WARPS_PER_BLOCK), BLOCK, 0, st>>>(out, rstd, x, w, N, C, eps);
+    const int nv = ceil_div(C / Vec<T>::N, 32);
+    const int grid = ceil_div(N, WARPS_PER_BLOCK);
+    if (nv <= 1) rmsnorm_forward_kernel<T, 1><<<grid, BLOCK, 0, st>>>(out, rstd, x, w, N, C, eps);
+    else if (nv <= 2) rmsnorm_forward_kernel<T, 2><<<grid, BLOCK, 0, st>>>(out, rstd, x, w, N, C, eps);
+    else if (nv <= 4) rmsnorm_forward_kernel<T, 4><<<grid, BLOCK, 0, st>>>(out, rstd, x, w, N, C, eps);
+    else if (nv <= 8) rmsnorm_forward_kernel<T, 8><<<grid, BLOCK, 0, st>>>(out, rstd, x, w, N, C, eps);
+    else rmsnorm_forward_wide_kernel<T><<<grid, BLOCK, 0, st>>>(out, rstd, x, w, N, C, eps);
     return 0;
 }
 template int rmsnorm_forward<float>(float*, float*, const float*, const float*, int, int, float, cudaStream_t);
@@ -129,20 +174,30 @@ __global__ void rmsnorm_backward_kernel(T* __restrict__ gx, float* __restrict__ 
         T* gxr = gx + (size_t)row * C;
         const float r = rstd[row];
         const bool in_w = row >= w_row0 && row < w_row1;
-        float xs[NV][V], gs[NV][V];
+        typename Vec<T>::Raw xraw[NV], graw[NV], oraw[NV];
         float c1 = 0.f;
+        // all three operand streams of the row are requested before anything is consumed; they stay packed until used
 #pragma unroll
         for (int a = 0; a < NV; ++a) {
             const int v = lane + a * 32;
             if (v < nvec) {
-                Vec<T>::load(xr + v * V, xs[a]);
-                Vec<T>::load(gr + v * V, gs[a]);
+                xraw[a] = Vec<T>::load_raw(xr + v * V);
+                graw[a] = Vec<T>::load_raw(gr + v * V);
+                oraw[a] = Vec<T>::load_raw(gxr + v * V);
+            }
+        }
+#pragma unroll
+        for (int a = 0; a < NV; ++a) {
+            const int v = lane + a * 32;
+            if (v < nvec) {
+                float xs[V], gs[V];
+                Vec<T>::unpack(xraw[a], xs);
+                Vec<T>::unpack(graw[a], gs);
 #pragma unroll
                 for (int i = 0; i < V; ++i) {
-                    const float n = xs[a][i] * r;
-                    if (in_w) gw_acc[a][i] += gs[a][i] * n;
-                    gs[a][i] *= w[v * V + i];
-                    c1 += gs[a][i] * n;
+                    const float n = xs[i] * r;
+                    if (in_w) gw_acc[a][i] += gs[i] * n;
+                    c1 += gs[i] * w[v * V + i] * n;
                 }
             }
         }
@@ -151,11 +206,13 @@ __global__ void rmsnorm_backward_kernel(T* __restrict__ gx, float* __restrict__ 
         for (int a = 0; a < NV; ++a) {
             const int v = lane + a * 32;
             if (v < nvec) {
-                float o[V];
-                Vec<T>::load(gxr + v * V, o);
+                float xs[V], gs[V], os[V];
+                Vec<T>::unpack(xraw[a], xs);
+                Vec<T>::unpack(graw[a], gs);
+                Vec<T>::unpack(oraw[a], os);
 #pragma unroll
-                for (int i = 0; i < V; ++i) o[i] += r * (gs[a][i] - xs[a][i] * r * c1);
-                Vec<T>::store(gxr + v * V, o);
+                for (int i = 0; i < V; ++i) os[i] += r * (gs[i] * w[v * V + i] - xs[i] * r * c1);
+                Vec<T>::store(gxr + v * V, os);
             }
         }
     }

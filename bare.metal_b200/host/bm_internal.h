@@ -61,6 +61,7 @@ struct bm_trainer_s {
     bm_train_config_t cfg;
     int S, B_cap, dtype, esize;
     /* reference-compatibility switches (all off by default; see bmx_trainer_set_option) */
+    int side_stream;          /* weight-gradient GEMMs on the backend's side stream (default on; env BM_NO_SIDE_STREAM) */
     int ref_norm_grad;        /* RMSNorm weight gradient = last sequence of the batch only */
     int ref_input_grad_carry; /* embedding scatter of sequence b uses the running sum of input gradients */
     float* d_gx_carry;        /* [S, D] running sum for the switch above */

@@ -198,6 +198,7 @@ bm_trainer_t* bm_create_trainer(bm_context_t* ctx, bm_model_t* model, const bm_t
         bm_destroy_trainer(t);
         return NULL;
     }
+    t->side_stream = getenv("BM_NO_SIDE_STREAM") ? 0 : 1;
     const char* rq = getenv("BM_REF_QUIRKS");
     if (rq && rq[0] == '1') bmx_trainer_set_option(t, "ref_quirks", 1);
     BM_LOG_INFO("Trainer created: %d weight tensors, S=%d, D=%d", t->n_params, t->S, a->dim);
@@ -280,9 +281,17 @@ static int backward(bm_trainer_t* t, int B, const uint8_t* d_attn_mask) {
     const int nw_acc = t->ref_norm_grad ? 0 : 1;
     const int nw_r0 = t->ref_norm_grad ? (B - 1) * S : 0, nw_r1 = M;
 
+    /* Weight-gradient GEMMs go to the context's side stream: each is enqueued right after the input-gradient GEMM that shares
+     * its operand, so it runs while the main stream executes the memory-bound kernel that follows (SwiGLU / RMSNorm backward,
+     * attention helpers). A ticket is waited for before a buffer the side GEMM reads is overwritten. */
+    const int side = t->side_stream;
+    int tk_head = -1, tk_down = -1, tk_gu = -1, tk_o = -1, tk_q = -1;
+#define SIDE_WGRAD(ticket, call) do { if (side) { TRY(bmc_side_begin(be)); } TRY(call); if (side) { (ticket) = bmc_side_end(be); if ((ticket) < 0) return -1; } } while (0)
+#define SIDE_WAIT(ticket) do { if (side && (ticket) >= 0) { TRY(bmc_side_wait(be, (ticket))); (ticket) = -1; } } while (0)
+
     /* LM head: logits buffer now holds dL/dlogits */
-    TRY(bmc_matmul_backward_w(be, dt, gptr(t, p_emb), t->logits, V, t->nf, D, M, D, V));
     TRY(bmc_matmul_backward_inp(be, dt, t->dn, D, 0, t->logits, V, wptr(t, p_emb), M, D, V));
+    SIDE_WGRAD(tk_head, bmc_matmul_backward_w(be, dt, gptr(t, p_emb), t->logits, V, t->nf, D, M, D, V));
     TRY(bmc_memset(be, t->dres, 0, (size_t)M * D * esz(t)));
     TRY(bmc_rmsnorm_backward(be, dt, t->dres, gptr(t, p_lnf), nw_acc, t->dn, t->x_last, wf32(t, p_lnf), t->rstdf, M, D, nw_r0, nw_r1));
     if (t->dp) TRY(bm_dp_bucket_ready(t->dp, L));
@@ -291,24 +300,38 @@ static int backward(bm_trainer_t* t, int B, const uint8_t* d_attn_mask) {
         bm_layer_act_t* c = &t->act[l];
         const int pb = 9 * l;
         /* MLP: dres is dL/d(x_{l+1}); the residual add routes it unchanged to both of its inputs */
-        TRY(bmc_matmul_backward_w(be, dt, gptr(t, pb + P_DOWN), t->dres, D, c->act, H, M, H, D));
         TRY(bmc_matmul_backward_inp(be, dt, t->dact, H, 0, t->dres, D, wptr(t, pb + P_DOWN), M, H, D));
+        SIDE_WGRAD(tk_down, bmc_matmul_backward_w(be, dt, gptr(t, pb + P_DOWN), t->dres, D, c->act, H, M, H, D));
+        SIDE_WAIT(tk_gu); /* the previous layer's gate/up weight gradient still reads dgu */
         TRY(bmc_swiglu_backward(be, dt, t->dgu, at(t->dgu, H, t), 2 * H, c->gu, at(c->gu, H, t), 2 * H, t->dact, H, M, H));
-        TRY(bmc_matmul_backward_w(be, dt, gptr(t, pb + P_GATE), t->dgu, 2 * H, c->n2, D, M, D, 2 * H));
         TRY(bmc_matmul_backward_inp(be, dt, t->dn, D, 0, t->dgu, 2 * H, wptr(t, pb + P_GATE), M, D, 2 * H));
+        SIDE_WGRAD(tk_gu, bmc_matmul_backward_w(be, dt, gptr(t, pb + P_GATE), t->dgu, 2 * H, c->n2, D, M, D, 2 * H));
+        SIDE_WAIT(tk_down); /* reads dres, which the norm backward accumulates into */
         TRY(bmc_rmsnorm_backward(be, dt, t->dres, gptr(t, pb + P_LN2), nw_acc, t->dn, c->x1, wf32(t, pb + P_LN2), c->rstd2, M, D, nw_r0, nw_r1));
         /* attention block: dres is now dL/d(x1) */
-        TRY(bmc_matmul_backward_w(be, dt, gptr(t, pb + P_O), t->dres, D, c->attn, QD, M, QD, D));
         TRY(bmc_matmul_backward_inp(be, dt, t->dattn, QD, 0, t->dres, D, wptr(t, pb + P_O), M, QD, D));
+        SIDE_WGRAD(tk_o, bmc_matmul_backward_w(be, dt, gptr(t, pb + P_O), t->dres, D, c->attn, QD, M, QD, D));
+        SIDE_WAIT(tk_q); /* the previous layer's QKV weight gradient still reads dqkv */
         TRY(bmc_attention_backward(be, dt, t->dqkv, QKVD, at(t->dqkv, QD, t), at(t->dqkv, QD + KV, t), QKVD, t->dattn, QD, c->attn,
                                    c->lse, c->qkv, QKVD, at(c->qkv, QD, t), at(c->qkv, QD + KV, t), QKVD, d_attn_mask, B, S, NH, NKV,
                                    HD, scale));
         TRY(bmc_rope(be, dt, t->dqkv, QKVD, at(t->dqkv, QD, t), QKVD, t->d_rope_cs, M, S, NH, NKV, HD, -1));
-        TRY(bmc_matmul_backward_w(be, dt, gptr(t, pb + P_Q), t->dqkv, QKVD, c->n1, D, M, D, QKVD));
         TRY(bmc_matmul_backward_inp(be, dt, t->dn, D, 0, t->dqkv, QKVD, wptr(t, pb + P_Q), M, D, QKVD));
+        SIDE_WGRAD(tk_q, bmc_matmul_backward_w(be, dt, gptr(t, pb + P_Q), t->dqkv, QKVD, c->n1, D, M, D, QKVD));
+        SIDE_WAIT(tk_o);
         TRY(bmc_rmsnorm_backward(be, dt, t->dres, gptr(t, pb + P_LN1), nw_acc, t->dn, c->x, wf32(t, pb + P_LN1), c->rstd1, M, D, nw_r0, nw_r1));
-        if (t->dp) TRY(bm_dp_bucket_ready(t->dp, l));
+        if (t->dp) {
+            /* a gradient bucket may close here: every weight gradient of this layer must be behind the main stream */
+            SIDE_WAIT(tk_gu);
+            SIDE_WAIT(tk_q);
+            TRY(bm_dp_bucket_ready(t->dp, l));
+        }
     }
+    SIDE_WAIT(tk_gu);
+    SIDE_WAIT(tk_q);
+    SIDE_WAIT(tk_head); /* the embedding scatter adds into the buffer the LM-head weight gradient accumulated into */
+#undef SIDE_WGRAD
+#undef SIDE_WAIT
     /* tied embedding: scatter dL/dx_0 on top of the LM-head wgrad already in the same buffer
      * (embed_backward, src/baremetal/trainer.c:302-346) */
     if (t->ref_input_grad_carry) TRY(bmc_seq_prefix_accumulate(be, dt, t->dres, t->d_gx_carry, B, (size_t)S * D));
@@ -554,6 +577,7 @@ int bmx_trainer_set_option(bm_trainer_t* t, const char* key, int value) {
     bmc_ctx_t* be = t->ctx->be;
     const int all = strcmp(key, "ref_quirks") == 0;
     int known = 0;
+    if (strcmp(key, "side_stream") == 0) { t->side_stream = value ? 1 : 0; return 0; }
     if (all || strcmp(key, "ref_norm_grad") == 0) { t->ref_norm_grad = value ? 1 : 0; known = 1; }
     if (all || strcmp(key, "ref_input_grad_carry") == 0) {
         known = 1;

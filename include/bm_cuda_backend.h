@@ -42,6 +42,14 @@ size_t     bmc_peak_allocated_bytes(bmc_ctx_t* ctx);          /* backend_get_pea
 int        bmc_upload(bmc_ctx_t* ctx, void* d_dst, const void* h_src, size_t bytes);    /* async H2D on the compute stream */
 int        bmc_download(bmc_ctx_t* ctx, void* h_dst, const void* d_src, size_t bytes);  /* D2H, returns after the copy */
 int        bmc_memset(bmc_ctx_t* ctx, void* d_ptr, int byte_value, size_t bytes);
+/* Second stream of the context. Calls between bmc_side_begin and bmc_side_end are enqueued on it, ordered after everything the main
+ * stream holds at bmc_side_begin, and may run concurrently with later main-stream work (the trainer puts weight-gradient GEMMs there
+ * so that they overlap the memory-bound kernels of the backward chain). bmc_side_end returns a ticket (0..15, reused round-robin: at
+ * most 16 may be outstanding) or a negative code; bmc_side_wait makes later main-stream work wait for the side work up to the ticket.
+ * bmc_sync waits for both streams. No reference counterpart: the reference encodes one command buffer at a time. */
+int        bmc_side_begin(bmc_ctx_t* ctx);
+int        bmc_side_end(bmc_ctx_t* ctx);
+int        bmc_side_wait(bmc_ctx_t* ctx, int ticket);
 int        bmc_copy(bmc_ctx_t* ctx, void* d_dst, const void* d_src, size_t bytes);
 int        bmc_sync(bmc_ctx_t* ctx);                          /* waits for the compute stream; returns bmc_status() */
 /* Non-zero when a kernel reported a failed bounded wait or a CUDA call failed since the last call. */
