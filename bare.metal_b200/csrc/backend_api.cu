@@ -373,12 +373,9 @@ int bmc_matmul_backward_w(bmc_ctx_t* ctx, int dtype, float* d_gw, const void* d_
     if (dtype == BMC_F32)
         return note(ctx, gemm_f32_simt(d_gw, C, 1, (const float*)d_gout, 1, ldgo, (const float*)d_inp, 1, ldi, nullptr, 0, OC, C, BT,
                                        ctx->stream));
-    // gw[OC, C] += gout^T[OC, BT] x inp[BT, C]: both operands MN-major, reduction over the tokens, split so
-    // that about two waves of CTAs exist even when OC x C is only a few dozen tiles.
-    const int tiles = ((OC + 127) / 128) * ((C + 191) / 192);
-    int splits = tiles >= 2 * ctx->num_sms ? 1 : (2 * ctx->num_sms + tiles - 1) / tiles;
-    const int kb_total = (BT + 63) / 64;
-    if (splits > kb_total / 4) splits = kb_total / 4 > 0 ? kb_total / 4 : 1;
+    // gw[OC, C] += gout^T[OC, BT] x inp[BT, C]: both operands MN-major, reduction over the tokens, split (by the GEMM) so that
+    // whole waves of work units exist even when OC x C is only a few dozen tiles.
+    const int splits = 0;
     GemmProblem g{OC, C, BT, (const bf16*)d_gout, ldgo, 1, (const bf16*)d_inp, ldi, 1, d_gw, C, GEMM_OUT_F32_ATOMIC, nullptr, 0, splits, 0};
     return note(ctx, run_umma(ctx, g));
 }

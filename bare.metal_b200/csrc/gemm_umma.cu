@@ -9,6 +9,7 @@
 
 #include <cuda.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include <atomic>
 
@@ -20,10 +21,12 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 64;
-constexpr int STAGES = 4;
+constexpr int STAGES = 4;         // one CTA per tile: 4 x (16 KB of A + 32 KB of B)
+constexpr int STAGES_PAIR = 6;    // CTA pair per tile: 6 x (16 KB of A + 16 KB = this CTA's half of B)
 constexpr int MAX_BN = 256;
 constexpr int A_STAGE_BYTES = BM * BK * 2;      // 16 KB
 constexpr int B_STAGE_BYTES = MAX_BN * BK * 2;  // 32 KB
+constexpr int B_HALF_STAGE_BYTES = B_STAGE_BYTES / 2;
 constexpr int MN_BOX_BYTES = 64 * BK * 2;       // one 64(mn) x 64(k) box of an MN-major operand
 constexpr int NUM_THREADS = 192;
 // Epilogue staging: each of the 4 epilogue warps owns 32 rows x 128 payload bytes (64 bf16 or 32 fp32 columns) at a
@@ -38,6 +41,7 @@ struct KArgs {
     int BN;
     int a_mn, b_mn;
     int tiles_m, tiles_n, splits, kb_total, kb_per_split;
+    int tile_rows;  // rows of C per work unit: 128, or 256 when a CTA pair shares the unit
     void* C;
     int ldc;
     int out_mode;
@@ -47,8 +51,8 @@ struct KArgs {
 };
 
 struct __align__(8) Barriers {
-    uint64_t full[STAGES];
-    uint64_t empty[STAGES];
+    uint64_t full[STAGES_PAIR];
+    uint64_t empty[STAGES_PAIR];
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
     uint32_t tmem_base;
@@ -61,12 +65,17 @@ __device__ __forceinline__ void decode_unit(const KArgs& p, int u, int& m0, int&
     const int tile = u - split * ntiles;
     const int tm = tile / p.tiles_n;
     const int tn = tile - tm * p.tiles_n;
-    m0 = tm * BM;
+    m0 = tm * p.tile_rows;
     n0 = tn * p.BN;
     kb0 = split * p.kb_per_split;
     kb1 = min(p.kb_total, kb0 + p.kb_per_split);
 }
 
+// CTAS = 1: one CTA computes a 128 x BN tile. CTAS = 2: the kernel is launched in clusters of two CTAs on neighbouring SMs; the
+// pair computes a 256 x BN tile with tcgen05.mma.cta_group::2 — each CTA holds its 128 rows of A and HALF of the B tile, the
+// leader (cluster rank 0) issues the UMMAs, each CTA's TMEM receives its 128 rows of the accumulator and each CTA runs its own
+// epilogue. B is read from shared memory once per pair instead of once per CTA.
+template <int CTAS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       const KArgs p) {
@@ -75,32 +84,38 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 
     // 1024-byte alignment: the 128B swizzle pattern is a function of address bits [7,10).
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    constexpr int NST = CTAS == 2 ? STAGES_PAIR : STAGES;
+    constexpr int BST = CTAS == 2 ? B_HALF_STAGE_BYTES : B_STAGE_BYTES;
     uint8_t* sA = smem;
-    uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
+    uint8_t* sB = smem + NST * A_STAGE_BYTES;
+    const uint32_t rank = CTAS == 2 ? cluster_ctarank() : 0u;   // 0 = leader of the pair
+    const int worker = CTAS == 2 ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int nworkers = CTAS == 2 ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int units = p.tiles_m * p.tiles_n * p.splits;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(&bars.full[s], 1);
+        for (int s = 0; s < NST; ++s) {
+            mbar_init(&bars.full[s], 1);   // pair: only the leader's is used; both CTAs' copies count bytes on it
             mbar_init(&bars.empty[s], 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&bars.acc_full[b], 1);
-            mbar_init(&bars.acc_empty[b], 4);
+            mbar_init(&bars.acc_empty[b], 4 * CTAS);  // pair: the leader's collects the epilogue warps of both CTAs
         }
         bars.abort_flag = 0;
         mbar_fence_init();
         fence_proxy_async_smem();
     }
     if (warp == 1) {
-        tmem_alloc(&bars.tmem_base, TMEM_COLS);
-        tmem_relinquish();
+        if (CTAS == 2) { tmem_alloc_pair(&bars.tmem_base, TMEM_COLS); tmem_relinquish_pair(); }
+        else { tmem_alloc(&bars.tmem_base, TMEM_COLS); tmem_relinquish(); }
     }
     tc_fence_before_sync();
     __syncthreads();
+    if (CTAS == 2) cluster_sync_all();  // the peer's barriers exist before anything is signalled across the pair
     tc_fence_after_sync();
     // Launched with programmatic stream serialisation, the set-up above overlaps the tail of the preceding kernel; nothing
     // before this point touches global memory. Without the launch attribute both instructions are no-ops.
@@ -109,7 +124,9 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     const uint32_t tmem_base = bars.tmem_base;
     volatile int* abort_flag = &bars.abort_flag;
 
-    const uint32_t stage_tx_bytes = (uint32_t)(BM * BK * 2 + p.BN * BK * 2);
+    // bytes one stage receives: this CTA's A tile and B tile — for a pair, both CTAs' (A tile + half B tile) on the leader's barrier
+    const uint32_t stage_tx_bytes = CTAS == 2 ? (uint32_t)(2 * (BM * BK * 2 + (p.BN / 2) * BK * 2)) : (uint32_t)(BM * BK * 2 + p.BN * BK * 2);
+    const int bn_local = CTAS == 2 ? p.BN / 2 : p.BN;  // B rows held by this CTA
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
@@ -118,17 +135,36 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             tma_prefetch_desc(&tmB);
             uint32_t c = 0;  // k-block counter across all of this CTA's units
             bool ok = true;
-            for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+            for (int u = worker; u < units && ok; u += nworkers) {
                 int m0, n0, kb0, kb1;
                 decode_unit(p, u, m0, n0, kb0, kb1);
+                m0 += (int)rank * BM;        // this CTA's rows of the tile
+                n0 += (int)rank * bn_local;  // this CTA's part of the B tile
                 for (int kb = kb0; kb < kb1; ++kb, ++c) {
-                    const int s = c % STAGES;
-                    const uint32_t ph = (c / STAGES) & 1;
+                    const int s = c % NST;
+                    const uint32_t ph = (c / NST) & 1;
                     if (!mbar_wait(&bars.empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
-                    mbar_expect_tx(&bars.full[s], stage_tx_bytes);
                     uint8_t* a_dst = sA + s * A_STAGE_BYTES;
-                    uint8_t* b_dst = sB + s * B_STAGE_BYTES;
+                    uint8_t* b_dst = sB + s * BST;
                     const int k0 = kb * BK;
+                    if (CTAS == 2) {
+                        const uint32_t full_leader = mapa_shared(&bars.full[s], 0);
+                        if (rank == 0) mbar_expect_tx(&bars.full[s], stage_tx_bytes);
+                        if (!p.a_mn) {
+                            tma_load_2d_pair(a_dst, &tmA, full_leader, k0, m0);
+                        } else {
+                            tma_load_2d_pair(a_dst, &tmA, full_leader, m0, k0);
+                            tma_load_2d_pair(a_dst + MN_BOX_BYTES, &tmA, full_leader, m0 + 64, k0);
+                        }
+                        if (!p.b_mn) {
+                            tma_load_2d_pair(b_dst, &tmB, full_leader, k0, n0);
+                        } else {
+                            for (int j = 0; j < bn_local / 64; ++j)
+                                tma_load_2d_pair(b_dst + j * MN_BOX_BYTES, &tmB, full_leader, n0 + 64 * j, k0);
+                        }
+                        continue;
+                    }
+                    mbar_expect_tx(&bars.full[s], stage_tx_bytes);
                     if (!p.a_mn) {
                         tma_load_2d(a_dst, &tmA, &bars.full[s], k0, m0);
                     } else {
@@ -144,16 +180,16 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                 }
             }
             // Tail: do not let the CTA retire while UMMA commits may still arrive on `empty`.
-            for (int i = 0; i < STAGES && ok; ++i, ++c) {
-                const int s = c % STAGES;
-                const uint32_t ph = (c / STAGES) & 1;
+            for (int i = 0; i < NST && ok; ++i, ++c) {
+                const int s = c % NST;
+                const uint32_t ph = (c / NST) & 1;
                 if (!mbar_wait(&bars.empty[s], ph ^ 1, abort_flag)) ok = false;
             }
         }
     } else if (warp == 1) {
         // ------------------------------ UMMA issuer --------------------------------
-        if (lane == 0) {
-            const uint32_t idesc = umma_idesc_bf16_f32(BM, p.BN, p.a_mn, p.b_mn);
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = umma_idesc_bf16_f32(BM * CTAS, p.BN, p.a_mn, p.b_mn);
             // K-major operand: rows of 128 B, 8-row swizzle atoms 1024 B apart; one UMMA (K=16) = 32 B along the row.
             // MN-major operand: 64(mn) x 64(k) boxes of 8 KB; 8-deep k groups 1024 B apart inside a box,
             // 64-wide mn groups one box apart; one UMMA (K=16) = two k groups = 2048 B.
@@ -162,7 +198,7 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             uint32_t c = 0;
             int it = 0;
             bool ok = true;
-            for (int u = blockIdx.x; u < units && ok; u += gridDim.x, ++it) {
+            for (int u = worker; u < units && ok; u += nworkers, ++it) {
                 int m0, n0, kb0, kb1;
                 decode_unit(p, u, m0, n0, kb0, kb1);
                 const int buf = it & 1;
@@ -171,21 +207,27 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                 tc_fence_after_sync();
                 const uint32_t tmem_acc = tmem_base + (uint32_t)buf * MAX_BN;
                 for (int kb = kb0; kb < kb1; ++kb, ++c) {
-                    const int s = c % STAGES;
-                    const uint32_t ph = (c / STAGES) & 1;
+                    const int s = c % NST;
+                    const uint32_t ph = (c / NST) & 1;
                     if (!mbar_wait(&bars.full[s], ph, abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
                     const uint32_t a_addr = smem_u32(sA + s * A_STAGE_BYTES);
-                    const uint32_t b_addr = smem_u32(sB + s * B_STAGE_BYTES);
+                    const uint32_t b_addr = smem_u32(sB + s * BST);
 #pragma unroll
                     for (int k = 0; k < BK / 16; ++k) {
                         const uint64_t ad = umma_smem_desc_sw128(a_addr + k * a_kstep, a_lbo, a_sbo);
                         const uint64_t bd = umma_smem_desc_sw128(b_addr + k * b_kstep, b_lbo, b_sbo);
-                        umma_bf16_ss(tmem_acc, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                        if (CTAS == 2) umma_bf16_ss_pair(tmem_acc, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                        else umma_bf16_ss(tmem_acc, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
                     }
-                    umma_commit(&bars.empty[s]);  // releases the stage once these UMMAs have read it
+                    // releases the stage (in both CTAs of a pair) once these UMMAs have read it
+                    if (CTAS == 2) umma_commit_pair(&bars.empty[s], 3);
+                    else umma_commit(&bars.empty[s]);
                 }
-                if (ok) umma_commit(&bars.acc_full[buf]);
+                if (ok) {
+                    if (CTAS == 2) umma_commit_pair(&bars.acc_full[buf], 3);
+                    else umma_commit(&bars.acc_full[buf]);
+                }
             }
         }
     } else {
@@ -193,9 +235,10 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         const int q = warp & 3;
         int it = 0;
         bool ok = true;
-        for (int u = blockIdx.x; u < units && ok; u += gridDim.x, ++it) {
+        for (int u = worker; u < units && ok; u += nworkers, ++it) {
             int m0, n0, kb0, kb1;
             decode_unit(p, u, m0, n0, kb0, kb1);
+            m0 += (int)rank * BM;
             const int buf = it & 1;
             const uint32_t acc_ph = (it >> 1) & 1;
             ok = mbar_wait(&bars.acc_full[buf], acc_ph, abort_flag);
@@ -207,7 +250,7 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             // Accumulator rows live one per thread (TMEM lane = output row), but a warp-wide store of one 16-byte piece per
             // row would touch 32 different 128-byte lines. So full chunks go through the warp's staging rows and leave (and
             // the residual arrives) as whole 128-byte row segments, 4 rows per instruction.
-            uint8_t* stg = smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + q * STG_WARP_BYTES;
+            uint8_t* stg = smem + NST * (A_STAGE_BYTES + BST) + q * STG_WARP_BYTES;
             uint8_t* my_row = stg + lane * STG_PITCH;
             const int sub = lane & 7, rgrp = lane >> 3;
             const int row_base = m0 + q * 32;
@@ -324,7 +367,10 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             }
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bars.acc_empty[buf]);
+            if (lane == 0) {
+                if (CTAS == 2 && rank != 0) mbar_arrive_cluster(mapa_shared(&bars.acc_empty[buf], 0));
+                else mbar_arrive(&bars.acc_empty[buf]);
+            }
         }
     }
 
@@ -339,8 +385,12 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     }
     tc_fence_before_sync();
     __syncthreads();
+    if (CTAS == 2) cluster_sync_all();  // no signal of the peer may still be on its way to this CTA's barriers
     tc_fence_after_sync();
-    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+    if (warp == 1) {
+        if (CTAS == 2) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+        else tmem_dealloc(tmem_base, TMEM_COLS);
+    }
 }
 
 // ---------------------------------------------------------------------------------------
@@ -377,11 +427,12 @@ int make_map(CUtensorMap* tm, const void* base, uint64_t inner, uint64_t outer, 
     return r == CUDA_SUCCESS ? 0 : -11;
 }
 
-int choose_tile_n(int N, int b_mn) {
-    const int step = b_mn ? 64 : 32;
+// pair: B is split over the two CTAs, so an MN-major B tile must be two whole 64-wide boxes per CTA
+int choose_tile_n(int N, int b_mn, int ctas) {
+    const int step = b_mn ? 64 * ctas : 32;
     int best = 64;
     double best_cost = 1e30;
-    for (int bn = 64; bn <= MAX_BN; bn += step) {
+    for (int bn = (step > 64 ? step : 64); bn <= MAX_BN; bn += step) {
         const double padded = (double)((N + bn - 1) / bn) * bn;
         const double cost = padded * (1.0 + 24.0 / bn);
         if (cost < best_cost - 1e-9 || (cost < best_cost + 1e-9 && bn > best)) {
@@ -406,26 +457,44 @@ int gemm_bf16_umma(const GemmProblem& g, int* err_flag, cudaStream_t stream) {
     if (g.splits > 1 && g.out_mode != GEMM_OUT_F32_ATOMIC) return -4;
 
     static bool attr_done = false;
+    static bool pair_off = false;
     if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             SMEM_DYN_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_umma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DYN_BYTES);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_bf16_umma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DYN_BYTES);
         if (e != cudaSuccess) return -5;
+        pair_off = getenv("BM_GEMM_1CTA") != nullptr;
         int dev = 0;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
         attr_done = true;
     }
 
+    // CTA pairs (256-row tiles) whenever there are at least 256 rows and the caller did not fix a narrow tile
+    const int ctas = (!pair_off && g.M >= 2 * BM && g.tile_n == 0) ? 2 : 1;
     KArgs p;
     p.M = g.M; p.N = g.N; p.K = g.K;
-    p.BN = g.tile_n > 0 ? g.tile_n : choose_tile_n(g.N, g.b_mn_major);
-    if (p.BN < 32 || p.BN > MAX_BN || (p.BN % 32) || (g.b_mn_major && (p.BN % 64))) return -6;
+    p.BN = g.tile_n > 0 ? g.tile_n : choose_tile_n(g.N, g.b_mn_major, ctas);
+    if (p.BN < 32 || p.BN > MAX_BN || (p.BN % 32) || (g.b_mn_major && (p.BN % (64 * ctas)))) return -6;
+    p.tile_rows = BM * ctas;
     p.a_mn = g.a_mn_major ? 1 : 0;
     p.b_mn = g.b_mn_major ? 1 : 0;
-    p.tiles_m = (g.M + BM - 1) / BM;
+    p.tiles_m = (g.M + p.tile_rows - 1) / p.tile_rows;
     p.tiles_n = (g.N + p.BN - 1) / p.BN;
     p.kb_total = (g.K + BK - 1) / BK;
     int splits = g.splits > 0 ? g.splits : 1;
+    if (g.splits <= 0 && g.out_mode == GEMM_OUT_F32_ATOMIC) {
+        // Split the reduction axis so that the waves of work units fill the machine: minimise
+        // waves x (k-blocks per unit + a fixed cost per unit for pipeline fill and the accumulator drain).
+        const long workers = ctas == 2 ? g_num_sms / 2 : g_num_sms;
+        const long tiles = (long)p.tiles_m * p.tiles_n;
+        long best = -1;
+        const int max_s = p.kb_total / 4 > 16 ? 16 : (p.kb_total / 4 > 1 ? p.kb_total / 4 : 1);
+        for (int sp = 1; sp <= max_s; ++sp) {
+            const long waves = (tiles * sp + workers - 1) / workers;
+            const long cost = waves * ((p.kb_total + sp - 1) / sp + 8);
+            if (best < 0 || cost < best) { best = cost; splits = sp; }
+        }
+    }
     if (splits > p.kb_total) splits = p.kb_total;
     p.kb_per_split = (p.kb_total + splits - 1) / splits;
     p.splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;
@@ -438,28 +507,39 @@ int gemm_bf16_umma(const GemmProblem& g, int* err_flag, cudaStream_t stream) {
     if (!p.a_mn) rc = make_map(&tmA, g.A, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda, BK, BM);
     else         rc = make_map(&tmA, g.A, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)g.lda, 64, BK);
     if (rc) return rc;
-    if (!p.b_mn) rc = make_map(&tmB, g.B, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb, BK, (uint32_t)p.BN);
+    if (!p.b_mn) rc = make_map(&tmB, g.B, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb, BK, (uint32_t)(p.BN / ctas));
     else         rc = make_map(&tmB, g.B, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb, 64, BK);
     if (rc) return rc;
 
     const long units = (long)p.tiles_m * p.tiles_n * p.splits;
-    const int grid = (int)(units < g_num_sms ? units : g_num_sms);
     g_launches.fetch_add(1);
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = SMEM_DYN_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute at[2];
+    int na = 0;
     if (g.pdl) {
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(grid);
-        cfg.blockDim = dim3(NUM_THREADS);
-        cfg.dynamicSmemBytes = SMEM_DYN_BYTES;
-        cfg.stream = stream;
-        cudaLaunchAttribute at[1];
-        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        at[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = at;
-        cfg.numAttrs = 1;
-        return cudaLaunchKernelEx(&cfg, gemm_bf16_umma_kernel, tmA, tmB, p) == cudaSuccess ? 0 : -7;
+        at[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
     }
-    gemm_bf16_umma_kernel<<<grid, NUM_THREADS, SMEM_DYN_BYTES, stream>>>(tmA, tmB, p);
-    return cudaGetLastError() == cudaSuccess ? 0 : -7;
+    if (ctas == 2) {
+        at[na].id = cudaLaunchAttributeClusterDimension;
+        at[na].val.clusterDim.x = 2;
+        at[na].val.clusterDim.y = 1;
+        at[na].val.clusterDim.z = 1;
+        ++na;
+        const int pairs = g_num_sms / 2;
+        cfg.gridDim = dim3((unsigned)(2 * (units < pairs ? units : pairs)));
+        cfg.attrs = at;
+        cfg.numAttrs = na;
+        return cudaLaunchKernelEx(&cfg, gemm_bf16_umma_kernel<2>, tmA, tmB, p) == cudaSuccess ? 0 : -7;
+    }
+    cfg.gridDim = dim3((unsigned)(units < g_num_sms ? units : g_num_sms));
+    cfg.attrs = at;
+    cfg.numAttrs = na;
+    return cudaLaunchKernelEx(&cfg, gemm_bf16_umma_kernel<1>, tmA, tmB, p) == cudaSuccess ? 0 : -7;
 }
 
 }  // namespace bmb

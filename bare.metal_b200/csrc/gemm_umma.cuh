@@ -37,7 +37,7 @@ struct GemmProblem {
     int out_mode;
     const __nv_bfloat16* R;  // optional residual added in the epilogue (GEMM_OUT_BF16 only), same shape as C
     int ldr;
-    int splits;  // >1 only with GEMM_OUT_F32_ATOMIC
+    int splits;  // >1 only with GEMM_OUT_F32_ATOMIC; 0 = choose (fills the machine with whole waves of work units)
     int tile_n;  // 0 = choose
     int pdl;     // 1 = launch with programmatic stream serialisation (the predecessor must be a kernel of the same stream)
 };

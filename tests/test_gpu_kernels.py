@@ -42,7 +42,7 @@ DTYPES = [BMC_F32, BMC_BF16]
 # (BT, C, OC): SmolLM2 projection shapes at small BT, tile-edge cases, and the reference's odd test shape scaled to the
 # 8-element granularity TMA needs (test/simd_matmul_test.c:30 uses BT37 C53 OC70)
 GEMM_SHAPES = [(64, 576, 576), (64, 576, 192), (37, 56, 72), (200, 960, 1600), (130, 2560, 960), (256, 960, 5120), (3, 16, 8),
-               (129, 64, 200), (300, 72, 160)]
+               (129, 64, 200), (300, 72, 160), (700, 960, 1600), (513, 192, 960), (1024, 320, 136)]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
