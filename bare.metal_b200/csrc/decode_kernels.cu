@@ -358,32 +358,38 @@ decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, 
     float mx[MUL];
 #pragma unroll
     for (int h = 0; h < MUL; ++h) mx[h] = -INFINITY;
-    for (int t0 = 0; t0 < len; t0 += ATT_THREADS / 8) {
-        const int t = t0 + slot;
-        float s[MUL];
+    constexpr int PU = 4;  // positions in flight per 8-lane group: the K rows of all four are requested before any is used
+    for (int t0 = 0; t0 < len; t0 += PU * (ATT_THREADS / 8)) {
+        float4 kv[PU][EPL / 4];
 #pragma unroll
-        for (int h = 0; h < MUL; ++h) s[h] = 0.f;
-        if (t < len) {
-            const float* kt = kc + (size_t)(t_begin + t) * KV + sub * EPL;
-            float4 kv[EPL / 4];
+        for (int u = 0; u < PU; ++u) {
+            const int t = t0 + slot + u * (ATT_THREADS / 8);
+            if (t < len) {
+                const float* kt = kc + (size_t)(t_begin + t) * KV + sub * EPL;
 #pragma unroll
-            for (int i = 0; i < EPL / 4; ++i) kv[i] = *reinterpret_cast<const float4*>(kt + i * 4);
+                for (int i = 0; i < EPL / 4; ++i) kv[u][i] = *reinterpret_cast<const float4*>(kt + i * 4);
+            } else {
 #pragma unroll
-            for (int i = 0; i < EPL / 4; ++i)
-#pragma unroll
-                for (int h = 0; h < MUL; ++h)
-                    s[h] = fmaf(qr[h][i * 4], kv[i].x, fmaf(qr[h][i * 4 + 1], kv[i].y, fmaf(qr[h][i * 4 + 2], kv[i].z, fmaf(qr[h][i * 4 + 3], kv[i].w, s[h]))));
+                for (int i = 0; i < EPL / 4; ++i) kv[u][i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
         }
 #pragma unroll
-        for (int h = 0; h < MUL; ++h) {
-            float v = s[h];
-            v += __shfl_xor_sync(0xffffffffu, v, 1);
-            v += __shfl_xor_sync(0xffffffffu, v, 2);
-            v += __shfl_xor_sync(0xffffffffu, v, 4);
-            v *= scale;
-            if (t < len) {
-                if (sub == 0) sc[(size_t)h * chunk + t] = v;
-                mx[h] = fmaxf(mx[h], v);
+        for (int u = 0; u < PU; ++u) {
+            const int t = t0 + slot + u * (ATT_THREADS / 8);
+#pragma unroll
+            for (int h = 0; h < MUL; ++h) {
+                float v = 0.f;
+#pragma unroll
+                for (int i = 0; i < EPL / 4; ++i)
+                    v = fmaf(qr[h][i * 4], kv[u][i].x, fmaf(qr[h][i * 4 + 1], kv[u][i].y, fmaf(qr[h][i * 4 + 2], kv[u][i].z, fmaf(qr[h][i * 4 + 3], kv[u][i].w, v))));
+                v += __shfl_xor_sync(0xffffffffu, v, 1);
+                v += __shfl_xor_sync(0xffffffffu, v, 2);
+                v += __shfl_xor_sync(0xffffffffu, v, 4);
+                v *= scale;
+                if (t < len) {
+                    if (sub == 0) sc[(size_t)h * chunk + t] = v;
+                    mx[h] = fmaxf(mx[h], v);
+                }
             }
         }
     }
@@ -427,15 +433,16 @@ decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, 
     float4 acc[MUL];
 #pragma unroll
     for (int h = 0; h < MUL; ++h) acc[h] = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int t0 = grp; t0 < len; t0 += 4 * GROUPS) {
-        float4 v[4];
+    constexpr int VU = 8;  // V rows in flight per thread
+    for (int t0 = grp; t0 < len; t0 += VU * GROUPS) {
+        float4 v[VU];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < VU; ++u) {
             const int t = t0 + u * GROUPS;
             v[u] = t < len ? *reinterpret_cast<const float4*>(vc + (size_t)(t_begin + t) * KV + d4 * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < VU; ++u) {
             const int t = t0 + u * GROUPS;
             if (t < len) {
 #pragma unroll
