@@ -350,7 +350,7 @@ constexpr int BWD_DYN_SMEM = 2 * KV_TILE_BYTES + 2 * 2 * Q_BYTES + 2 * P_BYTES +
 constexpr uint32_t BT_S = 0, BT_DP = 128, BT_DV = 256, BT_DK = 320, BT_DQ = 384;
 
 struct __align__(8) BwdBars {
-    uint64_t kv_full, q_full[2], q_empty[2], sdp_full, pds_ready, dq_full;
+    uint64_t kv_full, q_full[2], q_empty[2], sdp_full, sdp_free, pds_ready, dq_full;
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -409,6 +409,7 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         mbar_init(&bars.kv_full, 1);
         for (int i = 0; i < 2; ++i) { mbar_init(&bars.q_full[i], 1); mbar_init(&bars.q_empty[i], 1); }
         mbar_init(&bars.sdp_full, 1);
+        mbar_init(&bars.sdp_free, 16);
         mbar_init(&bars.pds_ready, 16);
         mbar_init(&bars.dq_full, 1);
         bars.abort_flag = 0;
@@ -459,19 +460,37 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             const uint64_t p_mn = umma_smem_desc_sw128(smem_u32(sP), FQ * 128, 1024);        // M = 128 keys: LBO = next key half (16 KB)
             const uint64_t d_mn = umma_smem_desc_sw128(smem_u32(sD), FQ * 128, 1024);
             const uint64_t d_km = umma_smem_desc_sw128(smem_u32(sD), 16, 1024);
+            // Software pipeline: S and dP of tile it+1 are issued as soon as the compute warps have read tile it's out of TMEM
+            // (sdp_free), i.e. BEFORE the dV/dK/dQ UMMAs of tile it, so the exponentials of tile it+1 run while the tensor
+            // core works through the second stage of tile it.
             bool ok = mbar_wait(&bars.kv_full, 0, abort_flag);
+            if (ok && total > 0) {
+                ok = mbar_wait(&bars.q_full[0], 0, abort_flag);
+                if (ok) {
+                    tc_fence_after_sync();
+#pragma unroll
+                    for (int k = 0; k < FHD / 16; ++k) umma_bf16_ss(tmem + BT_S, q_km0 + 2 * k, k_km + 2 * k, id_s, k > 0 ? 1u : 0u);
+#pragma unroll
+                    for (int k = 0; k < FHD / 16; ++k) umma_bf16_ss(tmem + BT_DP, g_km0 + 2 * k, v_km + 2 * k, id_s, k > 0 ? 1u : 0u);
+                    umma_commit(&bars.sdp_full);
+                }
+            }
             for (int it = 0; it < total && ok; ++it) {
                 const int st = it & 1;
                 const uint64_t so = (uint64_t)(st * (Q_BYTES >> 4));
-                if (!mbar_wait(&bars.q_full[st], (it >> 1) & 1, abort_flag)) { ok = false; break; }
-                tc_fence_after_sync();
                 BTRACE(0, it);
-                // S and dP of this tile (their TMEM columns were released by pds_ready of the previous tile)
+                if (it + 1 < total) {
+                    const int nx = (it + 1) & 1;
+                    const uint64_t sn = (uint64_t)(nx * (Q_BYTES >> 4));
+                    if (!mbar_wait(&bars.sdp_free, it & 1, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(&bars.q_full[nx], ((it + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+                    tc_fence_after_sync();
 #pragma unroll
-                for (int k = 0; k < FHD / 16; ++k) umma_bf16_ss(tmem + BT_S, q_km0 + so + 2 * k, k_km + 2 * k, id_s, k > 0 ? 1u : 0u);
+                    for (int k = 0; k < FHD / 16; ++k) umma_bf16_ss(tmem + BT_S, q_km0 + sn + 2 * k, k_km + 2 * k, id_s, k > 0 ? 1u : 0u);
 #pragma unroll
-                for (int k = 0; k < FHD / 16; ++k) umma_bf16_ss(tmem + BT_DP, g_km0 + so + 2 * k, v_km + 2 * k, id_s, k > 0 ? 1u : 0u);
-                umma_commit(&bars.sdp_full);
+                    for (int k = 0; k < FHD / 16; ++k) umma_bf16_ss(tmem + BT_DP, g_km0 + sn + 2 * k, v_km + 2 * k, id_s, k > 0 ? 1u : 0u);
+                    umma_commit(&bars.sdp_full);
+                }
                 BTRACE(1, it);
                 // P and dS in shared memory, and dQ of the previous tile read out of TMEM
                 if (!mbar_wait(&bars.pds_ready, it & 1, abort_flag)) { ok = false; break; }
@@ -520,6 +539,10 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             tmem_ld_32x32(lane_addr + BT_S + cg * 32, sv);
             tmem_ld_32x32(lane_addr + BT_DP + cg * 32, dv);
             tmem_ld_wait();
+            // S and dP are in registers: their TMEM columns may receive the next tile
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars.sdp_free);
             if (cw == 0 && lane == 0) BTRACE(5, it);
             const bool diag = (mb == nblk) || (n0 + FK > p.S);
             uint32_t pp[16], dd[16];
