@@ -345,12 +345,12 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 // dQ tiles are added into an fp32 scratch with red.global.add.v4.f32 (another key block adds to the same rows);
 // dK and dV are written once at the end, so they need no atomics and are deterministic.
 // Reference: attention_backward_tiled, src/kernels/backward.metal:820 (same two-level loop, float atomics for dK/dV there).
-constexpr int BWD_THREADS = 576;  // TMA warp, UMMA warp, 16 compute warps
-constexpr int BWD_DYN_SMEM = 2 * KV_TILE_BYTES + 2 * 2 * Q_BYTES + 2 * P_BYTES + 1024;  // K,V + 2 stages of (Q,dO) + P + dS = 160 KB
-constexpr uint32_t BT_S = 0, BT_DP = 128, BT_DV = 256, BT_DK = 320, BT_DQ = 384;
+constexpr int BWD_THREADS = 608;  // TMA warp, UMMA warp (S, dP), 16 compute warps, second UMMA warp (dV, dK, dQ)
+constexpr int BWD_DYN_SMEM = 2 * KV_TILE_BYTES + 2 * 2 * Q_BYTES + 4 * P_BYTES + 1024;  // K,V + 2 stages of (Q,dO) + 2 x (P + dS) = 224 KB
+constexpr uint32_t BT_S = 0, BT_DP = 128, BT_DV = 256, BT_DK = 320, BT_DQ = 384;  // dQ: two buffers of 64 columns (384, 448)
 
 struct __align__(8) BwdBars {
-    uint64_t kv_full, q_full[2], q_empty[2], sdp_full, sdp_free, pds_ready, dq_full;
+    uint64_t kv_full, q_full[2], q_empty[2], sdp_full, sdp_free, pds_ready[2], dq_full[2];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -392,8 +392,8 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     uint8_t* sV = sK + KV_TILE_BYTES;
     uint8_t* sQ = sV + KV_TILE_BYTES;       // 2 stages
     uint8_t* sG = sQ + 2 * Q_BYTES;         // 2 stages (dO tiles)
-    uint8_t* sP = sG + 2 * Q_BYTES;         // [2 key halves][128 query rows][128 B]
-    uint8_t* sD = sP + P_BYTES;             // dS, same layout
+    uint8_t* sP = sG + 2 * Q_BYTES;         // 2 buffers x [2 key halves][128 query rows][128 B]
+    uint8_t* sD = sP + 2 * P_BYTES;         // dS, same layout, 2 buffers
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nblk = blockIdx.x, kh = blockIdx.y, b = blockIdx.z;   // key block 0 has the most work and starts first
@@ -410,8 +410,7 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         for (int i = 0; i < 2; ++i) { mbar_init(&bars.q_full[i], 1); mbar_init(&bars.q_empty[i], 1); }
         mbar_init(&bars.sdp_full, 1);
         mbar_init(&bars.sdp_free, 16);
-        mbar_init(&bars.pds_ready, 16);
-        mbar_init(&bars.dq_full, 1);
+        for (int i = 0; i < 2; ++i) { mbar_init(&bars.pds_ready[i], 16); mbar_init(&bars.dq_full[i], 1); }
         bars.abort_flag = 0;
         mbar_fence_init();
         fence_proxy_async_smem();
@@ -447,19 +446,11 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         // ------------------------------ UMMA issuer --------------------------------
         if (lane == 0) {
             const uint32_t id_s = umma_idesc_bf16_f32(FQ, FK, 0, 0);     // S, dP: A K-major, B K-major, N = 128
-            const uint32_t id_kv = umma_idesc_bf16_f32(FK, FHD, 1, 1);   // dV, dK: A MN-major, B MN-major, N = 64
-            const uint32_t id_q = umma_idesc_bf16_f32(FQ, FHD, 0, 1);    // dQ: A K-major, B MN-major, N = 64
-            // descriptor bases; K-major tiles step +2 (32 B) per UMMA, MN-major tiles +128 (2048 B = 16 rows)
+            // descriptor bases; K-major tiles step +2 (32 B) per UMMA
             const uint64_t k_km = umma_smem_desc_sw128(smem_u32(sK), 16, 1024);
             const uint64_t v_km = umma_smem_desc_sw128(smem_u32(sV), 16, 1024);
-            const uint64_t k_mn = umma_smem_desc_sw128(smem_u32(sK), FK * 128, 1024);        // N = 64: a single MN group
             const uint64_t q_km0 = umma_smem_desc_sw128(smem_u32(sQ), 16, 1024);
             const uint64_t g_km0 = umma_smem_desc_sw128(smem_u32(sG), 16, 1024);
-            const uint64_t q_mn0 = umma_smem_desc_sw128(smem_u32(sQ), FQ * 128, 1024);
-            const uint64_t g_mn0 = umma_smem_desc_sw128(smem_u32(sG), FQ * 128, 1024);
-            const uint64_t p_mn = umma_smem_desc_sw128(smem_u32(sP), FQ * 128, 1024);        // M = 128 keys: LBO = next key half (16 KB)
-            const uint64_t d_mn = umma_smem_desc_sw128(smem_u32(sD), FQ * 128, 1024);
-            const uint64_t d_km = umma_smem_desc_sw128(smem_u32(sD), 16, 1024);
             // Software pipeline: S and dP of tile it+1 are issued as soon as the compute warps have read tile it's out of TMEM
             // (sdp_free), i.e. BEFORE the dV/dK/dQ UMMAs of tile it, so the exponentials of tile it+1 run while the tensor
             // core works through the second stage of tile it.
@@ -475,36 +466,56 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                     umma_commit(&bars.sdp_full);
                 }
             }
+            for (int it = 0; it + 1 < total && ok; ++it) {
+                const int nx = (it + 1) & 1;
+                const uint64_t sn = (uint64_t)(nx * (Q_BYTES >> 4));
+                BTRACE(0, it);
+                if (!mbar_wait(&bars.sdp_free, it & 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(&bars.q_full[nx], ((it + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+                tc_fence_after_sync();
+#pragma unroll
+                for (int k = 0; k < FHD / 16; ++k) umma_bf16_ss(tmem + BT_S, q_km0 + sn + 2 * k, k_km + 2 * k, id_s, k > 0 ? 1u : 0u);
+#pragma unroll
+                for (int k = 0; k < FHD / 16; ++k) umma_bf16_ss(tmem + BT_DP, g_km0 + sn + 2 * k, v_km + 2 * k, id_s, k > 0 ? 1u : 0u);
+                umma_commit(&bars.sdp_full);
+                BTRACE(1, it);
+            }
+        }
+    } else if (warp == 18) {
+        // ------------------------------ second UMMA issuer: dV, dK, dQ ----------------
+        // A thread's UMMAs are accepted one at a time; with the first-stage and second-stage products issued by two threads
+        // the tensor core's queue is fed from both while the compute warps work on the tile in between.
+        if (lane == 0) {
+            const uint32_t id_kv = umma_idesc_bf16_f32(FK, FHD, 1, 1);   // dV, dK: A MN-major, B MN-major, N = 64
+            const uint32_t id_q = umma_idesc_bf16_f32(FQ, FHD, 0, 1);    // dQ: A K-major, B MN-major, N = 64
+            // MN-major tiles step +128 (2048 B = 16 rows) per UMMA
+            const uint64_t k_mn = umma_smem_desc_sw128(smem_u32(sK), FK * 128, 1024);        // N = 64: a single MN group
+            const uint64_t q_mn0 = umma_smem_desc_sw128(smem_u32(sQ), FQ * 128, 1024);
+            const uint64_t g_mn0 = umma_smem_desc_sw128(smem_u32(sG), FQ * 128, 1024);
+            const uint64_t p_mn = umma_smem_desc_sw128(smem_u32(sP), FQ * 128, 1024);        // M = 128 keys: LBO = next key half (16 KB)
+            const uint64_t d_mn = umma_smem_desc_sw128(smem_u32(sD), FQ * 128, 1024);
+            const uint64_t d_km = umma_smem_desc_sw128(smem_u32(sD), 16, 1024);
+            bool ok = mbar_wait(&bars.kv_full, 0, abort_flag);
             for (int it = 0; it < total && ok; ++it) {
                 const int st = it & 1;
                 const uint64_t so = (uint64_t)(st * (Q_BYTES >> 4));
-                BTRACE(0, it);
-                if (it + 1 < total) {
-                    const int nx = (it + 1) & 1;
-                    const uint64_t sn = (uint64_t)(nx * (Q_BYTES >> 4));
-                    if (!mbar_wait(&bars.sdp_free, it & 1, abort_flag)) { ok = false; break; }
-                    if (!mbar_wait(&bars.q_full[nx], ((it + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
-                    tc_fence_after_sync();
-#pragma unroll
-                    for (int k = 0; k < FHD / 16; ++k) umma_bf16_ss(tmem + BT_S, q_km0 + sn + 2 * k, k_km + 2 * k, id_s, k > 0 ? 1u : 0u);
-#pragma unroll
-                    for (int k = 0; k < FHD / 16; ++k) umma_bf16_ss(tmem + BT_DP, g_km0 + sn + 2 * k, v_km + 2 * k, id_s, k > 0 ? 1u : 0u);
-                    umma_commit(&bars.sdp_full);
-                }
-                BTRACE(1, it);
-                // P and dS in shared memory, and dQ of the previous tile read out of TMEM
-                if (!mbar_wait(&bars.pds_ready, it & 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(&bars.q_full[st], (it >> 1) & 1, abort_flag)) { ok = false; break; }
+                // P and dS of this tile are in shared-memory buffer it & 1; the dQ columns of that parity were read out two tiles ago
+                const int pb = it & 1;
+                const uint64_t po = (uint64_t)(pb * (P_BYTES >> 4));
+                if (!mbar_wait(&bars.pds_ready[pb], (it >> 1) & 1, abort_flag)) { ok = false; break; }
                 tc_fence_after_sync();
                 BTRACE(2, it);
 #pragma unroll
-                for (int k = 0; k < FQ / 16; ++k) umma_bf16_ss(tmem + BT_DV, p_mn + 128 * k, g_mn0 + so + 128 * k, id_kv, (it > 0 || k > 0) ? 1u : 0u);
+                for (int k = 0; k < FQ / 16; ++k) umma_bf16_ss(tmem + BT_DV, p_mn + po + 128 * k, g_mn0 + so + 128 * k, id_kv, (it > 0 || k > 0) ? 1u : 0u);
 #pragma unroll
-                for (int k = 0; k < FQ / 16; ++k) umma_bf16_ss(tmem + BT_DK, d_mn + 128 * k, q_mn0 + so + 128 * k, id_kv, (it > 0 || k > 0) ? 1u : 0u);
+                for (int k = 0; k < FQ / 16; ++k) umma_bf16_ss(tmem + BT_DK, d_mn + po + 128 * k, q_mn0 + so + 128 * k, id_kv, (it > 0 || k > 0) ? 1u : 0u);
 #pragma unroll
                 for (int k = 0; k < FK / 16; ++k)
-                    umma_bf16_ss(tmem + BT_DQ, d_km + (uint64_t)((k >> 2) * ((FQ * 128) >> 4) + (k & 3) * 2), k_mn + 128 * k, id_q, k > 0 ? 1u : 0u);
+                    umma_bf16_ss(tmem + BT_DQ + pb * FHD, d_km + po + (uint64_t)((k >> 2) * ((FQ * 128) >> 4) + (k & 3) * 2), k_mn + 128 * k, id_q,
+                                 k > 0 ? 1u : 0u);
                 umma_commit(&bars.q_empty[st]);
-                umma_commit(&bars.dq_full);
+                umma_commit(&bars.dq_full[pb]);
                 BTRACE(3, it);
             }
         }
@@ -562,20 +573,18 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 dd[i >> 1] = *reinterpret_cast<uint32_t*>(&hd);
             }
             if (cw == 0 && lane == 0) BTRACE(6, it);
-            if (it > 0) {
-                // the UMMAs of the previous tile are done: P/dS may be overwritten and its dQ tile is complete
-                ok = mbar_wait(&bars.dq_full, (it - 1) & 1, abort_flag);
+            const int pb = it & 1;
+            if (it >= 2) {
+                // the second-stage UMMAs of tile it-2 have read this P/dS buffer
+                ok = mbar_wait(&bars.dq_full[pb], ((it - 2) >> 1) & 1, abort_flag);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
-                tc_fence_after_sync();
-                tmem_ld_32x16(lane_addr + BT_DQ + cg * 16, dq_regs);
-                tmem_ld_wait();
             }
             if (cw == 0 && lane == 0) BTRACE(7, it);
             // rows of P and dS: key half = cg / 2, 16-byte chunks (cg & 1) * 4 .. +3 of the 128-byte row
             {
-                uint8_t* prow = sP + (cg >> 1) * (FQ * 128) + r * 128;
-                uint8_t* drow = sD + (cg >> 1) * (FQ * 128) + r * 128;
+                uint8_t* prow = sP + pb * P_BYTES + (cg >> 1) * (FQ * 128) + r * 128;
+                uint8_t* drow = sD + pb * P_BYTES + (cg >> 1) * (FQ * 128) + r * 128;
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     const int cc = ((cg & 1) * 4 + c) ^ (r & 7);
@@ -586,10 +595,16 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             tc_fence_before_sync();
             fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bars.pds_ready);
+            if (lane == 0) mbar_arrive(&bars.pds_ready[pb]);
             if (cw == 0 && lane == 0) BTRACE(8, it);
             if (it > 0) {
-                // add the previous tile's dQ into the fp32 scratch while the tensor core works on this tile
+                // the previous tile's dQ (the other TMEM buffer) goes into the fp32 scratch while the tensor core works on this tile
+                ok = mbar_wait(&bars.dq_full[pb ^ 1], ((it - 1) >> 1) & 1, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after_sync();
+                tmem_ld_32x16(lane_addr + BT_DQ + (pb ^ 1) * FHD + cg * 16, dq_regs);
+                tmem_ld_wait();
                 const int pq = prev_q0 + r;
                 if (pq < p.S) {
                     float* dst = p.dq_acc + (size_t)(row0 + pq) * QD + (size_t)prev_h * FHD + cg * 16;
@@ -606,13 +621,13 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             if (cw == 0 && lane == 0) BTRACE(9, it);
         }
         if (ok && total > 0) {
-            ok = mbar_wait(&bars.dq_full, (total - 1) & 1, abort_flag);
+            ok = mbar_wait(&bars.dq_full[(total - 1) & 1], ((total - 1) >> 1) & 1, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
         }
         if (ok) {
             tc_fence_after_sync();
             if (total > 0) {
-                tmem_ld_32x16(lane_addr + BT_DQ + cg * 16, dq_regs);
+                tmem_ld_32x16(lane_addr + BT_DQ + ((total - 1) & 1) * FHD + cg * 16, dq_regs);
                 tmem_ld_wait();
                 const int pq = prev_q0 + r;
                 if (pq < p.S) {
