@@ -211,6 +211,9 @@ int bmx_trainer_dp_init(bm_trainer_t* t, int rank, int world, const void* nccl_i
     for (int l = 0; l < L; ++l) layer_begin[l] = t->params[9 * l].off;
     layer_begin[L] = t->params[9 * L].off;
     t->dp = bm_dp_create(t->ctx->be, rank, world, nccl_id, t->P, L, layer_begin.data(), t->d_grad);
+    // Three streams (compute, weight-gradient side stream, communication) have only been exercised on one GPU; with the
+    // exchange active the weight gradients stay on the compute stream unless BM_DP_SIDE_STREAM=1 asks otherwise.
+    if (t->dp && !getenv("BM_DP_SIDE_STREAM")) t->side_stream = 0;
     return t->dp ? 0 : -2;
 }
 
