@@ -102,43 +102,56 @@ decode_gemv1_kernel(float* __restrict__ out, int ldo, const float* __restrict__ 
     }
     pdl_launch_dependents();
     pdl_wait();
-    float xr[CH * EPL];
+    // The operand row is fetched ONCE per block (every warp needs all of it), transformed, and parked in shared memory in
+    // the order the lanes consume it: float4 number f of the row belongs to chunk f / (32 * E4), lane (f / E4) % 32, piece
+    // f % E4, and is stored at chunk * 32 * E4 + piece * 32 + lane, so a warp reads 32 consecutive float4 per piece.
+    extern __shared__ float4 sx4[];
+    __shared__ float s_red[GEMV_WARPS];
+    constexpr int E4 = EPL / 4;
+    const int nvec = C / 4;
+    const float* xrow = x + (size_t)b * ldx;
     float ss = 0.f;
-#pragma unroll
-    for (int j = 0; j < CH; ++j) {
-        const int c = (j * 32 + lane) * EPL;
-#pragma unroll
-        for (int i = 0; i < EPL; i += 4) {
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (c < C) {
-                v = *reinterpret_cast<const float4*>(x + (size_t)b * ldx + c + i);
-                if (PRO == 1) {
-                    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-                } else if (PRO == 2) {
-                    const float4 u = *reinterpret_cast<const float4*>(x + (size_t)b * ldx + C + c + i);
-                    v.x = v.x / (1.0f + expf(-v.x)) * u.x; v.y = v.y / (1.0f + expf(-v.y)) * u.y;
-                    v.z = v.z / (1.0f + expf(-v.z)) * u.z; v.w = v.w / (1.0f + expf(-v.w)) * u.w;
-                }
+    for (int f = threadIdx.x; f < CH * 32 * E4; f += GEMV_WARPS * 32) {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (f < nvec) {
+            v = *reinterpret_cast<const float4*>(xrow + 4 * f);
+            if (PRO == 1) {
+                ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            } else if (PRO == 2) {
+                const float4 u = *reinterpret_cast<const float4*>(xrow + C + 4 * f);
+                v.x = v.x / (1.0f + expf(-v.x)) * u.x; v.y = v.y / (1.0f + expf(-v.y)) * u.y;
+                v.z = v.z / (1.0f + expf(-v.z)) * u.z; v.w = v.w / (1.0f + expf(-v.w)) * u.w;
             }
-            xr[j * EPL + i] = v.x; xr[j * EPL + i + 1] = v.y; xr[j * EPL + i + 2] = v.z; xr[j * EPL + i + 3] = v.w;
         }
+        const int within = f % (32 * E4);
+        sx4[(f / (32 * E4)) * (32 * E4) + (within % E4) * 32 + within / E4] = v;
     }
     if (PRO == 1) {
         ss = warp_sum_f(ss);
-        const float inv = 1.0f / sqrtf(ss / (float)C + eps);
+        if (lane == 0) s_red[warp] = ss;
+        __syncthreads();
+        float t = 0.f;
 #pragma unroll
-        for (int j = 0; j < CH; ++j) {
-            const int c = (j * 32 + lane) * EPL;
-            if (c < C) {
-#pragma unroll
-                for (int i = 0; i < EPL; i += 4) {
-                    const float4 g = *reinterpret_cast<const float4*>(lnw + c + i);
-                    xr[j * EPL + i] = xr[j * EPL + i] * inv * g.x; xr[j * EPL + i + 1] = xr[j * EPL + i + 1] * inv * g.y;
-                    xr[j * EPL + i + 2] = xr[j * EPL + i + 2] * inv * g.z; xr[j * EPL + i + 3] = xr[j * EPL + i + 3] * inv * g.w;
-                }
-            }
+        for (int i = 0; i < GEMV_WARPS; ++i) t += s_red[i];
+        const float inv = 1.0f / sqrtf(t / (float)C + eps);
+        for (int f = threadIdx.x; f < nvec; f += GEMV_WARPS * 32) {   // each thread rescales the pieces it wrote itself
+            const int within = f % (32 * E4);
+            const int idx = (f / (32 * E4)) * (32 * E4) + (within % E4) * 32 + within / E4;
+            const float4 g = *reinterpret_cast<const float4*>(lnw + 4 * f);
+            float4 v = sx4[idx];
+            v.x = v.x * inv * g.x; v.y = v.y * inv * g.y; v.z = v.z * inv * g.z; v.w = v.w * inv * g.w;
+            sx4[idx] = v;
         }
     }
+    __syncthreads();
+    float xr[CH * EPL];
+#pragma unroll
+    for (int j = 0; j < CH; ++j)
+#pragma unroll
+        for (int i4 = 0; i4 < E4; ++i4) {
+            const float4 v = sx4[j * (32 * E4) + i4 * 32 + lane];
+            xr[j * EPL + 4 * i4] = v.x; xr[j * EPL + 4 * i4 + 1] = v.y; xr[j * EPL + 4 * i4 + 2] = v.z; xr[j * EPL + 4 * i4 + 3] = v.w;
+        }
     bool first = true;
     for (; oc < OC; oc += 2 * stride) {
         const int oc1 = oc + stride;
@@ -291,7 +304,9 @@ __global__ void decode_rope_kv_kernel(float* __restrict__ qkv, float* __restrict
 // forward.metal:1284) and stores k, v into the cache row of the position (kv_store, forward.metal:1317); qkv then holds the
 // un-rotated projections and stays untouched.
 constexpr int ATT_THREADS = 256;
-template <int HD, int MUL, bool ROPE>
+// VPRE: the first V rows are requested together with the K rows (one memory round trip less; for grids of a few blocks per SM,
+// where latency, not occupancy, decides).
+template <int HD, int MUL, bool ROPE, bool VPRE>
 __global__ void __launch_bounds__(ATT_THREADS)
 decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, float* cache, const float* __restrict__ cs,
                         const int* __restrict__ pos_ptr, float* part, unsigned* tickets, int layer, int NB, int MS, int NH, int NKV,
@@ -353,6 +368,17 @@ decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, 
                 const float other = __shfl_xor_sync(0xffffffffu, mine, 4);
                 qr[h][i] = sub < 4 ? mine * c - other * s : other * s + mine * c;
             }
+        }
+    }
+    // the first V rows of phase 3 do not depend on the scores: request them now, with the K rows
+    constexpr int VU = 8;  // V rows in flight per thread
+    const int d4 = tid % D4, grp = tid / D4;
+    float4 vpre[VPRE ? VU : 1];
+    if (VPRE) {
+#pragma unroll
+        for (int u = 0; u < VU; ++u) {
+            const int t = grp + u * GROUPS;
+            vpre[u] = t < len ? *reinterpret_cast<const float4*>(vc + (size_t)(t_begin + t) * KV + d4 * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
     }
     float mx[MUL];
@@ -429,17 +455,16 @@ decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, 
     }
     __syncthreads();
     // phase 3
-    const int d4 = tid % D4, grp = tid / D4;
     float4 acc[MUL];
 #pragma unroll
     for (int h = 0; h < MUL; ++h) acc[h] = make_float4(0.f, 0.f, 0.f, 0.f);
-    constexpr int VU = 8;  // V rows in flight per thread
     for (int t0 = grp; t0 < len; t0 += VU * GROUPS) {
         float4 v[VU];
 #pragma unroll
         for (int u = 0; u < VU; ++u) {
             const int t = t0 + u * GROUPS;
-            v[u] = t < len ? *reinterpret_cast<const float4*>(vc + (size_t)(t_begin + t) * KV + d4 * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (VPRE && t0 == grp) v[u] = vpre[VPRE ? u : 0];
+            else v[u] = t < len ? *reinterpret_cast<const float4*>(vc + (size_t)(t_begin + t) * KV + d4 * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
         for (int u = 0; u < VU; ++u) {
@@ -706,9 +731,30 @@ __global__ void decode_argmax_kernel(int* __restrict__ out, const float* __restr
     const float* lr = logits + (size_t)blockIdx.x * V;
     float best = -INFINITY;
     int bi = 0x7fffffff;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        const float x = lr[i];
-        if (x > best || (x == best && i < bi)) { best = x; bi = i; }
+    if ((V & 3) == 0 && ((((size_t)blockIdx.x * V) & 3) == 0)) {
+        // 8 float4 per thread are requested before the first comparison: one memory round trip per 32768 logits
+        const int nv = V >> 2;
+        for (int base = 0; base < nv; base += 8 * (int)blockDim.x) {
+            float4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int f = base + u * (int)blockDim.x + (int)threadIdx.x;
+                v[u] = f < nv ? reinterpret_cast<const float4*>(lr)[f] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int i = 4 * (base + u * (int)blockDim.x + (int)threadIdx.x);   // ascending in u: ties keep the lowest index
+                if (v[u].x > best) { best = v[u].x; bi = i; }
+                if (v[u].y > best) { best = v[u].y; bi = i + 1; }
+                if (v[u].z > best) { best = v[u].z; bi = i + 2; }
+                if (v[u].w > best) { best = v[u].w; bi = i + 3; }
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < V; i += blockDim.x) {
+            const float x = lr[i];
+            if (x > best || (x == best && i < bi)) { best = x; bi = i; }
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -767,7 +813,8 @@ static int launch_gemv1(float* out, int ldo, const float* x, int ldx, const void
                         const float* lnw, float eps, int NB, int C, int OC, cudaStream_t st) {
     int gx = (OC + GEMV_WARPS - 1) / GEMV_WARPS;
     if (gx > 148 * 4) gx = 148 * 4;
-    return launch_k(decode_gemv1_kernel<WT, CH, PRO>, dim3(gx, NB), dim3(GEMV_WARPS * 32), 0, st, out, ldo, x, ldx, w, scales, res, ldr, lnw,
+    constexpr size_t smem = (size_t)CH * 32 * Epl<WT>::v * sizeof(float);  // the operand row, at most 12 KB
+    return launch_k(decode_gemv1_kernel<WT, CH, PRO>, dim3(gx, NB), dim3(GEMV_WARPS * 32), smem, st, out, ldo, x, ldx, w, scales, res, ldr, lnw,
                     eps, C, OC);
 }
 template <int WT, int PRO>
@@ -849,14 +896,18 @@ static int launch_attention(float* out, const float* qkv, float* cache, const fl
     static size_t attr_smem = 48 * 1024;
     if (smem > attr_smem) {
         if (smem > 220 * 1024) return -2;
-        cudaFuncSetAttribute(decode_attention_kernel<HD, MUL, ROPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(decode_attention_kernel<HD, MUL, ROPE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(decode_attention_kernel<HD, MUL, ROPE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         attr_smem = smem;
     }
     // scratch: tickets first (zeroed once by the owner; every launch leaves them zero), then the partial records
     unsigned* tickets = (unsigned*)scratch;
     float* part = scratch ? (float*)((char*)scratch + (((size_t)NB * NKV * sizeof(unsigned) + 15) / 16) * 16) : nullptr;
-    return launch_k(decode_attention_kernel<HD, MUL, ROPE>, dim3(NKV, NB, splits), dim3(ATT_THREADS), smem, st, out, qkv, cache, cs, pos, part,
-                    tickets, layer, NB, MS, NH, NKV, chunk, scale);
+    if ((long)NKV * NB * splits <= 2 * 148)
+        return launch_k(decode_attention_kernel<HD, MUL, ROPE, true>, dim3(NKV, NB, splits), dim3(ATT_THREADS), smem, st, out, qkv, cache, cs, pos,
+                        part, tickets, layer, NB, MS, NH, NKV, chunk, scale);
+    return launch_k(decode_attention_kernel<HD, MUL, ROPE, false>, dim3(NKV, NB, splits), dim3(ATT_THREADS), smem, st, out, qkv, cache, cs, pos,
+                    part, tickets, layer, NB, MS, NH, NKV, chunk, scale);
 }
 // head_dim 64 or 128; 1, 2, 3, 4 or 8 query heads per KV head. cs != null: RoPE and the cache store happen inside.
 // scratch (may be null: one slice per block): decode_attention_scratch_bytes() + 16 bytes, zero-initialised once.
