@@ -100,8 +100,24 @@ decode_gemv1_kernel(float* __restrict__ out, int ldo, const float* __restrict__ 
             if (c < C) { r0[j] = load_raw<WT>(w, scales, (size_t)oc, C, c); r1[j] = load_raw<WT>(w, scales, (size_t)o1, C, c); }
         }
     }
+    // norm gains of the float4 pieces this thread will transform: weights, so they can be requested before the wait as well
+    constexpr int NPIECE = (CH * 32 * (EPL / 4) + GEMV_WARPS * 32 - 1) / (GEMV_WARPS * 32);
+    float4 gain[PRO == 1 ? NPIECE : 1];
+    if (PRO == 1) {
+#pragma unroll
+        for (int k = 0; k < NPIECE; ++k) {
+            const int f = threadIdx.x + k * GEMV_WARPS * 32;
+            gain[k] = f < C / 4 ? *reinterpret_cast<const float4*>(lnw + 4 * f) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
     pdl_launch_dependents();
     pdl_wait();
+    // the residual of this warp's first two rows: requested now, needed only after the reduction
+    float res0 = 0.f, res1 = 0.f;
+    if (res && lane == 0 && oc < OC) {
+        res0 = res[(size_t)b * ldr + oc];
+        if (oc + stride < OC) res1 = res[(size_t)b * ldr + oc + stride];
+    }
     // The operand row is fetched ONCE per block (every warp needs all of it), transformed, and parked in shared memory in
     // the order the lanes consume it: float4 number f of the row belongs to chunk f / (32 * E4), lane (f / E4) % 32, piece
     // f % E4, and is stored at chunk * 32 * E4 + piece * 32 + lane, so a warp reads 32 consecutive float4 per piece.
@@ -134,10 +150,13 @@ decode_gemv1_kernel(float* __restrict__ out, int ldo, const float* __restrict__ 
 #pragma unroll
         for (int i = 0; i < GEMV_WARPS; ++i) t += s_red[i];
         const float inv = 1.0f / sqrtf(t / (float)C + eps);
-        for (int f = threadIdx.x; f < nvec; f += GEMV_WARPS * 32) {   // each thread rescales the pieces it wrote itself
+#pragma unroll
+        for (int k = 0; k < NPIECE; ++k) {   // each thread rescales the pieces it wrote itself
+            const int f = threadIdx.x + k * GEMV_WARPS * 32;
+            if (f >= nvec) break;
             const int within = f % (32 * E4);
             const int idx = (f / (32 * E4)) * (32 * E4) + (within % E4) * 32 + within / E4;
-            const float4 g = *reinterpret_cast<const float4*>(lnw + 4 * f);
+            const float4 g = gain[PRO == 1 ? k : 0];
             float4 v = sx4[idx];
             v.x = v.x * inv * g.x; v.y = v.y * inv * g.y; v.z = v.z * inv * g.z; v.w = v.w * inv * g.w;
             sx4[idx] = v;
@@ -176,8 +195,12 @@ decode_gemv1_kernel(float* __restrict__ out, int ldo, const float* __restrict__ 
         a0 = warp_sum_f(a0);
         a1 = warp_sum_f(a1);
         if (lane == 0) {
-            out[(size_t)b * ldo + oc] = a0 + (res ? res[(size_t)b * ldr + oc] : 0.f);
-            if (two) out[(size_t)b * ldo + oc1] = a1 + (res ? res[(size_t)b * ldr + oc1] : 0.f);
+            out[(size_t)b * ldo + oc] = a0 + res0;
+            if (two) out[(size_t)b * ldo + oc1] = a1 + res1;
+            // residuals of the next pair of rows (only the LM head has more than one pair per warp)
+            const int n0 = oc + 2 * stride, n1 = n0 + stride;
+            res0 = (res && n0 < OC) ? res[(size_t)b * ldr + n0] : 0.f;
+            res1 = (res && n1 < OC) ? res[(size_t)b * ldr + n1] : 0.f;
         }
     }
 }
