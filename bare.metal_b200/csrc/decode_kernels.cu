@@ -327,8 +327,8 @@ __global__ void decode_rope_kv_kernel(float* __restrict__ qkv, float* __restrict
 // forward.metal:1284) and stores k, v into the cache row of the position (kv_store, forward.metal:1317); qkv then holds the
 // un-rotated projections and stays untouched.
 constexpr int ATT_THREADS = 256;
-// VPRE: the first V rows are requested together with the K rows (one memory round trip less; for grids of a few blocks per SM,
-// where latency, not occupancy, decides).
+// VPRE (grids of a few blocks per SM, where latency, not occupancy, decides): the first K and V rows of the slice are requested
+// before the dependency wait, together.
 template <int HD, int MUL, bool ROPE, bool VPRE>
 __global__ void __launch_bounds__(ATT_THREADS)
 decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, float* cache, const float* __restrict__ cs,
@@ -340,11 +340,48 @@ decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, 
     constexpr int GROUPS = ATT_THREADS / D4;
     constexpr int PW = HD + 2;              // partial record: acc[HD], max, sum
     const int kh = blockIdx.x, b = blockIdx.y, z = blockIdx.z, nz = gridDim.z, tid = threadIdx.x;
-    pdl_launch_dependents();
-    pdl_wait();
+    // Before the dependency wait: everything that was written by EARLIER steps — the position counter (advanced by the last
+    // kernel of the previous step), the cache rows below the current position, the rotation table. Only the row of the
+    // current position is produced inside this step; whoever loaded it early reloads it after the wait.
     const int n = *pos_ptr + 1;
     const int t_begin = z * chunk, t_end = min(n, t_begin + chunk), len = max(t_end - t_begin, 0);
     const int QD = NH * HD, KV = NKV * HD;
+    constexpr int PU = 4;   // positions in flight per 8-lane group: the K rows of all four are requested before any is used
+    constexpr int VU = 8;   // V rows in flight per thread
+    const int sub = tid & 7, slot = tid >> 3;          // phase 1: 8 lanes per position, 32 positions per block iteration
+    const int d4 = tid % D4, grp = tid / D4;           // phase 3: one float4 of a V row per thread, GROUPS rows per block iteration
+    const int tn = n - 1 - t_begin;                    // the current position inside this slice (if 0 <= tn < len)
+    const float* kc = cache + (((size_t)layer * 2 + 0) * NB + b) * (size_t)MS * KV + (size_t)kh * HD;
+    const float* vc = cache + (((size_t)layer * 2 + 1) * NB + b) * (size_t)MS * KV + (size_t)kh * HD;
+    float4 kpre[VPRE ? PU : 1][EPL / 4];
+    if (VPRE) {
+#pragma unroll
+        for (int u = 0; u < PU; ++u) {
+            const int t = slot + u * (ATT_THREADS / 8);
+#pragma unroll
+            for (int i = 0; i < EPL / 4; ++i)
+                kpre[u][i] = t < len ? *reinterpret_cast<const float4*>(kc + (size_t)(t_begin + t) * KV + sub * EPL + i * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    float4 vpre[VPRE ? VU : 1];
+    if (VPRE) {
+#pragma unroll
+        for (int u = 0; u < VU; ++u) {
+            const int t = grp + u * GROUPS;
+            vpre[u] = t < len ? *reinterpret_cast<const float4*>(vc + (size_t)(t_begin + t) * KV + d4 * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    float rc[ROPE ? EPL : 1], rs[ROPE ? EPL : 1];      // rotation of this lane's query elements
+    if (ROPE) {
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+            const int p = (sub & 3) * EPL + i;
+            rc[i] = cs[((size_t)(n - 1) * (HD / 2) + p) * 2];
+            rs[i] = cs[((size_t)(n - 1) * (HD / 2) + p) * 2 + 1];
+        }
+    }
+    pdl_launch_dependents();
+    pdl_wait();
     float* sc = sm;                                    // [MUL][chunk]
     float* red = sm + (size_t)MUL * chunk;             // [MUL][GROUPS][HD] (phase 3) / [MUL][8] (phase 2)
     __shared__ float s_stat[2 * MUL];
@@ -364,12 +401,22 @@ decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, 
         }
         __syncthreads();  // the rows just written are read back below by other threads of this block
     }
-    const float* kc = cache + (((size_t)layer * 2 + 0) * NB + b) * (size_t)MS * KV + (size_t)kh * HD;
-    const float* vc = cache + (((size_t)layer * 2 + 1) * NB + b) * (size_t)MS * KV + (size_t)kh * HD;
+    // the row of the current position was (re)written inside this step: fetch it again where it was requested early
+    if (VPRE && tn >= 0 && tn < len) {
+#pragma unroll
+        for (int u = 0; u < PU; ++u)
+            if (slot + u * (ATT_THREADS / 8) == tn)
+#pragma unroll
+                for (int i = 0; i < EPL / 4; ++i) kpre[VPRE ? u : 0][i] = *reinterpret_cast<const float4*>(kc + (size_t)(n - 1) * KV + sub * EPL + i * 4);
+        {
+#pragma unroll
+            for (int u = 0; u < VU; ++u)
+                if (grp + u * GROUPS == tn) vpre[u] = *reinterpret_cast<const float4*>(vc + (size_t)(n - 1) * KV + d4 * 4);
+        }
+    }
     const float* qrow = qkv + (size_t)b * (QD + 2 * KV) + (size_t)kh * MUL * HD;
 
     // phase 1
-    const int sub = tid & 7, slot = tid >> 3;          // 32 positions per block iteration
     float qr[MUL][EPL];
 #pragma unroll
     for (int h = 0; h < MUL; ++h)
@@ -380,11 +427,9 @@ decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, 
         }
     if (ROPE) {
         // lanes sub 0..3 hold the first half of the head, sub 4..7 the second: the rotation partner sits 4 lanes away
-        constexpr int hd2 = HD / 2;
 #pragma unroll
         for (int i = 0; i < EPL; ++i) {
-            const int p = (sub & 3) * EPL + i;
-            const float c = cs[((size_t)(n - 1) * hd2 + p) * 2], s = cs[((size_t)(n - 1) * hd2 + p) * 2 + 1];
+            const float c = rc[ROPE ? i : 0], s = rs[ROPE ? i : 0];
 #pragma unroll
             for (int h = 0; h < MUL; ++h) {
                 const float mine = qr[h][i];
@@ -393,27 +438,18 @@ decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, 
             }
         }
     }
-    // the first V rows of phase 3 do not depend on the scores: request them now, with the K rows
-    constexpr int VU = 8;  // V rows in flight per thread
-    const int d4 = tid % D4, grp = tid / D4;
-    float4 vpre[VPRE ? VU : 1];
-    if (VPRE) {
-#pragma unroll
-        for (int u = 0; u < VU; ++u) {
-            const int t = grp + u * GROUPS;
-            vpre[u] = t < len ? *reinterpret_cast<const float4*>(vc + (size_t)(t_begin + t) * KV + d4 * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-    }
     float mx[MUL];
 #pragma unroll
     for (int h = 0; h < MUL; ++h) mx[h] = -INFINITY;
-    constexpr int PU = 4;  // positions in flight per 8-lane group: the K rows of all four are requested before any is used
     for (int t0 = 0; t0 < len; t0 += PU * (ATT_THREADS / 8)) {
         float4 kv[PU][EPL / 4];
 #pragma unroll
         for (int u = 0; u < PU; ++u) {
             const int t = t0 + slot + u * (ATT_THREADS / 8);
-            if (t < len) {
+            if (VPRE && t0 == 0) {
+#pragma unroll
+                for (int i = 0; i < EPL / 4; ++i) kv[u][i] = kpre[VPRE ? u : 0][i];
+            } else if (t < len) {
                 const float* kt = kc + (size_t)(t_begin + t) * KV + sub * EPL;
 #pragma unroll
                 for (int i = 0; i < EPL / 4; ++i) kv[u][i] = *reinterpret_cast<const float4*>(kt + i * 4);
