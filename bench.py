@@ -536,7 +536,7 @@ def main():
                          "unit": "TFLOP/s", "frac": (ach / peak_tf) if ach else None,
                          # DRAM bytes of ONE launch from the ncu capture of the gate/up forward GEMM (rows 32768, in 960, out 5120;
                          # algorithmic bytes of that launch 408e6), summarised in profiles/gemm_umma_gate_up_forward_ncu_full.md
-                         "traffic": 355.2e6, "traffic_case": "gate_up forward GEMM, 322 GFLOP, algorithmic 408e6 B",
+                         "traffic": 353.2e6, "traffic_case": "gate_up forward GEMM, 322 GFLOP, algorithmic 408e6 B",
                          "peak_source": f"bf16_tflops_sustained of {peak_src}", "launches": int(n_l),
                          "avg_launch_ms": (g_ms / n_l) if n_l else None, "avg_launch_flops": (g_fl / n_l) if n_l else None,
                          "share_of_step": (g_ms / ms_roof) if ms_roof else None,
