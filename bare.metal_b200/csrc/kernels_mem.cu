@@ -71,36 +71,52 @@ __global__ void rmsnorm_forward_kernel(T* __restrict__ out, float* __restrict__ 
                                        const float* __restrict__ w, int N, int C, float eps) {
     constexpr int V = Vec<T>::N;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row = blockIdx.x * WARPS_PER_BLOCK + warp;
-    if (row >= N) return;
-    const T* xr = x + (size_t)row * C;
-    T* orow = out + (size_t)row * C;
     const int nvec = C / V;
-    float f[NV][V];
-    float ss = 0.f;
+    // the gains of this lane's columns stay in registers for every row the warp handles
+    float wr[NV][V];
 #pragma unroll
     for (int a = 0; a < NV; ++a) {
         const int v = lane + a * 32;
-        if (v < nvec) Vec<T>::load(xr + v * V, f[a]);
+#pragma unroll
+        for (int i = 0; i < V; i += 4) {
+            float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (v < nvec) g = *reinterpret_cast<const float4*>(w + v * V + i);
+            wr[a][i] = g.x; wr[a][i + 1] = g.y; wr[a][i + 2] = g.z; wr[a][i + 3] = g.w;
+        }
     }
+    for (int row = blockIdx.x * WARPS_PER_BLOCK + warp; row < N; row += gridDim.x * WARPS_PER_BLOCK) {
+        const T* xr = x + (size_t)row * C;
+        T* orow = out + (size_t)row * C;
+        typename Vec<T>::Raw raw[NV];
 #pragma unroll
-    for (int a = 0; a < NV; ++a) {
-        const int v = lane + a * 32;
-        if (v < nvec)
+        for (int a = 0; a < NV; ++a) {
+            const int v = lane + a * 32;
+            if (v < nvec) raw[a] = Vec<T>::load_raw(xr + v * V);
+        }
+        float ss = 0.f;
 #pragma unroll
-            for (int i = 0; i < V; ++i) ss += f[a][i] * f[a][i];
-    }
-    ss = warp_sum(ss) / (float)C;
-    const float r = 1.0f / sqrtf(ss + eps);
-    if (lane == 0 && rstd) rstd[row] = r;
+        for (int a = 0; a < NV; ++a) {
+            const int v = lane + a * 32;
+            if (v < nvec) {
+                float f[V];
+                Vec<T>::unpack(raw[a], f);
 #pragma unroll
-    for (int a = 0; a < NV; ++a) {
-        const int v = lane + a * 32;
-        if (v < nvec) {
-            float o[V];
+                for (int i = 0; i < V; ++i) ss += f[i] * f[i];
+            }
+        }
+        ss = warp_sum(ss) / (float)C;
+        const float r = 1.0f / sqrtf(ss + eps);
+        if (lane == 0 && rstd) rstd[row] = r;
 #pragma unroll
-            for (int i = 0; i < V; ++i) o[i] = f[a][i] * r * w[v * V + i];
-            Vec<T>::store(orow + v * V, o);
+        for (int a = 0; a < NV; ++a) {
+            const int v = lane + a * 32;
+            if (v < nvec) {
+                float f[V], o[V];
+                Vec<T>::unpack(raw[a], f);
+#pragma unroll
+                for (int i = 0; i < V; ++i) o[i] = f[i] * r * wr[a][i];
+                Vec<T>::store(orow + v * V, o);
+            }
         }
     }
 }
@@ -135,12 +151,13 @@ __global__ void rmsnorm_forward_wide_kernel(T* __restrict__ out, float* __restri
 template <typename T> int rmsnorm_forward(T* out, float* rstd, const T* x, const float* w, int N, int C, float eps, cudaStream_t st) {
     if (C % Vec<T>::N) return -1;
     const int nv = ceil_div(C / Vec<T>::N, 32);
-    const int grid = ceil_div(N, WARPS_PER_BLOCK);
+    const int full = ceil_div(N, WARPS_PER_BLOCK);
+    const int grid = full < 148 * 8 ? full : 148 * 8;  // persistent over rows (the register-resident kernels loop)
     if (nv <= 1) rmsnorm_forward_kernel<T, 1><<<grid, BLOCK, 0, st>>>(out, rstd, x, w, N, C, eps);
     else if (nv <= 2) rmsnorm_forward_kernel<T, 2><<<grid, BLOCK, 0, st>>>(out, rstd, x, w, N, C, eps);
     else if (nv <= 4) rmsnorm_forward_kernel<T, 4><<<grid, BLOCK, 0, st>>>(out, rstd, x, w, N, C, eps);
     else if (nv <= 8) rmsnorm_forward_kernel<T, 8><<<grid, BLOCK, 0, st>>>(out, rstd, x, w, N, C, eps);
-    else rmsnorm_forward_wide_kernel<T><<<grid, BLOCK, 0, st>>>(out, rstd, x, w, N, C, eps);
+    else rmsnorm_forward_wide_kernel<T><<<full, BLOCK, 0, st>>>(out, rstd, x, w, N, C, eps);
     return 0;
 }
 template int rmsnorm_forward<float>(float*, float*, const float*, const float*, int, int, float, cudaStream_t);
@@ -159,9 +176,19 @@ __global__ void rmsnorm_backward_kernel(T* __restrict__ gx, float* __restrict__ 
                                         const T* __restrict__ x, const float* __restrict__ w, const float* __restrict__ rstd,
                                         int N, int C, int w_row0, int w_row1) {
     constexpr int V = Vec<T>::N;
-    extern __shared__ float s_gw[];  // [WARPS_PER_BLOCK][C]
+    extern __shared__ float s_gw[];  // [WARPS_PER_BLOCK][C], then the gains as float4 [NV][V/4][32 lanes]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nvec = C / V;
+    // The gains are read for every row. Straight from global memory a lane's 8 values sit 32 bytes from its neighbour's, so one
+    // scalar load costs 8 L1 wavefronts and the L1 data pipe, not HBM, bounds the kernel; parked in shared memory in lane order
+    // a float4 read is 4 conflict-free wavefronts.
+    float4* s_w4 = reinterpret_cast<float4*>(s_gw + (size_t)WARPS_PER_BLOCK * C);
+    for (int idx = threadIdx.x; idx < NV * (V / 4) * 32; idx += blockDim.x) {
+        const int l = idx & 31, ai = idx >> 5, a = ai / (V / 4), i4 = ai % (V / 4);
+        const int v = l + a * 32;
+        s_w4[idx] = v < nvec ? *reinterpret_cast<const float4*>(w + v * V + i4 * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    __syncthreads();
     float gw_acc[NV][V];
 #pragma unroll
     for (int a = 0; a < NV; ++a)
@@ -190,14 +217,19 @@ __global__ void rmsnorm_backward_kernel(T* __restrict__ gx, float* __restrict__ 
         for (int a = 0; a < NV; ++a) {
             const int v = lane + a * 32;
             if (v < nvec) {
-                float xs[V], gs[V];
+                float xs[V], gs[V], ws[V];
                 Vec<T>::unpack(xraw[a], xs);
                 Vec<T>::unpack(graw[a], gs);
+#pragma unroll
+                for (int i4 = 0; i4 < V / 4; ++i4) {
+                    const float4 g4 = s_w4[(a * (V / 4) + i4) * 32 + lane];
+                    ws[4 * i4] = g4.x; ws[4 * i4 + 1] = g4.y; ws[4 * i4 + 2] = g4.z; ws[4 * i4 + 3] = g4.w;
+                }
 #pragma unroll
                 for (int i = 0; i < V; ++i) {
                     const float n = xs[i] * r;
                     if (in_w) gw_acc[a][i] += gs[i] * n;
-                    c1 += gs[i] * w[v * V + i] * n;
+                    c1 += gs[i] * ws[i] * n;
                 }
             }
         }
@@ -206,12 +238,17 @@ __global__ void rmsnorm_backward_kernel(T* __restrict__ gx, float* __restrict__ 
         for (int a = 0; a < NV; ++a) {
             const int v = lane + a * 32;
             if (v < nvec) {
-                float xs[V], gs[V], os[V];
+                float xs[V], gs[V], os[V], ws[V];
                 Vec<T>::unpack(xraw[a], xs);
                 Vec<T>::unpack(graw[a], gs);
                 Vec<T>::unpack(oraw[a], os);
 #pragma unroll
-                for (int i = 0; i < V; ++i) os[i] += r * (gs[i] * w[v * V + i] - xs[i] * r * c1);
+                for (int i4 = 0; i4 < V / 4; ++i4) {
+                    const float4 g4 = s_w4[(a * (V / 4) + i4) * 32 + lane];
+                    ws[4 * i4] = g4.x; ws[4 * i4 + 1] = g4.y; ws[4 * i4 + 2] = g4.z; ws[4 * i4 + 3] = g4.w;
+                }
+#pragma unroll
+                for (int i = 0; i < V; ++i) os[i] += r * (gs[i] * ws[i] - xs[i] * r * c1);
                 Vec<T>::store(gxr + v * V, os);
             }
         }
@@ -256,7 +293,7 @@ static int rmsnorm_backward_launch(T* gx, float* gw, int gw_accumulate, const T*
                                    int N, int C, int w_row0, int w_row1, float* scratch, cudaStream_t st) {
     int nblocks = ceil_div(N, WARPS_PER_BLOCK);
     if (nblocks > RMS_BWD_MAX_BLOCKS) nblocks = RMS_BWD_MAX_BLOCKS;
-    const size_t smem = (size_t)WARPS_PER_BLOCK * C * sizeof(float);
+    const size_t smem = (size_t)WARPS_PER_BLOCK * C * sizeof(float) + (size_t)NV * Vec<T>::N * 32 * sizeof(float);
     static bool attr_done = false;
     if (!attr_done) {
         cudaFuncSetAttribute(rmsnorm_backward_kernel<T, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
