@@ -685,21 +685,32 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     if (warp == 1) tmem_dealloc(tmem, 512);
 }
 
-// delta[b, h, s] = sum_d gout * out. One warp per (row, head).
+// delta[b, h, s] = sum_d gout * out. Eight lanes per (row, head): one 16-byte load of each operand per lane.
 __global__ void flash_delta_umma_kernel(float* __restrict__ delta, const bf16* __restrict__ gout, const bf16* __restrict__ out, int ldo,
                                         int B, int S, int NH) {
-    const long wid = (blockIdx.x * (long)blockDim.x + threadIdx.x) >> 5;
-    const int lane = threadIdx.x & 31;
-    if (wid >= (long)B * S * NH) return;
-    const int h = (int)(wid % NH);
-    const long row = wid / NH;
-    const __nv_bfloat162 a = reinterpret_cast<const __nv_bfloat162*>(gout + row * ldo + (size_t)h * FHD)[lane];
-    const __nv_bfloat162 c = reinterpret_cast<const __nv_bfloat162*>(out + row * ldo + (size_t)h * FHD)[lane];
-    const float2 fa = __bfloat1622float2(a), fc = __bfloat1622float2(c);
-    float d = fa.x * fc.x + fa.y * fc.y;
+    const long gid = (blockIdx.x * (long)blockDim.x + threadIdx.x) >> 3;   // (row, head) index
+    const int sub = threadIdx.x & 7;
+    const long total = (long)B * S * NH;
+    float d = 0.f;
+    long row = 0;
+    int h = 0;
+    if (gid < total) {
+        h = (int)(gid % NH);
+        row = gid / NH;
+        const uint4 a = *reinterpret_cast<const uint4*>(gout + row * ldo + (size_t)h * FHD + sub * 8);
+        const uint4 c = *reinterpret_cast<const uint4*>(out + row * ldo + (size_t)h * FHD + sub * 8);
+        const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
+        const __nv_bfloat162* pc = reinterpret_cast<const __nv_bfloat162*>(&c);
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-    if (lane == 0) delta[((size_t)(row / S) * NH + h) * S + (row % S)] = d;
+        for (int i = 0; i < 4; ++i) {
+            const float2 fa = __bfloat1622float2(pa[i]), fc = __bfloat1622float2(pc[i]);
+            d = fmaf(fa.x, fc.x, fmaf(fa.y, fc.y, d));
+        }
+    }
+    d += __shfl_xor_sync(0xffffffffu, d, 1);
+    d += __shfl_xor_sync(0xffffffffu, d, 2);
+    d += __shfl_xor_sync(0xffffffffu, d, 4);
+    if (sub == 0 && gid < total) delta[((size_t)(row / S) * NH + h) * S + (row % S)] = d;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -767,7 +778,7 @@ int flash_attention_backward_umma(bf16* gq, int ldgq, bf16* gk, bf16* gv, int ld
     if (HD != FHD || NKV <= 0 || NH % NKV) return -1;
     if ((ldq % 8) || (ldkv % 8) || (ldo % 8) || (ldgkv % 8) || (ldgq % 4) || (((uintptr_t)q) & 15) || (((uintptr_t)k) & 15) ||
         (((uintptr_t)v) & 15) || (((uintptr_t)gout) & 15) || (((uintptr_t)gk) & 15) || (((uintptr_t)gv) & 15) || (((uintptr_t)gq) & 7) ||
-        (((uintptr_t)out) & 3))
+        (((uintptr_t)out) & 15))
         return -2;
     static bool attr_done = false;
     if (!attr_done) {
@@ -785,8 +796,8 @@ int flash_attention_backward_umma(bf16* gq, int ldgq, bf16* gk, bf16* gv, int ld
     if (!rc) rc = make_rows_map(&tg, gout, (uint64_t)NH * HD, rows, ldo, FQ);
     if (rc) return rc;
     cudaMemsetAsync(dq_acc, 0, rows * QD * sizeof(float), st);
-    const long warps = (long)rows * NH;
-    flash_delta_umma_kernel<<<(int)((warps * 32 + 255) / 256), 256, 0, st>>>(delta, gout, out, ldo, B, S, NH);
+    const long groups = (long)rows * NH;   // eight lanes each
+    flash_delta_umma_kernel<<<(int)((groups * 8 + 255) / 256), 256, 0, st>>>(delta, gout, out, ldo, B, S, NH);
 #ifdef BMB_TRACE
     long long* trace = nullptr;
     cudaMalloc(&trace, 10 * 32 * sizeof(long long));

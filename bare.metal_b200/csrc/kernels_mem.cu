@@ -402,15 +402,36 @@ template <typename T>
 __global__ void swiglu_forward_kernel(T* __restrict__ out, int ldo, const T* __restrict__ gate, const T* __restrict__ up, int ldgu,
                                       int rows, int HV) {
     constexpr int V = Vec<T>::N;
-    const long i = blockIdx.x * (long)blockDim.x + threadIdx.x;
-    if (i >= (long)rows * HV) return;
-    const int r = (int)(i / HV), c = (int)(i - (long)r * HV) * V;
-    float g[V], u[V], o[V];
-    Vec<T>::load(gate + (size_t)r * ldgu + c, g);
-    Vec<T>::load(up + (size_t)r * ldgu + c, u);
+    constexpr int U = 2;  // vectors per thread, both requested before either is used
+    const long total = (long)rows * HV;
+    const long i0 = (blockIdx.x * (long)blockDim.x) * U + threadIdx.x;
+    float g[U][V], u[U][V];
+    int r[U], c[U];
 #pragma unroll
-    for (int j = 0; j < V; ++j) o[j] = g[j] / (1.0f + expf(-g[j])) * u[j];
-    Vec<T>::store(out + (size_t)r * ldo + c, o);
+    for (int k = 0; k < U; ++k) {
+        const long i = i0 + (long)k * blockDim.x;
+        if (i < total) {
+            r[k] = (int)(i / HV);
+            c[k] = (int)(i - (long)r[k] * HV) * V;
+            Vec<T>::load(gate + (size_t)r[k] * ldgu + c[k], g[k]);
+            Vec<T>::load(up + (size_t)r[k] * ldgu + c[k], u[k]);
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+        const long i = i0 + (long)k * blockDim.x;
+        if (i < total) {
+            float o[V];
+#pragma unroll
+            for (int j = 0; j < V; ++j) {
+                // bf16 output carries 8 mantissa bits: the fast exponential and division are far inside its rounding; the fp32
+                // path keeps the exact forms the parity tests compare against
+                if (sizeof(T) == 2) o[j] = __fdividef(g[k][j], 1.0f + __expf(-g[k][j])) * u[k][j];
+                else o[j] = g[k][j] / (1.0f + expf(-g[k][j])) * u[k][j];
+            }
+            Vec<T>::store(out + (size_t)r[k] * ldo + c[k], o);
+        }
+    }
 }
 template <typename T>
 __global__ void swiglu_backward_kernel(T* __restrict__ ggate, T* __restrict__ gup, int ldg, const T* __restrict__ gate,
@@ -436,7 +457,7 @@ template <typename T> int swiglu_forward(T* out, int ldo, const T* gate, const T
     constexpr int V = Vec<T>::N;
     if (H % V || ldo % V || ldgu % V || !aligned16(gate) || !aligned16(up) || !aligned16(out)) return -1;
     const long n = (long)rows * (H / V);
-    swiglu_forward_kernel<T><<<ceil_div(n, 256), 256, 0, st>>>(out, ldo, gate, up, ldgu, rows, H / V);
+    swiglu_forward_kernel<T><<<ceil_div(n, 512), 256, 0, st>>>(out, ldo, gate, up, ldgu, rows, H / V);
     return 0;
 }
 template <typename T>
