@@ -308,6 +308,55 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                     c0 += 64;
                     continue;
                 }
+                if (bf16_fast && col0 + 32 <= p.N) {
+                    // 32-column remainder of a tile whose width is not a multiple of 64 (e.g. 160): same staging, 64 payload bytes
+                    // per row, 4 lanes per row and 8 rows per instruction on the way out
+                    uint32_t r[32];
+                    tmem_ld_32x32(taddr0 + c0, r);
+                    const int sub4 = lane & 3, rgrp8 = lane >> 2;
+                    if (p.R) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int rr = rgrp8 + 8 * i, grow = row_base + rr;
+                            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                            if (grow < p.M) v = *(const uint4*)(p.R + (size_t)grow * p.ldr + col0 + sub4 * 8);
+                            *(uint4*)(stg + rr * STG_PITCH + sub4 * 16) = v;
+                        }
+                        __syncwarp();
+                    }
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        float f[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(r[v * 8 + i]);
+                        if (p.R) {
+                            const uint4 rv = *(const uint4*)(my_row + v * 16);
+                            const __nv_bfloat162* rb = (const __nv_bfloat162*)&rv;
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const float2 t = __bfloat1622float2(rb[i]);
+                                f[2 * i] += t.x;
+                                f[2 * i + 1] += t.y;
+                            }
+                        }
+                        uint4 o;
+                        __nv_bfloat162* ob = (__nv_bfloat162*)&o;
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) ob[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+                        *(uint4*)(my_row + v * 16) = o;
+                    }
+                    __syncwarp();
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int rr = rgrp8 + 8 * i, grow = row_base + rr;
+                        if (grow < p.M)
+                            *(uint4*)((__nv_bfloat16*)p.C + (size_t)grow * p.ldc + col0 + sub4 * 8) = *(const uint4*)(stg + rr * STG_PITCH + sub4 * 16);
+                    }
+                    __syncwarp();
+                    c0 += 32;
+                    continue;
+                }
                 if (f32_fast && col0 + 32 <= p.N) {
                     uint32_t r[32];
                     tmem_ld_32x32(taddr0 + c0, r);
