@@ -241,6 +241,25 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             m0 += (int)rank * BM;
             const int buf = it & 1;
             const uint32_t acc_ph = (it >> 1) & 1;
+            const int sub = lane & 7, rgrp = lane >> 3;
+            const int row_base = m0 + q * 32;
+            const bool c_al = (((uintptr_t)p.C) & 15) == 0;
+            const bool bf16_fast = p.out_mode == GEMM_OUT_BF16 && c_al && (p.ldc % 8) == 0 && (n0 % 8) == 0 &&
+                                   (!p.R || ((((uintptr_t)p.R) & 15) == 0 && (p.ldr % 8) == 0));
+            const bool f32_fast = p.out_mode != GEMM_OUT_BF16 && c_al && (p.ldc % 4) == 0 && (n0 % 4) == 0;
+            // The residual does not depend on the accumulator: the first chunk's rows are requested before the wait for the
+            // UMMAs, every later chunk's while the previous chunk is converted and stored (a global load issued only when its
+            // chunk comes up costs a full memory latency per chunk, which made the short-K projections epilogue-bound).
+            uint4 rpre[8];
+            bool rpre_valid = false;
+            if (bf16_fast && p.R && 64 <= p.BN && n0 + 64 <= p.N) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int grow = row_base + rgrp + 4 * i;
+                    rpre[i] = grow < p.M ? *(const uint4*)(p.R + (size_t)grow * p.ldr + n0 + sub * 8) : make_uint4(0u, 0u, 0u, 0u);
+                }
+                rpre_valid = true;
+            }
             ok = mbar_wait(&bars.acc_full[buf], acc_ph, abort_flag);
             ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld is warp-collective: leave together or not at all
             if (!ok) break;
@@ -252,12 +271,6 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             // the residual arrives) as whole 128-byte row segments, 4 rows per instruction.
             uint8_t* stg = smem + NST * (A_STAGE_BYTES + BST) + q * STG_WARP_BYTES;
             uint8_t* my_row = stg + lane * STG_PITCH;
-            const int sub = lane & 7, rgrp = lane >> 3;
-            const int row_base = m0 + q * 32;
-            const bool c_al = (((uintptr_t)p.C) & 15) == 0;
-            const bool bf16_fast = p.out_mode == GEMM_OUT_BF16 && c_al && (p.ldc % 8) == 0 && (n0 % 8) == 0 &&
-                                   (!p.R || ((((uintptr_t)p.R) & 15) == 0 && (p.ldr % 8) == 0));
-            const bool f32_fast = p.out_mode != GEMM_OUT_BF16 && c_al && (p.ldc % 4) == 0 && (n0 % 4) == 0;
             for (int c0 = 0; c0 < p.BN;) {
                 const int col0 = n0 + c0;
                 if (col0 >= p.N) break;
@@ -266,14 +279,25 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                     tmem_ld_32x32(taddr0 + c0, ra);
                     tmem_ld_32x32(taddr0 + c0 + 32, rb2);
                     if (p.R) {
+                        if (!rpre_valid) {
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const int rr = rgrp + 4 * i, grow = row_base + rr;
-                            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                            if (grow < p.M) v = *(const uint4*)(p.R + (size_t)grow * p.ldr + col0 + sub * 8);
-                            *(uint4*)(stg + rr * STG_PITCH + sub * 16) = v;
+                            for (int i = 0; i < 8; ++i) {
+                                const int grow = row_base + rgrp + 4 * i;
+                                rpre[i] = grow < p.M ? *(const uint4*)(p.R + (size_t)grow * p.ldr + col0 + sub * 8) : make_uint4(0u, 0u, 0u, 0u);
+                            }
                         }
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) *(uint4*)(stg + (rgrp + 4 * i) * STG_PITCH + sub * 16) = rpre[i];
                         __syncwarp();
+                        // the next 64-column chunk's residual, if there is one
+                        rpre_valid = c0 + 128 <= p.BN && col0 + 128 <= p.N;
+                        if (rpre_valid) {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const int grow = row_base + rgrp + 4 * i;
+                                rpre[i] = grow < p.M ? *(const uint4*)(p.R + (size_t)grow * p.ldr + col0 + 64 + sub * 8) : make_uint4(0u, 0u, 0u, 0u);
+                            }
+                        }
                     }
                     tmem_ld_wait();
 #pragma unroll
