@@ -39,7 +39,7 @@ constexpr float LOG2E_F = 1.4426950408889634f;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
 
 struct __align__(8) FwdBars {
-    uint64_t q_full, kv_full[2], kv_empty[2], s_full[2], p_ready[2], pv_done[2];
+    uint64_t q_full, kv_full[2], kv_empty[2], s_full[2], s_free[2], p_ready[2], pv_done[2];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -98,6 +98,7 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             mbar_init(&bars.kv_full[i], 1);
             mbar_init(&bars.kv_empty[i], 1);
             mbar_init(&bars.s_full[i], 1);
+            mbar_init(&bars.s_free[i], 4);
             mbar_init(&bars.p_ready[i], 4);
             mbar_init(&bars.pv_done[i], 1);
         }
@@ -166,21 +167,27 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 if (n_b > 0) issue_qk(1, 0);
             }
             for (int j = 0; j < n_tiles && ok; ++j) {
+                // S of the NEXT key tile is issued as soon as the softmax warps have read this tile's S out of TMEM (s_free),
+                // i.e. before P V of this tile: the scores of tile j+1 are ready when the softmax of tile j ends, and the
+                // softmax of tile j+1 runs while the tensor core does P V of tile j.
                 bool next_loaded = false;
+                for (int x = 0; x < 2 && ok; ++x) {
+                    const int n_this = x ? n_b : n_a;
+                    if (j + 1 >= n_this) continue;
+                    if (!mbar_wait(&bars.s_free[x], j & 1, abort_flag)) { ok = false; break; }
+                    if (!next_loaded) {
+                        if (!mbar_wait(&bars.kv_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+                        next_loaded = true;
+                    }
+                    tc_fence_after_sync();
+                    issue_qk(x, j + 1);
+                }
                 for (int x = 0; x < 2 && ok; ++x) {
                     const int n_this = x ? n_b : n_a;
                     if (j >= n_this) continue;
                     if (!mbar_wait(&bars.p_ready[x], j & 1, abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
                     issue_pv(x, j);
-                    if (j + 1 < n_this) {
-                        if (!next_loaded) {
-                            if (!mbar_wait(&bars.kv_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
-                            tc_fence_after_sync();
-                            next_loaded = true;
-                        }
-                        issue_qk(x, j + 1);
-                    }
                 }
                 if (ok) umma_commit(&bars.kv_empty[j & 1]);  // every UMMA that reads stage j has been issued
             }
@@ -208,6 +215,10 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 #pragma unroll
             for (int ch = 0; ch < 4; ++ch) tmem_ld_32x32(s_addr + ch * 32, v[ch]);
             tmem_ld_wait();
+            // the scores are in registers: their TMEM columns may receive the next key tile
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars.s_free[x]);
             const int k0 = j * FK;
             if (j == n_mine - 1 || k0 + FK > p.S) {  // diagonal tile or ragged end: mask keys after the query / past the end
 #pragma unroll
