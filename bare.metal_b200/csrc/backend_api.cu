@@ -39,8 +39,9 @@ struct bmc_ctx_s {
     std::vector<cudaEvent_t> gt_events;  // pairs (begin, end)
     std::vector<double> gt_flops;
     size_t gt_used;
-    cudaGraph_t graph;
-    cudaGraphExec_t graph_exec;
+    cudaGraph_t graphs[2];
+    cudaGraphExec_t graph_execs[2];
+    int graph_slot;  // slot 0: inference session, slot 1: trainer
     // side stream (bmc_side_begin / _end / _wait): work that may overlap the main stream
     cudaStream_t side_stream;
     cudaEvent_t side_fork, side_done[16];
@@ -151,8 +152,8 @@ bmc_ctx_t* bmc_create(int device_ordinal) {
     ctx->attn_scratch_bytes = 0;
     ctx->gemm_timing = false;
     ctx->gt_used = 0;
-    ctx->graph = nullptr;
-    ctx->graph_exec = nullptr;
+    for (int i = 0; i < 2; ++i) { ctx->graphs[i] = nullptr; ctx->graph_execs[i] = nullptr; }
+    ctx->graph_slot = 0;
     if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) { delete ctx; return nullptr; }
     if (cudaMalloc(&ctx->d_err, sizeof(int)) != cudaSuccess) { delete ctx; return nullptr; }
     cudaMemset(ctx->d_err, 0, sizeof(int));
@@ -186,8 +187,10 @@ void bmc_destroy(bmc_ctx_t* ctx) {
         cudaEventDestroy(ctx->ev1[i]);
     }
     for (auto e : ctx->gt_events) cudaEventDestroy(e);
-    if (ctx->graph_exec) cudaGraphExecDestroy(ctx->graph_exec);
-    if (ctx->graph) cudaGraphDestroy(ctx->graph);
+    for (int i = 0; i < 2; ++i) {
+        if (ctx->graph_execs[i]) cudaGraphExecDestroy(ctx->graph_execs[i]);
+        if (ctx->graphs[i]) cudaGraphDestroy(ctx->graphs[i]);
+    }
     cudaStreamDestroy(ctx->stream);
     delete ctx;
 }
@@ -597,21 +600,40 @@ int bmc_decode_advance(bmc_ctx_t* ctx, int* d_pos) {
     BMC_CHECK_CTX(ctx);
     return note(ctx, decode_advance(d_pos, ctx->stream));
 }
+int bmc_graph_select(bmc_ctx_t* ctx, int slot) {
+    BMC_CHECK_CTX(ctx);
+    if (slot < 0 || slot > 1) return -1;
+    ctx->graph_slot = slot;
+    return 0;
+}
 int bmc_graph_begin(bmc_ctx_t* ctx) {
     BMC_CHECK_CTX(ctx);
-    if (ctx->graph_exec) { cudaGraphExecDestroy(ctx->graph_exec); ctx->graph_exec = nullptr; }
-    if (ctx->graph) { cudaGraphDestroy(ctx->graph); ctx->graph = nullptr; }
+    const int k = ctx->graph_slot;
+    if (ctx->graph_execs[k]) { cudaGraphExecDestroy(ctx->graph_execs[k]); ctx->graph_execs[k] = nullptr; }
+    if (ctx->graphs[k]) { cudaGraphDestroy(ctx->graphs[k]); ctx->graphs[k] = nullptr; }
     return cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess ? 0 : -1;
 }
 int bmc_graph_end(bmc_ctx_t* ctx) {
     BMC_CHECK_CTX(ctx);
-    if (cudaStreamEndCapture(ctx->stream, &ctx->graph) != cudaSuccess || !ctx->graph) return -1;
-    return cudaGraphInstantiate(&ctx->graph_exec, ctx->graph, 0) == cudaSuccess ? 0 : -2;
+    const int k = ctx->graph_slot;
+    if (cudaStreamEndCapture(ctx->stream, &ctx->graphs[k]) != cudaSuccess || !ctx->graphs[k]) {
+        cudaGetLastError();  // a failed capture must not poison the status of later launches
+        ctx->graphs[k] = nullptr;
+        return -1;
+    }
+    if (cudaGraphInstantiate(&ctx->graph_execs[k], ctx->graphs[k], 0) != cudaSuccess) {
+        cudaGetLastError();
+        ctx->graph_execs[k] = nullptr;
+        return -2;
+    }
+    return 0;
 }
 int bmc_graph_launch(bmc_ctx_t* ctx) {
     BMC_CHECK_CTX(ctx);
-    if (!ctx->graph_exec) return -1;
-    return cudaGraphLaunch(ctx->graph_exec, ctx->stream) == cudaSuccess ? 0 : -2;
+    const int k = ctx->graph_slot;
+    if (!ctx->graph_execs[k]) return -1;
+    return cudaGraphLaunch(ctx->graph_execs[k], ctx->stream) == cudaSuccess ? 0 : -2;
 }
+int bmc_gemm_timing_enabled(bmc_ctx_t* ctx) { return ctx && ctx->gemm_timing ? 1 : 0; }
 
 }  // extern "C"

@@ -355,6 +355,7 @@ static int run_step(bm_session_t* s) {
         return -1;
     }
     int rc;
+    bmc_graph_select(be, 0);
     if (s->graph_ready == 2) {
         rc = bmc_graph_launch(be);
     } else if (s->graph_ready == 1) {

@@ -84,6 +84,8 @@ static void free_activations(bm_trainer_t* t) {
 /* (Re)allocate everything whose size depends on the batch. */
 static int ensure_batch(bm_trainer_t* t, int B) {
     if (B <= t->B_cap) return 0;
+    t->graph_B = 0; /* every activation buffer moves: a captured step is stale */
+    t->graph_eager_steps = 0;
     free_activations(t);
     bmc_ctx_t* be = t->ctx->be;
     const bm_arch_t* a = &t->model->arch;
@@ -199,6 +201,9 @@ bm_trainer_t* bm_create_trainer(bm_context_t* ctx, bm_model_t* model, const bm_t
         return NULL;
     }
     t->side_stream = getenv("BM_NO_SIDE_STREAM") ? 0 : 1;
+    t->graph_mode = getenv("BM_NO_TRAIN_GRAPH") ? 0 : 1;
+    t->graph_B = 0;
+    t->graph_eager_steps = 0;
     const char* rq = getenv("BM_REF_QUIRKS");
     if (rq && rq[0] == '1') bmx_trainer_set_option(t, "ref_quirks", 1);
     BM_LOG_INFO("Trainer created: %d weight tensors, S=%d, D=%d", t->n_params, t->S, a->dim);
@@ -365,6 +370,44 @@ static int step_enqueue(bm_trainer_t* t, int B, const uint8_t* d_attn_mask, cons
         TRY(bmc_memset(be, t->d_grad, 0, t->P * sizeof(float)));
         if (t->ref_input_grad_carry) TRY(bmc_memset(be, t->d_gx_carry, 0, (size_t)t->S * t->model->arch.dim * sizeof(float)));
         if (t->dp) bm_dp_begin_window(t->dp);
+    }
+    /* The plain training step (no masks, one GPU, no profiling) replays its forward + backward as one CUDA graph from the third
+     * step on: about 850 launches become one, which matters to the synchronous bm_train_step, where the host cannot run
+     * ahead of the device. AdamW stays outside: its bias corrections change every step and travel as kernel arguments. */
+    const int graphable = t->graph_mode && train && !d_attn_mask && !d_row_weight && !t->dp && !t->profile && !bmc_gemm_timing_enabled(be);
+    if (graphable) {
+        int replayed = 0;
+        bmc_graph_select(be, 1);
+        if (t->graph_B == B) {
+            if (bmc_graph_launch(be) == 0) replayed = 1;
+            else t->graph_B = 0;
+        } else if (t->graph_eager_steps >= 2) {
+            int rc = bmc_graph_begin(be);
+            if (rc == 0) {
+                rc = forward_and_loss(t, B, NULL, NULL, 1);
+                if (rc == 0) rc = backward(t, B, NULL);
+                const int rc2 = bmc_graph_end(be);
+                if (rc == 0 && rc2 == 0 && bmc_graph_launch(be) == 0) {
+                    t->graph_B = B;
+                    replayed = 1;
+                } else {
+                    BM_LOG_ERROR("train step: CUDA graph capture failed (%d, %d); continuing without a graph", rc, rc2);
+                    t->graph_mode = 0;
+                }
+            } else {
+                t->graph_mode = 0;
+            }
+        }
+        if (replayed) {
+            t->window_microsteps += B;
+            t->accum_count++;
+            if (t->accum_count >= accum) {
+                TRY(adamw_apply(t));
+                t->accum_count = 0;
+            }
+            return 0;
+        }
+        t->graph_eager_steps++;
     }
     if (t->profile) bmc_timer_begin(be, 0);
     TRY(forward_and_loss(t, B, d_attn_mask, d_row_weight, train));
@@ -577,7 +620,11 @@ int bmx_trainer_set_option(bm_trainer_t* t, const char* key, int value) {
     bmc_ctx_t* be = t->ctx->be;
     const int all = strcmp(key, "ref_quirks") == 0;
     int known = 0;
+    /* any switch changes what a step enqueues: a captured graph is dropped and re-made after two eager steps */
+    t->graph_B = 0;
+    t->graph_eager_steps = 0;
     if (strcmp(key, "side_stream") == 0) { t->side_stream = value ? 1 : 0; return 0; }
+    if (strcmp(key, "train_graph") == 0) { t->graph_mode = value ? 1 : 0; return 0; }
     if (all || strcmp(key, "ref_norm_grad") == 0) { t->ref_norm_grad = value ? 1 : 0; known = 1; }
     if (all || strcmp(key, "ref_input_grad_carry") == 0) {
         known = 1;

@@ -203,6 +203,10 @@ int bmc_decode_argmax(bmc_ctx_t* ctx, int* d_out, const float* d_logits, int NB,
 int bmc_decode_argmax_advance(bmc_ctx_t* ctx, int* d_out, const float* d_logits, int NB, int V, int* d_pos);
 int bmc_decode_advance(bmc_ctx_t* ctx, int* d_pos);
 /* Record everything enqueued between begin and end into a CUDA graph and replay it with launch (one graph per context). */
+/* two graph slots per context (0 = default, used by the inference session; 1 = used by the trainer); begin/end/launch act on the
+ * selected slot */
+int bmc_graph_select(bmc_ctx_t* ctx, int slot);
+int bmc_gemm_timing_enabled(bmc_ctx_t* ctx);
 int bmc_graph_begin(bmc_ctx_t* ctx);
 int bmc_graph_end(bmc_ctx_t* ctx);
 int bmc_graph_launch(bmc_ctx_t* ctx);
