@@ -12,9 +12,14 @@ JSON line on rank 0:
   e2e    : the same through the public API bm_train_step() with HOST int32 buffers — host->device copy of
            inputs/targets and device->host read of the loss inside the timed region, every step;
   roofline: the tcgen05 GEMM kernel, achieved TFLOP/s = algorithmic 2*M*N*K FLOPs / per-launch CUDA-event time
-           collected live during the timed steps, against the measured bf16 peak (MEASURED_PEAKS.json);
+           collected live in two more steps of the same workload right after the timed ones (there the weight-gradient
+           GEMMs run on the main stream; in the timed steps they overlap other kernels, which an event pair would
+           also measure), against the measured bf16 peak (MEASURED_PEAKS.json);
   cpu_baseline: the reference's own host code + kernels running on this box's CPU cores (oracle/_ref), on a
            bounded sample of the same model (rank 0, N = 1 only).
+
+Other workloads (--workload attention | gemm | decode): the isolated GQA flash attention, the linear-layer GEMMs per
+shape, and Q8 prefill + greedy decode at batch 1 and 64; one JSON line per case.
 
 Reference arm (--impl reference): times oracle/_ref (the reference's C11 host code and its Metal kernel sources
 compiled for the CPU) on the host cores, same model, each step a bounded sample (1 sequence x 32 tokens).

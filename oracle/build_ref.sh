@@ -8,7 +8,7 @@
 # src/kernels/forward.metal:1810 and ATTN_MAXS in src/kernels/backward.metal:664, both 256) are raised
 # so the same kernels can serve as the oracle for sequences longer than 256 tokens.
 #
-# usage: oracle/build_ref.sh [reference_dir]      (default: $BM_REFERENCE or /root/reference)
+# usage: oracle/build_ref.sh [reference_dir]      (default: $BM_REFERENCE, else the checkout location built into the line below)
 set -euo pipefail
 HERE="$(cd "$(dirname "$0")" && pwd)"
 REF="${1:-${BM_REFERENCE:-/root/reference}}"
