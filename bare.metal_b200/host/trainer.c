@@ -204,6 +204,7 @@ bm_trainer_t* bm_create_trainer(bm_context_t* ctx, bm_model_t* model, const bm_t
     t->graph_mode = getenv("BM_NO_TRAIN_GRAPH") ? 0 : 1;
     t->graph_B = 0;
     t->graph_eager_steps = 0;
+    t->graph_seen_B = 0;
     const char* rq = getenv("BM_REF_QUIRKS");
     if (rq && rq[0] == '1') bmx_trainer_set_option(t, "ref_quirks", 1);
     BM_LOG_INFO("Trainer created: %d weight tensors, S=%d, D=%d", t->n_params, t->S, a->dim);
@@ -378,6 +379,11 @@ static int step_enqueue(bm_trainer_t* t, int B, const uint8_t* d_attn_mask, cons
     if (graphable) {
         int replayed = 0;
         bmc_graph_select(be, 1);
+        if (t->graph_seen_B != B) { /* scratch buffers are sized by eager steps of THIS batch before anything is captured */
+            t->graph_seen_B = B;
+            t->graph_eager_steps = 0;
+            t->graph_B = 0;
+        }
         if (t->graph_B == B) {
             if (bmc_graph_launch(be) == 0) replayed = 1;
             else t->graph_B = 0;

@@ -206,3 +206,29 @@ def test_resident_step_equals_host_step(product):
     assert product.bmx_train_last_loss(t2.tr) == l1
     assert product.bmx_trainer_launch_count(t2.tr) > 0
     t1.close(); t2.close()
+
+
+def test_graph_replay_matches_eager_steps_with_changing_batch(product):
+    """From the third plain step on forward + backward are replayed as a CUDA graph; losses and weights must be the same as with
+    the graph switched off, also when the batch size changes in between (the graph is dropped and re-made)."""
+    a = bmapi.make_arch("small")
+    w = bmapi.make_weights(a)
+    S = 64
+    plan = [2, 2, 2, 2, 3, 3, 3, 3, 2, 2, 2, 2]
+    x, y = bmapi.lcg_batch(sum(plan), S, a.vocab_size)
+    results = []
+    for graph in (1, 0):
+        tr = oc.LibTrainer(product, "gpu", a, w, S, BF16, bmapi.train_config(seq_len=S), quirks=False, tag=f"g{graph}")
+        assert product.bmx_trainer_set_option(tr.tr, b"train_graph", graph) == 0
+        assert product.bmx_trainer_set_option(tr.tr, b"side_stream", 0) == 0   # weight gradients in a fixed order on one stream
+        losses, off = [], 0
+        for B in plan:
+            losses.append(tr.step(np.ascontiguousarray(x[off:off + B]), np.ascontiguousarray(y[off:off + B])))
+            off += B
+        weights = [tr.read(bmapi.BMX_WEIGHT, i) for i in range(tr.n_tensors())]
+        tr.close()
+        results.append((losses, weights))
+    (l1, w1), (l0, w0) = results
+    assert np.allclose(l1, l0, rtol=0, atol=2e-3), (l1, l0)
+    for u, v in zip(w1, w0):
+        assert oc.rel_err(u, v) < 1e-3
