@@ -200,7 +200,7 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         const int qi = q0 + x * FQ + r;            // query position in the sequence
         const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
         const uint32_t s_addr = lane_addr + x * FK, o_addr = lane_addr + 2 * FK + x * FHD;
-        uint8_t* sPx = sP + x * P_BYTES;
+        const uint32_t sPx_addr = smem_u32(sP + x * P_BYTES);
         const float sl2 = p.scale * LOG2E_F;
         const int n_mine = x ? n_b : n_a;
         float m_ref = -INFINITY;   // the maximum O and l are currently referenced to (log2 domain)
@@ -288,10 +288,9 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             // P row -> swizzled smem (A operand of P V): key half = c / 8, 16-byte chunk inside the 128-byte row = c % 8
 #pragma unroll
             for (int c = 0; c < 16; ++c) {
-                uint8_t* prow = sPx + (c >> 3) * (FQ * 128) + r * 128;
+                const uint32_t prow = sPx_addr + (c >> 3) * (FQ * 128) + r * 128;
                 const int cc = (c & 7) ^ (r & 7);
-                *reinterpret_cast<uint4*>(prow + cc * 16) =
-                    make_uint4(v[c >> 2][(c & 3) * 4], v[c >> 2][(c & 3) * 4 + 1], v[c >> 2][(c & 3) * 4 + 2], v[c >> 2][(c & 3) * 4 + 3]);
+                st_shared_v4(prow + cc * 16, v[c >> 2][(c & 3) * 4], v[c >> 2][(c & 3) * 4 + 1], v[c >> 2][(c & 3) * 4 + 2], v[c >> 2][(c & 3) * 4 + 3]);
             }
             tc_fence_before_sync();
             fence_proxy_async_smem();  // generic-proxy smem writes -> visible to the UMMA (async proxy) reads
@@ -594,13 +593,13 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             if (cw == 0 && lane == 0) BTRACE(7, it);
             // rows of P and dS: key half = cg / 2, 16-byte chunks (cg & 1) * 4 .. +3 of the 128-byte row
             {
-                uint8_t* prow = sP + pb * P_BYTES + (cg >> 1) * (FQ * 128) + r * 128;
-                uint8_t* drow = sD + pb * P_BYTES + (cg >> 1) * (FQ * 128) + r * 128;
+                const uint32_t prow = smem_u32(sP + pb * P_BYTES + (cg >> 1) * (FQ * 128) + r * 128);
+                const uint32_t drow = smem_u32(sD + pb * P_BYTES + (cg >> 1) * (FQ * 128) + r * 128);
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     const int cc = ((cg & 1) * 4 + c) ^ (r & 7);
-                    *reinterpret_cast<uint4*>(prow + cc * 16) = make_uint4(pp[4 * c], pp[4 * c + 1], pp[4 * c + 2], pp[4 * c + 3]);
-                    *reinterpret_cast<uint4*>(drow + cc * 16) = make_uint4(dd[4 * c], dd[4 * c + 1], dd[4 * c + 2], dd[4 * c + 3]);
+                    st_shared_v4(prow + cc * 16, pp[4 * c], pp[4 * c + 1], pp[4 * c + 2], pp[4 * c + 3]);
+                    st_shared_v4(drow + cc * 16, dd[4 * c], dd[4 * c + 1], dd[4 * c + 2], dd[4 * c + 3]);
                 }
             }
             tc_fence_before_sync();
