@@ -5,11 +5,12 @@
 // tile. For each tile of 128 keys up to the diagonal and each X:
 //   S_X = Q_X K^T        UMMA 128x128x64, A = Q_X (K-major smem), B = K tile (K-major smem), accumulator in TMEM
 //   softmax              one warpgroup per X, one thread per query row: the S row is pulled into registers,
-//                        running max / sum in the log2 domain, P written as bf16 into a 128B-swizzled smem tile;
+//                        running max / sum in the log2 domain, P written back to TMEM as packed bf16 pairs
+//                        (tcgen05.st, 64 columns per tile: P never touches shared memory);
 //                        O_X in TMEM is rescaled only when the row maximum grew by more than 2^8 since the value the
 //                        accumulator is referenced to (the stale reference cancels in the final division)
-//   O_X += P_X V         UMMA 128x64x128, A = P_X (K-major smem), B = V tile (MN-major smem: the reduction index,
-//                        the key, is the row of V), accumulator in TMEM
+//   O_X += P_X V         UMMA 128x64x128, A = P_X read from TMEM (lane = query row, column = key pair), B = V tile
+//                        (MN-major smem: the reduction index, the key, is the row of V), accumulator in TMEM
 // The single UMMA-issuing thread interleaves the two tiles (PV_A(j), QK_A(j+1), PV_B(j), QK_B(j+1), ...) so that
 // the tensor core works on one tile while the other tile's warpgroup does its softmax. K/V tiles are
 // double-buffered by a TMA producer warp. 10 warps: TMA, UMMA, 4 + 4 softmax.
@@ -32,9 +33,10 @@ constexpr int FHD = 64;
 constexpr int Q_BYTES = FQ * FHD * 2;        // 16 KB per Q tile
 constexpr int KV_TILE_BYTES = FK * FHD * 2;  // 16 KB each for K and V
 constexpr int P_BYTES = FQ * FK * 2;         // 32 KB per P tile
-constexpr int FWD_DYN_SMEM = 2 * Q_BYTES + 2 * 2 * KV_TILE_BYTES + 2 * P_BYTES + 1024;
+constexpr int FWD_DYN_SMEM = 2 * Q_BYTES + 2 * 2 * KV_TILE_BYTES + 1024;  // Q x 2 tiles, K and V x 2 stages; P lives in tensor memory
 constexpr int FWD_THREADS = 320;
-constexpr uint32_t FWD_TMEM_COLS = 512;  // S_A [0,128) S_B [128,256) O_A [256,320) O_B [320,384)
+constexpr uint32_t FWD_TMEM_COLS = 512;  // S_A [0,128) S_B [128,256) O_A [256,320) O_B [320,384) P_A [384,448) P_B [448,512)
+constexpr uint32_t FWD_TMEM_P = 2 * FK + 2 * FHD;  // P as packed bf16 pairs: 128 keys = 64 columns per query tile
 constexpr float LOG2E_F = 1.4426950408889634f;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
 
@@ -80,7 +82,6 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     uint8_t* sQ = smem;                          // 2 tiles
     uint8_t* sK = sQ + 2 * Q_BYTES;              // 2 stages
     uint8_t* sV = sK + 2 * KV_TILE_BYTES;        // 2 stages
-    uint8_t* sP = sV + 2 * KV_TILE_BYTES;        // 2 tiles x [2 key halves][128 rows][128 B]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int qb = (int)gridDim.x - 1 - (int)blockIdx.x;  // latest (longest) query blocks first
@@ -142,7 +143,6 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             const uint64_t qd0 = umma_smem_desc_sw128(smem_u32(sQ), 16, 1024);
             const uint64_t kd0 = umma_smem_desc_sw128(smem_u32(sK), 16, 1024);
             const uint64_t vd0 = umma_smem_desc_sw128(smem_u32(sV), FK * 128, 1024);
-            const uint64_t pd0 = umma_smem_desc_sw128(smem_u32(sP), 16, 1024);
             auto issue_qk = [&](int x, int j) {
                 const uint64_t kd = kd0 + (uint64_t)((j & 1) * (KV_TILE_BYTES >> 4));
                 const uint64_t qd = qd0 + (uint64_t)(x * (Q_BYTES >> 4));
@@ -152,11 +152,10 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             };
             auto issue_pv = [&](int x, int j) {
                 const uint64_t vd = vd0 + (uint64_t)((j & 1) * (KV_TILE_BYTES >> 4));
-                const uint64_t pd = pd0 + (uint64_t)(x * (P_BYTES >> 4));
 #pragma unroll
                 for (int k = 0; k < FK / 16; ++k)
-                    // P: two 64-key halves of [128 rows x 128 B], 16 keys = 32 B inside a half; V: 16 keys = 2048 B
-                    umma_bf16_ss(tmem + 2 * FK + x * FHD, pd + (uint64_t)((k >> 2) * ((FQ * 128) >> 4) + (k & 3) * 2), vd + 128 * k, idesc_o,
+                    // P comes from tensor memory (16 keys = 8 columns of bf16 pairs); V: 16 keys = 2048 B
+                    umma_bf16_ts(tmem + 2 * FK + x * FHD, tmem + FWD_TMEM_P + x * (FK / 2) + 8 * k, vd + 128 * k, idesc_o,
                                  (j > 0 || k > 0) ? 1u : 0u);
                 umma_commit(&bars.pv_done[x]);
             };
@@ -200,7 +199,7 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         const int qi = q0 + x * FQ + r;            // query position in the sequence
         const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
         const uint32_t s_addr = lane_addr + x * FK, o_addr = lane_addr + 2 * FK + x * FHD;
-        const uint32_t sPx_addr = smem_u32(sP + x * P_BYTES);
+        const uint32_t p_addr = lane_addr + FWD_TMEM_P + x * (FK / 2);
         const float sl2 = p.scale * LOG2E_F;
         const int n_mine = x ? n_b : n_a;
         float m_ref = -INFINITY;   // the maximum O and l are currently referenced to (log2 domain)
@@ -250,7 +249,8 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 need = true;
             }
             const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-            // probabilities, packed to bf16 in place (pair i, i+1 of chunk ch -> v[ch][i / 2]); four independent sum chains
+            // probabilities, packed to bf16 pairs (keys 2c, 2c+1 -> column c of the P block in tensor memory); four independent sum chains
+            uint32_t pk[2][32];
             float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int ch = 0; ch < 4; ++ch)
@@ -262,7 +262,7 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                     p1 = ex2_approx(p1);
                     ls[(i >> 1) & 3] += p0 + p1;
                     __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
-                    v[ch][i >> 1] = *reinterpret_cast<uint32_t*>(&hh);
+                    pk[ch >> 1][(ch & 1) * 16 + (i >> 1)] = *reinterpret_cast<uint32_t*>(&hh);
                 }
             const float lsum = (ls[0] + ls[1]) + (ls[2] + ls[3]);
             l_run = l_run * corr + lsum;
@@ -282,18 +282,13 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                         for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
                         tmem_st_32x32(o_addr + ch * 32, o);
                     }
-                    tmem_st_wait();
                 }
             }
-            // P row -> swizzled smem (A operand of P V): key half = c / 8, 16-byte chunk inside the 128-byte row = c % 8
-#pragma unroll
-            for (int c = 0; c < 16; ++c) {
-                const uint32_t prow = sPx_addr + (c >> 3) * (FQ * 128) + r * 128;
-                const int cc = (c & 7) ^ (r & 7);
-                st_shared_v4(prow + cc * 16, v[c >> 2][(c & 3) * 4], v[c >> 2][(c & 3) * 4 + 1], v[c >> 2][(c & 3) * 4 + 2], v[c >> 2][(c & 3) * 4 + 3]);
-            }
+            // P row -> tensor memory, where P V reads it as its A operand (this thread's TMEM lane = its query row)
+            tmem_st_32x32(p_addr, pk[0]);
+            tmem_st_32x32(p_addr + 32, pk[1]);
+            tmem_st_wait();
             tc_fence_before_sync();
-            fence_proxy_async_smem();  // generic-proxy smem writes -> visible to the UMMA (async proxy) reads
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars.p_ready[x]);
         }

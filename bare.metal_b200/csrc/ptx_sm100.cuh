@@ -221,6 +221,19 @@ __device__ __forceinline__ void umma_bf16_ss(uint32_t tmem_d, uint64_t adesc, ui
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u)
         : "memory");
 }
+// Same, with the A operand read from tensor memory: lane = row of A, one 32-bit column = two consecutive K elements
+// (16 K elements = 8 columns), i.e. exactly what a 32x32b tensor-memory store of packed bf16 pairs writes.
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
 // Arrive on an mbarrier once every UMMA issued so far by this thread has completed.
 // Implies tcgen05.fence::before_thread_sync. Issued by ONE thread.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
