@@ -58,6 +58,25 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r
         : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// Blackwell's three-input max and packed two-wide fp32 arithmetic: half the issue slots of the scalar forms.
+__device__ __forceinline__ float max3_f(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// (d0, d1) = (a0, a1) * b + c
+__device__ __forceinline__ void fma2_f(float& d0, float& d1, float a0, float a1, float b, float c) {
+    asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %4};\n\tmov.b64 rc, {%5, %5};\n\t"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d0), "=f"(d1)
+        : "f"(a0), "f"(a1), "f"(b), "f"(c));
+}
+// (d0, d1) += (a0, a1)
+__device__ __forceinline__ void add2_f(float& d0, float& d1, float a0, float a1) {
+    asm("{\n\t.reg .b64 ra, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rd, {%0, %1};\n\tadd.rn.f32x2 rd, rd, ra;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "+f"(d0), "+f"(d1)
+        : "f"(a0), "f"(a1));
+}
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -235,7 +254,7 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 #pragma unroll
             for (int ch = 0; ch < 4; ++ch)
 #pragma unroll
-                for (int i = 0; i < 32; ++i) mxp[i & 7] = fmaxf(mxp[i & 7], __uint_as_float(v[ch][i]));
+                for (int i = 0; i < 32; i += 2) mxp[(i >> 1) & 7] = max3_f(mxp[(i >> 1) & 7], __uint_as_float(v[ch][i]), __uint_as_float(v[ch][i + 1]));
             float mx = fmaxf(fmaxf(fmaxf(mxp[0], mxp[1]), fmaxf(mxp[2], mxp[3])), fmaxf(fmaxf(mxp[4], mxp[5]), fmaxf(mxp[6], mxp[7])));
             mx *= sl2;
             // lazy rescale: keep the old reference unless the maximum grew by more than the threshold
@@ -251,20 +270,20 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
             // probabilities, packed to bf16 pairs (keys 2c, 2c+1 -> column c of the P block in tensor memory); four independent sum chains
             uint32_t pk[2][32];
-            float ls[4] = {0.f, 0.f, 0.f, 0.f};
+            float ls[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int ch = 0; ch < 4; ++ch)
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    float p0 = fmaf(__uint_as_float(v[ch][i]), sl2, -m_use);
-                    float p1 = fmaf(__uint_as_float(v[ch][i + 1]), sl2, -m_use);
+                    float p0, p1;
+                    fma2_f(p0, p1, __uint_as_float(v[ch][i]), __uint_as_float(v[ch][i + 1]), sl2, -m_use);
                     p0 = ex2_approx(p0);
                     p1 = ex2_approx(p1);
-                    ls[(i >> 1) & 3] += p0 + p1;
+                    add2_f(ls[2 * ((i >> 1) & 3)], ls[2 * ((i >> 1) & 3) + 1], p0, p1);
                     __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
                     pk[ch >> 1][(ch & 1) * 16 + (i >> 1)] = *reinterpret_cast<uint32_t*>(&hh);
                 }
-            const float lsum = (ls[0] + ls[1]) + (ls[2] + ls[3]);
+            const float lsum = ((ls[0] + ls[1]) + (ls[2] + ls[3])) + ((ls[4] + ls[5]) + (ls[6] + ls[7]));
             l_run = l_run * corr + lsum;
             if (j > 0) {
                 // P_X(j-1) must have been consumed (and O_X updated) before P is overwritten / O rescaled
