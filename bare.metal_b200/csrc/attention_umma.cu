@@ -13,7 +13,7 @@
 //                        (MN-major smem: the reduction index, the key, is the row of V), accumulator in TMEM
 // The single UMMA-issuing thread interleaves the two tiles (PV_A(j), QK_A(j+1), PV_B(j), QK_B(j+1), ...) so that
 // the tensor core works on one tile while the other tile's warpgroup does its softmax. K/V tiles are
-// double-buffered by a TMA producer warp. 10 warps: TMA, UMMA, 4 + 4 softmax.
+// double-buffered by a TMA producer warp. 12 warps: TMA, UMMA, two idle (they complete the control warpgroup), 4 + 4 softmax.
 // Same semantics as flash_fwd_kernel in attention_mma.cu (reference: attention_forward_train_tiled,
 // src/kernels/forward.metal:2122): out = softmax(scale * Q K^T, causal) V and lse = log-sum-exp of the scaled scores.
 #include <cuda.h>
@@ -34,7 +34,11 @@ constexpr int Q_BYTES = FQ * FHD * 2;        // 16 KB per Q tile
 constexpr int KV_TILE_BYTES = FK * FHD * 2;  // 16 KB each for K and V
 constexpr int P_BYTES = FQ * FK * 2;         // 32 KB per P tile
 constexpr int FWD_DYN_SMEM = 2 * Q_BYTES + 2 * 2 * KV_TILE_BYTES + 1024;  // Q x 2 tiles, K and V x 2 stages; P lives in tensor memory
-constexpr int FWD_THREADS = 320;
+constexpr int FWD_THREADS = 384;  // warpgroup 0: TMA warp, UMMA warp, two idle warps; warpgroups 1 and 2: softmax of tile A and tile B
+// Register budget: 3 warps per scheduler cap the kernel at 168 registers per thread. The control warpgroup hands most of
+// its share back (setmaxnreg.dec) and the two softmax warpgroups, which hold a 128-column score row per thread, take it
+// (setmaxnreg.inc): 128 x 72 + 256 x 216 = 384 x 168.
+constexpr int FWD_REGS_CONTROL = 72, FWD_REGS_SOFTMAX = 216;
 constexpr uint32_t FWD_TMEM_COLS = 512;  // S_A [0,128) S_B [128,256) O_A [256,320) O_B [320,384) P_A [384,448) P_B [448,512)
 constexpr uint32_t FWD_TMEM_P = 2 * FK + 2 * FHD;  // P as packed bf16 pairs: 128 keys = 64 columns per query tile
 constexpr float LOG2E_F = 1.4426950408889634f;
@@ -136,6 +140,8 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     const uint32_t tmem = bars.tmem_base;
     volatile int* abort_flag = &bars.abort_flag;
 
+    if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(FWD_REGS_CONTROL));
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
@@ -210,9 +216,11 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 if (ok) umma_commit(&bars.kv_empty[j & 1]);  // every UMMA that reads stage j has been issued
             }
         }
+    }
     } else {
-        // ------------------------------ softmax / epilogue: warps 2-5 = tile A, 6-9 = tile B ------------
-        const int x = (warp - 2) >> 2;
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(FWD_REGS_SOFTMAX));
+        // ------------------------------ softmax / epilogue: warps 4-7 = tile A, 8-11 = tile B ------------
+        const int x = (warp - 4) >> 2;
         const int quarter = warp & 3;              // TMEM lane quarter this warp may access
         const int r = quarter * 32 + lane;         // query row inside the tile
         const int qi = q0 + x * FQ + r;            // query position in the sequence
