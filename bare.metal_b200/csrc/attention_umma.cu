@@ -562,6 +562,34 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         bool ok = true;
         uint32_t dq_regs[16];
         int prev_h = 0, prev_q0 = 0;
+        // dQ of a finished tile (this thread: 16 fp32 of query row r) is added into the fp32 scratch. One red per row piece
+        // straight from the registers would touch 32 different lines per instruction, so the warp first transposes through
+        // shared memory: a thread parks its 64 bytes in the half row of the P buffer `buf` that holds its own P piece (free
+        // once that tile's second-stage UMMAs are done, and next written by this same thread), slots rotated by the row so
+        // that a quarter warp hits eight different 16-byte slots; then four lanes cover one row and an instruction adds
+        // eight 64-byte row pieces.
+        auto flush_dq = [&](int buf) {
+            const uint32_t base = smem_u32(sP + buf * P_BYTES + (cg >> 1) * (FQ * 128) + quarter * 32 * 128);
+            const uint32_t mine = base + lane * 128 + (((cg & 1) ^ ((lane >> 2) & 1)) * 64);
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                st_shared_v4(mine + ((c ^ (lane & 3)) * 16), dq_regs[4 * c], dq_regs[4 * c + 1], dq_regs[4 * c + 2], dq_regs[4 * c + 3]);
+            __syncwarp();
+            const int c = lane & 3;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int rr = 8 * i + (lane >> 3) + 4 * ((lane >> 2) & 1);   // row inside the warp's 32 rows
+                const uint32_t src = base + rr * 128 + (((cg & 1) ^ ((rr >> 2) & 1)) * 64) + ((c ^ (rr & 3)) * 16);
+                float4 v;
+                asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(src) : "memory");
+                const int pq = prev_q0 + quarter * 32 + rr;
+                if (pq < p.S) {
+                    float* dst = p.dq_acc + (size_t)(row0 + pq) * QD + (size_t)prev_h * FHD + cg * 16 + c * 4;
+                    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+                }
+            }
+            __syncwarp();
+        };
         for (int it = 0; it < total; ++it) {
             const int hl = it / per_head, mb = nblk + (it - hl * per_head);
             const int h = kh * mul + hl, q0 = mb * FQ;
@@ -637,16 +665,7 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 tc_fence_after_sync();
                 tmem_ld_32x16(lane_addr + BT_DQ + (pb ^ 1) * FHD + cg * 16, dq_regs);
                 tmem_ld_wait();
-                const int pq = prev_q0 + r;
-                if (pq < p.S) {
-                    float* dst = p.dq_acc + (size_t)(row0 + pq) * QD + (size_t)prev_h * FHD + cg * 16;
-#pragma unroll
-                    for (int c = 0; c < 4; ++c)
-                        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 4 * c), "f"(__uint_as_float(dq_regs[4 * c])),
-                                     "f"(__uint_as_float(dq_regs[4 * c + 1])), "f"(__uint_as_float(dq_regs[4 * c + 2])),
-                                     "f"(__uint_as_float(dq_regs[4 * c + 3]))
-                                     : "memory");
-                }
+                flush_dq(pb ^ 1);
             }
             prev_h = h;
             prev_q0 = q0;
@@ -661,16 +680,7 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             if (total > 0) {
                 tmem_ld_32x16(lane_addr + BT_DQ + ((total - 1) & 1) * FHD + cg * 16, dq_regs);
                 tmem_ld_wait();
-                const int pq = prev_q0 + r;
-                if (pq < p.S) {
-                    float* dst = p.dq_acc + (size_t)(row0 + pq) * QD + (size_t)prev_h * FHD + cg * 16;
-#pragma unroll
-                    for (int c = 0; c < 4; ++c)
-                        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 4 * c), "f"(__uint_as_float(dq_regs[4 * c])),
-                                     "f"(__uint_as_float(dq_regs[4 * c + 1])), "f"(__uint_as_float(dq_regs[4 * c + 2])),
-                                     "f"(__uint_as_float(dq_regs[4 * c + 3]))
-                                     : "memory");
-                }
+                flush_dq((total - 1) & 1);
             }
             // dK, dV: row = key, this warp's 16 columns
             const int kj = n0 + r;
