@@ -81,6 +81,12 @@ __device__ __forceinline__ void add2_f(float& d0, float& d1, float a0, float a1)
         : "+f"(d0), "+f"(d1)
         : "f"(a0), "f"(a1));
 }
+// (d0, d1) = (a0, a1) * (b0, b1)
+__device__ __forceinline__ void mul2_f(float& d0, float& d1, float a0, float a1, float b0, float b1) {
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmul.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d0), "=f"(d1)
+        : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -616,18 +622,21 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             if (lane == 0) mbar_arrive(&bars.sdp_free);
             if (cw == 0 && lane == 0) BTRACE(5, it);
             const bool diag = (mb == nblk) || (n0 + FK > p.S);
+            const float dlt_s = -dlt * p.scale;
             uint32_t pp[16], dd[16];
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
-                float p0 = ex2_approx(fmaf(__uint_as_float(sv[i]), sl2, -lse2));
-                float p1 = ex2_approx(fmaf(__uint_as_float(sv[i + 1]), sl2, -lse2));
+                float p0, p1, d0, d1;
+                fma2_f(p0, p1, __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]), sl2, -lse2);
+                fma2_f(d0, d1, __uint_as_float(dv[i]), __uint_as_float(dv[i + 1]), p.scale, dlt_s);   // scale * (dP - delta)
+                p0 = ex2_approx(p0);
+                p1 = ex2_approx(p1);
                 if (diag) {
                     const int kl = cg * 32 + i;   // key inside the tile; on the diagonal tile n0 == q0
                     if ((mb == nblk && kl > r) || n0 + kl >= p.S) p0 = 0.f;
                     if ((mb == nblk && kl + 1 > r) || n0 + kl + 1 >= p.S) p1 = 0.f;
                 }
-                const float d0 = p0 * (__uint_as_float(dv[i]) - dlt) * p.scale;
-                const float d1 = p1 * (__uint_as_float(dv[i + 1]) - dlt) * p.scale;
+                mul2_f(d0, d1, d0, d1, p0, p1);
                 __nv_bfloat162 hp = __floats2bfloat162_rn(p0, p1), hd = __floats2bfloat162_rn(d0, d1);
                 pp[i >> 1] = *reinterpret_cast<uint32_t*>(&hp);
                 dd[i >> 1] = *reinterpret_cast<uint32_t*>(&hd);
