@@ -596,17 +596,27 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             }
             __syncwarp();
         };
+        // per-row statistics of tile `t` (rows past the end: lse = +inf makes every probability zero); fetched one tile ahead
+        auto load_stats = [&](int t, float& lse_out, float& dlt_out) {
+            lse_out = INFINITY;
+            dlt_out = 0.f;
+            if (t < total) {
+                const int thl = t / per_head, tmb = nblk + (t - thl * per_head);
+                const int tq = tmb * FQ + r;
+                if (tq < p.S) {
+                    const size_t idx = ((size_t)b * p.NH + kh * mul + thl) * p.S + tq;
+                    lse_out = p.lse[idx];
+                    dlt_out = p.delta[idx];
+                }
+            }
+        };
+        float lse_next, dlt_next;
+        load_stats(0, lse_next, dlt_next);
         for (int it = 0; it < total; ++it) {
             const int hl = it / per_head, mb = nblk + (it - hl * per_head);
             const int h = kh * mul + hl, q0 = mb * FQ;
-            const int qi = q0 + r;
-            // per-row statistics (rows past the end: lse = +inf makes every probability zero)
-            float lse2 = INFINITY, dlt = 0.f;
-            if (qi < p.S) {
-                const size_t idx = ((size_t)b * p.NH + h) * p.S + qi;
-                lse2 = p.lse[idx] * LOG2E_F;
-                dlt = p.delta[idx];
-            }
+            const float lse2 = lse_next * LOG2E_F, dlt = dlt_next;
+            load_stats(it + 1, lse_next, dlt_next);
             ok = mbar_wait(&bars.sdp_full, it & 1, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
