@@ -94,6 +94,9 @@ __device__ __forceinline__ float ex2_approx(float x) {
 }
 
 struct FwdArgs {
+#ifdef BMB_TRACE
+    long long* trace;
+#endif
     bf16* out;
     int ldo;
     float* lse;
@@ -101,6 +104,12 @@ struct FwdArgs {
     float scale;
     int* err;
 };
+
+#ifdef BMB_TRACE
+#define FTRACE(slot, idx) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (idx) < 32) p.trace[(slot) * 32 + (idx)] = clock64(); } while (0)
+#else
+#define FTRACE(slot, idx) do { } while (0)
+#endif
 
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -211,6 +220,7 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                     }
                     tc_fence_after_sync();
                     issue_qk(x, j + 1);
+                    if (x == 0) FTRACE(0, j);
                 }
                 for (int x = 0; x < 2 && ok; ++x) {
                     const int n_this = x ? n_b : n_a;
@@ -218,6 +228,7 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                     if (!mbar_wait(&bars.p_ready[x], j & 1, abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
                     issue_pv(x, j);
+                    if (x == 0) FTRACE(1, j);
                 }
                 if (ok) umma_commit(&bars.kv_empty[j & 1]);  // every UMMA that reads stage j has been issued
             }
@@ -243,6 +254,7 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after_sync();
+            if (quarter == 0 && lane == 0) FTRACE(2 + 6 * x, j);
             uint32_t v[4][32];
 #pragma unroll
             for (int ch = 0; ch < 4; ++ch) tmem_ld_32x32(s_addr + ch * 32, v[ch]);
@@ -251,6 +263,7 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars.s_free[x]);
+            if (quarter == 0 && lane == 0) FTRACE(3 + 6 * x, j);
             const int k0 = j * FK;
             if (j == n_mine - 1 || k0 + FK > p.S) {  // diagonal tile or ragged end: mask keys after the query / past the end
 #pragma unroll
@@ -282,6 +295,7 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 need = true;
             }
             const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+            if (quarter == 0 && lane == 0) FTRACE(4 + 6 * x, j);
             // probabilities, packed to bf16 pairs (keys 2c, 2c+1 -> column c of the P block in tensor memory); four independent sum chains
             uint32_t pk[2][32];
             float ls[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -299,6 +313,7 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 }
             const float lsum = ((ls[0] + ls[1]) + (ls[2] + ls[3])) + ((ls[4] + ls[5]) + (ls[6] + ls[7]));
             l_run = l_run * corr + lsum;
+            if (quarter == 0 && lane == 0) FTRACE(5 + 6 * x, j);
             if (j > 0) {
                 // P_X(j-1) must have been consumed (and O_X updated) before P is overwritten / O rescaled
                 ok = mbar_wait(&bars.pv_done[x], (j - 1) & 1, abort_flag);
@@ -317,6 +332,7 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                     }
                 }
             }
+            if (quarter == 0 && lane == 0) FTRACE(6 + 6 * x, j);
             // P row -> tensor memory, where P V reads it as its A operand (this thread's TMEM lane = its query row)
             tmem_st_32x32(p_addr, pk[0]);
             tmem_st_32x32(p_addr + 32, pk[1]);
@@ -324,6 +340,7 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars.p_ready[x]);
+            if (quarter == 0 && lane == 0) FTRACE(7 + 6 * x, j);
         }
         if (ok && n_mine > 0) {
             ok = mbar_wait(&bars.pv_done[x], (n_mine - 1) & 1, abort_flag);
@@ -822,9 +839,35 @@ int flash_attention_forward_umma(bf16* out, int ldo, float* lse, const bf16* q, 
     if (!rc) rc = make_rows_map(&tk, k, (uint64_t)NKV * HD, rows, ldkv, FK);
     if (!rc) rc = make_rows_map(&tv, v, (uint64_t)NKV * HD, rows, ldkv, FK);
     if (rc) return rc;
+#ifdef BMB_TRACE
+    long long* trace = nullptr;
+    cudaMalloc(&trace, 14 * 32 * sizeof(long long));
+    cudaMemset(trace, 0, 14 * 32 * sizeof(long long));
+    FwdArgs a{trace, out, ldo, lse, S, NH, NKV, scale, err_flag};
+#else
     FwdArgs a{out, ldo, lse, S, NH, NKV, scale, err_flag};
+#endif
     dim3 grid((S + 2 * FQ - 1) / (2 * FQ), NH, B);
     flash_fwd_umma_kernel<<<grid, FWD_THREADS, FWD_DYN_SMEM, st>>>(tq, tk, tv, a);
+#ifdef BMB_TRACE
+    {
+        static int printed = 0;
+        cudaStreamSynchronize(st);
+        long long h[14 * 32];
+        cudaMemcpy(h, trace, sizeof h, cudaMemcpyDeviceToHost);
+        cudaFree(trace);
+        if (printed++ < 1) {
+            const char* names[14] = {"mma:qk_next", "mma:pv", "A:s_full", "A:ld", "A:max", "A:exp", "A:pv_done", "A:p_ready",
+                                     "B:s_full", "B:ld", "B:max", "B:exp", "B:pv_done", "B:p_ready"};
+            const long long t0 = h[2 * 32];
+            for (int j = 0; j < 14; ++j) {
+                fprintf(stderr, "fwd j=%2d", j);
+                for (int sl = 0; sl < 14; ++sl) fprintf(stderr, " %s=%lld", names[sl], h[sl * 32 + j] ? h[sl * 32 + j] - t0 : -1);
+                fprintf(stderr, "\n");
+            }
+        }
+    }
+#endif
     const cudaError_t le = cudaGetLastError();
     if (le != cudaSuccess) {
         fprintf(stderr, "flash_attention_forward_umma: launch failed: %s\n", cudaGetErrorString(le));
