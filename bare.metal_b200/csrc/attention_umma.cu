@@ -13,7 +13,7 @@
 //                        (MN-major smem: the reduction index, the key, is the row of V), accumulator in TMEM
 // The single UMMA-issuing thread interleaves the two tiles (PV_A(j), QK_A(j+1), PV_B(j), QK_B(j+1), ...) so that
 // the tensor core works on one tile while the other tile's warpgroup does its softmax. K/V tiles are
-// double-buffered by a TMA producer warp. 12 warps: TMA, UMMA, two idle (they complete the control warpgroup), 4 + 4 softmax.
+// in a four-stage ring filled by a TMA producer warp. 12 warps: TMA, UMMA, two idle (they complete the control warpgroup), 4 + 4 softmax.
 // Same semantics as flash_fwd_kernel in attention_mma.cu (reference: attention_forward_train_tiled,
 // src/kernels/forward.metal:2122): out = softmax(scale * Q K^T, causal) V and lse = log-sum-exp of the scaled scores.
 #include <cuda.h>
@@ -33,7 +33,11 @@ constexpr int FHD = 64;
 constexpr int Q_BYTES = FQ * FHD * 2;        // 16 KB per Q tile
 constexpr int KV_TILE_BYTES = FK * FHD * 2;  // 16 KB each for K and V
 constexpr int P_BYTES = FQ * FK * 2;         // 32 KB per P tile
-constexpr int FWD_DYN_SMEM = 2 * Q_BYTES + 2 * 2 * KV_TILE_BYTES + 1024;  // Q x 2 tiles, K and V x 2 stages; P lives in tensor memory
+// K/V stages: a stage is refilled only after every UMMA that read it has completed, and the refill (32 KB from L2) takes over a
+// thousand clocks, so with two stages S of key tile j+2 waited for the load that P V of tile j had just released. Four
+// stages put the load two tiles ahead of its use.
+constexpr int FWD_KV_STAGES = 4;
+constexpr int FWD_DYN_SMEM = 2 * Q_BYTES + FWD_KV_STAGES * 2 * KV_TILE_BYTES + 1024;  // Q x 2 tiles, K and V stages; P lives in tensor memory
 constexpr int FWD_THREADS = 384;  // warpgroup 0: TMA warp, UMMA warp, two idle warps; warpgroups 1 and 2: softmax of tile A and tile B
 // Register budget: 3 warps per scheduler cap the kernel at 168 registers per thread. The control warpgroup hands most of
 // its share back (setmaxnreg.dec) and the two softmax warpgroups, which hold a 128-column score row per thread, take it
@@ -45,7 +49,7 @@ constexpr float LOG2E_F = 1.4426950408889634f;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
 
 struct __align__(8) FwdBars {
-    uint64_t q_full, kv_full[2], kv_empty[2], s_full[2], s_free[2], p_ready[2], pv_done[2];
+    uint64_t q_full, kv_full[FWD_KV_STAGES], kv_empty[FWD_KV_STAGES], s_full[2], s_free[2], p_ready[2], pv_done[2];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -118,8 +122,8 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     __shared__ FwdBars bars;
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* sQ = smem;                          // 2 tiles
-    uint8_t* sK = sQ + 2 * Q_BYTES;              // 2 stages
-    uint8_t* sV = sK + 2 * KV_TILE_BYTES;        // 2 stages
+    uint8_t* sK = sQ + 2 * Q_BYTES;              // FWD_KV_STAGES stages
+    uint8_t* sV = sK + FWD_KV_STAGES * KV_TILE_BYTES;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int qb = (int)gridDim.x - 1 - (int)blockIdx.x;  // latest (longest) query blocks first
@@ -133,9 +137,11 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 
     if (threadIdx.x == 0) {
         mbar_init(&bars.q_full, 1);
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < FWD_KV_STAGES; ++i) {
             mbar_init(&bars.kv_full[i], 1);
             mbar_init(&bars.kv_empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
             mbar_init(&bars.s_full[i], 1);
             mbar_init(&bars.s_free[i], 4);
             mbar_init(&bars.p_ready[i], 4);
@@ -165,8 +171,8 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             tma_load_2d(sQ, &tmQ, &bars.q_full, h * FHD, row0 + q0);
             tma_load_2d(sQ + Q_BYTES, &tmQ, &bars.q_full, h * FHD, row0 + q0 + FQ);
             for (int j = 0; j < n_tiles; ++j) {
-                const int st = j & 1;
-                if (!mbar_wait(&bars.kv_empty[st], ((j >> 1) & 1) ^ 1, abort_flag)) break;
+                const int st = j % FWD_KV_STAGES;
+                if (!mbar_wait(&bars.kv_empty[st], ((j / FWD_KV_STAGES) & 1) ^ 1, abort_flag)) break;
                 mbar_expect_tx(&bars.kv_full[st], 2 * KV_TILE_BYTES);
                 tma_load_2d(sK + st * KV_TILE_BYTES, &tmK, &bars.kv_full[st], kh * FHD, row0 + j * FK);
                 tma_load_2d(sV + st * KV_TILE_BYTES, &tmV, &bars.kv_full[st], kh * FHD, row0 + j * FK);
@@ -184,14 +190,14 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             const uint64_t kd0 = umma_smem_desc_sw128(smem_u32(sK), 16, 1024);
             const uint64_t vd0 = umma_smem_desc_sw128(smem_u32(sV), FK * 128, 1024);
             auto issue_qk = [&](int x, int j) {
-                const uint64_t kd = kd0 + (uint64_t)((j & 1) * (KV_TILE_BYTES >> 4));
+                const uint64_t kd = kd0 + (uint64_t)((j % FWD_KV_STAGES) * (KV_TILE_BYTES >> 4));
                 const uint64_t qd = qd0 + (uint64_t)(x * (Q_BYTES >> 4));
 #pragma unroll
                 for (int k = 0; k < FHD / 16; ++k) umma_bf16_ss(tmem + x * FK, qd + 2 * k, kd + 2 * k, idesc_s, k > 0 ? 1u : 0u);
                 umma_commit(&bars.s_full[x]);
             };
             auto issue_pv = [&](int x, int j) {
-                const uint64_t vd = vd0 + (uint64_t)((j & 1) * (KV_TILE_BYTES >> 4));
+                const uint64_t vd = vd0 + (uint64_t)((j % FWD_KV_STAGES) * (KV_TILE_BYTES >> 4));
 #pragma unroll
                 for (int k = 0; k < FK / 16; ++k)
                     // P comes from tensor memory (16 keys = 8 columns of bf16 pairs); V: 16 keys = 2048 B
@@ -215,7 +221,7 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                     if (j + 1 >= n_this) continue;
                     if (!mbar_wait(&bars.s_free[x], j & 1, abort_flag)) { ok = false; break; }
                     if (!next_loaded) {
-                        if (!mbar_wait(&bars.kv_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+                        if (!mbar_wait(&bars.kv_full[(j + 1) % FWD_KV_STAGES], ((j + 1) / FWD_KV_STAGES) & 1, abort_flag)) { ok = false; break; }
                         next_loaded = true;
                     }
                     tc_fence_after_sync();
@@ -230,7 +236,7 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                     issue_pv(x, j);
                     if (x == 0) FTRACE(1, j);
                 }
-                if (ok) umma_commit(&bars.kv_empty[j & 1]);  // every UMMA that reads stage j has been issued
+                if (ok) umma_commit(&bars.kv_empty[j % FWD_KV_STAGES]);  // every UMMA that reads this stage has been issued
             }
         }
     }
