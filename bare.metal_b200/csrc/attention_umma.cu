@@ -571,11 +571,13 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 for (int k = 0; k < FQ / 16; ++k) umma_bf16_ss(tmem + BT_DV, p_mn + po + 128 * k, g_mn0 + so + 128 * k, id_kv, (it > 0 || k > 0) ? 1u : 0u);
 #pragma unroll
                 for (int k = 0; k < FQ / 16; ++k) umma_bf16_ss(tmem + BT_DK, d_mn + po + 128 * k, q_mn0 + so + 128 * k, id_kv, (it > 0 || k > 0) ? 1u : 0u);
+                // dQ does not read the Q / dO stage: release it now, so that its refill (32 KB, over a thousand clocks, and S / dP of
+                // the tile after next wait for it) starts eight UMMAs earlier
+                umma_commit(&bars.q_empty[st]);
 #pragma unroll
                 for (int k = 0; k < FK / 16; ++k)
                     umma_bf16_ss(tmem + BT_DQ + pb * FHD, d_km + po + (uint64_t)((k >> 2) * ((FQ * 128) >> 4) + (k & 3) * 2), k_mn + 128 * k, id_q,
                                  k > 0 ? 1u : 0u);
-                umma_commit(&bars.q_empty[st]);
                 umma_commit(&bars.dq_full[pb]);
                 BTRACE(3, it);
             }
