@@ -411,7 +411,7 @@ constexpr int BWD_DYN_SMEM = 2 * KV_TILE_BYTES + 2 * 2 * Q_BYTES + 4 * P_BYTES +
 constexpr uint32_t BT_S = 0, BT_DP = 128, BT_DV = 256, BT_DK = 320, BT_DQ = 384;  // dQ: two buffers of 64 columns (384, 448)
 
 struct __align__(8) BwdBars {
-    uint64_t kv_full, q_full[2], q_empty[2], sdp_full, sdp_free, pds_ready[2], dq_full[2];
+    uint64_t kv_full, q_full[2], q_empty[2], g_full[2], g_empty[2], sdp_full, sdp_free, pds_ready[2], dq_full[2];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -468,7 +468,7 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 
     if (threadIdx.x == 0) {
         mbar_init(&bars.kv_full, 1);
-        for (int i = 0; i < 2; ++i) { mbar_init(&bars.q_full[i], 1); mbar_init(&bars.q_empty[i], 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&bars.q_full[i], 1); mbar_init(&bars.q_empty[i], 1); mbar_init(&bars.g_full[i], 1); mbar_init(&bars.g_empty[i], 1); }
         mbar_init(&bars.sdp_full, 1);
         mbar_init(&bars.sdp_free, 16);
         for (int i = 0; i < 2; ++i) { mbar_init(&bars.pds_ready[i], 16); mbar_init(&bars.dq_full[i], 1); }
@@ -497,10 +497,13 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 const int st = it & 1;
                 const int hl = it / per_head, mb = nblk + (it - hl * per_head);
                 const int h = kh * mul + hl;
+                // Q and dO have a barrier pair each: the Q half of a stage is released after dK (issued first), the dO half after dV
                 if (!mbar_wait(&bars.q_empty[st], ((it >> 1) & 1) ^ 1, abort_flag)) break;
-                mbar_expect_tx(&bars.q_full[st], 2 * Q_BYTES);
+                mbar_expect_tx(&bars.q_full[st], Q_BYTES);
                 tma_load_2d(sQ + st * Q_BYTES, &tmQ, &bars.q_full[st], h * FHD, row0 + mb * FQ);
-                tma_load_2d(sG + st * Q_BYTES, &tmG, &bars.q_full[st], h * FHD, row0 + mb * FQ);
+                if (!mbar_wait(&bars.g_empty[st], ((it >> 1) & 1) ^ 1, abort_flag)) break;
+                mbar_expect_tx(&bars.g_full[st], Q_BYTES);
+                tma_load_2d(sG + st * Q_BYTES, &tmG, &bars.g_full[st], h * FHD, row0 + mb * FQ);
             }
         }
     } else if (warp == 1) {
@@ -517,7 +520,7 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             // core works through the second stage of tile it.
             bool ok = mbar_wait(&bars.kv_full, 0, abort_flag);
             if (ok && total > 0) {
-                ok = mbar_wait(&bars.q_full[0], 0, abort_flag);
+                ok = mbar_wait(&bars.q_full[0], 0, abort_flag) && mbar_wait(&bars.g_full[0], 0, abort_flag);
                 if (ok) {
                     tc_fence_after_sync();
 #pragma unroll
@@ -536,6 +539,8 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 tc_fence_after_sync();
 #pragma unroll
                 for (int k = 0; k < FHD / 16; ++k) umma_bf16_ss(tmem + BT_S, q_km0 + sn + 2 * k, k_km + 2 * k, id_s, k > 0 ? 1u : 0u);
+                if (!mbar_wait(&bars.g_full[nx], ((it + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+                tc_fence_after_sync();
 #pragma unroll
                 for (int k = 0; k < FHD / 16; ++k) umma_bf16_ss(tmem + BT_DP, g_km0 + sn + 2 * k, v_km + 2 * k, id_s, k > 0 ? 1u : 0u);
                 umma_commit(&bars.sdp_full);
@@ -561,19 +566,21 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 const int st = it & 1;
                 const uint64_t so = (uint64_t)(st * (Q_BYTES >> 4));
                 if (!mbar_wait(&bars.q_full[st], (it >> 1) & 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(&bars.g_full[st], (it >> 1) & 1, abort_flag)) { ok = false; break; }
                 // P and dS of this tile are in shared-memory buffer it & 1; the dQ columns of that parity were read out two tiles ago
                 const int pb = it & 1;
                 const uint64_t po = (uint64_t)(pb * (P_BYTES >> 4));
                 if (!mbar_wait(&bars.pds_ready[pb], (it >> 1) & 1, abort_flag)) { ok = false; break; }
                 tc_fence_after_sync();
                 BTRACE(2, it);
-#pragma unroll
-                for (int k = 0; k < FQ / 16; ++k) umma_bf16_ss(tmem + BT_DV, p_mn + po + 128 * k, g_mn0 + so + 128 * k, id_kv, (it > 0 || k > 0) ? 1u : 0u);
+                // The refill of a stage (over a thousand clocks) is what S / dP of the tile after next wait for, so each half is
+                // released as early as its last reader allows: Q after dK, dO after dV; dQ reads neither.
 #pragma unroll
                 for (int k = 0; k < FQ / 16; ++k) umma_bf16_ss(tmem + BT_DK, d_mn + po + 128 * k, q_mn0 + so + 128 * k, id_kv, (it > 0 || k > 0) ? 1u : 0u);
-                // dQ does not read the Q / dO stage: release it now, so that its refill (32 KB, over a thousand clocks, and S / dP of
-                // the tile after next wait for it) starts eight UMMAs earlier
                 umma_commit(&bars.q_empty[st]);
+#pragma unroll
+                for (int k = 0; k < FQ / 16; ++k) umma_bf16_ss(tmem + BT_DV, p_mn + po + 128 * k, g_mn0 + so + 128 * k, id_kv, (it > 0 || k > 0) ? 1u : 0u);
+                umma_commit(&bars.g_empty[st]);
 #pragma unroll
                 for (int k = 0; k < FK / 16; ++k)
                     umma_bf16_ss(tmem + BT_DQ + pb * FHD, d_km + po + (uint64_t)((k >> 2) * ((FQ * 128) >> 4) + (k & 3) * 2), k_mn + 128 * k, id_q,
