@@ -1,8 +1,8 @@
 """ctypes bindings and synthetic-input helpers shared by the tests, bench.py and smoke().
 
-The public C API is the reference's `include/baremetal.h` (functions at baremetal.h:120-206), so the
-same bindings drive both the product library (libbaremetal_b200.so) and the reference build used as
-the parity oracle (oracle/_ref/libbm_ref.so).
+The public C API is the reference's `include/baremetal.h` (functions at baremetal.h:120-206), so `bind_public_api`
+binds any library that exports it: the product library (libbaremetal_b200.so) here, and the reference build that the
+tests use as their parity oracle (loaded by oracle/oracle_check.py, not by this package).
 """
 import ctypes as C
 import os
@@ -178,7 +178,6 @@ def bind_public_api(lib):
 
 
 LIB_PATH = os.path.join(PKG_DIR, "libbaremetal_b200.so")
-REF_LIB_PATH = os.path.join(ROOT, "oracle", "_ref", "libbm_ref.so")
 
 BMX_WEIGHT, BMX_GRAD, BMX_ADAM_M, BMX_ADAM_V = 0, 1, 2, 3
 
@@ -222,29 +221,6 @@ def product_read(lib, trainer, what, i):
     if rc != 0:
         raise RuntimeError(f"bmx_trainer_read failed: {rc}")
     return out
-
-
-def reference_read(lib, trainer, what, i):
-    n = lib.bmref_state_size(trainer, i)
-    fn = {BMX_WEIGHT: lib.bmref_weight, BMX_GRAD: lib.bmref_grad, BMX_ADAM_M: lib.bmref_m, BMX_ADAM_V: lib.bmref_v}[what]
-    return np.ctypeslib.as_array(fn(trainer, i), (n,)).copy()
-
-
-def load_reference():
-    """The reference's own host code + kernels on CPU (built by oracle/build_ref.sh). None if absent."""
-    if not os.path.exists(REF_LIB_PATH):
-        return None
-    lib = bind_public_api(C.CDLL(REF_LIB_PATH))
-    vp, fp = C.c_void_p, C.POINTER(C.c_float)
-    lib.bmref_set_precision.argtypes = [vp, C.c_int]
-    lib.bmref_set_quant.argtypes = [vp, C.c_int]
-    lib.bmt_quantize_q8.restype, lib.bmt_quantize_q8.argtypes = C.c_size_t, [fp, vp, C.c_size_t]
-    lib.bmref_n_states.restype, lib.bmref_n_states.argtypes = C.c_int, [vp]
-    lib.bmref_state_size.restype, lib.bmref_state_size.argtypes = C.c_size_t, [vp, C.c_int]
-    for n in ("bmref_grad", "bmref_weight", "bmref_m", "bmref_v"):
-        getattr(lib, n).restype, getattr(lib, n).argtypes = fp, [vp, C.c_int]
-    lib.bmref_logits.restype, lib.bmref_logits.argtypes = fp, [vp]
-    return lib
 
 
 def read_state_file(path):

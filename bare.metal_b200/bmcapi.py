@@ -1,4 +1,5 @@
-"""Helpers for calling the backend C ABI (include/bm_cuda_backend.h) from the GPU tests."""
+"""ctypes access to the backend C ABI (include/bm_cuda_backend.h): a context, device buffers and typed calls of the bmc_* entry
+points, plus the bf16 bit conversions their callers need. Used by the kernel workloads of bench.py and by the GPU tests."""
 import ctypes as C
 
 import numpy as np

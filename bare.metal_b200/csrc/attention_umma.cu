@@ -843,11 +843,10 @@ int flash_attention_forward_umma(bf16* out, int ldo, float* lse, const bf16* q, 
     if ((ldq % 8) || (ldkv % 8) || (ldo % 8) || (((uintptr_t)q) & 15) || (((uintptr_t)k) & 15) || (((uintptr_t)v) & 15) ||
         (((uintptr_t)out) & 15))
         return -2;
-    static bool attr_done = false;
-    if (!attr_done) {
-        if (cudaFuncSetAttribute(flash_fwd_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_DYN_SMEM) != cudaSuccess) return -5;
-        attr_done = true;
-    }
+    static std::atomic<unsigned long long> attr_done{0};
+    if (first_use_on_current_device(attr_done) &&
+        cudaFuncSetAttribute(flash_fwd_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_DYN_SMEM) != cudaSuccess)
+        return -5;
     CUtensorMap tq, tk, tv;
     const uint64_t rows = (uint64_t)B * S;
     int rc = make_rows_map(&tq, q, (uint64_t)NH * HD, rows, ldq, FQ);
@@ -899,11 +898,10 @@ int flash_attention_backward_umma(bf16* gq, int ldgq, bf16* gk, bf16* gv, int ld
         (((uintptr_t)v) & 15) || (((uintptr_t)gout) & 15) || (((uintptr_t)gk) & 15) || (((uintptr_t)gv) & 15) || (((uintptr_t)gq) & 7) ||
         (((uintptr_t)out) & 15))
         return -2;
-    static bool attr_done = false;
-    if (!attr_done) {
-        if (cudaFuncSetAttribute(flash_bwd_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_DYN_SMEM) != cudaSuccess) return -5;
-        attr_done = true;
-    }
+    static std::atomic<unsigned long long> attr_done{0};
+    if (first_use_on_current_device(attr_done) &&
+        cudaFuncSetAttribute(flash_bwd_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_DYN_SMEM) != cudaSuccess)
+        return -5;
     const uint64_t rows = (uint64_t)B * S;
     const int QD = NH * HD;
     float* dq_acc = (float*)scratch;

@@ -316,15 +316,15 @@ float bmc_timer_end(bmc_ctx_t* ctx, int slot) {
 }
 
 // ---- embedding ---------------------------------------------------------------------------------------
-int bmc_embedding_forward(bmc_ctx_t* ctx, int dtype, void* d_out, const float* d_table, const int* d_tokens, int n_tok, int D) {
+int bmc_embedding_forward(bmc_ctx_t* ctx, int dtype, void* d_out, const float* d_table, const int* d_tokens, int n_tok, int D, int V) {
     BMC_CHECK_CTX(ctx);
-    if (dtype == BMC_F32) return note(ctx, embedding_forward<float>((float*)d_out, d_table, d_tokens, n_tok, D, ctx->stream));
-    return note(ctx, embedding_forward<bf16>((bf16*)d_out, d_table, d_tokens, n_tok, D, ctx->stream));
+    if (dtype == BMC_F32) return note(ctx, embedding_forward<float>((float*)d_out, d_table, d_tokens, n_tok, D, V, ctx->d_err, ctx->stream));
+    return note(ctx, embedding_forward<bf16>((bf16*)d_out, d_table, d_tokens, n_tok, D, V, ctx->d_err, ctx->stream));
 }
-int bmc_embedding_backward(bmc_ctx_t* ctx, int dtype, float* d_gwte, const void* d_gout, const int* d_tokens, int n_tok, int D) {
+int bmc_embedding_backward(bmc_ctx_t* ctx, int dtype, float* d_gwte, const void* d_gout, const int* d_tokens, int n_tok, int D, int V) {
     BMC_CHECK_CTX(ctx);
-    if (dtype == BMC_F32) return note(ctx, embedding_backward_f32(d_gwte, (const float*)d_gout, d_tokens, n_tok, D, ctx->stream));
-    return note(ctx, embedding_backward_bf16(d_gwte, (const bf16*)d_gout, d_tokens, n_tok, D, ctx->stream));
+    if (dtype == BMC_F32) return note(ctx, embedding_backward_f32(d_gwte, (const float*)d_gout, d_tokens, n_tok, D, V, ctx->d_err, ctx->stream));
+    return note(ctx, embedding_backward_bf16(d_gwte, (const bf16*)d_gout, d_tokens, n_tok, D, V, ctx->d_err, ctx->stream));
 }
 
 // ---- RMSNorm -----------------------------------------------------------------------------------------
@@ -481,9 +481,9 @@ int bmc_xent(bmc_ctx_t* ctx, int dtype, void* d_logits, int ldv, float* d_row_lo
     BMC_CHECK_CTX(ctx);
     int rc;
     if (dtype == BMC_F32)
-        rc = xent_forward_backward<float>((float*)d_logits, d_row_loss, d_targets, d_row_weight, B * S, V, ldv, grad_scale, ctx->stream);
+        rc = xent_forward_backward<float>((float*)d_logits, d_row_loss, d_targets, d_row_weight, B * S, V, ldv, grad_scale, ctx->d_err, ctx->stream);
     else
-        rc = xent_forward_backward<bf16>((bf16*)d_logits, d_row_loss, d_targets, d_row_weight, B * S, V, ldv, grad_scale, ctx->stream);
+        rc = xent_forward_backward<bf16>((bf16*)d_logits, d_row_loss, d_targets, d_row_weight, B * S, V, ldv, grad_scale, ctx->d_err, ctx->stream);
     if (rc) return rc;
     if (d_loss) rc = loss_reduce(d_loss, d_row_loss, B, S, d_row_weight != nullptr, ctx->stream);
     return note(ctx, rc, d_loss ? 2 : 1);

@@ -4,9 +4,34 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 namespace bmb {
 
 typedef __nv_bfloat16 bf16;
+
+// Function attributes (cudaFuncSetAttribute) and the SM count belong to a device, not to the process: a launcher keeps one
+// mask per set-up site and repeats the set-up the first time it runs with another device current. Setting an attribute
+// twice is harmless, so two host threads racing through the same first use need no lock.
+inline bool first_use_on_current_device(std::atomic<unsigned long long>& done_mask) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const unsigned long long bit = 1ull << (dev & 63);
+    if (done_mask.load(std::memory_order_acquire) & bit) return false;
+    done_mask.fetch_or(bit, std::memory_order_acq_rel);
+    return true;
+}
+inline int sm_count_current_device() {
+    static std::atomic<int> cached[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    int n = cached[dev & 63].load(std::memory_order_relaxed);
+    if (n == 0) {
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        cached[dev & 63].store(n, std::memory_order_relaxed);
+    }
+    return n;
+}
 
 // One 16-byte vector of T, processed as floats.
 template <typename T> struct Vec;

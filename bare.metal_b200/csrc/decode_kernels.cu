@@ -902,11 +902,9 @@ static int gemv_dispatch(float* out, int ldo, const float* x, int ldx, const voi
     }
     const size_t smem = (size_t)GEMV_TB * C * sizeof(float);
     if (smem > 200 * 1024) return -2;
-    static bool attr_done = false;
-    if (!attr_done) {
+    static std::atomic<unsigned long long> attr_done{0};
+    if (first_use_on_current_device(attr_done))
         cudaFuncSetAttribute(decode_gemvb_kernel<WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        attr_done = true;
-    }
     const int rows_per_block = GEMV_WARPS * GEMV_ROWS;
     int gx = (OC + rows_per_block - 1) / rows_per_block;
     if (gx > 148 * 4) gx = 148 * 4;
@@ -1009,11 +1007,9 @@ int prefill_attention_f32(float* out, int ldo, const float* q, int ldq, const fl
     if (HD != PF_HD) return -3;
     if (NKV <= 0 || NH % NKV || (ldo & 3) || (ldq & 3) || (ldkv & 3)) return -1;
     const size_t smem = (size_t)4 * PF_T * PF_PITCH * sizeof(float);
-    static bool attr_done = false;
-    if (!attr_done) {
+    static std::atomic<unsigned long long> attr_done{0};
+    if (first_use_on_current_device(attr_done))
         cudaFuncSetAttribute(prefill_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attr_done = true;
-    }
     return launch_k(prefill_attention_kernel, dim3((T + PF_T - 1) / PF_T, NH, NB), dim3(256), smem, st, out, ldo, q, ldq, k, v, ldkv, T, NH, NKV, scale);
 }
 int decode_swiglu(float* out, const float* gu, int NB, int H, cudaStream_t st) {

@@ -13,6 +13,7 @@
 
 #include <atomic>
 
+#include "common.cuh"
 #include "ptx_sm100.cuh"
 
 namespace bmb {
@@ -517,7 +518,6 @@ int choose_tile_n(int N, int b_mn, int ctas) {
 }
 
 std::atomic<long> g_launches{0};
-int g_num_sms = 0;
 
 }  // namespace
 
@@ -529,18 +529,14 @@ int gemm_bf16_umma(const GemmProblem& g, int* err_flag, cudaStream_t stream) {
     if ((((uintptr_t)g.A) & 15) || (((uintptr_t)g.B) & 15)) return -3;
     if (g.splits > 1 && g.out_mode != GEMM_OUT_F32_ATOMIC) return -4;
 
-    static bool attr_done = false;
-    static bool pair_off = false;
-    if (!attr_done) {
+    static std::atomic<unsigned long long> attr_done{0};
+    static const bool pair_off = getenv("BM_GEMM_1CTA") != nullptr;
+    if (first_use_on_current_device(attr_done)) {
         cudaError_t e = cudaFuncSetAttribute(gemm_bf16_umma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DYN_BYTES);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_bf16_umma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DYN_BYTES);
         if (e != cudaSuccess) return -5;
-        pair_off = getenv("BM_GEMM_1CTA") != nullptr;
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
-        attr_done = true;
     }
+    const int g_num_sms = sm_count_current_device();
 
     // CTA pairs (256-row tiles) whenever there are at least 256 rows and the caller did not fix a narrow tile
     const int ctas = (!pair_off && g.M >= 2 * BM && g.tile_n == 0) ? 2 : 1;

@@ -7,9 +7,12 @@
 namespace bmb {
 
 // ---- memory-bound kernels (kernels_mem.cu) ---------------------------------------------------
-template <typename T> int embedding_forward(T* out, const float* table, const int* tokens, int n_tok, int D, cudaStream_t st);
-int embedding_backward_f32(float* gwte, const float* gout, const int* tokens, int n_tok, int D, cudaStream_t st);
-int embedding_backward_bf16(float* gwte, const bf16* gout, const int* tokens, int n_tok, int D, cudaStream_t st);
+// Codes a kernel leaves in the context's error word (read by bmc_status) instead of using an id that is out of range as an index.
+constexpr int BMB_ERR_BAD_TOKEN = 2001;   // embedding gather / scatter met a token id outside [0, V)
+constexpr int BMB_ERR_BAD_TARGET = 2002;  // cross-entropy met a target id outside [0, V) on a row that counts
+template <typename T> int embedding_forward(T* out, const float* table, const int* tokens, int n_tok, int D, int V, int* err, cudaStream_t st);
+int embedding_backward_f32(float* gwte, const float* gout, const int* tokens, int n_tok, int D, int V, int* err, cudaStream_t st);
+int embedding_backward_bf16(float* gwte, const bf16* gout, const int* tokens, int n_tok, int D, int V, int* err, cudaStream_t st);
 
 template <typename T> int rmsnorm_forward(T* out, float* rstd, const T* x, const float* w, int N, int C, float eps, cudaStream_t st);
 // gx += d(rmsnorm)/dx ; gw (+)= sum over rows [w_row0, w_row1) of gout * x * rstd.
@@ -32,7 +35,7 @@ template <typename T> int add_forward(T* out, const T* a, const T* b, size_t n, 
 // row_weight (may be null): per-row gradient scale replacing grad_scale; 0 = masked row (zero gradient, zero loss). With
 // row weights the stored row loss is already weighted.
 template <typename T> int xent_forward_backward(T* logits, float* row_loss, const int* targets, const float* row_weight, int N, int V,
-                                                int ldv, float grad_scale, cudaStream_t st);
+                                                int ldv, float grad_scale, int* err, cudaStream_t st);
 // loss = (1/B) sum_b (1/S) sum_s row_loss   (weighted != 0: the rows are already weighted, so no 1/S)
 int loss_reduce(float* out, const float* row_loss, int B, int S, int weighted, cudaStream_t st);
 

@@ -16,49 +16,58 @@ inline bool aligned16(const void* p) { return (((uintptr_t)p) & 15) == 0; }
 // ------------------------------------------------------------------------------------------------
 // Embedding gather: out[t,:] = table[tokens[t],:]  (reference: embed_lookup, src/baremetal/trainer.c:275-298,
 // which reads the fp32 master table). One thread per 4 elements.
+// An id outside [0, V) never indexes the table: the row becomes zero and the error word is set (BMB_ERR_BAD_TOKEN).
 template <typename T>
 __global__ void embedding_forward_kernel(T* __restrict__ out, const float* __restrict__ table, const int* __restrict__ tokens,
-                                         int n_tok, int D4) {
+                                         int n_tok, int D4, int V, int* __restrict__ err) {
     const long i = blockIdx.x * (long)blockDim.x + threadIdx.x;
     if (i >= (long)n_tok * D4) return;
     const int t = (int)(i / D4), d4 = (int)(i - (long)t * D4);
-    const float4 v = reinterpret_cast<const float4*>(table + (size_t)tokens[t] * D4 * 4)[d4];
+    const int tok = tokens[t];
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if ((unsigned)tok < (unsigned)V) v = reinterpret_cast<const float4*>(table + (size_t)tok * D4 * 4)[d4];
+    else if (d4 == 0 && err) atomicExch(err, BMB_ERR_BAD_TOKEN);
     T* o = out + (size_t)t * D4 * 4 + d4 * 4;
     o[0] = from_f32<T>(v.x); o[1] = from_f32<T>(v.y); o[2] = from_f32<T>(v.z); o[3] = from_f32<T>(v.w);
 }
-template <typename T> int embedding_forward(T* out, const float* table, const int* tokens, int n_tok, int D, cudaStream_t st) {
+template <typename T> int embedding_forward(T* out, const float* table, const int* tokens, int n_tok, int D, int V, int* err, cudaStream_t st) {
     if (D % 4) return -1;
     const long n = (long)n_tok * (D / 4);
-    embedding_forward_kernel<T><<<ceil_div(n, 256), 256, 0, st>>>(out, table, tokens, n_tok, D / 4);
+    embedding_forward_kernel<T><<<ceil_div(n, 256), 256, 0, st>>>(out, table, tokens, n_tok, D / 4, V, err);
     return 0;
 }
-template int embedding_forward<float>(float*, const float*, const int*, int, int, cudaStream_t);
-template int embedding_forward<bf16>(bf16*, const float*, const int*, int, int, cudaStream_t);
+template int embedding_forward<float>(float*, const float*, const int*, int, int, int, int*, cudaStream_t);
+template int embedding_forward<bf16>(bf16*, const float*, const int*, int, int, int, int*, cudaStream_t);
 
 // Embedding scatter-add: gwte[tokens[t],:] += gout[t,:] with float atomics, on top of whatever the
 // buffer already holds (the tied LM-head wgrad) — reference: embedding_backward, src/kernels/backward.metal:636.
 template <typename T>
 __global__ void embedding_backward_kernel(float* __restrict__ gwte, const T* __restrict__ gout, const int* __restrict__ tokens,
-                                          int n_tok, int D4) {
+                                          int n_tok, int D4, int V, int* __restrict__ err) {
     const long i = blockIdx.x * (long)blockDim.x + threadIdx.x;
     if (i >= (long)n_tok * D4) return;
     const int t = (int)(i / D4), d4 = (int)(i - (long)t * D4);
+    const int tok = tokens[t];
+    if ((unsigned)tok >= (unsigned)V) {  // never scatter outside the table
+        if (d4 == 0 && err) atomicExch(err, BMB_ERR_BAD_TOKEN);
+        return;
+    }
     const T* g = gout + (size_t)t * D4 * 4 + d4 * 4;
-    float* dst = gwte + (size_t)tokens[t] * D4 * 4 + d4 * 4;
+    float* dst = gwte + (size_t)tok * D4 * 4 + d4 * 4;
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(to_f32(g[0])), "f"(to_f32(g[1])),
                  "f"(to_f32(g[2])), "f"(to_f32(g[3]))
                  : "memory");
 }
-int embedding_backward_f32(float* gwte, const float* gout, const int* tokens, int n_tok, int D, cudaStream_t st) {
+int embedding_backward_f32(float* gwte, const float* gout, const int* tokens, int n_tok, int D, int V, int* err, cudaStream_t st) {
     if (D % 4 || !aligned16(gwte)) return -1;
     const long n = (long)n_tok * (D / 4);
-    embedding_backward_kernel<float><<<ceil_div(n, 256), 256, 0, st>>>(gwte, gout, tokens, n_tok, D / 4);
+    embedding_backward_kernel<float><<<ceil_div(n, 256), 256, 0, st>>>(gwte, gout, tokens, n_tok, D / 4, V, err);
     return 0;
 }
-int embedding_backward_bf16(float* gwte, const bf16* gout, const int* tokens, int n_tok, int D, cudaStream_t st) {
+int embedding_backward_bf16(float* gwte, const bf16* gout, const int* tokens, int n_tok, int D, int V, int* err, cudaStream_t st) {
     if (D % 4 || !aligned16(gwte)) return -1;
     const long n = (long)n_tok * (D / 4);
-    embedding_backward_kernel<bf16><<<ceil_div(n, 256), 256, 0, st>>>(gwte, gout, tokens, n_tok, D / 4);
+    embedding_backward_kernel<bf16><<<ceil_div(n, 256), 256, 0, st>>>(gwte, gout, tokens, n_tok, D / 4, V, err);
     return 0;
 }
 
@@ -294,11 +303,9 @@ static int rmsnorm_backward_launch(T* gx, float* gw, int gw_accumulate, const T*
     int nblocks = ceil_div(N, WARPS_PER_BLOCK);
     if (nblocks > RMS_BWD_MAX_BLOCKS) nblocks = RMS_BWD_MAX_BLOCKS;
     const size_t smem = (size_t)WARPS_PER_BLOCK * C * sizeof(float) + (size_t)NV * Vec<T>::N * 32 * sizeof(float);
-    static bool attr_done = false;
-    if (!attr_done) {
+    static std::atomic<unsigned long long> attr_done{0};
+    if (first_use_on_current_device(attr_done))
         cudaFuncSetAttribute(rmsnorm_backward_kernel<T, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
-        attr_done = true;
-    }
     if (smem > 64 * 1024) return -2;
     rmsnorm_backward_kernel<T, NV><<<nblocks, BLOCK, smem, st>>>(gx, scratch, gout, x, w, rstd, N, C, w_row0, w_row1);
     rmsnorm_backward_reduce_kernel<<<ceil_div(C, 32), dim3(32, 32), 0, st>>>(gw, scratch, nblocks, C, gw_accumulate);
@@ -498,7 +505,7 @@ constexpr int XENT_THREADS = 512;
 template <typename T>
 __global__ void __launch_bounds__(XENT_THREADS)
 xent_kernel(T* __restrict__ logits, float* __restrict__ row_loss, const int* __restrict__ targets, const float* __restrict__ row_weight,
-            int V, int ldv, float grad_scale) {
+            int V, int ldv, float grad_scale, int* __restrict__ err) {
     constexpr int VN = Vec<T>::N;
     __shared__ float red[XENT_THREADS / 32];
     __shared__ float bcast;
@@ -553,10 +560,14 @@ xent_kernel(T* __restrict__ logits, float* __restrict__ row_loss, const int* __r
     __syncthreads();
     sum = bcast;
     const float inv = 1.0f / sum;
+    // A target outside [0, V) on a row that counts is never used as an index: the row's loss is 0, its gradient is the plain
+    // softmax, and the error word is set (BMB_ERR_BAD_TARGET). Rows with weight 0 never read their target.
     const int tgt = targets[row];
+    const bool tgt_ok = (unsigned)tgt < (unsigned)V;
     if (threadIdx.x == 0) {
-        const float nll = -(to_f32(lr[tgt]) - mx - logf(sum));
+        const float nll = tgt_ok ? -(to_f32(lr[tgt]) - mx - logf(sum)) : 0.f;
         row_loss[row] = row_weight ? nll * grad_scale : nll;
+        if (!tgt_ok && err) atomicExch(err, BMB_ERR_BAD_TARGET);
     }
     __syncthreads();  // the target logit is read before any thread overwrites it
     for (int v = threadIdx.x; v < nvec; v += XENT_THREADS) {
@@ -572,13 +583,13 @@ xent_kernel(T* __restrict__ logits, float* __restrict__ row_loss, const int* __r
 }
 template <typename T>
 int xent_forward_backward(T* logits, float* row_loss, const int* targets, const float* row_weight, int N, int V, int ldv, float grad_scale,
-                          cudaStream_t st) {
+                          int* err, cudaStream_t st) {
     if (V % Vec<T>::N || ldv % Vec<T>::N || !aligned16(logits)) return -1;
-    xent_kernel<T><<<N, XENT_THREADS, 0, st>>>(logits, row_loss, targets, row_weight, V, ldv, grad_scale);
+    xent_kernel<T><<<N, XENT_THREADS, 0, st>>>(logits, row_loss, targets, row_weight, V, ldv, grad_scale, err);
     return 0;
 }
-template int xent_forward_backward<float>(float*, float*, const int*, const float*, int, int, int, float, cudaStream_t);
-template int xent_forward_backward<bf16>(bf16*, float*, const int*, const float*, int, int, int, float, cudaStream_t);
+template int xent_forward_backward<float>(float*, float*, const int*, const float*, int, int, int, float, int*, cudaStream_t);
+template int xent_forward_backward<bf16>(bf16*, float*, const int*, const float*, int, int, int, float, int*, cudaStream_t);
 
 // loss = (1/B) sum_b (1/S) sum_s row_loss[b,s], summed in a fixed order
 // (reference: per-sequence mean scheduler.c:1634, batch mean trainer.c:528).

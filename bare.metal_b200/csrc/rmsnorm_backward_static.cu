@@ -74,11 +74,22 @@ extern "C" int bmc_rmsnorm_backward_static(void* cuda_stream, int dtype, void* d
     const int rc = scratch_on_current_device(&scratch);
     if (rc) return rc;
     cudaStream_t st = (cudaStream_t)cuda_stream;
+    int lrc;
     if (dtype == BMC_F32)
-        return bmb::rmsnorm_backward<float>((float*)d_gx, d_gw_f32, gw_accumulate, (const float*)d_gout, (const float*)d_x, d_w, d_rstd, N,
-                                            C, w_row0, w_row1, scratch, st);
-    if (dtype == BMC_BF16)
-        return bmb::rmsnorm_backward<bmb::bf16>((bmb::bf16*)d_gx, d_gw_f32, gw_accumulate, (const bmb::bf16*)d_gout, (const bmb::bf16*)d_x,
-                                                d_w, d_rstd, N, C, w_row0, w_row1, scratch, st);
-    return -2;
+        lrc = bmb::rmsnorm_backward<float>((float*)d_gx, d_gw_f32, gw_accumulate, (const float*)d_gout, (const float*)d_x, d_w, d_rstd, N,
+                                           C, w_row0, w_row1, scratch, st);
+    else if (dtype == BMC_BF16)
+        lrc = bmb::rmsnorm_backward<bmb::bf16>((bmb::bf16*)d_gx, d_gw_f32, gw_accumulate, (const bmb::bf16*)d_gout, (const bmb::bf16*)d_x,
+                                               d_w, d_rstd, N, C, w_row0, w_row1, scratch, st);
+    else
+        return -2;
+    if (lrc) return lrc;
+    // A launch that the runtime refused (a stream of another device, a first call made during stream capture, ...) is an
+    // error of this call, reported the way the context-based entry points report it: -200 - cudaError.
+    const cudaError_t le = cudaPeekAtLastError();
+    if (le != cudaSuccess) {
+        fprintf(stderr, "bmc_rmsnorm_backward_static: launch failed: %s\n", cudaGetErrorString(le));
+        return -200 - (int)le;
+    }
+    return 0;
 }

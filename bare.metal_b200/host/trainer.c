@@ -249,7 +249,7 @@ static int forward_and_loss(bm_trainer_t* t, int B, const uint8_t* d_attn_mask, 
     /* embedding rows come from the fp32 master (embed_lookup, src/baremetal/trainer.c:275-298); with the
      * "ref_stale_embedding" option, fp32 mode reads the initial table instead, as the reference does there. */
     TRY(bmc_embedding_forward(be, dt, t->act[0].x, (t->d_embed_frozen && dt == BMC_F32) ? t->d_embed_frozen : wf32(t, p_emb),
-                              t->d_tokens, M, D));
+                              t->d_tokens, M, D, V));
     for (int l = 0; l < L; ++l) {
         bm_layer_act_t* c = &t->act[l];
         const int pb = 9 * l;
@@ -341,7 +341,7 @@ static int backward(bm_trainer_t* t, int B, const uint8_t* d_attn_mask) {
     /* tied embedding: scatter dL/dx_0 on top of the LM-head wgrad already in the same buffer
      * (embed_backward, src/baremetal/trainer.c:302-346) */
     if (t->ref_input_grad_carry) TRY(bmc_seq_prefix_accumulate(be, dt, t->dres, t->d_gx_carry, B, (size_t)S * D));
-    TRY(bmc_embedding_backward(be, dt, gptr(t, p_emb), t->dres, t->d_tokens, M, D));
+    TRY(bmc_embedding_backward(be, dt, gptr(t, p_emb), t->dres, t->d_tokens, M, D, V));
     if (t->dp) TRY(bm_dp_bucket_ready(t->dp, -1));
     return 0;
 }
@@ -455,6 +455,23 @@ static float step_host(bm_trainer_t* t, const int* inputs, const int* targets, c
     if (T != t->S) {
         BM_LOG_ERROR("bm_train_step: S=%d != trainer S=%d (rebuild trainer for new S)", T, t->S);
         return -1.0f;
+    }
+    /* Ids index device memory (embedding gather and scatter, the target logit): a value outside [0, vocab_size) is refused here,
+     * before anything is uploaded or enqueued. A target on a row that the loss mask excludes is never read (as in
+     * xent_backward_masked, src/kernels/backward.metal:609-612), so ignore markers such as -100 are fine there. */
+    {
+        const int V = t->model->arch.vocab_size;
+        const size_t n = (size_t)B * T;
+        for (size_t i = 0; i < n; ++i) {
+            if ((unsigned)inputs[i] >= (unsigned)V) {
+                BM_LOG_ERROR("bm_train_step: input id %d at position %zu is outside the vocabulary [0, %d)", inputs[i], i, V);
+                return -1.0f;
+            }
+            if ((!loss_mask || loss_mask[i]) && (unsigned)targets[i] >= (unsigned)V) {
+                BM_LOG_ERROR("bm_train_step: target id %d at position %zu is outside the vocabulary [0, %d)", targets[i], i, V);
+                return -1.0f;
+            }
+        }
     }
     if (ensure_batch(t, B) != 0) return -1.0f;
     bmc_ctx_t* be = t->ctx->be;

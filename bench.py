@@ -135,11 +135,35 @@ def fill_weights(lib, model, a, seed=42, std=0.02):
         off += cnt
 
 
+REF_ARM_MAX_THREADS = 16   # every box quotes the same baseline, whatever number of cores its lease exposes
+REF_ARM_BUDGET_S = 200.0   # the timed steps of the reference arm stop after this much CPU wall time
+
+
 def reference_tokens_per_sec(steps, warmup, S_ref=32, B_ref=1):
-    """The reference's own training step on the host cores (oracle/_ref). Returns (tokens/s, cores, sample text)."""
-    ref = bmapi.load_reference()
+    """The reference's own training step on the host cores (oracle/_ref; the one place besides the parity checks where this
+    file executes anything under oracle/). Returns (tokens/s, threads, sample text, ms per step).
+
+    A launcher may export OMP_NUM_THREADS=1 for its workers (torch.distributed.run does): the thread count is therefore set
+    explicitly, to the cores this process may run on, capped at REF_ARM_MAX_THREADS. Timed steps stop once REF_ARM_BUDGET_S is
+    used up (at least two are always timed); the count actually timed is part of the sample text."""
+    try:
+        avail = len(os.sched_getaffinity(0))
+    except AttributeError:
+        avail = os.cpu_count() or 1
+    threads = max(1, min(avail, REF_ARM_MAX_THREADS))
+    os.environ["OMP_NUM_THREADS"] = str(threads)   # read by libgomp when the oracle library is the first to load it
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import oracle_check as oc
+    ref = oc.load_reference()
     if ref is None:
         return None, 0, "oracle/_ref/libbm_ref.so not built", None
+    try:   # libgomp may have been initialised already with the launcher's value
+        gomp = C.CDLL("libgomp.so.1")
+        gomp.omp_set_num_threads(C.c_int(threads))
+        gomp.omp_get_max_threads.restype = C.c_int
+        threads = int(gomp.omp_get_max_threads())
+    except OSError:
+        pass
     a = bmapi.make_arch(MODEL)
     a.precision = bmapi.BM_PRECISION_BF16
     ctx = ref.bm_create(bmapi.BM_DEVICE_METAL)
@@ -156,24 +180,27 @@ def reference_tokens_per_sec(steps, warmup, S_ref=32, B_ref=1):
     tr = ref.bm_create_trainer(ctx, model, C.byref(cfg))
     x, y = bmapi.lcg_batch(B_ref * (steps + warmup), S_ref, a.vocab_size)
     times = []
+    t_begin = time.perf_counter()
     for i in range(steps + warmup):
+        if len(times) >= 2 and time.perf_counter() - t_begin > REF_ARM_BUDGET_S:
+            break
         xs = np.ascontiguousarray(x[i * B_ref:(i + 1) * B_ref])
         ys = np.ascontiguousarray(y[i * B_ref:(i + 1) * B_ref])
         t0 = time.perf_counter()
         loss = ref.bm_train_step(tr, bmapi.as_int_ptr(xs), bmapi.as_int_ptr(ys), B_ref, S_ref)
         dt = time.perf_counter() - t0
-        if i >= warmup:
+        if i >= warmup or (i >= 1 and time.perf_counter() - t_begin > REF_ARM_BUDGET_S / 2):
             times.append(dt)
         if not np.isfinite(loss):
             raise RuntimeError("reference step returned a non-finite loss")
     ref.bm_destroy_trainer(tr)
     ref.bm_destroy_model(model)
     ref.bm_destroy(ctx)
-    cores = int(os.environ.get("OMP_NUM_THREADS", os.cpu_count() or 1))
     tps = B_ref * S_ref * len(times) / sum(times)
-    sample = (f"{MODEL} bf16-weights, {B_ref} sequence x {S_ref} tokens per step, {warmup} warm-up + {len(times)} timed "
-              f"steps, reference C11 host code + its kernel sources on {cores} host threads")
-    return tps, cores, sample, sum(times) / len(times) * 1e3
+    sample = (f"{MODEL} bf16-weights, {B_ref} sequence x {S_ref} tokens per step, {len(times)} timed steps of the {steps} asked for "
+              f"(time budget {REF_ARM_BUDGET_S:.0f} s), reference C11 host code + its kernel sources on {threads} host threads "
+              f"(cap {REF_ARM_MAX_THREADS}; {avail} cores available)")
+    return tps, threads, sample, sum(times) / len(times) * 1e3
 
 
 def run_reference_arm(args):
@@ -201,8 +228,7 @@ def run_reference_arm(args):
 def run_attention(args):
     """Isolated causal GQA flash attention forward + backward, bf16, 15 query / 5 KV heads, head_dim 64, batch 16
     (batch 4 at 8192 keeps the capture small); one JSON line per sequence length."""
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
-    from devutil import BMC_BF16, Backend, Ptr
+    from bmcapi import BMC_BF16, Backend, Ptr
     lib = bmapi.load_product()
     be = Backend(lib)
     lib.bmc_timer_begin.argtypes = [C.c_void_p, C.c_int]
@@ -251,8 +277,7 @@ def run_attention(args):
 def run_gemm(args):
     """The linear-layer GEMMs of the 360M step (forward, input gradient, weight gradient) in isolation, bf16 operands drawn
     from N(0,1), 16 x 2048 token rows; one JSON line per shape and kind. --shape picks one (e.g. gate_up)."""
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
-    from devutil import BMC_BF16, Backend, Ptr
+    from bmcapi import BMC_BF16, Backend, Ptr
     lib = bmapi.load_product()
     be = Backend(lib)
     lib.bmc_timer_begin.argtypes = [C.c_void_p, C.c_int]

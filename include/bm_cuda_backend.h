@@ -73,8 +73,10 @@ int        bmc_gemm_timing(bmc_ctx_t* ctx, int enable);
 int        bmc_gemm_timing_collect(bmc_ctx_t* ctx, double* out3);
 
 /* ---- embedding (embed_lookup src/baremetal/trainer.c:275-298; embedding_backward src/kernels/backward.metal:636) ---- */
-int bmc_embedding_forward(bmc_ctx_t* ctx, int dtype, void* d_out, const float* d_table_f32, const int* d_tokens, int n_tok, int D);
-int bmc_embedding_backward(bmc_ctx_t* ctx, int dtype, float* d_gwte_f32, const void* d_gout, const int* d_tokens, int n_tok, int D);
+/* V = rows of the table. A token id outside [0, V) is never used as an index: the gathered row is zero, the scatter skips it, and
+ * bmc_status() reports 2001 afterwards. */
+int bmc_embedding_forward(bmc_ctx_t* ctx, int dtype, void* d_out, const float* d_table_f32, const int* d_tokens, int n_tok, int D, int V);
+int bmc_embedding_backward(bmc_ctx_t* ctx, int dtype, float* d_gwte_f32, const void* d_gout, const int* d_tokens, int n_tok, int D, int V);
 
 /* ---- RMSNorm (rmsnorm_forward forward.metal:993; rmsnorm_backward_x / _w backward.metal:340,379) ----
  * forward also stores 1/rms per row in d_rstd (may be NULL).

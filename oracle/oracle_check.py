@@ -22,6 +22,32 @@ Q_NORM_GRAD, Q_GX_CARRY, Q_STALE_EMBED = 1, 2, 4
 Q_ALL = 7
 
 
+REF_LIB_PATH = os.path.join(HERE, "_ref", "libbm_ref.so")
+
+
+def reference_read(lib, trainer, what, i):
+    n = lib.bmref_state_size(trainer, i)
+    fn = {bmapi.BMX_WEIGHT: lib.bmref_weight, bmapi.BMX_GRAD: lib.bmref_grad, bmapi.BMX_ADAM_M: lib.bmref_m, bmapi.BMX_ADAM_V: lib.bmref_v}[what]
+    return np.ctypeslib.as_array(fn(trainer, i), (n,)).copy()
+
+
+def load_reference():
+    """The reference's own host code + kernels on CPU (built by oracle/build_ref.sh). None if absent."""
+    if not os.path.exists(REF_LIB_PATH):
+        return None
+    lib = bmapi.bind_public_api(C.CDLL(REF_LIB_PATH))
+    vp, fp = C.c_void_p, C.POINTER(C.c_float)
+    lib.bmref_set_precision.argtypes = [vp, C.c_int]
+    lib.bmref_set_quant.argtypes = [vp, C.c_int]
+    lib.bmt_quantize_q8.restype, lib.bmt_quantize_q8.argtypes = C.c_size_t, [fp, vp, C.c_size_t]
+    lib.bmref_n_states.restype, lib.bmref_n_states.argtypes = C.c_int, [vp]
+    lib.bmref_state_size.restype, lib.bmref_state_size.argtypes = C.c_size_t, [vp, C.c_int]
+    for n in ("bmref_grad", "bmref_weight", "bmref_m", "bmref_v"):
+        getattr(lib, n).restype, getattr(lib, n).argtypes = fp, [vp, C.c_int]
+    lib.bmref_logits.restype, lib.bmref_logits.argtypes = fp, [vp]
+    return lib
+
+
 def load_port():
     if not os.path.exists(PORT_PATH):
         raise RuntimeError(f"{PORT_PATH} missing: run `make -C oracle`")
@@ -121,7 +147,7 @@ class LibTrainer:
 
     def read(self, what, i):
         if self.kind == "reference":
-            return bmapi.reference_read(self.lib, self.tr, what, i)
+            return reference_read(self.lib, self.tr, what, i)
         return bmapi.product_read(self.lib, self.tr, what, i)
 
     def close(self):
@@ -209,7 +235,7 @@ class LibSession:
 
 def make_oracle(a, w, S, precision, cfg, prefer="reference", quirks=True):
     """The strongest checker available: the reference build when present, else the plain-C port."""
-    ref = bmapi.load_reference() if prefer == "reference" and quirks else None
+    ref = load_reference() if prefer == "reference" and quirks else None
     if ref is not None:
         return LibTrainer(ref, "reference", a, w, S, precision, cfg)
     return PortTrainer(a, w, S, precision, cfg, quirks=Q_ALL if quirks else 0)

@@ -15,6 +15,12 @@ seeded random-init models and LCG tokens; losses, per-tensor gradient norms, sam
 values are stored. Cases: scaled-down family members in fp32 and bf16-weight mode, batches of more than one sequence,
 and the 135M-parameter single-step fp32 configuration (B=1, S=64, AdamW lr 3e-4, beta (0.9, 0.95), wd 0.1).
 
+Part 2b (`--only TAG[,TAG...]` regenerates single files of parts 2, 2b and 3 by their tag) — the configurations that are
+benchmarked: ref_train_step_360m_{f32,bf16}_b2.npz (SmolLM2-360M, two sequences of 128 tokens, two optimizer steps) and
+ref_train_curve_135m_{f32,bf16}.npz (SmolLM2-135M, 50 optimizer steps on two sequences of 128 tokens each: the loss curve
+and sampled final weights), ref_decode_360m_f32_q8.npz (SmolLM2-360M with Q8 layers: a 64-token prompt and 16 greedy tokens,
+sampled logits only).
+
 Part 3 (`--only-decode` regenerates just this part) — ref_quantize_q8.npz: the reference's Q8 block quantiser on seeded
 inputs with its edge cases; ref_decode_*.npz: logits of the reference inference session after every prefix of a seeded
 prompt and a greedy continuation, fp32 / bf16 weights, plain and Q8.
@@ -106,6 +112,64 @@ def ref_train_case(ref, tag, arch_name, B, S, precision, steps, accum=1):
     print(f"ref_train_step_{tag}.npz: losses {losses}")
 
 
+def ref_curve_case(ref, tag, arch_name, B, S, precision, steps):
+    """Loss after every optimizer step of a `steps`-step run of the reference, plus norms and sampled values of the final weights
+    (the reference's own analogue runs 10 AdamW steps on real weights, test/g3_test.c:27)."""
+    a = bmapi.make_arch(arch_name)
+    w = bmapi.make_weights(a)
+    cfg = bmapi.train_config(seq_len=S)
+    x, y = bmapi.lcg_batch(B * steps, S, a.vocab_size)
+    tr = oc.LibTrainer(ref, "reference", a, w, S, precision, cfg, tag=tag)
+    n = tr.n_tensors()
+    losses = []
+    for st in range(steps):
+        losses.append(tr.step(np.ascontiguousarray(x[st * B:(st + 1) * B]), np.ascontiguousarray(y[st * B:(st + 1) * B])))
+        print(f"  {tag} step {st + 1}/{steps} loss {losses[-1]:.6f}", flush=True)
+    wn, wi, ws = [], [], []
+    for i in range(n):
+        t = tr.read(bmapi.BMX_WEIGHT, i)
+        idx = sample_idx(t.size, 1000 + i)
+        wn.append(np.linalg.norm(t.astype(np.float64)))
+        wi.append(np.pad(idx, (0, SAMPLE - idx.size), constant_values=-1))
+        ws.append(np.pad(t[idx], (0, SAMPLE - idx.size)))
+    tr.close()
+    np.savez_compressed(os.path.join(OUT, f"ref_train_curve_{tag}.npz"), arch=np.array(arch_name), B=B, S=S, precision=precision,
+                        steps=steps, n_tensors=n, losses=np.array(losses, np.float32), weight_norm=np.array(wn),
+                        weight_idx=np.array(wi), weight_val=np.array(ws, np.float32))
+    print(f"ref_train_curve_{tag}.npz: first {losses[0]:.5f} last {losses[-1]:.5f}")
+
+
+def ref_decode_sampled_case(ref, tag, arch_name, precision, quant, n_prompt, n_new, n_sample=256, top=8):
+    """Large-vocabulary variant of ref_decode_case: the logits of the full prompt and of every greedy step are stored only at
+    `n_sample` seeded vocabulary indices and at the reference's `top` largest entries."""
+    a = bmapi.make_arch(arch_name)
+    w = bmapi.make_weights(a, layer_scale=DECODE_LAYER_SCALE)
+    prompt = bmapi.lcg_tokens(n_prompt, a.vocab_size, seed=1234)
+    s = oc.LibSession(ref, "reference", a, w, precision, quant, tag=tag)
+    idx = np.sort(np.random.default_rng(99).choice(a.vocab_size, size=n_sample, replace=False)).astype(np.int64)
+    seq = list(int(t) for t in prompt)
+    greedy, margin, vals, top_ids, top_vals, amax = [], [], [], [], [], []
+    for k in range(n_new):
+        s.reset()
+        lg = s.forward(np.array(seq, np.int32))
+        order = np.argsort(lg)[::-1][:top]
+        greedy.append(int(np.argmax(lg)))
+        margin.append(float(lg[order[0]] - lg[order[1]]))
+        vals.append(lg[idx])
+        top_ids.append(order)
+        top_vals.append(lg[order])
+        amax.append(float(np.abs(lg).max()))
+        seq.append(greedy[-1])
+        print(f"  {tag} token {k + 1}/{n_new}: {greedy[-1]} margin {margin[-1]:.4g}", flush=True)
+    s.close()
+    np.savez_compressed(os.path.join(OUT, f"ref_decode_{tag}.npz"), arch=np.array(arch_name), precision=precision, quant=quant,
+                        layer_scale=DECODE_LAYER_SCALE, prompt=np.asarray(prompt, np.int32), sample_idx=idx,
+                        sample_logits=np.array(vals, np.float32), top_ids=np.array(top_ids, np.int32),
+                        top_logits=np.array(top_vals, np.float32), logit_absmax=np.array(amax, np.float32),
+                        greedy=np.array(greedy, np.int32), margin=np.array(margin, np.float32))
+    print(f"ref_decode_{tag}.npz: greedy {greedy} min margin {min(margin):.3g}")
+
+
 def q8_inputs():
     """Seeded quantiser inputs with the edge cases of the scheme: an all-zero block, a block whose extreme is negative,
     exact .5 ties after scaling, a huge dynamic range, denormal-sized values."""
@@ -158,12 +222,26 @@ def ref_decode_case(ref, tag, arch_name, precision, quant, n_prompt, n_new):
 def main():
     args = [a for a in sys.argv[1:] if not a.startswith("--")]
     ref_dir = args[0] if args else os.environ.get("BM_REFERENCE", "/root/reference")
-    ref = bmapi.load_reference()
+    ref = oc.load_reference()
     if ref is None:
         raise SystemExit("oracle/_ref/libbm_ref.so missing: run oracle/build_ref.sh first")
     F32, BF16 = bmapi.BM_PRECISION_FP32, bmapi.BM_PRECISION_BF16
     decode_cases = (("gqa_f32", "gqa", F32, 0), ("gqa_f32_q8", "gqa", F32, 8), ("gqa_bf16", "gqa", BF16, 0),
                     ("gqa_bf16_q8", "gqa", BF16, 8), ("tiny_f32_q8", "tiny", F32, 8))
+    big = {
+        "360m_bf16_b2": lambda: ref_train_case(ref, "360m_bf16_b2", "smollm2-360m", 2, 128, BF16, 2),
+        "360m_f32_b2": lambda: ref_train_case(ref, "360m_f32_b2", "smollm2-360m", 2, 128, F32, 2),
+        "135m_bf16_b2": lambda: ref_train_case(ref, "135m_bf16_b2", "smollm2-135m", 2, 128, BF16, 2),
+        "curve_135m_bf16": lambda: ref_curve_case(ref, "135m_bf16", "smollm2-135m", 2, 128, BF16, 50),
+        "curve_135m_f32": lambda: ref_curve_case(ref, "135m_f32", "smollm2-135m", 2, 128, F32, 50),
+        "decode_360m_f32_q8": lambda: ref_decode_sampled_case(ref, "360m_f32_q8", "smollm2-360m", F32, 8, 64, 16),
+        "decode_360m_bf16_q8": lambda: ref_decode_sampled_case(ref, "360m_bf16_q8", "smollm2-360m", BF16, 8, 64, 16),
+    }
+    for arg in sys.argv[1:]:
+        if arg.startswith("--only="):
+            for tag in arg[len("--only="):].split(","):
+                big[tag]()
+            return
     if "--only-decode" in sys.argv:
         ref_q8_case(ref)
         for tag, arch, prec, quant in decode_cases:
@@ -181,6 +259,9 @@ def main():
         ref_decode_case(ref, tag, arch, prec, quant, 12, 12)
     if "--skip-135m" not in sys.argv:
         ref_train_case(ref, "135m_f32_c1", "smollm2-135m", 1, 64, F32, 1)
+    if "--with-benchmarked-configs" in sys.argv:   # hours of CPU time: the 360M steps, the 135M 50-step curves, the 360M Q8 session
+        for fn in big.values():
+            fn()
 
 
 if __name__ == "__main__":

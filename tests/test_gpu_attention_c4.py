@@ -10,7 +10,7 @@ import pytest
 
 import oracle_check as oc
 import portk
-from devutil import BMC_BF16, BMC_F32, Backend, Ptr, bf16_round
+from bmcapi import BMC_BF16, BMC_F32, Backend, Ptr, bf16_round
 
 pytestmark = pytest.mark.gpu
 NH, NKV, HD = 15, 5, 64

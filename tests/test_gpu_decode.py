@@ -146,7 +146,7 @@ def test_135m_q8_decode_against_oracle(product):
 
 # ---- kernels of the inference path through the extern "C" backend ABI ----------------------------------------------------
 import portk  # noqa: E402
-from devutil import BMC_F32, Backend, Ptr, bf16_round, f32_to_bf16_bits  # noqa: E402
+from bmcapi import BMC_F32, Backend, Ptr, bf16_round, f32_to_bf16_bits  # noqa: E402
 
 RNG = np.random.default_rng(77)
 

@@ -8,7 +8,7 @@ import pytest
 
 import oracle_check as oc
 import portk
-from devutil import BMC_BF16, BMC_F32, Backend, Ptr, bf16_round
+from bmcapi import BMC_BF16, BMC_F32, Backend, Ptr, bf16_round
 
 pytestmark = pytest.mark.gpu
 RNG = np.random.default_rng(1234)
@@ -205,18 +205,18 @@ def test_embedding_gather_and_scatter(be, dtype, goldens):
     tokens = RNG.integers(0, 6, T).astype(np.int32)  # heavy repetition: atomics must accumulate
     dtok = be.put(tokens)
     out = be.zeros(T * D, dtype)
-    be.ok("embedding_forward", dtype, Ptr(out), Ptr(be.put(table)), Ptr(dtok), T, D)
+    be.ok("embedding_forward", dtype, Ptr(out), Ptr(be.put(table)), Ptr(dtok), T, D, V)
     ref = table[tokens]
     assert np.array_equal(be.get(out, (T, D), dtype), bf16_round(ref) if dtype == BMC_BF16 else ref)
     g0 = rnd(V, D)
     gw = be.put(g0)
-    be.ok("embedding_backward", dtype, Ptr(gw), Ptr(be.put(go, dtype)), Ptr(dtok), T, D)
+    be.ok("embedding_backward", dtype, Ptr(gw), Ptr(be.put(go, dtype)), Ptr(dtok), T, D, V)
     check(be.get(gw, (V, D)), portk.embedding_backward(g0, go, tokens), BMC_F32, 3)
     g = goldens  # test/embed_bwd_test.c: V8 D5 T6 -> D padded to 8 for the 4-float vector width
     gout = np.zeros((6, 8), np.float32)
     gout[:, :5] = g["embed_gout"].reshape(6, 5)
     gw = be.zeros(64)
-    be.ok("embedding_backward", BMC_F32, Ptr(gw), Ptr(be.put(gout)), Ptr(be.put(g["embed_tokens"])), 6, 8)
+    be.ok("embedding_backward", BMC_F32, Ptr(gw), Ptr(be.put(gout)), Ptr(be.put(g["embed_tokens"])), 6, 8, 8)
     check(be.get(gw, (8, 8))[:, :5], g["embed_gwte"].reshape(8, 5), BMC_F32, 3)
 
 

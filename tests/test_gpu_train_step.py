@@ -91,7 +91,7 @@ def test_masked_step_matches_reference(product, precision, use_attn_mask):
     """Completion-only loss with a padding mask (bm_train_step_masked; the reference's masked_sft_test.c): attn == 0 removes a
     position as key and as query, loss == 1 marks the rows that count, each sequence normalised by its own count; one
     sequence has no counted row at all."""
-    ref = bmapi.load_reference()
+    ref = oc.load_reference()
     if ref is None:
         pytest.skip("reference build not present")
     a = bmapi.make_arch("gqa")
@@ -162,7 +162,7 @@ def test_state_file_round_trip_and_layout(product, tmp_path):
 def test_reference_can_load_our_state_file(product, tmp_path):
     """Cross-implementation check of the checkpoint layout: a state written by the GPU trainer is accepted by the
     reference's bm_load_state (its loader validates the tensor count and every size, trainer.c:213-226)."""
-    ref = bmapi.load_reference()
+    ref = oc.load_reference()
     if ref is None:
         pytest.skip("reference build not present")
     a = bmapi.make_arch("tiny")

@@ -136,7 +136,7 @@ def _write_safetensors(path, tensors, dtype="F32"):
     header, blobs, off = {}, [], 0
     for name, arr in tensors.items():
         if dtype == "BF16":
-            from devutil import f32_to_bf16_bits
+            from bmcapi import f32_to_bf16_bits
             raw = f32_to_bf16_bits(arr).tobytes()
         else:
             raw = np.ascontiguousarray(arr, np.float32).tobytes()
@@ -188,7 +188,7 @@ def test_safetensors_directory_loader(product, tmp_path, dtype, sharded):
     expect = np.concatenate([w[k].ravel() for k, _ in bmapi.weight_shapes(a)])
     assert n.value == expect.size
     if dtype == "BF16":
-        from devutil import bf16_round
+        from bmcapi import bf16_round
         expect = bf16_round(expect)
     assert np.array_equal(flat, expect)
     assert lib.bmx_model_vocab_size(model) == a.vocab_size

@@ -223,14 +223,14 @@ def test_goldens_exist():
     assert os.path.exists(os.path.join(GOLD_DIR, "ref_train_step_135m_f32_c1.npz"))
 
 
-@pytest.mark.skipif(bmapi.load_reference() is None, reason="reference build oracle/_ref/libbm_ref.so not present")
+@pytest.mark.skipif(oc.load_reference() is None, reason="reference build oracle/_ref/libbm_ref.so not present")
 @pytest.mark.parametrize("arch,B,S,prec", [("tiny", 2, 16, 0), ("tiny", 1, 24, 2), ("small", 3, 24, 0)])
 def test_port_matches_live_reference_build(arch, B, S, prec):
     a = bmapi.make_arch(arch)
     w = bmapi.make_weights(a, seed=7)
     cfg = bmapi.train_config(seq_len=S)
     x, y = bmapi.lcg_batch(B * 2, S, a.vocab_size, seed=9)
-    r = oc.LibTrainer(bmapi.load_reference(), "reference", a, w, S, prec, cfg)
+    r = oc.LibTrainer(oc.load_reference(), "reference", a, w, S, prec, cfg)
     p = oc.PortTrainer(a, w, S, prec, cfg)
     for st in range(2):
         xs, ys = np.ascontiguousarray(x[st * B:(st + 1) * B]), np.ascontiguousarray(y[st * B:(st + 1) * B])
@@ -291,7 +291,7 @@ def test_product_host_quantiser_is_bit_exact_with_the_reference():
 
 
 def test_live_reference_quantiser_matches_port_on_random_blocks(port):
-    ref = bmapi.load_reference()
+    ref = oc.load_reference()
     if ref is None:
         pytest.skip("reference build absent")
     x = (np.random.default_rng(5).standard_normal(32 * 257) * 0.3).astype(np.float32)

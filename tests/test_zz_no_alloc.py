@@ -13,7 +13,7 @@ import numpy as np
 import pytest
 
 import oracle_check as oc
-from devutil import BMC_BF16, BMC_F32, Backend, Ptr, bf16_round
+from bmcapi import BMC_BF16, BMC_F32, Backend, Ptr, bf16_round
 
 pytestmark = pytest.mark.gpu
 
