@@ -14,13 +14,13 @@
 // The single UMMA-issuing thread interleaves the two tiles (PV_A(j), QK_A(j+1), PV_B(j), QK_B(j+1), ...) so that
 // the tensor core works on one tile while the other tile's warpgroup does its softmax. K/V tiles are
 // in a four-stage ring filled by a TMA producer warp. 12 warps: TMA, UMMA, two idle (they complete the control warpgroup), 4 + 4 softmax.
-// Same semantics as flash_fwd_kernel in attention_mma.cu (reference: attention_forward_train_tiled,
-// src/kernels/forward.metal:2122): out = softmax(scale * Q K^T, causal) V and lse = log-sum-exp of the scaled scores.
+// Reference: attention_forward_train_tiled, src/kernels/forward.metal:2122: out = softmax(scale * Q K^T, causal) V and
+// lse = log-sum-exp of the scaled scores.
 #include <cuda.h>
 #include <stdio.h>
 #include <stdlib.h>
 
-#include "attention_mma.cuh"
+#include "attention_umma.cuh"
 #include "ptx_sm100.cuh"
 
 namespace bmb {
@@ -424,6 +424,7 @@ struct BwdArgs {
     bf16 *gk, *gv;
     int ldgkv;
     const float *lse, *delta;
+    const float* rope_cs;   // [S][32][cos, sin] or null; when set, dK leaves rotated backwards (the transposed rotation of RoPE)
     int S, NH, NKV;
     float scale;
     int* err;
@@ -740,6 +741,26 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 tmem_ld_32x16(lane_addr + BT_DK + cg * 16, a);
                 tmem_ld_32x16(lane_addr + BT_DV + cg * 16, c2);
                 tmem_ld_wait();
+                if (p.rope_cs) {   // uniform over the warp: the tensor-memory load below is a warp-collective instruction
+                    // RoPE backward on dK (rope_backward_seq, src/kernels/backward.metal:980): column i of the first half pairs with
+                    // column i + 32, which another warp of this lane quarter owns; every warp of a quarter can read all columns
+                    // of its lanes, so the partner's 16 values are fetched as well.
+                    uint32_t o[16];
+                    tmem_ld_32x16(lane_addr + BT_DK + (cg ^ 2) * 16, o);
+                    tmem_ld_wait();
+                    if (kj < p.S) {   // rows past the end of the sequence have no table entry (and are not stored)
+                        const float4* cs4 = reinterpret_cast<const float4*>(p.rope_cs + ((size_t)kj * (FHD / 2) + (cg & 1) * 16) * 2);
+#pragma unroll
+                        for (int i = 0; i < 16; i += 2) {
+                            const float4 t = cs4[i >> 1];   // cos_i, sin_i, cos_i+1, sin_i+1
+                            const float m0 = __uint_as_float(a[i]), m1 = __uint_as_float(a[i + 1]);
+                            const float o0 = __uint_as_float(o[i]), o1 = __uint_as_float(o[i + 1]);
+                            // first half: g0 * cos + g1 * sin; second half: g1 * cos - g0 * sin  (g0 = first-half value, g1 = its partner)
+                            a[i] = __float_as_uint(cg < 2 ? m0 * t.x + o0 * t.y : m0 * t.x - o0 * t.y);
+                            a[i + 1] = __float_as_uint(cg < 2 ? m1 * t.z + o1 * t.w : m1 * t.z - o1 * t.w);
+                        }
+                    }
+                }
             } else {
 #pragma unroll
                 for (int i = 0; i < 16; ++i) { a[i] = 0u; c2[i] = 0u; }
@@ -806,6 +827,39 @@ __global__ void flash_delta_umma_kernel(float* __restrict__ delta, const bf16* _
     if (sub == 0 && gid < total) delta[((size_t)(row / S) * NH + h) * S + (row % S)] = d;
 }
 
+// dQ leaves the backward as fp32 sums in a scratch buffer (several key blocks add to the same rows); this pass turns them into
+// the bf16 gradient and, when a rotation table is given, applies RoPE backward on the way (rope_backward_seq,
+// src/kernels/backward.metal:980) so that no separate rotation pass reads and rewrites the tensor. One thread: four adjacent
+// columns of the first half of a head and their partners 32 columns further on.
+__global__ void dq_finish_kernel(bf16* __restrict__ gq, int ldgq, const float* __restrict__ acc, int rows, int NH, int S,
+                                 const float* __restrict__ cs) {
+    const long i = blockIdx.x * (long)blockDim.x + threadIdx.x;
+    if (i >= (long)rows * NH * 8) return;
+    const int c = (int)(i & 7) * 4;
+    const long rh = i >> 3;
+    const int h = (int)(rh % NH);
+    const long row = rh / NH;
+    const float* src = acc + ((size_t)row * NH + h) * FHD + c;
+    float4 x0 = *reinterpret_cast<const float4*>(src), x1 = *reinterpret_cast<const float4*>(src + 32);
+    if (cs) {
+        const float4* t = reinterpret_cast<const float4*>(cs + ((size_t)(row % S) * (FHD / 2) + c) * 2);
+        const float4 t0 = t[0], t1 = t[1];   // cos, sin of pairs c, c+1 | c+2, c+3
+        const float4 a = x0, b = x1;
+        x0.x = a.x * t0.x + b.x * t0.y; x1.x = b.x * t0.x - a.x * t0.y;
+        x0.y = a.y * t0.z + b.y * t0.w; x1.y = b.y * t0.z - a.y * t0.w;
+        x0.z = a.z * t1.x + b.z * t1.y; x1.z = b.z * t1.x - a.z * t1.y;
+        x0.w = a.w * t1.z + b.w * t1.w; x1.w = b.w * t1.z - a.w * t1.w;
+    }
+    bf16* dst = gq + (size_t)row * ldgq + (size_t)h * FHD + c;
+    __nv_bfloat162 lo0 = __floats2bfloat162_rn(x0.x, x0.y), lo1 = __floats2bfloat162_rn(x0.z, x0.w);
+    __nv_bfloat162 hi0 = __floats2bfloat162_rn(x1.x, x1.y), hi1 = __floats2bfloat162_rn(x1.z, x1.w);
+    uint2 w0, w1;
+    w0.x = *reinterpret_cast<uint32_t*>(&lo0); w0.y = *reinterpret_cast<uint32_t*>(&lo1);
+    w1.x = *reinterpret_cast<uint32_t*>(&hi0); w1.y = *reinterpret_cast<uint32_t*>(&hi1);
+    *reinterpret_cast<uint2*>(dst) = w0;
+    *reinterpret_cast<uint2*>(dst + 32) = w1;
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -835,7 +889,32 @@ int make_rows_map(CUtensorMap* tm, const void* base, uint64_t width, uint64_t ro
                : -11;
 }
 
+__global__ void cast_rows_kernel(bf16* __restrict__ out, int ldo, const float* __restrict__ in, int ldi, int rows, int cols4) {
+    const long i = blockIdx.x * (long)blockDim.x + threadIdx.x;
+    if (i >= (long)rows * cols4) return;
+    const int r = (int)(i / cols4), c = (int)(i - (long)r * cols4) * 4;
+    const float4 v = *reinterpret_cast<const float4*>(in + (size_t)r * ldi + c);
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 o;
+    o.x = *reinterpret_cast<uint32_t*>(&lo);
+    o.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(out + (size_t)r * ldo + c) = o;
+}
+
 }  // namespace
+
+bool flash_attention_supported(int HD, int NH, int NKV) { return HD == FHD && NKV > 0 && NH % NKV == 0; }
+
+size_t flash_attention_backward_scratch_bytes(int B, int S, int NH, int HD) {
+    return (size_t)B * S * NH * HD * sizeof(float) + (size_t)B * NH * S * sizeof(float);
+}
+
+int cast_rows_f32_to_bf16(bf16* out, int ldo, const float* in, int ldi, int rows, int cols, cudaStream_t st) {
+    if (cols % 4 || ldi % 4 || ldo % 4 || (((uintptr_t)out) & 7) || (((uintptr_t)in) & 15)) return -1;
+    const long n = (long)rows * (cols / 4);
+    cast_rows_kernel<<<(int)((n + 255) / 256), 256, 0, st>>>(out, ldo, in, ldi, rows, cols / 4);
+    return 0;
+}
 
 int flash_attention_forward_umma(bf16* out, int ldo, float* lse, const bf16* q, int ldq, const bf16* k, const bf16* v, int ldkv, int B,
                                  int S, int NH, int NKV, int HD, float scale, int* err_flag, cudaStream_t st) {
@@ -892,7 +971,8 @@ int flash_attention_forward_umma(bf16* out, int ldo, float* lse, const bf16* q, 
 
 int flash_attention_backward_umma(bf16* gq, int ldgq, bf16* gk, bf16* gv, int ldgkv, const bf16* gout, int ldo, const bf16* out,
                                   const float* lse, const bf16* q, int ldq, const bf16* k, const bf16* v, int ldkv, int B, int S, int NH,
-                                  int NKV, int HD, float scale, void* scratch, int* err_flag, cudaStream_t st) {
+                                  int NKV, int HD, float scale, void* scratch, const float* delta_in, const float* rope_cs, int* err_flag,
+                                  cudaStream_t st) {
     if (HD != FHD || NKV <= 0 || NH % NKV) return -1;
     if ((ldq % 8) || (ldkv % 8) || (ldo % 8) || (ldgkv % 8) || (ldgq % 4) || (((uintptr_t)q) & 15) || (((uintptr_t)k) & 15) ||
         (((uintptr_t)v) & 15) || (((uintptr_t)gout) & 15) || (((uintptr_t)gk) & 15) || (((uintptr_t)gv) & 15) || (((uintptr_t)gq) & 7) ||
@@ -905,7 +985,8 @@ int flash_attention_backward_umma(bf16* gq, int ldgq, bf16* gk, bf16* gv, int ld
     const uint64_t rows = (uint64_t)B * S;
     const int QD = NH * HD;
     float* dq_acc = (float*)scratch;
-    float* delta = dq_acc + rows * QD;
+    float* delta_own = dq_acc + rows * QD;
+    const float* delta = delta_in ? delta_in : delta_own;
     CUtensorMap tq, tk, tv, tg;
     int rc = make_rows_map(&tq, q, (uint64_t)NH * HD, rows, ldq, FQ);
     if (!rc) rc = make_rows_map(&tk, k, (uint64_t)NKV * HD, rows, ldkv, FK);
@@ -913,15 +994,17 @@ int flash_attention_backward_umma(bf16* gq, int ldgq, bf16* gk, bf16* gv, int ld
     if (!rc) rc = make_rows_map(&tg, gout, (uint64_t)NH * HD, rows, ldo, FQ);
     if (rc) return rc;
     cudaMemsetAsync(dq_acc, 0, rows * QD * sizeof(float), st);
-    const long groups = (long)rows * NH;   // eight lanes each
-    flash_delta_umma_kernel<<<(int)((groups * 8 + 255) / 256), 256, 0, st>>>(delta, gout, out, ldo, B, S, NH);
+    if (!delta_in) {
+        const long groups = (long)rows * NH;   // eight lanes each
+        flash_delta_umma_kernel<<<(int)((groups * 8 + 255) / 256), 256, 0, st>>>(delta_own, gout, out, ldo, B, S, NH);
+    }
 #ifdef BMB_TRACE
     long long* trace = nullptr;
     cudaMalloc(&trace, 10 * 32 * sizeof(long long));
     cudaMemset(trace, 0, 10 * 32 * sizeof(long long));
-    BwdArgs a{trace, dq_acc, gk, gv, ldgkv, lse, delta, S, NH, NKV, scale, err_flag};
+    BwdArgs a{trace, dq_acc, gk, gv, ldgkv, lse, delta, rope_cs, S, NH, NKV, scale, err_flag};
 #else
-    BwdArgs a{dq_acc, gk, gv, ldgkv, lse, delta, S, NH, NKV, scale, err_flag};
+    BwdArgs a{dq_acc, gk, gv, ldgkv, lse, delta, rope_cs, S, NH, NKV, scale, err_flag};
 #endif
     dim3 grid((S + FK - 1) / FK, NKV, B);
     flash_bwd_umma_kernel<<<grid, BWD_THREADS, BWD_DYN_SMEM, st>>>(tq, tk, tv, tg, a);
@@ -949,7 +1032,9 @@ int flash_attention_backward_umma(bf16* gq, int ldgq, bf16* gk, bf16* gv, int ld
         fprintf(stderr, "flash_attention_backward_umma: launch failed: %s\n", cudaGetErrorString(le));
         return -7;
     }
-    return cast_rows_f32_to_bf16(gq, ldgq, dq_acc, QD, (int)rows, QD, st);
+    const long n = (long)rows * NH * 8;
+    dq_finish_kernel<<<(int)((n + 255) / 256), 256, 0, st>>>(gq, ldgq, dq_acc, (int)rows, NH, S, rope_cs);
+    return 0;
 }
 
 }  // namespace bmb

@@ -11,7 +11,7 @@
 #include <mutex>
 #include <vector>
 
-#include "attention_mma.cuh"
+#include "attention_umma.cuh"
 #include "decode_kernels.cuh"
 #include "gemm_umma.cuh"
 #include "kernels.cuh"
@@ -383,6 +383,41 @@ int bmc_matmul_backward_w(bmc_ctx_t* ctx, int dtype, float* d_gw, const void* d_
     return note(ctx, run_umma(ctx, g));
 }
 
+// ---- linear layers with a fused neighbour (bf16 tensor-core path only; BMC_ERR_UNFUSED otherwise) ----
+int bmc_matmul_swiglu_forward(bmc_ctx_t* ctx, int dtype, void* d_gu, int ldgu, void* d_act, int ldact, const void* d_inp, int ldi,
+                              const void* d_w_gate_up, int BT, int C, int H) {
+    BMC_CHECK_CTX(ctx);
+    if (dtype != BMC_BF16 || (H % 128)) return BMC_ERR_UNFUSED;
+    GemmProblem g{BT, 2 * H, C, (const bf16*)d_inp, ldi, 0, (const bf16*)d_w_gate_up, C, 0, d_gu, ldgu, GEMM_OUT_BF16, nullptr, 0, 1, 0, 0};
+    g.epi = GEMM_EPI_SWIGLU_FWD;
+    g.C2 = d_act;
+    g.ldc2 = ldact;
+    const int rc = run_umma(ctx, g);
+    return rc == -8 ? BMC_ERR_UNFUSED : note(ctx, rc);
+}
+int bmc_matmul_backward_inp_swiglu(bmc_ctx_t* ctx, int dtype, void* d_dgu, int lddgu, const void* d_gout, int ldgo, const void* d_w_down,
+                                   const void* d_gu, int ldgu, int BT, int H, int OC) {
+    BMC_CHECK_CTX(ctx);
+    if (dtype != BMC_BF16 || (H % 128)) return BMC_ERR_UNFUSED;
+    // dact[BT, H] = gout[BT, OC] x W_down[OC, H] (MN-major B), never stored: the epilogue turns it into dgate | dup
+    GemmProblem g{BT, H, OC, (const bf16*)d_gout, ldgo, 0, (const bf16*)d_w_down, H, 1, d_dgu, lddgu, GEMM_OUT_BF16, (const bf16*)d_gu, ldgu, 1, 0, 0};
+    g.epi = GEMM_EPI_SWIGLU_BWD;
+    const int rc = run_umma(ctx, g);
+    return rc == -8 ? BMC_ERR_UNFUSED : note(ctx, rc);
+}
+int bmc_matmul_backward_inp_rowdot(bmc_ctx_t* ctx, int dtype, void* d_ginp, int ldgi, float* d_rowdot, const void* d_gout, int ldgo,
+                                   const void* d_weight, const void* d_other, int ldother, int BT, int C, int OC, int S, int NH) {
+    BMC_CHECK_CTX(ctx);
+    if (dtype != BMC_BF16 || NH * 64 != C || S <= 0 || (BT % S)) return BMC_ERR_UNFUSED;
+    GemmProblem g{BT, C, OC, (const bf16*)d_gout, ldgo, 0, (const bf16*)d_weight, C, 1, d_ginp, ldgi, GEMM_OUT_BF16, (const bf16*)d_other, ldother, 1, 0, 0};
+    g.epi = GEMM_EPI_ROWDOT;
+    g.aux = d_rowdot;
+    g.aux_S = S;
+    g.aux_NH = NH;
+    const int rc = run_umma(ctx, g);
+    return rc == -8 ? BMC_ERR_UNFUSED : note(ctx, rc);
+}
+
 // ---- RoPE --------------------------------------------------------------------------------------------
 int bmc_rope(bmc_ctx_t* ctx, int dtype, void* d_q, int ldq, void* d_k, int ldk, const float* d_cs_table, int rows, int S, int NH, int NKV,
              int HD, int dir) {
@@ -398,45 +433,42 @@ int bmc_attention_forward(bmc_ctx_t* ctx, int dtype, void* d_out, int ldo, float
     if (dtype == BMC_F32)
         return note(ctx, attention_forward_simt<float>((float*)d_out, ldo, d_lse, (const float*)d_q, ldq, (const float*)d_k,
                                                        (const float*)d_v, ldkv, d_mask, B, S, NH, NKV, HD, scale, ctx->stream));
-    if (flash_attention_supported(HD, NH, NKV, d_mask != nullptr)) {
-        static const bool use_mma = [] { const char* e = getenv("BM_ATTN_FWD"); return e && e[0] == 'm'; }();
-        if (!use_mma && (ldo % 8) == 0)
-            return note(ctx, flash_attention_forward_umma((bf16*)d_out, ldo, d_lse, (const bf16*)d_q, ldq, (const bf16*)d_k, (const bf16*)d_v,
-                                                          ldkv, B, S, NH, NKV, HD, scale, ctx->d_err, ctx->stream));
-        return note(ctx, flash_attention_forward((bf16*)d_out, ldo, d_lse, (const bf16*)d_q, ldq, (const bf16*)d_k, (const bf16*)d_v,
-                                                 ldkv, B, S, NH, NKV, HD, scale, ctx->stream));
-    }
+    if (!d_mask && flash_attention_supported(HD, NH, NKV) && (ldo % 8) == 0)
+        return note(ctx, flash_attention_forward_umma((bf16*)d_out, ldo, d_lse, (const bf16*)d_q, ldq, (const bf16*)d_k, (const bf16*)d_v,
+                                                      ldkv, B, S, NH, NKV, HD, scale, ctx->d_err, ctx->stream));
     return note(ctx, attention_forward_simt<bf16>((bf16*)d_out, ldo, d_lse, (const bf16*)d_q, ldq, (const bf16*)d_k, (const bf16*)d_v,
                                                   ldkv, d_mask, B, S, NH, NKV, HD, scale, ctx->stream));
 }
-int bmc_attention_backward(bmc_ctx_t* ctx, int dtype, void* d_gq, int ldgq, void* d_gk, void* d_gv, int ldgkv, const void* d_gout,
-                           int ldo, const void* d_out, const float* d_lse, const void* d_q, int ldq, const void* d_k, const void* d_v,
-                           int ldkv, const uint8_t* d_mask, int B, int S, int NH, int NKV, int HD, float scale) {
+// Attention backward; with d_delta / d_rope_cs the two neighbouring passes of the training step are folded in (see the header).
+int bmc_attention_backward_fused(bmc_ctx_t* ctx, int dtype, void* d_gq, int ldgq, void* d_gk, void* d_gv, int ldgkv, const void* d_gout,
+                                 int ldo, const void* d_out, const float* d_lse, const void* d_q, int ldq, const void* d_k, const void* d_v,
+                                 int ldkv, const uint8_t* d_mask, const float* d_delta, const float* d_rope_cs, int B, int S, int NH, int NKV,
+                                 int HD, float scale) {
     BMC_CHECK_CTX(ctx);
     const size_t rows = (size_t)B * S;
+    if (dtype == BMC_BF16 && !d_mask && flash_attention_supported(HD, NH, NKV) && (ldgkv % 8) == 0 && (ldo % 8) == 0) {
+        const size_t need = flash_attention_backward_scratch_bytes(B, S, NH, HD);
+        void* scratch = scratch_get(ctx, &ctx->attn_scratch, &ctx->attn_scratch_bytes, need);
+        if (!scratch) return -50;
+        return note(ctx, flash_attention_backward_umma((bf16*)d_gq, ldgq, (bf16*)d_gk, (bf16*)d_gv, ldgkv, (const bf16*)d_gout, ldo,
+                                                       (const bf16*)d_out, d_lse, (const bf16*)d_q, ldq, (const bf16*)d_k, (const bf16*)d_v,
+                                                       ldkv, B, S, NH, NKV, HD, scale, scratch, d_delta, d_rope_cs, ctx->d_err, ctx->stream),
+                    d_delta ? 3 : 4);
+    }
+    int rc;
     if (dtype == BMC_F32) {
         // gK/gV accumulate through atomics and must start from zero (reference: zero_buffer before attention_backward,
         // src/baremetal/scheduler.c:1372-1383). K and V rows may be interleaved with other columns, so clear row by row.
         cudaMemset2DAsync(d_gk, (size_t)ldgkv * 4, 0, (size_t)NKV * HD * 4, rows, ctx->stream);
         cudaMemset2DAsync(d_gv, (size_t)ldgkv * 4, 0, (size_t)NKV * HD * 4, rows, ctx->stream);
-        return note(ctx, attention_backward_simt<float>((float*)d_gq, ldgq, (float*)d_gk, (float*)d_gv, ldgkv, (const float*)d_gout, ldo,
-                                                        (const float*)d_out, d_lse, (const float*)d_q, ldq, (const float*)d_k,
-                                                        (const float*)d_v, ldkv, d_mask, B, S, NH, NKV, HD, scale, ctx->stream));
+        rc = attention_backward_simt<float>((float*)d_gq, ldgq, (float*)d_gk, (float*)d_gv, ldgkv, (const float*)d_gout, ldo,
+                                            (const float*)d_out, d_lse, (const float*)d_q, ldq, (const float*)d_k, (const float*)d_v, ldkv,
+                                            d_mask, B, S, NH, NKV, HD, scale, ctx->stream);
+        if (rc == 0 && d_rope_cs)
+            rc = rope_apply<float>((float*)d_gq, ldgq, (float*)d_gk, ldgkv, d_rope_cs, (int)rows, S, NH, NKV, HD, -1, ctx->stream);
+        return note(ctx, rc, d_rope_cs ? 2 : 1);
     }
-    if (flash_attention_supported(HD, NH, NKV, d_mask != nullptr)) {
-        const size_t need = flash_attention_backward_scratch_bytes(B, S, NH, HD);
-        void* scratch = scratch_get(ctx, &ctx->attn_scratch, &ctx->attn_scratch_bytes, need);
-        if (!scratch) return -50;
-        static const bool bwd_mma = [] { const char* e = getenv("BM_ATTN_BWD"); return e && e[0] == 'm'; }();
-        if (!bwd_mma && (ldgkv % 8) == 0 && (ldo % 8) == 0)
-            return note(ctx, flash_attention_backward_umma((bf16*)d_gq, ldgq, (bf16*)d_gk, (bf16*)d_gv, ldgkv, (const bf16*)d_gout, ldo,
-                                                           (const bf16*)d_out, d_lse, (const bf16*)d_q, ldq, (const bf16*)d_k, (const bf16*)d_v,
-                                                           ldkv, B, S, NH, NKV, HD, scale, scratch, ctx->d_err, ctx->stream), 3);
-        return note(ctx, flash_attention_backward((bf16*)d_gq, ldgq, (bf16*)d_gk, (bf16*)d_gv, ldgkv, (const bf16*)d_gout, ldo,
-                                                  (const bf16*)d_out, d_lse, (const bf16*)d_q, ldq, (const bf16*)d_k, (const bf16*)d_v,
-                                                  ldkv, B, S, NH, NKV, HD, scale, scratch, ctx->stream), 3);
-    }
-    // General shapes (head_dim != 64, masks): exact fp32 kernel into fp32 scratch, then one cast per output.
+    // General bf16 shapes (head_dim != 64, masks): exact fp32 kernel into fp32 scratch, then one cast per output.
     const int QD = NH * HD, KVD = NKV * HD;
     const size_t need = rows * (size_t)(QD + 2 * KVD) * sizeof(float);
     float* scratch = (float*)scratch_get(ctx, &ctx->attn_scratch, &ctx->attn_scratch_bytes, need);
@@ -445,13 +477,20 @@ int bmc_attention_backward(bmc_ctx_t* ctx, int dtype, void* d_gq, int ldgq, void
     float* sgk = sgq + rows * QD;
     float* sgv = sgk + rows * KVD;
     cudaMemsetAsync(sgk, 0, rows * 2 * KVD * sizeof(float), ctx->stream);
-    int rc = attention_backward_simt<bf16>(sgq, QD, sgk, sgv, KVD, (const bf16*)d_gout, ldo, (const bf16*)d_out, d_lse, (const bf16*)d_q,
-                                           ldq, (const bf16*)d_k, (const bf16*)d_v, ldkv, d_mask, B, S, NH, NKV, HD, scale, ctx->stream);
+    rc = attention_backward_simt<bf16>(sgq, QD, sgk, sgv, KVD, (const bf16*)d_gout, ldo, (const bf16*)d_out, d_lse, (const bf16*)d_q,
+                                       ldq, (const bf16*)d_k, (const bf16*)d_v, ldkv, d_mask, B, S, NH, NKV, HD, scale, ctx->stream);
     if (rc) return rc;
-    rc = cast_rows_f32_to_bf16((bf16*)d_gq, ldgq, sgq, QD, (int)rows, QD, ctx->stream);
+    if (d_rope_cs) rc = rope_apply<float>(sgq, QD, sgk, KVD, d_rope_cs, (int)rows, S, NH, NKV, HD, -1, ctx->stream);
+    if (!rc) rc = cast_rows_f32_to_bf16((bf16*)d_gq, ldgq, sgq, QD, (int)rows, QD, ctx->stream);
     if (!rc) rc = cast_rows_f32_to_bf16((bf16*)d_gk, ldgkv, sgk, KVD, (int)rows, KVD, ctx->stream);
     if (!rc) rc = cast_rows_f32_to_bf16((bf16*)d_gv, ldgkv, sgv, KVD, (int)rows, KVD, ctx->stream);
-    return note(ctx, rc, 4);
+    return note(ctx, rc, d_rope_cs ? 5 : 4);
+}
+int bmc_attention_backward(bmc_ctx_t* ctx, int dtype, void* d_gq, int ldgq, void* d_gk, void* d_gv, int ldgkv, const void* d_gout,
+                           int ldo, const void* d_out, const float* d_lse, const void* d_q, int ldq, const void* d_k, const void* d_v,
+                           int ldkv, const uint8_t* d_mask, int B, int S, int NH, int NKV, int HD, float scale) {
+    return bmc_attention_backward_fused(ctx, dtype, d_gq, ldgq, d_gk, d_gv, ldgkv, d_gout, ldo, d_out, d_lse, d_q, ldq, d_k, d_v, ldkv, d_mask,
+                                        nullptr, nullptr, B, S, NH, NKV, HD, scale);
 }
 
 // ---- SwiGLU / add ------------------------------------------------------------------------------------

@@ -1,8 +1,7 @@
 // Persistent, warp-specialised tcgen05 GEMM. See gemm_umma.cuh for the operand convention.
 //
-// CTA = 192 threads: warp 0 = TMA producer, warp 1 = TMEM owner + UMMA issuer,
-// warps 2..5 = epilogue (warp w reads TMEM lanes 32*(w&3) .. +31).
-// Tile = 128 (M) x tile_n (N, <= 256) x 64 (K per stage), 4-stage shared-memory ring,
+// CTA = 192 threads: warp 0 = TMA producer, warp 1 = TMEM owner + UMMA issuer, warps 2..5 = epilogue (warp w reads TMEM lanes 32*(w&3) .. +31; the two warps of a lane quarter split the columns).
+// Tile = 128 (M) x tile_n (N, <= 256) x 64 (K per stage), shared-memory ring of as many stages as fit (3 to 8),
 // two TMEM accumulator buffers of 256 fp32 columns so the epilogue of tile i overlaps the
 // main loop of tile i+1. One CTA per SM; work units (tile, k-split) are dealt round-robin.
 #include "gemm_umma.cuh"
@@ -22,19 +21,25 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 64;
-constexpr int STAGES = 4;         // one CTA per tile: 4 x (16 KB of A + 32 KB of B)
-constexpr int STAGES_PAIR = 6;    // CTA pair per tile: 6 x (16 KB of A + 16 KB = this CTA's half of B)
+constexpr int MAX_STAGES = 8;     // ring stages: as many (16 KB of A + this CTA's rows of B) as fit, see ring_stages()
 constexpr int MAX_BN = 256;
 constexpr int A_STAGE_BYTES = BM * BK * 2;      // 16 KB
-constexpr int B_STAGE_BYTES = MAX_BN * BK * 2;  // 32 KB
-constexpr int B_HALF_STAGE_BYTES = B_STAGE_BYTES / 2;
 constexpr int MN_BOX_BYTES = 64 * BK * 2;       // one 64(mn) x 64(k) box of an MN-major operand
-constexpr int NUM_THREADS = 192;
+constexpr int EPI_WARPS = 4;      // one epilogue warp per TMEM lane quarter (eight, two per quarter splitting the columns, measured slower:
+                                  // every GEMM of the step lost 5-14 % while only the heaviest epilogue gained)
+constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;
 // Epilogue staging: each of the 4 epilogue warps owns 32 rows x 128 payload bytes (64 bf16 or 32 fp32 columns) at a
 // 144-byte pitch, which makes both the row-per-thread accesses and the 8-lanes-per-row accesses bank-conflict free.
 constexpr int STG_PITCH = 144;
 constexpr int STG_WARP_BYTES = 32 * STG_PITCH;
-constexpr int SMEM_DYN_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 4 * STG_WARP_BYTES + 1024;
+constexpr int RING_BYTES = 192 * 1024;  // what the operand ring may use: 227 KB less the staging rows and the alignment slack
+constexpr int SMEM_DYN_BYTES = RING_BYTES + EPI_WARPS * STG_WARP_BYTES + 1024;
+static_assert(SMEM_DYN_BYTES <= 227 * 1024, "shared memory budget");
+// stages of (A tile + bn_local rows of B, 128 bytes each) that fit in the ring
+__host__ __device__ inline int ring_stages(int bn_local) {
+    const int n = RING_BYTES / (A_STAGE_BYTES + bn_local * BK * 2);
+    return n > MAX_STAGES ? MAX_STAGES : n;
+}
 constexpr uint32_t TMEM_COLS = 512;
 
 struct KArgs {
@@ -49,11 +54,15 @@ struct KArgs {
     const __nv_bfloat16* R;
     int ldr;
     int* err;
+    void* C2;
+    int ldc2;
+    float* aux;
+    int aux_S, aux_NH;
 };
 
 struct __align__(8) Barriers {
-    uint64_t full[STAGES_PAIR];
-    uint64_t empty[STAGES_PAIR];
+    uint64_t full[MAX_STAGES];
+    uint64_t empty[MAX_STAGES];
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
     uint32_t tmem_base;
@@ -76,7 +85,7 @@ __device__ __forceinline__ void decode_unit(const KArgs& p, int u, int& m0, int&
 // pair computes a 256 x BN tile with tcgen05.mma.cta_group::2 — each CTA holds its 128 rows of A and HALF of the B tile, the
 // leader (cluster rank 0) issues the UMMAs, each CTA's TMEM receives its 128 rows of the accumulator and each CTA runs its own
 // epilogue. B is read from shared memory once per pair instead of once per CTA.
-template <int CTAS>
+template <int CTAS, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       const KArgs p) {
@@ -85,8 +94,9 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 
     // 1024-byte alignment: the 128B swizzle pattern is a function of address bits [7,10).
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    constexpr int NST = CTAS == 2 ? STAGES_PAIR : STAGES;
-    constexpr int BST = CTAS == 2 ? B_HALF_STAGE_BYTES : B_STAGE_BYTES;
+    const int bn_local = CTAS == 2 ? p.BN / 2 : p.BN;  // B rows held by this CTA
+    const int BST = bn_local * BK * 2;
+    const int NST = ring_stages(bn_local);
     uint8_t* sA = smem;
     uint8_t* sB = smem + NST * A_STAGE_BYTES;
     const uint32_t rank = CTAS == 2 ? cluster_ctarank() : 0u;   // 0 = leader of the pair
@@ -104,7 +114,7 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&bars.acc_full[b], 1);
-            mbar_init(&bars.acc_empty[b], 4 * CTAS);  // pair: the leader's collects the epilogue warps of both CTAs
+            mbar_init(&bars.acc_empty[b], EPI_WARPS * CTAS);  // pair: the leader's collects the epilogue warps of both CTAs
         }
         bars.abort_flag = 0;
         mbar_fence_init();
@@ -127,23 +137,24 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 
     // bytes one stage receives: this CTA's A tile and B tile — for a pair, both CTAs' (A tile + half B tile) on the leader's barrier
     const uint32_t stage_tx_bytes = CTAS == 2 ? (uint32_t)(2 * (BM * BK * 2 + (p.BN / 2) * BK * 2)) : (uint32_t)(BM * BK * 2 + p.BN * BK * 2);
-    const int bn_local = CTAS == 2 ? p.BN / 2 : p.BN;  // B rows held by this CTA
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
             tma_prefetch_desc(&tmA);
             tma_prefetch_desc(&tmB);
-            uint32_t c = 0;  // k-block counter across all of this CTA's units
+            int s = 0;        // ring stage and its phase, advanced per k-block across all of this CTA's units
+            uint32_t ph = 0;
             bool ok = true;
             for (int u = worker; u < units && ok; u += nworkers) {
                 int m0, n0, kb0, kb1;
                 decode_unit(p, u, m0, n0, kb0, kb1);
                 m0 += (int)rank * BM;        // this CTA's rows of the tile
-                n0 += (int)rank * bn_local;  // this CTA's part of the B tile
-                for (int kb = kb0; kb < kb1; ++kb, ++c) {
-                    const int s = c % NST;
-                    const uint32_t ph = (c / NST) & 1;
+                // gated forward: the tile's first half comes from the gate rows h0.., its second half from the up rows H + h0..
+                const int n_second = EPI == GEMM_EPI_SWIGLU_FWD ? p.N / 2 + (n0 / p.BN) * (p.BN / 2) : 0;
+                if (EPI == GEMM_EPI_SWIGLU_FWD) n0 = CTAS == 2 ? (rank ? n_second : (n0 / p.BN) * (p.BN / 2)) : (n0 / p.BN) * (p.BN / 2);
+                else n0 += (int)rank * bn_local;  // this CTA's part of the B tile
+                for (int kb = kb0; kb < kb1; ++kb, s = (s + 1 == NST ? 0 : s + 1), ph ^= (s == 0)) {
                     if (!mbar_wait(&bars.empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
                     uint8_t* a_dst = sA + s * A_STAGE_BYTES;
                     uint8_t* b_dst = sB + s * BST;
@@ -172,7 +183,10 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                         tma_load_2d(a_dst, &tmA, &bars.full[s], m0, k0);
                         tma_load_2d(a_dst + MN_BOX_BYTES, &tmA, &bars.full[s], m0 + 64, k0);
                     }
-                    if (!p.b_mn) {
+                    if (EPI == GEMM_EPI_SWIGLU_FWD) {
+                        tma_load_2d(b_dst, &tmB, &bars.full[s], k0, n0);
+                        tma_load_2d(b_dst + (p.BN / 2) * BK * 2, &tmB, &bars.full[s], k0, n_second);
+                    } else if (!p.b_mn) {
                         tma_load_2d(b_dst, &tmB, &bars.full[s], k0, n0);
                     } else {
                         for (int j = 0; j < p.BN / 64; ++j)
@@ -181,9 +195,7 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                 }
             }
             // Tail: do not let the CTA retire while UMMA commits may still arrive on `empty`.
-            for (int i = 0; i < NST && ok; ++i, ++c) {
-                const int s = c % NST;
-                const uint32_t ph = (c / NST) & 1;
+            for (int i = 0; i < NST && ok; ++i, s = (s + 1 == NST ? 0 : s + 1), ph ^= (s == 0)) {
                 if (!mbar_wait(&bars.empty[s], ph ^ 1, abort_flag)) ok = false;
             }
         }
@@ -196,7 +208,8 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             // 64-wide mn groups one box apart; one UMMA (K=16) = two k groups = 2048 B.
             const uint32_t a_lbo = p.a_mn ? MN_BOX_BYTES : 16, a_sbo = 1024, a_kstep = p.a_mn ? 2048 : 32;
             const uint32_t b_lbo = p.b_mn ? MN_BOX_BYTES : 16, b_sbo = 1024, b_kstep = p.b_mn ? 2048 : 32;
-            uint32_t c = 0;
+            int s = 0;
+            uint32_t ph = 0;
             int it = 0;
             bool ok = true;
             for (int u = worker; u < units && ok; u += nworkers, ++it) {
@@ -207,9 +220,7 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                 if (!mbar_wait(&bars.acc_empty[buf], acc_ph ^ 1, abort_flag)) { ok = false; break; }
                 tc_fence_after_sync();
                 const uint32_t tmem_acc = tmem_base + (uint32_t)buf * MAX_BN;
-                for (int kb = kb0; kb < kb1; ++kb, ++c) {
-                    const int s = c % NST;
-                    const uint32_t ph = (c / NST) & 1;
+                for (int kb = kb0; kb < kb1; ++kb, s = (s + 1 == NST ? 0 : s + 1), ph ^= (s == 0)) {
                     if (!mbar_wait(&bars.full[s], ph, abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
                     const uint32_t a_addr = smem_u32(sA + s * A_STAGE_BYTES);
@@ -233,7 +244,12 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         }
     } else {
         // ------------------------------ epilogue -----------------------------------
+        // Warp w may touch TMEM lanes 32 * (w % 4) .. +31 (a hardware rule). With more than one warp per lane quarter the warps
+        // of a quarter split the tile's columns: [0, cmid) and [cmid, BN), cmid a multiple of 64.
         const int q = warp & 3;
+        const int ew = warp - 2, hsel = ew >> 2;
+        const int cmid = EPI_WARPS > 4 ? min(p.BN, ((p.BN / 32 + 3) / 4) * 64) : p.BN;
+        const int c_lo = hsel ? cmid : 0, c_hi = hsel ? p.BN : cmid;
         int it = 0;
         bool ok = true;
         for (int u = worker; u < units && ok; u += nworkers, ++it) {
@@ -244,6 +260,159 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             const uint32_t acc_ph = (it >> 1) & 1;
             const int sub = lane & 7, rgrp = lane >> 3;
             const int row_base = m0 + q * 32;
+            if constexpr (EPI == GEMM_EPI_SWIGLU_FWD || EPI == GEMM_EPI_SWIGLU_BWD) {
+                // Both gated-MLP epilogues move rows as [first 32 columns | second 32 columns] = 2 x 64 bytes through the warp's
+                // staging rows: lanes 0-3 of a row carry the piece that belongs at column h, lanes 4-7 the piece at column H + h.
+                uint8_t* stg = smem + NST * (A_STAGE_BYTES + BST) + ew * STG_WARP_BYTES;
+                uint8_t* my_row = stg + lane * STG_PITCH;
+                const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)buf * MAX_BN;
+                const int piece = sub & 3, second = sub >> 2;
+                if constexpr (EPI == GEMM_EPI_SWIGLU_FWD) {
+                    const int half = p.BN / 2, H = p.N / 2;
+                    const int h0 = (n0 / p.BN) * half;
+                    __nv_bfloat16* Cgu = (__nv_bfloat16*)p.C;
+                    __nv_bfloat16* Cact = (__nv_bfloat16*)p.C2;
+                    ok = mbar_wait(&bars.acc_full[buf], acc_ph, abort_flag);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    for (int c0 = c_lo / 2; c0 < c_hi / 2 && h0 + c0 < H; c0 += 64) {
+                        uint32_t pa[32];  // act of 64 hidden units, packed bf16 pairs
+#pragma unroll
+                        for (int sc = 0; sc < 2; ++sc) {
+                            uint32_t g[32], u[32];
+                            tmem_ld_32x32(taddr0 + c0 + sc * 32, g);
+                            tmem_ld_32x32(taddr0 + half + c0 + sc * 32, u);
+                            tmem_ld_wait();
+                            uint32_t pg[16], pu[16];
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                // act is computed from the stored (bf16-rounded) gate and up, which is what the backward differentiates
+                                const __nv_bfloat162 gb = __floats2bfloat162_rn(__uint_as_float(g[2 * i]), __uint_as_float(g[2 * i + 1]));
+                                const __nv_bfloat162 ub = __floats2bfloat162_rn(__uint_as_float(u[2 * i]), __uint_as_float(u[2 * i + 1]));
+                                const float2 gf = __bfloat1622float2(gb), uf = __bfloat1622float2(ub);
+                                const float2 a2 = f2_mul(f2_mul(gf, sigmoid2_approx(gf)), uf);   // silu(gate) * up
+                                const __nv_bfloat162 ab = __floats2bfloat162_rn(a2.x, a2.y);
+                                pg[i] = *(const uint32_t*)&gb;
+                                pu[i] = *(const uint32_t*)&ub;
+                                pa[sc * 16 + i] = *(const uint32_t*)&ab;
+                            }
+#pragma unroll
+                            for (int v = 0; v < 4; ++v) {
+                                *(uint4*)(my_row + v * 16) = make_uint4(pg[4 * v], pg[4 * v + 1], pg[4 * v + 2], pg[4 * v + 3]);
+                                *(uint4*)(my_row + 64 + v * 16) = make_uint4(pu[4 * v], pu[4 * v + 1], pu[4 * v + 2], pu[4 * v + 3]);
+                            }
+                            __syncwarp();
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const int rr = rgrp + 4 * i, grow = row_base + rr;
+                                if (grow < p.M)
+                                    *(uint4*)(Cgu + (size_t)grow * p.ldc + (second ? H : 0) + h0 + c0 + sc * 32 + piece * 8) =
+                                        *(const uint4*)(stg + rr * STG_PITCH + sub * 16);
+                            }
+                            __syncwarp();
+                        }
+#pragma unroll
+                        for (int v = 0; v < 8; ++v) *(uint4*)(my_row + v * 16) = make_uint4(pa[4 * v], pa[4 * v + 1], pa[4 * v + 2], pa[4 * v + 3]);
+                        __syncwarp();
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int rr = rgrp + 4 * i, grow = row_base + rr;
+                            if (grow < p.M)
+                                *(uint4*)(Cact + (size_t)grow * p.ldc2 + h0 + c0 + sub * 8) = *(const uint4*)(stg + rr * STG_PITCH + sub * 16);
+                        }
+                        __syncwarp();
+                    }
+                } else {
+                    const int H = p.N;
+                    __nv_bfloat16* Cd = (__nv_bfloat16*)p.C;
+                    // saved gate | up of the first 32 columns are requested before the wait for the accumulator, every later
+                    // group while the previous one is being worked on
+                    // Two register buffers keep the saved gate | up rows two 32-column groups ahead of their use (the first two are
+                    // requested before the wait for the accumulator), and the rows of the NEXT tile are pulled into L2 a whole tile
+                    // ahead: with one warp per scheduler nothing else hides the memory latency.
+                    uint4 preA[8], preB[8];
+                    auto fetch = [&](uint4 (&pre)[8], int c0) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int grow = row_base + rgrp + 4 * i;
+                            pre[i] = (grow < p.M && n0 + c0 < H) ? *(const uint4*)(p.R + (size_t)grow * p.ldr + (second ? H : 0) + n0 + c0 + piece * 8)
+                                                               : make_uint4(0u, 0u, 0u, 0u);
+                        }
+                    };
+                    fetch(preA, c_lo);
+                    fetch(preB, c_lo + 32);
+                    if (u + nworkers < units) {
+                        int m1, n1, ka, kb;
+                        decode_unit(p, u + nworkers, m1, n1, ka, kb);
+                        const int prow = m1 + (int)rank * BM + q * 32 + lane;
+                        if (prow < p.M) {
+                            const __nv_bfloat16* g0 = p.R + (size_t)prow * p.ldr + n1;
+                            for (int b = c_lo * 2; b < c_hi * 2 && n1 + b / 2 < H; b += 128) {
+                                prefetch_l2((const uint8_t*)g0 + b);
+                                prefetch_l2((const uint8_t*)(g0 + H) + b);
+                            }
+                        }
+                    }
+                    ok = mbar_wait(&bars.acc_full[buf], acc_ph, abort_flag);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    auto process = [&](uint4 (&pre)[8], int c0) {
+                        uint32_t d[32];
+                        tmem_ld_32x32(taddr0 + c0, d);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) *(uint4*)(stg + (rgrp + 4 * i) * STG_PITCH + sub * 16) = pre[i];
+                        __syncwarp();
+                        if (c0 + 64 < c_hi) fetch(pre, c0 + 64);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            const uint4 gv = *(const uint4*)(my_row + v * 16), uv = *(const uint4*)(my_row + 64 + v * 16);
+                            const __nv_bfloat162* gb = (const __nv_bfloat162*)&gv;
+                            const __nv_bfloat162* ub = (const __nv_bfloat162*)&uv;
+                            uint4 og, ou;
+                            __nv_bfloat162* ogb = (__nv_bfloat162*)&og;
+                            __nv_bfloat162* oub = (__nv_bfloat162*)&ou;
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                // dgate = dact * up * s * (1 + x * (1 - s)), dup = dact * x * s, s = sigmoid(x)
+                                const float2 x = __bfloat1622float2(gb[i]), uu = __bfloat1622float2(ub[i]);
+                                const float2 dd = make_float2(__uint_as_float(d[v * 8 + 2 * i]), __uint_as_float(d[v * 8 + 2 * i + 1]));
+                                const float2 sg = sigmoid2_approx(x);
+                                const float2 xs = f2_mul(x, sg);
+                                const float2 oms = f2_fma(sg, make_float2(-1.f, -1.f), make_float2(1.f, 1.f));
+                                const float2 w = f2_fma(x, oms, make_float2(1.f, 1.f));
+                                const float2 dg = f2_mul(f2_mul(dd, uu), f2_mul(sg, w));
+                                const float2 du = f2_mul(dd, xs);
+                                ogb[i] = __floats2bfloat162_rn(dg.x, dg.y);
+                                oub[i] = __floats2bfloat162_rn(du.x, du.y);
+                            }
+                            *(uint4*)(my_row + v * 16) = og;
+                            *(uint4*)(my_row + 64 + v * 16) = ou;
+                        }
+                        __syncwarp();
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int rr = rgrp + 4 * i, grow = row_base + rr;
+                            if (grow < p.M)
+                                *(uint4*)(Cd + (size_t)grow * p.ldc + (second ? H : 0) + n0 + c0 + piece * 8) = *(const uint4*)(stg + rr * STG_PITCH + sub * 16);
+                        }
+                        __syncwarp();
+                    };
+                    for (int c0 = c_lo; c0 < c_hi && n0 + c0 < H; c0 += 64) {
+                        process(preA, c0);
+                        if (n0 + c0 + 32 < H) process(preB, c0 + 32);
+                    }
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) {
+                    if (CTAS == 2 && rank != 0) mbar_arrive_cluster(mapa_shared(&bars.acc_empty[buf], 0));
+                    else mbar_arrive(&bars.acc_empty[buf]);
+                }
+                continue;
+            }
             const bool c_al = (((uintptr_t)p.C) & 15) == 0;
             const bool bf16_fast = p.out_mode == GEMM_OUT_BF16 && c_al && (p.ldc % 8) == 0 && (n0 % 8) == 0 &&
                                    (!p.R || ((((uintptr_t)p.R) & 15) == 0 && (p.ldr % 8) == 0));
@@ -251,13 +420,20 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             // The residual does not depend on the accumulator: the first chunk's rows are requested before the wait for the
             // UMMAs, every later chunk's while the previous chunk is converted and stored (a global load issued only when its
             // chunk comes up costs a full memory latency per chunk, which made the short-K projections epilogue-bound).
+            if (p.R && u + nworkers < units) {   // the next tile's rows of R are pulled into L2 a whole tile ahead of their use
+                int m1, n1, ka, kb;
+                decode_unit(p, u + nworkers, m1, n1, ka, kb);
+                const int prow = m1 + (int)rank * BM + q * 32 + lane;
+                if (prow < p.M && bf16_fast)
+                    for (int b = c_lo * 2; b < c_hi * 2 && n1 + b / 2 < p.N; b += 128) prefetch_l2((const uint8_t*)(p.R + (size_t)prow * p.ldr + n1) + b);
+            }
             uint4 rpre[8];
             bool rpre_valid = false;
-            if (bf16_fast && p.R && 64 <= p.BN && n0 + 64 <= p.N) {
+            if (bf16_fast && p.R && c_lo + 64 <= c_hi && n0 + c_lo + 64 <= p.N) {
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const int grow = row_base + rgrp + 4 * i;
-                    rpre[i] = grow < p.M ? *(const uint4*)(p.R + (size_t)grow * p.ldr + n0 + sub * 8) : make_uint4(0u, 0u, 0u, 0u);
+                    rpre[i] = grow < p.M ? *(const uint4*)(p.R + (size_t)grow * p.ldr + n0 + c_lo + sub * 8) : make_uint4(0u, 0u, 0u, 0u);
                 }
                 rpre_valid = true;
             }
@@ -270,12 +446,12 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             // Accumulator rows live one per thread (TMEM lane = output row), but a warp-wide store of one 16-byte piece per
             // row would touch 32 different 128-byte lines. So full chunks go through the warp's staging rows and leave (and
             // the residual arrives) as whole 128-byte row segments, 4 rows per instruction.
-            uint8_t* stg = smem + NST * (A_STAGE_BYTES + BST) + q * STG_WARP_BYTES;
+            uint8_t* stg = smem + NST * (A_STAGE_BYTES + BST) + ew * STG_WARP_BYTES;
             uint8_t* my_row = stg + lane * STG_PITCH;
-            for (int c0 = 0; c0 < p.BN;) {
+            for (int c0 = c_lo; c0 < c_hi;) {
                 const int col0 = n0 + c0;
                 if (col0 >= p.N) break;
-                if (bf16_fast && c0 + 64 <= p.BN && col0 + 64 <= p.N) {
+                if (bf16_fast && c0 + 64 <= c_hi && col0 + 64 <= p.N) {
                     uint32_t ra[32], rb2[32];
                     tmem_ld_32x32(taddr0 + c0, ra);
                     tmem_ld_32x32(taddr0 + c0 + 32, rb2);
@@ -291,7 +467,7 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                         for (int i = 0; i < 8; ++i) *(uint4*)(stg + (rgrp + 4 * i) * STG_PITCH + sub * 16) = rpre[i];
                         __syncwarp();
                         // the next 64-column chunk's residual, if there is one
-                        rpre_valid = c0 + 128 <= p.BN && col0 + 128 <= p.N;
+                        rpre_valid = c0 + 128 <= c_hi && col0 + 128 <= p.N;
                         if (rpre_valid) {
 #pragma unroll
                             for (int i = 0; i < 8; ++i) {
@@ -301,26 +477,42 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                         }
                     }
                     tmem_ld_wait();
+                    float rowdot = 0.f;
 #pragma unroll
                     for (int v = 0; v < 8; ++v) {
                         float f[8];
 #pragma unroll
                         for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v < 4 ? ra[(v & 3) * 8 + i] : rb2[(v & 3) * 8 + i]);
-                        if (p.R) {
+                        uint4 o;
+                        __nv_bfloat162* ob = (__nv_bfloat162*)&o;
+                        if constexpr (EPI == GEMM_EPI_ROWDOT) {
+                            // the products use the values as stored (rounded to bf16): the consumer of C reads those
                             const uint4 rv = *(const uint4*)(my_row + v * 16);
                             const __nv_bfloat162* rb = (const __nv_bfloat162*)&rv;
 #pragma unroll
                             for (int i = 0; i < 4; ++i) {
-                                const float2 t = __bfloat1622float2(rb[i]);
-                                f[2 * i] += t.x;
-                                f[2 * i + 1] += t.y;
+                                ob[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+                                const float2 t = __bfloat1622float2(rb[i]), c2 = __bfloat1622float2(ob[i]);
+                                rowdot = fmaf(c2.x, t.x, fmaf(c2.y, t.y, rowdot));
                             }
-                        }
-                        uint4 o;
-                        __nv_bfloat162* ob = (__nv_bfloat162*)&o;
+                        } else {
+                            if (p.R) {
+                                const uint4 rv = *(const uint4*)(my_row + v * 16);
+                                const __nv_bfloat162* rb = (const __nv_bfloat162*)&rv;
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) ob[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+                                for (int i = 0; i < 4; ++i) {
+                                    const float2 t = __bfloat1622float2(rb[i]);
+                                    f[2 * i] += t.x;
+                                    f[2 * i + 1] += t.y;
+                                }
+                            }
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) ob[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+                        }
                         *(uint4*)(my_row + v * 16) = o;  // a thread reads and rewrites only its own staging row
+                    }
+                    if constexpr (EPI == GEMM_EPI_ROWDOT) {
+                        if (row < p.M) p.aux[((size_t)(row / p.aux_S) * p.aux_NH + (col0 >> 6)) * p.aux_S + (row % p.aux_S)] = rowdot;
                     }
                     __syncwarp();
 #pragma unroll
@@ -532,17 +724,42 @@ int gemm_bf16_umma(const GemmProblem& g, int* err_flag, cudaStream_t stream) {
     static std::atomic<unsigned long long> attr_done{0};
     static const bool pair_off = getenv("BM_GEMM_1CTA") != nullptr;
     if (first_use_on_current_device(attr_done)) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_umma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DYN_BYTES);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_bf16_umma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DYN_BYTES);
+        cudaError_t e = cudaSuccess;
+#define BMB_GEMM_ATTR(CT, EP) \
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_bf16_umma_kernel<CT, EP>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DYN_BYTES)
+        BMB_GEMM_ATTR(1, GEMM_EPI_NONE); BMB_GEMM_ATTR(2, GEMM_EPI_NONE);
+        BMB_GEMM_ATTR(1, GEMM_EPI_SWIGLU_FWD); BMB_GEMM_ATTR(2, GEMM_EPI_SWIGLU_FWD);
+        BMB_GEMM_ATTR(1, GEMM_EPI_SWIGLU_BWD); BMB_GEMM_ATTR(2, GEMM_EPI_SWIGLU_BWD);
+        BMB_GEMM_ATTR(1, GEMM_EPI_ROWDOT); BMB_GEMM_ATTR(2, GEMM_EPI_ROWDOT);
+#undef BMB_GEMM_ATTR
         if (e != cudaSuccess) return -5;
     }
     const int g_num_sms = sm_count_current_device();
+    // Fused epilogues: bf16 output through the staged 128-byte row path only, so every pitch and pointer must be 16-byte aligned
+    // and the column counts whole 64- (or 128-) column groups; anything else is the caller's cue to use the unfused kernels.
+    if (g.epi != GEMM_EPI_NONE) {
+        if (g.out_mode != GEMM_OUT_BF16 || g.splits > 1 || (((uintptr_t)g.C) & 15) || (g.ldc % 8)) return -8;
+        if (g.epi == GEMM_EPI_SWIGLU_FWD) {
+            if (g.b_mn_major || (g.N % 256) || !g.C2 || (((uintptr_t)g.C2) & 15) || (g.ldc2 % 8) || (g.tile_n && g.tile_n != 256)) return -8;
+        } else if (g.epi == GEMM_EPI_SWIGLU_BWD) {
+            if ((g.N % 128) || !g.R || (((uintptr_t)g.R) & 15) || (g.ldr % 8) || (g.tile_n && (g.tile_n % 128))) return -8;
+        } else if (g.epi == GEMM_EPI_ROWDOT) {
+            if ((g.N % 64) || !g.R || (((uintptr_t)g.R) & 15) || (g.ldr % 8) || !g.aux || g.aux_S <= 0 || g.aux_NH * 64 != g.N ||
+                (g.M % g.aux_S) || (g.tile_n && (g.tile_n % 64)))
+                return -8;
+        } else {
+            return -8;
+        }
+    }
 
     // CTA pairs (256-row tiles) whenever there are at least 256 rows and the caller did not fix a narrow tile
     const int ctas = (!pair_off && g.M >= 2 * BM && g.tile_n == 0) ? 2 : 1;
     KArgs p;
     p.M = g.M; p.N = g.N; p.K = g.K;
     p.BN = g.tile_n > 0 ? g.tile_n : choose_tile_n(g.N, g.b_mn_major, ctas);
+    if (g.epi == GEMM_EPI_SWIGLU_FWD) p.BN = 256;                                   // 128 gate + 128 up columns of the same hidden units
+    else if (g.epi == GEMM_EPI_SWIGLU_BWD && (p.BN % 128)) p.BN = 256;
+    else if (g.epi == GEMM_EPI_ROWDOT && (p.BN % 64)) p.BN = 256;                   // whole heads per tile
     if (p.BN < 32 || p.BN > MAX_BN || (p.BN % 32) || (g.b_mn_major && (p.BN % (64 * ctas)))) return -6;
     p.tile_rows = BM * ctas;
     p.a_mn = g.a_mn_major ? 1 : 0;
@@ -570,13 +787,16 @@ int gemm_bf16_umma(const GemmProblem& g, int* err_flag, cudaStream_t stream) {
     p.C = g.C; p.ldc = g.ldc; p.out_mode = g.out_mode;
     p.R = g.R; p.ldr = g.ldr;
     p.err = err_flag;
+    p.C2 = g.C2; p.ldc2 = g.ldc2;
+    p.aux = g.aux; p.aux_S = g.aux_S; p.aux_NH = g.aux_NH;
 
     CUtensorMap tmA, tmB;
     int rc;
     if (!p.a_mn) rc = make_map(&tmA, g.A, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda, BK, BM);
     else         rc = make_map(&tmA, g.A, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)g.lda, 64, BK);
     if (rc) return rc;
-    if (!p.b_mn) rc = make_map(&tmB, g.B, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb, BK, (uint32_t)(p.BN / ctas));
+    if (!p.b_mn) rc = make_map(&tmB, g.B, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb, BK,
+                               (uint32_t)(g.epi == GEMM_EPI_SWIGLU_FWD ? p.BN / 2 : p.BN / ctas));
     else         rc = make_map(&tmB, g.B, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb, 64, BK);
     if (rc) return rc;
 
@@ -603,12 +823,26 @@ int gemm_bf16_umma(const GemmProblem& g, int* err_flag, cudaStream_t stream) {
         cfg.gridDim = dim3((unsigned)(2 * (units < pairs ? units : pairs)));
         cfg.attrs = at;
         cfg.numAttrs = na;
-        return cudaLaunchKernelEx(&cfg, gemm_bf16_umma_kernel<2>, tmA, tmB, p) == cudaSuccess ? 0 : -7;
+        cudaError_t le;
+        switch (g.epi) {
+            case GEMM_EPI_SWIGLU_FWD: le = cudaLaunchKernelEx(&cfg, gemm_bf16_umma_kernel<2, GEMM_EPI_SWIGLU_FWD>, tmA, tmB, p); break;
+            case GEMM_EPI_SWIGLU_BWD: le = cudaLaunchKernelEx(&cfg, gemm_bf16_umma_kernel<2, GEMM_EPI_SWIGLU_BWD>, tmA, tmB, p); break;
+            case GEMM_EPI_ROWDOT: le = cudaLaunchKernelEx(&cfg, gemm_bf16_umma_kernel<2, GEMM_EPI_ROWDOT>, tmA, tmB, p); break;
+            default: le = cudaLaunchKernelEx(&cfg, gemm_bf16_umma_kernel<2, GEMM_EPI_NONE>, tmA, tmB, p); break;
+        }
+        return le == cudaSuccess ? 0 : -7;
     }
     cfg.gridDim = dim3((unsigned)(units < g_num_sms ? units : g_num_sms));
     cfg.attrs = at;
     cfg.numAttrs = na;
-    return cudaLaunchKernelEx(&cfg, gemm_bf16_umma_kernel<1>, tmA, tmB, p) == cudaSuccess ? 0 : -7;
+    cudaError_t le;
+    switch (g.epi) {
+        case GEMM_EPI_SWIGLU_FWD: le = cudaLaunchKernelEx(&cfg, gemm_bf16_umma_kernel<1, GEMM_EPI_SWIGLU_FWD>, tmA, tmB, p); break;
+        case GEMM_EPI_SWIGLU_BWD: le = cudaLaunchKernelEx(&cfg, gemm_bf16_umma_kernel<1, GEMM_EPI_SWIGLU_BWD>, tmA, tmB, p); break;
+        case GEMM_EPI_ROWDOT: le = cudaLaunchKernelEx(&cfg, gemm_bf16_umma_kernel<1, GEMM_EPI_ROWDOT>, tmA, tmB, p); break;
+        default: le = cudaLaunchKernelEx(&cfg, gemm_bf16_umma_kernel<1, GEMM_EPI_NONE>, tmA, tmB, p); break;
+    }
+    return le == cudaSuccess ? 0 : -7;
 }
 
 }  // namespace bmb

@@ -24,6 +24,23 @@ enum GemmOut : int {
     GEMM_OUT_F32_ATOMIC = 2,  // C (fp32) += acc via red.global.add (split-K safe; C must hold the running sum)
 };
 
+// What the epilogue does with the accumulator tile besides storing it (GEMM_OUT_BF16 only). Each replaces a memory-bound kernel
+// of the training step and the round trip of its operand through HBM.
+enum GemmEpilogue : int {
+    GEMM_EPI_NONE = 0,
+    // Gated MLP, forward. B is the row-concatenated [gate; up] weight [2H, K]; N = 2H. A tile covers 128 hidden units: its first
+    // half is the gate projection and its second half the up projection of the SAME units (the two halves of B are fetched from
+    // rows h0 and H + h0). Stores gate and up (bf16) into C[:, h] and C[:, H + h] and act = silu(gate) * up into C2[:, h]
+    // (swiglu_forward, src/kernels/forward.metal:1179). H % 128 == 0.
+    GEMM_EPI_SWIGLU_FWD = 1,
+    // Gated MLP, backward: the accumulator is dact[M, N = H]; R holds the saved gate at R[:, h] and up at R[:, H + h]; stores
+    // dgate into C[:, h] and dup into C[:, H + h] (swiglu_backward, src/kernels/backward.metal:505). dact is never stored.
+    GEMM_EPI_SWIGLU_BWD = 2,
+    // Attention output gradient: stores C = acc (bf16) and aux[(b * NH + h) * S + s] = sum over the 64 columns of head h of
+    // C[row, :] * R[row, :], row = b * S + s: the row sums flash attention backward subtracts from dP. N % 64 == 0.
+    GEMM_EPI_ROWDOT = 3,
+};
+
 struct GemmProblem {
     int M, N, K;
     const __nv_bfloat16* A;
@@ -40,6 +57,11 @@ struct GemmProblem {
     int splits;  // >1 only with GEMM_OUT_F32_ATOMIC; 0 = choose (fills the machine with whole waves of work units)
     int tile_n;  // 0 = choose
     int pdl;     // 1 = launch with programmatic stream serialisation (the predecessor must be a kernel of the same stream)
+    int epi = GEMM_EPI_NONE;
+    void* C2 = nullptr;  // GEMM_EPI_SWIGLU_FWD: act [M, H] bf16
+    int ldc2 = 0;
+    float* aux = nullptr;  // GEMM_EPI_ROWDOT: [M / aux_S, aux_NH, aux_S] fp32
+    int aux_S = 0, aux_NH = 0;
 };
 
 // Launches on `stream`. Returns 0, or a negative code for an invalid problem / failed launch.

@@ -52,7 +52,7 @@ int argmax_first(int* out_index, const float* logits, int V, cudaStream_t st);
 int gemm_f32_simt(float* C, int ldc, int accumulate, const float* A, long sam, long sak, const float* B, long sbn, long sbk,
                   const float* R, int ldr, int M, int N, int K, cudaStream_t st);
 
-// ---- attention (attention_simt.cu: exact-softmax fp32 math; attention_mma.cu: bf16 tensor-core flash) ----
+// ---- attention (attention_simt.cu: exact-softmax fp32 math, masks, any head_dim; the bf16 tensor-core kernels are in attention_umma.cuh) ----
 // Layout as the reference: Q[row, h, :] at q + row*ldq + h*HD (row = b*S + s), K/V with NKV heads, causal, GQA.
 template <typename T> int attention_forward_simt(T* out, int ldo, float* lse, const T* q, int ldq, const T* k, const T* v, int ldkv,
                                                  const uint8_t* mask, int B, int S, int NH, int NKV, int HD, float scale,

@@ -84,6 +84,8 @@ struct bm_trainer_s {
     float *rstdf, *row_loss, *d_loss;
     /* backward temporaries */
     void *dres, *dn, *dact, *dgu, *dattn, *dqkv;
+    float* d_delta;           /* [B, NH, S] rowsum(dattn * attn), written by the O-projection input-gradient GEMM */
+    int fuse;                 /* fused GEMM epilogues / attention helpers (default on; option "fused_epilogues", env BM_NO_FUSE) */
     int *d_tokens, *d_targets;
     uint8_t* d_attn_mask;
     float* d_row_weight; /* per-row loss weights of a masked step */

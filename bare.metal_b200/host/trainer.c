@@ -70,6 +70,8 @@ static void free_activations(bm_trainer_t* t) {
     }
     bmc_free(be, t->x_last); bmc_free(be, t->nf); bmc_free(be, t->logits); bmc_free(be, t->rstdf); bmc_free(be, t->row_loss);
     bmc_free(be, t->dres); bmc_free(be, t->dn); bmc_free(be, t->dact); bmc_free(be, t->dgu); bmc_free(be, t->dattn); bmc_free(be, t->dqkv);
+    bmc_free(be, t->d_delta);
+    t->d_delta = NULL;
     bmc_free(be, t->d_tokens); bmc_free(be, t->d_targets); bmc_free(be, t->d_attn_mask); bmc_free(be, t->d_row_weight);
     t->x_last = t->nf = t->logits = NULL;
     t->rstdf = t->row_loss = NULL;
@@ -107,6 +109,7 @@ static int ensure_batch(bm_trainer_t* t, int B) {
     ALLOC(t->rstdf, M * sizeof(float)); ALLOC(t->row_loss, M * sizeof(float));
     ALLOC(t->dres, M * D * e); ALLOC(t->dn, M * D * e); ALLOC(t->dact, M * H * e); ALLOC(t->dgu, M * 2 * H * e);
     ALLOC(t->dattn, M * QD * e); ALLOC(t->dqkv, M * QKVD * e);
+    ALLOC(t->d_delta, (size_t)B * a->n_heads * t->S * sizeof(float));
     ALLOC(t->d_tokens, M * sizeof(int)); ALLOC(t->d_targets, M * sizeof(int));
     ALLOC(t->d_attn_mask, M); ALLOC(t->d_row_weight, M * sizeof(float));
 #undef ALLOC
@@ -201,6 +204,7 @@ bm_trainer_t* bm_create_trainer(bm_context_t* ctx, bm_model_t* model, const bm_t
         return NULL;
     }
     t->side_stream = getenv("BM_NO_SIDE_STREAM") ? 0 : 1;
+    t->fuse = getenv("BM_NO_FUSE") ? 0 : 1;
     t->graph_mode = getenv("BM_NO_TRAIN_GRAPH") ? 0 : 1;
     t->graph_B = 0;
     t->graph_eager_steps = 0;
@@ -261,8 +265,14 @@ static int forward_and_loss(bm_trainer_t* t, int B, const uint8_t* d_attn_mask, 
                                   d_attn_mask, B, S, NH, NKV, HD, scale));
         TRY(bmc_matmul_forward(be, dt, c->x1, D, c->attn, QD, wptr(t, pb + P_O), c->x, D, M, QD, D));
         TRY(bmc_rmsnorm_forward(be, dt, c->n2, c->rstd2, c->x1, wf32(t, pb + P_LN2), M, D, RMS_EPS));
-        TRY(bmc_matmul_forward(be, dt, c->gu, 2 * H, c->n2, D, wptr(t, pb + P_GATE), NULL, 0, M, D, 2 * H));
-        TRY(bmc_swiglu_forward(be, dt, c->act, H, c->gu, at(c->gu, H, t), 2 * H, M, H));
+        /* gate and up in one GEMM whose epilogue also writes act = silu(gate) * up; shapes without that form take two launches */
+        int frc = t->fuse ? bmc_matmul_swiglu_forward(be, dt, c->gu, 2 * H, c->act, H, c->n2, D, wptr(t, pb + P_GATE), M, D, H) : BMC_ERR_UNFUSED;
+        if (frc == BMC_ERR_UNFUSED) {
+            TRY(bmc_matmul_forward(be, dt, c->gu, 2 * H, c->n2, D, wptr(t, pb + P_GATE), NULL, 0, M, D, 2 * H));
+            TRY(bmc_swiglu_forward(be, dt, c->act, H, c->gu, at(c->gu, H, t), 2 * H, M, H));
+        } else {
+            TRY(frc);
+        }
         TRY(bmc_matmul_forward(be, dt, x_next, D, c->act, H, wptr(t, pb + P_DOWN), c->x1, D, M, H, D));
     }
     TRY(bmc_rmsnorm_forward(be, dt, t->nf, t->rstdf, t->x_last, wf32(t, p_lnf), M, D, RMS_EPS));
@@ -291,7 +301,7 @@ static int backward(bm_trainer_t* t, int B, const uint8_t* d_attn_mask) {
      * its operand, so it runs while the main stream executes the memory-bound kernel that follows (SwiGLU / RMSNorm backward,
      * attention helpers). A ticket is waited for before a buffer the side GEMM reads is overwritten. */
     const int side = t->side_stream;
-    int tk_head = -1, tk_down = -1, tk_gu = -1, tk_o = -1, tk_q = -1;
+    int tk_head = -1, tk_down = -1, tk_gu = -1, tk_o = -1, tk_q = -1, frc;
 #define SIDE_WGRAD(ticket, call) do { if (side) { TRY(bmc_side_begin(be)); } TRY(call); if (side) { (ticket) = bmc_side_end(be); if ((ticket) < 0) return -1; } } while (0)
 #define SIDE_WAIT(ticket) do { if (side && (ticket) >= 0) { TRY(bmc_side_wait(be, (ticket))); (ticket) = -1; } } while (0)
 
@@ -306,22 +316,34 @@ static int backward(bm_trainer_t* t, int B, const uint8_t* d_attn_mask) {
         bm_layer_act_t* c = &t->act[l];
         const int pb = 9 * l;
         /* MLP: dres is dL/d(x_{l+1}); the residual add routes it unchanged to both of its inputs */
-        TRY(bmc_matmul_backward_inp(be, dt, t->dact, H, 0, t->dres, D, wptr(t, pb + P_DOWN), M, H, D));
-        SIDE_WGRAD(tk_down, bmc_matmul_backward_w(be, dt, gptr(t, pb + P_DOWN), t->dres, D, c->act, H, M, H, D));
         SIDE_WAIT(tk_gu); /* the previous layer's gate/up weight gradient still reads dgu */
-        TRY(bmc_swiglu_backward(be, dt, t->dgu, at(t->dgu, H, t), 2 * H, c->gu, at(c->gu, H, t), 2 * H, t->dact, H, M, H));
+        /* down-projection input gradient whose epilogue applies SwiGLU backward (dact is never stored) */
+        frc = t->fuse ? bmc_matmul_backward_inp_swiglu(be, dt, t->dgu, 2 * H, t->dres, D, wptr(t, pb + P_DOWN), c->gu, 2 * H, M, H, D) : BMC_ERR_UNFUSED;
+        if (frc == BMC_ERR_UNFUSED) {
+            TRY(bmc_matmul_backward_inp(be, dt, t->dact, H, 0, t->dres, D, wptr(t, pb + P_DOWN), M, H, D));
+            TRY(bmc_swiglu_backward(be, dt, t->dgu, at(t->dgu, H, t), 2 * H, c->gu, at(c->gu, H, t), 2 * H, t->dact, H, M, H));
+        } else {
+            TRY(frc);
+        }
+        SIDE_WGRAD(tk_down, bmc_matmul_backward_w(be, dt, gptr(t, pb + P_DOWN), t->dres, D, c->act, H, M, H, D));
         TRY(bmc_matmul_backward_inp(be, dt, t->dn, D, 0, t->dgu, 2 * H, wptr(t, pb + P_GATE), M, D, 2 * H));
         SIDE_WGRAD(tk_gu, bmc_matmul_backward_w(be, dt, gptr(t, pb + P_GATE), t->dgu, 2 * H, c->n2, D, M, D, 2 * H));
         SIDE_WAIT(tk_down); /* reads dres, which the norm backward accumulates into */
         TRY(bmc_rmsnorm_backward(be, dt, t->dres, gptr(t, pb + P_LN2), nw_acc, t->dn, c->x1, wf32(t, pb + P_LN2), c->rstd2, M, D, nw_r0, nw_r1));
         /* attention block: dres is now dL/d(x1) */
-        TRY(bmc_matmul_backward_inp(be, dt, t->dattn, QD, 0, t->dres, D, wptr(t, pb + P_O), M, QD, D));
+        /* O-projection input gradient; its epilogue also leaves rowsum(dattn * attn) per (row, head) for attention backward */
+        const float* delta = NULL;
+        frc = (t->fuse && !d_attn_mask && HD == 64)
+                  ? bmc_matmul_backward_inp_rowdot(be, dt, t->dattn, QD, t->d_delta, t->dres, D, wptr(t, pb + P_O), c->attn, QD, M, QD, D, S, NH)
+                  : BMC_ERR_UNFUSED;
+        if (frc == BMC_ERR_UNFUSED) TRY(bmc_matmul_backward_inp(be, dt, t->dattn, QD, 0, t->dres, D, wptr(t, pb + P_O), M, QD, D));
+        else { TRY(frc); delta = t->d_delta; }
         SIDE_WGRAD(tk_o, bmc_matmul_backward_w(be, dt, gptr(t, pb + P_O), t->dres, D, c->attn, QD, M, QD, D));
         SIDE_WAIT(tk_q); /* the previous layer's QKV weight gradient still reads dqkv */
-        TRY(bmc_attention_backward(be, dt, t->dqkv, QKVD, at(t->dqkv, QD, t), at(t->dqkv, QD + KV, t), QKVD, t->dattn, QD, c->attn,
-                                   c->lse, c->qkv, QKVD, at(c->qkv, QD, t), at(c->qkv, QD + KV, t), QKVD, d_attn_mask, B, S, NH, NKV,
-                                   HD, scale));
-        TRY(bmc_rope(be, dt, t->dqkv, QKVD, at(t->dqkv, QD, t), QKVD, t->d_rope_cs, M, S, NH, NKV, HD, -1));
+        /* dQ and dK leave already rotated backwards (RoPE backward folded into the kernel's output pass) */
+        TRY(bmc_attention_backward_fused(be, dt, t->dqkv, QKVD, at(t->dqkv, QD, t), at(t->dqkv, QD + KV, t), QKVD, t->dattn, QD, c->attn,
+                                         c->lse, c->qkv, QKVD, at(c->qkv, QD, t), at(c->qkv, QD + KV, t), QKVD, d_attn_mask, delta,
+                                         t->d_rope_cs, B, S, NH, NKV, HD, scale));
         TRY(bmc_matmul_backward_inp(be, dt, t->dn, D, 0, t->dqkv, QKVD, wptr(t, pb + P_Q), M, D, QKVD));
         SIDE_WGRAD(tk_q, bmc_matmul_backward_w(be, dt, gptr(t, pb + P_Q), t->dqkv, QKVD, c->n1, D, M, D, QKVD));
         SIDE_WAIT(tk_o);
@@ -648,6 +670,7 @@ int bmx_trainer_set_option(bm_trainer_t* t, const char* key, int value) {
     t->graph_eager_steps = 0;
     if (strcmp(key, "side_stream") == 0) { t->side_stream = value ? 1 : 0; return 0; }
     if (strcmp(key, "train_graph") == 0) { t->graph_mode = value ? 1 : 0; return 0; }
+    if (strcmp(key, "fused_epilogues") == 0) { t->fuse = value ? 1 : 0; return 0; }
     if (all || strcmp(key, "ref_norm_grad") == 0) { t->ref_norm_grad = value ? 1 : 0; known = 1; }
     if (all || strcmp(key, "ref_input_grad_carry") == 0) {
         known = 1;

@@ -304,7 +304,20 @@ def run_gemm(args):
             "input_grad": lambda: be.call("matmul_backward_inp", BMC_BF16, Ptr(ginp), Cc, 0, Ptr(gout), OC, Ptr(w), BT, Cc, OC),
             "weight_grad": lambda: be.call("matmul_backward_w", BMC_BF16, Ptr(gw), Ptr(gout), OC, Ptr(inp), Cc, BT, Cc, OC),
         }
+        # the same GEMMs with the memory-bound kernel next to them folded into the epilogue (the forms the training step uses)
+        if name == "gate_up":
+            act = be.zeros(BT * H, BMC_BF16)
+            kinds["forward_swiglu"] = lambda: be.call("matmul_swiglu_forward", BMC_BF16, Ptr(out), OC, Ptr(act), H, Ptr(inp), Cc, Ptr(w), BT, Cc, H)
+        if name == "down":
+            gu, dgu = rand_bf16(BT * 2 * H), be.zeros(BT * 2 * H, BMC_BF16)
+            kinds["input_grad_swiglu"] = lambda: be.call("matmul_backward_inp_swiglu", BMC_BF16, Ptr(dgu), 2 * H, Ptr(gout), OC, Ptr(w), Ptr(gu), 2 * H, BT, H, OC)
+        if name == "o":
+            rd = be.zeros(BT * a.n_heads)
+            kinds["input_grad_rowdot"] = lambda: be.call("matmul_backward_inp_rowdot", BMC_BF16, Ptr(ginp), Cc, Ptr(rd), Ptr(gout), OC, Ptr(w), Ptr(inp), Cc,
+                                                         BT, Cc, OC, args.seq_len, a.n_heads)
         for kind, fn in kinds.items():
+            if args.kind and args.kind != kind:
+                continue
             for _ in range(max(args.warmup, 1)):
                 assert fn() == 0
             assert lib.bmc_sync(be.ctx) == 0
@@ -405,6 +418,7 @@ def main():
     ap.add_argument("--decode-tokens", type=int, default=256, help="--workload decode: generated tokens")
     ap.add_argument("--decode-batches", default="1,64", help="--workload decode: comma-separated sequence counts")
     ap.add_argument("--shape", default="", help="--workload gemm: qkv, o, gate_up, down or head (default all)")
+    ap.add_argument("--kind", default="", help="--workload gemm: forward, input_grad, weight_grad or one of the fused forms (default all)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)

@@ -111,6 +111,24 @@ int bmc_matmul_backward_inp(bmc_ctx_t* ctx, int dtype, void* d_ginp, int ldgi, i
 int bmc_matmul_backward_w(bmc_ctx_t* ctx, int dtype, float* d_gw_f32, const void* d_gout, int ldgo, const void* d_inp, int ldi,
                           int BT, int C, int OC);
 
+/* ---- linear layers that absorb the memory-bound kernel next to them (bf16 / tensor-core path). Each returns BMC_ERR_UNFUSED
+ *      without enqueuing anything when the dtype or the shape has no fused form; the caller then uses the separate entry points.
+ *   swiglu_forward      : [gate | up][BT, 2H] = inp[BT,C] * [W_gate; W_up]^T  and  act[BT,H] = silu(gate) * up in the same launch
+ *                         (matmul_forward_* followed by swiglu_forward, forward.metal:1179). d_w_gate_up: [2H, C], gate rows first.
+ *                         H % 128 == 0.
+ *   backward_inp_swiglu : [dgate | dup][BT, 2H] from gout[BT,OC] * W_down[OC,H] and the saved [gate | up]; the intermediate
+ *                         dact[BT,H] is never stored (matmul_backward_inp_* followed by swiglu_backward, backward.metal:505).
+ *   backward_inp_rowdot : ginp[BT,C] = gout[BT,OC] * W[OC,C]  and  rowdot[b][h][s] = sum over the 64 columns of head h of
+ *                         ginp[row,:] * other[row,:], row = b*S + s — the per-row sums attention backward subtracts from dP
+ *                         when ginp is the gradient of the attention output and `other` that output. C == NH * 64. ---- */
+#define BMC_ERR_UNFUSED (-70)
+int bmc_matmul_swiglu_forward(bmc_ctx_t* ctx, int dtype, void* d_gate_up, int ldgu, void* d_act, int ldact, const void* d_inp, int ldi,
+                              const void* d_w_gate_up, int BT, int C, int H);
+int bmc_matmul_backward_inp_swiglu(bmc_ctx_t* ctx, int dtype, void* d_dgate_dup, int lddgu, const void* d_gout, int ldgo,
+                                   const void* d_w_down, const void* d_gate_up, int ldgu, int BT, int H, int OC);
+int bmc_matmul_backward_inp_rowdot(bmc_ctx_t* ctx, int dtype, void* d_ginp, int ldgi, float* d_rowdot, const void* d_gout, int ldgo,
+                                   const void* d_weight, const void* d_other, int ldother, int BT, int C, int OC, int S, int NH);
+
 /* ---- RoPE (rope_forward_seq forward.metal:2225; rope_backward_seq backward.metal:980), in place.
  * d_cs_table: float[S][HD/2][2] = (cos, sin)(pos * inv_freq), built by the host with the reference's formula
  * (rope_inv_freq forward.metal:1260-1279). rows = B*S, position = row % S. dir: +1 forward, -1 backward. ---- */
@@ -127,6 +145,14 @@ int bmc_attention_forward(bmc_ctx_t* ctx, int dtype, void* d_out, int ldo, float
 int bmc_attention_backward(bmc_ctx_t* ctx, int dtype, void* d_gq, int ldgq, void* d_gk, void* d_gv, int ldgkv, const void* d_gout,
                            int ldo, const void* d_out, const float* d_lse, const void* d_q, int ldq, const void* d_k, const void* d_v,
                            int ldkv, const uint8_t* d_mask, int B, int S, int NH, int NKV, int HD, float scale);
+/* Same, with the two passes that surround it in the training step folded in (both optional, NULL = off):
+ *   d_delta   float[B][NH][S] = rowsum(gout * out) computed elsewhere (bmc_matmul_backward_inp_rowdot), so it is not recomputed;
+ *   d_rope_cs the rotation table of bmc_rope: d_gq and d_gk leave with RoPE backward (rope_backward_seq, backward.metal:980)
+ *             already applied, which saves a read-modify-write pass over both. */
+int bmc_attention_backward_fused(bmc_ctx_t* ctx, int dtype, void* d_gq, int ldgq, void* d_gk, void* d_gv, int ldgkv, const void* d_gout,
+                                 int ldo, const void* d_out, const float* d_lse, const void* d_q, int ldq, const void* d_k, const void* d_v,
+                                 int ldkv, const uint8_t* d_mask, const float* d_delta, const float* d_rope_cs, int B, int S, int NH, int NKV,
+                                 int HD, float scale);
 
 /* ---- SwiGLU (swiglu_forward forward.metal:1179; swiglu_backward backward.metal:505) ---- */
 int bmc_swiglu_forward(bmc_ctx_t* ctx, int dtype, void* d_out, int ldo, const void* d_gate, const void* d_up, int ldgu, int rows, int H);

@@ -36,6 +36,12 @@ def run_gpu(be, dtype, qkv, go, B, S):
     return be.get(out, (B, S, QD), dtype), be.get(dg, (B, S, LD), dtype)
 
 
+def rope_table(S):
+    inv = (np.float32(1.0) / np.power(np.float32(1e5), (2 * np.arange(HD // 2, dtype=np.float32)) / np.float32(HD))).astype(np.float32)
+    ang = (np.arange(S, dtype=np.float32)[:, None] * inv[None, :]).astype(np.float32)
+    return np.stack([np.cos(ang), np.sin(ang)], axis=-1).astype(np.float32)
+
+
 def close(got, ref, what):
     assert oc.rel_err(got, ref) < 2e-2, (what, oc.rel_err(got, ref))
     assert oc.cosine(got.ravel(), ref.ravel()) > 0.999, what
@@ -91,3 +97,33 @@ def test_exact_kernel_matches_oracle_at_2048(be):
     assert oc.rel_err(dg[0, :, :QD].reshape(S, NH, HD), gq) < 2e-5
     assert oc.rel_err(dg[0, :, QD:QD + KV].reshape(S, NKV, HD), gk) < 2e-5
     assert oc.rel_err(dg[0, :, QD + KV:].reshape(S, NKV, HD), gv) < 2e-5
+
+
+@pytest.mark.parametrize("S,B", [(384, 2), (200, 2), (2048, 1)])
+def test_backward_with_row_sums_supplied_and_rope_backward_folded_in(be, S, B):
+    """bmc_attention_backward_fused with delta from outside and the rotation table = bmc_attention_backward followed by the
+    backward rotation of dQ and dK; V's gradient is the same in both."""
+    rng = np.random.default_rng(S + 1)
+    dt, es = BMC_BF16, 2
+    qkv = bf16_round(rng.standard_normal((B * S, LD)).astype(np.float32))
+    go = bf16_round(rng.standard_normal((B * S, QD)).astype(np.float32))
+    d, dgo = be.put(qkv, dt), be.put(go, dt)
+    out, lse = be.zeros(B * S * QD, dt), be.zeros(B * NH * S)
+    args_f = (Ptr(out), QD, Ptr(lse), Ptr(d), LD, Ptr(d, QD * es), Ptr(d, (QD + KV) * es), LD, None, B, S, NH, NKV, HD, float(SCALE))
+    be.ok("attention_forward", dt, *args_f)
+    o = be.get(out, (B, S, NH, HD), dt)
+    delta = (o.astype(np.float64) * go.reshape(B, S, NH, HD)).sum(-1).transpose(0, 2, 1).astype(np.float32)
+    cs = be.put(rope_table(S))
+    ref, got = be.zeros(B * S * LD, dt), be.zeros(B * S * LD, dt)
+    tail = (Ptr(dgo), QD, Ptr(out), Ptr(lse), Ptr(d), LD, Ptr(d, QD * es), Ptr(d, (QD + KV) * es), LD, None)
+    be.ok("attention_backward", dt, Ptr(ref), LD, Ptr(ref, QD * es), Ptr(ref, (QD + KV) * es), LD, *tail, B, S, NH, NKV, HD, float(SCALE))
+    unrotated = be.get(ref, (B, S, LD), dt)
+    be.ok("attention_backward_fused", dt, Ptr(got), LD, Ptr(got, QD * es), Ptr(got, (QD + KV) * es), LD, *tail, Ptr(be.put(delta)), Ptr(cs),
+          B, S, NH, NKV, HD, float(SCALE))
+    g = be.get(got, (B, S, LD), dt)
+    for b in range(B):
+        rq, rk = portk.rope_seq(unrotated[b, :, :QD].reshape(S, NH, HD), unrotated[b, :, QD:QD + KV].reshape(S, NKV, HD), 1e5, -1)
+        # the unrotated reference was rounded to bf16 before the rotation, the fused path rotates fp32 values: two roundings apart
+        assert oc.rel_err(g[b, :, :QD].reshape(S, NH, HD), rq) < 1e-2
+        assert oc.rel_err(g[b, :, QD:QD + KV].reshape(S, NKV, HD), rk) < 1e-2
+    assert oc.rel_err(g[..., QD + KV:], unrotated[..., QD + KV:]) < 1e-3

@@ -10,7 +10,7 @@ import pytest
 
 import bmapi
 import oracle_check as oc
-from test_oracle_pins import DECODE_GOLDENS, decode_case
+from test_oracle_pins import DECODE_GOLDENS, DECODE_GOLDENS_SAMPLED, decode_case
 
 pytestmark = pytest.mark.gpu
 F32, BF16 = bmapi.BM_PRECISION_FP32, bmapi.BM_PRECISION_BF16
@@ -51,6 +51,27 @@ def test_step_logits_match_reference_session(product, path):
     safe = g["margin"] > 10 * TOL * np.abs(g["logits"]).max()
     n = len(out) if safe.all() else int(np.argmin(safe)) + 1
     assert out[:n] == list(g["greedy"][:n])
+
+
+@pytest.mark.parametrize("path", DECODE_GOLDENS_SAMPLED, ids=[os.path.basename(p)[11:-4] for p in DECODE_GOLDENS_SAMPLED])
+def test_smollm2_360m_q8_session_matches_reference_session(product, path):
+    """The benchmarked inference model: SmolLM2-360M with Q8 layer matrices, a 64-token prompt in one prefill pass and 16 greedy
+    tokens, against the reference session's recorded outputs (sampled logits, its eight largest logits and its greedy ids)."""
+    g, a, w = decode_case(path)
+    s = oc.LibSession(product, "gpu", a, w, int(g["precision"]), int(g["quant"]))
+    idx, top_ids = g["sample_idx"], g["top_ids"]
+    lg = s.forward(g["prompt"])
+    out = []
+    for k in range(len(g["greedy"])):
+        bound = TOL * float(g["logit_absmax"][k])
+        assert np.abs(lg[idx] - g["sample_logits"][k]).max() <= bound, (k, np.abs(lg[idx] - g["sample_logits"][k]).max(), bound)
+        assert np.abs(lg[top_ids[k]] - g["top_logits"][k]).max() <= bound, k
+        out.append(int(np.argmax(lg)))
+        if float(g["margin"][k]) > 10 * bound:   # else a near-tie in the reference: either id is right
+            assert out[-1] == int(g["greedy"][k]), (k, out, g["greedy"])
+        lg = s.step(int(g["greedy"][k]))   # continue on the reference's own sequence, so that every later step stays comparable
+    s.close()
+    assert sum(float(m) > 10 * TOL * float(x) for m, x in zip(g["margin"], g["logit_absmax"])) >= 12   # most steps are unambiguous
 
 
 @pytest.mark.parametrize("path", DECODE_GOLDENS, ids=IDS)

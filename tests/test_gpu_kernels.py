@@ -80,6 +80,69 @@ def test_matmul_golden_vectors(be, goldens, dtype):
     check(be.get(gw, (8, 16)), ref_gw, dtype)
 
 
+FUSED_MLP_SHAPES = [(64, 128, 128), (300, 192, 256), (1000, 960, 2560), (513, 576, 1536), (256, 64, 384)]
+
+
+@pytest.mark.parametrize("BT,C,H", FUSED_MLP_SHAPES)
+def test_gate_up_projection_with_swiglu_in_the_epilogue(be, BT, C, H):
+    """One launch = matmul_forward over [gate; up] followed by swiglu_forward: gate | up against the oracle GEMM, act against the
+    oracle activation of the stored (bf16) gate and up, and everything against the two-launch path."""
+    dt = BMC_BF16
+    x, w = rnd(BT, C, dtype=dt), rnd(2 * H, C, scale=2.0 * C ** -0.5, dtype=dt)
+    dx, dw = be.put(x, dt), be.put(w, dt)
+    gu, act = be.zeros(BT * 2 * H, dt), be.zeros(BT * H, dt)
+    be.ok("matmul_swiglu_forward", dt, Ptr(gu), 2 * H, Ptr(act), H, Ptr(dx), C, Ptr(dw), BT, C, H)
+    got_gu, got_act = be.get(gu, (BT, 2 * H), dt), be.get(act, (BT, H), dt)
+    check(got_gu, portk.matmul_forward(x, w), dt)
+    check(got_act, portk.swiglu_forward(got_gu[:, :H], got_gu[:, H:]), dt)
+    gu2, act2 = be.zeros(BT * 2 * H, dt), be.zeros(BT * H, dt)
+    be.ok("matmul_forward", dt, Ptr(gu2), 2 * H, Ptr(dx), C, Ptr(dw), None, 0, BT, C, 2 * H)
+    be.ok("swiglu_forward", dt, Ptr(act2), H, Ptr(gu2), Ptr(gu2, H * 2), 2 * H, BT, H)
+    assert np.array_equal(got_gu, be.get(gu2, (BT, 2 * H), dt))
+    assert oc.rel_err(got_act, be.get(act2, (BT, H), dt)) < 1e-2
+
+
+@pytest.mark.parametrize("BT,D,H", FUSED_MLP_SHAPES)
+def test_down_projection_input_gradient_with_swiglu_backward_in_the_epilogue(be, BT, D, H):
+    dt = BMC_BF16
+    go, w, gu = rnd(BT, D, dtype=dt), rnd(D, H, scale=H ** -0.5, dtype=dt), rnd(BT, 2 * H, scale=2.0, dtype=dt)
+    dgo, dw, dgu = be.put(go, dt), be.put(w, dt), be.put(gu, dt)
+    out = be.zeros(BT * 2 * H, dt)
+    be.ok("matmul_backward_inp_swiglu", dt, Ptr(out), 2 * H, Ptr(dgo), D, Ptr(dw), Ptr(dgu), 2 * H, BT, H, D)
+    dact = portk.matmul_backward_inp(go, w)
+    rg, ru = portk.swiglu_backward(gu[:, :H], gu[:, H:], dact)
+    got = be.get(out, (BT, 2 * H), dt)
+    check(got[:, :H], rg, dt)
+    check(got[:, H:], ru, dt)
+
+
+def test_fused_mlp_entry_points_decline_what_they_cannot_fuse(be):
+    z = be.zeros(64 * 512, BMC_F32)
+    assert be.call("matmul_swiglu_forward", BMC_F32, Ptr(z), 256, Ptr(z), 128, Ptr(z), 64, Ptr(z), 64, 64, 128) == -70   # fp32
+    assert be.call("matmul_swiglu_forward", BMC_BF16, Ptr(z), 272, Ptr(z), 136, Ptr(z), 64, Ptr(z), 64, 64, 136) == -70  # H % 128
+    assert be.call("matmul_backward_inp_swiglu", BMC_BF16, Ptr(z), 272, Ptr(z), 64, Ptr(z), Ptr(z), 272, 64, 136, 64) == -70
+    assert be.call("matmul_backward_inp_rowdot", BMC_BF16, Ptr(z), 96, Ptr(z), Ptr(z), 64, Ptr(z), Ptr(z), 96, 64, 96, 64, 32, 2) == -70
+    assert product_status(be) == 0
+
+
+def product_status(be):
+    return be.lib.bmc_sync(be.ctx)
+
+
+@pytest.mark.parametrize("B,S,NH,D", [(1, 64, 2, 128), (2, 160, 6, 384), (1, 512, 15, 960)])
+def test_o_projection_input_gradient_with_row_sums_in_the_epilogue(be, B, S, NH, D):
+    """ginp = gout * W and, per (row, head), the dot product of the stored ginp with another tensor of the same shape."""
+    dt = BMC_BF16
+    BT, QD = B * S, NH * 64
+    go, w, other = rnd(BT, D, dtype=dt), rnd(D, QD, scale=D ** -0.5, dtype=dt), rnd(BT, QD, dtype=dt)
+    gin, rd = be.zeros(BT * QD, dt), be.zeros(B * NH * S)
+    be.ok("matmul_backward_inp_rowdot", dt, Ptr(gin), QD, Ptr(rd), Ptr(be.put(go, dt)), D, Ptr(be.put(w, dt)), Ptr(be.put(other, dt)), QD, BT, QD, D, S, NH)
+    got = be.get(gin, (BT, QD), dt)
+    check(got, portk.matmul_backward_inp(go, w), dt)
+    ref = (got.reshape(B, S, NH, 64).astype(np.float64) * other.reshape(B, S, NH, 64)).sum(-1).transpose(0, 2, 1)
+    assert np.abs(be.get(rd, (B, NH, S)) - ref).max() <= 1e-4 * max(1.0, np.abs(ref).max())
+
+
 def test_matmul_rejects_misaligned_leading_dimension_in_bf16(be):
     x, w = be.put(rnd(8, 53), BMC_BF16), be.put(rnd(70, 53), BMC_BF16)
     assert be.call("matmul_forward", BMC_BF16, Ptr(be.zeros(8 * 70, BMC_BF16)), 70, Ptr(x), 53, Ptr(w), None, 0, 8, 53, 70) != 0

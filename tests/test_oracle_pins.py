@@ -256,7 +256,9 @@ def test_quirk_flags_change_only_what_they_name():
 
 
 # ---- inference: Q8 quantiser and decode with a KV cache ---------------------------------------------------------------
-DECODE_GOLDENS = sorted(glob.glob(os.path.join(GOLD_DIR, "ref_decode_*.npz")))
+# full-logit fixtures of the scaled-down models; the SmolLM2-360M fixtures (ref_decode_360m_*) store sampled logits only
+DECODE_GOLDENS = sorted(p for p in glob.glob(os.path.join(GOLD_DIR, "ref_decode_*.npz")) if "_360m_" not in os.path.basename(p))
+DECODE_GOLDENS_SAMPLED = sorted(glob.glob(os.path.join(GOLD_DIR, "ref_decode_360m_*.npz")))
 
 
 def _quantize(fn, x):
