@@ -39,6 +39,8 @@ struct bm_model_s {
 int bm_model_alloc(bm_model_t* m, const bm_arch_t* arch);
 void bm_model_release(bm_model_t* m);
 int bm_arch_supported(const bm_arch_t* arch);
+float* bm_build_rope_table(float theta, int scaling, float factor, float low, float high, float orig, int S, int HD);
+float* bm_build_rope_table_arch(const bm_arch_t* a, int S, int HD);
 int bm_load_bin(bm_model_t* m, const char* path);
 int bm_load_safetensors_dir(bm_model_t* m, const char* dir);
 

@@ -2,6 +2,7 @@
  * Layout and file formats follow the reference: flat fp32 buffer in a fixed tensor order
  * (src/baremetal/model.c:41-178), legacy .bin checkpoint = 256 x int32 header + that buffer
  * (src/baremetal/checkpoint.c:12-88). */
+#include <math.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -115,4 +116,37 @@ int bm_load_bin(bm_model_t* m, const char* path) {
     }
     BM_LOG_INFO("Loaded checkpoint: %s (%zu params)", path, m->n_parameters);
     return 0;
+}
+
+/* cos/sin table [S][HD/2][cos, sin] with the reference's fp32 arithmetic (rope_inv_freq incl. the llama3 frequency rule,
+ * src/kernels/forward.metal:1260-1279; angle = float(pos) * inv_freq, rope_forward_seq forward.metal:2241-2243), evaluated with
+ * the host libm. One builder for the trainer, the inference session and the kernel-name backend, so that all three rotate by
+ * bit-identical angles. Caller frees. */
+float* bm_build_rope_table(float theta, int scaling, float factor, float low, float high, float orig, int S, int HD) {
+    const int hd2 = HD / 2;
+    float* cs = (float*)malloc((size_t)S * hd2 * 2 * sizeof(float));
+    if (!cs) return NULL;
+    for (int i = 0; i < hd2; ++i) {
+        float inv = 1.0f / powf(theta, (float)(2 * i) / (float)HD);
+        if (scaling == BM_ROPE_LLAMA3) {
+            const float pi = 3.14159265358979323846f;
+            const float wavelen = 2.0f * pi / inv;
+            const float low_w = orig / low, high_w = orig / high;
+            if (wavelen > low_w) inv /= factor;
+            if (wavelen >= high_w && wavelen <= low_w) {
+                const float smooth = (orig / wavelen - low) / (high - low);
+                inv = (1.0f - smooth) * inv / factor + smooth * inv;
+            }
+        }
+        for (int s = 0; s < S; ++s) {
+            const float ang = (float)s * inv;
+            cs[((size_t)s * hd2 + i) * 2] = cosf(ang);
+            cs[((size_t)s * hd2 + i) * 2 + 1] = sinf(ang);
+        }
+    }
+    return cs;
+}
+float* bm_build_rope_table_arch(const bm_arch_t* a, int S, int HD) {
+    return bm_build_rope_table(a->rope_theta, a->rope_scaling, a->rope_factor, a->rope_low_freq_factor, a->rope_high_freq_factor,
+                               a->rope_original_max, S, HD);
 }

@@ -32,17 +32,35 @@ static char* read_file(const char* path, size_t* len_out) {
 }
 
 /* value text following "key": in a flat JSON object (first occurrence); NULL when absent */
+/* Value of member `key` of the JSON object that starts at the first '{' of `json`. Only that object's own members are
+ * looked at: a key of the same name inside a nested object or array, or text inside a string, never matches. */
 static const char* json_value(const char* json, const char* key) {
-    char pat[128];
-    snprintf(pat, sizeof pat, "\"%s\"", key);
-    const char* p = strstr(json, pat);
+    const char* p = strchr(json, '{');
     if (!p) return NULL;
-    p += strlen(pat);
-    while (*p && isspace((unsigned char)*p)) ++p;
-    if (*p != ':') return NULL;
-    ++p;
-    while (*p && isspace((unsigned char)*p)) ++p;
-    return p;
+    const size_t klen = strlen(key);
+    int depth = 0;
+    for (; *p; ++p) {
+        if (*p == '"') {
+            const char* start = p + 1;
+            for (++p; *p && *p != '"'; ++p)
+                if (*p == '\\' && p[1]) ++p;
+            if (!*p) return NULL;
+            if (depth == 1 && (size_t)(p - start) == klen && strncmp(start, key, klen) == 0) {
+                const char* q = p + 1;
+                while (*q && isspace((unsigned char)*q)) ++q;
+                if (*q == ':') {   /* a member name, not a string value */
+                    ++q;
+                    while (*q && isspace((unsigned char)*q)) ++q;
+                    return q;
+                }
+            }
+        } else if (*p == '{' || *p == '[') {
+            ++depth;
+        } else if (*p == '}' || *p == ']') {
+            if (--depth <= 0) return NULL;
+        }
+    }
+    return NULL;
 }
 static int json_int(const char* json, const char* key, int dflt) {
     const char* v = json_value(json, key);
@@ -135,6 +153,29 @@ int bm_load_safetensors_dir(bm_model_t* m, const char* dir) {
     a.max_seq_len = json_int(cfg, "max_position_embeddings", 2048);
     a.head_dim = json_int(cfg, "head_dim", a.n_heads > 0 ? a.dim / a.n_heads : 0);
     a.rope_theta = (float)json_num(cfg, "rope_theta", 10000.0);
+    /* "rope_scaling": null, or an object; only the llama3 rule exists in the engine (src/baremetal/config.c:192-211,289-294).
+     * Any other rule would train and decode with the wrong frequencies, so it is refused instead of ignored. */
+    {
+        const char* rs = json_value(cfg, "rope_scaling");
+        if (rs && *rs == '{') {
+            const char* ty = json_value(rs, "rope_type");
+            if (!ty) ty = json_value(rs, "type");
+            if (!ty || strncmp(ty, "\"llama3\"", 8) != 0) {
+                BM_LOG_ERROR("config.json: rope_scaling type %.16s is not supported (only \"llama3\")", ty ? ty : "(none)");
+                free(cfg);
+                return -1;
+            }
+            a.rope_scaling = BM_ROPE_LLAMA3;
+            a.rope_factor = (float)json_num(rs, "factor", 1.0);
+            a.rope_low_freq_factor = (float)json_num(rs, "low_freq_factor", 1.0);
+            a.rope_high_freq_factor = (float)json_num(rs, "high_freq_factor", 4.0);
+            a.rope_original_max = (float)json_num(rs, "original_max_position_embeddings", 0.0);
+            if (a.rope_factor <= 0.0f) a.rope_factor = 1.0f;
+            if (a.rope_low_freq_factor <= 0.0f) a.rope_low_freq_factor = 1.0f;
+            if (a.rope_high_freq_factor <= 0.0f) a.rope_high_freq_factor = 4.0f;
+            if (a.rope_original_max <= 0.0f) a.rope_original_max = a.max_seq_len > 0 ? (float)a.max_seq_len : 8192.0f;
+        }
+    }
     a.weight_tie = json_bool(cfg, "tie_word_embeddings", 1);
     a.bias = json_bool(cfg, "attention_bias", 0);
     a.norm = BM_NORM_RMSNORM;

@@ -221,15 +221,9 @@ bm_session_t* bmx_create_session_batched(bm_context_t* ctx, bm_model_t* model, i
     /* RoPE table with the reference's fp32 formula (rope_inv_freq, src/kernels/forward.metal:1260-1279) */
     if (ok) {
         const int hd2 = HD / 2;
-        float* cs = (float*)malloc((size_t)MS * hd2 * 2 * sizeof(float));
-        for (int i = 0; i < hd2; i++) {
-            const float inv = 1.0f / powf(a->rope_theta, (float)(2 * i) / (float)HD);
-            for (int p = 0; p < MS; p++) {
-                cs[((size_t)p * hd2 + i) * 2] = cosf((float)p * inv);
-                cs[((size_t)p * hd2 + i) * 2 + 1] = sinf((float)p * inv);
-            }
-        }
-        s->cs = upload_f32(s, cs, (size_t)MS * hd2 * 2);
+        float* cs = bm_build_rope_table_arch(a, MS, HD);   /* the same builder as the trainer: frequency scaling included */
+        s->cs = cs ? upload_f32(s, cs, (size_t)MS * hd2 * 2) : NULL;
+        if (!s->cs) ok = 0;
         bmc_sync(be);
         free(cs);
     }

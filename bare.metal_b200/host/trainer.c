@@ -27,35 +27,6 @@
 
 static size_t esz(const bm_trainer_t* t) { return (size_t)t->esize; }
 
-/* cos/sin table with the reference's fp32 arithmetic (rope_inv_freq, src/kernels/forward.metal:1260-1279;
- * angle = float(pos) * inv_freq, rope_forward_seq forward.metal:2241-2243), evaluated with the host libm. */
-static float* build_rope_table(const bm_arch_t* a, int S, int HD) {
-    const int hd2 = HD / 2;
-    float* cs = (float*)malloc((size_t)S * hd2 * 2 * sizeof(float));
-    if (!cs) return NULL;
-    for (int i = 0; i < hd2; ++i) {
-        float inv = 1.0f / powf(a->rope_theta, (float)(2 * i) / (float)HD);
-        if (a->rope_scaling == BM_ROPE_LLAMA3) {
-            const float pi = 3.14159265358979323846f;
-            const float factor = a->rope_factor, low = a->rope_low_freq_factor, high = a->rope_high_freq_factor;
-            const float orig = a->rope_original_max;
-            const float wavelen = 2.0f * pi / inv;
-            const float low_w = orig / low, high_w = orig / high;
-            if (wavelen > low_w) inv /= factor;
-            if (wavelen >= high_w && wavelen <= low_w) {
-                const float smooth = (orig / wavelen - low) / (high - low);
-                inv = (1.0f - smooth) * inv / factor + smooth * inv;
-            }
-        }
-        for (int s = 0; s < S; ++s) {
-            const float ang = (float)s * inv;
-            cs[((size_t)s * hd2 + i) * 2] = cosf(ang);
-            cs[((size_t)s * hd2 + i) * 2 + 1] = sinf(ang);
-        }
-    }
-    return cs;
-}
-
 static void free_activations(bm_trainer_t* t) {
     bmc_ctx_t* be = t->ctx->be;
     if (t->act) {
@@ -181,7 +152,7 @@ bm_trainer_t* bm_create_trainer(bm_context_t* ctx, bm_model_t* model, const bm_t
     t->d_v = (float*)bmc_alloc(be, t->P * sizeof(float));
     t->d_loss = (float*)bmc_alloc(be, 16);
     if (t->dtype == BMC_BF16) t->d_wlow = bmc_alloc(be, t->P * 2);
-    float* cs = build_rope_table(a, t->S, HD);
+    float* cs = bm_build_rope_table_arch(a, t->S, HD);
     t->d_rope_cs = (float*)bmc_alloc(be, (size_t)t->S * (HD / 2) * 2 * sizeof(float));
     if (!t->d_master || !t->d_grad || !t->d_m || !t->d_v || !t->d_loss || !t->d_rope_cs || !cs || (t->dtype == BMC_BF16 && !t->d_wlow)) {
         BM_LOG_ERROR("bm_create_trainer: out of memory");

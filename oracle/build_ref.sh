@@ -39,3 +39,20 @@ g++ -std=c++17 -O2 -fPIC -fopenmp -ffp-contract=off -D__HAVE_BFLOAT__=1 -Wno-att
   -c "$HERE/ref_cpu_backend.cpp" -o "$OUT/obj/ref_cpu_backend.o"
 g++ -shared -fopenmp -Wl,--no-undefined -o "$OUT/libbm_ref.so" "${objs[@]}" "$OUT/obj/ref_cpu_backend.o" -lm
 echo "built $OUT/libbm_ref.so"
+
+# The same unmodified reference host objects linked against the product's CUDA backend (its backend_* functions, include/backend.h)
+# instead of the CPU backend above, and the reference's own kernel test programs built against that backend. Both are checkers for
+# the backend ABI of the product; they need a GPU to run.
+PKG="$HERE/../bare.metal_b200"
+if [ -f "$PKG/libbaremetal_b200.so" ]; then
+  gcc -shared -Wl,-Bsymbolic -Wl,--no-undefined -o "$OUT/libbm_ref_cuda.so" "${objs[@]}" -L"$PKG" -lbaremetal_b200 \
+    -Wl,-rpath,'$ORIGIN/../../bare.metal_b200' -lm
+  echo "built $OUT/libbm_ref_cuda.so"
+  mkdir -p "$OUT/kernel_tests"
+  for t in matmul_bwd_test rmsnorm_bwd_test rope_seq_bwd_test rope_real_test xent_bwd_test embed_bwd_test adamw_test attn_bwd_test \
+           attn_fwd_test attn_real_test train_attn_tiled_test; do
+    gcc $CFLAGS -o "$OUT/kernel_tests/$t" "$REF/test/$t.c" "$OUT/obj/log.o" -L"$PKG" -lbaremetal_b200 \
+      -Wl,-rpath,'$ORIGIN/../../../bare.metal_b200' -lm
+  done
+  echo "built $OUT/kernel_tests/"
+fi

@@ -31,11 +31,16 @@ def reference_read(lib, trainer, what, i):
     return np.ctypeslib.as_array(fn(trainer, i), (n,)).copy()
 
 
-def load_reference():
-    """The reference's own host code + kernels on CPU (built by oracle/build_ref.sh). None if absent."""
-    if not os.path.exists(REF_LIB_PATH):
+REF_CUDA_LIB_PATH = os.path.join(HERE, "_ref", "libbm_ref_cuda.so")
+KERNEL_TESTS_DIR = os.path.join(HERE, "_ref", "kernel_tests")
+
+
+def load_reference(path=REF_LIB_PATH):
+    """The reference's own host code + kernels on CPU (built by oracle/build_ref.sh). None if absent.
+    With path=REF_CUDA_LIB_PATH: the same host code linked against the product's CUDA backend (needs a GPU)."""
+    if not os.path.exists(path):
         return None
-    lib = bmapi.bind_public_api(C.CDLL(REF_LIB_PATH))
+    lib = bmapi.bind_public_api(C.CDLL(path))
     vp, fp = C.c_void_p, C.POINTER(C.c_float)
     lib.bmref_set_precision.argtypes = [vp, C.c_int]
     lib.bmref_set_quant.argtypes = [vp, C.c_int]

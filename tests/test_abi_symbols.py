@@ -7,7 +7,7 @@ import re
 import bmapi
 
 ROOT = bmapi.ROOT
-DECL = re.compile(r"^\s*(?:[A-Za-z_][\w\s\*]*?)\b((?:bm|bmc|bmx)_[a-z0-9_]+)\s*\(", re.M)
+DECL = re.compile(r"^\s*(?:[A-Za-z_][\w\s\*]*?)\b((?:bm|bmc|bmx|backend)_[a-z0-9_]+)\s*\(", re.M)
 
 
 def declared_functions(header):
@@ -22,7 +22,7 @@ def declared_functions(header):
 def test_library_exports_every_declared_symbol():
     lib = C.CDLL(bmapi.LIB_PATH)
     total = 0
-    for header in ("baremetal.h", "baremetal_ext.h", "bm_cuda_backend.h"):
+    for header in ("baremetal.h", "baremetal_ext.h", "bm_cuda_backend.h", "backend.h"):
         names = declared_functions(header)
         assert len(names) > 10, header
         missing = [n for n in sorted(names) if not hasattr(lib, n)]
@@ -41,6 +41,20 @@ def test_reference_api_surface_is_complete():
     bm_get_num_parameters bm_get_arch_name bm_print_model_info""".split()
     lib = C.CDLL(bmapi.LIB_PATH)
     assert len(expected) == 39
+    for n in expected:
+        assert hasattr(lib, n), n
+
+
+def test_reference_backend_abi_is_complete():
+    """The 22 functions of the reference's internal backend interface (src/backend/backend.h:17-67), by name."""
+    expected = """backend_create backend_destroy backend_get_allocated_memory backend_get_peak_allocated_memory backend_get_device_info
+    backend_get_gpu_busy_ms backend_get_command_buffers backend_reset_gpu_timing backend_encode_wait_timed backend_buffer_alloc
+    backend_buffer_free backend_buffer_map backend_buffer_unmap backend_buffer_size backend_kernel_create backend_kernel_destroy
+    backend_kernel_dispatch backend_synchronize backend_encode_begin backend_encode_dispatch backend_encode_commit
+    backend_encode_wait""".split()
+    lib = C.CDLL(bmapi.LIB_PATH)
+    assert len(expected) == 22
+    assert set(expected) == declared_functions("backend.h")
     for n in expected:
         assert hasattr(lib, n), n
 

@@ -53,25 +53,40 @@ def test_step_logits_match_reference_session(product, path):
     assert out[:n] == list(g["greedy"][:n])
 
 
+# Logit bounds for the 32-layer model, as a fraction of the largest logit. Token-by-token decode does fp32 arithmetic in another
+# summation order. The one-pass prefill runs its GEMMs on the tensor cores with operands split into two bf16 terms (16 mantissa
+# bits, about 2^-17 per product), and 32 layers whose matrices were scaled up by 8 for the fixture amplify that: 1e-3 there.
+TOL_360M = {"steps": 3e-4, "prefill": 1e-3}
+
+
+@pytest.mark.parametrize("mode", ["steps", "prefill"])
 @pytest.mark.parametrize("path", DECODE_GOLDENS_SAMPLED, ids=[os.path.basename(p)[11:-4] for p in DECODE_GOLDENS_SAMPLED])
-def test_smollm2_360m_q8_session_matches_reference_session(product, path):
-    """The benchmarked inference model: SmolLM2-360M with Q8 layer matrices, a 64-token prompt in one prefill pass and 16 greedy
-    tokens, against the reference session's recorded outputs (sampled logits, its eight largest logits and its greedy ids)."""
+def test_smollm2_360m_q8_session_matches_reference_session(product, path, mode):
+    """The benchmarked inference model: SmolLM2-360M with Q8 layer matrices, a 64-token prompt (token by token, or in one prefill
+    pass) and 16 greedy tokens, against the reference session's recorded outputs (sampled logits, its eight largest logits and its
+    greedy ids)."""
     g, a, w = decode_case(path)
     s = oc.LibSession(product, "gpu", a, w, int(g["precision"]), int(g["quant"]))
     idx, top_ids = g["sample_idx"], g["top_ids"]
-    lg = s.forward(g["prompt"])
-    out = []
+    if mode == "steps":
+        os.environ["BM_NO_PREFILL"] = "1"
+    try:
+        lg = s.forward(g["prompt"])
+    finally:
+        os.environ.pop("BM_NO_PREFILL", None)
+    out, worst = [], 0.0
     for k in range(len(g["greedy"])):
-        bound = TOL * float(g["logit_absmax"][k])
-        assert np.abs(lg[idx] - g["sample_logits"][k]).max() <= bound, (k, np.abs(lg[idx] - g["sample_logits"][k]).max(), bound)
-        assert np.abs(lg[top_ids[k]] - g["top_logits"][k]).max() <= bound, k
+        bound = TOL_360M[mode] * float(g["logit_absmax"][k])
+        err = max(np.abs(lg[idx] - g["sample_logits"][k]).max(), np.abs(lg[top_ids[k]] - g["top_logits"][k]).max())
+        worst = max(worst, err / float(g["logit_absmax"][k]))
+        assert err <= bound, (k, err, bound)
         out.append(int(np.argmax(lg)))
         if float(g["margin"][k]) > 10 * bound:   # else a near-tie in the reference: either id is right
             assert out[-1] == int(g["greedy"][k]), (k, out, g["greedy"])
         lg = s.step(int(g["greedy"][k]))   # continue on the reference's own sequence, so that every later step stays comparable
     s.close()
-    assert sum(float(m) > 10 * TOL * float(x) for m, x in zip(g["margin"], g["logit_absmax"])) >= 12   # most steps are unambiguous
+    print(f"360m decode {os.path.basename(path)} {mode}: worst logit error {worst:.2e} of the largest logit")
+    assert sum(float(m) > 10 * TOL_360M[mode] * float(x) for m, x in zip(g["margin"], g["logit_absmax"])) >= 12   # most steps are unambiguous
 
 
 @pytest.mark.parametrize("path", DECODE_GOLDENS, ids=IDS)
