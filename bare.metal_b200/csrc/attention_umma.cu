@@ -104,6 +104,7 @@ struct FwdArgs {
     bf16* out;
     int ldo;
     float* lse;
+    const uint32_t* keymask;   // [B][ceil(S / 32)] bit i of word w = position 32 * w + i takes part (null: every position does)
     int S, NH, NKV;
     float scale;
     int* err;
@@ -271,13 +272,25 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             if (lane == 0) mbar_arrive(&bars.s_free[x]);
             if (quarter == 0 && lane == 0) FTRACE(3 + 6 * x, j);
             const int k0 = j * FK;
-            if (j == n_mine - 1 || k0 + FK > p.S) {  // diagonal tile or ragged end: mask keys after the query / past the end
+            // padding mask (attention_forward_seq_masked, src/kernels/forward.metal:1853): one word of key bits per 32 columns
+            uint32_t mw[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
+            bool tile_masked = false;
+            if (p.keymask) {
+                const int W = (p.S + 31) >> 5;
+#pragma unroll
+                for (int ch = 0; ch < 4; ++ch) {
+                    const int wi = (k0 >> 5) + ch;
+                    mw[ch] = wi < W ? p.keymask[(size_t)b * W + wi] : 0u;
+                    tile_masked |= mw[ch] != 0xffffffffu;
+                }
+            }
+            if (j == n_mine - 1 || k0 + FK > p.S || tile_masked) {  // diagonal tile, ragged end or masked keys
 #pragma unroll
                 for (int ch = 0; ch < 4; ++ch)
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         const int kj = k0 + ch * 32 + i;
-                        if (kj > qi || kj >= p.S) v[ch][i] = __float_as_uint(-INFINITY);
+                        if (kj > qi || kj >= p.S || !((mw[ch] >> i) & 1u)) v[ch][i] = __float_as_uint(-INFINITY);
                     }
             }
             // eight independent max chains (a single chain of 128 dependent FMNMX would be latency-bound)
@@ -354,7 +367,10 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         }
         if (ok && n_mine > 0) {
             tc_fence_after_sync();
-            const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+            // a masked position is no query either: its output row is zero, and its log-sum-exp +infinity makes every probability
+            // the backward recomputes for it zero (no gradient to or from the row)
+            const bool q_on = !p.keymask || (qi < p.S && ((p.keymask[(size_t)b * ((p.S + 31) >> 5) + (qi >> 5)] >> (qi & 31)) & 1u));
+            const float inv = (l_run > 0.f && q_on) ? 1.0f / l_run : 0.f;
             bf16* orow = p.out + (size_t)(row0 + qi) * p.ldo + (size_t)h * FHD;
 #pragma unroll
             for (int ch = 0; ch < FHD / 32; ++ch) {
@@ -374,7 +390,7 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 }
             }
             if (qi < p.S)
-                p.lse[((size_t)b * p.NH + h) * p.S + qi] = l_run > 0.f ? (m_ref + log2f(l_run)) * (1.0f / LOG2E_F) : -INFINITY;
+                p.lse[((size_t)b * p.NH + h) * p.S + qi] = !q_on ? INFINITY : l_run > 0.f ? (m_ref + log2f(l_run)) * (1.0f / LOG2E_F) : -INFINITY;
             tc_fence_before_sync();
         }
     }
@@ -425,6 +441,7 @@ struct BwdArgs {
     int ldgkv;
     const float *lse, *delta;
     const float* rope_cs;   // [S][32][cos, sin] or null; when set, dK leaves rotated backwards (the transposed rotation of RoPE)
+    const uint32_t* keymask;   // as in the forward; masked queries need nothing here: the forward stored +infinity as their log-sum-exp
     int S, NH, NKV;
     float scale;
     int* err;
@@ -643,6 +660,12 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 }
             }
         };
+        // this warp's 32 key columns of the padding mask (all ones without a mask)
+        uint32_t kw = 0xffffffffu;
+        if (p.keymask) {
+            const int W = (p.S + 31) >> 5, wi = (n0 >> 5) + cg;
+            kw = wi < W ? p.keymask[(size_t)b * W + wi] : 0u;
+        }
         float lse_next, dlt_next;
         load_stats(0, lse_next, dlt_next);
         for (int it = 0; it < total; ++it) {
@@ -664,7 +687,7 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars.sdp_free);
             if (cw == 0 && lane == 0) BTRACE(5, it);
-            const bool diag = (mb == nblk) || (n0 + FK > p.S);
+            const bool diag = (mb == nblk) || (n0 + FK > p.S) || kw != 0xffffffffu;
             const float dlt_s = -dlt * p.scale;
             uint32_t pp[16], dd[16];
 #pragma unroll
@@ -676,8 +699,8 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 p1 = ex2_approx(p1);
                 if (diag) {
                     const int kl = cg * 32 + i;   // key inside the tile; on the diagonal tile n0 == q0
-                    if ((mb == nblk && kl > r) || n0 + kl >= p.S) p0 = 0.f;
-                    if ((mb == nblk && kl + 1 > r) || n0 + kl + 1 >= p.S) p1 = 0.f;
+                    if ((mb == nblk && kl > r) || n0 + kl >= p.S || !((kw >> i) & 1u)) p0 = 0.f;
+                    if ((mb == nblk && kl + 1 > r) || n0 + kl + 1 >= p.S || !((kw >> (i + 1)) & 1u)) p1 = 0.f;
                 }
                 mul2_f(d0, d1, d0, d1, p0, p1);
                 __nv_bfloat162 hp = __floats2bfloat162_rn(p0, p1), hd = __floats2bfloat162_rn(d0, d1);
@@ -889,6 +912,16 @@ int make_rows_map(CUtensorMap* tm, const void* base, uint64_t width, uint64_t ro
                : -11;
 }
 
+// uint8 mask [B, S] -> one bit per position, [B][ceil(S / 32)] words
+__global__ void pack_mask_kernel(uint32_t* __restrict__ bits, const uint8_t* __restrict__ mask, int B, int S) {
+    const int W = (S + 31) >> 5;
+    const long gw = (blockIdx.x * (long)blockDim.x + threadIdx.x) >> 5;   // one warp per word
+    if (gw >= (long)B * W) return;
+    const int bb = (int)(gw / W), w = (int)(gw - (long)bb * W), pos = w * 32 + (threadIdx.x & 31);
+    const unsigned vote = __ballot_sync(0xffffffffu, pos < S && mask[(size_t)bb * S + pos] != 0);
+    if ((threadIdx.x & 31) == 0) bits[gw] = vote;
+}
+
 __global__ void cast_rows_kernel(bf16* __restrict__ out, int ldo, const float* __restrict__ in, int ldi, int rows, int cols4) {
     const long i = blockIdx.x * (long)blockDim.x + threadIdx.x;
     if (i >= (long)rows * cols4) return;
@@ -916,8 +949,15 @@ int cast_rows_f32_to_bf16(bf16* out, int ldo, const float* in, int ldi, int rows
     return 0;
 }
 
-int flash_attention_forward_umma(bf16* out, int ldo, float* lse, const bf16* q, int ldq, const bf16* k, const bf16* v, int ldkv, int B,
-                                 int S, int NH, int NKV, int HD, float scale, int* err_flag, cudaStream_t st) {
+size_t flash_attention_mask_bits_bytes(int B, int S) { return (size_t)B * ((S + 31) / 32) * sizeof(uint32_t); }
+int flash_attention_pack_mask(uint32_t* bits, const uint8_t* mask, int B, int S, cudaStream_t st) {
+    const long threads = (long)B * ((S + 31) / 32) * 32;
+    pack_mask_kernel<<<(int)((threads + 255) / 256), 256, 0, st>>>(bits, mask, B, S);
+    return 0;
+}
+
+int flash_attention_forward_umma(bf16* out, int ldo, float* lse, const bf16* q, int ldq, const bf16* k, const bf16* v, int ldkv,
+                                 const uint32_t* keymask, int B, int S, int NH, int NKV, int HD, float scale, int* err_flag, cudaStream_t st) {
     if (HD != FHD || NKV <= 0 || NH % NKV) return -1;
     if ((ldq % 8) || (ldkv % 8) || (ldo % 8) || (((uintptr_t)q) & 15) || (((uintptr_t)k) & 15) || (((uintptr_t)v) & 15) ||
         (((uintptr_t)out) & 15))
@@ -936,9 +976,9 @@ int flash_attention_forward_umma(bf16* out, int ldo, float* lse, const bf16* q, 
     long long* trace = nullptr;
     cudaMalloc(&trace, 14 * 32 * sizeof(long long));
     cudaMemset(trace, 0, 14 * 32 * sizeof(long long));
-    FwdArgs a{trace, out, ldo, lse, S, NH, NKV, scale, err_flag};
+    FwdArgs a{trace, out, ldo, lse, keymask, S, NH, NKV, scale, err_flag};
 #else
-    FwdArgs a{out, ldo, lse, S, NH, NKV, scale, err_flag};
+    FwdArgs a{out, ldo, lse, keymask, S, NH, NKV, scale, err_flag};
 #endif
     dim3 grid((S + 2 * FQ - 1) / (2 * FQ), NH, B);
     flash_fwd_umma_kernel<<<grid, FWD_THREADS, FWD_DYN_SMEM, st>>>(tq, tk, tv, a);
@@ -971,8 +1011,8 @@ int flash_attention_forward_umma(bf16* out, int ldo, float* lse, const bf16* q, 
 
 int flash_attention_backward_umma(bf16* gq, int ldgq, bf16* gk, bf16* gv, int ldgkv, const bf16* gout, int ldo, const bf16* out,
                                   const float* lse, const bf16* q, int ldq, const bf16* k, const bf16* v, int ldkv, int B, int S, int NH,
-                                  int NKV, int HD, float scale, void* scratch, const float* delta_in, const float* rope_cs, int* err_flag,
-                                  cudaStream_t st) {
+                                  int NKV, int HD, float scale, void* scratch, const float* delta_in, const float* rope_cs,
+                                  const uint32_t* keymask, int* err_flag, cudaStream_t st) {
     if (HD != FHD || NKV <= 0 || NH % NKV) return -1;
     if ((ldq % 8) || (ldkv % 8) || (ldo % 8) || (ldgkv % 8) || (ldgq % 4) || (((uintptr_t)q) & 15) || (((uintptr_t)k) & 15) ||
         (((uintptr_t)v) & 15) || (((uintptr_t)gout) & 15) || (((uintptr_t)gk) & 15) || (((uintptr_t)gv) & 15) || (((uintptr_t)gq) & 7) ||
@@ -1002,9 +1042,9 @@ int flash_attention_backward_umma(bf16* gq, int ldgq, bf16* gk, bf16* gv, int ld
     long long* trace = nullptr;
     cudaMalloc(&trace, 10 * 32 * sizeof(long long));
     cudaMemset(trace, 0, 10 * 32 * sizeof(long long));
-    BwdArgs a{trace, dq_acc, gk, gv, ldgkv, lse, delta, rope_cs, S, NH, NKV, scale, err_flag};
+    BwdArgs a{trace, dq_acc, gk, gv, ldgkv, lse, delta, rope_cs, keymask, S, NH, NKV, scale, err_flag};
 #else
-    BwdArgs a{dq_acc, gk, gv, ldgkv, lse, delta, rope_cs, S, NH, NKV, scale, err_flag};
+    BwdArgs a{dq_acc, gk, gv, ldgkv, lse, delta, rope_cs, keymask, S, NH, NKV, scale, err_flag};
 #endif
     dim3 grid((S + FK - 1) / FK, NKV, B);
     flash_bwd_umma_kernel<<<grid, BWD_THREADS, BWD_DYN_SMEM, st>>>(tq, tk, tv, tg, a);

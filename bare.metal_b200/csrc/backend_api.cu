@@ -33,6 +33,8 @@ struct bmc_ctx_s {
     size_t rms_scratch_floats;
     void* attn_scratch;
     size_t attn_scratch_bytes;
+    void* mask_bits;  // padding mask of the attention kernels, one bit per position
+    size_t mask_bits_bytes;
     cudaEvent_t ev0[8], ev1[8];
     // optional per-launch timing of the tensor-core GEMM (bmc_gemm_timing)
     bool gemm_timing;
@@ -150,6 +152,8 @@ bmc_ctx_t* bmc_create(int device_ordinal) {
     ctx->rms_scratch_floats = 0;
     ctx->attn_scratch = nullptr;
     ctx->attn_scratch_bytes = 0;
+    ctx->mask_bits = nullptr;
+    ctx->mask_bits_bytes = 0;
     ctx->gemm_timing = false;
     ctx->gt_used = 0;
     for (int i = 0; i < 2; ++i) { ctx->graphs[i] = nullptr; ctx->graph_execs[i] = nullptr; }
@@ -181,6 +185,7 @@ void bmc_destroy(bmc_ctx_t* ctx) {
     for (auto& kv : ctx->allocs) cudaFree(kv.first);
     if (ctx->rms_scratch) cudaFree(ctx->rms_scratch);
     if (ctx->attn_scratch) cudaFree(ctx->attn_scratch);
+    if (ctx->mask_bits) cudaFree(ctx->mask_bits);
     cudaFree(ctx->d_err);
     for (int i = 0; i < 8; ++i) {
         cudaEventDestroy(ctx->ev0[i]);
@@ -433,9 +438,15 @@ int bmc_attention_forward(bmc_ctx_t* ctx, int dtype, void* d_out, int ldo, float
     if (dtype == BMC_F32)
         return note(ctx, attention_forward_simt<float>((float*)d_out, ldo, d_lse, (const float*)d_q, ldq, (const float*)d_k,
                                                        (const float*)d_v, ldkv, d_mask, B, S, NH, NKV, HD, scale, ctx->stream));
-    if (!d_mask && flash_attention_supported(HD, NH, NKV) && (ldo % 8) == 0)
+    if (flash_attention_supported(HD, NH, NKV) && (ldo % 8) == 0) {
+        const uint32_t* bits = nullptr;
+        if (d_mask) {   // the tensor-core kernels take the padding mask as bits
+            bits = (const uint32_t*)scratch_get(ctx, &ctx->mask_bits, &ctx->mask_bits_bytes, flash_attention_mask_bits_bytes(B, S));
+            if (!bits || flash_attention_pack_mask((uint32_t*)bits, d_mask, B, S, ctx->stream)) return -50;
+        }
         return note(ctx, flash_attention_forward_umma((bf16*)d_out, ldo, d_lse, (const bf16*)d_q, ldq, (const bf16*)d_k, (const bf16*)d_v,
-                                                      ldkv, B, S, NH, NKV, HD, scale, ctx->d_err, ctx->stream));
+                                                      ldkv, bits, B, S, NH, NKV, HD, scale, ctx->d_err, ctx->stream), d_mask ? 2 : 1);
+    }
     return note(ctx, attention_forward_simt<bf16>((bf16*)d_out, ldo, d_lse, (const bf16*)d_q, ldq, (const bf16*)d_k, (const bf16*)d_v,
                                                   ldkv, d_mask, B, S, NH, NKV, HD, scale, ctx->stream));
 }
@@ -446,13 +457,19 @@ int bmc_attention_backward_fused(bmc_ctx_t* ctx, int dtype, void* d_gq, int ldgq
                                  int HD, float scale) {
     BMC_CHECK_CTX(ctx);
     const size_t rows = (size_t)B * S;
-    if (dtype == BMC_BF16 && !d_mask && flash_attention_supported(HD, NH, NKV) && (ldgkv % 8) == 0 && (ldo % 8) == 0) {
+    if (dtype == BMC_BF16 && flash_attention_supported(HD, NH, NKV) && (ldgkv % 8) == 0 && (ldo % 8) == 0) {
         const size_t need = flash_attention_backward_scratch_bytes(B, S, NH, HD);
         void* scratch = scratch_get(ctx, &ctx->attn_scratch, &ctx->attn_scratch_bytes, need);
         if (!scratch) return -50;
+        const uint32_t* bits = nullptr;
+        if (d_mask) {
+            bits = (const uint32_t*)scratch_get(ctx, &ctx->mask_bits, &ctx->mask_bits_bytes, flash_attention_mask_bits_bytes(B, S));
+            if (!bits || flash_attention_pack_mask((uint32_t*)bits, d_mask, B, S, ctx->stream)) return -50;
+        }
         return note(ctx, flash_attention_backward_umma((bf16*)d_gq, ldgq, (bf16*)d_gk, (bf16*)d_gv, ldgkv, (const bf16*)d_gout, ldo,
                                                        (const bf16*)d_out, d_lse, (const bf16*)d_q, ldq, (const bf16*)d_k, (const bf16*)d_v,
-                                                       ldkv, B, S, NH, NKV, HD, scale, scratch, d_delta, d_rope_cs, ctx->d_err, ctx->stream),
+                                                       ldkv, B, S, NH, NKV, HD, scale, scratch, d_delta, d_rope_cs, bits, ctx->d_err,
+                                                       ctx->stream),
                     d_delta ? 3 : 4);
     }
     int rc;

@@ -3,7 +3,8 @@
 // Gradients are produced in fp32 in one flat array (trainer-state order: layer 0 .. layer L-1, final norm,
 // tied embedding). Layers are grouped into buckets; as soon as backward has finished the lowest layer of a
 // bucket, the compute stream records an event, and the communication stream (a) casts that fp32 range to
-// bf16 into a flat bf16 gradient array, (b) all-reduces it in place (sum). Backward runs from the last layer
+// bf16 into a flat bf16 gradient array, (b) all-reduces it in place (sum) — a trainer in fp32 mode skips the cast and all-reduces
+// the fp32 range itself, so that its 1e-4 parity bound also holds across ranks. Backward runs from the last layer
 // to the first, so buckets complete from the end of the array towards the start and their reductions overlap
 // the remaining backward work; the final-norm + embedding bucket completes last. AdamW then reads the reduced
 // bf16 gradients with grad_scale = 1 / (sequences per rank * world).
@@ -14,6 +15,7 @@
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
+#include <time.h>
 
 #include <vector>
 
@@ -35,6 +37,8 @@ struct NcclApi {
     int (*CommDestroy)(ncclComm_t);
     int (*AllReduce)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t);
     const char* (*GetErrorString)(int);
+    int (*CommGetAsyncError)(ncclComm_t, int*);  // optional
+    int (*CommAbort)(ncclComm_t);                // optional
 };
 
 NcclApi* nccl() {
@@ -50,6 +54,8 @@ NcclApi* nccl() {
             api.CommDestroy = (int (*)(ncclComm_t))dlsym(api.lib, "ncclCommDestroy");
             api.AllReduce = (int (*)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t))dlsym(api.lib, "ncclAllReduce");
             api.GetErrorString = (const char* (*)(int))dlsym(api.lib, "ncclGetErrorString");
+            api.CommGetAsyncError = (int (*)(ncclComm_t, int*))dlsym(api.lib, "ncclCommGetAsyncError");
+            api.CommAbort = (int (*)(ncclComm_t))dlsym(api.lib, "ncclCommAbort");
             if (api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllReduce) state = 1;
         }
         if (state != 1) fprintf(stderr, "[ERROR] data parallel: cannot load NCCL (libnccl.so.2): %s\n", dlerror());
@@ -77,7 +83,44 @@ struct bm_dp_s {
     float* d_loss_buf;
     size_t P;
     int last_microstep;
+    int f32;          // gradients travel as fp32 (trainer in fp32 mode)
+    int failed;       // a wait ran out or NCCL reported an asynchronous error: the communicator has been aborted
+    double timeout_s; // host-side bound on every wait for the communication stream (env BM_DP_TIMEOUT_S, default 600)
 };
+
+namespace {
+// Host-side wait for the communication stream with a deadline: polls the stream (and NCCL's asynchronous error state where
+// the library offers it) instead of blocking, so that a peer that exited or never joined ends this rank's step with an error
+// instead of hanging it behind a spinning NCCL kernel. On expiry or error the communicator is aborted (ncclCommAbort frees the
+// stream) and every later exchange fails fast.
+int wait_comm(bm_dp_s* dp) {
+    if (dp->failed) return -1;
+    NcclApi* api = nccl();
+    struct timespec t0, t;
+    clock_gettime(CLOCK_MONOTONIC, &t0);
+    for (long it = 0;; ++it) {
+        const cudaError_t q = cudaStreamQuery(dp->comm_stream);
+        if (q == cudaSuccess) return 0;
+        int async_err = 0;
+        bool bad = q != cudaErrorNotReady;
+        if (!bad && api && api->CommGetAsyncError && (it & 63) == 0 && api->CommGetAsyncError(dp->comm, &async_err) == ncclSuccess && async_err != ncclSuccess)
+            bad = true;
+        clock_gettime(CLOCK_MONOTONIC, &t);
+        const double el = (double)(t.tv_sec - t0.tv_sec) + 1e-9 * (double)(t.tv_nsec - t0.tv_nsec);
+        if (bad || el > dp->timeout_s) {
+            fprintf(stderr, "[ERROR] data parallel: %s after %.1f s on rank %d; aborting the communicator\n",
+                    bad ? "communication error" : "gradient exchange timed out", el, dp->rank);
+            if (api && api->CommAbort && dp->comm) { api->CommAbort(dp->comm); dp->comm = nullptr; }
+            dp->failed = 1;
+            return -1;
+        }
+        if (it > 1000) {   // after the first microseconds of spinning, yield the core between polls
+            struct timespec ns = {0, 50000};
+            nanosleep(&ns, nullptr);
+        }
+    }
+}
+}  // namespace
 
 extern "C" {
 
@@ -110,7 +153,7 @@ int bmx_dp_unique_id(void* out_id) {
 }
 
 struct bm_dp_s* bm_dp_create(bmc_ctx_t* be, int rank, int world, const void* nccl_id, size_t P, int n_layers, const size_t* layer_begin,
-                             float* d_grad_f32) {
+                             float* d_grad_f32, int grads_f32) {
     NcclApi* api = nccl();
     if (!api || !be || !nccl_id || world < 1 || rank < 0 || rank >= world) return nullptr;
     bm_dp_s* dp = new bm_dp_s();
@@ -120,6 +163,11 @@ struct bm_dp_s* bm_dp_create(bmc_ctx_t* be, int rank, int world, const void* ncc
     dp->P = P;
     dp->d_grad_f32 = d_grad_f32;
     dp->last_microstep = 1;
+    dp->f32 = grads_f32 ? 1 : 0;
+    dp->failed = 0;
+    dp->timeout_s = 600.0;
+    if (const char* te = getenv("BM_DP_TIMEOUT_S")) if (atof(te) > 0) dp->timeout_s = atof(te);
+    dp->d_grad_bf16 = nullptr;
     ncclUniqueId id;
     memcpy(&id, nccl_id, sizeof id);
     int rc = api->CommInitRank(&dp->comm, world, id, rank);
@@ -130,7 +178,7 @@ struct bm_dp_s* bm_dp_create(bmc_ctx_t* be, int rank, int world, const void* ncc
     }
     cudaStreamCreateWithFlags(&dp->comm_stream, cudaStreamNonBlocking);
     cudaEventCreateWithFlags(&dp->done_ev, cudaEventDisableTiming);
-    if (cudaMalloc(&dp->d_grad_bf16, P * sizeof(bmb::bf16)) != cudaSuccess || cudaMalloc(&dp->d_loss_buf, 16) != cudaSuccess) {
+    if ((!dp->f32 && cudaMalloc(&dp->d_grad_bf16, P * sizeof(bmb::bf16)) != cudaSuccess) || cudaMalloc(&dp->d_loss_buf, 16) != cudaSuccess) {
         fprintf(stderr, "[ERROR] data parallel: out of device memory\n");
         delete dp;
         return nullptr;
@@ -150,7 +198,7 @@ struct bm_dp_s* bm_dp_create(bmc_ctx_t* be, int rank, int world, const void* ncc
 
 void bm_dp_destroy(struct bm_dp_s* dp) {
     if (!dp) return;
-    cudaStreamSynchronize(dp->comm_stream);
+    if (!dp->failed) wait_comm(dp);
     NcclApi* api = nccl();
     if (api && dp->comm) api->CommDestroy(dp->comm);
     for (auto& ev : dp->ready_ev) cudaEventDestroy(ev);
@@ -165,41 +213,68 @@ int bm_dp_world(struct bm_dp_s* dp) { return dp ? dp->world : 1; }
 void bm_dp_begin_window(struct bm_dp_s*) {}
 void bm_dp_set_last_microstep(struct bm_dp_s* dp, int is_last) { if (dp) dp->last_microstep = is_last; }
 
+// cast (bf16 mode) + all-reduce of one bucket on the communication stream, behind an event recorded now on the compute stream
+static int reduce_bucket(struct bm_dp_s* dp, size_t i) {
+    NcclApi* api = nccl();
+    if (!api || dp->failed) return -3;
+    cudaStream_t compute = (cudaStream_t)bmc_stream(dp->be);
+    const Bucket& b = dp->buckets[i];
+    cudaEventRecord(dp->ready_ev[i], compute);
+    cudaStreamWaitEvent(dp->comm_stream, dp->ready_ev[i], 0);
+    const size_t n = b.end - b.begin;
+    int rc;
+    if (dp->f32) {
+        rc = api->AllReduce(dp->d_grad_f32 + b.begin, dp->d_grad_f32 + b.begin, n, ncclFloat32, ncclSum, dp->comm, dp->comm_stream);
+    } else {
+        if (bmb::cast_f32_to_bf16(dp->d_grad_bf16 + b.begin, dp->d_grad_f32 + b.begin, n, dp->comm_stream)) return -1;
+        rc = api->AllReduce(dp->d_grad_bf16 + b.begin, dp->d_grad_bf16 + b.begin, n, ncclBfloat16, ncclSum, dp->comm, dp->comm_stream);
+    }
+    if (rc != ncclSuccess) {
+        fprintf(stderr, "[ERROR] ncclAllReduce failed: %s\n", api->GetErrorString ? api->GetErrorString(rc) : "?");
+        return -2;
+    }
+    return 0;
+}
+
 int bm_dp_bucket_ready(struct bm_dp_s* dp, int layer) {
     if (!dp || !dp->last_microstep) return 0;
-    NcclApi* api = nccl();
-    cudaStream_t compute = (cudaStream_t)bmc_stream(dp->be);
     for (size_t i = 0; i < dp->buckets.size(); ++i) {
-        const Bucket& b = dp->buckets[i];
-        if (b.ready_at != layer) continue;
-        cudaEventRecord(dp->ready_ev[i], compute);
-        cudaStreamWaitEvent(dp->comm_stream, dp->ready_ev[i], 0);
-        const size_t n = b.end - b.begin;
-        if (bmb::cast_f32_to_bf16(dp->d_grad_bf16 + b.begin, dp->d_grad_f32 + b.begin, n, dp->comm_stream)) return -1;
-        const int rc = api->AllReduce(dp->d_grad_bf16 + b.begin, dp->d_grad_bf16 + b.begin, n, ncclBfloat16, ncclSum, dp->comm, dp->comm_stream);
-        if (rc != ncclSuccess) {
-            fprintf(stderr, "[ERROR] ncclAllReduce failed: %s\n", api->GetErrorString ? api->GetErrorString(rc) : "?");
-            return -2;
-        }
+        if (dp->buckets[i].ready_at != layer) continue;
+        const int rc = reduce_bucket(dp, i);
+        if (rc) return rc;
+    }
+    return 0;
+}
+
+// Every bucket at once: for a window that ends before its last micro-step (bm_train_flush), whose gradients were never exchanged.
+// A collective call: every rank must make it.
+int bm_dp_reduce_all(struct bm_dp_s* dp) {
+    if (!dp) return 0;
+    for (size_t i = 0; i < dp->buckets.size(); ++i) {
+        const int rc = reduce_bucket(dp, i);
+        if (rc) return rc;
     }
     return 0;
 }
 
 int bm_dp_adamw(struct bm_dp_s* dp, bm_trainer_t* t, const float* hp) {
+    if (dp->failed) return -3;
     cudaStream_t compute = (cudaStream_t)bmc_stream(dp->be);
     cudaEventRecord(dp->done_ev, dp->comm_stream);
     cudaStreamWaitEvent(compute, dp->done_ev, 0);
+    if (dp->f32) return bmc_adamw(dp->be, t->d_master, t->d_wlow, dp->d_grad_f32, BMC_F32, t->d_m, t->d_v, t->P, hp);
     return bmc_adamw(dp->be, t->d_master, t->d_wlow, dp->d_grad_bf16, BMC_BF16, t->d_m, t->d_v, t->P, hp);
 }
 
 float bm_dp_mean_loss(struct bm_dp_s* dp, float local_loss) {
     NcclApi* api = nccl();
     if (!dp || !api) return local_loss;
+    if (dp->failed) return -1.0f;
     cudaMemcpyAsync(dp->d_loss_buf, &local_loss, sizeof(float), cudaMemcpyHostToDevice, dp->comm_stream);
     if (api->AllReduce(dp->d_loss_buf, dp->d_loss_buf, 1, ncclFloat32, ncclSum, dp->comm, dp->comm_stream) != ncclSuccess) return -1.0f;
     float sum = 0.f;
     cudaMemcpyAsync(&sum, dp->d_loss_buf, sizeof(float), cudaMemcpyDeviceToHost, dp->comm_stream);
-    cudaStreamSynchronize(dp->comm_stream);
+    if (wait_comm(dp) != 0) return -1.0f;   // bounded: a peer that left ends the step with an error, not a hang
     return sum / (float)dp->world;
 }
 
@@ -210,7 +285,7 @@ int bmx_trainer_dp_init(bm_trainer_t* t, int rank, int world, const void* nccl_i
     std::vector<size_t> layer_begin(L + 1);
     for (int l = 0; l < L; ++l) layer_begin[l] = t->params[9 * l].off;
     layer_begin[L] = t->params[9 * L].off;
-    t->dp = bm_dp_create(t->ctx->be, rank, world, nccl_id, t->P, L, layer_begin.data(), t->d_grad);
+    t->dp = bm_dp_create(t->ctx->be, rank, world, nccl_id, t->P, L, layer_begin.data(), t->d_grad, t->dtype == BMC_F32);
     // Three streams (compute, weight-gradient side stream, communication) have only been exercised on one GPU; with the
     // exchange active the weight gradients stay on the compute stream unless BM_DP_SIDE_STREAM=1 asks otherwise.
     if (t->dp && !getenv("BM_DP_SIDE_STREAM")) t->side_stream = 0;

@@ -68,10 +68,11 @@ void bm_load_weights(bm_model_t* model, const char* path) {
     BM_LOG_ERROR("Failed to load weights from %s", path);
 }
 
+/* Writes the model's host weights: a Hugging Face safetensors directory, or the legacy .bin file when the path ends in ".bin"
+ * (host/safetensors.c). The reference declares this function and leaves it unimplemented (src/baremetal/checkpoint.c:84-88).
+ * Weights a trainer has updated live on the device: bmx_trainer_sync_model() brings them back into the model first. */
 void bm_save_weights(bm_model_t* model, const char* path) {
-    (void)model; (void)path;
-    /* unimplemented in the reference as well (bmt_checkpoint_save returns -1, src/baremetal/checkpoint.c:84-88) */
-    fprintf(stderr, "[WARN] bm_save_weights: not implemented\n");
+    if (bm_save_weights_to(model, path) != 0) BM_LOG_ERROR("bm_save_weights: could not write %s", path ? path : "(null)");
 }
 
 void bm_destroy_model(bm_model_t* model) {
@@ -186,6 +187,15 @@ float* bmx_model_weight_buffer(bm_model_t* model, size_t* n_out) {
 int bmx_gemm_timing(bm_context_t* ctx, int enable) { return ctx ? bmc_gemm_timing(ctx->be, enable) : -1; }
 int bmx_gemm_timing_collect(bm_context_t* ctx, double* out3) { return ctx ? bmc_gemm_timing_collect(ctx->be, out3) : -1; }
 int bmx_model_vocab_size(const bm_model_t* model) { return model ? model->arch.vocab_size : 0; }
+double bmx_model_arch_field(const bm_model_t* model, const char* name) {
+    if (!model || !name) return -1.0;
+    const bm_arch_t* a = &model->arch;
+#define F(n) if (strcmp(name, #n) == 0) return (double)a->n
+    F(dim); F(hidden_dim); F(n_layers); F(n_heads); F(n_kv_heads); F(vocab_size); F(max_seq_len); F(head_dim); F(weight_tie);
+    F(rope_theta); F(rope_scaling); F(rope_factor); F(rope_low_freq_factor); F(rope_high_freq_factor); F(rope_original_max);
+#undef F
+    return -1.0;
+}
 int bmx_model_set_quant(bm_model_t* model, int bits) {
     if (!model || (bits != 0 && bits != 8)) return -1; /* Q4 is outside this build */
     model->quant_bits = bits;

@@ -36,6 +36,7 @@ struct bm_model_s {
     float *embed, *ln1w, *qw, *kw, *vw, *ow, *ln2w, *gate, *up, *down, *lnfw;
 };
 
+#define BM_CHECKPOINT_MAGIC 20250718 /* src/baremetal/checkpoint.h:11 */
 int bm_model_alloc(bm_model_t* m, const bm_arch_t* arch);
 void bm_model_release(bm_model_t* m);
 int bm_arch_supported(const bm_arch_t* arch);
@@ -43,6 +44,7 @@ float* bm_build_rope_table(float theta, int scaling, float factor, float low, fl
 float* bm_build_rope_table_arch(const bm_arch_t* a, int S, int HD);
 int bm_load_bin(bm_model_t* m, const char* path);
 int bm_load_safetensors_dir(bm_model_t* m, const char* dir);
+int bm_save_weights_to(const bm_model_t* m, const char* path);
 
 /* One entry per trainable tensor, in trainer-state order (per layer ln1w, qw, kw, vw, ow, ln2w, gate,
  * up, down; then lnfw; then the tied embedding — src/baremetal/graph.c:288-369, trainer.c:86-111).

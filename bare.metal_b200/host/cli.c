@@ -5,14 +5,21 @@
  *   - a file of raw little-endian int32 token ids (any name ending in .bin, .tok or .tokens), or
  *   - the literal lcg:<seed> for the reference's synthetic token stream (bench/train_bench.c:286-290),
  * instead of a text file. Windows are contiguous: sequence b of step k continues where the previous one ended and the
- * target of a position is the next token of the stream (tools/cli.c:762-768). */
+ * target of a position is the next token of the stream (tools/cli.c:762-768).
+ *
+ * Data parallel: started once per GPU with RANK / WORLD_SIZE / LOCAL_RANK in the environment (as torchrun exports them), every
+ * process trains a replica on its own sequences of the global batch — rank r takes sequences r*B .. r*B+B-1 of the world*B
+ * sequences of a step — and gradients are all-reduced over NCCL. The 128-byte NCCL id travels through a file in <output_dir>;
+ * rank 0 prints the step lines (the loss is the mean over all ranks) and writes the checkpoints. */
 #ifndef BAREMETAL_TRAIN
 #define BAREMETAL_TRAIN
 #endif
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
+#include <sys/stat.h>
 #include <time.h>
+#include <unistd.h>
 
 #include "../../include/baremetal.h"
 #include "../../include/baremetal_ext.h"
@@ -35,6 +42,41 @@ static int ends_with(const char* s, const char* suf) {
     return a >= b && strcmp(s + a - b, suf) == 0;
 }
 
+static int env_int(const char* name, int dflt) {
+    const char* v = getenv(name);
+    return (v && v[0]) ? atoi(v) : dflt;
+}
+/* Rank 0 creates the NCCL id and leaves it in <dir>/.bm_nccl_id.<port>; the other ranks wait for a file that is not older than
+ * this process (a file left behind by an earlier run on the same port is ignored). Returns 0 on success. */
+static int exchange_nccl_id(const char* dir, int rank, unsigned char id[128], char* path, size_t path_len) {
+    const char* port = getenv("MASTER_PORT");
+    snprintf(path, path_len, "%s/.bm_nccl_id.%s", dir, (port && port[0]) ? port : "0");
+    if (rank == 0) {
+        char tmp[600];
+        snprintf(tmp, sizeof tmp, "%s.tmp", path);
+        if (bmx_dp_unique_id(id) != 0) return -1;
+        FILE* f = fopen(tmp, "wb");
+        if (!f) return -1;
+        const int ok = fwrite(id, 1, 128, f) == 128;
+        fclose(f);
+        return (ok && rename(tmp, path) == 0) ? 0 : -1;
+    }
+    const time_t started = time(NULL);
+    for (int tries = 0; tries < 6000; ++tries) {   /* up to ten minutes: rank 0 may still be loading the model */
+        struct stat st;
+        if (stat(path, &st) == 0 && st.st_size == 128 && st.st_mtime >= started - 30) {
+            FILE* f = fopen(path, "rb");
+            if (f) {
+                const int ok = fread(id, 1, 128, f) == 128;
+                fclose(f);
+                if (ok) return 0;
+            }
+        }
+        usleep(100000);
+    }
+    return -1;
+}
+
 static int usage(const char* argv0) {
     fprintf(stderr, "Usage: %s train <model_dir|model.bin> <data_file> <output_dir> [options]\n", argv0);
     fprintf(stderr, "  <data_file>         int32 token ids (*.bin, *.tok, *.tokens) or lcg:<seed> for the synthetic stream\n");
@@ -47,6 +89,7 @@ static int usage(const char* argv0) {
     fprintf(stderr, "  --save-every <int>  Save checkpoint every N steps (default: 0 = no save)\n");
     fprintf(stderr, "  --resume <path>     Resume from checkpoint\n");
     fprintf(stderr, "  --precision <bf16|fp32>  Weight precision (default: bf16)\n");
+    fprintf(stderr, "  --save-weights <p>  After training, export the weights: a safetensors directory, or a legacy file if <p> ends in .bin\n");
     fprintf(stderr, "  --lora-rank <int>   must be 0: adapters are outside this build\n");
     return 1;
 }
@@ -56,7 +99,7 @@ int main(int argc, char** argv) {
     const char *model_path = argv[2], *data_file = argv[3], *output_dir = argv[4];
     int max_steps = 100, seq_len = 64, batch_size = 1, grad_accum = 1, save_every = 0, lora_rank = 0;
     float lr = 3e-4f, wd = 0.0f;
-    const char *resume_path = NULL, *prec_str = NULL;
+    const char *resume_path = NULL, *prec_str = NULL, *save_weights = NULL;
     for (int i = 5; i < argc; i++) {
         if (strcmp(argv[i], "--steps") == 0 && i + 1 < argc) max_steps = atoi(argv[++i]);
         else if (strcmp(argv[i], "--seq-len") == 0 && i + 1 < argc) seq_len = atoi(argv[++i]);
@@ -67,6 +110,7 @@ int main(int argc, char** argv) {
         else if (strcmp(argv[i], "--save-every") == 0 && i + 1 < argc) save_every = atoi(argv[++i]);
         else if (strcmp(argv[i], "--resume") == 0 && i + 1 < argc) resume_path = argv[++i];
         else if (strcmp(argv[i], "--precision") == 0 && i + 1 < argc) prec_str = argv[++i];
+        else if (strcmp(argv[i], "--save-weights") == 0 && i + 1 < argc) save_weights = argv[++i];
         else if (strcmp(argv[i], "--lora-rank") == 0 && i + 1 < argc) lora_rank = atoi(argv[++i]);
     }
     if (batch_size < 1) {
@@ -77,7 +121,12 @@ int main(int argc, char** argv) {
         fprintf(stderr, "Error: LoRA adapters are outside this build (--lora-rank must be 0)\n");
         return 1;
     }
-    bm_context_t* ctx = bm_create(BM_DEVICE_CUDA);
+    const int rank = env_int("RANK", 0), world = env_int("WORLD_SIZE", 1);
+    if (world < 1 || rank < 0 || rank >= world) {
+        fprintf(stderr, "Error: RANK=%d is outside WORLD_SIZE=%d\n", rank, world);
+        return 1;
+    }
+    bm_context_t* ctx = bm_create(BM_DEVICE_CUDA);   /* device: BM_CUDA_DEVICE, else LOCAL_RANK, else 0 */
     if (!ctx) {
         fprintf(stderr, "No CUDA (sm_100) device available; this engine has no CPU fallback\n");
         return 1;
@@ -109,7 +158,7 @@ int main(int argc, char** argv) {
     if (strncmp(data_file, "lcg:", 4) == 0) {
         size_t np = 0;
         (void)bmx_model_weight_buffer(model, &np);
-        n_tokens = (long)max_steps * batch_size * seq_len + 1;
+        n_tokens = (long)max_steps * world * batch_size * seq_len + 1;
         tokens = (int*)malloc((size_t)n_tokens * sizeof(int));
         /* vocabulary size: the embedding is the first tensor of the buffer; ask the model info instead of guessing */
         unsigned s = (unsigned)atoi(data_file + 4);
@@ -154,12 +203,23 @@ int main(int argc, char** argv) {
         bm_load_state(trainer, resume_path);
         fprintf(stderr, "[train] resumed from %s\n", resume_path);
     }
+    char id_path[512] = "";
+    if (world > 1) {
+        unsigned char id[128];
+        if (exchange_nccl_id(output_dir, rank, id, id_path, sizeof id_path) != 0 || bmx_trainer_dp_init(trainer, rank, world, id) != 0) {
+            fprintf(stderr, "[train] rank %d: data-parallel set-up failed (NCCL id file %s)\n", rank, id_path);
+            return 1;
+        }
+        fprintf(stderr, "[train] rank %d of %d: data parallel, %d sequences per rank per step\n", rank, world, batch_size);
+    }
     const int batch_tokens = batch_size * seq_len;
     int* inputs = (int*)malloc((size_t)batch_tokens * sizeof(int));
     int* targets = (int*)malloc((size_t)batch_tokens * sizeof(int));
     long pos = 0;
     double total_step_time = 0.0;
     for (int step = 0; step < max_steps; step++) {
+        /* this rank's sequences of the step's global batch: r*B .. r*B+B-1 of world*B contiguous windows */
+        pos = ((long)step * world + rank) * batch_tokens;
         for (int b = 0; b < batch_size; b++)
             for (int i = 0; i < seq_len; i++) {
                 inputs[b * seq_len + i] = tokens[pos % n_tokens];
@@ -170,6 +230,11 @@ int main(int argc, char** argv) {
         const float loss = bm_train_step(trainer, inputs, targets, batch_size, seq_len);
         const double step_ms = now_ms() - t0;
         total_step_time += step_ms;
+        if (loss < 0.0f) {
+            fprintf(stderr, "[train] rank %d: step %d failed\n", rank, step + 1);
+            return 1;
+        }
+        if (rank != 0) continue;   /* replicas are identical: one rank reports and saves (tools/cli.c:777-786) */
         printf("step %d/%d: loss=%.4f  step_ms=%.0f  gpu_mem=%.1fMB  rss=%zuMB\n", step + 1, max_steps, loss, step_ms,
                (double)(bmx_trainer_device_bytes(trainer) / (1024 * 1024)), rss_mb());
         if (save_every > 0 && (step + 1) % save_every == 0) {
@@ -179,8 +244,15 @@ int main(int argc, char** argv) {
             fprintf(stderr, "[train] saved checkpoint to %s\n", path);
         }
     }
-    bm_train_flush(trainer);
-    printf("Avg step time: %.1fms\n", total_step_time / max_steps);
+    bm_train_flush(trainer);   /* collective under data parallel: every rank reaches it after the same number of steps */
+    if (rank == 0) {
+        if (save_weights && bmx_trainer_sync_model(trainer) == 0) {
+            bm_save_weights(model, save_weights);
+            fprintf(stderr, "[train] exported weights to %s\n", save_weights);
+        }
+        printf("Avg step time: %.1fms\n", total_step_time / max_steps);
+        if (id_path[0]) unlink(id_path);
+    }
     free(inputs); free(targets); free(tokens);
     bm_destroy_trainer(trainer);
     bm_destroy_model(model);

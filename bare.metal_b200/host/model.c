@@ -9,7 +9,6 @@
 
 #include "bm_internal.h"
 
-#define BM_CHECKPOINT_MAGIC 20250718 /* src/baremetal/checkpoint.h:11 */
 
 int bm_log_verbose(void) {
     static int v = -1;

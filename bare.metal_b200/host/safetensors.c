@@ -7,7 +7,9 @@
  * {"dtype", "shape", "data_offsets": [begin, end]} (offsets relative to the end of the header), then the raw data. */
 #include <ctype.h>
 #include <math.h>
+#include <errno.h>
 #include <stdio.h>
+#include <sys/stat.h>
 #include <stdlib.h>
 #include <string.h>
 
@@ -263,5 +265,108 @@ int bm_load_safetensors_dir(bm_model_t* m, const char* dir) {
         return -1;
     }
     BM_LOG_INFO("Loaded safetensors directory %s (%zu params)", dir, m->n_parameters);
+    return 0;
+}
+
+/* ---- export -----------------------------------------------------------------------------------------------------------------
+ * bm_save_weights (include/baremetal.h; declared but left unimplemented by the reference, src/baremetal/checkpoint.c:84-88).
+ * A path ending in ".bin" gets the legacy single-file layout (256 x int32 header, then the flat fp32 payload,
+ * src/baremetal/checkpoint.c:19-72); any other path is created as a directory holding config.json and model.safetensors with
+ * the Hugging Face Llama tensor names (src/baremetal/config.c:14-31), F32, tied embedding stored once — what
+ * bm_load_safetensors_dir above and the reference's loader (src/baremetal/checkpoint_st.c:541-637) read back. */
+static int save_bin(const bm_model_t* m, const char* path) {
+    const bm_arch_t* a = &m->arch;
+    int32_t h[256];
+    memset(h, 0, sizeof h);
+    h[0] = BM_CHECKPOINT_MAGIC; h[1] = 1; h[2] = (int32_t)a->precision;
+    h[3] = a->dim; h[4] = a->hidden_dim; h[5] = a->n_layers; h[6] = a->n_heads; h[7] = a->n_kv_heads; h[8] = a->vocab_size;
+    h[9] = a->max_seq_len; h[10] = (int32_t)a->norm; h[11] = (int32_t)a->activation; h[12] = (int32_t)a->pos_enc;
+    h[13] = (int32_t)a->attention; h[14] = a->bias; h[15] = a->weight_tie; h[16] = a->has_qk_norm; h[17] = a->has_ffn_post_norm;
+    h[18] = a->head_dim; h[19] = a->gated_mlp; h[20] = a->embed_scale; h[21] = a->weight_layout; h[22] = a->gemma_norm;
+    h[23] = (int32_t)a->rope_theta;
+    FILE* f = fopen(path, "wb");
+    if (!f) return -1;
+    const int ok = fwrite(h, sizeof(int32_t), 256, f) == 256 && fwrite(m->weight_buffer, sizeof(float), m->n_parameters, f) == m->n_parameters;
+    return (fclose(f) == 0 && ok) ? 0 : -1;
+}
+
+int bm_save_weights_to(const bm_model_t* m, const char* path) {
+    if (!m || !m->weight_buffer || !path) return -1;
+    const size_t plen = strlen(path);
+    if (plen > 4 && strcmp(path + plen - 4, ".bin") == 0) return save_bin(m, path);
+    if (plen > 3000) return -1;
+    if (mkdir(path, 0777) != 0 && errno != EEXIST) {
+        BM_LOG_ERROR("bm_save_weights: cannot create directory %s", path);
+        return -1;
+    }
+    const bm_arch_t* a = &m->arch;
+    char file[4096];
+    snprintf(file, sizeof file, "%s/config.json", path);
+    FILE* f = fopen(file, "w");
+    if (!f) return -1;
+    fprintf(f, "{\n  \"architectures\": [\"LlamaForCausalLM\"],\n  \"model_type\": \"llama\",\n  \"hidden_size\": %d,\n"
+               "  \"intermediate_size\": %d,\n  \"num_hidden_layers\": %d,\n  \"num_attention_heads\": %d,\n"
+               "  \"num_key_value_heads\": %d,\n  \"head_dim\": %d,\n  \"vocab_size\": %d,\n  \"max_position_embeddings\": %d,\n"
+               "  \"rms_norm_eps\": 1e-05,\n  \"rope_theta\": %.9g,\n  \"hidden_act\": \"silu\",\n  \"attention_bias\": false,\n"
+               "  \"mlp_bias\": false,\n  \"tie_word_embeddings\": true,\n  \"torch_dtype\": \"float32\",\n",
+            a->dim, a->hidden_dim, a->n_layers, a->n_heads, a->n_kv_heads, m->head_size, a->vocab_size, a->max_seq_len, (double)a->rope_theta);
+    if (a->rope_scaling == BM_ROPE_LLAMA3)
+        fprintf(f, "  \"rope_scaling\": {\"rope_type\": \"llama3\", \"factor\": %.9g, \"low_freq_factor\": %.9g, \"high_freq_factor\": %.9g, "
+                   "\"original_max_position_embeddings\": %d}\n}\n",
+                (double)a->rope_factor, (double)a->rope_low_freq_factor, (double)a->rope_high_freq_factor, (int)a->rope_original_max);
+    else
+        fprintf(f, "  \"rope_scaling\": null\n}\n");
+    if (fclose(f) != 0) return -1;
+
+    /* header: one entry per tensor in file order, offsets relative to the start of the data section */
+    const size_t D = a->dim, H = a->hidden_dim, V = a->vocab_size, QD = (size_t)a->n_heads * m->head_size, KV = m->kv_dim;
+    struct { const char* suffix; const float* base; size_t rows, cols; } per_layer[9] = {
+        {"input_layernorm.weight", m->ln1w, D, 0},          {"self_attn.q_proj.weight", m->qw, QD, D},
+        {"self_attn.k_proj.weight", m->kw, KV, D},          {"self_attn.v_proj.weight", m->vw, KV, D},
+        {"self_attn.o_proj.weight", m->ow, D, QD},          {"post_attention_layernorm.weight", m->ln2w, D, 0},
+        {"mlp.gate_proj.weight", m->gate, H, D},            {"mlp.up_proj.weight", m->up, H, D},
+        {"mlp.down_proj.weight", m->down, D, H}};
+    const size_t cap = 512 + (size_t)(9 * a->n_layers + 2) * 200;
+    char* hdr = (char*)malloc(cap);
+    if (!hdr) return -1;
+    size_t hl = 0, off = 0;
+    hl += (size_t)snprintf(hdr + hl, cap - hl, "{\"__metadata__\":{\"format\":\"pt\"}");
+#define ENTRY(name_fmt, name_arg, rows_, cols_) do { \
+        const size_t n__ = (cols_) ? (size_t)(rows_) * (cols_) : (size_t)(rows_); \
+        hl += (size_t)snprintf(hdr + hl, cap - hl, ",\"" name_fmt "\":{\"dtype\":\"F32\",\"shape\":[", name_arg); \
+        if (cols_) hl += (size_t)snprintf(hdr + hl, cap - hl, "%zu,%zu", (size_t)(rows_), (size_t)(cols_)); \
+        else hl += (size_t)snprintf(hdr + hl, cap - hl, "%zu", (size_t)(rows_)); \
+        hl += (size_t)snprintf(hdr + hl, cap - hl, "],\"data_offsets\":[%zu,%zu]}", off, off + n__ * 4); \
+        off += n__ * 4; \
+    } while (0)
+    ENTRY("%s", "model.embed_tokens.weight", V, D);
+    for (int l = 0; l < a->n_layers; ++l)
+        for (int k = 0; k < 9; ++k) {
+            char nm[128];
+            snprintf(nm, sizeof nm, "model.layers.%d.%s", l, per_layer[k].suffix);
+            ENTRY("%s", nm, per_layer[k].rows, per_layer[k].cols);
+        }
+    ENTRY("%s", "model.norm.weight", D, 0);
+#undef ENTRY
+    hl += (size_t)snprintf(hdr + hl, cap - hl, "}");
+    while (hl % 8) hdr[hl++] = ' ';   /* the data section starts 8-byte aligned */
+    snprintf(file, sizeof file, "%s/model.safetensors", path);
+    f = fopen(file, "wb");
+    if (!f) { free(hdr); return -1; }
+    const uint64_t hlen = (uint64_t)hl;
+    int ok = fwrite(&hlen, 8, 1, f) == 1 && fwrite(hdr, 1, hl, f) == hl;
+    free(hdr);
+    ok = ok && fwrite(m->embed, 4, V * D, f) == V * D;
+    for (int l = 0; l < a->n_layers && ok; ++l)
+        for (int k = 0; k < 9 && ok; ++k) {
+            const size_t n = per_layer[k].cols ? per_layer[k].rows * per_layer[k].cols : per_layer[k].rows;
+            ok = fwrite(per_layer[k].base + (size_t)l * n, 4, n, f) == n;
+        }
+    ok = ok && fwrite(m->lnfw, 4, D, f) == D;
+    if (fclose(f) != 0 || !ok) {
+        BM_LOG_ERROR("bm_save_weights: write to %s failed", file);
+        return -1;
+    }
+    BM_LOG_INFO("Saved %zu parameters to %s (config.json + model.safetensors)", m->n_parameters, path);
     return 0;
 }

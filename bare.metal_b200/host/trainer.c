@@ -248,10 +248,16 @@ static int forward_and_loss(bm_trainer_t* t, int B, const uint8_t* d_attn_mask, 
     }
     TRY(bmc_rmsnorm_forward(be, dt, t->nf, t->rstdf, t->x_last, wf32(t, p_lnf), M, D, RMS_EPS));
     TRY(bmc_matmul_forward(be, dt, t->logits, V, t->nf, D, wptr(t, p_emb), NULL, 0, M, D, V));
+    if (t->profile) bmc_timer_begin(be, 3);   /* the loss phase is timed by itself, as src/baremetal/trainer.c:400-423 does */
     /* gradient of the per-sequence mean loss: (softmax - onehot) / S (xent_backward, src/kernels/backward.metal:585);
      * the 1 / (number of sequences) factor is applied by AdamW (src/anneal/adamw.metal:38). */
     (void)with_grad;
     TRY(bmc_xent(be, dt, t->logits, V, t->row_loss, t->d_loss, t->d_targets, d_row_weight, B, S, V, 1.0f / (float)S));
+    if (t->profile) {
+        const double loss_ms = bmc_timer_end(be, 3);
+        t->prof_loss_ms += loss_ms;
+        t->prof_forward_ms -= loss_ms;   /* the caller's forward bracket spans the loss kernels too */
+    }
     return 0;
 }
 
@@ -304,7 +310,7 @@ static int backward(bm_trainer_t* t, int B, const uint8_t* d_attn_mask) {
         /* attention block: dres is now dL/d(x1) */
         /* O-projection input gradient; its epilogue also leaves rowsum(dattn * attn) per (row, head) for attention backward */
         const float* delta = NULL;
-        frc = (t->fuse && !d_attn_mask && HD == 64)
+        frc = (t->fuse && HD == 64)
                   ? bmc_matmul_backward_inp_rowdot(be, dt, t->dattn, QD, t->d_delta, t->dres, D, wptr(t, pb + P_O), c->attn, QD, M, QD, D, S, NH)
                   : BMC_ERR_UNFUSED;
         if (frc == BMC_ERR_UNFUSED) TRY(bmc_matmul_backward_inp(be, dt, t->dattn, QD, 0, t->dres, D, wptr(t, pb + P_O), M, QD, D));
@@ -507,9 +513,18 @@ float bm_train_eval_masked(bm_trainer_t* t, const int* inputs, const int* target
     return step_host(t, inputs, targets, attn_mask, loss_mask, B, T, 0);
 }
 
+/* Applies the gradients of a window that has not reached grad_accum_steps micro-steps (bm_train_flush, src/baremetal/trainer.c:535-543).
+ * Under data parallel this is a collective call: the micro-steps so far never exchanged their gradients (only a window's last
+ * micro-step does), so every rank all-reduces the whole gradient here before AdamW. */
 void bm_train_flush(bm_trainer_t* t) {
     if (!t) return;
     if (t->accum_count > 0) {
+        if (t->dp && bm_dp_reduce_all(t->dp) != 0) {
+            BM_LOG_ERROR("bm_train_flush: gradient exchange failed; the partial window is dropped");
+            t->accum_count = 0;
+            t->window_microsteps = 0;
+            return;
+        }
         adamw_apply(t);
         t->accum_count = 0;
         bmc_sync(t->ctx->be);
@@ -666,6 +681,14 @@ int bmx_trainer_set_option(bm_trainer_t* t, const char* key, int value) {
         }
     }
     return known ? 0 : -1;
+}
+/* Copies the fp32 master weights from the device back into the model the trainer was created from, so that bm_save_weights
+ * exports the trained weights. */
+int bmx_trainer_sync_model(bm_trainer_t* t) {
+    if (!t) return -1;
+    for (int i = 0; i < t->n_params; ++i)
+        if (bmc_download(t->ctx->be, t->params[i].host_src, t->d_master + t->params[i].off, t->params[i].n * sizeof(float)) != 0) return -2;
+    return 0;
 }
 long bmx_trainer_launch_count(bm_trainer_t* t) { return t ? bmc_launch_count(t->ctx->be) : 0; }
 size_t bmx_trainer_device_bytes(bm_trainer_t* t) { return t ? bmc_allocated_bytes(t->ctx->be) : 0; }

@@ -40,6 +40,10 @@ int    bmx_trainer_read(bm_trainer_t* t, int what, int i, float* host_out);
  *   "ref_quirks"           all of the above.
  * Set before the first step. Also enabled for every trainer by the environment variable BM_REF_QUIRKS=1. */
 int    bmx_trainer_set_option(bm_trainer_t* t, const char* key, int value);
+/* Copies the trained fp32 master weights from the device back into the bm_model_t the trainer was created from, so that
+ * bm_save_weights(model, path) exports them (a safetensors directory, or the legacy file when path ends in ".bin"). The reference
+ * has no counterpart: its bm_save_weights is unimplemented (src/baremetal/checkpoint.c:84-88). 0 on success. */
+int    bmx_trainer_sync_model(bm_trainer_t* t);
 long   bmx_trainer_launch_count(bm_trainer_t* t);
 size_t bmx_trainer_device_bytes(bm_trainer_t* t);
 
@@ -60,6 +64,9 @@ float  bmx_timer_end(bm_context_t* ctx, int slot);
  * weights without going through a file. *n_out receives the element count. */
 float* bmx_model_weight_buffer(bm_model_t* model, size_t* n_out);
 int    bmx_model_vocab_size(const bm_model_t* model);
+/* One field of the model's bm_arch_t by name ("dim", "n_layers", "rope_theta", "rope_scaling", "rope_factor", ...), -1 for an unknown
+ * name: what a loader made of a checkpoint's own description (config.json or the .bin header). */
+double bmx_model_arch_field(const bm_model_t* model, const char* name);
 /* per-launch timing of the tensor-core GEMM (see bmc_gemm_timing in bm_cuda_backend.h) */
 int    bmx_gemm_timing(bm_context_t* ctx, int enable);
 int    bmx_gemm_timing_collect(bm_context_t* ctx, double* out3);

@@ -127,3 +127,35 @@ def test_backward_with_row_sums_supplied_and_rope_backward_folded_in(be, S, B):
         assert oc.rel_err(g[b, :, :QD].reshape(S, NH, HD), rq) < 1e-2
         assert oc.rel_err(g[b, :, QD:QD + KV].reshape(S, NKV, HD), rk) < 1e-2
     assert oc.rel_err(g[..., QD + KV:], unrotated[..., QD + KV:]) < 1e-3
+
+
+@pytest.mark.parametrize("S,B", [(300, 2), (1024, 1)])
+def test_padding_mask_on_the_tensor_core_kernels(be, S, B):
+    """A position whose mask byte is 0 is neither key nor query (attention_forward_seq_masked, src/kernels/forward.metal:1853;
+    attention_backward_masked, src/kernels/backward.metal:738): the bf16 tensor-core kernels against the exact fp32 kernel, which
+    the masked training-step tests tie to the reference. Padding at the end of one sequence, a hole inside another."""
+    rng = np.random.default_rng(S)
+    qkv = bf16_round(rng.standard_normal((B * S, LD)).astype(np.float32))
+    go = bf16_round(rng.standard_normal((B * S, QD)).astype(np.float32))
+    mask = np.ones((B, S), np.uint8)
+    mask[0, S - 70:] = 0
+    mask[B - 1, 40:170] = 0
+    mask[B - 1, 5] = 0
+    dm = be.put(mask.reshape(-1))
+    res = {}
+    for dtype in (BMC_BF16, BMC_F32):
+        es = 2 if dtype == BMC_BF16 else 4
+        d, dgo = be.put(qkv, dtype), be.put(go, dtype)
+        out, lse, dg = be.zeros(B * S * QD, dtype), be.zeros(B * NH * S), be.zeros(B * S * LD, dtype)
+        be.ok("attention_forward", dtype, Ptr(out), QD, Ptr(lse), Ptr(d), LD, Ptr(d, QD * es), Ptr(d, (QD + KV) * es), LD, Ptr(dm), B, S, NH, NKV, HD, float(SCALE))
+        be.ok("attention_backward", dtype, Ptr(dg), LD, Ptr(dg, QD * es), Ptr(dg, (QD + KV) * es), LD, Ptr(dgo), QD, Ptr(out), Ptr(lse), Ptr(d), LD,
+              Ptr(d, QD * es), Ptr(d, (QD + KV) * es), LD, Ptr(dm), B, S, NH, NKV, HD, float(SCALE))
+        res[dtype] = (be.get(out, (B, S, QD), dtype), be.get(dg, (B, S, LD), dtype))
+    (o16, g16), (o32, g32) = res[BMC_BF16], res[BMC_F32]
+    off = mask == 0
+    assert not o16[off].any() and not g16[off][:, :QD].any()            # masked queries: zero output, zero dQ
+    assert not g16[off][:, QD:].any()                                   # masked keys: zero dK and dV
+    close(o16, o32, "O")
+    close(g16[..., :QD], g32[..., :QD], "dQ")
+    close(g16[..., QD:QD + KV], g32[..., QD:QD + KV], "dK")
+    close(g16[..., QD + KV:], g32[..., QD + KV:], "dV")

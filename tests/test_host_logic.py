@@ -51,6 +51,82 @@ def test_bin_checkpoint_round_trip_through_the_host_layer(product, tmp_path):
     lib.bm_destroy_model(model)
 
 
+def test_save_weights_round_trip_safetensors_and_bin(product, tmp_path):
+    """bm_save_weights writes a Hugging Face safetensors directory (or the legacy .bin): an independent reader sees the Llama tensor
+    names, shapes and values, and loading the export back gives the same buffer bit for bit."""
+    from safetensors.numpy import load_file
+    lib = product
+    lib.bm_save_weights.argtypes = [C.c_void_p, C.c_char_p]
+    a = bmapi.make_arch("gqa")
+    w = bmapi.make_weights(a, seed=11)
+    src = str(tmp_path / "src.bin")
+    bmapi.write_bin_checkpoint(src, a, w)
+    model = lib.bm_create_model(None, C.byref(a))
+    lib.bm_load_weights(model, src.encode())
+    out_dir, out_bin = str(tmp_path / "export"), str(tmp_path / "export.bin")
+    lib.bm_save_weights(model, out_dir.encode())
+    lib.bm_save_weights(model, out_bin.encode())
+    assert open(out_bin, "rb").read() == open(src, "rb").read()
+    t = load_file(os.path.join(out_dir, "model.safetensors"))
+    assert len(t) == 9 * a.n_layers + 2 and "lm_head.weight" not in t
+    assert np.array_equal(t["model.embed_tokens.weight"], w["embed"]) and np.array_equal(t["model.norm.weight"], w["lnfw"])
+    for l in range(a.n_layers):
+        for name, key in (("input_layernorm", "ln1w"), ("self_attn.q_proj", "qw"), ("self_attn.k_proj", "kw"), ("self_attn.v_proj", "vw"),
+                          ("self_attn.o_proj", "ow"), ("post_attention_layernorm", "ln2w"), ("mlp.gate_proj", "gate"), ("mlp.up_proj", "up"),
+                          ("mlp.down_proj", "down")):
+            assert np.array_equal(t[f"model.layers.{l}.{name}.weight"], w[key][l]), (l, name)
+    import json
+    cfg = json.load(open(os.path.join(out_dir, "config.json")))
+    assert cfg["hidden_size"] == a.dim and cfg["num_key_value_heads"] == a.n_kv_heads and cfg["tie_word_embeddings"] is True
+    assert cfg["rope_theta"] == 100000.0 and cfg["rope_scaling"] is None
+    back = lib.bm_create_model(None, C.byref(bmapi.make_arch("tiny")))   # the loader re-creates the buffers from config.json
+    lib.bm_load_weights(back, out_dir.encode())
+    n = C.c_size_t()
+    flat = np.ctypeslib.as_array(lib.bmx_model_weight_buffer(back, C.byref(n)), (lib.bm_get_num_parameters(back),))
+    assert np.array_equal(flat, np.concatenate([w[k].ravel() for k, _ in bmapi.weight_shapes(a)]))
+    lib.bm_destroy_model(model)
+    lib.bm_destroy_model(back)
+
+
+def test_config_json_rope_scaling_is_parsed_or_refused(product, tmp_path):
+    """rope_scaling of type llama3 reaches the architecture (src/baremetal/config.c:192-211); any other rule is refused, because the
+    engine would otherwise rotate by the wrong frequencies without saying so; a key inside a nested object never shadows a
+    top-level one."""
+    from safetensors.numpy import save_file
+    import json
+    lib = product
+    a = bmapi.make_arch("tiny")
+    w = bmapi.make_weights(a)
+    names = {"model.embed_tokens.weight": w["embed"], "model.norm.weight": w["lnfw"]}
+    for l in range(a.n_layers):
+        for name, key in (("input_layernorm", "ln1w"), ("self_attn.q_proj", "qw"), ("self_attn.k_proj", "kw"), ("self_attn.v_proj", "vw"),
+                          ("self_attn.o_proj", "ow"), ("post_attention_layernorm", "ln2w"), ("mlp.gate_proj", "gate"), ("mlp.up_proj", "up"),
+                          ("mlp.down_proj", "down")):
+            names[f"model.layers.{l}.{name}.weight"] = np.ascontiguousarray(w[key][l])
+    base = {"model_type": "llama", "text_config": {"hidden_size": 9999}, "hidden_size": a.dim, "intermediate_size": a.hidden_dim,
+            "num_hidden_layers": a.n_layers, "num_attention_heads": a.n_heads, "num_key_value_heads": a.n_kv_heads,
+            "vocab_size": a.vocab_size, "max_position_embeddings": 4096, "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+            "tie_word_embeddings": True}
+    lib.bmx_model_arch_field.restype = C.c_double
+    lib.bmx_model_arch_field.argtypes = [C.c_void_p, C.c_char_p]
+    for scaling, ok in (({"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                          "original_max_position_embeddings": 8192}, True), ({"type": "yarn", "factor": 4.0}, False), (None, True)):
+        d = tmp_path / f"m_{'none' if scaling is None else scaling.get('rope_type', scaling.get('type'))}"
+        d.mkdir()
+        json.dump(dict(base, rope_scaling=scaling), open(d / "config.json", "w"))
+        save_file(names, str(d / "model.safetensors"))
+        m = lib.bm_create_model(None, C.byref(bmapi.make_arch("tiny")))
+        lib.bm_load_weights(m, str(d).encode())
+        loaded = lib.bm_get_num_parameters(m) > 0 and abs(lib.bmx_model_arch_field(m, b"rope_theta") - 500000.0) < 1
+        assert loaded == ok, scaling
+        if ok:
+            assert lib.bmx_model_arch_field(m, b"dim") == a.dim   # not the 9999 of the nested object
+            assert lib.bmx_model_arch_field(m, b"rope_scaling") == (1 if scaling else 0)
+            if scaling:
+                assert lib.bmx_model_arch_field(m, b"rope_factor") == 32.0 and lib.bmx_model_arch_field(m, b"rope_original_max") == 8192.0
+        lib.bm_destroy_model(m)
+
+
 def test_unsupported_architectures_are_rejected(product):
     lib = product
     for field in ("bias", "has_qk_norm", "has_ffn_post_norm", "gemma_norm", "embed_scale"):
