@@ -98,9 +98,6 @@ __device__ __forceinline__ float ex2_approx(float x) {
 }
 
 struct FwdArgs {
-#ifdef BMB_TRACE
-    long long* trace;
-#endif
     bf16* out;
     int ldo;
     float* lse;
@@ -110,11 +107,6 @@ struct FwdArgs {
     int* err;
 };
 
-#ifdef BMB_TRACE
-#define FTRACE(slot, idx) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (idx) < 32) p.trace[(slot) * 32 + (idx)] = clock64(); } while (0)
-#else
-#define FTRACE(slot, idx) do { } while (0)
-#endif
 
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -227,7 +219,6 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                     }
                     tc_fence_after_sync();
                     issue_qk(x, j + 1);
-                    if (x == 0) FTRACE(0, j);
                 }
                 for (int x = 0; x < 2 && ok; ++x) {
                     const int n_this = x ? n_b : n_a;
@@ -235,7 +226,6 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                     if (!mbar_wait(&bars.p_ready[x], j & 1, abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
                     issue_pv(x, j);
-                    if (x == 0) FTRACE(1, j);
                 }
                 if (ok) umma_commit(&bars.kv_empty[j % FWD_KV_STAGES]);  // every UMMA that reads this stage has been issued
             }
@@ -261,7 +251,6 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after_sync();
-            if (quarter == 0 && lane == 0) FTRACE(2 + 6 * x, j);
             uint32_t v[4][32];
 #pragma unroll
             for (int ch = 0; ch < 4; ++ch) tmem_ld_32x32(s_addr + ch * 32, v[ch]);
@@ -270,7 +259,6 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars.s_free[x]);
-            if (quarter == 0 && lane == 0) FTRACE(3 + 6 * x, j);
             const int k0 = j * FK;
             // padding mask (attention_forward_seq_masked, src/kernels/forward.metal:1853): one word of key bits per 32 columns
             uint32_t mw[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
@@ -314,7 +302,6 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 need = true;
             }
             const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-            if (quarter == 0 && lane == 0) FTRACE(4 + 6 * x, j);
             // probabilities, packed to bf16 pairs (keys 2c, 2c+1 -> column c of the P block in tensor memory); four independent sum chains
             uint32_t pk[2][32];
             float ls[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -332,7 +319,6 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 }
             const float lsum = ((ls[0] + ls[1]) + (ls[2] + ls[3])) + ((ls[4] + ls[5]) + (ls[6] + ls[7]));
             l_run = l_run * corr + lsum;
-            if (quarter == 0 && lane == 0) FTRACE(5 + 6 * x, j);
             if (j > 0) {
                 // P_X(j-1) must have been consumed (and O_X updated) before P is overwritten / O rescaled
                 ok = mbar_wait(&bars.pv_done[x], (j - 1) & 1, abort_flag);
@@ -351,7 +337,6 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                     }
                 }
             }
-            if (quarter == 0 && lane == 0) FTRACE(6 + 6 * x, j);
             // P row -> tensor memory, where P V reads it as its A operand (this thread's TMEM lane = its query row)
             tmem_st_32x32(p_addr, pk[0]);
             tmem_st_32x32(p_addr + 32, pk[1]);
@@ -359,7 +344,6 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars.p_ready[x]);
-            if (quarter == 0 && lane == 0) FTRACE(7 + 6 * x, j);
         }
         if (ok && n_mine > 0) {
             ok = mbar_wait(&bars.pv_done[x], (n_mine - 1) & 1, abort_flag);
@@ -433,9 +417,6 @@ struct __align__(8) BwdBars {
 };
 
 struct BwdArgs {
-#ifdef BMB_TRACE
-    long long* trace;
-#endif
     float* dq_acc;   // [B*S, NH*64] fp32, zero on entry
     bf16 *gk, *gv;
     int ldgkv;
@@ -447,11 +428,6 @@ struct BwdArgs {
     int* err;
 };
 
-#ifdef BMB_TRACE
-#define BTRACE(slot, idx) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (idx) < 32) p.trace[(slot) * 32 + (idx)] = clock64(); } while (0)
-#else
-#define BTRACE(slot, idx) do { } while (0)
-#endif
 __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
@@ -551,7 +527,6 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             for (int it = 0; it + 1 < total && ok; ++it) {
                 const int nx = (it + 1) & 1;
                 const uint64_t sn = (uint64_t)(nx * (Q_BYTES >> 4));
-                BTRACE(0, it);
                 if (!mbar_wait(&bars.sdp_free, it & 1, abort_flag)) { ok = false; break; }
                 if (!mbar_wait(&bars.q_full[nx], ((it + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
                 tc_fence_after_sync();
@@ -562,7 +537,6 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 #pragma unroll
                 for (int k = 0; k < FHD / 16; ++k) umma_bf16_ss(tmem + BT_DP, g_km0 + sn + 2 * k, v_km + 2 * k, id_s, k > 0 ? 1u : 0u);
                 umma_commit(&bars.sdp_full);
-                BTRACE(1, it);
             }
         }
     } else if (warp == 18) {
@@ -590,7 +564,6 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 const uint64_t po = (uint64_t)(pb * (P_BYTES >> 4));
                 if (!mbar_wait(&bars.pds_ready[pb], (it >> 1) & 1, abort_flag)) { ok = false; break; }
                 tc_fence_after_sync();
-                BTRACE(2, it);
                 // The refill of a stage (over a thousand clocks) is what S / dP of the tile after next wait for, so each half is
                 // released as early as its last reader allows: Q after dK, dO after dV; dQ reads neither.
 #pragma unroll
@@ -604,7 +577,6 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                     umma_bf16_ss(tmem + BT_DQ + pb * FHD, d_km + po + (uint64_t)((k >> 2) * ((FQ * 128) >> 4) + (k & 3) * 2), k_mn + 128 * k, id_q,
                                  k > 0 ? 1u : 0u);
                 umma_commit(&bars.dq_full[pb]);
-                BTRACE(3, it);
             }
         }
     } else {
@@ -677,7 +649,6 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after_sync();
-            if (cw == 0 && lane == 0) BTRACE(4, it);
             uint32_t sv[32], dv[32];
             tmem_ld_32x32(lane_addr + BT_S + cg * 32, sv);
             tmem_ld_32x32(lane_addr + BT_DP + cg * 32, dv);
@@ -686,7 +657,6 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars.sdp_free);
-            if (cw == 0 && lane == 0) BTRACE(5, it);
             const bool diag = (mb == nblk) || (n0 + FK > p.S) || kw != 0xffffffffu;
             const float dlt_s = -dlt * p.scale;
             uint32_t pp[16], dd[16];
@@ -707,7 +677,6 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 pp[i >> 1] = *reinterpret_cast<uint32_t*>(&hp);
                 dd[i >> 1] = *reinterpret_cast<uint32_t*>(&hd);
             }
-            if (cw == 0 && lane == 0) BTRACE(6, it);
             const int pb = it & 1;
             if (it >= 2) {
                 // the second-stage UMMAs of tile it-2 have read this P/dS buffer
@@ -715,7 +684,6 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
             }
-            if (cw == 0 && lane == 0) BTRACE(7, it);
             // rows of P and dS: key half = cg / 2, 16-byte chunks (cg & 1) * 4 .. +3 of the 128-byte row
             {
                 const uint32_t prow = smem_u32(sP + pb * P_BYTES + (cg >> 1) * (FQ * 128) + r * 128);
@@ -731,7 +699,6 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars.pds_ready[pb]);
-            if (cw == 0 && lane == 0) BTRACE(8, it);
             if (it > 0) {
                 // the previous tile's dQ (the other TMEM buffer) goes into the fp32 scratch while the tensor core works on this tile
                 ok = mbar_wait(&bars.dq_full[pb ^ 1], ((it - 1) >> 1) & 1, abort_flag);
@@ -744,7 +711,6 @@ flash_bwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             }
             prev_h = h;
             prev_q0 = q0;
-            if (cw == 0 && lane == 0) BTRACE(9, it);
         }
         if (ok && total > 0) {
             ok = mbar_wait(&bars.dq_full[(total - 1) & 1], ((total - 1) >> 1) & 1, abort_flag);
@@ -972,35 +938,9 @@ int flash_attention_forward_umma(bf16* out, int ldo, float* lse, const bf16* q, 
     if (!rc) rc = make_rows_map(&tk, k, (uint64_t)NKV * HD, rows, ldkv, FK);
     if (!rc) rc = make_rows_map(&tv, v, (uint64_t)NKV * HD, rows, ldkv, FK);
     if (rc) return rc;
-#ifdef BMB_TRACE
-    long long* trace = nullptr;
-    cudaMalloc(&trace, 14 * 32 * sizeof(long long));
-    cudaMemset(trace, 0, 14 * 32 * sizeof(long long));
-    FwdArgs a{trace, out, ldo, lse, keymask, S, NH, NKV, scale, err_flag};
-#else
     FwdArgs a{out, ldo, lse, keymask, S, NH, NKV, scale, err_flag};
-#endif
     dim3 grid((S + 2 * FQ - 1) / (2 * FQ), NH, B);
     flash_fwd_umma_kernel<<<grid, FWD_THREADS, FWD_DYN_SMEM, st>>>(tq, tk, tv, a);
-#ifdef BMB_TRACE
-    {
-        static int printed = 0;
-        cudaStreamSynchronize(st);
-        long long h[14 * 32];
-        cudaMemcpy(h, trace, sizeof h, cudaMemcpyDeviceToHost);
-        cudaFree(trace);
-        if (printed++ < 1) {
-            const char* names[14] = {"mma:qk_next", "mma:pv", "A:s_full", "A:ld", "A:max", "A:exp", "A:pv_done", "A:p_ready",
-                                     "B:s_full", "B:ld", "B:max", "B:exp", "B:pv_done", "B:p_ready"};
-            const long long t0 = h[2 * 32];
-            for (int j = 0; j < 14; ++j) {
-                fprintf(stderr, "fwd j=%2d", j);
-                for (int sl = 0; sl < 14; ++sl) fprintf(stderr, " %s=%lld", names[sl], h[sl * 32 + j] ? h[sl * 32 + j] - t0 : -1);
-                fprintf(stderr, "\n");
-            }
-        }
-    }
-#endif
     const cudaError_t le = cudaGetLastError();
     if (le != cudaSuccess) {
         fprintf(stderr, "flash_attention_forward_umma: launch failed: %s\n", cudaGetErrorString(le));
@@ -1038,35 +978,9 @@ int flash_attention_backward_umma(bf16* gq, int ldgq, bf16* gk, bf16* gv, int ld
         const long groups = (long)rows * NH;   // eight lanes each
         flash_delta_umma_kernel<<<(int)((groups * 8 + 255) / 256), 256, 0, st>>>(delta_own, gout, out, ldo, B, S, NH);
     }
-#ifdef BMB_TRACE
-    long long* trace = nullptr;
-    cudaMalloc(&trace, 10 * 32 * sizeof(long long));
-    cudaMemset(trace, 0, 10 * 32 * sizeof(long long));
-    BwdArgs a{trace, dq_acc, gk, gv, ldgkv, lse, delta, rope_cs, keymask, S, NH, NKV, scale, err_flag};
-#else
     BwdArgs a{dq_acc, gk, gv, ldgkv, lse, delta, rope_cs, keymask, S, NH, NKV, scale, err_flag};
-#endif
     dim3 grid((S + FK - 1) / FK, NKV, B);
     flash_bwd_umma_kernel<<<grid, BWD_THREADS, BWD_DYN_SMEM, st>>>(tq, tk, tv, tg, a);
-#ifdef BMB_TRACE
-    {
-        static int printed = 0;
-        cudaStreamSynchronize(st);
-        long long h[10 * 32];
-        cudaMemcpy(h, trace, sizeof h, cudaMemcpyDeviceToHost);
-        cudaFree(trace);
-        if (printed++ < 1) {
-            const char* names[10] = {"mma:q_full", "mma:sdp_issued", "mma:pds_ready", "mma:st2_issued", "cw:sdp_full", "cw:ld_done", "cw:math_done",
-                                     "cw:dq_ld_done", "cw:arrived", "cw:red_done"};
-            const long long t0 = h[0];
-            for (int j = 0; j < 10; ++j) {
-                fprintf(stderr, "it=%2d", j);
-                for (int sl = 0; sl < 10; ++sl) fprintf(stderr, " %s=%lld", names[sl], h[sl * 32 + j] ? h[sl * 32 + j] - t0 : -1);
-                fprintf(stderr, "\n");
-            }
-        }
-    }
-#endif
     const cudaError_t le = cudaGetLastError();
     if (le != cudaSuccess) {
         fprintf(stderr, "flash_attention_backward_umma: launch failed: %s\n", cudaGetErrorString(le));

@@ -17,6 +17,7 @@
 #include "kernels.cuh"
 
 using namespace bmb;
+namespace bmb { int wait_probe_launch(int* err, cudaStream_t st); }
 
 struct bmc_ctx_s {
     int device;
@@ -691,5 +692,9 @@ int bmc_graph_launch(bmc_ctx_t* ctx) {
     return cudaGraphLaunch(ctx->graph_execs[k], ctx->stream) == cudaSuccess ? 0 : -2;
 }
 int bmc_gemm_timing_enabled(bmc_ctx_t* ctx) { return ctx && ctx->gemm_timing ? 1 : 0; }
+int bmc_selftest_bounded_wait(bmc_ctx_t* ctx) {
+    BMC_CHECK_CTX(ctx);
+    return note(ctx, wait_probe_launch(ctx->d_err, ctx->stream));
+}
 
 }  // extern "C"

@@ -54,6 +54,10 @@ int        bmc_copy(bmc_ctx_t* ctx, void* d_dst, const void* d_src, size_t bytes
 int        bmc_sync(bmc_ctx_t* ctx);                          /* waits for the compute stream; returns bmc_status() */
 /* Non-zero when a kernel reported a failed bounded wait or a CUDA call failed since the last call. */
 int        bmc_status(bmc_ctx_t* ctx);
+/* Self-test of the bounded waits: enqueues a one-CTA kernel that waits (2 ms limit) on a barrier nothing arrives at. The kernel gives
+ * up, leaves code 1999 in the error word and returns; the next bmc_status() / bmc_sync() reports 1999 once and the context stays
+ * usable. No counterpart in the reference (its Metal kernels have no device-side waits). */
+int        bmc_selftest_bounded_wait(bmc_ctx_t* ctx);
 void*      bmc_stream(bmc_ctx_t* ctx);                        /* the cudaStream_t work is enqueued on */
 /* Kernel launches issued through this context since creation (all entry points). */
 long       bmc_launch_count(bmc_ctx_t* ctx);

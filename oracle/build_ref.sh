@@ -8,10 +8,10 @@
 # src/kernels/forward.metal:1810 and ATTN_MAXS in src/kernels/backward.metal:664, both 256) are raised
 # so the same kernels can serve as the oracle for sequences longer than 256 tokens.
 #
-# usage: oracle/build_ref.sh [reference_dir]      (default: $BM_REFERENCE, else the checkout location built into the line below)
+# usage: oracle/build_ref.sh [reference_dir]      (default: $BM_REFERENCE, else a directory named "reference" beside this repository)
 set -euo pipefail
 HERE="$(cd "$(dirname "$0")" && pwd)"
-REF="${1:-${BM_REFERENCE:-/root/reference}}"
+REF="${1:-${BM_REFERENCE:-$HERE/../../reference}}"
 OUT="$HERE/_ref"
 MAXS="${BM_REF_ATTN_MAXS:-8192}"
 if [ ! -f "$REF/src/baremetal/trainer.c" ]; then

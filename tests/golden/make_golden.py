@@ -18,8 +18,9 @@ and the 135M-parameter single-step fp32 configuration (B=1, S=64, AdamW lr 3e-4,
 Part 2b (`--only TAG[,TAG...]` regenerates single files of parts 2, 2b and 3 by their tag) — the configurations that are
 benchmarked: ref_train_step_360m_{f32,bf16}_b2.npz (SmolLM2-360M, two sequences of 128 tokens, two optimizer steps) and
 ref_train_curve_135m_{f32,bf16}.npz (SmolLM2-135M, 50 optimizer steps on two sequences of 128 tokens each: the loss curve
-and sampled final weights), ref_decode_360m_f32_q8.npz (SmolLM2-360M with Q8 layers: a 64-token prompt and 16 greedy tokens,
-sampled logits only).
+and sampled final weights), ref_decode_360m_{f32,bf16}_q8.npz (SmolLM2-360M with Q8 layers: a 64-token prompt and 16 greedy tokens,
+sampled logits only), oracle_attention_s8192_group.npz (the isolated-attention configuration at 8192 tokens, one KV group, from the
+plain-C oracle).
 
 Part 3 (`--only-decode` regenerates just this part) — ref_quantize_q8.npz: the reference's Q8 block quantiser on seeded
 inputs with its edge cases; ref_decode_*.npz: logits of the reference inference session after every prefix of a seeded
@@ -170,6 +171,35 @@ def ref_decode_sampled_case(ref, tag, arch_name, precision, quant, n_prompt, n_n
     print(f"ref_decode_{tag}.npz: greedy {greedy} min margin {min(margin):.3g}")
 
 
+def c4_group_inputs(S, seed=8192):
+    """Q (3 query heads), K, V (their one KV head) and dO for one KV group of the isolated-attention configuration, N(0,1) by seed,
+    rounded to bf16. Shared by the generator below and by tests/test_gpu_attention_c4.py."""
+    from bmcapi import bf16_round
+    rng = np.random.default_rng(seed)
+    q = bf16_round(rng.standard_normal((S, 3, 64)).astype(np.float32))
+    k = bf16_round(rng.standard_normal((S, 1, 64)).astype(np.float32))
+    v = bf16_round(rng.standard_normal((S, 1, 64)).astype(np.float32))
+    go = bf16_round(rng.standard_normal((S, 3, 64)).astype(np.float32))
+    return q, k, v, go
+
+
+def c4_group_case(S=8192, every=32):
+    """Isolated causal attention at S = 8192 for ONE KV group (one KV head and the three query heads that share it): O, dQ, dK, dV
+    from the plain-C restatement of attention_forward_seq / attention_backward (src/kernels/forward.metal:1811,
+    src/kernels/backward.metal:665, oracle/bm_oracle.c, pinned to the reference's own attention goldens by tests/test_oracle_pins.py).
+    About 80 GFLOP of scalar work; every 32nd row and the tensor norms are stored."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import portk
+    q, k, v, go = c4_group_inputs(S)
+    o = portk.attention_forward(q, k, v, 0.125)
+    gq, gk, gv = portk.attention_backward(go, q, k, v, 0.125)
+    rows = np.arange(0, S, every)
+    np.savez_compressed(os.path.join(OUT, f"oracle_attention_s{S}_group.npz"), S=S, rows=rows, checksum=float(np.float64(q.sum()) + k.sum() + v.sum() + go.sum()),
+                        o=o[rows], gq=gq[rows], gk=gk[rows], gv=gv[rows],
+                        norms=np.array([np.linalg.norm(t.astype(np.float64)) for t in (o, gq, gk, gv)]))
+    print(f"oracle_attention_s{S}_group.npz: {rows.size} rows")
+
+
 def q8_inputs():
     """Seeded quantiser inputs with the edge cases of the scheme: an all-zero block, a block whose extreme is negative,
     exact .5 ties after scaling, a huge dynamic range, denormal-sized values."""
@@ -221,7 +251,7 @@ def ref_decode_case(ref, tag, arch_name, precision, quant, n_prompt, n_new):
 
 def main():
     args = [a for a in sys.argv[1:] if not a.startswith("--")]
-    ref_dir = args[0] if args else os.environ.get("BM_REFERENCE", "/root/reference")
+    ref_dir = args[0] if args else (os.environ.get("BM_REFERENCE") or os.path.join(os.path.dirname(ROOT), "reference"))
     ref = oc.load_reference()
     if ref is None:
         raise SystemExit("oracle/_ref/libbm_ref.so missing: run oracle/build_ref.sh first")
@@ -236,6 +266,7 @@ def main():
         "curve_135m_f32": lambda: ref_curve_case(ref, "135m_f32", "smollm2-135m", 2, 128, F32, 50),
         "decode_360m_f32_q8": lambda: ref_decode_sampled_case(ref, "360m_f32_q8", "smollm2-360m", F32, 8, 64, 16),
         "decode_360m_bf16_q8": lambda: ref_decode_sampled_case(ref, "360m_bf16_q8", "smollm2-360m", BF16, 8, 64, 16),
+        "c4_s8192_group": lambda: c4_group_case(8192),
     }
     for arg in sys.argv[1:]:
         if arg.startswith("--only="):

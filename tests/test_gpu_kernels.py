@@ -392,7 +392,15 @@ def test_seq_prefix_accumulate(be):
 
 
 def test_bounded_wait_reports_instead_of_hanging(be):
-    """A GEMM on a context whose stream is healthy leaves the status word at zero: no bounded wait ran out."""
-    x, w = be.put(rnd(128, 64), BMC_BF16), be.put(rnd(64, 64), BMC_BF16)
-    be.ok("matmul_forward", BMC_BF16, Ptr(be.zeros(128 * 64, BMC_BF16)), 64, Ptr(x), 64, Ptr(w), None, 0, 128, 64, 64)
+    """A wait that cannot complete ends with a status code, not with a hang: bmc_selftest_bounded_wait runs the kernels' own wait
+    primitive (2 ms limit in that translation unit) on a barrier nothing arrives at. The status is reported once, then cleared, and
+    the context goes on to run a tensor-core GEMM whose result is right and whose own waits all completed (status 0)."""
+    assert be.lib.bmc_status(be.ctx) == 0
+    assert be.call("selftest_bounded_wait") == 0
+    assert be.lib.bmc_sync(be.ctx) == 1999          # the wait ran out and said so
+    assert be.lib.bmc_status(be.ctx) == 0           # reported once
+    x, w = rnd(128, 64, dtype=BMC_BF16), rnd(64, 64, dtype=BMC_BF16)
+    out = be.zeros(128 * 64, BMC_BF16)
+    be.ok("matmul_forward", BMC_BF16, Ptr(out), 64, Ptr(be.put(x, BMC_BF16)), 64, Ptr(be.put(w, BMC_BF16)), None, 0, 128, 64, 64)
+    check(be.get(out, (128, 64), BMC_BF16), portk.matmul_forward(x, w), BMC_BF16)
     assert be.lib.bmc_status(be.ctx) == 0

@@ -4,7 +4,7 @@ Some embedders of this library cannot let it call cudaMalloc — they have given
 or they run loops in which the implicit device-wide synchronisation of cudaMalloc/cudaFree is not acceptable. For them the
 backend has one entry point whose scratch is a fixed array inside the library. This test calls it through the C ABI twice in a
 row (different shapes, so the second call meets the first call's leftovers in the shared scratch) and requires the same
-gradients as bmc_rmsnorm_backward, within the tolerances the other kernel tests use; it also checks that a row wider than
+gradients as bmc_rmsnorm_backward and as the CPU oracle, within the tolerances the other kernel tests use; it also checks that a row wider than
 the built-in scratch is refused. The file name sorts last so that a run that stops at the first failure has already
 executed every other test."""
 import ctypes as C
@@ -13,6 +13,7 @@ import numpy as np
 import pytest
 
 import oracle_check as oc
+import portk
 from bmcapi import BMC_BF16, BMC_F32, Backend, Ptr, bf16_round
 
 pytestmark = pytest.mark.gpu
@@ -48,6 +49,10 @@ def _one_case(be, rng, dtype, N, C_, accumulate, row0):
     ga, gb = be.get(gw_a, (C_,)), be.get(gw_b, (C_,))
     assert oc.rel_err(gb, ga) <= rel
     assert np.isfinite(b).all() and np.isfinite(gb).all()
+    # and against the CPU oracle, like the regular entry point's own test: gx accumulates, the gain gradient covers rows [row0, N)
+    ref_gw = portk.rmsnorm_backward_w(go[row0:], x[row0:]) + (gw0 if accumulate else 0.0)
+    assert oc.rel_err(b, portk.rmsnorm_backward_x(go, w, x, gx0)) <= (1e-5 if dtype == BMC_F32 else 2e-2)
+    assert oc.rel_err(gb, ref_gw) <= (1e-5 if dtype == BMC_F32 else 2e-2)
 
 
 def test_static_scratch_entry_point_matches_regular_one_twice_in_a_row(product):
