@@ -973,11 +973,11 @@ int flash_attention_backward_umma(bf16* gq, int ldgq, bf16* gk, bf16* gv, int ld
     if (!rc) rc = make_rows_map(&tv, v, (uint64_t)NKV * HD, rows, ldkv, FK);
     if (!rc) rc = make_rows_map(&tg, gout, (uint64_t)NH * HD, rows, ldo, FQ);
     if (rc) return rc;
-    cudaMemsetAsync(dq_acc, 0, rows * QD * sizeof(float), st);
     if (!delta_in) {
         const long groups = (long)rows * NH;   // eight lanes each
         flash_delta_umma_kernel<<<(int)((groups * 8 + 255) / 256), 256, 0, st>>>(delta_own, gout, out, ldo, B, S, NH);
     }
+    cudaMemsetAsync(dq_acc, 0, rows * QD * sizeof(float), st);
     BwdArgs a{dq_acc, gk, gv, ldgkv, lse, delta, rope_cs, keymask, S, NH, NKV, scale, err_flag};
     dim3 grid((S + FK - 1) / FK, NKV, B);
     flash_bwd_umma_kernel<<<grid, BWD_THREADS, BWD_DYN_SMEM, st>>>(tq, tk, tv, tg, a);

@@ -581,10 +581,116 @@ xent_kernel(T* __restrict__ logits, float* __restrict__ row_loss, const int* __r
         Vec<T>::store(lr + v * VN, o);
     }
 }
+// bf16 rows of up to XENT_THREADS * XENT_NV * 8 = 49152 logits stay in registers from the first sweep to the last: the row is read
+// from memory once and written once (the general kernel above reads it three times, twice from L2), and the exponential is
+// evaluated once per element: e = exp(x - max) is summed in fp32 and parked, rounded to bf16, in the registers that held x; the
+// gradient (e / sum - onehot) * scale is bf16 anyway. Same results as xent_kernel to bf16 rounding.
+constexpr int XENT_NV = 12;
+__global__ void __launch_bounds__(XENT_THREADS)
+xent_rowreg_kernel(bf16* __restrict__ logits, float* __restrict__ row_loss, const int* __restrict__ targets,
+                   const float* __restrict__ row_weight, int V, int ldv, float grad_scale, int* __restrict__ err) {
+    __shared__ float red[XENT_THREADS / 32];
+    __shared__ float bcast;
+    const int row = blockIdx.x;
+    bf16* lr = logits + (size_t)row * ldv;
+    const int nvec = V / 8;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (row_weight) grad_scale = row_weight[row];
+    if (row_weight && grad_scale == 0.f) {   // masked row: zero gradient, zero loss
+        for (int v = threadIdx.x; v < nvec; v += XENT_THREADS) *reinterpret_cast<uint4*>(lr + v * 8) = make_uint4(0u, 0u, 0u, 0u);
+        if (threadIdx.x == 0) row_loss[row] = 0.f;
+        return;
+    }
+    uint4 raw[XENT_NV];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < XENT_NV; ++k) {
+        const int v = threadIdx.x + k * XENT_THREADS;
+        raw[k] = make_uint4(0xff80ff80u, 0xff80ff80u, 0xff80ff80u, 0xff80ff80u);   // -inf pairs: neutral for the maximum, exp gives 0
+        if (v < nvec) raw[k] = *reinterpret_cast<const uint4*>(lr + v * 8);
+        float f[8];
+        Vec<bf16>::unpack(raw[k], f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) mx = fmaxf(mx, f[i]);
+    }
+    mx = warp_max(mx);
+    if (lane == 0) red[warp] = mx;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < XENT_THREADS / 32 ? red[lane] : -INFINITY;
+        t = warp_max(t);
+        if (lane == 0) bcast = t;
+    }
+    __syncthreads();
+    mx = bcast;
+    const int tgt = targets[row];
+    const bool tgt_ok = (unsigned)tgt < (unsigned)V;
+    float x_tgt = 0.f;   // the target's logit, seen by the thread that holds it
+    float sum = 0.f;
+#pragma unroll
+    for (int k = 0; k < XENT_NV; ++k) {
+        const int v = threadIdx.x + k * XENT_THREADS;
+        float f[8];
+        Vec<bf16>::unpack(raw[k], f);
+        if (tgt_ok && (tgt >> 3) == v) x_tgt = f[tgt & 7];
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw[k]);
+#pragma unroll
+        for (int i = 0; i < 8; i += 2) {
+            const float e0 = __expf(f[i] - mx), e1 = __expf(f[i + 1] - mx);
+            sum += e0 + e1;
+            h[i >> 1] = __floats2bfloat162_rn(e0, e1);
+        }
+    }
+    sum = warp_sum(sum);
+    __syncthreads();
+    if (lane == 0) red[warp] = sum;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < XENT_THREADS / 32 ? red[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) bcast = t;
+    }
+    __syncthreads();
+    sum = bcast;
+    const float inv = 1.0f / sum;
+    if (tgt_ok && ((tgt >> 3) % XENT_THREADS) == (int)threadIdx.x && (tgt >> 3) < nvec) {
+        const float nll = -(x_tgt - mx - logf(sum));
+        row_loss[row] = row_weight ? nll * grad_scale : nll;
+    }
+    if (!tgt_ok && threadIdx.x == 0) {   // never used as an index: zero loss, plain softmax gradient, error word set
+        row_loss[row] = 0.f;
+        if (err) atomicExch(err, BMB_ERR_BAD_TARGET);
+    }
+    const float ps = inv * grad_scale;
+#pragma unroll
+    for (int k = 0; k < XENT_NV; ++k) {
+        const int v = threadIdx.x + k * XENT_THREADS;
+        if (v >= nvec) continue;
+        float f[8];
+        Vec<bf16>::unpack(raw[k], f);
+        uint4 o;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int i = 0; i < 8; i += 2) {
+            float g0 = f[i] * ps, g1 = f[i + 1] * ps;
+            if (v * 8 + i == tgt) g0 -= grad_scale;
+            if (v * 8 + i + 1 == tgt) g1 -= grad_scale;
+            h[i >> 1] = __floats2bfloat162_rn(g0, g1);
+        }
+        *reinterpret_cast<uint4*>(lr + v * 8) = o;
+    }
+}
+
 template <typename T>
 int xent_forward_backward(T* logits, float* row_loss, const int* targets, const float* row_weight, int N, int V, int ldv, float grad_scale,
                           int* err, cudaStream_t st) {
     if (V % Vec<T>::N || ldv % Vec<T>::N || !aligned16(logits)) return -1;
+    if constexpr (sizeof(T) == 2) {
+        if (V / 8 <= XENT_THREADS * XENT_NV) {
+            xent_rowreg_kernel<<<N, XENT_THREADS, 0, st>>>(logits, row_loss, targets, row_weight, V, ldv, grad_scale, err);
+            return 0;
+        }
+    }
     xent_kernel<T><<<N, XENT_THREADS, 0, st>>>(logits, row_loss, targets, row_weight, V, ldv, grad_scale, err);
     return 0;
 }

@@ -525,6 +525,22 @@ const float* bmx_session_logits(bm_session_t* s) {
     return s->h_logits;
 }
 int bmx_session_position(bm_session_t* s) { return s ? s->pos : -1; }
+/* Bytes of weights one step must read at the least: the matrices in the precision the model asks for (Q8: int8 blocks of 32 with one
+ * fp32 scale = 1.125 bytes per weight, as the reference counts them, bench/bench.c:339-348), whatever layout the session streams. */
+size_t bmx_session_algorithmic_weight_bytes(bm_session_t* s) {
+    if (!s) return 0;
+    size_t n = 0;
+    for (int l = 0; l < s->model->arch.n_layers; l++) {
+        const bm_mat_t* ms[4] = {&s->layers[l].qkv, &s->layers[l].o, &s->layers[l].gu, &s->layers[l].down};
+        for (int i = 0; i < 4; i++) {
+            const size_t e = (size_t)ms[i]->OC * ms[i]->C;
+            n += s->wtype == BMC_W_Q8 ? e + e / 32 * 4 : s->wtype == BMC_W_BF16 ? e * 2 : e * 4;
+        }
+    }
+    n += (size_t)s->model->arch.vocab_size * s->model->arch.dim * (s->head_type == BMC_W_BF16 ? 2 : 4);
+    return n;
+}
+/* Bytes of weights the session actually streams per step (the tensor-core path of >= 8 sequences reads bf16 expansions). */
 size_t bmx_session_weight_bytes(bm_session_t* s) {
     if (!s) return 0;
     size_t n = 0;

@@ -84,7 +84,11 @@ bm_session_t* bmx_create_session_batched(bm_context_t* ctx, bm_model_t* model, i
 int    bmx_session_generate_greedy(bm_session_t* s, const int* prompt, int n_prompt, int n_new, int* out);
 const float* bmx_session_logits(bm_session_t* s);
 int    bmx_session_position(bm_session_t* s);
+/* Weight bytes per decode step: what the session actually streams (the tensor-core path of >= 8 sequences reads bf16 expansions of
+ * the Q8 values), and the algorithmic minimum in the model's own precision (Q8 = 1.125 bytes per weight, as bench/bench.c:339-348
+ * of the reference counts). Roofline fractions are quoted on the second. */
 size_t bmx_session_weight_bytes(bm_session_t* s);
+size_t bmx_session_algorithmic_weight_bytes(bm_session_t* s);
 
 /* Data parallel: every rank holds a full replica and calls bm_train_step with its own B sequences;
  * gradients are summed across ranks (bf16 buckets over NCCL, overlapped with backward) before AdamW and the
