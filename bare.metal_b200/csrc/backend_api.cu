@@ -27,7 +27,7 @@ struct bmc_ctx_s {
     size_t allocated, peak;
     std::map<void*, size_t> allocs;
     std::mutex mu;
-    long launches;
+    long launches, launches_at_capture;
     int num_sms;
     // scratch owned by the context
     float* rms_scratch;
@@ -44,6 +44,7 @@ struct bmc_ctx_s {
     size_t gt_used;
     cudaGraph_t graphs[2];
     cudaGraphExec_t graph_execs[2];
+    long graph_kernels[2];  // kernel nodes of each captured graph: what one replay adds to `launches`
     int graph_slot;  // slot 0: inference session, slot 1: trainer
     // side stream (bmc_side_begin / _end / _wait): work that may overlap the main stream
     cudaStream_t side_stream;
@@ -668,6 +669,7 @@ int bmc_graph_begin(bmc_ctx_t* ctx) {
     const int k = ctx->graph_slot;
     if (ctx->graph_execs[k]) { cudaGraphExecDestroy(ctx->graph_execs[k]); ctx->graph_execs[k] = nullptr; }
     if (ctx->graphs[k]) { cudaGraphDestroy(ctx->graphs[k]); ctx->graphs[k] = nullptr; }
+    ctx->launches_at_capture = ctx->launches;
     return cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess ? 0 : -1;
 }
 int bmc_graph_end(bmc_ctx_t* ctx) {
@@ -683,13 +685,28 @@ int bmc_graph_end(bmc_ctx_t* ctx) {
         ctx->graph_execs[k] = nullptr;
         return -2;
     }
+    // the capture itself went through note(), which counted launches that did not run: take them back, and count the graph's
+    // kernel nodes once per replay instead
+    size_t n_nodes = 0;
+    ctx->graph_kernels[k] = 0;
+    if (cudaGraphGetNodes(ctx->graphs[k], nullptr, &n_nodes) == cudaSuccess && n_nodes) {
+        std::vector<cudaGraphNode_t> nodes(n_nodes);
+        if (cudaGraphGetNodes(ctx->graphs[k], nodes.data(), &n_nodes) == cudaSuccess)
+            for (size_t i = 0; i < n_nodes; ++i) {
+                cudaGraphNodeType ty;
+                if (cudaGraphNodeGetType(nodes[i], &ty) == cudaSuccess && ty == cudaGraphNodeTypeKernel) ++ctx->graph_kernels[k];
+            }
+    }
+    ctx->launches = ctx->launches_at_capture;
     return 0;
 }
 int bmc_graph_launch(bmc_ctx_t* ctx) {
     BMC_CHECK_CTX(ctx);
     const int k = ctx->graph_slot;
     if (!ctx->graph_execs[k]) return -1;
-    return cudaGraphLaunch(ctx->graph_execs[k], ctx->stream) == cudaSuccess ? 0 : -2;
+    if (cudaGraphLaunch(ctx->graph_execs[k], ctx->stream) != cudaSuccess) return -2;
+    ctx->launches += ctx->graph_kernels[k];
+    return 0;
 }
 int bmc_gemm_timing_enabled(bmc_ctx_t* ctx) { return ctx && ctx->gemm_timing ? 1 : 0; }
 int bmc_selftest_bounded_wait(bmc_ctx_t* ctx) {

@@ -582,9 +582,9 @@ xent_kernel(T* __restrict__ logits, float* __restrict__ row_loss, const int* __r
     }
 }
 // bf16 rows of up to XENT_THREADS * XENT_NV * 8 = 49152 logits stay in registers from the first sweep to the last: the row is read
-// from memory once and written once (the general kernel above reads it three times, twice from L2), and the exponential is
-// evaluated once per element: e = exp(x - max) is summed in fp32 and parked, rounded to bf16, in the registers that held x; the
-// gradient (e / sum - onehot) * scale is bf16 anyway. Same results as xent_kernel to bf16 rounding.
+// from memory once and written once (the general kernel above reads it three times, twice from L2). The arithmetic is the general
+// kernel's, element for element (exp evaluated again in the last sweep rather than parked at reduced precision), so the two differ
+// only in the order of the fp32 row sum.
 constexpr int XENT_NV = 12;
 __global__ void __launch_bounds__(XENT_THREADS)
 xent_rowreg_kernel(bf16* __restrict__ logits, float* __restrict__ row_loss, const int* __restrict__ targets,
@@ -633,13 +633,8 @@ xent_rowreg_kernel(bf16* __restrict__ logits, float* __restrict__ row_loss, cons
         float f[8];
         Vec<bf16>::unpack(raw[k], f);
         if (tgt_ok && (tgt >> 3) == v) x_tgt = f[tgt & 7];
-        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw[k]);
 #pragma unroll
-        for (int i = 0; i < 8; i += 2) {
-            const float e0 = __expf(f[i] - mx), e1 = __expf(f[i + 1] - mx);
-            sum += e0 + e1;
-            h[i >> 1] = __floats2bfloat162_rn(e0, e1);
-        }
+        for (int i = 0; i < 8; ++i) sum += expf(f[i] - mx);
     }
     sum = warp_sum(sum);
     __syncthreads();
@@ -661,7 +656,6 @@ xent_rowreg_kernel(bf16* __restrict__ logits, float* __restrict__ row_loss, cons
         row_loss[row] = 0.f;
         if (err) atomicExch(err, BMB_ERR_BAD_TARGET);
     }
-    const float ps = inv * grad_scale;
 #pragma unroll
     for (int k = 0; k < XENT_NV; ++k) {
         const int v = threadIdx.x + k * XENT_THREADS;
@@ -672,9 +666,8 @@ xent_rowreg_kernel(bf16* __restrict__ logits, float* __restrict__ row_loss, cons
         __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
         for (int i = 0; i < 8; i += 2) {
-            float g0 = f[i] * ps, g1 = f[i + 1] * ps;
-            if (v * 8 + i == tgt) g0 -= grad_scale;
-            if (v * 8 + i + 1 == tgt) g1 -= grad_scale;
+            const float g0 = (expf(f[i] - mx) * inv - (v * 8 + i == tgt ? 1.0f : 0.0f)) * grad_scale;
+            const float g1 = (expf(f[i + 1] - mx) * inv - (v * 8 + i + 1 == tgt ? 1.0f : 0.0f)) * grad_scale;
             h[i >> 1] = __floats2bfloat162_rn(g0, g1);
         }
         *reinterpret_cast<uint4*>(lr + v * 8) = o;
