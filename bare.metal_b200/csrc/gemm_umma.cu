@@ -208,8 +208,15 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             // 64-wide mn groups one box apart; one UMMA (K=16) = two k groups = 2048 B.
             const uint32_t a_lbo = p.a_mn ? MN_BOX_BYTES : 16, a_sbo = 1024, a_kstep = p.a_mn ? 2048 : 32;
             const uint32_t b_lbo = p.b_mn ? MN_BOX_BYTES : 16, b_sbo = 1024, b_kstep = p.b_mn ? 2048 : 32;
+            // One thread issues every UMMA, so the instructions between two of them are on the critical path whenever a UMMA
+            // is shorter than they are (tiles narrower than 256 columns). The descriptors of stage 0 are built once; a stage or a
+            // k step only moves the 14-bit start-address field (units of 16 bytes; shared memory ends below 256 KB, so the
+            // field never carries into its neighbour).
+            const uint64_t adesc0 = umma_smem_desc_sw128(smem_u32(sA), a_lbo, a_sbo);
+            const uint64_t bdesc0 = umma_smem_desc_sw128(smem_u32(sB), b_lbo, b_sbo);
+            const uint32_t a_st16 = A_STAGE_BYTES >> 4, b_st16 = (uint32_t)BST >> 4, a_k16 = a_kstep >> 4, b_k16 = b_kstep >> 4;
             int s = 0;
-            uint32_t ph = 0;
+            uint32_t ph = 0, a_off = 0, b_off = 0;   // stage s starts a_off / b_off sixteen-byte units into its ring
             int it = 0;
             bool ok = true;
             for (int u = worker; u < units && ok; u += nworkers, ++it) {
@@ -220,21 +227,24 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                 if (!mbar_wait(&bars.acc_empty[buf], acc_ph ^ 1, abort_flag)) { ok = false; break; }
                 tc_fence_after_sync();
                 const uint32_t tmem_acc = tmem_base + (uint32_t)buf * MAX_BN;
-                for (int kb = kb0; kb < kb1; ++kb, s = (s + 1 == NST ? 0 : s + 1), ph ^= (s == 0)) {
+                uint32_t acc = 0u;   // the tile's first UMMA overwrites the accumulator
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(&bars.full[s], ph, abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
-                    const uint32_t a_addr = smem_u32(sA + s * A_STAGE_BYTES);
-                    const uint32_t b_addr = smem_u32(sB + s * BST);
+                    uint64_t ad = adesc0 + a_off, bd = bdesc0 + b_off;
 #pragma unroll
                     for (int k = 0; k < BK / 16; ++k) {
-                        const uint64_t ad = umma_smem_desc_sw128(a_addr + k * a_kstep, a_lbo, a_sbo);
-                        const uint64_t bd = umma_smem_desc_sw128(b_addr + k * b_kstep, b_lbo, b_sbo);
-                        if (CTAS == 2) umma_bf16_ss_pair(tmem_acc, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
-                        else umma_bf16_ss(tmem_acc, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                        if (CTAS == 2) umma_bf16_ss_pair(tmem_acc, ad, bd, idesc, acc);
+                        else umma_bf16_ss(tmem_acc, ad, bd, idesc, acc);
+                        acc = 1u;
+                        ad += a_k16;
+                        bd += b_k16;
                     }
                     // releases the stage (in both CTAs of a pair) once these UMMAs have read it
                     if (CTAS == 2) umma_commit_pair(&bars.empty[s], 3);
                     else umma_commit(&bars.empty[s]);
+                    if (++s == NST) { s = 0; ph ^= 1u; a_off = 0; b_off = 0; }
+                    else { a_off += a_st16; b_off += b_st16; }
                 }
                 if (ok) {
                     if (CTAS == 2) umma_commit_pair(&bars.acc_full[buf], 3);
@@ -693,15 +703,18 @@ int make_map(CUtensorMap* tm, const void* base, uint64_t inner, uint64_t outer, 
     return r == CUDA_SUCCESS ? 0 : -11;
 }
 
-// pair: B is split over the two CTAs, so an MN-major B tile must be two whole 64-wide boxes per CTA
+// pair: B is split over the two CTAs, so an MN-major B tile must be two whole 64-wide boxes per CTA.
+// The thread that issues the UMMAs spends about 520 cycles per 64-deep k-block whatever the tile's width (barrier wait, four
+// instruction issues, commit: measured with an issue loop of its own), while the four UMMAs of a k-block take 2 * bn cycles.
+// So below 256 columns a tile costs as much time as a 256-wide one: take the fewest tiles, and among equals the narrowest.
 int choose_tile_n(int N, int b_mn, int ctas) {
     const int step = b_mn ? 64 * ctas : 32;
     int best = 64;
-    double best_cost = 1e30;
+    long best_cost = -1;
     for (int bn = (step > 64 ? step : 64); bn <= MAX_BN; bn += step) {
-        const double padded = (double)((N + bn - 1) / bn) * bn;
-        const double cost = padded * (1.0 + 24.0 / bn);
-        if (cost < best_cost - 1e-9 || (cost < best_cost + 1e-9 && bn > best)) {
+        const long tiles = (N + bn - 1) / bn;
+        const long cost = tiles * (2 * bn > 520 ? 2 * bn : 520);
+        if (best_cost < 0 || cost < best_cost) {
             best_cost = cost;
             best = bn;
         }

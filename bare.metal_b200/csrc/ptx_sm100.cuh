@@ -102,14 +102,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait. `abort_flag` lives in shared memory and is shared by every role of the CTA:
 // the first waiter that times out raises it, everybody else sees it and leaves too.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = global_timer_ns();
+    // The clock is not looked at before 512 polls have failed: one read of %globaltimer costs several hundred cycles, and a
+    // waiter that paid it at its first miss (the UMMA issuer meets a stage that is a few cycles from ready at nearly every
+    // k-block) slept through the moment its barrier completed. The limit counts from that first reading.
+    uint64_t t0 = 0;
     uint32_t it = 0;
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((++it & 255u) == 0) {
+        if ((++it & 511u) == 0) {
             if (*abort_flag) return false;
-            if (global_timer_ns() - t0 > BMB_WAIT_LIMIT_NS) {
+            const uint64_t now = global_timer_ns();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > BMB_WAIT_LIMIT_NS) {
                 *abort_flag = 1;
                 return false;
             }
