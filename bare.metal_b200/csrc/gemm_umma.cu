@@ -21,7 +21,11 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 64;
-constexpr int MAX_STAGES = 8;     // ring stages: as many (16 KB of A + this CTA's rows of B) as fit, see ring_stages()
+constexpr int KPS = 2;            // 64-deep k-blocks per ring stage. A stage costs its issuing thread one barrier wait and one commit
+                                  // (about 250 cycles together, more than the 53 an instruction issue costs), so with one k-block
+                                  // per stage the thread needed ~520 cycles for the 512 the tensor pipe takes at 256 columns and
+                                  // could never run ahead of it; two k-blocks per stage halve that share.
+constexpr int MAX_STAGES = 8;     // ring stages: as many KPS x (16 KB of A + this CTA's rows of B) as fit, see ring_stages()
 constexpr int MAX_BN = 256;
 constexpr int A_STAGE_BYTES = BM * BK * 2;      // 16 KB
 constexpr int MN_BOX_BYTES = 64 * BK * 2;       // one 64(mn) x 64(k) box of an MN-major operand
@@ -35,9 +39,9 @@ constexpr int STG_WARP_BYTES = 32 * STG_PITCH;
 constexpr int RING_BYTES = 192 * 1024;  // what the operand ring may use: 227 KB less the staging rows and the alignment slack
 constexpr int SMEM_DYN_BYTES = RING_BYTES + EPI_WARPS * STG_WARP_BYTES + 1024;
 static_assert(SMEM_DYN_BYTES <= 227 * 1024, "shared memory budget");
-// stages of (A tile + bn_local rows of B, 128 bytes each) that fit in the ring
+// stages of KPS x (A tile + bn_local rows of B, 128 bytes each) that fit in the ring
 __host__ __device__ inline int ring_stages(int bn_local) {
-    const int n = RING_BYTES / (A_STAGE_BYTES + bn_local * BK * 2);
+    const int n = RING_BYTES / (KPS * (A_STAGE_BYTES + bn_local * BK * 2));
     return n > MAX_STAGES ? MAX_STAGES : n;
 }
 constexpr uint32_t TMEM_COLS = 512;
@@ -97,8 +101,8 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     const int bn_local = CTAS == 2 ? p.BN / 2 : p.BN;  // B rows held by this CTA
     const int BST = bn_local * BK * 2;
     const int NST = ring_stages(bn_local);
-    uint8_t* sA = smem;
-    uint8_t* sB = smem + NST * A_STAGE_BYTES;
+    uint8_t* sA = smem;                              // stage s: KPS A tiles at sA + s * KPS * A_STAGE_BYTES
+    uint8_t* sB = smem + NST * KPS * A_STAGE_BYTES;  // stage s: KPS B tiles at sB + s * KPS * BST
     const uint32_t rank = CTAS == 2 ? cluster_ctarank() : 0u;   // 0 = leader of the pair
     const int worker = CTAS == 2 ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
     const int nworkers = CTAS == 2 ? (int)(gridDim.x >> 1) : (int)gridDim.x;
@@ -154,43 +158,51 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                 const int n_second = EPI == GEMM_EPI_SWIGLU_FWD ? p.N / 2 + (n0 / p.BN) * (p.BN / 2) : 0;
                 if (EPI == GEMM_EPI_SWIGLU_FWD) n0 = CTAS == 2 ? (rank ? n_second : (n0 / p.BN) * (p.BN / 2)) : (n0 / p.BN) * (p.BN / 2);
                 else n0 += (int)rank * bn_local;  // this CTA's part of the B tile
-                for (int kb = kb0; kb < kb1; ++kb, s = (s + 1 == NST ? 0 : s + 1), ph ^= (s == 0)) {
+                for (int kb = kb0; kb < kb1; kb += KPS, s = (s + 1 == NST ? 0 : s + 1), ph ^= (s == 0)) {
                     if (!mbar_wait(&bars.empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
-                    uint8_t* a_dst = sA + s * A_STAGE_BYTES;
-                    uint8_t* b_dst = sB + s * BST;
-                    const int k0 = kb * BK;
+                    const int g = min(KPS, kb1 - kb);   // k-blocks in this stage (the last stage of a unit may hold fewer)
                     if (CTAS == 2) {
                         const uint32_t full_leader = mapa_shared(&bars.full[s], 0);
-                        if (rank == 0) mbar_expect_tx(&bars.full[s], stage_tx_bytes);
-                        if (!p.a_mn) {
-                            tma_load_2d_pair(a_dst, &tmA, full_leader, k0, m0);
-                        } else {
-                            tma_load_2d_pair(a_dst, &tmA, full_leader, m0, k0);
-                            tma_load_2d_pair(a_dst + MN_BOX_BYTES, &tmA, full_leader, m0 + 64, k0);
-                        }
-                        if (!p.b_mn) {
-                            tma_load_2d_pair(b_dst, &tmB, full_leader, k0, n0);
-                        } else {
-                            for (int j = 0; j < bn_local / 64; ++j)
-                                tma_load_2d_pair(b_dst + j * MN_BOX_BYTES, &tmB, full_leader, n0 + 64 * j, k0);
+                        if (rank == 0) mbar_expect_tx(&bars.full[s], stage_tx_bytes * (uint32_t)g);
+                        for (int j = 0; j < g; ++j) {
+                            uint8_t* a_dst = sA + (s * KPS + j) * A_STAGE_BYTES;
+                            uint8_t* b_dst = sB + (s * KPS + j) * BST;
+                            const int k0 = (kb + j) * BK;
+                            if (!p.a_mn) {
+                                tma_load_2d_pair(a_dst, &tmA, full_leader, k0, m0);
+                            } else {
+                                tma_load_2d_pair(a_dst, &tmA, full_leader, m0, k0);
+                                tma_load_2d_pair(a_dst + MN_BOX_BYTES, &tmA, full_leader, m0 + 64, k0);
+                            }
+                            if (!p.b_mn) {
+                                tma_load_2d_pair(b_dst, &tmB, full_leader, k0, n0);
+                            } else {
+                                for (int jb = 0; jb < bn_local / 64; ++jb)
+                                    tma_load_2d_pair(b_dst + jb * MN_BOX_BYTES, &tmB, full_leader, n0 + 64 * jb, k0);
+                            }
                         }
                         continue;
                     }
-                    mbar_expect_tx(&bars.full[s], stage_tx_bytes);
-                    if (!p.a_mn) {
-                        tma_load_2d(a_dst, &tmA, &bars.full[s], k0, m0);
-                    } else {
-                        tma_load_2d(a_dst, &tmA, &bars.full[s], m0, k0);
-                        tma_load_2d(a_dst + MN_BOX_BYTES, &tmA, &bars.full[s], m0 + 64, k0);
-                    }
-                    if (EPI == GEMM_EPI_SWIGLU_FWD) {
-                        tma_load_2d(b_dst, &tmB, &bars.full[s], k0, n0);
-                        tma_load_2d(b_dst + (p.BN / 2) * BK * 2, &tmB, &bars.full[s], k0, n_second);
-                    } else if (!p.b_mn) {
-                        tma_load_2d(b_dst, &tmB, &bars.full[s], k0, n0);
-                    } else {
-                        for (int j = 0; j < p.BN / 64; ++j)
-                            tma_load_2d(b_dst + j * MN_BOX_BYTES, &tmB, &bars.full[s], n0 + 64 * j, k0);
+                    mbar_expect_tx(&bars.full[s], stage_tx_bytes * (uint32_t)g);
+                    for (int j = 0; j < g; ++j) {
+                        uint8_t* a_dst = sA + (s * KPS + j) * A_STAGE_BYTES;
+                        uint8_t* b_dst = sB + (s * KPS + j) * BST;
+                        const int k0 = (kb + j) * BK;
+                        if (!p.a_mn) {
+                            tma_load_2d(a_dst, &tmA, &bars.full[s], k0, m0);
+                        } else {
+                            tma_load_2d(a_dst, &tmA, &bars.full[s], m0, k0);
+                            tma_load_2d(a_dst + MN_BOX_BYTES, &tmA, &bars.full[s], m0 + 64, k0);
+                        }
+                        if (EPI == GEMM_EPI_SWIGLU_FWD) {
+                            tma_load_2d(b_dst, &tmB, &bars.full[s], k0, n0);
+                            tma_load_2d(b_dst + (p.BN / 2) * BK * 2, &tmB, &bars.full[s], k0, n_second);
+                        } else if (!p.b_mn) {
+                            tma_load_2d(b_dst, &tmB, &bars.full[s], k0, n0);
+                        } else {
+                            for (int jb = 0; jb < p.BN / 64; ++jb)
+                                tma_load_2d(b_dst + jb * MN_BOX_BYTES, &tmB, &bars.full[s], n0 + 64 * jb, k0);
+                        }
                     }
                 }
             }
@@ -214,7 +226,8 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             // field never carries into its neighbour).
             const uint64_t adesc0 = umma_smem_desc_sw128(smem_u32(sA), a_lbo, a_sbo);
             const uint64_t bdesc0 = umma_smem_desc_sw128(smem_u32(sB), b_lbo, b_sbo);
-            const uint32_t a_st16 = A_STAGE_BYTES >> 4, b_st16 = (uint32_t)BST >> 4, a_k16 = a_kstep >> 4, b_k16 = b_kstep >> 4;
+            const uint32_t a_kb16 = A_STAGE_BYTES >> 4, b_kb16 = (uint32_t)BST >> 4;          // one k-block inside a stage
+            const uint32_t a_st16 = KPS * a_kb16, b_st16 = KPS * b_kb16, a_k16 = a_kstep >> 4, b_k16 = b_kstep >> 4;
             int s = 0;
             uint32_t ph = 0, a_off = 0, b_off = 0;   // stage s starts a_off / b_off sixteen-byte units into its ring
             int it = 0;
@@ -228,17 +241,21 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                 tc_fence_after_sync();
                 const uint32_t tmem_acc = tmem_base + (uint32_t)buf * MAX_BN;
                 uint32_t acc = 0u;   // the tile's first UMMA overwrites the accumulator
-                for (int kb = kb0; kb < kb1; ++kb) {
+                for (int kb = kb0; kb < kb1; kb += KPS) {
                     if (!mbar_wait(&bars.full[s], ph, abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
-                    uint64_t ad = adesc0 + a_off, bd = bdesc0 + b_off;
+                    const int g = min(KPS, kb1 - kb);
+                    uint32_t ja = a_off, jb = b_off;
+                    for (int j = 0; j < g; ++j, ja += a_kb16, jb += b_kb16) {
+                        uint64_t ad = adesc0 + ja, bd = bdesc0 + jb;
 #pragma unroll
-                    for (int k = 0; k < BK / 16; ++k) {
-                        if (CTAS == 2) umma_bf16_ss_pair(tmem_acc, ad, bd, idesc, acc);
-                        else umma_bf16_ss(tmem_acc, ad, bd, idesc, acc);
-                        acc = 1u;
-                        ad += a_k16;
-                        bd += b_k16;
+                        for (int k = 0; k < BK / 16; ++k) {
+                            if (CTAS == 2) umma_bf16_ss_pair(tmem_acc, ad, bd, idesc, acc);
+                            else umma_bf16_ss(tmem_acc, ad, bd, idesc, acc);
+                            acc = 1u;
+                            ad += a_k16;
+                            bd += b_k16;
+                        }
                     }
                     // releases the stage (in both CTAs of a pair) once these UMMAs have read it
                     if (CTAS == 2) umma_commit_pair(&bars.empty[s], 3);
@@ -273,7 +290,7 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             if constexpr (EPI == GEMM_EPI_SWIGLU_FWD || EPI == GEMM_EPI_SWIGLU_BWD) {
                 // Both gated-MLP epilogues move rows as [first 32 columns | second 32 columns] = 2 x 64 bytes through the warp's
                 // staging rows: lanes 0-3 of a row carry the piece that belongs at column h, lanes 4-7 the piece at column H + h.
-                uint8_t* stg = smem + NST * (A_STAGE_BYTES + BST) + ew * STG_WARP_BYTES;
+                uint8_t* stg = smem + NST * KPS * (A_STAGE_BYTES + BST) + ew * STG_WARP_BYTES;
                 uint8_t* my_row = stg + lane * STG_PITCH;
                 const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)buf * MAX_BN;
                 const int piece = sub & 3, second = sub >> 2;
@@ -456,7 +473,7 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             // Accumulator rows live one per thread (TMEM lane = output row), but a warp-wide store of one 16-byte piece per
             // row would touch 32 different 128-byte lines. So full chunks go through the warp's staging rows and leave (and
             // the residual arrives) as whole 128-byte row segments, 4 rows per instruction.
-            uint8_t* stg = smem + NST * (A_STAGE_BYTES + BST) + ew * STG_WARP_BYTES;
+            uint8_t* stg = smem + NST * KPS * (A_STAGE_BYTES + BST) + ew * STG_WARP_BYTES;
             uint8_t* my_row = stg + lane * STG_PITCH;
             for (int c0 = c_lo; c0 < c_hi;) {
                 const int col0 = n0 + c0;
