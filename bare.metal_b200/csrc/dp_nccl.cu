@@ -86,6 +86,14 @@ struct bm_dp_s {
     int f32;          // gradients travel as fp32 (trainer in fp32 mode)
     int failed;       // a wait ran out or NCCL reported an asynchronous error: the communicator has been aborted
     double timeout_s; // host-side bound on every wait for the communication stream (env BM_DP_TIMEOUT_S, default 600)
+    // BM_DP_PROFILE=1: CUDA events around every bucket's exchange and at the end of backward; rank 0 prints the averages when
+    // the exchange is destroyed. The step is synchronised after AdamW has been enqueued, so profiled steps are slower.
+    int profile;
+    long prof_steps;
+    std::vector<cudaEvent_t> t0_ev, t1_ev;
+    cudaEvent_t bwd_done_ev, all_done_ev;
+    std::vector<double> prof_start_ms, prof_dur_ms;   // per bucket: start after the first bucket became ready, duration
+    double prof_tail_ms;                              // end of the last exchange minus end of backward: what AdamW waited for
 };
 
 namespace {
@@ -125,17 +133,23 @@ int wait_comm(bm_dp_s* dp) {
 extern "C" {
 
 // Bucket plan (pure host logic): groups of `layers_per_bucket` layers, highest layers first — the order in which
-// backward completes them — then one tail bucket holding the final norm and the tied embedding, which the
-// embedding scatter completes last. Bucket i covers elements [begin[i], end[i]) of the flat parameter order and is
-// complete when backward reports ready_at[i] (a layer index, or -1 for the tail). Returns the bucket count;
-// fills the arrays when cap is large enough.
+// backward completes them —, layer 0 in a bucket of its own, then one tail bucket holding the final norm and the tied
+// embedding, which the embedding scatter completes last. Whatever is exchanged after backward has ended is exposed (nothing is
+// left to hide it behind), so the last two buckets are kept small: one layer and the embedding. Bucket i covers elements
+// [begin[i], end[i]) of the flat parameter order and is complete when backward reports ready_at[i] (a layer index, or -1 for
+// the tail). Returns the bucket count; fills the arrays when cap is large enough.
 int bmx_dp_plan_buckets(int n_layers, const size_t* layer_begin, size_t n_params_total, int layers_per_bucket, size_t* begin,
                         size_t* end, int* ready_at, int cap) {
     if (layers_per_bucket < 1) layers_per_bucket = 1;
     int n = 0;
-    for (int hi = n_layers; hi > 0; hi -= layers_per_bucket) {
-        const int lo = hi - layers_per_bucket > 0 ? hi - layers_per_bucket : 0;
+    const int first_grouped = n_layers > 1 ? 1 : 0;   // layers [first_grouped, n_layers) are grouped from the top
+    for (int hi = n_layers; hi > first_grouped; hi -= layers_per_bucket) {
+        const int lo = hi - layers_per_bucket > first_grouped ? hi - layers_per_bucket : first_grouped;
         if (n < cap && begin) { begin[n] = layer_begin[lo]; end[n] = layer_begin[hi]; ready_at[n] = lo; }
+        ++n;
+    }
+    if (first_grouped) {
+        if (n < cap && begin) { begin[n] = layer_begin[0]; end[n] = layer_begin[1]; ready_at[n] = 0; }
         ++n;
     }
     if (n < cap && begin) { begin[n] = layer_begin[n_layers]; end[n] = n_params_total; ready_at[n] = -1; }
@@ -192,13 +206,40 @@ struct bm_dp_s* bm_dp_create(bmc_ctx_t* be, int rank, int world, const void* ncc
     bmx_dp_plan_buckets(n_layers, layer_begin, P, per, bb.data(), be_.data(), br.data(), nb);
     for (int i = 0; i < nb; ++i) dp->buckets.push_back(Bucket{bb[i], be_[i], br[i]});
     dp->ready_ev.resize(dp->buckets.size());
-    for (auto& ev : dp->ready_ev) cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+    dp->profile = getenv("BM_DP_PROFILE") != nullptr;
+    for (auto& ev : dp->ready_ev) cudaEventCreateWithFlags(&ev, dp->profile ? cudaEventDefault : cudaEventDisableTiming);
+    dp->prof_steps = 0;
+    dp->prof_tail_ms = 0.0;
+    if (dp->profile) {
+        dp->t0_ev.resize(dp->buckets.size());
+        dp->t1_ev.resize(dp->buckets.size());
+        for (auto& ev : dp->t0_ev) cudaEventCreate(&ev);
+        for (auto& ev : dp->t1_ev) cudaEventCreate(&ev);
+        cudaEventCreate(&dp->bwd_done_ev);
+        cudaEventCreate(&dp->all_done_ev);
+        dp->prof_start_ms.assign(dp->buckets.size(), 0.0);
+        dp->prof_dur_ms.assign(dp->buckets.size(), 0.0);
+    }
     return dp;
 }
 
 void bm_dp_destroy(struct bm_dp_s* dp) {
     if (!dp) return;
     if (!dp->failed) wait_comm(dp);
+    if (dp->profile && dp->rank == 0 && dp->prof_steps > 0) {
+        const double n = (double)dp->prof_steps, esz = dp->f32 ? 4.0 : 2.0;
+        fprintf(stderr, "[dp profile] %ld steps, %d ranks, %s gradients; times in ms, averages per step\n", dp->prof_steps, dp->world,
+                dp->f32 ? "fp32" : "bf16");
+        for (size_t i = 0; i < dp->buckets.size(); ++i) {
+            const double mb = (double)(dp->buckets[i].end - dp->buckets[i].begin) * esz / 1e6, dur = dp->prof_dur_ms[i] / n;
+            fprintf(stderr, "[dp profile] bucket %zu (ready at layer %d): %.1f MB, starts %.2f after the first bucket, takes %.3f (bus %.0f GB/s)\n", i,
+                    dp->buckets[i].ready_at, mb, dp->prof_start_ms[i] / n, dur, dur > 0 ? mb / dur * 2.0 * (dp->world - 1) / dp->world : 0.0);
+        }
+        fprintf(stderr, "[dp profile] last exchange ends %.3f after backward ends (what AdamW waits for)\n", dp->prof_tail_ms / n);
+    }
+    for (auto& ev : dp->t0_ev) cudaEventDestroy(ev);
+    for (auto& ev : dp->t1_ev) cudaEventDestroy(ev);
+    if (dp->profile) { cudaEventDestroy(dp->bwd_done_ev); cudaEventDestroy(dp->all_done_ev); }
     NcclApi* api = nccl();
     if (api && dp->comm) api->CommDestroy(dp->comm);
     for (auto& ev : dp->ready_ev) cudaEventDestroy(ev);
@@ -221,6 +262,7 @@ static int reduce_bucket(struct bm_dp_s* dp, size_t i) {
     const Bucket& b = dp->buckets[i];
     cudaEventRecord(dp->ready_ev[i], compute);
     cudaStreamWaitEvent(dp->comm_stream, dp->ready_ev[i], 0);
+    if (dp->profile) cudaEventRecord(dp->t0_ev[i], dp->comm_stream);
     const size_t n = b.end - b.begin;
     int rc;
     if (dp->f32) {
@@ -233,6 +275,7 @@ static int reduce_bucket(struct bm_dp_s* dp, size_t i) {
         fprintf(stderr, "[ERROR] ncclAllReduce failed: %s\n", api->GetErrorString ? api->GetErrorString(rc) : "?");
         return -2;
     }
+    if (dp->profile) cudaEventRecord(dp->t1_ev[i], dp->comm_stream);
     return 0;
 }
 
@@ -260,10 +303,30 @@ int bm_dp_reduce_all(struct bm_dp_s* dp) {
 int bm_dp_adamw(struct bm_dp_s* dp, bm_trainer_t* t, const float* hp) {
     if (dp->failed) return -3;
     cudaStream_t compute = (cudaStream_t)bmc_stream(dp->be);
+    if (dp->profile) {
+        cudaEventRecord(dp->bwd_done_ev, compute);
+        cudaEventRecord(dp->all_done_ev, dp->comm_stream);
+    }
     cudaEventRecord(dp->done_ev, dp->comm_stream);
     cudaStreamWaitEvent(compute, dp->done_ev, 0);
-    if (dp->f32) return bmc_adamw(dp->be, t->d_master, t->d_wlow, dp->d_grad_f32, BMC_F32, t->d_m, t->d_v, t->P, hp);
-    return bmc_adamw(dp->be, t->d_master, t->d_wlow, dp->d_grad_bf16, BMC_BF16, t->d_m, t->d_v, t->P, hp);
+    const int rc = dp->f32 ? bmc_adamw(dp->be, t->d_master, t->d_wlow, dp->d_grad_f32, BMC_F32, t->d_m, t->d_v, t->P, hp)
+                           : bmc_adamw(dp->be, t->d_master, t->d_wlow, dp->d_grad_bf16, BMC_BF16, t->d_m, t->d_v, t->P, hp);
+    if (dp->profile && rc == 0 && wait_comm(dp) == 0 && cudaEventSynchronize(dp->bwd_done_ev) == cudaSuccess) {
+        float ms = 0.f;
+        bool ok = true;
+        for (size_t i = 0; i < dp->buckets.size() && ok; ++i) {
+            ok = cudaEventElapsedTime(&ms, dp->ready_ev[0], dp->t0_ev[i]) == cudaSuccess;
+            if (ok) dp->prof_start_ms[i] += ms;
+            ok = ok && cudaEventElapsedTime(&ms, dp->t0_ev[i], dp->t1_ev[i]) == cudaSuccess;
+            if (ok) dp->prof_dur_ms[i] += ms;
+        }
+        if (ok && cudaEventElapsedTime(&ms, dp->bwd_done_ev, dp->all_done_ev) == cudaSuccess) {
+            dp->prof_tail_ms += ms;
+            ++dp->prof_steps;
+        }
+        cudaGetLastError();   // a bucket that was not exchanged this step leaves its events unrecorded: not an error of the step
+    }
+    return rc;
 }
 
 float bm_dp_mean_loss(struct bm_dp_s* dp, float local_loss) {
