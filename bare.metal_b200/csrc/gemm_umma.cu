@@ -73,12 +73,27 @@ struct __align__(8) Barriers {
     int abort_flag;
 };
 
+// Work unit -> tile. Tiles run row-tile-major (all column tiles of a row tile are neighbours, so one wave of CTAs shares its A
+// rows) inside column groups of RASTER_GN tiles: with more column tiles than that (the LM head has 192) a wave would otherwise
+// sweep tens of MB of B per row tile and, with C streaming through L2 beside it, fetch B from DRAM once per row tile (measured:
+// 1.7 GB of DRAM reads for 110 MB of operands at 8192 rows). Inside a group B's slice stays in L2 for every row tile.
+constexpr int RASTER_GN = 32;
 __device__ __forceinline__ void decode_unit(const KArgs& p, int u, int& m0, int& n0, int& kb0, int& kb1) {
     const int ntiles = p.tiles_m * p.tiles_n;
     const int split = u / ntiles;
     const int tile = u - split * ntiles;
-    const int tm = tile / p.tiles_n;
-    const int tn = tile - tm * p.tiles_n;
+    int tm, tn;
+    if (p.tiles_n <= RASTER_GN) {
+        tm = tile / p.tiles_n;
+        tn = tile - tm * p.tiles_n;
+    } else {
+        const int per_group = RASTER_GN * p.tiles_m;
+        const int g = tile / per_group;
+        const int idx = tile - g * per_group;
+        const int w = min(RASTER_GN, p.tiles_n - g * RASTER_GN);   // the last group may be narrower
+        tm = idx / w;
+        tn = g * RASTER_GN + (idx - tm * w);
+    }
     m0 = tm * p.tile_rows;
     n0 = tn * p.BN;
     kb0 = split * p.kb_per_split;
