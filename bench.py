@@ -274,6 +274,32 @@ def run_attention(args):
     return 0
 
 
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) and algorithmic bytes of ONE launch of every GEMM of the 360M training
+# step, in MB, from ncu --set full captures at 32768 rows (the LM head at 8192 rows). (dram, algorithmic, launches per layer);
+# the head runs once per step. The forward projections with a residual read 63 MB more in the step than in their capture.
+GEMM_NCU_DRAM_MB = {
+    "qkv forward": (122.9, 170.9, 1), "qkv input_grad": (142.5, 170.9, 1), "qkv weight_grad": (205.8, 173.9, 1),
+    "o forward": (89.8, 127.7, 1), "o input_grad_rowdot": (165.4, 190.5, 1), "o weight_grad": (138.0, 129.5, 1),
+    "gate_up forward_swiglu": (524.4, 576.0, 1), "gate_up input_grad": (426.9, 408.2, 1), "gate_up weight_grad": (557.9, 418.1, 1),
+    "down forward": (216.0, 235.6, 1), "down input_grad_swiglu": (809.7, 738.8, 1), "down weight_grad": (298.0, 240.5, 1),
+}
+GEMM_NCU_HEAD_MB_8192_ROWS = {"head forward": (2455.5, 915.4), "head input_grad": (1034.1, 915.4), "head weight_grad": (1344.6, 1009.8)}
+
+
+def gemm_step_traffic(model, rows):
+    """DRAM and algorithmic bytes per average GEMM launch of the step. The table holds the 360M shapes at 32768 rows; for any other
+    model or row count there is no capture and the traffic is reported as null."""
+    if model != "smollm2-360m" or rows != 32768:
+        return {"dram_bytes_per_launch": None, "case": "no ncu capture for this model / row count"}
+    L = 32
+    dram = L * sum(d * n for d, _, n in GEMM_NCU_DRAM_MB.values()) + 4.0 * sum(d for d, _ in GEMM_NCU_HEAD_MB_8192_ROWS.values())
+    alg = L * sum(a * n for _, a, n in GEMM_NCU_DRAM_MB.values()) + 4.0 * sum(a for _, a in GEMM_NCU_HEAD_MB_8192_ROWS.values())
+    launches = L * sum(n for _, _, n in GEMM_NCU_DRAM_MB.values()) + len(GEMM_NCU_HEAD_MB_8192_ROWS)
+    return {"dram_bytes_per_launch": dram / launches * 1e6,
+            "case": f"mean over the {launches} GEMM launches of a step from per-shape ncu captures (head scaled x4 from 8192 rows); "
+                    f"algorithmic {alg / launches:.1f}e6 B per launch"}
+
+
 def run_gemm(args):
     """The linear-layer GEMMs of the 360M step (forward, input gradient, weight gradient) in isolation, bf16 operands drawn
     from N(0,1), 16 x 2048 token rows; one JSON line per shape and kind. --shape picks one (e.g. gate_up)."""
@@ -560,6 +586,7 @@ def main():
 
     if rank == 0:
         peaks, peak_src = measured_peaks()
+        gemm_traffic = gemm_step_traffic(args.model, B * S)
         fpt = flops_per_token(a, S)
         tflops = value * fpt / 1e12
         n_l, g_ms, g_fl = gt[0], gt[1], gt[2]
@@ -583,9 +610,9 @@ def main():
             "gpu_launches": int(launches1 - launches0),
             "roofline": {"kernel": "gemm_bf16_umma_kernel (tcgen05)", "bound": "tensor", "achieved": ach, "peak": peak_tf,
                          "unit": "TFLOP/s", "frac": (ach / peak_tf) if ach else None,
-                         # DRAM bytes of ONE launch from the ncu capture of the gate/up forward GEMM (rows 32768, in 960, out 5120;
-                         # algorithmic bytes of that launch 408e6), summarised in profiles/gemm_umma_gate_up_forward_ncu_full.md
-                         "traffic": 353.2e6, "traffic_case": "gate_up forward GEMM, 322 GFLOP, algorithmic 408e6 B",
+                         # DRAM bytes of the step's average GEMM launch, from the ncu captures of every shape and kind
+                         # (GEMM_NCU_DRAM_MB below; profiles/gemm_umma_step_shapes_ncu_full.md)
+                         "traffic": gemm_traffic["dram_bytes_per_launch"], "traffic_case": gemm_traffic["case"],
                          "peak_source": f"bf16_tflops_sustained of {peak_src}", "launches": int(n_l),
                          "avg_launch_ms": (g_ms / n_l) if n_l else None, "avg_launch_flops": (g_fl / n_l) if n_l else None,
                          "share_of_step": (g_ms / ms_roof) if ms_roof else None,
