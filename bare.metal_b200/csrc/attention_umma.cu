@@ -849,6 +849,311 @@ __global__ void dq_finish_kernel(bf16* __restrict__ gq, int ldgq, const float* _
     *reinterpret_cast<uint2*>(dst + 32) = w1;
 }
 
+
+// ================================ prefill: fp32-accurate attention on the tensor pipe ==========================================
+// The inference session keeps fp32 activations (the reference's attention_forward_prefill_tiled, src/kernels/forward.metal:2024,
+// is fp32 arithmetic), so bf16 operands would miss its accuracy by two orders of magnitude. Every fp32 operand x is therefore
+// split into bf16 hi = rn(x) and lo = rn(x - hi), and each product is the sum of three tensor-core products:
+//   S = Qh Kh^T + Ql Kh^T + Qh Kl^T          O += Ph Vh + Pl Vh + Ph Vl
+// (the lo x lo terms are below 2^-17 of the result). Accumulation is fp32 in tensor memory, the softmax fp32 in registers.
+// One CTA = 128 queries of one head: warp 0 TMA, warp 1 UMMA issuer, warps 4-7 softmax (one query row per thread).
+// Tensor memory: S0 [0,128) S1 [128,256) O [256,320) Ph [320,384) Pl [384,448) (P as packed bf16 pairs, the A operand of P V).
+// Shared memory: Q hi|lo 32 KB, two stages of K hi|lo and V hi|lo (64 KB each).
+constexpr int PF_THREADS = 256;
+constexpr int PF_KV_STAGES = 2;
+constexpr int PF_DYN_SMEM = 2 * Q_BYTES + PF_KV_STAGES * 4 * KV_TILE_BYTES + 1024;
+constexpr uint32_t PF_T_O = 2 * FK, PF_T_PH = 2 * FK + FHD, PF_T_PL = 2 * FK + FHD + FK / 2;
+
+struct PfBars {
+    uint64_t q_full, kv_full[PF_KV_STAGES], kv_empty[PF_KV_STAGES], s_full[2], p_ready, pv_done;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+struct PfArgs {
+    float* out;
+    int ldo;
+    int T, NH, NKV;
+    float scale;
+    int* err;
+};
+
+__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+        "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+
+// fp32 rows -> [hi 64 | lo 64] bf16 per head; one thread per four values. Columns [0, QD) of a row are Q, the K and V rows come
+// from their own pointers (the packed QKV rows of the session).
+__global__ void prefill_split_kernel(bf16* __restrict__ qs, bf16* __restrict__ ks, bf16* __restrict__ vs, const float* __restrict__ q, int ldq,
+                                     const float* __restrict__ k, const float* __restrict__ v, int ldkv, long rows, int NH, int NKV) {
+    const int per_row = (NH + 2 * NKV) * (FHD / 4);
+    const long i = blockIdx.x * (long)blockDim.x + threadIdx.x;
+    if (i >= rows * per_row) return;
+    const long r = i / per_row;
+    int c = (int)(i - r * per_row);
+    int head = c / (FHD / 4);
+    const int d = (c - head * (FHD / 4)) * 4;
+    const float* src;
+    bf16* dst;
+    if (head < NH) {
+        src = q + (size_t)r * ldq + head * FHD + d;
+        dst = qs + ((size_t)r * NH + head) * (2 * FHD) + d;
+    } else if (head < NH + NKV) {
+        head -= NH;
+        src = k + (size_t)r * ldkv + head * FHD + d;
+        dst = ks + ((size_t)r * NKV + head) * (2 * FHD) + d;
+    } else {
+        head -= NH + NKV;
+        src = v + (size_t)r * ldkv + head * FHD + d;
+        dst = vs + ((size_t)r * NKV + head) * (2 * FHD) + d;
+    }
+    const float4 x = *reinterpret_cast<const float4*>(src);
+    const __nv_bfloat162 h0 = __floats2bfloat162_rn(x.x, x.y), h1 = __floats2bfloat162_rn(x.z, x.w);
+    const float2 f0 = __bfloat1622float2(h0), f1 = __bfloat1622float2(h1);
+    const __nv_bfloat162 l0 = __floats2bfloat162_rn(x.x - f0.x, x.y - f0.y), l1 = __floats2bfloat162_rn(x.z - f1.x, x.w - f1.y);
+    uint2 hv, lv;
+    hv.x = *reinterpret_cast<const uint32_t*>(&h0); hv.y = *reinterpret_cast<const uint32_t*>(&h1);
+    lv.x = *reinterpret_cast<const uint32_t*>(&l0); lv.y = *reinterpret_cast<const uint32_t*>(&l1);
+    *reinterpret_cast<uint2*>(dst) = hv;
+    *reinterpret_cast<uint2*>(dst + FHD) = lv;
+}
+
+__global__ void __launch_bounds__(PF_THREADS, 1)
+prefill_attention_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                              const __grid_constant__ CUtensorMap tmV, const PfArgs p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ PfBars bars;
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* sQ = smem;                                   // hi box, lo box
+    uint8_t* sK = sQ + 2 * Q_BYTES;                       // per stage: hi box, lo box
+    uint8_t* sV = sK + PF_KV_STAGES * 2 * KV_TILE_BYTES;  // per stage: hi box, lo box
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qb = (int)gridDim.x - 1 - (int)blockIdx.x;  // longest query blocks first
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int kh = h / (p.NH / p.NKV);
+    const int q0 = qb * FQ;
+    const int row0 = b * p.T;
+    const int n_tiles = qb + 1;   // causal, FQ == FK
+
+    if (threadIdx.x == 0) {
+        mbar_init(&bars.q_full, 1);
+        for (int i = 0; i < PF_KV_STAGES; ++i) {
+            mbar_init(&bars.kv_full[i], 1);
+            mbar_init(&bars.kv_empty[i], 1);
+        }
+        mbar_init(&bars.s_full[0], 1);
+        mbar_init(&bars.s_full[1], 1);
+        mbar_init(&bars.p_ready, 4);
+        mbar_init(&bars.pv_done, 1);
+        bars.abort_flag = 0;
+        mbar_fence_init();
+        fence_proxy_async_smem();
+    }
+    if (warp == 1) {
+        tmem_alloc(&bars.tmem_base, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = bars.tmem_base;
+    volatile int* abort_flag = &bars.abort_flag;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+            mbar_expect_tx(&bars.q_full, 2 * Q_BYTES);
+            tma_load_2d(sQ, &tmQ, &bars.q_full, h * 2 * FHD, row0 + q0);
+            tma_load_2d(sQ + Q_BYTES, &tmQ, &bars.q_full, h * 2 * FHD + FHD, row0 + q0);
+            for (int j = 0; j < n_tiles; ++j) {
+                const int st = j % PF_KV_STAGES;
+                if (!mbar_wait(&bars.kv_empty[st], ((j / PF_KV_STAGES) & 1) ^ 1, abort_flag)) break;
+                mbar_expect_tx(&bars.kv_full[st], 4 * KV_TILE_BYTES);
+                uint8_t* kd = sK + st * 2 * KV_TILE_BYTES;
+                uint8_t* vd = sV + st * 2 * KV_TILE_BYTES;
+                tma_load_2d(kd, &tmK, &bars.kv_full[st], kh * 2 * FHD, row0 + j * FK);
+                tma_load_2d(kd + KV_TILE_BYTES, &tmK, &bars.kv_full[st], kh * 2 * FHD + FHD, row0 + j * FK);
+                tma_load_2d(vd, &tmV, &bars.kv_full[st], kh * 2 * FHD, row0 + j * FK);
+                tma_load_2d(vd + KV_TILE_BYTES, &tmV, &bars.kv_full[st], kh * 2 * FHD + FHD, row0 + j * FK);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ UMMA issuer --------------------------------
+        if (lane == 0) {
+            const uint32_t idesc_s = umma_idesc_bf16_f32(FQ, FK, 0, 0);    // S = Q K^T : both operands K-major
+            const uint32_t idesc_o = umma_idesc_bf16_f32(FQ, FHD, 0, 1);   // O += P V  : P from tensor memory, V MN-major
+            const uint64_t qh = umma_smem_desc_sw128(smem_u32(sQ), 16, 1024), ql = qh + (uint64_t)(Q_BYTES >> 4);
+            const uint64_t kd0 = umma_smem_desc_sw128(smem_u32(sK), 16, 1024);
+            const uint64_t vd0 = umma_smem_desc_sw128(smem_u32(sV), FK * 128, 1024);
+            auto issue_qk = [&](int j) {
+                const uint64_t kh_d = kd0 + (uint64_t)((j % PF_KV_STAGES) * ((2 * KV_TILE_BYTES) >> 4)), kl_d = kh_d + (uint64_t)(KV_TILE_BYTES >> 4);
+                const uint32_t ts = tmem + (uint32_t)(j & 1) * FK;
+#pragma unroll
+                for (int k = 0; k < FHD / 16; ++k) umma_bf16_ss(ts, qh + 2 * k, kh_d + 2 * k, idesc_s, k > 0 ? 1u : 0u);
+#pragma unroll
+                for (int k = 0; k < FHD / 16; ++k) umma_bf16_ss(ts, ql + 2 * k, kh_d + 2 * k, idesc_s, 1u);
+#pragma unroll
+                for (int k = 0; k < FHD / 16; ++k) umma_bf16_ss(ts, qh + 2 * k, kl_d + 2 * k, idesc_s, 1u);
+                umma_commit(&bars.s_full[j & 1]);
+            };
+            auto issue_pv = [&](int j) {
+                const uint64_t vh_d = vd0 + (uint64_t)((j % PF_KV_STAGES) * ((2 * KV_TILE_BYTES) >> 4)), vl_d = vh_d + (uint64_t)(KV_TILE_BYTES >> 4);
+#pragma unroll
+                for (int k = 0; k < FK / 16; ++k) umma_bf16_ts(tmem + PF_T_O, tmem + PF_T_PH + 8 * k, vh_d + 128 * k, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+                for (int k = 0; k < FK / 16; ++k) umma_bf16_ts(tmem + PF_T_O, tmem + PF_T_PL + 8 * k, vh_d + 128 * k, idesc_o, 1u);
+#pragma unroll
+                for (int k = 0; k < FK / 16; ++k) umma_bf16_ts(tmem + PF_T_O, tmem + PF_T_PH + 8 * k, vl_d + 128 * k, idesc_o, 1u);
+                umma_commit(&bars.pv_done);
+                umma_commit(&bars.kv_empty[j % PF_KV_STAGES]);
+            };
+            bool ok = mbar_wait(&bars.q_full, 0, abort_flag) && mbar_wait(&bars.kv_full[0], 0, abort_flag);
+            if (ok) {
+                tc_fence_after_sync();
+                issue_qk(0);
+            }
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                if (j + 1 < n_tiles) {
+                    // S of the next key tile goes to the other S buffer (its previous scores were consumed before p_ready(j-1))
+                    if (!mbar_wait(&bars.kv_full[(j + 1) % PF_KV_STAGES], ((j + 1) / PF_KV_STAGES) & 1, abort_flag)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    issue_qk(j + 1);
+                }
+                if (!mbar_wait(&bars.p_ready, j & 1, abort_flag)) { ok = false; break; }
+                tc_fence_after_sync();
+                issue_pv(j);
+            }
+        }
+    } else if (warp >= 4) {
+        // ------------------------------ softmax / epilogue -------------------------
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;
+        const int qi = q0 + r;
+        const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
+        const float sl2 = p.scale * LOG2E_F;
+        float m_ref = -INFINITY, l_run = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles; ++j) {
+            ok = mbar_wait(&bars.s_full[j & 1], (j >> 1) & 1, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after_sync();
+            uint32_t v[4][32];
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch) tmem_ld_32x32(lane_addr + (uint32_t)(j & 1) * FK + ch * 32, v[ch]);
+            tmem_ld_wait();
+            const int k0 = j * FK;
+            if (j == n_tiles - 1) {   // diagonal tile (also the ragged end: a key past the sequence is past every valid query)
+#pragma unroll
+                for (int ch = 0; ch < 4; ++ch)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (k0 + ch * 32 + i > qi) v[ch][i] = __float_as_uint(-INFINITY);
+            }
+            float mxp[8];
+#pragma unroll
+            for (int t = 0; t < 8; ++t) mxp[t] = -INFINITY;
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch)
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) mxp[(i >> 1) & 7] = max3_f(mxp[(i >> 1) & 7], __uint_as_float(v[ch][i]), __uint_as_float(v[ch][i + 1]));
+            float mx = fmaxf(fmaxf(fmaxf(mxp[0], mxp[1]), fmaxf(mxp[2], mxp[3])), fmaxf(fmaxf(mxp[4], mxp[5]), fmaxf(mxp[6], mxp[7])));
+            mx *= sl2;
+            float corr = 1.0f;
+            bool need = false;
+            if (mx > m_ref) {   // every valid row sees key 0, so mx is finite from the first tile on
+                if (m_ref != -INFINITY) { corr = ex2_approx(m_ref - mx); need = true; }
+                m_ref = mx;
+            }
+            const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+            if (j > 0) {
+                // P V of the previous tile has read P and updated O: P may be overwritten and O rescaled
+                ok = mbar_wait(&bars.pv_done, (j - 1) & 1, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after_sync();
+                if (__any_sync(0xffffffffu, need)) {
+#pragma unroll
+                    for (int ch = 0; ch < FHD / 32; ++ch) {
+                        uint32_t o[32];
+                        tmem_ld_32x32(lane_addr + PF_T_O + ch * 32, o);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+                        tmem_st_32x32(lane_addr + PF_T_O + ch * 32, o);
+                    }
+                }
+            }
+            float ls[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch) {
+                uint32_t ph[16], pl[16];   // 32 keys = 16 columns of bf16 pairs
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float p0, p1;
+                    fma2_f(p0, p1, __uint_as_float(v[ch][i]), __uint_as_float(v[ch][i + 1]), sl2, -m_use);
+                    p0 = ex2_approx(p0);
+                    p1 = ex2_approx(p1);
+                    add2_f(ls[(i >> 1) & 1 ? 2 : 0], ls[(i >> 1) & 1 ? 3 : 1], p0, p1);
+                    const __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
+                    const float2 hf = __bfloat1622float2(hh);
+                    const __nv_bfloat162 ll = __floats2bfloat162_rn(p0 - hf.x, p1 - hf.y);
+                    ph[i >> 1] = *reinterpret_cast<const uint32_t*>(&hh);
+                    pl[i >> 1] = *reinterpret_cast<const uint32_t*>(&ll);
+                }
+                tmem_st_32x16(lane_addr + PF_T_PH + ch * 16, ph);
+                tmem_st_32x16(lane_addr + PF_T_PL + ch * 16, pl);
+            }
+            l_run = l_run * corr + ((ls[0] + ls[1]) + (ls[2] + ls[3]));
+            tmem_st_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars.p_ready);
+        }
+        if (ok) {
+            ok = mbar_wait(&bars.pv_done, (n_tiles - 1) & 1, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok) {
+            tc_fence_after_sync();
+            const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+            float* orow = p.out + (size_t)(row0 + qi) * p.ldo + (size_t)h * FHD;
+#pragma unroll
+            for (int ch = 0; ch < FHD / 32; ++ch) {
+                uint32_t o[32];
+                tmem_ld_32x32(lane_addr + PF_T_O + ch * 32, o);
+                tmem_ld_wait();
+                if (qi < p.T) {
+#pragma unroll
+                    for (int c = 0; c < 8; ++c)
+                        *reinterpret_cast<float4*>(orow + ch * 32 + c * 4) =
+                            make_float4(__uint_as_float(o[c * 4]) * inv, __uint_as_float(o[c * 4 + 1]) * inv, __uint_as_float(o[c * 4 + 2]) * inv,
+                                        __uint_as_float(o[c * 4 + 3]) * inv);
+                }
+            }
+            tc_fence_before_sync();
+        }
+    }
+
+    // ------------------------------ teardown ---------------------------------------
+    __syncwarp();
+    if (*abort_flag) {
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 2000000ull) __nanosleep(1000);
+        if (threadIdx.x == 0 && p.err) atomicExch(p.err, 2500 + (int)blockIdx.x);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    if (warp == 1) tmem_dealloc(tmem, 512);
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -988,6 +1293,42 @@ int flash_attention_backward_umma(bf16* gq, int ldgq, bf16* gk, bf16* gv, int ld
     }
     const long n = (long)rows * NH * 8;
     dq_finish_kernel<<<(int)((n + 255) / 256), 256, 0, st>>>(gq, ldgq, dq_acc, (int)rows, NH, S, rope_cs);
+    return 0;
+}
+
+size_t prefill_attention_umma_scratch_bytes(long rows, int NH, int NKV) { return (size_t)rows * (NH + 2 * NKV) * 2 * FHD * sizeof(bf16); }
+
+// fp32 in, fp32 out; q [rows, ldq], k / v [rows, ldkv] (rows = NB * T, sequence b owns rows b*T ..), out [rows, ldo]. `scratch` holds the
+// split operands (prefill_attention_umma_scratch_bytes).
+int prefill_attention_umma(float* out, int ldo, const float* q, int ldq, const float* k, const float* v, int ldkv, int NB, int T, int NH, int NKV,
+                           int HD, float scale, void* scratch, int* err_flag, cudaStream_t st) {
+    if (HD != FHD || NKV <= 0 || NH % NKV || NB <= 0 || T <= 0) return -1;
+    if ((ldq % 4) || (ldkv % 4) || (ldo % 4) || (((uintptr_t)q) & 15) || (((uintptr_t)k) & 15) || (((uintptr_t)v) & 15) || (((uintptr_t)out) & 15) ||
+        (((uintptr_t)scratch) & 15))
+        return -2;
+    static std::atomic<unsigned long long> attr_done{0};
+    if (first_use_on_current_device(attr_done) &&
+        cudaFuncSetAttribute(prefill_attention_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_DYN_SMEM) != cudaSuccess)
+        return -5;
+    const long rows = (long)NB * T;
+    bf16* qs = (bf16*)scratch;
+    bf16* ks = qs + (size_t)rows * NH * 2 * FHD;
+    bf16* vs = ks + (size_t)rows * NKV * 2 * FHD;
+    const long n = rows * (NH + 2 * NKV) * (FHD / 4);
+    prefill_split_kernel<<<(int)((n + 255) / 256), 256, 0, st>>>(qs, ks, vs, q, ldq, k, v, ldkv, rows, NH, NKV);
+    CUtensorMap tq, tk, tv;
+    int rc = make_rows_map(&tq, qs, (uint64_t)NH * 2 * FHD, (uint64_t)rows, (uint64_t)NH * 2 * FHD, FQ);
+    if (!rc) rc = make_rows_map(&tk, ks, (uint64_t)NKV * 2 * FHD, (uint64_t)rows, (uint64_t)NKV * 2 * FHD, FK);
+    if (!rc) rc = make_rows_map(&tv, vs, (uint64_t)NKV * 2 * FHD, (uint64_t)rows, (uint64_t)NKV * 2 * FHD, FK);
+    if (rc) return rc;
+    PfArgs a{out, ldo, T, NH, NKV, scale, err_flag};
+    dim3 grid((T + FQ - 1) / FQ, NH, NB);
+    prefill_attention_umma_kernel<<<grid, PF_THREADS, PF_DYN_SMEM, st>>>(tq, tk, tv, a);
+    const cudaError_t le = cudaGetLastError();
+    if (le != cudaSuccess) {
+        fprintf(stderr, "prefill_attention_umma: launch failed: %s\n", cudaGetErrorString(le));
+        return -7;
+    }
     return 0;
 }
 

@@ -25,6 +25,13 @@ int flash_attention_backward_umma(bf16* gq, int ldgq, bf16* gk, bf16* gv, int ld
                                   int NKV, int HD, float scale, void* scratch, const float* delta_in, const float* rope_cs,
                                   const uint32_t* keymask, int* err_flag, cudaStream_t st);
 
+// Causal GQA attention for the inference session's prefill: fp32 in, fp32 out, fp32-accurate on the tensor pipe (each fp32 operand
+// is split into bf16 hi + lo and each product is three tcgen05 products). Replaces attention_forward_prefill_tiled
+// (src/kernels/forward.metal:2024). q [NB*T, ldq], k / v [NB*T, ldkv], out [NB*T, ldo]; head_dim 64.
+size_t prefill_attention_umma_scratch_bytes(long rows, int NH, int NKV);
+int prefill_attention_umma(float* out, int ldo, const float* q, int ldq, const float* k, const float* v, int ldkv, int NB, int T, int NH, int NKV,
+                           int HD, float scale, void* scratch, int* err_flag, cudaStream_t st);
+
 // out[r, 0:cols] (bf16, pitch ldo) = in[r, 0:cols] (fp32, pitch ldi)
 int cast_rows_f32_to_bf16(bf16* out, int ldo, const float* in, int ldi, int rows, int cols, cudaStream_t st);
 

@@ -636,7 +636,10 @@ int bmc_decode_kv_scatter(bmc_ctx_t* ctx, float* d_cache, const float* d_qkv, in
 int bmc_prefill_attention(bmc_ctx_t* ctx, float* d_out, int ldo, const float* d_q, int ldq, const float* d_k, const float* d_v, int ldkv, int NB,
                           int T, int NH, int NKV, int HD, float scale) {
     BMC_CHECK_CTX(ctx);
-    return note(ctx, prefill_attention_f32(d_out, ldo, d_q, ldq, d_k, d_v, ldkv, NB, T, NH, NKV, HD, scale, ctx->stream));
+    // tcgen05 kernel on split bf16 operands (fp32-accurate); the split copies of Q, K and V live in the attention scratch
+    void* scratch = scratch_get(ctx, &ctx->attn_scratch, &ctx->attn_scratch_bytes, prefill_attention_umma_scratch_bytes((long)NB * T, NH, NKV));
+    if (!scratch) return -4;
+    return note(ctx, prefill_attention_umma(d_out, ldo, d_q, ldq, d_k, d_v, ldkv, NB, T, NH, NKV, HD, scale, scratch, ctx->d_err, ctx->stream), 2);
 }
 int bmc_decode_swiglu(bmc_ctx_t* ctx, float* d_out, const float* d_gate_up, int NB, int H) {
     BMC_CHECK_CTX(ctx);

@@ -642,128 +642,6 @@ __global__ void decode_kv_scatter_kernel(float* __restrict__ cache, const float*
     *reinterpret_cast<float4*>(cache + ((((size_t)layer * 2 + which) * NB + b) * (size_t)MS + t) * KV + c * 4) = v;
 }
 
-// Prefill attention, fp32 throughout (attention_forward_prefill, src/kernels/forward.metal): causal softmax(Q K^T * scale) V over
-// the prompt of each sequence, head_dim 64. One block = 64 queries of one head; K/V tiles of 64 keys go through shared memory;
-// a thread owns a 4 x 4 patch of the score tile (rows ty + 16 i, keys tx + 16 j) and of the output tile (rows ty + 16 i, four
-// adjacent dims), with the usual running max / sum per row.
-constexpr int PF_T = 64, PF_HD = 64, PF_PITCH = 68;
-__global__ void __launch_bounds__(256)
-prefill_attention_kernel(float* __restrict__ out, int ldo, const float* __restrict__ q, int ldq, const float* __restrict__ k,
-                         const float* __restrict__ v, int ldkv, int T, int NH, int NKV, float scale) {
-    extern __shared__ float sm[];
-    float* Qs = sm;                        // [64][68]
-    float* Ks = Qs + PF_T * PF_PITCH;      // [64][68]
-    float* Vs = Ks + PF_T * PF_PITCH;      // [64][68]
-    float* Ps = Vs + PF_T * PF_PITCH;      // [64][68]
-    const int qt = blockIdx.x, h = blockIdx.y, b = blockIdx.z, tid = threadIdx.x;
-    const int kh = h / (NH / NKV);
-    const int tx = tid & 15, ty = tid >> 4;
-    pdl_wait();
-    const size_t row0 = (size_t)b * T;
-    const int q0 = qt * PF_T;
-    for (int i = tid; i < PF_T * (PF_HD / 4); i += 256) {
-        const int r = i / (PF_HD / 4), c4 = i % (PF_HD / 4);
-        float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (q0 + r < T) val = *reinterpret_cast<const float4*>(q + (row0 + q0 + r) * ldq + (size_t)h * PF_HD + c4 * 4);
-        *reinterpret_cast<float4*>(Qs + r * PF_PITCH + c4 * 4) = val;
-    }
-    float o[4][4], m[4], l[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        m[i] = -INFINITY;
-        l[i] = 0.f;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
-    }
-    for (int kt = 0; kt <= qt; ++kt) {
-        const int k0 = kt * PF_T;
-        __syncthreads();  // previous tile fully consumed (and Qs written, first time round)
-        for (int i = tid; i < PF_T * (PF_HD / 4); i += 256) {
-            const int r = i / (PF_HD / 4), c4 = i % (PF_HD / 4);
-            float4 kv = make_float4(0.f, 0.f, 0.f, 0.f), vv = kv;
-            if (k0 + r < T) {
-                kv = *reinterpret_cast<const float4*>(k + (row0 + k0 + r) * ldkv + (size_t)kh * PF_HD + c4 * 4);
-                vv = *reinterpret_cast<const float4*>(v + (row0 + k0 + r) * ldkv + (size_t)kh * PF_HD + c4 * 4);
-            }
-            *reinterpret_cast<float4*>(Ks + r * PF_PITCH + c4 * 4) = kv;
-            *reinterpret_cast<float4*>(Vs + r * PF_PITCH + c4 * 4) = vv;
-        }
-        __syncthreads();
-        float sc[4][4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-#pragma unroll
-            for (int j = 0; j < 4; ++j) sc[i][j] = 0.f;
-#pragma unroll 4
-        for (int d = 0; d < PF_HD; d += 4) {
-            float4 qv[4], kv[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) qv[i] = *reinterpret_cast<const float4*>(Qs + (ty + 16 * i) * PF_PITCH + d);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) kv[j] = *reinterpret_cast<const float4*>(Ks + (tx + 16 * j) * PF_PITCH + d);
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    sc[i][j] = fmaf(qv[i].x, kv[j].x, fmaf(qv[i].y, kv[j].y, fmaf(qv[i].z, kv[j].z, fmaf(qv[i].w, kv[j].w, sc[i][j]))));
-        }
-        // scale, causal mask, running softmax statistics per row (16 lanes share a row)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int qi = q0 + ty + 16 * i;
-            float mx = -INFINITY;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int kj = k0 + tx + 16 * j;
-                sc[i][j] = kj <= qi ? sc[i][j] * scale : -INFINITY;
-                mx = fmaxf(mx, sc[i][j]);
-            }
-#pragma unroll
-            for (int off = 8; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-            const float mnew = fmaxf(m[i], mx);
-            const float corr = m[i] == -INFINITY ? 0.f : expf(m[i] - mnew);
-            float sum = 0.f;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float p = sc[i][j] == -INFINITY ? 0.f : expf(sc[i][j] - mnew);
-                Ps[(ty + 16 * i) * PF_PITCH + tx + 16 * j] = p;
-                sum += p;
-            }
-#pragma unroll
-            for (int off = 8; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
-            l[i] = l[i] * corr + sum;
-            m[i] = mnew;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) o[i][j] *= corr;
-        }
-        __syncthreads();
-#pragma unroll 4
-        for (int c = 0; c < PF_T; c += 4) {
-            float4 pv[4], vv[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) pv[i] = *reinterpret_cast<const float4*>(Ps + (ty + 16 * i) * PF_PITCH + c);
-#pragma unroll
-            for (int kk = 0; kk < 4; ++kk) vv[kk] = *reinterpret_cast<const float4*>(Vs + (c + kk) * PF_PITCH + tx * 4);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                o[i][0] = fmaf(pv[i].x, vv[0].x, fmaf(pv[i].y, vv[1].x, fmaf(pv[i].z, vv[2].x, fmaf(pv[i].w, vv[3].x, o[i][0]))));
-                o[i][1] = fmaf(pv[i].x, vv[0].y, fmaf(pv[i].y, vv[1].y, fmaf(pv[i].z, vv[2].y, fmaf(pv[i].w, vv[3].y, o[i][1]))));
-                o[i][2] = fmaf(pv[i].x, vv[0].z, fmaf(pv[i].y, vv[1].z, fmaf(pv[i].z, vv[2].z, fmaf(pv[i].w, vv[3].z, o[i][2]))));
-                o[i][3] = fmaf(pv[i].x, vv[0].w, fmaf(pv[i].y, vv[1].w, fmaf(pv[i].z, vv[2].w, fmaf(pv[i].w, vv[3].w, o[i][3]))));
-            }
-        }
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int qi = q0 + ty + 16 * i;
-        if (qi < T) {
-            const float inv = 1.0f / l[i];
-            *reinterpret_cast<float4*>(out + (row0 + qi) * ldo + (size_t)h * PF_HD + tx * 4) =
-                make_float4(o[i][0] * inv, o[i][1] * inv, o[i][2] * inv, o[i][3] * inv);
-        }
-    }
-}
-
 __global__ void decode_swiglu_kernel(float* __restrict__ out, const float* __restrict__ gu, int H, int NB) {
     pdl_wait();
     const long i = blockIdx.x * (long)blockDim.x + threadIdx.x;
@@ -1002,16 +880,6 @@ int decode_kv_scatter(float* cache, const float* qkv, int ldqkv, int layer, int 
     return launch_k(decode_kv_scatter_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, cache, qkv, ldqkv, layer, NB, T, MS, QD, KV);
 }
 // head_dim 64 only (returns -3 otherwise); all pitches multiples of 4 floats
-int prefill_attention_f32(float* out, int ldo, const float* q, int ldq, const float* k, const float* v, int ldkv, int NB, int T, int NH,
-                          int NKV, int HD, float scale, cudaStream_t st) {
-    if (HD != PF_HD) return -3;
-    if (NKV <= 0 || NH % NKV || (ldo & 3) || (ldq & 3) || (ldkv & 3)) return -1;
-    const size_t smem = (size_t)4 * PF_T * PF_PITCH * sizeof(float);
-    static std::atomic<unsigned long long> attr_done{0};
-    if (first_use_on_current_device(attr_done))
-        cudaFuncSetAttribute(prefill_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return launch_k(prefill_attention_kernel, dim3((T + PF_T - 1) / PF_T, NH, NB), dim3(256), smem, st, out, ldo, q, ldq, k, v, ldkv, T, NH, NKV, scale);
-}
 int decode_swiglu(float* out, const float* gu, int NB, int H, cudaStream_t st) {
     const long n = (long)NB * H;
     return launch_k(decode_swiglu_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, out, gu, H, NB);

@@ -23,9 +23,6 @@ int decode_prep(bf16* a, int parts, const float* x, int ldx, int mode, const flo
                 const float* init_src, int ldr, int n_out, int rows, int C, cudaStream_t st);
 // prefill: cache[layer][0|1][b][t][:] = k | v columns of row b * T + t of the packed [q | k | v] matrix
 int decode_kv_scatter(float* cache, const float* qkv, int ldqkv, int layer, int NB, int T, int MS, int QD, int KV, cudaStream_t st);
-// fp32 causal attention over the prompt rows of each sequence (row = b * T + t), head_dim 64
-int prefill_attention_f32(float* out, int ldo, const float* q, int ldq, const float* k, const float* v, int ldkv, int NB, int T, int NH,
-                          int NKV, int HD, float scale, cudaStream_t st);
 int decode_swiglu(float* out, const float* gu, int NB, int H, cudaStream_t st);
 int decode_embed(float* out, int ttype, const void* table, const int* tokens, int NB, int D, cudaStream_t st);
 int decode_argmax(int* out, const float* logits, int NB, int V, int* pos_to_advance, cudaStream_t st);

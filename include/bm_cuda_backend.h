@@ -224,8 +224,9 @@ int bmc_decode_prep(bmc_ctx_t* ctx, void* d_a, int parts, const float* d_x, int 
 int bmc_decode_gemm(bmc_ctx_t* ctx, float* d_out, int ldo, const void* d_a, const void* d_w, int parts, int rows, int C, int OC);
 /* prefill (bmt_scheduler_copy_prefill_kv, src/baremetal/session.c:136): K | V columns of prompt row b * T + t into cache[layer][0|1][b][t] */
 int bmc_decode_kv_scatter(bmc_ctx_t* ctx, float* d_cache, const float* d_qkv, int ldqkv, int layer, int NB, int T, int MS, int QD, int KV);
-/* attention_forward_prefill (src/kernels/forward.metal): fp32 causal attention over the T prompt rows of each of NB sequences; head_dim 64
- * (-3 otherwise: use bmc_attention_forward with BMC_F32) */
+/* attention_forward_prefill_tiled (src/kernels/forward.metal:2024): causal attention over the T prompt rows of each of NB sequences,
+ * fp32 in and out, fp32-accurate on the tensor pipe (operands split into bf16 hi + lo, three tcgen05 products per product);
+ * head_dim 64 (-1 otherwise: use bmc_attention_forward with BMC_F32) */
 int bmc_prefill_attention(bmc_ctx_t* ctx, float* d_out, int ldo, const float* d_q, int ldq, const float* d_k, const float* d_v, int ldkv, int NB,
                           int T, int NH, int NKV, int HD, float scale);
 int bmc_decode_swiglu(bmc_ctx_t* ctx, float* d_out, const float* d_gate_up, int NB, int H);
