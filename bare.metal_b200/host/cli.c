@@ -14,6 +14,7 @@
 #ifndef BAREMETAL_TRAIN
 #define BAREMETAL_TRAIN
 #endif
+#include <math.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -77,8 +78,193 @@ static int exchange_nccl_id(const char* dir, int rank, unsigned char id[128], ch
     return -1;
 }
 
+/* ---- `parity`: the reference's architecture parity harness (test/parity/parity.c), fixture format "baremetal.parity/v1" ----
+ * A fixture is a JSON object {format, model, precision, prompt_token_ids[], generated_token_ids[], vocab_size, logits_file}
+ * next to a raw little-endian float32 file with the full-vocabulary logits after the prompt (test/parity/make_fixture.py).
+ * Checks, thresholds and output lines are the reference's: cosine of the prefill logits (0.9999 fp32, 0.999 otherwise), their
+ * argmax, and the greedy continuation token by token. */
+static char* read_text_file(const char* path) {
+    FILE* f = fopen(path, "rb");
+    if (!f) return NULL;
+    fseek(f, 0, SEEK_END);
+    const long n = ftell(f);
+    fseek(f, 0, SEEK_SET);
+    char* buf = (char*)malloc((size_t)n + 1);
+    if (!buf || fread(buf, 1, (size_t)n, f) != (size_t)n) { free(buf); fclose(f); return NULL; }
+    buf[n] = 0;
+    fclose(f);
+    return buf;
+}
+/* value text of member `key` of the top-level object (keys inside nested values or strings never match) */
+static const char* fx_value(const char* json, const char* key) {
+    const char* p = strchr(json, '{');
+    if (!p) return NULL;
+    const size_t klen = strlen(key);
+    int depth = 0;
+    for (; *p; ++p) {
+        if (*p == '"') {
+            const char* start = p + 1;
+            for (++p; *p && *p != '"'; ++p)
+                if (*p == '\\' && p[1]) ++p;
+            if (!*p) return NULL;
+            if (depth == 1 && (size_t)(p - start) == klen && strncmp(start, key, klen) == 0) {
+                const char* q = p + 1;
+                while (*q == ' ' || *q == '\t' || *q == '\n' || *q == '\r') ++q;
+                if (*q == ':') {
+                    ++q;
+                    while (*q == ' ' || *q == '\t' || *q == '\n' || *q == '\r') ++q;
+                    return q;
+                }
+            }
+        } else if (*p == '{' || *p == '[') {
+            ++depth;
+        } else if (*p == '}' || *p == ']') {
+            if (--depth <= 0) return NULL;
+        }
+    }
+    return NULL;
+}
+static int* fx_int_array(const char* json, const char* key, int* n_out) {
+    const char* v = fx_value(json, key);
+    *n_out = 0;
+    if (!v || *v != '[') return NULL;
+    int cap = 64, n = 0;
+    int* out = (int*)malloc((size_t)cap * sizeof(int));
+    for (const char* p = v + 1; out && *p && *p != ']';) {
+        if (*p == '-' || (*p >= '0' && *p <= '9')) {
+            char* end = NULL;
+            const long x = strtol(p, &end, 10);
+            if (n == cap) { cap *= 2; out = (int*)realloc(out, (size_t)cap * sizeof(int)); if (!out) break; }
+            out[n++] = (int)x;
+            p = end;
+        } else {
+            ++p;
+        }
+    }
+    *n_out = n;
+    return out;
+}
+static int fx_string(const char* json, const char* key, char* out, size_t cap) {
+    const char* v = fx_value(json, key);
+    if (!v || *v != '"') return -1;
+    size_t n = 0;
+    for (++v; *v && *v != '"' && n + 1 < cap; ++v) out[n++] = *v;
+    out[n] = 0;
+    return 0;
+}
+static int argmax_first(const float* x, int n) {   /* first index of the maximum (strict >), as the reference's sampler */
+    int b = 0;
+    for (int i = 1; i < n; i++)
+        if (x[i] > x[b]) b = i;
+    return b;
+}
+static int parity_main(int argc, char** argv) {
+    const char *model_dir = NULL, *fixture_path = NULL, *prec_arg = NULL;
+    int max_gen = 0, max_seq = 0;
+    for (int i = 2; i < argc; i++) {
+        if (strcmp(argv[i], "--model") == 0 && i + 1 < argc) model_dir = argv[++i];
+        else if (strcmp(argv[i], "--fixture") == 0 && i + 1 < argc) fixture_path = argv[++i];
+        else if (strcmp(argv[i], "--precision") == 0 && i + 1 < argc) prec_arg = argv[++i];
+        else if (strcmp(argv[i], "--gen") == 0 && i + 1 < argc) max_gen = atoi(argv[++i]);
+        else if (strcmp(argv[i], "--max-seq") == 0 && i + 1 < argc) max_seq = atoi(argv[++i]);
+        else model_dir = fixture_path = NULL;
+    }
+    if (!model_dir || !fixture_path) {
+        fprintf(stderr, "usage: %s parity --model DIR --fixture FILE [--precision fp32|bf16] [--gen N] [--max-seq N]\n", argv[0]);
+        return 2;
+    }
+    char* fx = read_text_file(fixture_path);
+    if (!fx) { fprintf(stderr, "cannot read fixture: %s\n", fixture_path); return 1; }
+    char prec_name[32] = "fp32", model_name[128] = "", logits_file[512] = "";
+    fx_string(fx, "precision", prec_name, sizeof prec_name);
+    if (prec_arg) snprintf(prec_name, sizeof prec_name, "%s", prec_arg);
+    fx_string(fx, "model", model_name, sizeof model_name);
+    int np = 0, ng = 0;
+    int* prompt = fx_int_array(fx, "prompt_token_ids", &np);
+    int* golden_gen = fx_int_array(fx, "generated_token_ids", &ng);
+    if (!prompt || !golden_gen || np < 1 || ng < 1) { fprintf(stderr, "fixture missing prompt_token_ids or generated_token_ids\n"); return 1; }
+    if (max_gen > 0 && max_gen < ng) ng = max_gen;
+    const char* vv = fx_value(fx, "vocab_size");
+    const int vocab = vv ? atoi(vv) : 0;
+    if (vocab <= 0 || fx_string(fx, "logits_file", logits_file, sizeof logits_file)) { fprintf(stderr, "fixture missing vocab_size or logits_file\n"); return 1; }
+    char logits_path[2048];
+    const char* slash = strrchr(fixture_path, '/');
+    if (slash) snprintf(logits_path, sizeof logits_path, "%.*s/%s", (int)(slash - fixture_path), fixture_path, logits_file);
+    else snprintf(logits_path, sizeof logits_path, "%s", logits_file);
+    float* golden_logits = (float*)malloc((size_t)vocab * sizeof(float));
+    FILE* lf = fopen(logits_path, "rb");
+    if (!lf || !golden_logits || fread(golden_logits, sizeof(float), (size_t)vocab, lf) != (size_t)vocab) {
+        fprintf(stderr, "cannot read %d logits from %s\n", vocab, logits_path);
+        return 1;
+    }
+    fclose(lf);
+    if (strcmp(prec_name, "fp16") == 0) { fprintf(stderr, "fp16 weights are not supported by this backend (use bf16 or fp32)\n"); return 1; }
+    const int is_fp32 = strcmp(prec_name, "bf16") != 0;
+    printf("parity: %s (%s)\n", model_name[0] ? model_name : model_dir, prec_name);
+    printf("  prompt: %d tokens, gen: %d\n", np, ng);
+
+    bm_context_t* ctx = bm_create(BM_DEVICE_CUDA);
+    if (!ctx) { fprintf(stderr, "bm_create failed\n"); return 1; }
+    bm_arch_t a;
+    memset(&a, 0, sizeof a);   /* placeholder: bm_load_weights takes the architecture from the checkpoint */
+    a.dim = 64; a.hidden_dim = 64; a.n_layers = 1; a.n_heads = 1; a.n_kv_heads = 1; a.vocab_size = 8; a.padded_vocab_size = 8;
+    a.max_seq_len = 64; a.head_dim = 64; a.norm = BM_NORM_RMSNORM; a.activation = BM_ACT_SWIGLU; a.pos_enc = BM_POS_ROPE;
+    a.attention = BM_ATTN_GQA; a.weight_tie = 1; a.gated_mlp = 1; a.rope_theta = 10000.0f;
+    a.precision = is_fp32 ? BM_PRECISION_FP32 : BM_PRECISION_BF16;
+    bm_model_t* m = bm_create_model(ctx, &a);
+    if (!m) return 1;
+    bm_load_weights(m, model_dir);
+    if (bm_get_num_parameters(m) <= 64 * 64 * 8) { fprintf(stderr, "failed to load weights from %s\n", model_dir); return 1; }
+    if (vocab != bmx_model_vocab_size(m)) { fprintf(stderr, "vocab mismatch: fixture %d, model %d\n", vocab, bmx_model_vocab_size(m)); return 1; }
+    bm_compile(m);
+    const int need = np + ng + 1;
+    bm_session_t* sess = bmx_create_session_batched(ctx, m, 1, max_seq > need ? max_seq : need);
+    if (!sess) { fprintf(stderr, "session creation failed\n"); return 1; }
+    bm_reset_session(sess);
+    float* logits = bm_forward(sess, prompt, np);
+    if (!logits) { fprintf(stderr, "forward failed\n"); return 1; }
+    double dot = 0.0, na = 0.0, nb = 0.0, max_diff = 0.0;
+    for (int i = 0; i < vocab; i++) {
+        dot += (double)logits[i] * golden_logits[i];
+        na += (double)logits[i] * logits[i];
+        nb += (double)golden_logits[i] * golden_logits[i];
+        const double d = fabs((double)logits[i] - (double)golden_logits[i]);
+        if (d > max_diff) max_diff = d;
+    }
+    const double cosv = (na > 0 && nb > 0) ? dot / (sqrt(na) * sqrt(nb)) : 0.0;
+    const double threshold = is_fp32 ? 0.9999 : 0.999;
+    int failures = 0;
+    printf("  logits cos: %.7f (min %.4f)  max|diff|: %.3e\n", cosv, threshold, max_diff);
+    if (cosv < threshold) { printf("FAIL: logits cosine below threshold\n"); failures++; }
+    const int got_argmax = argmax_first(logits, vocab), want_argmax = argmax_first(golden_logits, vocab);
+    printf("  argmax: got %d, want %d\n", got_argmax, want_argmax);
+    if (got_argmax != want_argmax) { printf("FAIL: argmax mismatch\n"); failures++; }
+    int* gen = (int*)malloc((size_t)ng * sizeof(int));
+    if (!gen) return 1;
+    gen[0] = got_argmax;
+    int n_done = 1;
+    for (int i = 1; i < ng; i++, n_done++) {
+        logits = bm_step(sess, gen[i - 1]);
+        if (!logits) { printf("FAIL: step %d returned NULL\n", i); failures++; break; }
+        gen[i] = argmax_first(logits, vocab);
+    }
+    int first_bad = -1;
+    for (int i = 0; i < n_done; i++)
+        if (gen[i] != golden_gen[i]) { first_bad = i; break; }
+    if (first_bad < 0 && n_done == ng) printf("  tokens: match (%d/%d)\n", ng, ng);
+    else if (first_bad >= 0) { printf("FAIL: token mismatch at %d: got %d, want %d\n", first_bad, gen[first_bad], golden_gen[first_bad]); failures++; }
+    free(gen); free(golden_logits); free(golden_gen); free(prompt); free(fx);
+    bm_destroy_session(sess);
+    bm_destroy_model(m);
+    bm_destroy(ctx);
+    if (failures) { printf("PARITY FAIL\n"); return 1; }
+    printf("PARITY PASS\n");
+    return 0;
+}
+
 static int usage(const char* argv0) {
     fprintf(stderr, "Usage: %s train <model_dir|model.bin> <data_file> <output_dir> [options]\n", argv0);
+    fprintf(stderr, "       %s parity --model DIR --fixture FILE [--precision fp32|bf16] [--gen N] [--max-seq N]\n", argv0);
     fprintf(stderr, "  <data_file>         int32 token ids (*.bin, *.tok, *.tokens) or lcg:<seed> for the synthetic stream\n");
     fprintf(stderr, "  --steps <int>       Max training steps (default: 100)\n");
     fprintf(stderr, "  --seq-len <int>     Sequence length S (default: 64)\n");
@@ -95,6 +281,7 @@ static int usage(const char* argv0) {
 }
 
 int main(int argc, char** argv) {
+    if (argc >= 2 && strcmp(argv[1], "parity") == 0) return parity_main(argc, argv);
     if (argc < 2 || strcmp(argv[1], "train") != 0 || argc < 5) return usage(argv[0]);
     const char *model_path = argv[2], *data_file = argv[3], *output_dir = argv[4];
     int max_steps = 100, seq_len = 64, batch_size = 1, grad_accum = 1, save_every = 0, lora_rank = 0;
