@@ -154,8 +154,6 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     const uint32_t tmem_base = bars.tmem_base;
     volatile int* abort_flag = &bars.abort_flag;
 
-    // bytes one stage receives: this CTA's A tile and B tile — for a pair, both CTAs' (A tile + half B tile) on the leader's barrier
-    const uint32_t stage_tx_bytes = CTAS == 2 ? (uint32_t)(2 * (BM * BK * 2 + (p.BN / 2) * BK * 2)) : (uint32_t)(BM * BK * 2 + p.BN * BK * 2);
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
@@ -176,48 +174,49 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                 for (int kb = kb0; kb < kb1; kb += KPS, s = (s + 1 == NST ? 0 : s + 1), ph ^= (s == 0)) {
                     if (!mbar_wait(&bars.empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
                     const int g = min(KPS, kb1 - kb);   // k-blocks in this stage (the last stage of a unit may hold fewer)
+                    uint8_t* a_stage = sA + s * KPS * A_STAGE_BYTES;
+                    uint8_t* b_stage = sB + s * KPS * BST;
+                    const int k0 = kb * BK;
+                    // A K-major operand arrives one k-block per copy (a 128-byte swizzled row cannot be wider than 64 elements).
+                    // An MN-major operand arrives one 64-wide group of rows per copy, KPS k-blocks deep: a copy costs the issuing
+                    // thread as much as a UMMA costs its thread, and the weight-gradient GEMMs (both operands MN-major, four
+                    // copies per k-block) were bound by this thread. Such a box always holds KPS k-blocks, also when the unit ends
+                    // after the first (what lies beyond K is zero-filled; what lies beyond the unit's split is not used).
+                    const uint32_t tx = (uint32_t)((p.a_mn ? KPS : g) * A_STAGE_BYTES + (p.b_mn ? KPS : g) * BST) * (CTAS == 2 ? 2u : 1u);
                     if (CTAS == 2) {
                         const uint32_t full_leader = mapa_shared(&bars.full[s], 0);
-                        if (rank == 0) mbar_expect_tx(&bars.full[s], stage_tx_bytes * (uint32_t)g);
-                        for (int j = 0; j < g; ++j) {
-                            uint8_t* a_dst = sA + (s * KPS + j) * A_STAGE_BYTES;
-                            uint8_t* b_dst = sB + (s * KPS + j) * BST;
-                            const int k0 = (kb + j) * BK;
-                            if (!p.a_mn) {
-                                tma_load_2d_pair(a_dst, &tmA, full_leader, k0, m0);
-                            } else {
-                                tma_load_2d_pair(a_dst, &tmA, full_leader, m0, k0);
-                                tma_load_2d_pair(a_dst + MN_BOX_BYTES, &tmA, full_leader, m0 + 64, k0);
-                            }
-                            if (!p.b_mn) {
-                                tma_load_2d_pair(b_dst, &tmB, full_leader, k0, n0);
-                            } else {
-                                for (int jb = 0; jb < bn_local / 64; ++jb)
-                                    tma_load_2d_pair(b_dst + jb * MN_BOX_BYTES, &tmB, full_leader, n0 + 64 * jb, k0);
-                            }
+                        if (rank == 0) mbar_expect_tx(&bars.full[s], tx);
+                        if (!p.a_mn) {
+                            for (int j = 0; j < g; ++j) tma_load_2d_pair(a_stage + j * A_STAGE_BYTES, &tmA, full_leader, k0 + j * BK, m0);
+                        } else {
+                            tma_load_2d_pair(a_stage, &tmA, full_leader, m0, k0);
+                            tma_load_2d_pair(a_stage + KPS * MN_BOX_BYTES, &tmA, full_leader, m0 + 64, k0);
+                        }
+                        if (!p.b_mn) {
+                            for (int j = 0; j < g; ++j) tma_load_2d_pair(b_stage + j * BST, &tmB, full_leader, k0 + j * BK, n0);
+                        } else {
+                            for (int jb = 0; jb < bn_local / 64; ++jb)
+                                tma_load_2d_pair(b_stage + jb * KPS * MN_BOX_BYTES, &tmB, full_leader, n0 + 64 * jb, k0);
                         }
                         continue;
                     }
-                    mbar_expect_tx(&bars.full[s], stage_tx_bytes * (uint32_t)g);
-                    for (int j = 0; j < g; ++j) {
-                        uint8_t* a_dst = sA + (s * KPS + j) * A_STAGE_BYTES;
-                        uint8_t* b_dst = sB + (s * KPS + j) * BST;
-                        const int k0 = (kb + j) * BK;
-                        if (!p.a_mn) {
-                            tma_load_2d(a_dst, &tmA, &bars.full[s], k0, m0);
-                        } else {
-                            tma_load_2d(a_dst, &tmA, &bars.full[s], m0, k0);
-                            tma_load_2d(a_dst + MN_BOX_BYTES, &tmA, &bars.full[s], m0 + 64, k0);
+                    mbar_expect_tx(&bars.full[s], tx);
+                    if (!p.a_mn) {
+                        for (int j = 0; j < g; ++j) tma_load_2d(a_stage + j * A_STAGE_BYTES, &tmA, &bars.full[s], k0 + j * BK, m0);
+                    } else {
+                        tma_load_2d(a_stage, &tmA, &bars.full[s], m0, k0);
+                        tma_load_2d(a_stage + KPS * MN_BOX_BYTES, &tmA, &bars.full[s], m0 + 64, k0);
+                    }
+                    if (EPI == GEMM_EPI_SWIGLU_FWD) {
+                        for (int j = 0; j < g; ++j) {
+                            tma_load_2d(b_stage + j * BST, &tmB, &bars.full[s], k0 + j * BK, n0);
+                            tma_load_2d(b_stage + j * BST + (p.BN / 2) * BK * 2, &tmB, &bars.full[s], k0 + j * BK, n_second);
                         }
-                        if (EPI == GEMM_EPI_SWIGLU_FWD) {
-                            tma_load_2d(b_dst, &tmB, &bars.full[s], k0, n0);
-                            tma_load_2d(b_dst + (p.BN / 2) * BK * 2, &tmB, &bars.full[s], k0, n_second);
-                        } else if (!p.b_mn) {
-                            tma_load_2d(b_dst, &tmB, &bars.full[s], k0, n0);
-                        } else {
-                            for (int jb = 0; jb < p.BN / 64; ++jb)
-                                tma_load_2d(b_dst + jb * MN_BOX_BYTES, &tmB, &bars.full[s], n0 + 64 * jb, k0);
-                        }
+                    } else if (!p.b_mn) {
+                        for (int j = 0; j < g; ++j) tma_load_2d(b_stage + j * BST, &tmB, &bars.full[s], k0 + j * BK, n0);
+                    } else {
+                        for (int jb = 0; jb < p.BN / 64; ++jb)
+                            tma_load_2d(b_stage + jb * KPS * MN_BOX_BYTES, &tmB, &bars.full[s], n0 + 64 * jb, k0);
                     }
                 }
             }
@@ -231,18 +230,19 @@ gemm_bf16_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         if (lane == 0 && rank == 0) {
             const uint32_t idesc = umma_idesc_bf16_f32(BM * CTAS, p.BN, p.a_mn, p.b_mn);
             // K-major operand: rows of 128 B, 8-row swizzle atoms 1024 B apart; one UMMA (K=16) = 32 B along the row.
-            // MN-major operand: 64(mn) x 64(k) boxes of 8 KB; 8-deep k groups 1024 B apart inside a box,
-            // 64-wide mn groups one box apart; one UMMA (K=16) = two k groups = 2048 B.
-            const uint32_t a_lbo = p.a_mn ? MN_BOX_BYTES : 16, a_sbo = 1024, a_kstep = p.a_mn ? 2048 : 32;
-            const uint32_t b_lbo = p.b_mn ? MN_BOX_BYTES : 16, b_sbo = 1024, b_kstep = p.b_mn ? 2048 : 32;
+            // MN-major operand: per 64-wide mn group one box of 64(mn) x KPS*64(k), KPS * 8 KB; 8-deep k groups 1024 B apart inside
+            // a box, mn groups one box apart; one UMMA (K=16) = two k groups = 2048 B; a k-block = 8 KB further into every box.
+            const uint32_t a_lbo = p.a_mn ? KPS * MN_BOX_BYTES : 16, a_sbo = 1024, a_kstep = p.a_mn ? 2048 : 32;
+            const uint32_t b_lbo = p.b_mn ? KPS * MN_BOX_BYTES : 16, b_sbo = 1024, b_kstep = p.b_mn ? 2048 : 32;
             // One thread issues every UMMA, so the instructions between two of them are on the critical path whenever a UMMA
             // is shorter than they are (tiles narrower than 256 columns). The descriptors of stage 0 are built once; a stage or a
             // k step only moves the 14-bit start-address field (units of 16 bytes; shared memory ends below 256 KB, so the
             // field never carries into its neighbour).
             const uint64_t adesc0 = umma_smem_desc_sw128(smem_u32(sA), a_lbo, a_sbo);
             const uint64_t bdesc0 = umma_smem_desc_sw128(smem_u32(sB), b_lbo, b_sbo);
-            const uint32_t a_kb16 = A_STAGE_BYTES >> 4, b_kb16 = (uint32_t)BST >> 4;          // one k-block inside a stage
-            const uint32_t a_st16 = KPS * a_kb16, b_st16 = KPS * b_kb16, a_k16 = a_kstep >> 4, b_k16 = b_kstep >> 4;
+            const uint32_t a_kb16 = (p.a_mn ? MN_BOX_BYTES : A_STAGE_BYTES) >> 4;             // one k-block inside a stage
+            const uint32_t b_kb16 = (uint32_t)(p.b_mn ? MN_BOX_BYTES : BST) >> 4;
+            const uint32_t a_st16 = KPS * (A_STAGE_BYTES >> 4), b_st16 = KPS * ((uint32_t)BST >> 4), a_k16 = a_kstep >> 4, b_k16 = b_kstep >> 4;
             int s = 0;
             uint32_t ph = 0, a_off = 0, b_off = 0;   // stage s starts a_off / b_off sixteen-byte units into its ring
             int it = 0;
@@ -828,6 +828,7 @@ int gemm_bf16_umma(const GemmProblem& g, int* err_flag, cudaStream_t stream) {
     }
     if (splits > p.kb_total) splits = p.kb_total;
     p.kb_per_split = (p.kb_total + splits - 1) / splits;
+    if (splits > 1) p.kb_per_split = (p.kb_per_split + KPS - 1) / KPS * KPS;   // whole ring stages per split: only the end of K may leave one half empty
     p.splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;
     p.C = g.C; p.ldc = g.ldc; p.out_mode = g.out_mode;
     p.R = g.R; p.ldr = g.ldr;
@@ -838,11 +839,11 @@ int gemm_bf16_umma(const GemmProblem& g, int* err_flag, cudaStream_t stream) {
     CUtensorMap tmA, tmB;
     int rc;
     if (!p.a_mn) rc = make_map(&tmA, g.A, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda, BK, BM);
-    else         rc = make_map(&tmA, g.A, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)g.lda, 64, BK);
+    else         rc = make_map(&tmA, g.A, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)g.lda, 64, KPS * BK);
     if (rc) return rc;
     if (!p.b_mn) rc = make_map(&tmB, g.B, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb, BK,
                                (uint32_t)(g.epi == GEMM_EPI_SWIGLU_FWD ? p.BN / 2 : p.BN / ctas));
-    else         rc = make_map(&tmB, g.B, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb, 64, BK);
+    else         rc = make_map(&tmB, g.B, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb, 64, KPS * BK);
     if (rc) return rc;
 
     const long units = (long)p.tiles_m * p.tiles_n * p.splits;
