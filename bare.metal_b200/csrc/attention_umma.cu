@@ -132,7 +132,7 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         mbar_init(&bars.q_full, 1);
         for (int i = 0; i < FWD_KV_STAGES; ++i) {
             mbar_init(&bars.kv_full[i], 1);
-            mbar_init(&bars.kv_empty[i], 1);
+            mbar_init(&bars.kv_empty[i], n_b > 0 ? 2 : 1);   // one arrival per issuing thread
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&bars.s_full[i], 1);
@@ -171,25 +171,28 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 tma_load_2d(sV + st * KV_TILE_BYTES, &tmV, &bars.kv_full[st], kh * FHD, row0 + j * FK);
             }
         }
-    } else if (warp == 1) {
-        // ------------------------------ UMMA issuer --------------------------------
-        if (lane == 0) {
+    } else if (warp == 1 || warp == 2) {
+        // ------------------------------ UMMA issuers: warp 1 for query tile A, warp 2 for tile B ------------------
+        // One thread per query tile: a thread that issues for both tiles meets their barriers in a fixed order (five waits per key
+        // tile at ~160 cycles each, 24 issues at ~53) and makes one tile wait behind the other's.
+        const int x = warp - 1;
+        const int n_this = x ? n_b : n_a;
+        if (lane == 0 && n_this > 0) {
             const uint32_t idesc_s = umma_idesc_bf16_f32(FQ, FK, 0, 0);    // S = Q K^T : both operands K-major
             const uint32_t idesc_o = umma_idesc_bf16_f32(FQ, FHD, 0, 1);   // O += P V  : P K-major, V MN-major
             // Descriptors differ only in their 14-bit start-address field (address >> 4), so each is built once and
             // stepped by plain integer adds: +2 per 32 B (one K-step inside a 128-byte row), +128 per 2048 B
             // (16 rows of an MN-major tile), +1024 per 16 KB (tile stage / key half).
-            const uint64_t qd0 = umma_smem_desc_sw128(smem_u32(sQ), 16, 1024);
+            const uint64_t qd = umma_smem_desc_sw128(smem_u32(sQ), 16, 1024) + (uint64_t)(x * (Q_BYTES >> 4));
             const uint64_t kd0 = umma_smem_desc_sw128(smem_u32(sK), 16, 1024);
             const uint64_t vd0 = umma_smem_desc_sw128(smem_u32(sV), FK * 128, 1024);
-            auto issue_qk = [&](int x, int j) {
+            auto issue_qk = [&](int j) {
                 const uint64_t kd = kd0 + (uint64_t)((j % FWD_KV_STAGES) * (KV_TILE_BYTES >> 4));
-                const uint64_t qd = qd0 + (uint64_t)(x * (Q_BYTES >> 4));
 #pragma unroll
                 for (int k = 0; k < FHD / 16; ++k) umma_bf16_ss(tmem + x * FK, qd + 2 * k, kd + 2 * k, idesc_s, k > 0 ? 1u : 0u);
                 umma_commit(&bars.s_full[x]);
             };
-            auto issue_pv = [&](int x, int j) {
+            auto issue_pv = [&](int j) {
                 const uint64_t vd = vd0 + (uint64_t)((j % FWD_KV_STAGES) * (KV_TILE_BYTES >> 4));
 #pragma unroll
                 for (int k = 0; k < FK / 16; ++k)
@@ -201,33 +204,26 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             bool ok = mbar_wait(&bars.q_full, 0, abort_flag) && mbar_wait(&bars.kv_full[0], 0, abort_flag);
             if (ok) {
                 tc_fence_after_sync();
-                issue_qk(0, 0);
-                if (n_b > 0) issue_qk(1, 0);
+                issue_qk(0);
             }
             for (int j = 0; j < n_tiles && ok; ++j) {
                 // S of the NEXT key tile is issued as soon as the softmax warps have read this tile's S out of TMEM (s_free),
                 // i.e. before P V of this tile: the scores of tile j+1 are ready when the softmax of tile j ends, and the
                 // softmax of tile j+1 runs while the tensor core does P V of tile j.
-                bool next_loaded = false;
-                for (int x = 0; x < 2 && ok; ++x) {
-                    const int n_this = x ? n_b : n_a;
-                    if (j + 1 >= n_this) continue;
+                if (j + 1 < n_this) {
                     if (!mbar_wait(&bars.s_free[x], j & 1, abort_flag)) { ok = false; break; }
-                    if (!next_loaded) {
-                        if (!mbar_wait(&bars.kv_full[(j + 1) % FWD_KV_STAGES], ((j + 1) / FWD_KV_STAGES) & 1, abort_flag)) { ok = false; break; }
-                        next_loaded = true;
-                    }
+                    if (!mbar_wait(&bars.kv_full[(j + 1) % FWD_KV_STAGES], ((j + 1) / FWD_KV_STAGES) & 1, abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
-                    issue_qk(x, j + 1);
+                    issue_qk(j + 1);
                 }
-                for (int x = 0; x < 2 && ok; ++x) {
-                    const int n_this = x ? n_b : n_a;
-                    if (j >= n_this) continue;
+                if (j < n_this) {
                     if (!mbar_wait(&bars.p_ready[x], j & 1, abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
-                    issue_pv(x, j);
+                    issue_pv(j);
+                    umma_commit(&bars.kv_empty[j % FWD_KV_STAGES]);  // every UMMA of this query tile that reads the stage has been issued
+                } else {
+                    mbar_arrive(&bars.kv_empty[j % FWD_KV_STAGES]);  // a key tile this query tile does not attend
                 }
-                if (ok) umma_commit(&bars.kv_empty[j % FWD_KV_STAGES]);  // every UMMA that reads this stage has been issued
             }
         }
     }
