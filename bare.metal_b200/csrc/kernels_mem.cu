@@ -581,14 +581,20 @@ xent_kernel(T* __restrict__ logits, float* __restrict__ row_loss, const int* __r
         Vec<T>::store(lr + v * VN, o);
     }
 }
-// bf16 rows of up to XENT_THREADS * XENT_NV * 8 = 49152 logits stay in registers from the first sweep to the last: the row is read
-// from memory once and written once (the general kernel above reads it three times, twice from L2). The arithmetic is the general
-// kernel's, element for element (exp evaluated again in the last sweep rather than parked at reduced precision), so the two differ
-// only in the order of the fp32 row sum.
-constexpr int XENT_NV = 12;
-__global__ void __launch_bounds__(XENT_THREADS)
-xent_rowreg_kernel(bf16* __restrict__ logits, float* __restrict__ row_loss, const int* __restrict__ targets,
-                   const float* __restrict__ row_weight, int V, int ldv, float grad_scale, int* __restrict__ err) {
+// bf16 rows of up to 49152 logits are parked in shared memory (96 KB) by the first sweep, so the row is read from memory once and
+// written once (the general kernel above reads it three times, twice from L2), and two CTAs share an SM: while one waits for its
+// row to arrive the other does its arithmetic. (A variant that kept the row in registers, one CTA per SM, ran at the general
+// kernel's speed: load, arithmetic and store phases of the one resident row do not overlap.)
+constexpr int XENT_SMEM_MAX_V = 49152;
+__device__ __forceinline__ float exp2_fast(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__global__ void __launch_bounds__(XENT_THREADS, 2)
+xent_rowsmem_kernel(bf16* __restrict__ logits, float* __restrict__ row_loss, const int* __restrict__ targets,
+                    const float* __restrict__ row_weight, int V, int ldv, float grad_scale, int* __restrict__ err) {
+    extern __shared__ uint4 xent_row[];   // V / 8 vectors of eight bf16
     __shared__ float red[XENT_THREADS / 32];
     __shared__ float bcast;
     const int row = blockIdx.x;
@@ -601,17 +607,25 @@ xent_rowreg_kernel(bf16* __restrict__ logits, float* __restrict__ row_loss, cons
         if (threadIdx.x == 0) row_loss[row] = 0.f;
         return;
     }
-    uint4 raw[XENT_NV];
     float mx = -INFINITY;
+    for (int v0 = threadIdx.x; v0 < nvec; v0 += 4 * XENT_THREADS) {   // four loads in flight per thread
+        uint4 r[4];
 #pragma unroll
-    for (int k = 0; k < XENT_NV; ++k) {
-        const int v = threadIdx.x + k * XENT_THREADS;
-        raw[k] = make_uint4(0xff80ff80u, 0xff80ff80u, 0xff80ff80u, 0xff80ff80u);   // -inf pairs: neutral for the maximum, exp gives 0
-        if (v < nvec) raw[k] = *reinterpret_cast<const uint4*>(lr + v * 8);
-        float f[8];
-        Vec<bf16>::unpack(raw[k], f);
+        for (int k = 0; k < 4; ++k) {
+            const int v = v0 + k * XENT_THREADS;
+            if (v < nvec) r[k] = *reinterpret_cast<const uint4*>(lr + v * 8);
+        }
 #pragma unroll
-        for (int i = 0; i < 8; ++i) mx = fmaxf(mx, f[i]);
+        for (int k = 0; k < 4; ++k) {
+            const int v = v0 + k * XENT_THREADS;
+            if (v < nvec) {
+                xent_row[v] = r[k];
+                float f[8];
+                Vec<bf16>::unpack(r[k], f);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) mx = fmaxf(mx, f[i]);
+            }
+        }
     }
     mx = warp_max(mx);
     if (lane == 0) red[warp] = mx;
@@ -623,18 +637,17 @@ xent_rowreg_kernel(bf16* __restrict__ logits, float* __restrict__ row_loss, cons
     }
     __syncthreads();
     mx = bcast;
-    const int tgt = targets[row];
-    const bool tgt_ok = (unsigned)tgt < (unsigned)V;
-    float x_tgt = 0.f;   // the target's logit, seen by the thread that holds it
     float sum = 0.f;
-#pragma unroll
-    for (int k = 0; k < XENT_NV; ++k) {
-        const int v = threadIdx.x + k * XENT_THREADS;
+    // exp(x - max) = 2^(x * log2(e) - max * log2(e)): one FMA and one ex2.approx (relative error 2^-22, far below the bf16 rounding of
+    // the gradient) instead of libm's expf, whose two evaluations per element made the kernel arithmetic-bound (1.7 ms for 1.0 ms
+    // of memory traffic)
+    constexpr float L2E = 1.4426950408889634f;
+    const float mxl = -mx * L2E;
+    for (int v = threadIdx.x; v < nvec; v += XENT_THREADS) {   // a thread re-reads the vectors it stored itself
         float f[8];
-        Vec<bf16>::unpack(raw[k], f);
-        if (tgt_ok && (tgt >> 3) == v) x_tgt = f[tgt & 7];
+        Vec<bf16>::unpack(xent_row[v], f);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) sum += expf(f[i] - mx);
+        for (int i = 0; i < 8; ++i) sum += exp2_fast(fmaf(f[i], L2E, mxl));
     }
     sum = warp_sum(sum);
     __syncthreads();
@@ -648,28 +661,28 @@ xent_rowreg_kernel(bf16* __restrict__ logits, float* __restrict__ row_loss, cons
     __syncthreads();
     sum = bcast;
     const float inv = 1.0f / sum;
-    if (tgt_ok && ((tgt >> 3) % XENT_THREADS) == (int)threadIdx.x && (tgt >> 3) < nvec) {
-        const float nll = -(x_tgt - mx - logf(sum));
+    // A target outside [0, V) on a row that counts is never used as an index: the row's loss is 0, its gradient is the plain
+    // softmax, and the error word is set.
+    const int tgt = targets[row];
+    const bool tgt_ok = (unsigned)tgt < (unsigned)V;
+    if (threadIdx.x == 0) {
+        float nll = 0.f;
+        if (tgt_ok) nll = -(__bfloat162float(reinterpret_cast<const bf16*>(xent_row)[tgt]) - mx - logf(sum));
         row_loss[row] = row_weight ? nll * grad_scale : nll;
+        if (!tgt_ok && err) atomicExch(err, BMB_ERR_BAD_TARGET);
     }
-    if (!tgt_ok && threadIdx.x == 0) {   // never used as an index: zero loss, plain softmax gradient, error word set
-        row_loss[row] = 0.f;
-        if (err) atomicExch(err, BMB_ERR_BAD_TARGET);
-    }
+    const float ps = inv * grad_scale;
+    const int tv = tgt_ok ? (tgt >> 3) : -1;
+    for (int v = threadIdx.x; v < nvec; v += XENT_THREADS) {
+        float f[8], g[8];
+        Vec<bf16>::unpack(xent_row[v], f);
 #pragma unroll
-    for (int k = 0; k < XENT_NV; ++k) {
-        const int v = threadIdx.x + k * XENT_THREADS;
-        if (v >= nvec) continue;
-        float f[8];
-        Vec<bf16>::unpack(raw[k], f);
+        for (int i = 0; i < 8; ++i) g[i] = exp2_fast(fmaf(f[i], L2E, mxl)) * ps;
+        if (v == tv) g[tgt & 7] -= grad_scale;   // (p - 1) * scale for the target's element
         uint4 o;
         __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
-        for (int i = 0; i < 8; i += 2) {
-            const float g0 = (expf(f[i] - mx) * inv - (v * 8 + i == tgt ? 1.0f : 0.0f)) * grad_scale;
-            const float g1 = (expf(f[i + 1] - mx) * inv - (v * 8 + i + 1 == tgt ? 1.0f : 0.0f)) * grad_scale;
-            h[i >> 1] = __floats2bfloat162_rn(g0, g1);
-        }
+        for (int i = 0; i < 8; i += 2) h[i >> 1] = __floats2bfloat162_rn(g[i], g[i + 1]);
         *reinterpret_cast<uint4*>(lr + v * 8) = o;
     }
 }
@@ -679,8 +692,12 @@ int xent_forward_backward(T* logits, float* row_loss, const int* targets, const 
                           int* err, cudaStream_t st) {
     if (V % Vec<T>::N || ldv % Vec<T>::N || !aligned16(logits)) return -1;
     if constexpr (sizeof(T) == 2) {
-        if (V / 8 <= XENT_THREADS * XENT_NV) {
-            xent_rowreg_kernel<<<N, XENT_THREADS, 0, st>>>(logits, row_loss, targets, row_weight, V, ldv, grad_scale, err);
+        if (V <= XENT_SMEM_MAX_V) {
+            static std::atomic<unsigned long long> attr_done{0};
+            if (first_use_on_current_device(attr_done) &&
+                cudaFuncSetAttribute(xent_rowsmem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, XENT_SMEM_MAX_V * 2) != cudaSuccess)
+                return -5;
+            xent_rowsmem_kernel<<<N, XENT_THREADS, (size_t)V * 2, st>>>(logits, row_loss, targets, row_weight, V, ldv, grad_scale, err);
             return 0;
         }
     }
