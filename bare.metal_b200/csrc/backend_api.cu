@@ -587,25 +587,25 @@ int bmc_decode_rmsnorm(bmc_ctx_t* ctx, float* d_out, const float* d_x, const flo
     BMC_CHECK_CTX(ctx);
     return note(ctx, decode_rmsnorm(d_out, d_x, d_w, NB, C, eps, ctx->stream));
 }
-int bmc_decode_rope_kv(bmc_ctx_t* ctx, float* d_qkv, float* d_cache, const float* d_cs_table, const int* d_pos, int layer, int NB, int MS,
+int bmc_decode_rope_kv(bmc_ctx_t* ctx, float* d_qkv, void* d_cache, int cache_dtype, const float* d_cs_table, const int* d_pos, int layer, int NB, int MS,
                        int NH, int NKV, int HD) {
     BMC_CHECK_CTX(ctx);
-    return note(ctx, decode_rope_kv(d_qkv, d_cache, d_cs_table, d_pos, layer, NB, MS, NH, NKV, HD, ctx->stream));
+    return note(ctx, decode_rope_kv(d_qkv, d_cache, cache_dtype == BMC_BF16, d_cs_table, d_pos, layer, NB, MS, NH, NKV, HD, ctx->stream));
 }
 size_t bmc_decode_attention_scratch_bytes(int NB, int MS, int NH, int NKV, int HD) {
     return decode_attention_scratch_bytes(NB, MS, NH, NKV, HD) + 16;
 }
-int bmc_decode_attention(bmc_ctx_t* ctx, float* d_out, const float* d_qkv, const float* d_cache, const int* d_pos, void* d_scratch, int layer,
+int bmc_decode_attention(bmc_ctx_t* ctx, float* d_out, const float* d_qkv, const void* d_cache, int cache_dtype, const int* d_pos, void* d_scratch, int layer,
                          int NB, int MS, int NH, int NKV, int HD, float scale) {
     BMC_CHECK_CTX(ctx);
-    return note(ctx, decode_attention(d_out, d_qkv, const_cast<float*>(d_cache), nullptr, d_pos, d_scratch, layer, NB, MS, NH, NKV, HD, scale,
+    return note(ctx, decode_attention(d_out, d_qkv, const_cast<void*>(d_cache), cache_dtype == BMC_BF16, nullptr, d_pos, d_scratch, layer, NB, MS, NH, NKV, HD, scale,
                                       ctx->stream));
 }
-int bmc_decode_attention_fused(bmc_ctx_t* ctx, float* d_out, const float* d_qkv, float* d_cache, const float* d_cs_table, const int* d_pos,
+int bmc_decode_attention_fused(bmc_ctx_t* ctx, float* d_out, const float* d_qkv, void* d_cache, int cache_dtype, const float* d_cs_table, const int* d_pos,
                                void* d_scratch, int layer, int NB, int MS, int NH, int NKV, int HD, float scale) {
     BMC_CHECK_CTX(ctx);
     if (!d_cs_table) return note(ctx, -1);
-    return note(ctx, decode_attention(d_out, d_qkv, d_cache, d_cs_table, d_pos, d_scratch, layer, NB, MS, NH, NKV, HD, scale, ctx->stream));
+    return note(ctx, decode_attention(d_out, d_qkv, d_cache, cache_dtype == BMC_BF16, d_cs_table, d_pos, d_scratch, layer, NB, MS, NH, NKV, HD, scale, ctx->stream));
 }
 int bmc_decode_prep(bmc_ctx_t* ctx, void* d_a, int parts, const float* d_x, int ldx, int mode, const float* d_norm_weight, float eps,
                     float* d_init_out, int ldo, const float* d_init_src, int ldr, int n_out, int rows, int C) {
@@ -629,9 +629,9 @@ int bmc_decode_gemm(bmc_ctx_t* ctx, float* d_out, int ldo, const void* d_a, cons
                   getenv("BM_NO_PDL") ? 0 : 1};
     return note(ctx, run_umma(ctx, g));
 }
-int bmc_decode_kv_scatter(bmc_ctx_t* ctx, float* d_cache, const float* d_qkv, int ldqkv, int layer, int NB, int T, int MS, int QD, int KV) {
+int bmc_decode_kv_scatter(bmc_ctx_t* ctx, void* d_cache, int cache_dtype, const float* d_qkv, int ldqkv, int layer, int NB, int T, int MS, int QD, int KV) {
     BMC_CHECK_CTX(ctx);
-    return note(ctx, decode_kv_scatter(d_cache, d_qkv, ldqkv, layer, NB, T, MS, QD, KV, ctx->stream));
+    return note(ctx, decode_kv_scatter(d_cache, cache_dtype == BMC_BF16, d_qkv, ldqkv, layer, NB, T, MS, QD, KV, ctx->stream));
 }
 int bmc_prefill_attention(bmc_ctx_t* ctx, float* d_out, int ldo, const float* d_q, int ldq, const float* d_k, const float* d_v, int ldkv, int NB,
                           int T, int NH, int NKV, int HD, float scale) {

@@ -292,9 +292,34 @@ __global__ void decode_rmsnorm_kernel(float* __restrict__ out, const float* __re
     for (int i = threadIdx.x; i < C; i += blockDim.x) out[(size_t)blockIdx.x * C + i] = xr[i] * inv * w[i];
 }
 
+// Element type of the KV cache: fp32 as the reference keeps it (the default, and what every parity test runs), or bf16 on request
+// (half the bytes of the one memory-bound part of batched decode; values are rounded when a row is stored).
+template <typename CT> struct KvT;
+template <> struct KvT<float> {
+    static __device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+    static __device__ __forceinline__ void st1(float* p, float v) { *p = v; }
+    static __device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct KvT<bf16> {
+    static __device__ __forceinline__ float4 ld4(const bf16* p) {
+        const uint2 r = *reinterpret_cast<const uint2*>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x)), b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+    static __device__ __forceinline__ void st1(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+    static __device__ __forceinline__ void st4(bf16* p, float4 v) {
+        const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 r;
+        r.x = *reinterpret_cast<const uint32_t*>(&a);
+        r.y = *reinterpret_cast<const uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = r;
+    }
+};
+
 // RoPE on this token's q and k at position *pos, then k and v into the cache. qkv: [NB][QD + 2 KV].
-// cache: [L][2][NB][MS][KV] fp32. cs: [MS][HD/2][2].
-__global__ void decode_rope_kv_kernel(float* __restrict__ qkv, float* __restrict__ cache, const float* __restrict__ cs,
+// cache: [L][2][NB][MS][KV] fp32 or bf16. cs: [MS][HD/2][2].
+template <typename CT>
+__global__ void decode_rope_kv_kernel(float* __restrict__ qkv, CT* __restrict__ cache, const float* __restrict__ cs,
                                       const int* __restrict__ pos_ptr, int layer, int NB, int MS, int NH, int NKV, int HD) {
     const int b = blockIdx.x;
     pdl_wait();
@@ -310,11 +335,11 @@ __global__ void decode_rope_kv_kernel(float* __restrict__ qkv, float* __restrict
         base[p + hd2] = x0 * s + x1 * c;
     }
     __syncthreads();
-    float* kc = cache + (((size_t)layer * 2 + 0) * NB + b) * (size_t)MS * KV + (size_t)pos * KV;
-    float* vc = cache + (((size_t)layer * 2 + 1) * NB + b) * (size_t)MS * KV + (size_t)pos * KV;
+    CT* kc = cache + (((size_t)layer * 2 + 0) * NB + b) * (size_t)MS * KV + (size_t)pos * KV;
+    CT* vc = cache + (((size_t)layer * 2 + 1) * NB + b) * (size_t)MS * KV + (size_t)pos * KV;
     for (int i = threadIdx.x; i < KV; i += blockDim.x) {
-        kc[i] = row[QD + i];
-        vc[i] = row[QD + KV + i];
+        KvT<CT>::st1(kc + i, row[QD + i]);
+        KvT<CT>::st1(vc + i, row[QD + KV + i]);
     }
 }
 
@@ -329,9 +354,9 @@ __global__ void decode_rope_kv_kernel(float* __restrict__ qkv, float* __restrict
 constexpr int ATT_THREADS = 256;
 // VPRE (grids of a few blocks per SM, where latency, not occupancy, decides): the first K and V rows of the slice are requested
 // before the dependency wait, together.
-template <int HD, int MUL, bool ROPE, bool VPRE>
+template <int HD, int MUL, bool ROPE, bool VPRE, typename CT>
 __global__ void __launch_bounds__(ATT_THREADS)
-decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, float* cache, const float* __restrict__ cs,
+decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, CT* cache, const float* __restrict__ cs,
                         const int* __restrict__ pos_ptr, float* part, unsigned* tickets, int layer, int NB, int MS, int NH, int NKV,
                         int chunk, float scale) {
     extern __shared__ float sm[];
@@ -351,8 +376,8 @@ decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, 
     const int sub = tid & 7, slot = tid >> 3;          // phase 1: 8 lanes per position, 32 positions per block iteration
     const int d4 = tid % D4, grp = tid / D4;           // phase 3: one float4 of a V row per thread, GROUPS rows per block iteration
     const int tn = n - 1 - t_begin;                    // the current position inside this slice (if 0 <= tn < len)
-    const float* kc = cache + (((size_t)layer * 2 + 0) * NB + b) * (size_t)MS * KV + (size_t)kh * HD;
-    const float* vc = cache + (((size_t)layer * 2 + 1) * NB + b) * (size_t)MS * KV + (size_t)kh * HD;
+    const CT* kc = cache + (((size_t)layer * 2 + 0) * NB + b) * (size_t)MS * KV + (size_t)kh * HD;
+    const CT* vc = cache + (((size_t)layer * 2 + 1) * NB + b) * (size_t)MS * KV + (size_t)kh * HD;
     float4 kpre[VPRE ? PU : 1][EPL / 4];
     if (VPRE) {
 #pragma unroll
@@ -360,7 +385,7 @@ decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, 
             const int t = slot + u * (ATT_THREADS / 8);
 #pragma unroll
             for (int i = 0; i < EPL / 4; ++i)
-                kpre[u][i] = t < len ? *reinterpret_cast<const float4*>(kc + (size_t)(t_begin + t) * KV + sub * EPL + i * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                kpre[u][i] = t < len ? KvT<CT>::ld4(kc + (size_t)(t_begin + t) * KV + sub * EPL + i * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
     }
     float4 vpre[VPRE ? VU : 1];
@@ -368,7 +393,7 @@ decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, 
 #pragma unroll
         for (int u = 0; u < VU; ++u) {
             const int t = grp + u * GROUPS;
-            vpre[u] = t < len ? *reinterpret_cast<const float4*>(vc + (size_t)(t_begin + t) * KV + d4 * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            vpre[u] = t < len ? KvT<CT>::ld4(vc + (size_t)(t_begin + t) * KV + d4 * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
     }
     float rc[ROPE ? EPL : 1], rs[ROPE ? EPL : 1];      // rotation of this lane's query elements
@@ -389,15 +414,15 @@ decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, 
     if (ROPE && n - 1 >= t_begin && n - 1 < t_begin + chunk) {  // block-uniform: the slice that owns the new position
         constexpr int hd2 = HD / 2;
         const float* krow = qkv + (size_t)b * (QD + 2 * KV) + QD + (size_t)kh * HD;
-        float* kdst = cache + (((size_t)layer * 2 + 0) * NB + b) * (size_t)MS * KV + (size_t)(n - 1) * KV + (size_t)kh * HD;
-        float* vdst = cache + (((size_t)layer * 2 + 1) * NB + b) * (size_t)MS * KV + (size_t)(n - 1) * KV + (size_t)kh * HD;
+        CT* kdst = cache + (((size_t)layer * 2 + 0) * NB + b) * (size_t)MS * KV + (size_t)(n - 1) * KV + (size_t)kh * HD;
+        CT* vdst = cache + (((size_t)layer * 2 + 1) * NB + b) * (size_t)MS * KV + (size_t)(n - 1) * KV + (size_t)kh * HD;
         if (tid < hd2) {
             const float c = cs[((size_t)(n - 1) * hd2 + tid) * 2], s = cs[((size_t)(n - 1) * hd2 + tid) * 2 + 1];
             const float x0 = krow[tid], x1 = krow[tid + hd2];
-            kdst[tid] = x0 * c - x1 * s;
-            kdst[tid + hd2] = x0 * s + x1 * c;
+            KvT<CT>::st1(kdst + tid, x0 * c - x1 * s);
+            KvT<CT>::st1(kdst + tid + hd2, x0 * s + x1 * c);
         } else if (tid >= 128 && tid < 128 + HD) {
-            vdst[tid - 128] = krow[KV + tid - 128];
+            KvT<CT>::st1(vdst + tid - 128, krow[KV + tid - 128]);
         }
         __syncthreads();  // the rows just written are read back below by other threads of this block
     }
@@ -407,11 +432,11 @@ decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, 
         for (int u = 0; u < PU; ++u)
             if (slot + u * (ATT_THREADS / 8) == tn)
 #pragma unroll
-                for (int i = 0; i < EPL / 4; ++i) kpre[VPRE ? u : 0][i] = *reinterpret_cast<const float4*>(kc + (size_t)(n - 1) * KV + sub * EPL + i * 4);
+                for (int i = 0; i < EPL / 4; ++i) kpre[VPRE ? u : 0][i] = KvT<CT>::ld4(kc + (size_t)(n - 1) * KV + sub * EPL + i * 4);
         {
 #pragma unroll
             for (int u = 0; u < VU; ++u)
-                if (grp + u * GROUPS == tn) vpre[u] = *reinterpret_cast<const float4*>(vc + (size_t)(n - 1) * KV + d4 * 4);
+                if (grp + u * GROUPS == tn) vpre[u] = KvT<CT>::ld4(vc + (size_t)(n - 1) * KV + d4 * 4);
         }
     }
     const float* qrow = qkv + (size_t)b * (QD + 2 * KV) + (size_t)kh * MUL * HD;
@@ -450,9 +475,9 @@ decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, 
 #pragma unroll
                 for (int i = 0; i < EPL / 4; ++i) kv[u][i] = kpre[VPRE ? u : 0][i];
             } else if (t < len) {
-                const float* kt = kc + (size_t)(t_begin + t) * KV + sub * EPL;
+                const CT* kt = kc + (size_t)(t_begin + t) * KV + sub * EPL;
 #pragma unroll
-                for (int i = 0; i < EPL / 4; ++i) kv[u][i] = *reinterpret_cast<const float4*>(kt + i * 4);
+                for (int i = 0; i < EPL / 4; ++i) kv[u][i] = KvT<CT>::ld4(kt + i * 4);
             } else {
 #pragma unroll
                 for (int i = 0; i < EPL / 4; ++i) kv[u][i] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -523,7 +548,7 @@ decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, 
         for (int u = 0; u < VU; ++u) {
             const int t = t0 + u * GROUPS;
             if (VPRE && t0 == grp) v[u] = vpre[VPRE ? u : 0];
-            else v[u] = t < len ? *reinterpret_cast<const float4*>(vc + (size_t)(t_begin + t) * KV + d4 * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            else v[u] = t < len ? KvT<CT>::ld4(vc + (size_t)(t_begin + t) * KV + d4 * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
         for (int u = 0; u < VU; ++u) {
@@ -628,7 +653,8 @@ decode_prep_kernel(bf16* __restrict__ a, int parts, const float* __restrict__ x,
 }
 
 // Prefill: K and V of every prompt row (row = b * T + t of a packed [q | k | v] matrix, k already rotated) into the cache.
-__global__ void decode_kv_scatter_kernel(float* __restrict__ cache, const float* __restrict__ qkv, int ldqkv, int layer, int NB, int T, int MS,
+template <typename CT>
+__global__ void decode_kv_scatter_kernel(CT* __restrict__ cache, const float* __restrict__ qkv, int ldqkv, int layer, int NB, int T, int MS,
                                          int QD, int KV) {
     pdl_wait();
     const long i = blockIdx.x * (long)blockDim.x + threadIdx.x;  // float4 index over [NB*T][2][KV/4]
@@ -639,7 +665,7 @@ __global__ void decode_kv_scatter_kernel(float* __restrict__ cache, const float*
     const long row = i / (2 * kv4);
     const int b = (int)(row / T), t = (int)(row - (long)b * T);
     const float4 v = *reinterpret_cast<const float4*>(qkv + row * ldqkv + QD + which * KV + c * 4);
-    *reinterpret_cast<float4*>(cache + ((((size_t)layer * 2 + which) * NB + b) * (size_t)MS + t) * KV + c * 4) = v;
+    KvT<CT>::st4(cache + ((((size_t)layer * 2 + which) * NB + b) * (size_t)MS + t) * KV + c * 4, v);
 }
 
 __global__ void decode_swiglu_kernel(float* __restrict__ out, const float* __restrict__ gu, int H, int NB) {
@@ -802,9 +828,10 @@ int decode_gemv(float* out, int ldo, const float* x, int ldx, int wtype, const v
 int decode_rmsnorm(float* out, const float* x, const float* w, int NB, int C, float eps, cudaStream_t st) {
     return launch_k(decode_rmsnorm_kernel, dim3(NB), dim3(256), 0, st, out, x, w, C, eps);
 }
-int decode_rope_kv(float* qkv, float* cache, const float* cs, const int* pos, int layer, int NB, int MS, int NH, int NKV, int HD,
+int decode_rope_kv(float* qkv, void* cache, int cache_bf16, const float* cs, const int* pos, int layer, int NB, int MS, int NH, int NKV, int HD,
                    cudaStream_t st) {
-    return launch_k(decode_rope_kv_kernel, dim3(NB), dim3(256), 0, st, qkv, cache, cs, pos, layer, NB, MS, NH, NKV, HD);
+    if (cache_bf16) return launch_k(decode_rope_kv_kernel<bf16>, dim3(NB), dim3(256), 0, st, qkv, (bf16*)cache, cs, pos, layer, NB, MS, NH, NKV, HD);
+    return launch_k(decode_rope_kv_kernel<float>, dim3(NB), dim3(256), 0, st, qkv, (float*)cache, cs, pos, layer, NB, MS, NH, NKV, HD);
 }
 // Number of position slices for a cache of MS rows: enough blocks to fill the GPU about four times over.
 static void attention_split(int NB, int NKV, int MS, int* chunk, int* splits) {
@@ -821,8 +848,8 @@ size_t decode_attention_scratch_bytes(int NB, int MS, int NH, int NKV, int HD) {
     attention_split(NB, NKV, MS, &chunk, &splits);
     return (size_t)NB * NH * splits * (HD + 2) * sizeof(float) + (size_t)NB * NKV * sizeof(unsigned);
 }
-template <int HD, int MUL, bool ROPE>
-static int launch_attention(float* out, const float* qkv, float* cache, const float* cs, const int* pos, void* scratch, int layer, int NB,
+template <int HD, int MUL, bool ROPE, typename CT>
+static int launch_attention(float* out, const float* qkv, CT* cache, const float* cs, const int* pos, void* scratch, int layer, int NB,
                             int MS, int NH, int NKV, float scale, cudaStream_t st) {
     int chunk, splits;
     attention_split(NB, NKV, MS, &chunk, &splits);
@@ -831,31 +858,37 @@ static int launch_attention(float* out, const float* qkv, float* cache, const fl
     static size_t attr_smem = 48 * 1024;
     if (smem > attr_smem) {
         if (smem > 220 * 1024) return -2;
-        cudaFuncSetAttribute(decode_attention_kernel<HD, MUL, ROPE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        cudaFuncSetAttribute(decode_attention_kernel<HD, MUL, ROPE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(decode_attention_kernel<HD, MUL, ROPE, true, CT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(decode_attention_kernel<HD, MUL, ROPE, false, CT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         attr_smem = smem;
     }
     // scratch: tickets first (zeroed once by the owner; every launch leaves them zero), then the partial records
     unsigned* tickets = (unsigned*)scratch;
     float* part = scratch ? (float*)((char*)scratch + (((size_t)NB * NKV * sizeof(unsigned) + 15) / 16) * 16) : nullptr;
     if ((long)NKV * NB * splits <= 2 * 148)
-        return launch_k(decode_attention_kernel<HD, MUL, ROPE, true>, dim3(NKV, NB, splits), dim3(ATT_THREADS), smem, st, out, qkv, cache, cs, pos,
+        return launch_k(decode_attention_kernel<HD, MUL, ROPE, true, CT>, dim3(NKV, NB, splits), dim3(ATT_THREADS), smem, st, out, qkv, cache, cs, pos,
                         part, tickets, layer, NB, MS, NH, NKV, chunk, scale);
-    return launch_k(decode_attention_kernel<HD, MUL, ROPE, false>, dim3(NKV, NB, splits), dim3(ATT_THREADS), smem, st, out, qkv, cache, cs, pos,
+    return launch_k(decode_attention_kernel<HD, MUL, ROPE, false, CT>, dim3(NKV, NB, splits), dim3(ATT_THREADS), smem, st, out, qkv, cache, cs, pos,
                     part, tickets, layer, NB, MS, NH, NKV, chunk, scale);
 }
 // head_dim 64 or 128; 1, 2, 3, 4 or 8 query heads per KV head. cs != null: RoPE and the cache store happen inside.
 // scratch (may be null: one slice per block): decode_attention_scratch_bytes() + 16 bytes, zero-initialised once.
-int decode_attention(float* out, const float* qkv, float* cache, const float* cs, const int* pos, void* scratch, int layer, int NB, int MS,
-                     int NH, int NKV, int HD, float scale, cudaStream_t st) {
+int decode_attention(float* out, const float* qkv, void* cache, int cache_bf16, const float* cs, const int* pos, void* scratch, int layer, int NB,
+                     int MS, int NH, int NKV, int HD, float scale, cudaStream_t st) {
     if (NKV <= 0 || NH % NKV) return -1;
     const int mul = NH / NKV;
-#define BM_ATT_CASE(hd, m)                                                                                                            \
+#define BM_ATT_CASE_T(hd, m, CT)                                                                                                      \
     if (HD == hd && mul == m)                                                                                                         \
-        return cs ? launch_attention<hd, m, true>(out, qkv, cache, cs, pos, scratch, layer, NB, MS, NH, NKV, scale, st)               \
-                  : launch_attention<hd, m, false>(out, qkv, cache, cs, pos, scratch, layer, NB, MS, NH, NKV, scale, st);
+        return cs ? launch_attention<hd, m, true, CT>(out, qkv, (CT*)cache, cs, pos, scratch, layer, NB, MS, NH, NKV, scale, st)      \
+                  : launch_attention<hd, m, false, CT>(out, qkv, (CT*)cache, cs, pos, scratch, layer, NB, MS, NH, NKV, scale, st);
+#define BM_ATT_CASE(hd, m) BM_ATT_CASE_T(hd, m, float)
+    if (cache_bf16) {   // bf16 cache: head_dim 64 only
+        BM_ATT_CASE_T(64, 1, bf16) BM_ATT_CASE_T(64, 2, bf16) BM_ATT_CASE_T(64, 3, bf16) BM_ATT_CASE_T(64, 4, bf16) BM_ATT_CASE_T(64, 8, bf16)
+        return -3;
+    }
     BM_ATT_CASE(64, 1) BM_ATT_CASE(64, 2) BM_ATT_CASE(64, 3) BM_ATT_CASE(64, 4) BM_ATT_CASE(64, 8)
     BM_ATT_CASE(128, 1) BM_ATT_CASE(128, 2) BM_ATT_CASE(128, 4) BM_ATT_CASE(128, 8)
+#undef BM_ATT_CASE_T
 #undef BM_ATT_CASE
     return -3;
 }
@@ -874,10 +907,12 @@ int decode_prep(bf16* a, int parts, const float* x, int ldx, int mode, const flo
     if (mode == 2) return launch_k(decode_prep_kernel<2>, dim3(rows, ny), dim3(256), 0, st, a, parts, x, ldx, lnw, eps, init_out, ldo, init_src, ldr, n_out, C);
     return launch_k(decode_prep_kernel<0>, dim3(rows, ny), dim3(256), 0, st, a, parts, x, ldx, lnw, eps, init_out, ldo, init_src, ldr, n_out, C);
 }
-int decode_kv_scatter(float* cache, const float* qkv, int ldqkv, int layer, int NB, int T, int MS, int QD, int KV, cudaStream_t st) {
+int decode_kv_scatter(void* cache, int cache_bf16, const float* qkv, int ldqkv, int layer, int NB, int T, int MS, int QD, int KV, cudaStream_t st) {
     if ((KV & 3) || (QD & 3) || (ldqkv & 3) || T > MS) return -1;
     const long n = (long)NB * T * 2 * (KV / 4);
-    return launch_k(decode_kv_scatter_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, cache, qkv, ldqkv, layer, NB, T, MS, QD, KV);
+    if (cache_bf16)
+        return launch_k(decode_kv_scatter_kernel<bf16>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, (bf16*)cache, qkv, ldqkv, layer, NB, T, MS, QD, KV);
+    return launch_k(decode_kv_scatter_kernel<float>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, (float*)cache, qkv, ldqkv, layer, NB, T, MS, QD, KV);
 }
 // head_dim 64 only (returns -3 otherwise); all pitches multiples of 4 floats
 int decode_swiglu(float* out, const float* gu, int NB, int H, cudaStream_t st) {

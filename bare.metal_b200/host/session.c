@@ -40,7 +40,9 @@ struct bm_session_s {
     float* lnf;
     void* head;   /* [V, D] bf16 or fp32: LM head */
     float* embed; /* [V, D] fp32 embedding table as loaded (src/baremetal/session.c:114-123); aliases head in fp32 mode */
-    float *cache, *cs, *x, *xn, *qkv, *att, *x1, *gu, *act, *logits;
+    void* cache;   /* [L][2][NB][MS][KV], fp32 (the reference's layout) or bf16 (bmx_create_session_kv) */
+    int kv_dtype;  /* BMC_F32 or BMC_BF16 */
+    float *cs, *x, *xn, *qkv, *att, *x1, *gu, *act, *logits;
     int *d_pos, *d_tokens, *d_next, *d_gen;
     void* att_scratch;
     void* a_op; /* tensor-core path: bf16 split operand rows */
@@ -165,7 +167,18 @@ static float* upload_f32(bm_session_t* s, const float* src, size_t n) {
 }
 
 bm_session_t* bmx_create_session_batched(bm_context_t* ctx, bm_model_t* model, int n_sequences, int max_positions) {
+    return bmx_create_session_kv(ctx, model, n_sequences, max_positions, getenv("BM_KV_BF16") ? 1 : 0);
+}
+
+/* kv_bf16 = 0: fp32 KV cache, the reference's (its kv buffers are fp32 whatever the weight precision) and what every parity test
+ * runs. kv_bf16 = 1: keys and values are rounded to bf16 when they enter the cache, which halves the bytes the attention of a
+ * decode step reads — the one memory-bound part of batched decode. head_dim 64 only. */
+bm_session_t* bmx_create_session_kv(bm_context_t* ctx, bm_model_t* model, int n_sequences, int max_positions, int kv_bf16) {
     if (!ctx || !ctx->be || !model || !model->weight_buffer || n_sequences < 1) return NULL;
+    if (kv_bf16 && model->head_size != 64) {
+        BM_LOG_ERROR("bm_create_session: a bf16 KV cache needs head_dim 64");
+        return NULL;
+    }
     const bm_arch_t* a = &model->arch;
     if (model->precision == BM_PRECISION_FP16) {
         BM_LOG_ERROR("bm_create_session: fp16 weights are not supported by this backend");
@@ -180,6 +193,7 @@ bm_session_t* bmx_create_session_batched(bm_context_t* ctx, bm_model_t* model, i
     s->ctx = ctx;
     s->model = model;
     s->NB = n_sequences;
+    s->kv_dtype = kv_bf16 ? BMC_BF16 : BMC_F32;
     s->tc_weights = !getenv("BM_NO_TC_DECODE"); /* split-bf16 copies: prefill of any session, decode of batched ones */
     s->tc = s->tc_weights && n_sequences >= BM_TC_MIN_SEQUENCES;
     s->MS = max_positions > 0 ? max_positions : (a->max_seq_len > 0 ? a->max_seq_len : 2048);
@@ -229,7 +243,7 @@ bm_session_t* bmx_create_session_batched(bm_context_t* ctx, bm_model_t* model, i
     }
 #define DALLOC(p, n) do { (p) = bmc_alloc(be, (size_t)(n)); if (!(p)) ok = 0; } while (0)
     if (ok) {
-        DALLOC(s->cache, (size_t)L * 2 * NB * MS * KV * sizeof(float));
+        DALLOC(s->cache, (size_t)L * 2 * NB * MS * KV * (kv_bf16 ? 2 : sizeof(float)));
         DALLOC(s->x, (size_t)NB * D * 4); DALLOC(s->xn, (size_t)NB * D * 4); DALLOC(s->qkv, (size_t)NB * (QD + 2 * KV) * 4);
         DALLOC(s->att, (size_t)NB * QD * 4); DALLOC(s->x1, (size_t)NB * D * 4); DALLOC(s->gu, (size_t)NB * 2 * H * 4);
         DALLOC(s->act, (size_t)NB * H * 4); DALLOC(s->logits, (size_t)NB * V * 4);
@@ -301,7 +315,7 @@ static int enqueue_step(bm_session_t* s) {
         if (s->tc) {
             TRYS(bmc_decode_prep(be, s->a_op, y->qkv.parts, s->x, D, 1, y->ln1, eps, s->qkv, QD + 2 * KV, NULL, 0, QD + 2 * KV, NB, D));
             TRYS(bmc_decode_gemm(be, s->qkv, QD + 2 * KV, s->a_op, y->qkv.wx, y->qkv.parts, NB, D, QD + 2 * KV));
-            TRYS(bmc_decode_attention_fused(be, s->att, s->qkv, s->cache, s->cs, s->d_pos, s->att_scratch, l, NB, MS, NH, NKV, HD, scale));
+            TRYS(bmc_decode_attention_fused(be, s->att, s->qkv, s->cache, s->kv_dtype, s->cs, s->d_pos, s->att_scratch, l, NB, MS, NH, NKV, HD, scale));
             TRYS(bmc_decode_prep(be, s->a_op, y->o.parts, s->att, QD, 0, NULL, 0.0f, s->x1, D, s->x, D, D, NB, QD));
             TRYS(bmc_decode_gemm(be, s->x1, D, s->a_op, y->o.wx, y->o.parts, NB, QD, D));
             TRYS(bmc_decode_prep(be, s->a_op, y->gu.parts, s->x1, D, 1, y->ln2, eps, s->gu, 2 * H, NULL, 0, 2 * H, NB, D));
@@ -312,7 +326,7 @@ static int enqueue_step(bm_session_t* s) {
         }
         if (fused) {
             TRYS(bmc_decode_gemv_fused(be, s->qkv, QD + 2 * KV, s->x, D, s->wtype, y->qkv.w, y->qkv.scales, NULL, 0, 1, y->ln1, eps, NB, D, QD + 2 * KV));
-            TRYS(bmc_decode_attention_fused(be, s->att, s->qkv, s->cache, s->cs, s->d_pos, s->att_scratch, l, NB, MS, NH, NKV, HD, scale));
+            TRYS(bmc_decode_attention_fused(be, s->att, s->qkv, s->cache, s->kv_dtype, s->cs, s->d_pos, s->att_scratch, l, NB, MS, NH, NKV, HD, scale));
             TRYS(bmc_decode_gemv(be, s->x1, D, s->att, QD, s->wtype, y->o.w, y->o.scales, s->x, D, NB, QD, D));
             TRYS(bmc_decode_gemv_fused(be, s->gu, 2 * H, s->x1, D, s->wtype, y->gu.w, y->gu.scales, NULL, 0, 1, y->ln2, eps, NB, D, 2 * H));
             TRYS(bmc_decode_gemv_fused(be, s->x, D, s->gu, 2 * H, s->wtype, y->down.w, y->down.scales, s->x1, D, 2, NULL, 0.0f, NB, H, D));
@@ -320,8 +334,8 @@ static int enqueue_step(bm_session_t* s) {
         }
         TRYS(bmc_decode_rmsnorm(be, s->xn, s->x, y->ln1, NB, D, eps));
         TRYS(bmc_decode_gemv(be, s->qkv, QD + 2 * KV, s->xn, D, s->wtype, y->qkv.w, y->qkv.scales, NULL, 0, NB, D, QD + 2 * KV));
-        TRYS(bmc_decode_rope_kv(be, s->qkv, s->cache, s->cs, s->d_pos, l, NB, MS, NH, NKV, HD));
-        TRYS(bmc_decode_attention(be, s->att, s->qkv, s->cache, s->d_pos, s->att_scratch, l, NB, MS, NH, NKV, HD, scale));
+        TRYS(bmc_decode_rope_kv(be, s->qkv, s->cache, s->kv_dtype, s->cs, s->d_pos, l, NB, MS, NH, NKV, HD));
+        TRYS(bmc_decode_attention(be, s->att, s->qkv, s->cache, s->kv_dtype, s->d_pos, s->att_scratch, l, NB, MS, NH, NKV, HD, scale));
         TRYS(bmc_decode_gemv(be, s->x1, D, s->att, QD, s->wtype, y->o.w, y->o.scales, s->x, D, NB, QD, D));
         TRYS(bmc_decode_rmsnorm(be, s->xn, s->x1, y->ln2, NB, D, eps));
         TRYS(bmc_decode_gemv(be, s->gu, 2 * H, s->xn, D, s->wtype, y->gu.w, y->gu.scales, NULL, 0, NB, D, 2 * H));
@@ -405,7 +419,7 @@ static int prefill(bm_session_t* s, const int* tokens, int T) {
         TRYP(bmc_decode_prep(be, aop, y->qkv.parts, x, D, 1, y->ln1, eps, qkv, W, NULL, 0, W, (int)R, D));
         TRYP(bmc_decode_gemm(be, qkv, W, aop, y->qkv.wx, y->qkv.parts, (int)R, D, W));
         TRYP(bmc_rope(be, BMC_F32, qkv, W, qkv + QD, W, s->cs, (int)R, T, NH, NKV, HD, 1));
-        TRYP(bmc_decode_kv_scatter(be, s->cache, qkv, W, l, NB, T, MS, QD, KV));
+        TRYP(bmc_decode_kv_scatter(be, s->cache, s->kv_dtype, qkv, W, l, NB, T, MS, QD, KV));
         if (HD == 64) TRYP(bmc_prefill_attention(be, att, QD, qkv, W, qkv + QD, qkv + QD + KV, W, NB, T, NH, NKV, HD, scale));
         else TRYP(bmc_attention_forward(be, BMC_F32, att, QD, lse, qkv, W, qkv + QD, qkv + QD + KV, W, NULL, NB, T, NH, NKV, HD, scale));
         TRYP(bmc_decode_prep(be, aop, y->o.parts, att, QD, 0, NULL, 0.0f, x1, D, x, D, D, (int)R, QD));
@@ -540,6 +554,7 @@ size_t bmx_session_algorithmic_weight_bytes(bm_session_t* s) {
     n += (size_t)s->model->arch.vocab_size * s->model->arch.dim * (s->head_type == BMC_W_BF16 ? 2 : 4);
     return n;
 }
+int bmx_session_kv_bytes_per_element(bm_session_t* s) { return s ? (s->kv_dtype == BMC_BF16 ? 2 : 4) : 0; }
 /* Bytes of weights the session actually streams per step (the tensor-core path of >= 8 sequences reads bf16 expansions). */
 size_t bmx_session_weight_bytes(bm_session_t* s) {
     if (!s) return 0;

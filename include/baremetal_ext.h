@@ -80,6 +80,10 @@ size_t bmx_quantize_q8(const float* src, int8_t* q, float* scales, size_t n);
 /* A session that advances n_sequences independent sequences in lock step (the reference API is single-sequence:
  * bm_create_session == n_sequences 1). max_positions = KV cache length per sequence (0: the model's max_seq_len). */
 bm_session_t* bmx_create_session_batched(bm_context_t* ctx, bm_model_t* model, int n_sequences, int max_positions);
+/* the same with the element type of the KV cache chosen: 0 = fp32 (the reference's, and the default; env BM_KV_BF16=1 flips the
+ * default), 1 = bf16 (half the attention bytes of a decode step; head_dim 64) */
+bm_session_t* bmx_create_session_kv(bm_context_t* ctx, bm_model_t* model, int n_sequences, int max_positions, int kv_bf16);
+int    bmx_session_kv_bytes_per_element(bm_session_t* s);
 /* prompt: int[n_sequences][n_prompt]; out: int[n_sequences][n_new] greedy continuations (lowest index among maxima). */
 int    bmx_session_generate_greedy(bm_session_t* s, const int* prompt, int n_prompt, int n_new, int* out);
 const float* bmx_session_logits(bm_session_t* s);

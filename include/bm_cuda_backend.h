@@ -189,11 +189,12 @@ int bmc_argmax(bmc_ctx_t* ctx, int* d_index, const float* d_logits, int V);
 
 /* ---- token-by-token inference (decode walk src/baremetal/scheduler.c:712-996; kernels matmul_forward_q8_vec forward.metal:575,
  *      rmsnorm_forward_v2 :1019, rope_forward :1284, kv_store :1317, attention_forward :1362, swiglu_forward :1179), batched over
- *      NB independent sequences that share one position counter. Activations and the KV cache are fp32.
+ *      NB independent sequences that share one position counter. Activations are fp32; the KV cache holds fp32 elements
+ *      (cache_dtype BMC_F32: what the reference keeps, scheduler.c kv buffers) or, on request, bf16 (BMC_BF16, head_dim 64).
  *      Weight types: BMC_W_Q8 = int8 q[OC][C] + float scale[OC][C/32] (the values of the reference's 36-byte blocks,
  *      src/baremetal/quant.h:19-22, stored as two arrays), BMC_W_BF16, BMC_W_F32.
  *      d_pos is a DEVICE int holding the position of the token being processed (so a captured step can be replayed).
- *      KV cache layout: float[L][2][NB][MS][KV]; rope table float[MS][HD/2][2]. ---- */
+ *      KV cache layout: element[L][2][NB][MS][KV]; rope table float[MS][HD/2][2]. ---- */
 enum { BMC_W_Q8 = 0, BMC_W_BF16 = 1, BMC_W_F32 = 2 };
 int bmc_decode_gemv(bmc_ctx_t* ctx, float* d_out, int ldo, const float* d_x, int ldx, int wtype, const void* d_w, const float* d_scales,
                     const float* d_residual, int ldr, int NB, int C, int OC);
@@ -204,15 +205,15 @@ int bmc_decode_gemv(bmc_ctx_t* ctx, float* d_out, int ldo, const float* d_x, int
 int bmc_decode_gemv_fused(bmc_ctx_t* ctx, float* d_out, int ldo, const float* d_x, int ldx, int wtype, const void* d_w, const float* d_scales,
                           const float* d_residual, int ldr, int prologue, const float* d_norm_weight, float eps, int NB, int C, int OC);
 int bmc_decode_rmsnorm(bmc_ctx_t* ctx, float* d_out, const float* d_x, const float* d_w, int NB, int C, float eps);
-int bmc_decode_rope_kv(bmc_ctx_t* ctx, float* d_qkv, float* d_cache, const float* d_cs_table, const int* d_pos, int layer, int NB, int MS,
+int bmc_decode_rope_kv(bmc_ctx_t* ctx, float* d_qkv, void* d_cache, int cache_dtype, const float* d_cs_table, const int* d_pos, int layer, int NB, int MS,
                        int NH, int NKV, int HD);
 /* d_scratch: NULL (one block per sequence and KV head walks every position) or a buffer of bmc_decode_attention_scratch_bytes(),
  * zeroed once by the caller, which lets the positions be split over several blocks that merge their softmax partials. */
 size_t bmc_decode_attention_scratch_bytes(int NB, int MS, int NH, int NKV, int HD);
-int bmc_decode_attention(bmc_ctx_t* ctx, float* d_out, const float* d_qkv, const float* d_cache, const int* d_pos, void* d_scratch, int layer,
+int bmc_decode_attention(bmc_ctx_t* ctx, float* d_out, const float* d_qkv, const void* d_cache, int cache_dtype, const int* d_pos, void* d_scratch, int layer,
                          int NB, int MS, int NH, int NKV, int HD, float scale);
 /* rope_forward + kv_store + attention_forward in one kernel: d_qkv holds the raw projections and is left untouched */
-int bmc_decode_attention_fused(bmc_ctx_t* ctx, float* d_out, const float* d_qkv, float* d_cache, const float* d_cs_table, const int* d_pos,
+int bmc_decode_attention_fused(bmc_ctx_t* ctx, float* d_out, const float* d_qkv, void* d_cache, int cache_dtype, const float* d_cs_table, const int* d_pos,
                                void* d_scratch, int layer, int NB, int MS, int NH, int NKV, int HD, float scale);
 /* Tensor-core products with fp32-accurate results, for many rows (batched decode, prefill). bmc_decode_prep splits the fp32 operand
  * rows (mode 0 = x, 1 = RMSNorm(x) * weight, 2 = silu(gate) * up of [gate | up] rows) into bf16 [hi | lo] (parts 2) or [hi | lo | hi]
@@ -223,7 +224,7 @@ int bmc_decode_prep(bmc_ctx_t* ctx, void* d_a, int parts, const float* d_x, int 
                     float* d_init_out, int ldo, const float* d_init_src, int ldr, int n_out, int rows, int C);
 int bmc_decode_gemm(bmc_ctx_t* ctx, float* d_out, int ldo, const void* d_a, const void* d_w, int parts, int rows, int C, int OC);
 /* prefill (bmt_scheduler_copy_prefill_kv, src/baremetal/session.c:136): K | V columns of prompt row b * T + t into cache[layer][0|1][b][t] */
-int bmc_decode_kv_scatter(bmc_ctx_t* ctx, float* d_cache, const float* d_qkv, int ldqkv, int layer, int NB, int T, int MS, int QD, int KV);
+int bmc_decode_kv_scatter(bmc_ctx_t* ctx, void* d_cache, int cache_dtype, const float* d_qkv, int ldqkv, int layer, int NB, int T, int MS, int QD, int KV);
 /* attention_forward_prefill_tiled (src/kernels/forward.metal:2024): causal attention over the T prompt rows of each of NB sequences,
  * fp32 in and out, fp32-accurate on the tensor pipe (operands split into bf16 hi + lo, three tcgen05 products per product);
  * head_dim 64 (-1 otherwise: use bmc_attention_forward with BMC_F32) */
