@@ -855,12 +855,16 @@ static int launch_attention(float* out, const float* qkv, CT* cache, const float
     attention_split(NB, NKV, MS, &chunk, &splits);
     if (splits > 1 && !scratch) { chunk = (MS + 31) / 32 * 32; splits = 1; }
     const size_t smem = ((size_t)MUL * chunk + (size_t)MUL * (ATT_THREADS / (HD / 4)) * HD) * sizeof(float);
-    static size_t attr_smem = 48 * 1024;
-    if (smem > attr_smem) {
+    // the largest dynamic shared memory size this instantiation has been granted, per device (kernel attributes are per device)
+    static size_t attr_smem[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    size_t& granted = attr_smem[dev & 63];
+    if (smem > 48 * 1024 && smem > granted) {
         if (smem > 220 * 1024) return -2;
         cudaFuncSetAttribute(decode_attention_kernel<HD, MUL, ROPE, true, CT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         cudaFuncSetAttribute(decode_attention_kernel<HD, MUL, ROPE, false, CT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attr_smem = smem;
+        granted = smem;
     }
     // scratch: tickets first (zeroed once by the owner; every launch leaves them zero), then the partial records
     unsigned* tickets = (unsigned*)scratch;
