@@ -78,6 +78,7 @@ void* scratch_get(bmc_ctx_t* ctx, void** slot, size_t* cap, size_t bytes) {
         *cap = 0;
     }
     if (cudaMalloc(slot, bytes) != cudaSuccess) return nullptr;
+    cudaMemsetAsync(*slot, 0, bytes, ctx->stream);   // nothing a kernel reads may depend on what a previous owner left in the memory
     *cap = bytes;
     return *slot;
 }
@@ -209,6 +210,9 @@ void* bmc_alloc(bmc_ctx_t* ctx, size_t bytes) {
         cudaGetLastError();
         return nullptr;
     }
+    // Zero-filled: cudaMalloc hands back whatever the previous owner left, and padding rows or a scratch row that a launch of a
+    // smaller shape never writes must not make results depend on the process's allocation history. Creation-time cost only.
+    cudaMemsetAsync(p, 0, bytes, ctx->stream);
     std::lock_guard<std::mutex> lk(ctx->mu);
     ctx->allocs[p] = bytes;
     ctx->allocated += bytes;
