@@ -45,6 +45,9 @@ struct bmc_ctx_s {
     cudaGraph_t graphs[2];
     cudaGraphExec_t graph_execs[2];
     long graph_kernels[2];  // kernel nodes of each captured graph: what one replay adds to `launches`
+    // early read-back (bmc_early_readback / bmc_early_wait): a pinned pair {loss, error word} and the event that says it has landed
+    float* h_early;
+    cudaEvent_t early_ev;
     int graph_slot;  // slot 0: inference session, slot 1: trainer
     // side stream (bmc_side_begin / _end / _wait): work that may overlap the main stream
     cudaStream_t side_stream;
@@ -197,6 +200,7 @@ void bmc_destroy(bmc_ctx_t* ctx) {
     for (auto e : ctx->gt_events) cudaEventDestroy(e);
     for (int i = 0; i < 2; ++i) {
         if (ctx->graph_execs[i]) cudaGraphExecDestroy(ctx->graph_execs[i]);
+        if (i == 0 && ctx->h_early) { cudaEventDestroy(ctx->early_ev); cudaFreeHost(ctx->h_early); ctx->h_early = nullptr; }
         if (ctx->graphs[i]) cudaGraphDestroy(ctx->graphs[i]);
     }
     cudaStreamDestroy(ctx->stream);
@@ -716,6 +720,32 @@ int bmc_graph_launch(bmc_ctx_t* ctx) {
     return 0;
 }
 int bmc_gemm_timing_enabled(bmc_ctx_t* ctx) { return ctx && ctx->gemm_timing ? 1 : 0; }
+// Copies *d_value and the error word to pinned host memory and records an event behind the copies, all on the context's stream and
+// all capturable: inside a stream capture the event becomes an external event node, so the host can wait for THIS point of a
+// replayed graph (bmc_early_wait) while the rest of the graph is still running.
+int bmc_early_readback(bmc_ctx_t* ctx, const float* d_value) {
+    BMC_CHECK_CTX(ctx);
+    if (!ctx->h_early) {
+        if (cudaMallocHost((void**)&ctx->h_early, 2 * sizeof(float)) != cudaSuccess) { ctx->h_early = nullptr; return -1; }
+        if (cudaEventCreateWithFlags(&ctx->early_ev, cudaEventDisableTiming) != cudaSuccess) { cudaFreeHost(ctx->h_early); ctx->h_early = nullptr; return -1; }
+    }
+    if (cudaMemcpyAsync(ctx->h_early, d_value, sizeof(float), cudaMemcpyDeviceToHost, ctx->stream) != cudaSuccess) return -2;
+    if (cudaMemcpyAsync(ctx->h_early + 1, ctx->d_err, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream) != cudaSuccess) return -2;
+    return cudaEventRecordWithFlags(ctx->early_ev, ctx->stream, cudaEventRecordExternal) == cudaSuccess ? 0 : -3;
+}
+// Waits for the most recent bmc_early_readback to land. *status_out is the error word as it stood at that point of the stream.
+int bmc_early_wait(bmc_ctx_t* ctx, float* value_out, int* status_out) {
+    BMC_CHECK_CTX(ctx);
+    if (!ctx->h_early) return -1;
+    const cudaError_t e = cudaEventSynchronize(ctx->early_ev);
+    if (e != cudaSuccess) {
+        ctx->sticky_status = -200 - (int)e;
+        return ctx->sticky_status;
+    }
+    if (value_out) *value_out = ctx->h_early[0];
+    if (status_out) memcpy(status_out, ctx->h_early + 1, sizeof(int));
+    return ctx->sticky_status;
+}
 int bmc_selftest_bounded_wait(bmc_ctx_t* ctx) {
     BMC_CHECK_CTX(ctx);
     return note(ctx, wait_probe_launch(ctx->d_err, ctx->stream));

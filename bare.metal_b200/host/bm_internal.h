@@ -69,6 +69,7 @@ struct bm_trainer_s {
     int graph_mode;           /* forward + backward of the plain step replayed as a CUDA graph: 0 off, 1 on (env BM_NO_TRAIN_GRAPH) */
     int graph_B;              /* batch the captured graph is for (0 = none) */
     int graph_eager_steps;    /* plain steps run eagerly with the current settings (the first ones size scratch buffers) */
+    int loss_is_early;        /* the step just enqueued was a graph replay: its loss is read back right after the forward pass */
     int graph_seen_B;         /* batch of those eager steps: a different batch starts the count again */
     int ref_norm_grad;        /* RMSNorm weight gradient = last sequence of the batch only */
     int ref_input_grad_carry; /* embedding scatter of sequence b uses the running sum of input gradients */

@@ -364,6 +364,7 @@ static int adamw_apply(bm_trainer_t* t) {
 static int step_enqueue(bm_trainer_t* t, int B, const uint8_t* d_attn_mask, const float* d_row_weight, int train) {
     bmc_ctx_t* be = t->ctx->be;
     const int accum = t->cfg.grad_accum_steps > 0 ? t->cfg.grad_accum_steps : 1;
+    t->loss_is_early = 0;
     if (train && t->accum_count == 0) {
         /* gradients accumulate over the B sequences and over micro-steps; cleared at the start of a window
          * (src/baremetal/trainer.c:459-470) */
@@ -390,6 +391,9 @@ static int step_enqueue(bm_trainer_t* t, int B, const uint8_t* d_attn_mask, cons
             int rc = bmc_graph_begin(be);
             if (rc == 0) {
                 rc = forward_and_loss(t, B, NULL, NULL, 1);
+                /* the loss is final here: hand it to the host now, so that bm_train_step can return (and its caller prepare the
+                 * next batch) while backward and AdamW are still running */
+                if (rc == 0) rc = bmc_early_readback(be, t->d_loss);
                 if (rc == 0) rc = backward(t, B, NULL);
                 const int rc2 = bmc_graph_end(be);
                 if (rc == 0 && rc2 == 0 && bmc_graph_launch(be) == 0) {
@@ -403,6 +407,7 @@ static int step_enqueue(bm_trainer_t* t, int B, const uint8_t* d_attn_mask, cons
                 t->graph_mode = 0;
             }
         }
+        t->loss_is_early = replayed;
         if (replayed) {
             t->window_microsteps += B;
             t->accum_count++;
@@ -438,6 +443,16 @@ static int step_enqueue(bm_trainer_t* t, int B, const uint8_t* d_attn_mask, cons
 
 static float read_loss(bm_trainer_t* t) {
     float loss = -1.0f;
+    if (t->loss_is_early) {
+        /* graph-replayed step: the loss and the error word were copied out right after the forward pass. Returning now leaves
+         * backward and AdamW running; every later call goes through the same stream and so stays ordered behind them. An error raised
+         * by backward shows in the error word of the NEXT step (or of any call that synchronises). */
+        int st = 0;
+        t->loss_is_early = 0;
+        if (bmc_early_wait(t->ctx->be, &loss, &st) != 0) return -1.0f;
+        if (st == 0) return loss;
+        /* something failed: take the slow path below, which synchronises, reports and clears */
+    }
     if (bmc_download(t->ctx->be, &loss, t->d_loss, sizeof(float)) != 0) return -1.0f;
     const int st = bmc_status(t->ctx->be);
     if (st) {

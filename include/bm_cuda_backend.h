@@ -63,6 +63,11 @@ void*      bmc_stream(bmc_ctx_t* ctx);                        /* the cudaStream_
 long       bmc_launch_count(bmc_ctx_t* ctx);
 /* Pinned host memory for staging step inputs. */
 void*      bmc_host_alloc(size_t bytes);
+/* A value the host needs before the stream has drained (the loss of a training step, known after the forward pass): _readback
+ * enqueues a copy of *d_value and of the error word to pinned memory plus an event behind them (capturable: inside a CUDA graph the
+ * event is an external event node); _wait blocks until that point of the stream has been reached. */
+int        bmc_early_readback(bmc_ctx_t* ctx, const float* d_value);
+int        bmc_early_wait(bmc_ctx_t* ctx, float* value_out, int* status_out);
 void       bmc_host_free(void* p);
 /* GPU-side phase timing (replaces backend_encode_wait_timed / backend_get_gpu_busy_ms, backend.h:32-37):
  * bmc_timer_begin/end bracket work on the compute stream with events; end returns elapsed ms (blocking). */
