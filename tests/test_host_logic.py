@@ -205,6 +205,9 @@ def test_dp_bucket_plan_partitions_the_parameters(product):
         assert list(r)[-1] == -1 and list(r)[:-1] == sorted(list(r)[:-1], reverse=True)  # completion order of backward
         for bi, ri in zip(list(b)[:-1], list(r)[:-1]):
             assert bi == 100 * ri  # a bucket is complete when its lowest layer is
+        if L > 1:
+            # what is exchanged after backward has ended is exposed: layer 0 travels alone, and the embedding bucket is the last
+            assert (b[n - 2], e[n - 2], r[n - 2]) == (0, 100, 0) and (b[n - 1], e[n - 1]) == (100 * L, P)
 
 
 def _write_safetensors(path, tensors, dtype="F32"):
