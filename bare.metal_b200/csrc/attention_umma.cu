@@ -108,6 +108,8 @@ struct FwdArgs {
 };
 
 
+// MASKED = false: no padding mask (the plain training step); the mask words, their loads and the per-element tests are compiled out
+template <bool MASKED>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const FwdArgs p) {
@@ -259,7 +261,7 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             // padding mask (attention_forward_seq_masked, src/kernels/forward.metal:1853): one word of key bits per 32 columns
             uint32_t mw[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
             bool tile_masked = false;
-            if (p.keymask) {
+            if (MASKED && p.keymask) {
                 const int W = (p.S + 31) >> 5;
 #pragma unroll
                 for (int ch = 0; ch < 4; ++ch) {
@@ -274,7 +276,7 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         const int kj = k0 + ch * 32 + i;
-                        if (kj > qi || kj >= p.S || !((mw[ch] >> i) & 1u)) v[ch][i] = __float_as_uint(-INFINITY);
+                        if (kj > qi || kj >= p.S || (MASKED && !((mw[ch] >> i) & 1u))) v[ch][i] = __float_as_uint(-INFINITY);
                     }
             }
             // eight independent max chains (a single chain of 128 dependent FMNMX would be latency-bound)
@@ -349,7 +351,7 @@ flash_fwd_umma_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             tc_fence_after_sync();
             // a masked position is no query either: its output row is zero, and its log-sum-exp +infinity makes every probability
             // the backward recomputes for it zero (no gradient to or from the row)
-            const bool q_on = !p.keymask || (qi < p.S && ((p.keymask[(size_t)b * ((p.S + 31) >> 5) + (qi >> 5)] >> (qi & 31)) & 1u));
+            const bool q_on = !MASKED || !p.keymask || (qi < p.S && ((p.keymask[(size_t)b * ((p.S + 31) >> 5) + (qi >> 5)] >> (qi & 31)) & 1u));
             const float inv = (l_run > 0.f && q_on) ? 1.0f / l_run : 0.f;
             bf16* orow = p.out + (size_t)(row0 + qi) * p.ldo + (size_t)h * FHD;
 #pragma unroll
@@ -1231,7 +1233,8 @@ int flash_attention_forward_umma(bf16* out, int ldo, float* lse, const bf16* q, 
         return -2;
     static std::atomic<unsigned long long> attr_done{0};
     if (first_use_on_current_device(attr_done) &&
-        cudaFuncSetAttribute(flash_fwd_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_DYN_SMEM) != cudaSuccess)
+        (cudaFuncSetAttribute(flash_fwd_umma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_DYN_SMEM) != cudaSuccess ||
+         cudaFuncSetAttribute(flash_fwd_umma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_DYN_SMEM) != cudaSuccess))
         return -5;
     CUtensorMap tq, tk, tv;
     const uint64_t rows = (uint64_t)B * S;
@@ -1241,7 +1244,8 @@ int flash_attention_forward_umma(bf16* out, int ldo, float* lse, const bf16* q, 
     if (rc) return rc;
     FwdArgs a{out, ldo, lse, keymask, S, NH, NKV, scale, err_flag};
     dim3 grid((S + 2 * FQ - 1) / (2 * FQ), NH, B);
-    flash_fwd_umma_kernel<<<grid, FWD_THREADS, FWD_DYN_SMEM, st>>>(tq, tk, tv, a);
+    if (keymask) flash_fwd_umma_kernel<true><<<grid, FWD_THREADS, FWD_DYN_SMEM, st>>>(tq, tk, tv, a);
+    else flash_fwd_umma_kernel<false><<<grid, FWD_THREADS, FWD_DYN_SMEM, st>>>(tq, tk, tv, a);
     const cudaError_t le = cudaGetLastError();
     if (le != cudaSuccess) {
         fprintf(stderr, "flash_attention_forward_umma: launch failed: %s\n", cudaGetErrorString(le));
