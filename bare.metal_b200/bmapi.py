@@ -107,6 +107,29 @@ def write_bin_checkpoint(path, a, w):
             f.write(np.ascontiguousarray(w[name], np.float32).tobytes())
 
 
+ADAPTER_MAGIC = 0x424D4C52
+ADAPTER_TARGETS = {"q": 1, "k": 2, "v": 4, "o": 8, "gate": 16, "up": 32, "down": 64}   # src/baremetal/lora.h:13-21
+ADAPTER_WEIGHT_KEY = {"q": "qw", "k": "kw", "v": "vw", "o": "ow", "gate": "gate", "up": "up", "down": "down"}
+
+
+def write_adapter_file(path, a, rank, alpha, entries, header_overrides=None):
+    """Adapter file as bm_save_adapter writes it and bm_load_adapter reads it (src/baremetal/adapter.c:20-40, :85-147):
+    an 11-word header, then per entry five int32 {layer, target bit, r, c, oc} followed by A[r][c] and B[oc][r] as fp32.
+    `entries` is a list of (layer, target name, A, B); `header_overrides` replaces header fields by name (for tests)."""
+    h = dict(magic=ADAPTER_MAGIC, version=1, dim=a.dim, layers=a.n_layers, n_heads=a.n_heads, n_kv_heads=a.n_kv_heads,
+             vocab=a.vocab_size, head_size=a.head_dim, rank=rank, alpha=float(alpha), n_adapters=len(entries))
+    h.update(header_overrides or {})
+    with open(path, "wb") as f:
+        f.write(struct.pack("<II7ifi", h["magic"], h["version"], h["dim"], h["layers"], h["n_heads"], h["n_kv_heads"],
+                            h["vocab"], h["head_size"], h["rank"], h["alpha"], h["n_adapters"]))
+        for layer, target, A, B in entries:
+            A, B = np.ascontiguousarray(A, np.float32), np.ascontiguousarray(B, np.float32)
+            tbit = ADAPTER_TARGETS[target] if isinstance(target, str) else int(target)
+            f.write(struct.pack("<5i", layer, tbit, A.shape[0], A.shape[1], B.shape[0]))
+            f.write(A.tobytes())
+            f.write(B.tobytes())
+
+
 def state_tensor_order(a):
     """Tensor order of the trainer-state file and of the optimizer-state list: per layer ln1w, qw, kw,
     vw, ow, ln2w, gate, up, down; then lnfw; then the tied embedding (src/baremetal/graph.c:288-369,
@@ -158,6 +181,7 @@ def bind_public_api(lib):
         "bm_get_supported_precision": (C.c_int, [vp]),
         "bm_create_model": (vp, [vp, C.POINTER(BmArch)]), "bm_load_weights": (None, [vp, C.c_char_p]),
         "bm_destroy_model": (None, [vp]), "bm_get_num_parameters": (C.c_int, [vp]),
+        "bm_load_adapter": (C.c_int, [vp, C.c_char_p]),
         "bm_create_trainer": (vp, [vp, vp, C.POINTER(BmTrainConfig)]),
         "bm_train_step": (C.c_float, [vp, ip, ip, C.c_int, C.c_int]),
         "bm_train_step_masked": (C.c_float, [vp, ip, ip, C.c_void_p, C.c_void_p, C.c_int, C.c_int]),

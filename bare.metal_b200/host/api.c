@@ -84,8 +84,8 @@ void bm_destroy_model(bm_model_t* model) {
 void bm_compile(bm_model_t* model) { (void)model; }
 void bm_autotune(bm_model_t* model, int warmup, int iterations) { (void)model; (void)warmup; (void)iterations; }
 
-/* ---- outside this build (tokenizer, adapters, sampled generation driver): same signatures, failure values ---------------------------------------------- */
-int bm_load_adapter(bm_model_t* model, const char* path) { (void)model; (void)path; return -1; }
+/* ---- outside this build (tokenizer, adapter training, sampled generation driver): same signatures, failure values --------------------------------------
+ * bm_load_adapter() is in host/adapter.c. */
 int bm_run_tokens(bm_context_t* ctx, bm_model_t* model, const int* prompt_ids, int n_prompt, int steps, float temperature, int top_k,
                   float top_p, uint64_t seed, bm_token_cb_t callback, void* user_data) {
     (void)ctx; (void)model; (void)prompt_ids; (void)n_prompt; (void)steps; (void)temperature; (void)top_k; (void)top_p; (void)seed;

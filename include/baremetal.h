@@ -8,9 +8,11 @@
  *
  * Scope of this build: the training path (bm_create .. bm_create_trainer, bm_train_step*, state
  * save/load, profiling), the inference session (bm_create_session, bm_forward, bm_step; fp32 / bf16 /
- * Q8 weights) and the greedy sampler run on the GPU backend. Entry points of the reference outside
- * those paths (tokenizer, adapters, weight export, the sampled-generation driver) are exported so
- * that the header is complete, and return the failure value of their signature.
+ * Q8 weights) and the greedy sampler run on the GPU backend; weight export (bm_save_weights) and
+ * adapter loading (bm_load_adapter merges the low-rank updates into the host weights) are host code.
+ * Entry points of the reference outside those paths (tokenizer, adapter training and bm_save_adapter,
+ * the sampled-generation driver) are exported so that the header is complete, and return the failure
+ * value of their signature.
  */
 #ifndef BAREMETAL_H
 #define BAREMETAL_H
@@ -52,7 +54,7 @@ typedef struct {
 /* ------------------------------------------------------------------ training configuration
  * Honoured: learning_rate, beta1, beta2, epsilon, weight_decay, grad_accum_steps, seq_len.
  * Carried but not read, exactly like the reference: grad_clip, warmup_steps, max_steps,
- * use_master_weights. lora_* must be 0 (adapters are outside this build). */
+ * use_master_weights. lora_* must be 0 (training of adapters is outside this build). */
 typedef struct {
     float learning_rate, beta1, beta2, epsilon, weight_decay, grad_clip;
     int grad_accum_steps, warmup_steps, max_steps, use_master_weights, seq_len, lora_rank;
@@ -81,6 +83,9 @@ void bm_compile(bm_model_t* model);
 void bm_autotune(bm_model_t* model, int warmup, int iterations);
 
 /* ------------------------------------------------------------------ inference */
+/* Adds scale * B * A of every entry of an adapter file to the model's host weights (call it before creating a
+ * session or trainer). 0 on success; -1 for an unreadable file, a header of another architecture or an entry
+ * whose target or shape does not fit the model. */
 int bm_load_adapter(bm_model_t* model, const char* path);
 bm_session_t* bm_create_session(bm_context_t* ctx, bm_model_t* model);
 float* bm_forward(bm_session_t* sess, const int* tokens, int n_tokens);

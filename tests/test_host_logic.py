@@ -159,8 +159,107 @@ def test_out_of_scope_entry_points_return_their_failure_values(product):
     lib.bm_create_tokenizer.restype = C.c_void_p
     assert not lib.bm_create_session(None, None)  # no context: no session
     assert not lib.bm_create_tokenizer(b"/nonexistent")
-    assert lib.bm_load_adapter(None, b"x") == -1
     assert lib.bm_save_adapter(None, b"x") == -1
+
+
+def _adapter_case(a, rank, seed, targets):
+    """Random A [r][c] and B [oc][r] for every (layer, target) asked for."""
+    rng = np.random.default_rng(seed)
+    shapes = dict(bmapi.weight_shapes(a))
+    entries = []
+    for layer, tgt in targets:
+        oc, c = shapes[bmapi.ADAPTER_WEIGHT_KEY[tgt]][1:]
+        entries.append((layer, tgt, rng.standard_normal((rank, c), dtype=np.float32) * np.float32(0.1),
+                        rng.standard_normal((oc, rank), dtype=np.float32) * np.float32(0.1)))
+    return entries
+
+
+def _merged(w, entries, rank, alpha):
+    """The reference's merge (src/baremetal/adapter.c:201-208): fp32 sum over k in increasing order, then w += scale * sum."""
+    out = {k: v.copy() for k, v in w.items()}
+    scale = np.float32(alpha) / np.float32(rank)
+    for layer, tgt, A, B in entries:
+        acc = np.zeros((B.shape[0], A.shape[1]), np.float32)
+        for k in range(rank):
+            acc += B[:, k:k + 1] * A[k:k + 1, :]
+        out[bmapi.ADAPTER_WEIGHT_KEY[tgt]][layer] += scale * acc
+    return out
+
+
+def _model_with_weights(lib, a, w, tmp_path):
+    path = str(tmp_path / "base.bin")
+    bmapi.write_bin_checkpoint(path, a, w)
+    model = lib.bm_create_model(None, C.byref(a))
+    lib.bm_load_weights(model, path.encode())
+    n = C.c_size_t()
+    flat = np.ctypeslib.as_array(lib.bmx_model_weight_buffer(model, C.byref(n)), (n.value,))
+    return model, flat
+
+
+def test_load_adapter_merges_every_target_into_the_host_weights(product, tmp_path):
+    """bm_load_adapter adds (alpha / rank) * B * A to the projection each entry names and leaves everything else alone; the
+    merged buffer equals the reference's arithmetic float for float."""
+    lib = product
+    a = bmapi.make_arch("gqa")
+    w = bmapi.make_weights(a, seed=5)
+    rank, alpha = 4, 12.0
+    targets = [(l, t) for l in range(a.n_layers) for t in ("q", "k", "v", "o", "gate", "up", "down")][::-1]  # any order
+    entries = _adapter_case(a, rank, 17, targets)
+    path = str(tmp_path / "all.bmlora")
+    bmapi.write_adapter_file(path, a, rank, alpha, entries)
+    model, flat = _model_with_weights(lib, a, w, tmp_path)
+    assert lib.bm_load_adapter(model, path.encode()) == 0
+    want = _merged(w, entries, rank, alpha)
+    expect = np.concatenate([want[k].ravel() for k, _ in bmapi.weight_shapes(a)])
+    assert np.array_equal(flat, expect)
+    for k in ("embed", "ln1w", "ln2w", "lnfw"):
+        assert np.array_equal(want[k], w[k])
+    # a second adapter on one projection of one layer stacks on the first
+    one = _adapter_case(a, 2, 23, [(1, "down")])
+    path2 = str(tmp_path / "one.bmlora")
+    bmapi.write_adapter_file(path2, a, 2, 1.0, one)
+    assert lib.bm_load_adapter(model, path2.encode()) == 0
+    want2 = _merged(want, one, 2, 1.0)
+    assert np.array_equal(flat, np.concatenate([want2[k].ravel() for k, _ in bmapi.weight_shapes(a)]))
+    lib.bm_destroy_model(model)
+
+
+def test_load_adapter_refuses_what_does_not_fit_the_model(product, tmp_path):
+    """Failure values of src/baremetal/adapter.c:151-196: unreadable file, bad magic / version, another architecture, an entry of
+    another rank, shape or target, a truncated payload; plus a layer index outside the model, which this build refuses."""
+    lib = product
+    a = bmapi.make_arch("gqa")
+    w = bmapi.make_weights(a, seed=5)
+    model, flat = _model_with_weights(lib, a, w, tmp_path)
+    before = flat.copy()
+    good = _adapter_case(a, 2, 1, [(0, "q")])
+    p = str(tmp_path / "bad.bmlora")
+    assert lib.bm_load_adapter(None, p.encode()) == -1
+    assert lib.bm_load_adapter(model, None) == -1
+    assert lib.bm_load_adapter(model, str(tmp_path / "missing").encode()) == -1
+    for over in ({"magic": 0x12345678}, {"version": 2}, {"dim": a.dim + 1}, {"layers": a.n_layers + 1}, {"n_heads": a.n_heads * 2},
+                 {"n_kv_heads": a.n_kv_heads + 1}, {"vocab": a.vocab_size - 1}, {"head_size": a.head_dim * 2}, {"rank": 0},
+                 {"n_adapters": 0}, {"rank": 3}):
+        bmapi.write_adapter_file(p, a, 2, 4.0, good, header_overrides=over)
+        assert lib.bm_load_adapter(model, p.encode()) == -1, over
+    _, _, A, B = good[0]
+    for bad in ((0, "k", A, B),                       # q-sized B on the k projection: oc mismatch
+                (0, 128, A, B),                       # not a target bit
+                (0, 3, A, B),                         # two bits at once
+                (a.n_layers, "q", A, B), (-1, "q", A, B),
+                (0, "q", A[:, :-1], B)):              # c mismatch
+        bmapi.write_adapter_file(p, a, 2, 4.0, [bad])
+        assert lib.bm_load_adapter(model, p.encode()) == -1, bad[:2]
+    bmapi.write_adapter_file(p, a, 2, 4.0, good)
+    blob = open(p, "rb").read()
+    for cut in (10, 44, 44 + 12, len(blob) - 4):
+        open(p, "wb").write(blob[:cut])
+        assert lib.bm_load_adapter(model, p.encode()) == -1, cut
+    assert np.array_equal(flat, before)               # none of the refused files touched the weights
+    open(p, "wb").write(blob)
+    assert lib.bm_load_adapter(model, p.encode()) == 0
+    assert not np.array_equal(flat, before)
+    lib.bm_destroy_model(model)
 
 
 def test_greedy_sampler_takes_the_first_maximum(product):

@@ -5,6 +5,7 @@
  2. against golden outputs of the reference's training step executed on CPU (tests/golden/ref_train_step_*.npz);
  3. against that reference build itself when oracle/_ref/libbm_ref.so is present.
 """
+import ctypes as C
 import glob
 import os
 
@@ -245,6 +246,55 @@ def test_port_matches_live_reference_build(arch, B, S, prec):
     for i in range(p.n_tensors()):
         assert oc.rel_err(p.read(bmapi.BMX_WEIGHT, i), r.read(bmapi.BMX_WEIGHT, i)) < 1e-5
     r.close(); p.close()
+
+
+@pytest.mark.skipif(oc.load_reference() is None, reason="reference build oracle/_ref/libbm_ref.so not present")
+def test_adapter_merge_matches_live_reference_build(tmp_path):
+    """bm_load_adapter of the product and of the reference build, given the same base weights and adapter file, leave the same
+    merged weights: the reference's are read back through a trainer created after the merge (fp32 working copies)."""
+    ref, prod = oc.load_reference(), bmapi.load_product()
+    a = bmapi.make_arch("gqa")
+    w = bmapi.make_weights(a, seed=5)
+    rank, alpha = 4, 6.0
+    rng = np.random.default_rng(3)
+    shapes = dict(bmapi.weight_shapes(a))
+    entries = []
+    for layer, tgt in [(0, "q"), (0, "down"), (1, "k"), (1, "v"), (1, "o"), (0, "gate"), (1, "up")]:
+        oc_, c = shapes[bmapi.ADAPTER_WEIGHT_KEY[tgt]][1:]
+        entries.append((layer, tgt, rng.standard_normal((rank, c), dtype=np.float32) * np.float32(0.1),
+                        rng.standard_normal((oc_, rank), dtype=np.float32) * np.float32(0.1)))
+    base, adp = str(tmp_path / "base.bin"), str(tmp_path / "a.bmlora")
+    bmapi.write_bin_checkpoint(base, a, w)
+    bmapi.write_adapter_file(adp, a, rank, alpha, entries)
+
+    pm = prod.bm_create_model(None, C.byref(a))
+    prod.bm_load_weights(pm, base.encode())
+    assert prod.bm_load_adapter(pm, adp.encode()) == 0
+    n = C.c_size_t()
+    flat = np.ctypeslib.as_array(prod.bmx_model_weight_buffer(pm, C.byref(n)), (n.value,)).copy()
+    prod.bm_destroy_model(pm)
+    got, off = {}, 0
+    for k, shp in bmapi.weight_shapes(a):
+        got[k] = flat[off:off + int(np.prod(shp))].reshape(shp)
+        off += int(np.prod(shp))
+
+    ctx = ref.bm_create(bmapi.BM_DEVICE_METAL)
+    rm = ref.bm_create_model(ctx, C.byref(a))
+    ref.bm_load_weights(rm, base.encode())
+    assert ref.bm_load_adapter(rm, adp.encode()) == 0
+    cfg = bmapi.train_config(seq_len=16)
+    tr = ref.bm_create_trainer(ctx, rm, C.byref(cfg))
+    assert tr
+    changed = 0
+    for i, (k, l) in enumerate(bmapi.state_tensor_order(a)):
+        r = oc.reference_read(ref, tr, bmapi.BMX_WEIGHT, i)
+        mine = (got[k] if l is None else got[k][l]).ravel()
+        assert np.array_equal(r, mine), (k, l)
+        changed += int(not np.array_equal(mine, (w[k] if l is None else w[k][l]).ravel()))
+    assert changed == len(entries)
+    ref.bm_destroy_trainer(tr)
+    ref.bm_destroy_model(rm)
+    ref.bm_destroy(ctx)
 
 
 def test_quirk_flags_change_only_what_they_name():
