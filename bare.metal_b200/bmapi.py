@@ -227,6 +227,7 @@ def load_product():
         "bmx_gemm_timing": (C.c_int, [vp, C.c_int]), "bmx_gemm_timing_collect": (C.c_int, [vp, C.POINTER(C.c_double)]),
         "bmx_model_set_quant": (C.c_int, [vp, C.c_int]), "bmx_model_vocab_size": (C.c_int, [vp]),
         "bmx_quantize_q8": (C.c_size_t, [fp, vp, fp, C.c_size_t]),
+        "bmx_quantize_q4": (C.c_size_t, [fp, vp, fp, C.c_size_t]),
         "bmx_create_session_batched": (vp, [vp, vp, C.c_int, C.c_int]), "bmx_create_session_kv": (vp, [vp, vp, C.c_int, C.c_int, C.c_int]),
         "bmx_session_kv_bytes_per_element": (C.c_int, [vp]),
         "bmx_session_generate_greedy": (C.c_int, [vp, ip, C.c_int, C.c_int, ip]),

@@ -197,7 +197,7 @@ double bmx_model_arch_field(const bm_model_t* model, const char* name) {
     return -1.0;
 }
 int bmx_model_set_quant(bm_model_t* model, int bits) {
-    if (!model || (bits != 0 && bits != 8)) return -1; /* Q4 is outside this build */
+    if (!model || (bits != 0 && bits != 4 && bits != 8)) return -1;
     model->quant_bits = bits;
     return 0;
 }

@@ -6,6 +6,10 @@
  *   then       final RMSNorm -> LM-head GEMV (never quantised, src/baremetal/graph.c:228-239) -> logits.
  * Q8 quantisation is the reference's (bmt_quantize_q8, src/baremetal/quant.c:10-29,54-60): per 32 weights of a row,
  * scale = amax / 127, q = lroundf(w / scale) clamped to [-128, 127]; applied to every 2-D layer matrix.
+ * Q4 (bmt_quantize_q4, src/baremetal/quant.c:31-52) is the same scheme with scale = amax / 7 and q clamped to [-8, 7]. The
+ * reference multiplies x * ((float)q * scale) for both widths (matmul_forward_q8 / matmul_forward_q4, src/kernels/forward.metal:
+ * 575-650, 830-858), so a Q4 session keeps its codes as int8 and runs the Q8 kernels: same results as the reference's Q4, at
+ * 1.125 instead of 0.625 bytes per weight (a GEMV over packed nibbles is not built).
  * The whole step is enqueued without host synchronisation and, after the first token, replayed as a CUDA graph; the
  * position lives in device memory. bm_forward with several tokens runs the same step per token, which the reference
  * establishes as equivalent to its sequence prefill (test/prefill_test.c).
@@ -83,6 +87,38 @@ size_t bmx_quantize_q8(const float* src, int8_t* q, float* scales, size_t n) {
     return n / 32;
 }
 
+/* one 32-wide block of the reference's 4-bit quantiser (src/baremetal/quant.c:31-52), codes left unpacked: the reference stores
+ * code 2j in the low and code 2j+1 in the high nibble of byte j and sign-extends them again in its kernels */
+static void quantize_q4_block(const float* p, float* scale_out, int8_t* q) {
+    float amax = 0.0f;
+    for (int i = 0; i < 32; i++) {
+        const float a = fabsf(p[i]);
+        if (a > amax) amax = a;
+    }
+    const float scale = amax / 7.0f;
+    *scale_out = scale;
+    if (scale == 0.0f) {
+        memset(q, 0, 32);
+        return;
+    }
+    const float inv = 1.0f / scale;
+    for (int i = 0; i < 32; i++) {
+        long v = lroundf(p[i] * inv);
+        if (v > 7) v = 7;
+        if (v < -8) v = -8;
+        q[i] = (int8_t)v;
+    }
+}
+/* exported for tests: as bmx_quantize_q8, with codes in [-8, 7] */
+size_t bmx_quantize_q4(const float* src, int8_t* q, float* scales, size_t n) {
+    if (n == 0 || (n % 32) != 0) return 0;
+    for (size_t b = 0; b < n / 32; b++) quantize_q4_block(src + b * 32, &scales[b], q + b * 32);
+    return n / 32;
+}
+static size_t quantize_blocks(int bits, const float* src, int8_t* q, float* scales, size_t n) {
+    return bits == 4 ? bmx_quantize_q4(src, q, scales, n) : bmx_quantize_q8(src, q, scales, n);
+}
+
 /* upload `rows` (OC x C fp32, given as up to three row blocks that are concatenated) in the session's weight type */
 static int upload_matrix(bm_session_t* s, bm_mat_t* m, int wtype, const float* const* parts, const int* part_rows, int n_parts, int C) {
     bmc_ctx_t* be = s->ctx->be;
@@ -101,10 +137,10 @@ static int upload_matrix(bm_session_t* s, bm_mat_t* m, int wtype, const float* c
     int rc = 0;
     if (wtype == BMC_W_Q8) {
         /* quantised from the loaded values; a bf16 checkpoint was widened exactly, so this equals the reference's
-         * bmt_quantize_q8_bf16 for bf16 sources and bmt_quantize_q8 for fp32 ones (src/baremetal/scheduler.c:378-384) */
+         * bmt_quantize_q8_bf16 / _q4_bf16 for bf16 sources and bmt_quantize_q8 / _q4 for fp32 ones (src/baremetal/scheduler.c:378-392) */
         int8_t* q = (int8_t*)malloc(n);
         float* sc = (float*)malloc(n / 32 * sizeof(float));
-        bmx_quantize_q8(host, q, sc, n);
+        quantize_blocks(s->model->quant_bits, host, q, sc, n);
         m->w = bmc_alloc(be, n);
         m->scales = (float*)bmc_alloc(be, n / 32 * sizeof(float));
         if (!m->w || !m->scales) rc = -1;
@@ -133,7 +169,7 @@ static int upload_matrix(bm_session_t* s, bm_mat_t* m, int wtype, const float* c
         if (wtype == BMC_W_Q8) {
             int8_t* q = (int8_t*)malloc(n);
             float* sc = (float*)malloc(n / 32 * sizeof(float));
-            bmx_quantize_q8(host, q, sc, n);
+            quantize_blocks(s->model->quant_bits, host, q, sc, n);
             for (size_t i = 0; i < n; i++) eff[i] = (float)q[i] * sc[i / 32];
             free(q);
             free(sc);
@@ -198,7 +234,7 @@ bm_session_t* bmx_create_session_kv(bm_context_t* ctx, bm_model_t* model, int n_
     s->tc = s->tc_weights && n_sequences >= BM_TC_MIN_SEQUENCES;
     s->MS = max_positions > 0 ? max_positions : (a->max_seq_len > 0 ? a->max_seq_len : 2048);
     const int lowp = model->precision == BM_PRECISION_BF16;
-    s->wtype = model->quant_bits == 8 ? BMC_W_Q8 : (lowp ? BMC_W_BF16 : BMC_W_F32);
+    s->wtype = (model->quant_bits == 8 || model->quant_bits == 4) ? BMC_W_Q8 : (lowp ? BMC_W_BF16 : BMC_W_F32);
     s->head_type = lowp ? BMC_W_BF16 : BMC_W_F32;
     bmc_ctx_t* be = ctx->be;
     const int L = a->n_layers, D = a->dim, H = a->hidden_dim, V = a->vocab_size, HD = model->head_size;
@@ -540,7 +576,8 @@ const float* bmx_session_logits(bm_session_t* s) {
 }
 int bmx_session_position(bm_session_t* s) { return s ? s->pos : -1; }
 /* Bytes of weights one step must read at the least: the matrices in the precision the model asks for (Q8: int8 blocks of 32 with one
- * fp32 scale = 1.125 bytes per weight, as the reference counts them, bench/bench.c:339-348), whatever layout the session streams. */
+ * fp32 scale = 1.125 bytes per weight, Q4: 0.625, as the reference counts them, bench/bench.c:339-348), whatever layout the session
+ * streams. */
 size_t bmx_session_algorithmic_weight_bytes(bm_session_t* s) {
     if (!s) return 0;
     size_t n = 0;
@@ -548,7 +585,7 @@ size_t bmx_session_algorithmic_weight_bytes(bm_session_t* s) {
         const bm_mat_t* ms[4] = {&s->layers[l].qkv, &s->layers[l].o, &s->layers[l].gu, &s->layers[l].down};
         for (int i = 0; i < 4; i++) {
             const size_t e = (size_t)ms[i]->OC * ms[i]->C;
-            n += s->wtype == BMC_W_Q8 ? e + e / 32 * 4 : s->wtype == BMC_W_BF16 ? e * 2 : e * 4;
+            n += s->wtype == BMC_W_Q8 ? (s->model->quant_bits == 4 ? e / 2 : e) + e / 32 * 4 : s->wtype == BMC_W_BF16 ? e * 2 : e * 4;
         }
     }
     n += (size_t)s->model->arch.vocab_size * s->model->arch.dim * (s->head_type == BMC_W_BF16 ? 2 : 4);

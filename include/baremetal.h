@@ -8,7 +8,7 @@
  *
  * Scope of this build: the training path (bm_create .. bm_create_trainer, bm_train_step*, state
  * save/load, profiling), the inference session (bm_create_session, bm_forward, bm_step; fp32 / bf16 /
- * Q8 weights) and the greedy sampler run on the GPU backend; weight export (bm_save_weights) and
+ * Q8 / Q4 weights) and the greedy sampler run on the GPU backend; weight export (bm_save_weights) and
  * adapter loading (bm_load_adapter merges the low-rank updates into the host weights) are host code.
  * Entry points of the reference outside those paths (tokenizer, adapter training and bm_save_adapter,
  * the sampled-generation driver) are exported so that the header is complete, and return the failure

@@ -72,11 +72,15 @@ int    bmx_gemm_timing(bm_context_t* ctx, int enable);
 int    bmx_gemm_timing_collect(bm_context_t* ctx, double* out3);
 
 /* ---- inference ----
- * Q8 selection: the reference sets bm_model_s::quant_bits from its CLI (tools/cli.c:886); here through a call. bits = 0 or 8. */
+ * Q8 / Q4 selection: the reference sets bm_model_s::quant_bits from its CLI (tools/cli.c:886); here through a call. bits = 0, 4 or 8.
+ * A 4-bit session gives the reference's Q4 results but keeps its codes as int8 (1.125 bytes per weight on the device). */
 int    bmx_model_set_quant(bm_model_t* model, int bits);
 /* The reference's Q8 block quantiser (bmt_quantize_q8, src/baremetal/quant.c:10-29,54-60) with the int8 values and the scales
  * in two arrays: q[n], scales[n/32]. Returns the number of blocks, 0 when n is not a positive multiple of 32. */
 size_t bmx_quantize_q8(const float* src, int8_t* q, float* scales, size_t n);
+/* The reference's Q4 block quantiser (bmt_quantize_q4, src/baremetal/quant.c:31-52, 73-79) with the codes unpacked: q[n] in [-8, 7]
+ * (the reference packs code 2j into the low and 2j+1 into the high nibble of byte j), scales[n/32] = amax / 7. */
+size_t bmx_quantize_q4(const float* src, int8_t* q, float* scales, size_t n);
 /* A session that advances n_sequences independent sequences in lock step (the reference API is single-sequence:
  * bm_create_session == n_sequences 1). max_positions = KV cache length per sequence (0: the model's max_seq_len). */
 bm_session_t* bmx_create_session_batched(bm_context_t* ctx, bm_model_t* model, int n_sequences, int max_positions);

@@ -525,7 +525,7 @@ float orc_step(orc_t* o, const int* inputs, const int* targets, int B) {
 
 /* ======================= inference: prefill / decode with a KV cache, Q8 or plain weights =========================
  * Restates the reference's decode walk (src/baremetal/scheduler.c:712-996 over the graph of src/baremetal/graph.c:109-240):
- * fp32 activations, fp32 KV cache, layer matrices optionally Q8 (src/baremetal/quant.c:10-29), LM head never quantised
+ * fp32 activations, fp32 KV cache, layer matrices optionally Q8 or Q4 (src/baremetal/quant.c:10-52), LM head never quantised
  * (graph.c:228-239). Matmul with Q8 weights: val += x[i] * ((float)q[i] * scale) (matmul_forward_q8,
  * src/kernels/forward.metal:625-648). */
 size_t orc_quantize_q8(const float* src, int8_t* q, float* scales, size_t n) {
@@ -548,6 +548,30 @@ size_t orc_quantize_q8(const float* src, int8_t* q, float* scales, size_t n) {
     return n / 32;
 }
 
+/* Q4 (src/baremetal/quant.c:31-52): scale = amax / 7, codes clamped to [-8, 7]. The reference packs code 2j into the low and
+ * code 2j+1 into the high nibble of byte j and its kernels sign-extend them again (matmul_forward_q4,
+ * src/kernels/forward.metal:830-858: val += x[2j] * ((float)lo * s); val += x[2j+1] * ((float)hi * s), the Q8 arithmetic on the
+ * narrower codes); here the codes stay one per byte. */
+size_t orc_quantize_q4(const float* src, int8_t* q, float* scales, size_t n) {
+    if (n == 0 || (n % 32) != 0) return 0;
+    for (size_t b = 0; b < n / 32; b++) {
+        const float* p = src + b * 32;
+        float amax = 0.0f;
+        for (int i = 0; i < 32; i++) { const float a = fabsf(p[i]); if (a > amax) amax = a; }
+        const float scale = amax / 7.0f;
+        scales[b] = scale;
+        if (scale == 0.0f) { memset(q + b * 32, 0, 32); continue; }
+        const float inv = 1.0f / scale;
+        for (int i = 0; i < 32; i++) {
+            long v = lroundf(p[i] * inv);
+            if (v > 7) v = 7;
+            if (v < -8) v = -8;
+            q[b * 32 + i] = (int8_t)v;
+        }
+    }
+    return n / 32;
+}
+
 typedef struct { float* w; int8_t* q; float* sc; int OC, C; } orc_mat_t;
 typedef struct {
     int D, H, L, NH, NKV, V, HD, MS, pos, quant;
@@ -561,11 +585,12 @@ typedef struct {
 static void mat_init(orc_mat_t* m, const float* src, int OC, int C, int quant, int round_bf16) {
     m->OC = OC; m->C = C; m->w = NULL; m->q = NULL; m->sc = NULL;
     const size_t n = (size_t)OC * C;
-    if (quant == 8) {
-        /* from the loaded fp32 values (src/baremetal/scheduler.c:378-384; a bf16 source widens exactly) */
+    if (quant == 8 || quant == 4) {
+        /* from the loaded fp32 values (src/baremetal/scheduler.c:378-392; a bf16 source widens exactly) */
         m->q = (int8_t*)malloc(n);
         m->sc = (float*)malloc(n / 32 * sizeof(float));
-        orc_quantize_q8(src, m->q, m->sc, n);
+        if (quant == 8) orc_quantize_q8(src, m->q, m->sc, n);
+        else orc_quantize_q4(src, m->q, m->sc, n);
     } else {
         m->w = (float*)malloc(n * sizeof(float));
         for (size_t i = 0; i < n; i++) m->w[i] = round_bf16 ? bf16_round(src[i]) : src[i];

@@ -45,6 +45,7 @@ def load_reference(path=REF_LIB_PATH):
     lib.bmref_set_precision.argtypes = [vp, C.c_int]
     lib.bmref_set_quant.argtypes = [vp, C.c_int]
     lib.bmt_quantize_q8.restype, lib.bmt_quantize_q8.argtypes = C.c_size_t, [fp, vp, C.c_size_t]
+    lib.bmt_quantize_q4.restype, lib.bmt_quantize_q4.argtypes = C.c_size_t, [fp, vp, C.c_size_t]
     lib.bmref_n_states.restype, lib.bmref_n_states.argtypes = C.c_int, [vp]
     lib.bmref_state_size.restype, lib.bmref_state_size.argtypes = C.c_size_t, [vp, C.c_int]
     for n in ("bmref_grad", "bmref_weight", "bmref_m", "bmref_v"):
@@ -68,6 +69,7 @@ def load_port():
     lib.orc_xent.restype = C.c_float
     lib.orc_argmax.restype = C.c_int
     lib.orc_quantize_q8.restype, lib.orc_quantize_q8.argtypes = C.c_size_t, [fp, vp, fp, C.c_size_t]
+    lib.orc_quantize_q4.restype, lib.orc_quantize_q4.argtypes = C.c_size_t, [fp, vp, fp, C.c_size_t]
     lib.orc_dec_create.restype = vp
     lib.orc_dec_create.argtypes = [C.c_int] * 10 + [C.c_float, fp]
     lib.orc_dec_destroy.argtypes = [vp]

@@ -90,6 +90,7 @@ const std::map<std::string, KernelEntry>& kernel_table() {
     REG(fwd, matmul_forward_naive)
     REG(fwd, matmul_forward_bf16)
     REG(fwd, matmul_forward_q8)
+    REG(fwd, matmul_forward_q4)
     REG(fwd, rmsnorm_forward)
     REG(fwd, swiglu_forward)
     REG(fwd, add_forward)

@@ -22,9 +22,9 @@ and sampled final weights), ref_decode_360m_{f32,bf16}_q8.npz (SmolLM2-360M with
 sampled logits only), oracle_attention_s8192_group.npz (the isolated-attention configuration at 8192 tokens, one KV group, from the
 plain-C oracle).
 
-Part 3 (`--only-decode` regenerates just this part) — ref_quantize_q8.npz: the reference's Q8 block quantiser on seeded
-inputs with its edge cases; ref_decode_*.npz: logits of the reference inference session after every prefix of a seeded
-prompt and a greedy continuation, fp32 / bf16 weights, plain and Q8.
+Part 3 (`--only-decode` regenerates just this part) — ref_quantize_q8.npz / ref_quantize_q4.npz: the reference's Q8 and Q4 block
+quantisers on seeded inputs with their edge cases (Q4 codes stored unpacked, one per byte); ref_decode_*.npz: logits of the
+reference inference session after every prefix of a seeded prompt and a greedy continuation, fp32 / bf16 weights, plain, Q8 and Q4.
 """
 import ctypes as C
 import os
@@ -222,6 +222,23 @@ def ref_q8_case(ref):
     print(f"ref_quantize_q8.npz: {nb} blocks")
 
 
+def ref_q4_case(ref):
+    """Same inputs through bmt_quantize_q4; q4_block_t is {f32 scale; u8 qs[16]} with code 2j in the low and code 2j+1 in the high
+    nibble of byte j (src/baremetal/quant.h:39-42, quant.c:44-50). Stored: the sign-extended codes, one per byte."""
+    x = q8_inputs()
+    x[64:96] = (np.arange(32, dtype=np.float32) - 16.0) * 0.5   # amax 8 -> scale 8/7: quotients on and next to .5
+    nb = x.size // 32
+    blocks = np.zeros(nb, dtype=np.dtype([("scale", "<f4"), ("qs", "u1", (16,))]))
+    assert blocks.itemsize == 20
+    assert ref.bmt_quantize_q4(oc.fptr(x), blocks.ctypes.data, x.size) == nb
+    lo = (blocks["qs"] & 0x0F).astype(np.int8)
+    hi = (blocks["qs"] >> 4).astype(np.int8)
+    q = np.stack([lo, hi], axis=-1).reshape(nb, 32)
+    q = np.where(q > 7, q - 16, q).astype(np.int8)
+    np.savez_compressed(os.path.join(OUT, "ref_quantize_q4.npz"), x=x, scale=blocks["scale"].copy(), q=q)
+    print(f"ref_quantize_q4.npz: {nb} blocks, codes {q.min()}..{q.max()}")
+
+
 def ref_decode_case(ref, tag, arch_name, precision, quant, n_prompt, n_new):
     """Logits of the reference session after every prefix (2..n_prompt tokens) of a seeded prompt, then a greedy
     continuation, each token from a fresh prefill of the whole prefix (the barrier-free path of the CPU build)."""
@@ -257,7 +274,8 @@ def main():
         raise SystemExit("oracle/_ref/libbm_ref.so missing: run oracle/build_ref.sh first")
     F32, BF16 = bmapi.BM_PRECISION_FP32, bmapi.BM_PRECISION_BF16
     decode_cases = (("gqa_f32", "gqa", F32, 0), ("gqa_f32_q8", "gqa", F32, 8), ("gqa_bf16", "gqa", BF16, 0),
-                    ("gqa_bf16_q8", "gqa", BF16, 8), ("tiny_f32_q8", "tiny", F32, 8))
+                    ("gqa_bf16_q8", "gqa", BF16, 8), ("tiny_f32_q8", "tiny", F32, 8), ("gqa_f32_q4", "gqa", F32, 4),
+                    ("gqa_bf16_q4", "gqa", BF16, 4))
     big = {
         "360m_bf16_b2": lambda: ref_train_case(ref, "360m_bf16_b2", "smollm2-360m", 2, 128, BF16, 2),
         "360m_f32_b2": lambda: ref_train_case(ref, "360m_f32_b2", "smollm2-360m", 2, 128, F32, 2),
@@ -268,13 +286,17 @@ def main():
         "decode_360m_bf16_q8": lambda: ref_decode_sampled_case(ref, "360m_bf16_q8", "smollm2-360m", BF16, 8, 64, 16),
         "c4_s8192_group": lambda: c4_group_case(8192),
     }
+    small = {"quantize_q4": lambda: ref_q4_case(ref)}
+    for tag, arch, prec, quant in decode_cases:
+        small["decode_" + tag] = (lambda t=tag, a=arch, p=prec, q=quant: ref_decode_case(ref, t, a, p, q, 12, 12))
     for arg in sys.argv[1:]:
         if arg.startswith("--only="):
             for tag in arg[len("--only="):].split(","):
-                big[tag]()
+                (big | small)[tag]()
             return
     if "--only-decode" in sys.argv:
         ref_q8_case(ref)
+        ref_q4_case(ref)
         for tag, arch, prec, quant in decode_cases:
             ref_decode_case(ref, tag, arch, prec, quant, 12, 12)
         return
@@ -286,6 +308,7 @@ def main():
     ref_train_case(ref, "gqa_bf16_b2", "gqa", 2, 128, BF16, 2)
     ref_train_case(ref, "small_f32_accum2", "small", 2, 64, F32, 2, accum=2)
     ref_q8_case(ref)
+    ref_q4_case(ref)
     for tag, arch, prec, quant in decode_cases:
         ref_decode_case(ref, tag, arch, prec, quant, 12, 12)
     if "--skip-135m" not in sys.argv:

@@ -120,7 +120,7 @@ def _batched(product, a, w, precision, quant, NB, MS):
     return ctx, model, sess
 
 
-@pytest.mark.parametrize("precision,quant,NB", [(F32, 0, 3), (BF16, 8, 11), (BF16, 0, 8), (F32, 8, 1), (F32, 8, 5), (F32, 0, 16), (BF16, 8, 64)])
+@pytest.mark.parametrize("precision,quant,NB", [(F32, 0, 3), (BF16, 8, 11), (BF16, 0, 8), (F32, 8, 1), (F32, 8, 5), (F32, 0, 16), (BF16, 8, 64), (BF16, 4, 11)])
 def test_batched_sequences_equal_single_sequences(product, precision, quant, NB):
     """NB sequences decoded in lock step give, per sequence, exactly the ids and logits of that sequence decoded alone."""
     a = bmapi.make_arch("gqa")

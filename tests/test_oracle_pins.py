@@ -347,6 +347,32 @@ def test_product_host_quantiser_is_bit_exact_with_the_reference():
     assert np.array_equal(q, g["q"]) and np.array_equal(sc.view(np.uint32), g["scale"].view(np.uint32))
 
 
+def test_quantize_q4_port_and_product_are_bit_exact_with_the_reference(port):
+    """bmt_quantize_q4 on the same seeded blocks (scale = amax / 7, codes in [-8, 7], src/baremetal/quant.c:31-52): the fixture holds the
+    reference's codes sign-extended and unpacked; the port's and the product's host quantiser give the same codes and scales."""
+    g = np.load(os.path.join(GOLD_DIR, "ref_quantize_q4.npz"))
+    x = np.ascontiguousarray(g["x"])
+    for fn in (port.orc_quantize_q4, bmapi.load_product().bmx_quantize_q4):
+        q, sc = _quantize(fn, x)
+        assert np.array_equal(q, g["q"]) and np.array_equal(sc.view(np.uint32), g["scale"].view(np.uint32))
+        assert q.min() >= -8 and q.max() <= 7
+        one = np.ones(33, np.float32)
+        assert fn(oc.fptr(one), q.ctypes.data, oc.fptr(sc), 33) == 0 and fn(oc.fptr(one), q.ctypes.data, oc.fptr(sc), 0) == 0
+
+
+def test_live_reference_q4_quantiser_matches_port_on_random_blocks(port):
+    ref = oc.load_reference()
+    if ref is None:
+        pytest.skip("reference build absent")
+    x = (np.random.default_rng(6).standard_normal(32 * 257) * 0.3).astype(np.float32)
+    blocks = np.zeros(x.size // 32, dtype=np.dtype([("scale", "<f4"), ("qs", "u1", (16,))]))   # q4_block_t, src/baremetal/quant.h:39-42
+    assert ref.bmt_quantize_q4(oc.fptr(x), blocks.ctypes.data, x.size) == x.size // 32
+    codes = np.stack([blocks["qs"] & 0x0F, blocks["qs"] >> 4], axis=-1).reshape(-1, 32).astype(np.int8)
+    codes = np.where(codes > 7, codes - 16, codes).astype(np.int8)
+    q, sc = _quantize(port.orc_quantize_q4, x)
+    assert np.array_equal(q, codes) and np.array_equal(sc, blocks["scale"])
+
+
 def test_live_reference_quantiser_matches_port_on_random_blocks(port):
     ref = oc.load_reference()
     if ref is None:
