@@ -213,6 +213,49 @@ def test_135m_q8_decode_against_oracle(product):
     dec.close()
 
 
+@pytest.mark.parametrize("quant", [0, 4])
+def test_session_after_adapter_merge_against_oracle(product, quant, tmp_path):
+    """bm_load_weights -> bm_load_adapter -> session: the logits are those of the plain-C oracle on base weights + (alpha / rank) * B * A
+    (merged here with numpy in the reference's summation order), and differ from the base model's."""
+    a = bmapi.make_arch("gqa")
+    w = bmapi.make_weights(a, layer_scale=8.0)
+    rank, alpha = 4, 8.0
+    rng = np.random.default_rng(31)
+    shapes = dict(bmapi.weight_shapes(a))
+    entries, merged = [], {k: v.copy() for k, v in w.items()}
+    for layer, tgt in [(0, "q"), (0, "v"), (1, "o"), (1, "gate"), (0, "down")]:
+        key = bmapi.ADAPTER_WEIGHT_KEY[tgt]
+        oc_, c = shapes[key][1:]
+        A = rng.standard_normal((rank, c), dtype=np.float32) * np.float32(0.1)
+        B = rng.standard_normal((oc_, rank), dtype=np.float32) * np.float32(0.1)
+        entries.append((layer, tgt, A, B))
+        acc = np.zeros((oc_, c), np.float32)
+        for k in range(rank):
+            acc += B[:, k:k + 1] * A[k:k + 1, :]
+        merged[key][layer] += (np.float32(alpha) / np.float32(rank)) * acc
+    base, adp = str(tmp_path / "base.bin"), str(tmp_path / "a.bmlora")
+    bmapi.write_bin_checkpoint(base, a, w)
+    bmapi.write_adapter_file(adp, a, rank, alpha, entries)
+    ctx = product.bm_create(bmapi.BM_DEVICE_METAL)
+    model = product.bm_create_model(ctx, C.byref(a))
+    product.bm_load_weights(model, base.encode())
+    assert product.bm_load_adapter(model, adp.encode()) == 0
+    assert product.bmx_model_set_quant(model, quant) == 0
+    sess = product.bm_create_session(ctx, model)
+    assert sess
+    dec, plain = oc.PortDecoder(a, merged, F32, quant, 16), oc.PortDecoder(a, w, F32, quant, 16)
+    V = a.vocab_size
+    for t in bmapi.lcg_tokens(6, V, seed=5):
+        lg = np.ctypeslib.as_array(product.bm_step(sess, int(t)), shape=(V,)).copy()
+        lo, lb = dec.step(t), plain.step(t)
+        assert close(lg, lo), np.abs(lg - lo).max()
+    assert np.abs(lo - lb).max() > 100 * TOL * np.abs(lo).max()   # the adapter changed the model
+    dec.close(); plain.close()
+    product.bm_destroy_session(sess)
+    product.bm_destroy_model(model)
+    product.bm_destroy(ctx)
+
+
 # ---- kernels of the inference path through the extern "C" backend ABI ----------------------------------------------------
 import portk  # noqa: E402
 from bmcapi import BMC_BF16, BMC_F32, Backend, Ptr, bf16_round, f32_to_bf16_bits  # noqa: E402
