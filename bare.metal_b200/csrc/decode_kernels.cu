@@ -43,8 +43,17 @@ __device__ __forceinline__ void dequant4(uint32_t pk, float s, float* w) {
     w[3] = (__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7543)) - 8388736.0f) * s;
 }
 
-// WT: 0 = Q8 (q + scales), 1 = bf16, 2 = fp32. Elements one lane reads with one 16-byte load:
-template <int WT> struct Epl { static constexpr int v = WT == 0 ? 16 : (WT == 1 ? 8 : 4); };
+// eight 4-bit codes of one 32-bit word -> (float)q * scale, q = the nibble read as a two's-complement number in [-8, 7]
+// (matmul_forward_q4, src/kernels/forward.metal:849-854: element 2j is the low and 2j+1 the high nibble of byte j, so
+// element i of a little-endian word is bits [4i, 4i+4)). nibble ^ 8 = q + 8, placed in the mantissa of 2^23.
+__device__ __forceinline__ void dequant8_nibbles(uint32_t pk, float s, float* w) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) w[i] = (__uint_as_float(((pk >> (4 * i)) & 0xFu) ^ 0x4B000008u) - 8388616.0f) * s;
+}
+
+// WT: 0 = Q8 (q + scales), 1 = bf16, 2 = fp32, 3 = Q4 (two codes per byte + scales). Elements one lane reads with one load
+// (16 bytes; 8 bytes for Q4):
+template <int WT> struct Epl { static constexpr int v = (WT == 0 || WT == 3) ? 16 : (WT == 1 ? 8 : 4); };
 
 // raw 16-byte weight chunk of one lane (+ its block scale for Q8), loaded before the data it multiplies is known
 struct RawW { uint4 v; float s; };
@@ -57,6 +66,10 @@ __device__ __forceinline__ RawW load_raw(const void* w, const float* scales, siz
         r.s = scales[row * (C / 32) + (c >> 5)];
     } else if (WT == 1) {
         r.v = *reinterpret_cast<const uint4*>((const bf16*)w + row * C + c);
+    } else if (WT == 3) {
+        const uint2 h = *reinterpret_cast<const uint2*>((const uint8_t*)w + ((row * C + c) >> 1));
+        r.v = make_uint4(h.x, h.y, 0u, 0u);
+        r.s = scales[row * (C / 32) + (c >> 5)];
     } else {
         r.v = *reinterpret_cast<const uint4*>((const float*)w + row * C + c);
     }
@@ -71,6 +84,8 @@ __device__ __forceinline__ void expand_raw(const RawW& r, float* wv) {
         wv[2] = __uint_as_float(r.v.y << 16); wv[3] = __uint_as_float(r.v.y & 0xffff0000u);
         wv[4] = __uint_as_float(r.v.z << 16); wv[5] = __uint_as_float(r.v.z & 0xffff0000u);
         wv[6] = __uint_as_float(r.v.w << 16); wv[7] = __uint_as_float(r.v.w & 0xffff0000u);
+    } else if (WT == 3) {
+        dequant8_nibbles(r.v.x, r.s, wv); dequant8_nibbles(r.v.y, r.s, wv + 8);
     } else {
         wv[0] = __uint_as_float(r.v.x); wv[1] = __uint_as_float(r.v.y); wv[2] = __uint_as_float(r.v.z); wv[3] = __uint_as_float(r.v.w);
     }
@@ -243,6 +258,11 @@ decode_gemvb_kernel(float* __restrict__ out, int ldo, const float* __restrict__ 
                     const uint2 pk = *reinterpret_cast<const uint2*>((const bf16*)w + row * C + c);
                     wv[r][0] = __uint_as_float(pk.x << 16); wv[r][1] = __uint_as_float(pk.x & 0xffff0000u);
                     wv[r][2] = __uint_as_float(pk.y << 16); wv[r][3] = __uint_as_float(pk.y & 0xffff0000u);
+                } else if (WT == 3) {
+                    const uint32_t pk = *reinterpret_cast<const uint16_t*>((const uint8_t*)w + ((row * C + c) >> 1));
+                    const float sc = scales[row * (C / 32) + (c >> 5)];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) wv[r][i] = (__uint_as_float(((pk >> (4 * i)) & 0xFu) ^ 0x4B000008u) - 8388616.0f) * sc;
                 } else {
                     const float4 v = *reinterpret_cast<const float4*>((const float*)w + row * C + c);
                     wv[r][0] = v.x; wv[r][1] = v.y; wv[r][2] = v.z; wv[r][3] = v.w;
@@ -823,7 +843,9 @@ int decode_gemv(float* out, int ldo, const float* x, int ldx, int wtype, const v
     if (C % 32 || NB <= 0 || (ldx & 3) || prologue < 0 || prologue > 2 || (prologue == 1 && !lnw)) return -1;
     if (wtype == 0) return gemv_dispatch<0>(out, ldo, x, ldx, w, scales, res, ldr, prologue, lnw, eps, NB, C, OC, st);
     if (wtype == 1) return gemv_dispatch<1>(out, ldo, x, ldx, w, scales, res, ldr, prologue, lnw, eps, NB, C, OC, st);
-    return gemv_dispatch<2>(out, ldo, x, ldx, w, scales, res, ldr, prologue, lnw, eps, NB, C, OC, st);
+    if (wtype == 2) return gemv_dispatch<2>(out, ldo, x, ldx, w, scales, res, ldr, prologue, lnw, eps, NB, C, OC, st);
+    if (wtype == 3) return gemv_dispatch<3>(out, ldo, x, ldx, w, scales, res, ldr, prologue, lnw, eps, NB, C, OC, st);
+    return -1;
 }
 int decode_rmsnorm(float* out, const float* x, const float* w, int NB, int C, float eps, cudaStream_t st) {
     return launch_k(decode_rmsnorm_kernel, dim3(NB), dim3(256), 0, st, out, x, w, C, eps);

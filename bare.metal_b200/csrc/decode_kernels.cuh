@@ -3,7 +3,8 @@
 #include "common.cuh"
 
 namespace bmb {
-// wtype: 0 = Q8 (w = int8 q[OC][C], scales = float[OC][C/32]), 1 = bf16, 2 = fp32. out[b, oc] = x[b,:] . w[oc,:] (+ res[b, oc])
+// wtype: 0 = Q8 (w = int8 q[OC][C], scales = float[OC][C/32]), 1 = bf16, 2 = fp32, 3 = Q4 (w = uint8 [OC][C/2], element 2j in the low
+// and 2j+1 in the high nibble of byte j, scales as Q8). out[b, oc] = x[b,:] . w[oc,:] (+ res[b, oc])
 // prologue: 0 = none, 1 = RMSNorm(x) * lnw folded in, 2 = x is [gate | up] (2C wide) and the operand is silu(gate) * up
 int decode_gemv(float* out, int ldo, const float* x, int ldx, int wtype, const void* w, const float* scales, const float* res, int ldr,
                 int prologue, const float* lnw, float eps, int NB, int C, int OC, cudaStream_t st);

@@ -8,8 +8,8 @@
  * scale = amax / 127, q = lroundf(w / scale) clamped to [-128, 127]; applied to every 2-D layer matrix.
  * Q4 (bmt_quantize_q4, src/baremetal/quant.c:31-52) is the same scheme with scale = amax / 7 and q clamped to [-8, 7]. The
  * reference multiplies x * ((float)q * scale) for both widths (matmul_forward_q8 / matmul_forward_q4, src/kernels/forward.metal:
- * 575-650, 830-858), so a Q4 session keeps its codes as int8 and runs the Q8 kernels: same results as the reference's Q4, at
- * 1.125 instead of 0.625 bytes per weight (a GEMV over packed nibbles is not built).
+ * 575-650, 830-858). On the device a Q4 matrix is the reference's block content as two arrays: two codes per byte (element 2j of a
+ * row in the low, 2j+1 in the high nibble of byte j) and the scales, 0.625 bytes per weight.
  * The whole step is enqueued without host synchronisation and, after the first token, replayed as a CUDA graph; the
  * position lives in device memory. bm_forward with several tokens runs the same step per token, which the reference
  * establishes as equivalent to its sequence prefill (test/prefill_test.c).
@@ -22,8 +22,8 @@
 #include "bm_internal.h"
 
 typedef struct {
-    void* w;       /* int8 q[OC][C], or bf16 / fp32 [OC][C] */
-    float* scales; /* Q8 only: [OC][C/32] */
+    void* w;       /* int8 q[OC][C] (Q8), uint8 [OC][C/2] (Q4, two codes per byte), or bf16 / fp32 [OC][C] */
+    float* scales; /* Q8 and Q4: [OC][C/32] */
     void* wx;      /* tensor-core path only: bf16 [OC][parts * C], [w | w] or [w_hi | w_hi | w_lo] of the SAME weight values */
     int parts;
     int OC, C;
@@ -135,16 +135,23 @@ static int upload_matrix(bm_session_t* s, bm_mat_t* m, int wtype, const float* c
         off += (size_t)part_rows[i] * C;
     }
     int rc = 0;
-    if (wtype == BMC_W_Q8) {
+    if (wtype == BMC_W_Q8 || wtype == BMC_W_Q4) {
         /* quantised from the loaded values; a bf16 checkpoint was widened exactly, so this equals the reference's
          * bmt_quantize_q8_bf16 / _q4_bf16 for bf16 sources and bmt_quantize_q8 / _q4 for fp32 ones (src/baremetal/scheduler.c:378-392) */
         int8_t* q = (int8_t*)malloc(n);
         float* sc = (float*)malloc(n / 32 * sizeof(float));
-        quantize_blocks(s->model->quant_bits, host, q, sc, n);
-        m->w = bmc_alloc(be, n);
+        quantize_blocks(wtype == BMC_W_Q4 ? 4 : 8, host, q, sc, n);
+        size_t wbytes = n;
+        if (wtype == BMC_W_Q4) {
+            /* the reference's nibble order (src/baremetal/quant.c:44-50); C is even, so a byte never straddles two rows */
+            uint8_t* pk = (uint8_t*)q;
+            for (size_t j = 0; j < n / 2; j++) pk[j] = (uint8_t)(((uint8_t)q[2 * j] & 0x0F) | (((uint8_t)q[2 * j + 1] & 0x0F) << 4));
+            wbytes = n / 2;
+        }
+        m->w = bmc_alloc(be, wbytes);
         m->scales = (float*)bmc_alloc(be, n / 32 * sizeof(float));
         if (!m->w || !m->scales) rc = -1;
-        else { bmc_upload(be, m->w, q, n); bmc_upload(be, m->scales, sc, n / 32 * sizeof(float)); bmc_sync(be); }
+        else { bmc_upload(be, m->w, q, wbytes); bmc_upload(be, m->scales, sc, n / 32 * sizeof(float)); bmc_sync(be); }
         free(q);
         free(sc);
     } else if (wtype == BMC_W_BF16) {
@@ -166,10 +173,10 @@ static int upload_matrix(bm_session_t* s, bm_mat_t* m, int wtype, const float* c
         uint16_t* hi = (uint16_t*)malloc(n * 2);
         uint16_t* lo = (uint16_t*)malloc(n * 2);
         uint16_t* wx = (uint16_t*)malloc(n * 2 * parts);
-        if (wtype == BMC_W_Q8) {
+        if (wtype == BMC_W_Q8 || wtype == BMC_W_Q4) {
             int8_t* q = (int8_t*)malloc(n);
             float* sc = (float*)malloc(n / 32 * sizeof(float));
-            quantize_blocks(s->model->quant_bits, host, q, sc, n);
+            quantize_blocks(wtype == BMC_W_Q4 ? 4 : 8, host, q, sc, n);
             for (size_t i = 0; i < n; i++) eff[i] = (float)q[i] * sc[i / 32];
             free(q);
             free(sc);
@@ -234,7 +241,7 @@ bm_session_t* bmx_create_session_kv(bm_context_t* ctx, bm_model_t* model, int n_
     s->tc = s->tc_weights && n_sequences >= BM_TC_MIN_SEQUENCES;
     s->MS = max_positions > 0 ? max_positions : (a->max_seq_len > 0 ? a->max_seq_len : 2048);
     const int lowp = model->precision == BM_PRECISION_BF16;
-    s->wtype = (model->quant_bits == 8 || model->quant_bits == 4) ? BMC_W_Q8 : (lowp ? BMC_W_BF16 : BMC_W_F32);
+    s->wtype = model->quant_bits == 8 ? BMC_W_Q8 : model->quant_bits == 4 ? BMC_W_Q4 : (lowp ? BMC_W_BF16 : BMC_W_F32);
     s->head_type = lowp ? BMC_W_BF16 : BMC_W_F32;
     bmc_ctx_t* be = ctx->be;
     const int L = a->n_layers, D = a->dim, H = a->hidden_dim, V = a->vocab_size, HD = model->head_size;
@@ -585,7 +592,7 @@ size_t bmx_session_algorithmic_weight_bytes(bm_session_t* s) {
         const bm_mat_t* ms[4] = {&s->layers[l].qkv, &s->layers[l].o, &s->layers[l].gu, &s->layers[l].down};
         for (int i = 0; i < 4; i++) {
             const size_t e = (size_t)ms[i]->OC * ms[i]->C;
-            n += s->wtype == BMC_W_Q8 ? (s->model->quant_bits == 4 ? e / 2 : e) + e / 32 * 4 : s->wtype == BMC_W_BF16 ? e * 2 : e * 4;
+            n += s->wtype == BMC_W_Q8 ? e + e / 32 * 4 : s->wtype == BMC_W_Q4 ? e / 2 + e / 32 * 4 : s->wtype == BMC_W_BF16 ? e * 2 : e * 4;
         }
     }
     n += (size_t)s->model->arch.vocab_size * s->model->arch.dim * (s->head_type == BMC_W_BF16 ? 2 : 4);
@@ -600,7 +607,7 @@ size_t bmx_session_weight_bytes(bm_session_t* s) {
         const bm_mat_t* ms[4] = {&s->layers[l].qkv, &s->layers[l].o, &s->layers[l].gu, &s->layers[l].down};
         for (int i = 0; i < 4; i++) {
             const size_t e = (size_t)ms[i]->OC * ms[i]->C;
-            n += s->tc ? e * 2 * ms[i]->parts : s->wtype == BMC_W_Q8 ? e + e / 32 * 4 : s->wtype == BMC_W_BF16 ? e * 2 : e * 4;
+            n += s->tc ? e * 2 * ms[i]->parts : s->wtype == BMC_W_Q8 ? e + e / 32 * 4 : s->wtype == BMC_W_Q4 ? e / 2 + e / 32 * 4 : s->wtype == BMC_W_BF16 ? e * 2 : e * 4;
         }
     }
     n += (size_t)s->model->arch.vocab_size * s->model->arch.dim * (s->tc ? 2 * s->head_parts : s->head_type == BMC_W_BF16 ? 2 : 4);

@@ -73,7 +73,7 @@ int    bmx_gemm_timing_collect(bm_context_t* ctx, double* out3);
 
 /* ---- inference ----
  * Q8 / Q4 selection: the reference sets bm_model_s::quant_bits from its CLI (tools/cli.c:886); here through a call. bits = 0, 4 or 8.
- * A 4-bit session gives the reference's Q4 results but keeps its codes as int8 (1.125 bytes per weight on the device). */
+ * A 4-bit session holds two codes per byte plus one fp32 scale per 32 weights (0.625 bytes per weight), the reference's Q4 block content. */
 int    bmx_model_set_quant(bm_model_t* model, int bits);
 /* The reference's Q8 block quantiser (bmt_quantize_q8, src/baremetal/quant.c:10-29,54-60) with the int8 values and the scales
  * in two arrays: q[n], scales[n/32]. Returns the number of blocks, 0 when n is not a positive multiple of 32. */

@@ -197,10 +197,12 @@ int bmc_argmax(bmc_ctx_t* ctx, int* d_index, const float* d_logits, int V);
  *      NB independent sequences that share one position counter. Activations are fp32; the KV cache holds fp32 elements
  *      (cache_dtype BMC_F32: what the reference keeps, scheduler.c kv buffers) or, on request, bf16 (BMC_BF16, head_dim 64).
  *      Weight types: BMC_W_Q8 = int8 q[OC][C] + float scale[OC][C/32] (the values of the reference's 36-byte blocks,
- *      src/baremetal/quant.h:19-22, stored as two arrays), BMC_W_BF16, BMC_W_F32.
+ *      src/baremetal/quant.h:19-22, stored as two arrays), BMC_W_BF16, BMC_W_F32, BMC_W_Q4 = uint8 qs[OC][C/2] + float
+ *      scale[OC][C/32] (the reference's 20-byte blocks, quant.h:39-42, as two arrays: element 2j of a row in the low and 2j+1 in
+ *      the high nibble of byte j, two's-complement codes in [-8, 7]). Any other value is refused (-1).
  *      d_pos is a DEVICE int holding the position of the token being processed (so a captured step can be replayed).
  *      KV cache layout: element[L][2][NB][MS][KV]; rope table float[MS][HD/2][2]. ---- */
-enum { BMC_W_Q8 = 0, BMC_W_BF16 = 1, BMC_W_F32 = 2 };
+enum { BMC_W_Q8 = 0, BMC_W_BF16 = 1, BMC_W_F32 = 2, BMC_W_Q4 = 3 };
 int bmc_decode_gemv(bmc_ctx_t* ctx, float* d_out, int ldo, const float* d_x, int ldx, int wtype, const void* d_w, const float* d_scales,
                     const float* d_residual, int ldr, int NB, int C, int OC);
 /* The same product with a prologue folded into the operand load (single-sequence kernel, C <= 3072):

@@ -299,10 +299,24 @@ def _q8(w):
     return q.reshape(w.shape), sc.reshape(w.shape[0], -1)
 
 
-@pytest.mark.parametrize("wtype", [0, 1, 2])
+def _q4(w):
+    """Q4 codes from the oracle's quantiser, packed as the reference packs them: element 2j low, 2j+1 high nibble of byte j. The
+    quantiser never produces -8 (|w| / scale <= 7), the format holds it: a few codes are set to the extremes by hand."""
+    q = np.zeros(w.size, np.int8)
+    sc = np.zeros(w.size // 32, np.float32)
+    assert oc.load_port().orc_quantize_q4(oc.fptr(np.ascontiguousarray(w)), q.ctypes.data, oc.fptr(sc), w.size) == w.size // 32
+    q[:8] = [-8, 7, -1, 0, 1, -8, -7, 7]
+    q[-3:] = [-8, 7, -8]
+    u = q.view(np.uint8).reshape(w.shape[0], -1, 2) & 0x0F
+    packed = np.ascontiguousarray((u[:, :, 0] | (u[:, :, 1] << 4)).astype(np.uint8))
+    return q.reshape(w.shape), sc.reshape(w.shape[0], -1), packed
+
+
+@pytest.mark.parametrize("wtype", [0, 1, 2, 3])
 @pytest.mark.parametrize("NB,C,OC,prologue", [(1, 960, 1600, 0), (1, 960, 5120, 1), (2, 2560, 960, 2), (3, 576, 77, 1), (5, 384, 200, 0), (17, 1024, 130, 0)])
 def test_decode_gemv_all_weight_types(be, wtype, NB, C, OC, prologue):
-    """out = operand(x) W^T + residual, Q8 / bf16 / fp32 weights, plain / RMSNorm / SwiGLU operand, single-sequence and batched kernels."""
+    """out = operand(x) W^T + residual, Q8 / bf16 / fp32 / packed Q4 weights, plain / RMSNorm / SwiGLU operand, single-sequence and
+    batched kernels."""
     if prologue and NB >= 4:
         pytest.skip("prologues exist in the single-sequence kernel only")
     w = rndf(OC, C, scale=0.05)
@@ -319,6 +333,11 @@ def test_decode_gemv_all_weight_types(be, wtype, NB, C, OC, prologue):
         dw = be.alloc(hb.nbytes)
         assert be.lib.bmc_upload(be.ctx, dw, hb.ctypes.data, hb.nbytes) == 0
         dsc = None
+    elif wtype == 3:
+        q, sc, packed = _q4(w)
+        assert q.min() == -8 and q.max() == 7 and packed.shape == (OC, C // 2)
+        weff = q.astype(np.float32) * np.repeat(sc, 32, axis=1)
+        dw, dsc = be.put(packed), be.put(sc)
     else:
         weff, dw, dsc = w, be.put(w), None
     if prologue == 1:
